@@ -1,0 +1,329 @@
+// Control step of the partial allreduce, templated on the execution environment.
+//
+// Env must provide (all at system scope, i.e. visible to every rank):
+//   ld_acq64 / st_rel64 / ld_acq32 / st_rel32, cas64 / cas32 (return the old
+//   value), add32 (returns the old value), fence(), now_ns(), pause().
+//
+// One rank calls, per step and per channel, in this order:
+//   wait_slot_free()  -> write its gradient into publish slot (epoch % 2)
+//   ctl_step()        -> publish, elect / wait for the round, build the Plan
+//   <data phase>      -> reduce + update (participant) or apply mailbox (drain)
+//   finish()          -> completion signalling, lock release
+// Every wait is bounded by StepConfig::timeout_ns; when one runs out the step
+// returns ROLE_ABORT and sets a sticky status bit that the host reads.
+#pragma once
+#include "channel.h"
+
+#if defined(__CUDACC__)
+#define ESGD_T __device__ __forceinline__
+#else
+#define ESGD_T inline
+#endif
+
+namespace esgd {
+
+struct ChannelView {
+  ChannelCtl* ctl[kMaxRanks];
+};
+
+struct StepPolicy {
+  int32_t base_mode;       // MODE_SOLO / MODE_MAJORITY / MODE_SYNC
+  int32_t include_stale;   // sum unconsumed gradients of ranks that have not arrived
+  int64_t limiter;         // eager rounds between synchronous rounds; < 0: never force
+  uint64_t seed;           // majority initiator stream
+};
+
+ESGD_HD uint32_t bit_of(int r) { return 1u << r; }
+ESGD_HD int popc32(uint32_t x) {
+  int c = 0;
+  while (x) { x &= x - 1; ++c; }
+  return c;
+}
+
+// The publish slot for `epoch` was last used for epoch-2.  Its readers belong
+// to a round whose descriptor reached this rank before they started, so the
+// slot is free once every round visible here has completed.
+template <class E>
+ESGD_T bool wait_slot_free(ChannelCtl* me, uint64_t timeout_ns) {
+  uint64_t t0 = E::now_ns();
+  for (;;) {
+    uint64_t lr = E::ld_acq64(&me->latest_round);
+    uint64_t rd = E::ld_acq64(&me->round_done);
+    if (rd >= lr) return true;
+    if (E::now_ns() - t0 > timeout_ns) {
+      me->status |= ST_TIMEOUT_SLOT;
+      return false;
+    }
+    E::pause();
+  }
+}
+
+// Runs on the elected activator of round k.  Returns 0 or a status bit.
+template <class E>
+ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, const StepPolicy& pol,
+                                uint64_t k, bool sync_round, uint64_t t0) {
+  const int P = cfg.world, me_r = cfg.rank;
+  ChannelCtl* me = v.ctl[me_r];
+
+  // Rounds never overlap: the previous one must have completed everywhere.
+  while (E::ld_acq64(&me->round_done) + 1 < k) {
+    if (E::now_ns() - t0 > cfg.timeout_ns) return ST_TIMEOUT_DONE;
+    E::pause();
+  }
+  uint64_t consumed_prev[kMaxRanks];
+  for (int j = 0; j < P; ++j) consumed_prev[j] = 0;
+  if (k > 1) {
+    const RoundDesc* dp = &me->desc[(k - 1) % kDescRing];
+    if (dp->round != k - 1) return ST_DESC_LAPPED;
+    for (int j = 0; j < P; ++j) consumed_prev[j] = dp->consumed[j];
+  }
+
+  if (sync_round) {  // full-arrival barrier
+    for (int j = 0; j < P; ++j) {
+      while (E::ld_acq64(&me->pub_epoch[j]) < k) {
+        if (E::now_ns() - t0 > cfg.timeout_ns) return ST_TIMEOUT_ARRIVAL;
+        E::pause();
+      }
+    }
+  } else if (cfg.grace_ns > 0) {
+    // Ranks that arrive within the grace window of the first one are still fresh:
+    // without it, near-simultaneous arrivals would all but one count as absent.
+    const uint64_t tg = E::now_ns();
+    for (;;) {
+      int arrived = 0;
+      for (int j = 0; j < P; ++j) arrived += (E::ld_acq64(&me->pub_epoch[j]) >= k) ? 1 : 0;
+      if (arrived >= P) break;
+      if (E::now_ns() - tg > cfg.grace_ns) break;
+      E::pause();
+    }
+  }
+
+  // One consistent snapshot of who has what; every reducer honours it.
+  RoundDesc d;
+  d.round = k;
+  d.activator = (uint32_t)me_r;
+  d.n_fresh = d.n_contrib = 0;
+  d.fresh_mask = d.contrib_mask = d.push_mask = d.accum_mask = 0;
+  d.is_sync = sync_round ? 1u : 0u;
+  for (int j = 0; j < kMaxRanks; ++j) { d.read_epoch[j] = 0; d.consumed[j] = 0; }
+  for (int j = 0; j < P; ++j) {
+    uint64_t e = E::ld_acq64(&me->pub_epoch[j]);
+    bool fresh = (e >= k) || (j == me_r);
+    bool stale = !fresh && pol.include_stale && e > consumed_prev[j];
+    d.consumed[j] = consumed_prev[j];
+    if (fresh) { d.fresh_mask |= bit_of(j); d.n_fresh++; e = k; }
+    else d.push_mask |= bit_of(j);
+    if (fresh || stale) {
+      d.contrib_mask |= bit_of(j);
+      d.n_contrib++;
+      d.read_epoch[j] = e;
+      d.consumed[j] = e;
+    }
+  }
+
+  // Lock the mailboxes of the absent ranks on behalf of this round's pushers.
+  uint32_t locked = 0, st = 0;
+  for (int j = 0; j < P && !st; ++j) {
+    if (!(d.push_mask & bit_of(j))) continue;
+    ChannelCtl* cj = v.ctl[j];
+    while (E::cas32(&cj->mbox_lock, 0u, (uint32_t)(1 + me_r)) != 0u) {
+      if (E::now_ns() - t0 > cfg.timeout_ns) { st = ST_TIMEOUT_LOCK; break; }
+      E::pause();
+    }
+    if (st) break;
+    locked |= bit_of(j);
+    uint32_t cnt = E::ld_acq32(&cj->mbox_count);
+    if (cnt > 0) d.accum_mask |= bit_of(j);
+    E::st_rel32(&cj->mbox_count, cnt + 1);
+  }
+  if (st) {
+    for (int j = 0; j < P; ++j)
+      if (locked & bit_of(j)) {
+        ChannelCtl* cj = v.ctl[j];
+        E::st_rel32(&cj->mbox_count, E::ld_acq32(&cj->mbox_count) - 1);
+        E::st_rel32(&cj->mbox_lock, 0u);
+      }
+    return st;
+  }
+
+  // Activation = one descriptor store per peer, then the round number.
+  E::st_rel32(&me->done_count[k % kDescRing], 0u);
+  for (int j = 0; j < P; ++j) {
+    RoundDesc* dj = &v.ctl[j]->desc[k % kDescRing];
+    *dj = d;
+  }
+  E::fence();
+  for (int j = 0; j < P; ++j) E::st_rel64(&v.ctl[j]->latest_round, k);
+  me->stat_rounds_activated++;
+  return 0;
+}
+
+template <class E>
+ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPolicy& pol, Plan* plan) {
+  const int P = cfg.world, i = cfg.rank;
+  ChannelCtl* me = v.ctl[i];
+  const uint64_t k = me->local_step + 1;
+  me->local_step = k;
+  const uint64_t t0 = E::now_ns();
+
+  plan->role = ROLE_ABORT;
+  plan->n_src = plan->n_push = 0;
+  plan->part_index = 0;
+  plan->part_count = 1;
+  plan->activator = i;
+  plan->holds_own_lock = 0;
+  plan->round = k;
+  plan->scale = 1.0f;
+  plan->drain_rounds = 0.0f;
+
+  const bool sync_round = (pol.base_mode == MODE_SYNC) || limiter_is_sync(k, pol.limiter);
+  plan->is_sync = sync_round ? 1 : 0;
+  bool may_activate = true;
+  if (!sync_round && pol.base_mode == MODE_MAJORITY)
+    may_activate = (majority_initiator(pol.seed, k, P) == i);
+
+  // Publish: the gradient is already in slot (k % 2); make it visible, then the epoch.
+  E::fence();
+  for (int j = 0; j < P; ++j) E::st_rel64(&v.ctl[j]->pub_epoch[i], k);
+
+  bool tried = false;
+  uint64_t lr;
+  for (;;) {
+    lr = E::ld_acq64(&me->latest_round);
+    if (lr >= k) break;
+    if (may_activate && !tried) {
+      tried = true;
+      if (E::cas64(&v.ctl[cfg.home]->owner, k - 1, k) == k - 1) {
+        uint32_t st = activate_round<E>(v, cfg, pol, k, sync_round, t0);
+        if (st) { me->status |= st; me->stat_wait_ns += E::now_ns() - t0; return; }
+        continue;
+      }
+    }
+    if (E::now_ns() - t0 > cfg.timeout_ns) {
+      me->status |= ST_TIMEOUT_ROUND;
+      me->stat_wait_ns += E::now_ns() - t0;
+      return;
+    }
+    E::pause();
+  }
+
+  const RoundDesc* d = &me->desc[k % kDescRing];
+  const bool participant = (lr == k) && (d->round == k) && (d->fresh_mask & bit_of(i));
+  if (sync_round) me->stat_sync_rounds++;
+
+  if (participant) {
+    if (E::ld_acq32(&me->mbox_count) != 0) me->status |= ST_MBOX_NOT_EMPTY;
+    plan->role = ROLE_PARTICIPANT;
+    plan->activator = (int32_t)d->activator;
+    plan->part_count = (int32_t)d->n_fresh;
+    plan->part_index = popc32(d->fresh_mask & (bit_of(i) - 1u));
+    plan->scale = cfg.average_world == 1 ? 1.0f / (float)P
+                  : cfg.average_world == 2 ? 1.0f : 1.0f / (float)d->n_contrib;
+    for (int j = 0; j < P; ++j) {
+      if (d->contrib_mask & bit_of(j)) {
+        plan->src_rank[plan->n_src] = j;
+        plan->src_parity[plan->n_src] = (int32_t)(d->read_epoch[j] % kSlotDepth);
+        plan->n_src++;
+      }
+      if (d->push_mask & bit_of(j)) {
+        plan->push_rank[plan->n_push] = j;
+        plan->push_accum[plan->n_push] = (d->accum_mask & bit_of(j)) ? 1 : 0;
+        plan->n_push++;
+      }
+    }
+    me->stat_rounds_participated++;
+    me->stat_contrib_sum += d->n_contrib;
+    me->stat_last_round = k;
+    me->stat_last_contrib = d->n_contrib;
+  } else {
+    // Absent from round k (it ran, or is running, without this rank's fresh
+    // gradient).  Whatever this rank missed is in its mailbox once round k is done.
+    while (E::ld_acq64(&me->round_done) < k) {
+      if (E::now_ns() - t0 > cfg.timeout_ns) {
+        me->status |= ST_TIMEOUT_DONE;
+        me->stat_wait_ns += E::now_ns() - t0;
+        return;
+      }
+      E::pause();
+    }
+    while (E::cas32(&me->mbox_lock, 0u, (uint32_t)(1 + i)) != 0u) {
+      if (E::now_ns() - t0 > cfg.timeout_ns) {
+        me->status |= ST_TIMEOUT_LOCK;
+        me->stat_wait_ns += E::now_ns() - t0;
+        return;
+      }
+      E::pause();
+    }
+    uint32_t cnt = E::ld_acq32(&me->mbox_count);
+    me->stat_rounds_absent++;
+    me->stat_last_round = E::ld_acq64(&me->latest_round);
+    me->stat_last_contrib = 0;
+    if (cnt == 0) {
+      E::st_rel32(&me->mbox_lock, 0u);
+      plan->role = ROLE_IDLE;
+    } else {
+      E::st_rel32(&me->mbox_count, 0u);
+      plan->role = ROLE_DRAIN;
+      plan->holds_own_lock = 1;
+      plan->drain_rounds = (float)cnt;
+    }
+  }
+  // A published gradient that was never consumed and is now superseded is dropped
+  // (the reference overwrites its send buffer the same way).
+  if (k >= 2) {
+    const uint64_t rr = participant ? k - 1 : me->stat_last_round;
+    const RoundDesc* dl = &me->desc[rr % kDescRing];
+    if (dl->round == rr && dl->consumed[i] + 1 < k) me->stat_dropped_grads++;
+  }
+  me->stat_wait_ns += E::now_ns() - t0;
+}
+
+// Called once per rank after its data phase.
+template <class E>
+ESGD_T void finish_step(const ChannelView& v, const StepConfig& cfg, const Plan* plan) {
+  ChannelCtl* me = v.ctl[cfg.rank];
+  if (plan->role == ROLE_PARTICIPANT) {
+    E::fence();
+    ChannelCtl* act = v.ctl[plan->activator];
+    uint32_t old = E::add32(&act->done_count[plan->round % kDescRing], 1u);
+    if ((int32_t)old == plan->part_count - 1) {
+      E::fence();
+      for (int n = 0; n < plan->n_push; ++n) E::st_rel32(&v.ctl[plan->push_rank[n]]->mbox_lock, 0u);
+      for (int j = 0; j < cfg.world; ++j) E::st_rel64(&v.ctl[j]->round_done, plan->round);
+    }
+  } else if (plan->role == ROLE_DRAIN && plan->holds_own_lock) {
+    E::fence();
+    E::st_rel32(&me->mbox_lock, 0u);
+  }
+}
+
+// End of training: collect whatever is still in the mailbox (no new round).
+template <class E>
+ESGD_T void ctl_flush(const ChannelView& v, const StepConfig& cfg, Plan* plan) {
+  ChannelCtl* me = v.ctl[cfg.rank];
+  const uint64_t t0 = E::now_ns();
+  plan->role = ROLE_ABORT;
+  plan->n_src = plan->n_push = 0;
+  plan->holds_own_lock = 0;
+  plan->round = E::ld_acq64(&me->latest_round);
+  while (E::ld_acq64(&me->round_done) < plan->round) {
+    if (E::now_ns() - t0 > cfg.timeout_ns) { me->status |= ST_TIMEOUT_DONE; return; }
+    E::pause();
+  }
+  while (E::cas32(&me->mbox_lock, 0u, (uint32_t)(1 + cfg.rank)) != 0u) {
+    if (E::now_ns() - t0 > cfg.timeout_ns) { me->status |= ST_TIMEOUT_LOCK; return; }
+    E::pause();
+  }
+  uint32_t cnt = E::ld_acq32(&me->mbox_count);
+  if (cnt == 0) {
+    E::st_rel32(&me->mbox_lock, 0u);
+    plan->role = ROLE_IDLE;
+  } else {
+    E::st_rel32(&me->mbox_count, 0u);
+    plan->role = ROLE_DRAIN;
+    plan->holds_own_lock = 1;
+    plan->drain_rounds = (float)cnt;
+  }
+}
+
+}  // namespace esgd

@@ -1,0 +1,201 @@
+"""NVLink backend of the partial allreduce: peer-mapped arenas + sm_100a kernels.
+
+Each rank allocates one arena per channel with ``cudaMalloc``
+(``[control block | publish slot 0 | publish slot 1 | fp32 mailbox]``), exports
+it with a CUDA IPC handle and maps every peer's arena, so the kernels read and
+write the other GPUs' memory directly over NVLink 5 / NVSwitch.  This replaces
+the reference's buffers, pools and MPI transport (fflib2 src/ffbuffer.c,
+src/ffstorage.c, src/components/mpi/*) and its progress thread: whoever takes
+part in a round does the reduction itself with one-sided peer loads, so a rank
+that has not arrived needs no agent running on its behalf.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional
+
+import torch
+
+from . import _native as N
+
+_MODES = {"solo": N.MODE_SOLO, "majority": N.MODE_MAJORITY, "sync": N.MODE_SYNC}
+_AVG = {"contributors": N.AVG_CONTRIBUTORS, "world": N.AVG_WORLD, "sum": N.AVG_SUM}
+HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
+
+
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
+
+
+class ArenaLayout:
+    def __init__(self, count: int, slot_dtype: torch.dtype):
+        if count % 8:
+            raise ValueError("channel element count must be a multiple of 8")
+        esz = 2 if slot_dtype == torch.bfloat16 else 4
+        self.ctl = 0
+        self.slot0 = _align(int(N.cuda().esgd_dev_ctl_bytes()))
+        self.slot1 = self.slot0 + _align(count * esz)
+        self.mbox = self.slot1 + _align(count * esz)
+        self.total = self.mbox + _align(count * 4)
+
+
+class Arena:
+    """One cudaMalloc'd, zeroed, IPC-exportable allocation on the current device."""
+
+    def __init__(self, nbytes: int, export: bool = True):
+        self.ptr = C.c_void_p()
+        self.handle = (C.c_ubyte * 64)()
+        N.check_cuda(N.cuda().esgd_arena_alloc(nbytes, C.byref(self.ptr), self.handle if export else None),
+                     "arena allocation")
+        self.nbytes = nbytes
+        self.base = int(self.ptr.value)
+
+    def free(self):
+        if self.ptr:
+            N.cuda().esgd_arena_free(self.ptr)
+            self.ptr = C.c_void_p()
+
+
+def open_peer(handle_bytes: bytes) -> int:
+    buf = (C.c_ubyte * 64).from_buffer_copy(handle_bytes)
+    ptr = C.c_void_p()
+    N.check_cuda(N.cuda().esgd_arena_open(buf, C.byref(ptr)), "opening a peer arena (CUDA IPC)")
+    return int(ptr.value)
+
+
+class NvlinkChannel:
+    """One persistent partial-allreduce channel of ``count`` elements on this GPU.
+
+    ``grad_in`` is the flat gradient the backward pass writes.  With ``w32``/
+    ``mom`` (and optionally ``w16``) the reduction is fused with the momentum-SGD
+    update; otherwise the averaged gradient is written to ``out``.
+    """
+
+    def __init__(self, count: int, rank: int, world: int, bases: List[int], device: torch.device,
+                 grad_in: torch.Tensor, slot_dtype: torch.dtype = torch.bfloat16, mode: str = "solo",
+                 limiter: int = 32, seed: int = 6545343, average: str = "contributors",
+                 include_stale: bool = True, timeout_s: float = 20.0, grace_us: float = 50.0, home: int = 0,
+                 w32: Optional[torch.Tensor] = None, mom: Optional[torch.Tensor] = None,
+                 w16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 hyper: Optional[torch.Tensor] = None, max_blocks: int = 592):
+        self.lib = N.cuda()
+        self.count, self.rank, self.world, self.device = count, rank, world, device
+        self.max_blocks = max_blocks
+        self.layout = ArenaLayout(count, slot_dtype)
+        self.bases = list(bases)
+        self.grad_in, self.w32, self.mom, self.w16, self.out = grad_in, w32, mom, w16, out
+        if hyper is None:
+            hyper = torch.zeros(HYPER_LEN, dtype=torch.float32, device=device)
+            hyper[4] = 1.0
+        self.hyper = hyper
+        assert grad_in.numel() == count and grad_in.is_contiguous()
+        self._dch = torch.zeros(int(self.lib.esgd_dev_channel_bytes()), dtype=torch.uint8, device=device)
+        d = N.ChannelDesc()
+        L = self.layout
+        for j in range(world):
+            d.ctl[j] = bases[j] + L.ctl
+            d.slot0[j] = bases[j] + L.slot0
+            d.slot1[j] = bases[j] + L.slot1
+            d.mbox[j] = bases[j] + L.mbox
+        d.rank, d.world, d.base_mode = rank, world, _MODES[mode]
+        d.include_stale, d.average, d.home = int(include_stale), _AVG[average], home
+        d.slot_bf16 = int(slot_dtype == torch.bfloat16)
+        d.grad_in_bf16 = int(grad_in.dtype == torch.bfloat16)
+        d.limiter, d.seed = limiter, seed
+        d.timeout_ns, d.grace_ns, d.count = int(timeout_s * 1e9), int(grace_us * 1e3), count
+        d.grad_in = grad_in.data_ptr()
+        d.w32 = w32.data_ptr() if w32 is not None else None
+        d.mom = mom.data_ptr() if mom is not None else None
+        d.w16 = w16.data_ptr() if w16 is not None else None
+        d.out = out.data_ptr() if out is not None else None
+        d.out_bf16 = int(out is not None and out.dtype == torch.bfloat16)
+        d.hyper = self.hyper.data_ptr()
+        self._desc = d
+        stream = torch.cuda.current_stream(device)
+        N.check_cuda(self.lib.esgd_channel_configure(self._dch.data_ptr(), C.byref(d), stream.cuda_stream),
+                     "channel configuration")
+        self._ctl_host = (C.c_ubyte * int(self.lib.esgd_dev_ctl_bytes()))()
+
+    @property
+    def dev_ptr(self) -> int:
+        return self._dch.data_ptr()
+
+    def step(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Enqueue pack + control + reduce/update for one step on ``stream``."""
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
+                     "partial allreduce launch")
+
+    def flush(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_channel_flush(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
+                     "partial allreduce flush launch")
+
+    def stats(self) -> dict:
+        """Synchronising read of this rank's counters and sticky status word."""
+        s = torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_memcpy_d2h(self._ctl_host, C.c_void_p(self.bases[self.rank] + self.layout.ctl),
+                                              len(self._ctl_host), s.cuda_stream), "reading channel counters")
+        raw = (C.c_uint64 * 16)()
+        N.host().esgd_ctl_stats(self._ctl_host, raw)
+        return N.parse_stats(raw)
+
+    def check(self, where: str = "") -> None:
+        st = self.stats()["status"]
+        if st:
+            raise N.ChannelError(st, where or "gpu rank %d" % self.rank)
+
+
+def create_arenas(count: int, slot_dtype: torch.dtype, rank: int, world: int,
+                  exchange: Optional[Callable] = None):
+    """Allocate this rank's arena and map the peers'.  Returns (own Arena, bases)."""
+    layout = ArenaLayout(count, slot_dtype)
+    arena = Arena(layout.total, export=world > 1)
+    if world == 1:
+        return arena, [arena.base]
+    handles = exchange(bytes(arena.handle))
+    bases = [arena.base if r == rank else open_peer(h) for r, h in enumerate(handles)]
+    exchange("mapped")
+    return arena, bases
+
+
+class EmulatedWorld:
+    """``world`` ranks of one channel on ONE GPU, stepped by a single cooperative
+    launch (one block per rank).  Exercises the device protocol, the peer-pointer
+    data path and the mailbox on a single-GPU box."""
+
+    def __init__(self, world: int, count: int, device: torch.device, slot_dtype=torch.bfloat16,
+                 grad_dtype=torch.float32, fused: bool = False, **kw):
+        self.world, self.count, self.device = world, count, device
+        layout = ArenaLayout(count, slot_dtype)
+        self.arenas = [Arena(layout.total, export=False) for _ in range(world)]
+        bases = [a.base for a in self.arenas]
+        self.grads = [torch.zeros(count, dtype=grad_dtype, device=device) for _ in range(world)]
+        self.outs = [torch.zeros(count, dtype=torch.float32, device=device) for _ in range(world)]
+        self.w32 = [torch.zeros(count, dtype=torch.float32, device=device) for _ in range(world)] if fused else None
+        self.mom = [torch.zeros(count, dtype=torch.float32, device=device) for _ in range(world)] if fused else None
+        self.w16 = [torch.zeros(count, dtype=torch.bfloat16, device=device) for _ in range(world)] if fused else None
+        self.hyper = torch.zeros(HYPER_LEN, dtype=torch.float32, device=device)
+        self.hyper[4] = 1.0
+        self.channels = []
+        for r in range(world):
+            self.channels.append(NvlinkChannel(
+                count, r, world, bases, device, self.grads[r], slot_dtype=slot_dtype,
+                w32=self.w32[r] if fused else None, mom=self.mom[r] if fused else None,
+                w16=self.w16[r] if fused else None, out=None if fused else self.outs[r], hyper=self.hyper, **kw))
+        self._chans = torch.tensor([c.dev_ptr for c in self.channels], dtype=torch.int64, device=device)
+        self._delays = torch.zeros(world, dtype=torch.int64, device=device)
+
+    def step(self, delays_us=None, flush: bool = False) -> None:
+        if delays_us is not None:
+            self._delays.copy_(torch.tensor([int(d * 1000) for d in delays_us], dtype=torch.int64))
+        else:
+            self._delays.zero_()
+        s = torch.cuda.current_stream(self.device)
+        N.check_cuda(N.cuda().esgd_emulated_step(self._chans.data_ptr(), self._delays.data_ptr(), self.world,
+                                                 int(flush), s.cuda_stream), "emulated multi-rank step")
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        for a in self.arenas:
+            a.free()

@@ -1,0 +1,160 @@
+"""Partial-allreduce protocol on the CPU backend, ranks as threads of one process.
+
+Mirrors the reference's evaluation programs with assertable invariants
+(fflib2 evaluation/solo_allreduce_correctness.c, rand_allreduce_correctness.c,
+allreduce.c, limiter.c, solo_allreduce_multiple.c): closed-form sums for the
+synchronous mode at 1..8 ranks including non-powers of two, and, for the eager
+modes under random delays, (a) untorn results, (b) identical accumulated
+updates on every rank, (c) the limiter's sync pattern.
+"""
+import random
+import threading
+import time
+
+import numpy as np
+import pytest
+
+from eagersgd_b200.parallel import _native as N
+from eagersgd_b200.parallel.cpu_channel import CpuChannel, LocalSegments
+
+
+def _run(world, mode, limiter, steps, count=512, dtype=np.float64, delay=0.002, seed=0, average="sum",
+         include_stale=True, slow_rank=None):
+    segs = LocalSegments(world, count, dtype)
+    applied = [np.zeros(count, dtype=np.float64) for _ in range(world)]
+    infos = [[] for _ in range(world)]
+    errors = []
+
+    def worker(r):
+        try:
+            ch = CpuChannel(segs.bases, r, world, count, dtype, mode=mode, limiter=limiter, seed=99,
+                            average=average, include_stale=include_stale, timeout_s=30)
+            rng = random.Random(seed * 131 + r)
+            for k in range(1, steps + 1):
+                if delay and (rng.random() < 0.3 or r == slow_rank):
+                    time.sleep(rng.random() * delay)
+                g = np.full(count, (r + 1) * 1000 + k, dtype=dtype)
+                out, info = ch.step(g)
+                assert np.all(out == out[0]), "torn result"
+                applied[r] += out
+                infos[r].append((info.role, info.round, info.n_contrib, info.n_fresh, info.is_sync))
+        except Exception as e:  # noqa
+            errors.append((r, repr(e)))
+
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errors, errors
+    stats = []
+    for r in range(world):
+        ch = CpuChannel(segs.bases, r, world, count, dtype, mode=mode, limiter=limiter, seed=99, average=average,
+                        timeout_s=10)
+        out, info = ch.flush()
+        applied[r] += out
+        stats.append(ch.stats())
+    return applied, infos, stats
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 5, 8])
+def test_sync_closed_form(world):
+    steps = 25
+    applied, infos, _ = _run(world, "sync", -1, steps, dtype=np.int64, delay=0.001)
+    total = sum((r + 1) * 1000 + k for r in range(world) for k in range(1, steps + 1))
+    for r in range(world):
+        assert applied[r][0] == total
+        assert all(i[0] == N.ROLE_PARTICIPANT and i[2] == world for i in infos[r])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32, np.int64])
+def test_sync_datatypes(dtype):
+    applied, _, _ = _run(3, "sync", -1, 5, dtype=dtype, delay=0)
+    total = sum((r + 1) * 1000 + k for r in range(3) for k in range(1, 6))
+    assert applied[0][0] == total
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_eager_replicas_agree(mode, world):
+    """Every rank ends with the same sum of round results: nothing a round produced is lost."""
+    applied, infos, stats = _run(world, mode, -1, 60)
+    for r in range(1, world):
+        assert np.array_equal(applied[r], applied[0])
+    published = sum((r + 1) * 1000 + k for r in range(world) for k in range(1, 61))
+    assert 0 < applied[0][0] <= published  # a superseded gradient may be dropped, never duplicated
+    assert all(s["status"] == 0 for s in stats)
+
+
+def test_limiter_pattern_and_exactness():
+    """limiter=3: steps 4, 8, 12 ... are synchronous with every rank contributing."""
+    world, steps = 4, 24
+    applied, infos, stats = _run(world, "solo", 3, steps)
+    for r in range(world):
+        for k, info in enumerate(infos[r], start=1):
+            if k % 4 == 0:
+                assert info[4] == 1 and info[0] == N.ROLE_PARTICIPANT and info[2] == world and info[1] == k
+            else:
+                assert info[4] == 0
+        assert stats[r]["sync_rounds"] == steps // 4
+    for r in range(1, world):
+        assert np.array_equal(applied[r], applied[0])
+
+
+def test_limiter_zero_is_synchronous():
+    applied, _, _ = _run(3, "solo", 0, 10, dtype=np.int64)
+    assert applied[0][0] == sum((r + 1) * 1000 + k for r in range(3) for k in range(1, 11))
+
+
+def test_solo_does_not_wait_for_a_slow_rank():
+    """A constantly slow rank must not hold the others back (solo_allreduce_multiple.c)."""
+    world, steps, count = 3, 12, 64
+    segs = LocalSegments(world, count, np.float32)
+    t_done = [0.0] * world
+
+    def worker(r):
+        ch = CpuChannel(segs.bases, r, world, count, np.float32, mode="solo", limiter=-1, timeout_s=30)
+        for k in range(steps):
+            if r == 2:
+                time.sleep(0.03)
+            ch.step(np.ones(count, dtype=np.float32))
+        t_done[r] = time.time()
+
+    t0 = time.time()
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert min(t_done[0], t_done[1]) - t0 < 0.5 * (t_done[2] - t0)
+
+
+def test_majority_initiator_stream_is_shared():
+    lib = N.host()
+    seq = [lib.esgd_majority_initiator(6545343, k, 8) for k in range(1, 200)]
+    assert set(seq) == set(range(8))
+    assert seq == [lib.esgd_majority_initiator(6545343, k, 8) for k in range(1, 200)]
+
+
+def test_averaging_modes():
+    for average, expect in (("world", lambda s, n, w: s / w), ("contributors", lambda s, n, w: s / n)):
+        world, count = 4, 16
+        segs = LocalSegments(world, count, np.float32)
+        outs = [None] * world
+
+        def worker(r):
+            ch = CpuChannel(segs.bases, r, world, count, np.float32, mode="sync", limiter=-1, average=average)
+            outs[r], _ = ch.step(np.full(count, r + 1.0, dtype=np.float32))
+
+        th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+        [t.start() for t in th]
+        [t.join() for t in th]
+        for r in range(world):
+            assert np.allclose(outs[r], 10.0 / 4)
+
+
+def test_dead_rank_times_out_with_status():
+    """Failure detection on the host: a rank that never joins a synchronous round
+    makes the others' bounded wait run out with an error status."""
+    world, count = 2, 16
+    segs = LocalSegments(world, count, np.float32)
+    ch = CpuChannel(segs.bases, 0, world, count, np.float32, mode="sync", limiter=-1, timeout_s=0.3)
+    with pytest.raises(N.ChannelError) as e:
+        ch.step(np.ones(count, dtype=np.float32))
+    assert e.value.status & 2
