@@ -1,0 +1,241 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-50 v1.5 training throughput (images/s) under seeded,
+injected load imbalance, bf16 compute with fp32 master weights, batch 256 per GPU,
+solo-allreduce eager-SGD with ~25 MB gradient buckets.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+Rank 0 prints one JSON line.  ``--impl ddp`` runs the synchronous PyTorch/NCCL
+data-parallel baseline on the same model; ``--impl reference`` reports whether the
+unmodified reference can run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp"])
+    ap.add_argument("--mode", default="solo", choices=["solo", "majority", "sync"])
+    ap.add_argument("--model", default="resnet50", choices=["resnet50", "resnet32"])
+    ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: 256 / 128)")
+    ap.add_argument("--limiter", type=int, default=32)
+    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--imbalance", default="auto", choices=["auto", "none"],
+                    help="auto: each step 2 random ranks are delayed by Exp(0.5 x step time) when N > 1")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """The reference is TensorFlow 1.x + Horovod + MPI (fflib2 links libmpi, the custom op
+    links tensorflow_framework); none of those exist in this image and nothing can be fetched."""
+    why = None
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    try:
+        import tensorflow  # noqa: F401
+    except Exception:
+        why = "reference needs TensorFlow 1.x, Horovod, mpi4py and an MPI library; none is installed and there is no network"
+    if why is None and not os.path.isdir(ref):
+        why = "baseline/_ref is absent: the reference tree has no installable python project at its root"
+    if why is None:
+        why = "reference run loop requires mpirun with MPI_THREAD_MULTIPLE; no MPI launcher in this image"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import eagersgd_b200 as es
+    from eagersgd_b200.models.resnet import cifar_resnet, imagenet_resnet
+    from eagersgd_b200.parallel import _native as N
+    from eagersgd_b200.train.step import TrainStep
+
+    group = es.init()
+    rank, world, dev = group.rank, group.world, group.device
+    assert world == args.gpus, "launch with torchrun --nproc-per-node %d (WORLD_SIZE=%d)" % (args.gpus, world)
+    torch.backends.cudnn.benchmark = True
+    torch.manual_seed(1234)  # identical replicas through a shared seed
+    if args.model == "resnet50":
+        batch, res, classes = args.batch or 256, 224, 1000
+        model = imagenet_resnet(50, 1, classes)
+        name = "ResNet-50 v1.5"
+    else:
+        batch, res, classes = args.batch or 128, 32, 10
+        model = cifar_resnet(32, 1, classes)
+        name = "ResNet-32 (CIFAR)"
+    step = TrainStep(model, group, impl=args.impl, mode=args.mode, limiter=args.limiter, bucket_mb=args.bucket_mb,
+                     lr=0.01, momentum=0.9, weight_decay=1e-4)
+
+    # synthetic data of the named shape, in pinned host memory (3 distinct batches)
+    g = torch.Generator().manual_seed(100 + rank)
+    host_batches = []
+    for _ in range(3):
+        x = torch.randn(batch, 3, res, res, generator=g).to(torch.bfloat16)
+        x = x.contiguous(memory_format=torch.channels_last).pin_memory()
+        y = torch.randint(0, classes, (batch,), generator=g).pin_memory()
+        host_batches.append((x, y))
+    dev_batches = [(x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)) for x, y in host_batches]
+    torch.cuda.synchronize()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        group.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (untimed), also measures the undisturbed step time ----
+    for i in range(max(args.warmup, 3)):
+        if i == max(args.warmup, 3) - 2:
+            sync_all()
+            t_w = time.perf_counter()
+        step.run_device(*dev_batches[i % 3])
+    torch.cuda.synchronize()
+    base_step_s = (time.perf_counter() - t_w) / 2.0
+    bs = torch.tensor([base_step_s], device=dev)
+    if world > 1:
+        dist.all_reduce(bs, op=dist.ReduceOp.MAX)
+    base_step_s = float(bs.item())
+
+    inject = args.imbalance == "auto" and world > 1
+    delay_rng = random.Random(4242)  # same stream on every rank
+
+    def delays_for_step():
+        if not inject:
+            return 0.0
+        d = 0.0
+        for victim in (delay_rng.randrange(world), delay_rng.randrange(world)):
+            e = delay_rng.expovariate(1.0 / (0.5 * base_step_s))
+            if victim == rank:
+                d += e
+        return min(d, 5.0 * base_step_s)
+
+    def timed(fn, batches):
+        sampler = ClockSampler(dev.index)
+        launches0 = N.launch_count()
+        sync_all()
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        last = None
+        for i in range(args.steps):
+            d = delays_for_step()
+            if d > 0:
+                step.inject_delay(d)
+            last = fn(*batches[i % 3])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        group.barrier()
+        clocks = sampler.stop()
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks, N.launch_count() - launches0, last
+
+    ms_dev, clocks, launches, _ = timed(step.run_device, dev_batches)
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e, _, _, last_loss = timed(step.run_host, host_batches)
+        e2e = {"value": world * batch * args.steps / (ms_e2e / 1e3), "unit": "images/s",
+               "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": host_batches[0][0].numel() * 2 + host_batches[0][1].numel() * 8,
+               "d2h_bytes_per_step": 4, "last_loss": last_loss}
+    stats = step.stats()
+    step.close()
+
+    if rank == 0:
+        out = {
+            "metric": "train_images_per_sec_under_injected_imbalance", "impl": args.impl,
+            "value": world * batch * args.steps / (ms_dev / 1e3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic N(0,1) images, uniform labels, random-init weights",
+            "config": {"model": name, "global_batch": batch * world, "per_gpu_batch": batch, "seq_len": None,
+                       "image": [res, res, 3], "classes": classes, "parallelism": "dp%d" % world,
+                       "collective": args.mode + "-allreduce" if args.impl == "ours" else "nccl-allreduce",
+                       "bucket_mb": args.bucket_mb, "limiter": args.limiter,
+                       "optimizer": "momentum SGD 0.9, wd 1e-4, fp32 master weights",
+                       "imbalance": ("2 random ranks/step delayed by Exp(mean 0.5 x %.1f ms)" % (base_step_s * 1e3))
+                       if inject else "none (single rank)" if world == 1 else "none",
+                       "l2": "per-step working set (activations + 51 MB gradients) exceeds the 126 MB L2"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "eager_stats": stats,
+        }
+        print(json.dumps(out))
+    es.finalize()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -15,6 +15,9 @@
 #include <stdio.h>
 #include <string.h>
 #include "partial_allreduce.cuh"
+#include "launch_count.cuh"
+
+namespace esgd { std::atomic<uint64_t> g_launches{0}; }
 
 using namespace esgd;
 
@@ -162,6 +165,7 @@ int esgd_channel_step(void* dch, uint64_t count, int max_blocks, void* stream) {
   pack_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
   ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch);
   data_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
+  count_launch(3);
   return (int)cudaGetLastError();
 }
 
@@ -170,6 +174,7 @@ int esgd_channel_flush(void* dch, uint64_t count, int max_blocks, void* stream) 
   int g = grid_for(count, max_blocks);
   flush_ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch);
   data_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
+  count_launch(2);
   return (int)cudaGetLastError();
 }
 
@@ -178,11 +183,13 @@ int esgd_emulated_step(void* chans, void* delay_ns, int world, int flush, void* 
   void* args[] = {&chans, &delay_ns, &flush};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)emulated_step_kernel, dim3(world), dim3(256), args, 0,
                                               (cudaStream_t)stream);
+  count_launch();
   return (int)e;
 }
 
 int esgd_spin(uint64_t ns, void* stream) {
   spin_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ns);
+  count_launch();
   return (int)cudaGetLastError();
 }
 
@@ -227,6 +234,8 @@ int esgd_memcpy_d2h(void* dst, const void* src, uint64_t bytes, void* stream) {
   if (e != cudaSuccess) return (int)e;
   return (int)cudaStreamSynchronize((cudaStream_t)stream);
 }
+
+uint64_t esgd_launch_count(void) { return g_launches.load(); }
 
 const char* esgd_cuda_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 

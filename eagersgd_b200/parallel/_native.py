@@ -106,6 +106,7 @@ def cuda():
         lib.esgd_arena_free.argtypes = [C.c_void_p]
         lib.esgd_enable_peer.argtypes = [C.c_int]
         lib.esgd_memcpy_d2h.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
+        lib.esgd_launch_count.restype = C.c_uint64
         lib.esgd_cuda_error_string.restype = C.c_char_p
         lib.esgd_cuda_error_string.argtypes = [C.c_int]
         _cuda = lib
@@ -120,3 +121,8 @@ def check_cuda(code: int, what: str) -> None:
 
 def parse_stats(raw) -> dict:
     return {n: int(raw[i]) for i, n in enumerate(STAT_NAMES)}
+
+
+def launch_count() -> int:
+    """Kernels launched so far by the CUDA library of this package."""
+    return int(cuda().esgd_launch_count())

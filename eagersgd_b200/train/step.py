@@ -1,0 +1,106 @@
+"""One training step of an image classifier: the call a user of the framework makes.
+
+``TrainStep`` prepares the model for B200 (NHWC activations, bf16 weights for
+convolutions and dense layers with fp32 master copies, fp32 batch-norm), wraps
+momentum SGD in one of the eager-SGD optimizers and exposes
+
+* ``run_device(x, y)``: forward, backward, partial allreduce + fused update,
+  inputs already on the GPU, no host synchronisation;
+* ``run_host(x_pinned, y_pinned)``: the same, end to end — host-to-device copy of
+  the batch from pinned memory first, device-to-host read of the loss last.
+
+It stands where the reference's ``resnet_model_fn`` builds loss, optimizer wrap and
+train op (official/resnet/resnet_run_loop_solo_imagenet_300.py:220-456).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..optim.eager import MajorityAllreduceOptimizer, SoloAllreduceOptimizer, SyncAllreduceOptimizer
+from ..parallel import _native as N
+from ..parallel.group import Group
+
+
+def prepare_model(model: nn.Module, device: torch.device, compute_dtype=torch.bfloat16) -> nn.Module:
+    """NHWC, low-precision conv/dense weights, fp32 normalisation layers."""
+    model = model.to(device)
+    if device.type == "cuda":
+        model = model.to(memory_format=torch.channels_last)
+        for m in model.modules():
+            if isinstance(m, (nn.Conv2d, nn.Linear, nn.LSTM)):
+                m.to(compute_dtype)
+    return model
+
+
+class TrainStep:
+    def __init__(self, model: nn.Module, group: Group, impl: str = "ours", mode: str = "solo", limiter: int = 32,
+                 bucket_mb: float = 25.0, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 1e-4,
+                 compute_dtype=torch.bfloat16, loss_fn=None):
+        self.group, self.impl, self.device = group, impl, group.device
+        self.compute_dtype = compute_dtype if self.device.type == "cuda" else torch.float32
+        self.loss_fn = loss_fn or F.cross_entropy
+        if impl == "ddp":
+            self.model = model.to(self.device)
+            if self.device.type == "cuda":
+                self.model = self.model.to(memory_format=torch.channels_last)
+            self.net = self.model
+            if group.world > 1:
+                from torch.nn.parallel import DistributedDataParallel as DDP
+                self.net = DDP(self.model, device_ids=[self.device.index] if self.device.type == "cuda" else None,
+                               bucket_cap_mb=bucket_mb, gradient_as_bucket_view=True)
+            self.opt = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
+            self.autocast = self.device.type == "cuda"
+        else:
+            self.model = prepare_model(model, self.device, self.compute_dtype)
+            self.net = self.model
+            inner = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
+            cls = {"solo": SoloAllreduceOptimizer, "majority": MajorityAllreduceOptimizer,
+                   "sync": SyncAllreduceOptimizer}[mode]
+            kw = dict(bucket_mb=bucket_mb)
+            if mode != "sync":
+                kw["limiter"] = limiter
+            self.opt = cls(inner, group, **kw)
+            self.autocast = False
+        self._xbuf = self._ybuf = None
+
+    def run_device(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        self.opt.zero_grad()
+        if self.autocast:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = self.net(x)
+        else:
+            logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
+                              else x.to(self.compute_dtype))
+        loss = self.loss_fn(logits.float(), y)
+        loss.backward()
+        self.opt.step()
+        return loss.detach()
+
+    def run_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> float:
+        """End to end: pinned host batch in, python float loss out."""
+        if self._xbuf is None or self._xbuf.shape != x_host.shape:
+            self._xbuf = torch.empty_like(x_host, device=self.device)
+            self._ybuf = torch.empty_like(y_host, device=self.device)
+        self._xbuf.copy_(x_host, non_blocking=True)
+        self._ybuf.copy_(y_host, non_blocking=True)
+        return float(self.run_device(self._xbuf, self._ybuf).item())
+
+    def inject_delay(self, seconds: float) -> None:
+        """Seeded load imbalance: hold this rank's compute stream (GPU) or sleep (CPU)."""
+        if self.device.type == "cuda":
+            N.check_cuda(N.cuda().esgd_spin(int(seconds * 1e9), torch.cuda.current_stream(self.device).cuda_stream),
+                         "delay injection")
+        else:
+            import time
+            time.sleep(seconds)
+
+    def stats(self) -> Optional[dict]:
+        return self.opt.stats() if hasattr(self.opt, "stats") else None
+
+    def close(self) -> None:
+        if hasattr(self.opt, "close"):
+            self.opt.close()

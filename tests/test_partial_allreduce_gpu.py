@@ -1,0 +1,198 @@
+"""NVLink partial-allreduce kernels on one GPU.
+
+Multi-rank behaviour is exercised by ``EmulatedWorld``: all ranks of a channel
+live on one device and are stepped by a single cooperative launch (one block per
+rank), because separate launches that wait on one another are not guaranteed to
+run concurrently on one GPU.  Oracles: closed-form sums (fflib2
+evaluation/allreduce.c:34-38) and a plain PyTorch fp32 momentum SGD.
+"""
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("slot_dtype", [torch.float32, torch.bfloat16])
+def test_sync_closed_form(world, slot_dtype):
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    count = 4096 + 64
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=slot_dtype, mode="sync", limiter=-1, average="sum",
+                      timeout_s=2.0)
+    try:
+        for k in range(1, 6):
+            for r in range(world):
+                w.grads[r].fill_(float(r + 1 + k))
+            w.step()
+            torch.cuda.synchronize()
+            expect = float(sum(r + 1 + k for r in range(world)))
+            for r in range(world):
+                assert torch.all(w.outs[r] == expect), (world, k, r, w.outs[r][:4])
+        for c in w.channels:
+            st = c.stats()
+            assert st["status"] == 0 and st["participated"] == 5 and st["local_step"] == 5
+    finally:
+        w.close()
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_eager_modes_replicas_agree(mode, world):
+    """Random late arrivals: results are never torn and all ranks accumulate the same total."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    count = 2048
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode=mode, limiter=5, average="sum",
+                      timeout_s=2.0, grace_us=0.0)
+    rng = random.Random(world * 7 + len(mode))
+    applied = [torch.zeros(count, dtype=torch.float64, device=_dev()) for _ in range(world)]
+    try:
+        steps = 30
+        for k in range(1, steps + 1):
+            for r in range(world):
+                w.grads[r].fill_(float((r + 1) * 100 + k))
+            delays = [rng.choice([0, 0, 20, 200]) for _ in range(world)]
+            w.step(delays_us=delays)
+            torch.cuda.synchronize()
+            for r in range(world):
+                o = w.outs[r]
+                assert torch.all(o == o[0]), "torn result"
+                applied[r] += o.double()
+        w.step(flush=True)
+        torch.cuda.synchronize()
+        for r in range(world):
+            applied[r] += w.outs[r].double()
+        for r in range(1, world):
+            assert torch.equal(applied[r], applied[0])
+        published = sum((r + 1) * 100 + k for r in range(world) for k in range(1, steps + 1))
+        assert 0 < applied[0][0].item() <= published
+        sts = [c.stats() for c in w.channels]
+        assert all(s["status"] == 0 for s in sts)
+        assert all(s["sync_rounds"] == steps // 6 for s in sts)
+    finally:
+        w.close()
+
+
+def test_contributor_average_and_stale_flag():
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    world, count = 4, 1024
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode="sync", limiter=-1,
+                      average="contributors", timeout_s=2.0)
+    try:
+        for r in range(world):
+            w.grads[r].fill_(float(r + 1))
+        w.step()
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.allclose(w.outs[r], torch.full_like(w.outs[r], 2.5))
+    finally:
+        w.close()
+
+
+@pytest.mark.parametrize("param_dtype", [torch.float32, torch.bfloat16])
+def test_fused_momentum_sgd_matches_torch(param_dtype):
+    """world=1 channel with the fused update vs torch.optim.SGD on fp32 master weights."""
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas, HYPER_LEN
+    dev = _dev()
+    count = 8192
+    torch.manual_seed(0)
+    w0 = torch.randn(count, device=dev)
+    slot_dtype = param_dtype
+    arena, bases = create_arenas(count, slot_dtype, 0, 1)
+    grad = torch.zeros(count, dtype=param_dtype, device=dev)
+    w32, mom = w0.clone(), torch.zeros(count, device=dev)
+    w16 = w0.to(torch.bfloat16) if param_dtype == torch.bfloat16 else None
+    hyper = torch.tensor([0.1, 0.9, 1e-2, 0.0, 1.0, 0, 0, 0], dtype=torch.float32, device=dev)
+    ch = NvlinkChannel(count, 0, 1, bases, dev, grad, slot_dtype=slot_dtype, mode="solo", limiter=3, w32=w32,
+                       mom=mom, w16=w16, hyper=hyper, timeout_s=2.0)
+    ref = torch.nn.Parameter(w0.clone())
+    opt = torch.optim.SGD([ref], lr=0.1, momentum=0.9, weight_decay=1e-2)
+    for k in range(5):
+        g = torch.randn(count, device=dev)
+        grad.copy_(g)
+        ref.grad = grad.float().clone()
+        opt.step()
+        ch.step()
+        torch.cuda.synchronize()
+        assert torch.allclose(w32, ref.detach(), rtol=1e-5, atol=1e-6), k
+        if w16 is not None:
+            assert torch.equal(w16, w32.to(torch.bfloat16))
+    assert ch.stats()["status"] == 0
+    arena.free()
+
+
+def test_bounded_wait_reports_status_and_context_survives():
+    """A synchronous round whose second rank never publishes: the kernel's wait runs
+    out after ~0.3 s, the status word says so, and the CUDA context stays usable."""
+    from eagersgd_b200.parallel.nvlink_channel import Arena, ArenaLayout, NvlinkChannel
+    dev = _dev()
+    count = 1024
+    layout = ArenaLayout(count, torch.float32)
+    arenas = [Arena(layout.total, export=False) for _ in range(2)]
+    grad = torch.ones(count, device=dev)
+    out = torch.zeros(count, device=dev)
+    ch = NvlinkChannel(count, 0, 2, [a.base for a in arenas], dev, grad, slot_dtype=torch.float32, mode="sync",
+                       limiter=-1, out=out, timeout_s=0.3)
+    ch.step()
+    torch.cuda.synchronize()
+    st = ch.stats()
+    assert st["status"] & 2, st
+    assert torch.all(out == 0)
+    from eagersgd_b200.parallel import ChannelError
+    with pytest.raises(ChannelError):
+        ch.check()
+    assert (torch.ones(4, device=dev) * 2).sum().item() == 8.0
+    for a in arenas:
+        a.free()
+
+
+def test_optimizer_wrapper_fused_matches_sgd():
+    import eagersgd_b200 as es
+    dev = _dev()
+    torch.manual_seed(1)
+    mk = lambda: torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 10)).to(dev)
+    m1, m2 = mk(), mk()
+    m2.load_state_dict(m1.state_dict())
+    o1 = torch.optim.SGD(m1.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    o2 = es.SoloAllreduceOptimizer(torch.optim.SGD(m2.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4),
+                                   es.Group(), limiter=2, bucket_mb=0.02)
+    assert o2.fused and len(o2.buckets) > 1
+    for k in range(6):
+        x = torch.randn(32, 64, device=dev)
+        y = torch.randint(0, 10, (32,), device=dev)
+        for m, o in ((m1, o1), (m2, o2)):
+            o.zero_grad()
+            torch.nn.functional.cross_entropy(m(x), y).backward()
+            o.step()
+    torch.cuda.synchronize()
+    for p1, p2 in zip(m1.parameters(), m2.parameters()):
+        assert torch.allclose(p1, p2, rtol=1e-4, atol=1e-5)
+    assert o2.stats()["status"] == 0
+    o2.close()
+
+
+def test_optimizer_wrapper_generic_inner_optimizer():
+    """Any torch optimizer can be wrapped: the averaged gradient lands in .grad (Adam here)."""
+    import eagersgd_b200 as es
+    dev = _dev()
+    torch.manual_seed(2)
+    m1 = torch.nn.Linear(32, 8).to(dev)
+    m2 = torch.nn.Linear(32, 8).to(dev)
+    m2.load_state_dict(m1.state_dict())
+    o1 = torch.optim.Adam(m1.parameters(), lr=1e-2)
+    o2 = es.MajorityAllreduceOptimizer(torch.optim.Adam(m2.parameters(), lr=1e-2), es.Group())
+    assert not o2.fused
+    for k in range(4):
+        x = torch.randn(16, 32, device=dev)
+        for m, o in ((m1, o1), (m2, o2)):
+            o.zero_grad()
+            m(x).square().mean().backward()
+            o.step()
+    for p1, p2 in zip(m1.parameters(), m2.parameters()):
+        assert torch.allclose(p1, p2, rtol=1e-5, atol=1e-6)
+    o2.close()
