@@ -96,13 +96,17 @@ class EagerOptimizer:
         cap = max(int(bucket_mb * (1 << 20) / esz), 1)
         self.buckets: List[_Bucket] = []
         for gi, g in enumerate(self.optimizer.param_groups):
-            cur = None
+            open_by_dtype: Dict[torch.dtype, _Bucket] = {}
             # reverse order: the last layers' gradients are ready first (the reference
-            # walks reversed(grads_and_vars) too, opt_esgd_solo_imagenet_imbalance.py:28)
+            # walks reversed(grads_and_vars) too, opt_esgd_solo_imagenet_imbalance.py:28);
+            # one open bucket per dtype, so bf16 weights and fp32 norm parameters do not
+            # fragment each other's buckets
             for p in reversed([p for p in g["params"] if p.requires_grad]):
-                if cur is None or (cur.count + p.numel() > cap and cur.count > 0) or cur.params[0].dtype != p.dtype:
+                cur = open_by_dtype.get(p.dtype)
+                if cur is None or (cur.count + p.numel() > cap and cur.count > 0):
                     cur = _Bucket(len(self.buckets), gi)
                     self.buckets.append(cur)
+                    open_by_dtype[p.dtype] = cur
                 cur.add(p)
         self._bucket_of: Dict[int, _Bucket] = {}
         for b in self.buckets:

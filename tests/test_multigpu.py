@@ -1,0 +1,174 @@
+"""Partial allreduce across real GPUs: one process per GPU, CUDA-IPC peer arenas.
+
+Closed-form and oracle checks at the world size the box offers (2, 4 or 8), the
+three imbalance regimes of the reference's evaluation programs (balanced,
+randomly imbalanced, constantly imbalanced: fflib2 evaluation/ssgd_synch_send.c:
+66-189) with assertable invariants, and failure detection without faulting a GPU
+(a rank that does not join a synchronous round makes the others' bounded wait
+run out with a status word).
+"""
+import os
+import random
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _world():
+    return min(torch.cuda.device_count(), 8)
+
+
+def _setup(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import eagersgd_b200 as es
+    torch.cuda.set_device(rank)
+    return es, es.init()
+
+
+def _channel(group, count, mode, limiter, average, slot_dtype=torch.float32, timeout_s=5.0, grace_us=0.0,
+             fused=False):
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas
+    dev = group.device
+    arena, bases = create_arenas(count, slot_dtype, group.rank, group.world, group.exchange)
+    grad = torch.zeros(count, device=dev)
+    out = torch.zeros(count, device=dev)
+    ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=slot_dtype, mode=mode,
+                       limiter=limiter, average=average, out=out, timeout_s=timeout_s, grace_us=grace_us)
+    return arena, ch, grad, out
+
+
+def _sync_closed_form(rank, world, slot_bf16):
+    es, group = _setup(rank, world)
+    count = 1 << 20
+    arena, ch, grad, out = _channel(group, count, "sync", -1, "sum",
+                                    torch.bfloat16 if slot_bf16 else torch.float32)
+    ok = True
+    for k in range(1, 6):
+        grad.fill_(float(rank + 1 + k))
+        ch.step()
+        torch.cuda.synchronize()
+        expect = float(sum(r + 1 + k for r in range(world)))
+        ok = ok and bool(torch.all(out == expect))
+    st = ch.stats()
+    group.barrier()
+    arena.free()
+    es.finalize()
+    return ok, st
+
+
+@pytest.mark.parametrize("slot_bf16", [False, True])
+def test_sync_closed_form(slot_bf16):
+    for ok, st in run_ranks(_sync_closed_form, _world(), (slot_bf16,)):
+        assert ok and st["status"] == 0 and st["participated"] == 5
+
+
+def _eager_regimes(rank, world, mode):
+    es, group = _setup(rank, world)
+    from eagersgd_b200.parallel import _native as N
+    count = 1 << 18
+    arena, ch, grad, out = _channel(group, count, mode, 7, "sum")
+    applied = torch.zeros(count, dtype=torch.float64, device=group.device)
+    rng = random.Random(77)  # shared stream: every rank knows who is delayed
+    torn = False
+    steps = 0
+    stream = torch.cuda.current_stream()
+    for phase in ("balanced", "random", "constant"):
+        for _ in range(16):
+            steps += 1
+            victims = {"balanced": [], "random": [rng.randrange(world)], "constant": [0]}[phase]
+            if rank in victims:
+                N.cuda().esgd_spin(2_000_000, stream.cuda_stream)  # 2 ms late
+            grad.fill_(float((rank + 1) * 100 + steps))
+            ch.step()
+            torch.cuda.synchronize()
+            torn = torn or not bool(torch.all(out == out[0]))
+            applied += out.double()
+    group.barrier()  # every round any rank opened has completed
+    ch.flush()
+    torch.cuda.synchronize()
+    applied += out.double()
+    st = ch.stats()
+    total = applied[0].item()
+    group.barrier()
+    arena.free()
+    es.finalize()
+    return torn, total, st, steps
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+def test_eager_three_regimes(mode):
+    world = _world()
+    res = run_ranks(_eager_regimes, world, (mode,))
+    steps = res[0][3]
+    published = sum((r + 1) * 100 + k for r in range(world) for k in range(1, steps + 1))
+    for torn, total, st, _ in res:
+        assert not torn
+        assert st["status"] == 0
+        assert total == res[0][1]          # replicas accumulated the same updates
+        assert 0 < total <= published      # nothing duplicated
+        assert st["sync_rounds"] == steps // 8
+
+
+def _wrapper_sync_equals_big_batch(rank, world):
+    es, group = _setup(rank, world)
+    dev = group.device
+    torch.manual_seed(5)
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 4)).to(dev)
+    ref = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 4)).to(dev)
+    ref.load_state_dict(model.state_dict())
+    opt = es.SyncAllreduceOptimizer(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9), group)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    g = torch.Generator().manual_seed(9)
+    for k in range(5):
+        xs = torch.randn(world, 8, 32, generator=g).to(dev)
+        ys = torch.randn(world, 8, 4, generator=g).to(dev)
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(model(xs[rank]), ys[rank]).backward()
+        opt.step()
+        ropt.zero_grad()
+        torch.nn.functional.mse_loss(ref(xs.view(-1, 32)), ys.view(-1, 4)).backward()
+        ropt.step()
+    torch.cuda.synchronize()
+    err = max((a - b).abs().max().item() for a, b in zip(model.parameters(), ref.parameters()))
+    st = opt.stats()
+    opt.close()
+    es.finalize()
+    return err, st
+
+
+def test_sync_wrapper_equals_large_batch_sgd():
+    for err, st in run_ranks(_wrapper_sync_equals_big_batch, _world()):
+        assert err < 1e-5 and st["status"] == 0
+
+
+def _absent_rank(rank, world):
+    es, group = _setup(rank, world)
+    arena, ch, grad, out = _channel(group, 4096, "sync", -1, "sum", timeout_s=1.0)
+    grad.fill_(1.0)
+    ch.step()                      # round 1: everyone joins
+    torch.cuda.synchronize()
+    ok_first = bool(torch.all(out == float(world)))
+    group.barrier()
+    status = 0
+    if rank != world - 1:          # the last rank does not join round 2 (it stays alive and idle)
+        ch.step()
+        torch.cuda.synchronize()
+        status = ch.stats()["status"]
+    alive = float((torch.ones(8, device=group.device) * 3).sum().item())
+    group.barrier()
+    arena.free()
+    es.finalize()
+    return ok_first, status, alive
+
+
+def test_missing_rank_is_detected_by_bounded_wait():
+    world = _world()
+    res = run_ranks(_absent_rank, world)
+    for r, (ok_first, status, alive) in enumerate(res):
+        assert ok_first and alive == 24.0
+        if r != world - 1:
+            assert status != 0     # arrival or round timeout, reported instead of hanging
