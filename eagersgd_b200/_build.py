@@ -157,7 +157,7 @@ def _build_cuda_locked(srcs, force, verbose, jobs):
         log.close()
         if rc != 0:
             raise RuntimeError("nvcc failed for %s:\n%s" % (src, open(obj + ".log").read()[-4000:]))
-    cmd = [nvcc, "-shared", "-o", CUDA_LIB + ".tmp"] + objs + ["-lcuda"] + CUDA_ARCH_FLAGS
+    cmd = [nvcc, "-shared", "-o", CUDA_LIB + ".tmp"] + objs + CUDA_ARCH_FLAGS
     subprocess.run(cmd, check=True)
     os.replace(CUDA_LIB + ".tmp", CUDA_LIB)
     _stamp(CUDA_LIB, srcs)
