@@ -1,0 +1,287 @@
+// Fused batch-norm kernels for NHWC bf16 activations viewed as [M = N*H*W, C].
+//
+//   bn_stats        : per-channel sum / sum of squares (fp32) of a conv output
+//   bn_finalize     : mean / inv-std, scale / shift, running-statistics update
+//   bn_apply        : z = act(scale*y + shift [+ residual])           (one read, one write)
+//   bn_bwd_reduce   : g = dz * [z > 0];  dbeta = sum g, dgamma = sum g*xhat
+//   bn_bwd_apply    : dy = gamma*invstd*(g - dbeta/M - xhat*dgamma/M), optional dres = g
+//
+// Training-mode semantics, momentum and eps follow the reference model
+// (official/resnet/resnet_model.py:51-60: decay 0.997, eps 1e-5, fused=True) and its
+// CPU restatement (deep500 .../cpp/operators/batchnormalization_op_training.cpp:48-329).
+// Threads map to channel groups of 8 (one 16-byte vector), rows are strided over
+// blocks, partial sums meet in shared memory and then in fp32 global atomics.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "launch_count.cuh"
+
+namespace {
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float v[8]) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 f = __bfloat1622float2(h[q]);
+    v[2 * q] = f.x;
+    v[2 * q + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float v[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// Block = 256 threads = (C/8 channel groups) x (256/(C/8) row lanes) when C/8 <= 256;
+// wider layers loop over channel groups.
+struct Map {
+  int groups;      // C / 8
+  int g_per_blk;   // channel groups handled per pass by a block (<= 256)
+  int rows_par;    // rows processed in parallel by a block
+};
+__device__ __forceinline__ Map make_map(int C) {
+  Map m;
+  m.groups = C / 8;
+  m.g_per_blk = m.groups < 256 ? m.groups : 256;
+  m.rows_par = 256 / m.g_per_blk;
+  return m;
+}
+
+__global__ void __launch_bounds__(256) bn_stats_kernel(const __nv_bfloat16* __restrict__ y, int64_t M, int C,
+                                                       float* __restrict__ sum, float* __restrict__ sqsum) {
+  const Map mp = make_map(C);
+  __shared__ float s_sum[256 * 8], s_sq[256 * 8];
+  for (int g0 = 0; g0 < mp.groups; g0 += mp.g_per_blk) {
+    const int gl = threadIdx.x % mp.g_per_blk, rl = threadIdx.x / mp.g_per_blk;
+    const int g = g0 + gl;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (g < mp.groups && rl < mp.rows_par) {
+      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
+        float v[8];
+        ld8(y + r * C + g * 8, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { a[q] += v[q]; b[q] += v[q] * v[q]; }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { s_sum[threadIdx.x * 8 + q] = a[q]; s_sq[threadIdx.x * 8 + q] = b[q]; }
+    __syncthreads();
+    if (rl == 0 && g < mp.groups) {
+      for (int rr = 1; rr < mp.rows_par; ++rr) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          a[q] += s_sum[(rr * mp.g_per_blk + gl) * 8 + q];
+          b[q] += s_sq[(rr * mp.g_per_blk + gl) * 8 + q];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { atomicAdd(sum + g * 8 + q, a[q]); atomicAdd(sqsum + g * 8 + q, b[q]); }
+    }
+    __syncthreads();
+  }
+}
+
+// One thread per channel.  Writes mean, invstd, scale = gamma*invstd, shift = beta - mean*scale.
+__global__ void bn_finalize_kernel(const float* sum, const float* sqsum, const float* gamma, const float* beta,
+                                   float* running_mean, float* running_var, float* mean_out, float* invstd_out,
+                                   float* scale, float* shift, int C, float inv_count, float unbias, float momentum,
+                                   float eps) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float mean = sum[c] * inv_count;
+  float var = fmaxf(sqsum[c] * inv_count - mean * mean, 0.0f);
+  float invstd = rsqrtf(var + eps);
+  mean_out[c] = mean;
+  invstd_out[c] = invstd;
+  float sc = gamma[c] * invstd;
+  scale[c] = sc;
+  shift[c] = beta[c] - mean * sc;
+  if (running_mean != nullptr) {
+    running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * mean;
+    running_var[c] = (1.0f - momentum) * running_var[c] + momentum * var * unbias;
+  }
+}
+
+__global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __restrict__ y,
+                                                       const __nv_bfloat16* __restrict__ res,
+                                                       __nv_bfloat16* __restrict__ z, const float* __restrict__ scale,
+                                                       const float* __restrict__ shift, int64_t total_groups, int C,
+                                                       int relu) {
+  const int groups = C / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_groups;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % groups);
+    float v[8], sc[8], sh[8];
+    ld8(y + i * 8, v);
+    *reinterpret_cast<float4*>(sc) = *reinterpret_cast<const float4*>(scale + g * 8);
+    *reinterpret_cast<float4*>(sc + 4) = *reinterpret_cast<const float4*>(scale + g * 8 + 4);
+    *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(shift + g * 8);
+    *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(shift + g * 8 + 4);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = v[q] * sc[q] + sh[q];
+    if (res != nullptr) {
+      float r[8];
+      ld8(res + i * 8, r);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] += r[q];
+    }
+    if (relu) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = fmaxf(v[q], 0.0f);
+    }
+    st8(z + i * 8, v);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
+                     const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
+                     const float* __restrict__ invstd, int64_t M, int C, int relu, float* __restrict__ dbeta,
+                     float* __restrict__ dgamma) {
+  const Map mp = make_map(C);
+  __shared__ float s_a[256 * 8], s_b[256 * 8];
+  for (int g0 = 0; g0 < mp.groups; g0 += mp.g_per_blk) {
+    const int gl = threadIdx.x % mp.g_per_blk, rl = threadIdx.x / mp.g_per_blk;
+    const int g = g0 + gl;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (g < mp.groups && rl < mp.rows_par) {
+      float mu[8], is[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { mu[q] = mean[g * 8 + q]; is[q] = invstd[g * 8 + q]; }
+      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
+        float d[8], yy[8];
+        ld8(dz + r * C + g * 8, d);
+        ld8(y + r * C + g * 8, yy);
+        if (relu) {
+          float zz[8];
+          ld8(z + r * C + g * 8, zz);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { a[q] += d[q]; b[q] += d[q] * (yy[q] - mu[q]) * is[q]; }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { s_a[threadIdx.x * 8 + q] = a[q]; s_b[threadIdx.x * 8 + q] = b[q]; }
+    __syncthreads();
+    if (rl == 0 && g < mp.groups) {
+      for (int rr = 1; rr < mp.rows_par; ++rr) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          a[q] += s_a[(rr * mp.g_per_blk + gl) * 8 + q];
+          b[q] += s_b[(rr * mp.g_per_blk + gl) * 8 + q];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { atomicAdd(dbeta + g * 8 + q, a[q]); atomicAdd(dgamma + g * 8 + q, b[q]); }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
+                    const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
+                    const float* __restrict__ invstd, const float* __restrict__ gamma,
+                    const float* __restrict__ dbeta, const float* __restrict__ dgamma,
+                    __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dres, int64_t total_groups, int C,
+                    int relu, float inv_count) {
+  const int groups = C / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_groups;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % groups);
+    float d[8], yy[8];
+    ld8(dz + i * 8, d);
+    ld8(y + i * 8, yy);
+    if (relu) {
+      float zz[8];
+      ld8(z + i * 8, zz);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
+    }
+    if (dres != nullptr) st8(dres + i * 8, d);
+    float o[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int c = g * 8 + q;
+      const float is = invstd[c];
+      const float xhat = (yy[q] - mean[c]) * is;
+      o[q] = gamma[c] * is * (d[q] - dbeta[c] * inv_count - xhat * dgamma[c] * inv_count);
+    }
+    st8(dy + i * 8, o);
+  }
+}
+
+int blocks_for(int64_t work_items, int per_block) {
+  int64_t b = (work_items + per_block - 1) / per_block;
+  const int64_t cap = 148 * 8;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+extern "C" {
+
+// sum / sqsum must be zeroed by the caller (they accumulate).
+int esgd_bn_stats(const void* y, int64_t M, int C, float* sum, float* sqsum, void* stream) {
+  if (C % 8) return -1;
+  int g = C / 8 < 256 ? C / 8 : 256;
+  int rows_par = 256 / g;
+  bn_stats_kernel<<<blocks_for(M, rows_par * 16), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, M, C, sum, sqsum);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_bn_finalize(const float* sum, const float* sqsum, const float* gamma, const float* beta,
+                     float* running_mean, float* running_var, float* mean, float* invstd, float* scale,
+                     float* shift, int C, int64_t count, float momentum, float eps, void* stream) {
+  float unbias = count > 1 ? (float)count / (float)(count - 1) : 1.0f;
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+      sum, sqsum, gamma, beta, running_mean, running_var, mean, invstd, scale, shift, C, 1.0f / (float)count,
+      unbias, momentum, eps);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_bn_apply(const void* y, const void* residual, void* z, const float* scale, const float* shift, int64_t M,
+                  int C, int relu, void* stream) {
+  if (C % 8) return -1;
+  int64_t groups = M * (C / 8);
+  bn_apply_kernel<<<blocks_for(groups, 256 * 4), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, (const __nv_bfloat16*)residual, (__nv_bfloat16*)z, scale, shift, groups, C, relu);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+// dbeta / dgamma must be zeroed by the caller.
+int esgd_bn_bwd_reduce(const void* dz, const void* z, const void* y, const float* mean, const float* invstd,
+                       int64_t M, int C, int relu, float* dbeta, float* dgamma, void* stream) {
+  if (C % 8) return -1;
+  int g = C / 8 < 256 ? C / 8 : 256;
+  int rows_par = 256 / g;
+  bn_bwd_reduce_kernel<<<blocks_for(M, rows_par * 16), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, M, C, relu, dbeta,
+      dgamma);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_bn_bwd_apply(const void* dz, const void* z, const void* y, const float* mean, const float* invstd,
+                      const float* gamma, const float* dbeta, const float* dgamma, void* dy, void* dres, int64_t M,
+                      int C, int relu, void* stream) {
+  if (C % 8) return -1;
+  int64_t groups = M * (C / 8);
+  bn_bwd_apply_kernel<<<blocks_for(groups, 256 * 4), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, gamma, dbeta,
+      dgamma, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, groups, C, relu, 1.0f / (float)M);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,270 @@
+// Softmax cross-entropy (forward + backward in one pass), 3x3/2 max pooling and
+// global average pooling for NHWC bf16 activations.
+//
+// Reference semantics: sparse softmax cross-entropy averaged over the batch
+// (official/resnet/resnet_run_loop_solo_imagenet_300.py:321-322; CPU restatements
+// deep500 .../cpp/operators/softmax_op.cpp:53-96, python/softmax_crossentropy_op.py:11-49),
+// max_pooling2d 3x3 stride 2 'SAME' and reduce_mean over H,W (resnet_model.py:521-549;
+// maxpool_op.cpp, globalaveragepool_op.cpp).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+#include "launch_count.cuh"
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float r = sh[0];
+  for (int w = 1; w < nw; ++w) r = is_max ? fmaxf(r, sh[w]) : r + sh[w];
+  __syncthreads();
+  return r;
+}
+
+// One block per sample.  loss_sum accumulates sum_i loss_i * inv_batch; dlogits = (softmax - onehot) * grad_scale.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels,
+                                                         int classes, int ld, float inv_batch, float grad_scale,
+                                                         float* __restrict__ loss_sum, float* __restrict__ per_sample,
+                                                         T* __restrict__ dlogits) {
+  __shared__ float sh[8];
+  const int row = blockIdx.x;
+  const T* x = logits + (size_t)row * ld;
+  float mx = -FLT_MAX;
+  for (int c = threadIdx.x; c < classes; c += blockDim.x) mx = fmaxf(mx, to_f(x[c]));
+  mx = block_reduce(mx, true, sh);
+  float se = 0.0f;
+  for (int c = threadIdx.x; c < classes; c += blockDim.x) se += __expf(to_f(x[c]) - mx);
+  se = block_reduce(se, false, sh);
+  const int label = (int)labels[row];
+  const float lse = mx + __logf(se);
+  if (threadIdx.x == 0) {
+    float li = lse - to_f(x[label]);
+    if (per_sample != nullptr) per_sample[row] = li;
+    atomicAdd(loss_sum, li * inv_batch);
+  }
+  if (dlogits != nullptr) {
+    T* d = dlogits + (size_t)row * ld;
+    const float inv_se = 1.0f / se;
+    for (int c = threadIdx.x; c < classes; c += blockDim.x) {
+      float p = __expf(to_f(x[c]) - mx) * inv_se;
+      d[c] = from_f<T>((p - (c == label ? 1.0f : 0.0f)) * grad_scale);
+    }
+  }
+}
+
+// ---- max pool 3x3 stride 2 pad 1, NHWC, vectors of 8 channels -----------------
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float v[8]) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 f = __bfloat1622float2(h[q]);
+    v[2 * q] = f.x;
+    v[2 * q + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float v[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ y, int N, int H, int W, int C,
+                                                          int OH, int OW) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * OH * OW * G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    int64_t t = i / G;
+    const int ow = (int)(t % OW); t /= OW;
+    const int oh = (int)(t % OH);
+    const int n = (int)(t / OH);
+    float m[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) m[q] = -FLT_MAX;
+    for (int r = 0; r < 3; ++r) {
+      const int h = oh * 2 - 1 + r;
+      if (h < 0 || h >= H) continue;
+      for (int s = 0; s < 3; ++s) {
+        const int w = ow * 2 - 1 + s;
+        if (w < 0 || w >= W) continue;
+        float v[8];
+        ld8(x + (((int64_t)n * H + h) * W + w) * C + g * 8, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) m[q] = fmaxf(m[q], v[q]);
+      }
+    }
+    st8(y + i * 8, m);
+  }
+}
+
+// Gather form: an input pixel receives dy of every window whose first maximum (scan order) it is.
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ dy,
+                                                          __nv_bfloat16* __restrict__ dx, int N, int H, int W, int C,
+                                                          int OH, int OW) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * H * W * G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    int64_t t = i / G;
+    const int w = (int)(t % W); t /= W;
+    const int h = (int)(t % H);
+    const int n = (int)(t / H);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // windows that contain row h: oh in {h/2, (h+1)/2} (one window when h is even); same for columns
+    const int ohs[2] = {h / 2, (h + 1) / 2}, ows[2] = {w / 2, (w + 1) / 2};
+    const int noh = ohs[0] == ohs[1] ? 1 : 2, now = ows[0] == ows[1] ? 1 : 2;
+    for (int a = 0; a < noh; ++a) {
+      const int oh = ohs[a];
+      if (oh >= OH) continue;
+      for (int b = 0; b < now; ++b) {
+        const int ow = ows[b];
+        if (ow >= OW) continue;
+        // position of (h, w) inside the window, in scan order
+        const int my_pos = (h - (oh * 2 - 1)) * 3 + (w - (ow * 2 - 1));
+        float best[8];
+        int first[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { best[q] = -FLT_MAX; first[q] = -1; }
+        for (int r = 0; r < 3; ++r) {
+          const int hh = oh * 2 - 1 + r;
+          if (hh < 0 || hh >= H) continue;
+          for (int s = 0; s < 3; ++s) {
+            const int ww = ow * 2 - 1 + s;
+            if (ww < 0 || ww >= W) continue;
+            float v[8];
+            ld8(x + (((int64_t)n * H + hh) * W + ww) * C + g * 8, v);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (v[q] > best[q]) { best[q] = v[q]; first[q] = r * 3 + s; }
+          }
+        }
+        float d[8];
+        ld8(dy + ((((int64_t)n * OH + oh) * OW + ow) * C + g * 8), d);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (first[q] == my_pos) acc[q] += d[q];
+      }
+    }
+    st8(dx + i * 8, acc);
+  }
+}
+
+// ---- global average pool: [N, HW, C] -> [N, C] -----------------------------------
+__global__ void __launch_bounds__(256) avgpool_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ y, int N, int HW, int C) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    const int n = (int)(i / G);
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int p = 0; p < HW; ++p) {
+      float v[8];
+      ld8(x + ((int64_t)n * HW + p) * C + g * 8, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) a[q] += v[q];
+    }
+    const float inv = 1.0f / (float)HW;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) a[q] *= inv;
+    st8(y + i * 8, a);
+  }
+}
+
+__global__ void __launch_bounds__(256) avgpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                          __nv_bfloat16* __restrict__ dx, int N, int HW, int C) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * HW * G;
+  const float inv = 1.0f / (float)HW;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    const int n = (int)(i / ((int64_t)HW * G));
+    float v[8];
+    ld8(dy + ((int64_t)n * G + g) * 8, v);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] *= inv;
+    st8(dx + i * 8, v);
+  }
+}
+
+int grid_for(int64_t items) {
+  int64_t b = (items + 255) / 256;
+  const int64_t cap = 148 * 16;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+extern "C" {
+
+// loss_sum (one float) must be zeroed by the caller.
+int esgd_softmax_ce(const void* logits, int is_bf16, const int64_t* labels, int batch, int classes, int ld,
+                    float grad_scale, float* loss_sum, float* per_sample, void* dlogits, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (is_bf16)
+    softmax_ce_kernel<__nv_bfloat16><<<batch, 256, 0, s>>>((const __nv_bfloat16*)logits, labels, classes, ld,
+                                                           1.0f / batch, grad_scale, loss_sum, per_sample,
+                                                           (__nv_bfloat16*)dlogits);
+  else
+    softmax_ce_kernel<float><<<batch, 256, 0, s>>>((const float*)logits, labels, classes, ld, 1.0f / batch,
+                                                   grad_scale, loss_sum, per_sample, (float*)dlogits);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_maxpool3x3s2_fwd(const void* x, void* y, int N, int H, int W, int C, void* stream) {
+  if (C % 8) return -1;
+  const int OH = (H + 1) / 2, OW = (W + 1) / 2;
+  maxpool_fwd_kernel<<<grid_for((int64_t)N * OH * OW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C, OH, OW);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_maxpool3x3s2_bwd(const void* x, const void* dy, void* dx, int N, int H, int W, int C, void* stream) {
+  if (C % 8) return -1;
+  const int OH = (H + 1) / 2, OW = (W + 1) / 2;
+  maxpool_bwd_kernel<<<grid_for((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, OH, OW);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_avgpool_fwd(const void* x, void* y, int N, int HW, int C, void* stream) {
+  if (C % 8) return -1;
+  avgpool_fwd_kernel<<<grid_for((int64_t)N * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, HW, C);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+int esgd_avgpool_bwd(const void* dy, void* dx, int N, int HW, int C, void* stream) {
+  if (C % 8) return -1;
+  avgpool_bwd_kernel<<<grid_for((int64_t)N * HW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, HW, C);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -18,6 +18,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import functional as ops
+
 BN_MOMENTUM_TF = 0.997  # tf decay; torch momentum = 1 - decay
 BN_EPS = 1e-5
 
@@ -27,20 +29,35 @@ IMAGENET_BLOCKS = {
 }
 
 
-def _bn(ch: int, zero_gamma: bool = False) -> nn.BatchNorm2d:
-    bn = nn.BatchNorm2d(ch, eps=BN_EPS, momentum=1.0 - BN_MOMENTUM_TF)
+class BatchNormAct(nn.BatchNorm2d):
+    """Batch norm fused with an optional residual add and ReLU (one kernel pass each way)."""
+
+    def forward(self, y, relu: bool = True, residual=None, stats=None):  # noqa: D102
+        return ops.bn_act(y, self.weight, self.bias, self.running_mean, self.running_var, self.momentum, relu,
+                          residual, stats, self.training)
+
+
+def _bn(ch: int, zero_gamma: bool = False) -> BatchNormAct:
+    bn = BatchNormAct(ch, eps=BN_EPS, momentum=1.0 - BN_MOMENTUM_TF)
     if zero_gamma:
         nn.init.zeros_(bn.weight)
     return bn
 
 
 class _Conv(nn.Conv2d):
-    """conv2d_fixed_padding: explicit symmetric padding when strided (resnet_model.py:63-101)."""
+    """conv2d_fixed_padding: explicit symmetric padding when strided (resnet_model.py:63-101).
+
+    ``forward`` returns ``(y, stats)`` where ``stats`` holds the per-channel sum and sum of
+    squares of ``y`` when the kernel produced them in its epilogue (else ``None``).
+    """
 
     def __init__(self, cin, cout, k, stride):
         super().__init__(cin, cout, k, stride=stride, padding=(k - 1) // 2, bias=False)
-        # variance_scaling_initializer() of the reference: fan-in, truncated normal ~ He/√2-ish
+        # variance_scaling_initializer() of the reference: fan-in scaling
         nn.init.kaiming_normal_(self.weight, mode="fan_in", nonlinearity="linear")
+
+    def forward(self, x):  # noqa: D102
+        return ops.conv2d(x, self.weight, self.stride[0], self.padding[0], want_stats=self.training)
 
 
 class _Block(nn.Module):
@@ -66,42 +83,35 @@ class _Block(nn.Module):
         for idx, (ci, co, k, s) in enumerate(spec):
             conv = _Conv(ci, co, k, s)
             convs.append(conv)
+            registry.append(("conv", conv))
             last = idx == len(spec) - 1
-            if version == 1:
-                registry.append(("conv", conv))
-                bn = _bn(co, zero_gamma=last)
+            if version == 1 or not last:
+                bn = _bn(co, zero_gamma=(last and version == 1))
                 bns.append(bn)
                 registry.append(("bn", bn))
-            else:
-                registry.append(("conv", conv))
-                if not last:
-                    bn = _bn(co)
-                    bns.append(bn)
-                    registry.append(("bn", bn))
         self.convs = nn.ModuleList(convs)
         self.bns = nn.ModuleList(bns)
         self.cout = cout
 
     def forward(self, x):
+        n = len(self.convs)
         if self.version == 1:
             shortcut = x
             if self.proj is not None:
-                shortcut = self.proj_bn(self.proj(x))
+                ys, st = self.proj(x)
+                shortcut = self.proj_bn(ys, relu=False, stats=st)
             y = x
-            n = len(self.convs)
             for i in range(n):
-                y = self.bns[i](self.convs[i](y))
-                if i < n - 1:
-                    y = F.relu(y, inplace=True)
-            return F.relu(y + shortcut, inplace=True)
-        pre = F.relu(self.pre_bn(x))
-        shortcut = self.proj(pre) if self.proj is not None else x
+                yc, st = self.convs[i](y)
+                # the last batch norm also adds the shortcut and applies the block's final ReLU
+                y = self.bns[i](yc, relu=True, residual=shortcut if i == n - 1 else None, stats=st)
+            return y
+        pre = self.pre_bn(x, relu=True)
+        shortcut = self.proj(pre)[0] if self.proj is not None else x
         y = pre
-        n = len(self.convs)
         for i in range(n):
-            y = self.convs[i](y)
-            if i < n - 1:
-                y = F.relu(self.bns[i](y), inplace=True)
+            yc, st = self.convs[i](y)
+            y = self.bns[i](yc, relu=True, stats=st) if i < n - 1 else yc
         return y + shortcut
 
 
@@ -137,19 +147,20 @@ class ResNet(nn.Module):
         self.feature_dim = cin
 
     def features(self, x):
-        x = self.stem(x)
+        x, st = self.stem(x)
         if self.stem_bn is not None:
-            x = F.relu(self.stem_bn(x), inplace=True)
+            x = self.stem_bn(x, relu=True, stats=st)
         if self.first_pool:
-            x = F.max_pool2d(x, 3, 2, 1)
+            x = ops.max_pool_3x3_s2(x)
         for blk in self.blocks:
             x = blk(x)
         if self.final_bn is not None:
-            x = F.relu(self.final_bn(x), inplace=True)
-        return torch.flatten(F.adaptive_avg_pool2d(x, 1), 1)
+            x = self.final_bn(x, relu=True)
+        return ops.global_avg_pool(x)
 
     def forward(self, x):
-        return self.fc(self.features(x))
+        """Logits (fp32 on the native path)."""
+        return ops.linear(self.features(x), self.fc.weight, self.fc.bias)
 
 
 def imagenet_resnet(size: int = 50, version: int = 1, num_classes: int = 1001) -> ResNet:

@@ -1,0 +1,290 @@
+"""Autograd functions over the hand-written sm_100a kernels (NHWC bf16 activations).
+
+Activations are 4-D ``channels_last`` tensors, i.e. ``[N, H, W, C]`` in memory,
+which makes a 1x1 convolution a plain ``[N*H*W, Cin] x [Cout, Cin]^T`` GEMM on
+the tcgen05 tensor cores, with the batch-norm statistics accumulated in the GEMM
+epilogue.  On CPU tensors every function falls back to the same mathematics in
+PyTorch, which is what the CPU tests and oracles use.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..parallel import _native as N
+from .gemm import gemm
+
+BN_EPS = 1e-5
+
+
+def _lib():
+    lib = N.cuda()
+    if not getattr(lib, "_nn_bound", False):
+        vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+        lib.esgd_bn_stats.argtypes = [vp, i64, i32, vp, vp, vp]
+        lib.esgd_bn_finalize.argtypes = [vp] * 10 + [i32, i64, f32, f32, vp]
+        lib.esgd_bn_apply.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp]
+        lib.esgd_bn_bwd_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp, vp, vp]
+        lib.esgd_bn_bwd_apply.argtypes = [vp] * 10 + [i64, i32, i32, vp]
+        lib.esgd_softmax_ce.argtypes = [vp, i32, vp, i32, i32, i32, f32, vp, vp, vp, vp]
+        lib.esgd_maxpool3x3s2_fwd.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        lib.esgd_maxpool3x3s2_bwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        lib.esgd_avgpool_fwd.argtypes = [vp, vp, i32, i32, i32, vp]
+        lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
+        lib._nn_bound = True
+    return lib
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ck(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError("%s failed with code %d" % (what, rc))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return t.data_ptr() if t is not None else None
+
+
+def nhwc_2d(x: torch.Tensor) -> torch.Tensor:
+    """[N, C, H, W] channels_last -> contiguous [N*H*W, C] view (no copy when already NHWC)."""
+    n, c, h, w = x.shape
+    return x.permute(0, 2, 3, 1).contiguous().view(n * h * w, c)
+
+
+def from_2d(y2d: torch.Tensor, n: int, h: int, w: int) -> torch.Tensor:
+    return y2d.view(n, h, w, y2d.shape[1]).permute(0, 3, 1, 2)
+
+
+def native(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+# --------------------------------------------------------------------------- 1x1 convolution / dense
+class _Conv1x1(torch.autograd.Function):
+    """y = x (*) w for a 1x1 kernel; optionally also returns per-channel sum / sum-of-squares of y."""
+
+    @staticmethod
+    def forward(ctx, x, w, want_stats: bool):
+        n, cin, h, wd = x.shape
+        cout = w.shape[0]
+        x2d = nhwc_2d(x)
+        w2d = w.reshape(cout, cin)
+        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        y2d = gemm(x2d, w2d, col_sum=stats[0] if want_stats else None, col_sqsum=stats[1] if want_stats else None)
+        ctx.save_for_backward(x2d, w2d)
+        ctx.dims = (n, h, wd, cin, cout, w.shape)
+        ctx.mark_non_differentiable(*( [stats] if want_stats else []))
+        y = from_2d(y2d, n, h, wd)
+        return (y, stats) if want_stats else y
+
+    @staticmethod
+    def backward(ctx, dy, *unused):
+        x2d, w2d = ctx.saved_tensors
+        n, h, wd, cin, cout, wshape = ctx.dims
+        dy2d = nhwc_2d(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = from_2d(gemm(dy2d, w2d, b_kmajor=False), n, h, wd)          # [M,Cout] x W[Cout(K),Cin(N)]
+        if ctx.needs_input_grad[1]:
+            m = dy2d.shape[0]
+            splits = max(1, min(148, (m // 64) // 8))
+            dw32 = gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, splits=max(splits, 2))  # [Cout, Cin] fp32
+            dw = dw32.to(torch.bfloat16).view(wshape)
+        return dx, dw, None
+
+
+def conv1x1(x: torch.Tensor, w: torch.Tensor, want_stats: bool = False):
+    if native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+        return _Conv1x1.apply(x, w, want_stats)
+    y = F.conv2d(x, w)
+    if want_stats:
+        yf = y.float()
+        return y, torch.stack([yf.sum((0, 2, 3)), (yf * yf).sum((0, 2, 3))]).detach()
+    return y
+
+
+def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, want_stats: bool = False):
+    """NHWC convolution; returns ``(y, stats)`` (``stats`` is None unless produced by the kernel epilogue).
+
+    1x1 kernels run as tcgen05 GEMMs (a strided 1x1 first gathers the kept pixels).
+    """
+    k = w.shape[2]
+    if k == 1 and native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+        if stride > 1:
+            x = x[:, :, ::stride, ::stride].contiguous(memory_format=torch.channels_last)
+        out = conv1x1(x, w, want_stats)
+        return out if want_stats else (out, None)
+    return F.conv2d(x, w, None, stride, padding), None
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = b is not None
+        return gemm(x, w, bias=b.float() if b is not None else None, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy16 = dy.to(torch.bfloat16).contiguous()
+        dx = gemm(dy16, w, b_kmajor=False) if ctx.needs_input_grad[0] else None
+        dw = gemm(dy16, x, a_kmajor=False, b_kmajor=False, out_dtype=torch.float32).to(w.dtype) \
+            if ctx.needs_input_grad[1] else None
+        db = dy.sum(0).to(w.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense layer; fp32 logits out of bf16 operands on the native path."""
+    if native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+        return _Linear.apply(x.contiguous(), w, b)
+    return F.linear(x, w, b)
+
+
+# --------------------------------------------------------------------------- batch norm (+ residual) (+ ReLU)
+class _BnAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, gamma, beta, residual, running_mean, running_var, momentum, relu, stats):
+        n, c, h, w = y.shape
+        lib = _lib()
+        y2d = nhwc_2d(y)
+        m = y2d.shape[0]
+        s = _stream(y)
+        if stats is None:
+            stats = torch.zeros(2, c, dtype=torch.float32, device=y.device)
+            _ck(lib.esgd_bn_stats(y2d.data_ptr(), m, c, stats[0].data_ptr(), stats[1].data_ptr(), s), "bn_stats")
+        aux = torch.empty(4, c, dtype=torch.float32, device=y.device)  # mean, invstd, scale, shift
+        _ck(lib.esgd_bn_finalize(stats[0].data_ptr(), stats[1].data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                 _ptr(running_mean), _ptr(running_var), aux[0].data_ptr(), aux[1].data_ptr(),
+                                 aux[2].data_ptr(), aux[3].data_ptr(), c, m, momentum, BN_EPS, s), "bn_finalize")
+        r2d = nhwc_2d(residual) if residual is not None else None
+        z2d = torch.empty_like(y2d)
+        _ck(lib.esgd_bn_apply(y2d.data_ptr(), _ptr(r2d), z2d.data_ptr(), aux[2].data_ptr(), aux[3].data_ptr(), m, c,
+                              int(relu), s), "bn_apply")
+        ctx.save_for_backward(y2d, z2d, gamma, aux)
+        ctx.cfg = (n, h, w, c, relu, residual is not None)
+        return from_2d(z2d, n, h, w)
+
+    @staticmethod
+    def backward(ctx, dz):
+        y2d, z2d, gamma, aux = ctx.saved_tensors
+        n, h, w, c, relu, has_res = ctx.cfg
+        lib = _lib()
+        dz2d = nhwc_2d(dz)
+        m = y2d.shape[0]
+        s = _stream(dz)
+        red = torch.zeros(2, c, dtype=torch.float32, device=dz.device)  # dbeta, dgamma
+        _ck(lib.esgd_bn_bwd_reduce(dz2d.data_ptr(), z2d.data_ptr(), y2d.data_ptr(), aux[0].data_ptr(),
+                                   aux[1].data_ptr(), m, c, int(relu), red[0].data_ptr(), red[1].data_ptr(), s),
+            "bn_bwd_reduce")
+        dy2d = torch.empty_like(y2d)
+        dres2d = torch.empty_like(y2d) if has_res else None
+        _ck(lib.esgd_bn_bwd_apply(dz2d.data_ptr(), z2d.data_ptr(), y2d.data_ptr(), aux[0].data_ptr(),
+                                  aux[1].data_ptr(), gamma.data_ptr(), red[0].data_ptr(), red[1].data_ptr(),
+                                  dy2d.data_ptr(), _ptr(dres2d), m, c, int(relu), s), "bn_bwd_apply")
+        dres = from_2d(dres2d, n, h, w) if has_res else None
+        return from_2d(dy2d, n, h, w), red[1].to(gamma.dtype), red[0].to(gamma.dtype), dres, None, None, None, None, None
+
+
+def bn_act(y: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, running_mean: Optional[torch.Tensor],
+           running_var: Optional[torch.Tensor], momentum: float = 0.003, relu: bool = True,
+           residual: Optional[torch.Tensor] = None, stats: Optional[torch.Tensor] = None,
+           training: bool = True) -> torch.Tensor:
+    """z = act(batch_norm(y) [+ residual]) with batch statistics (training) in fused kernels."""
+    if native(y) and training and y.shape[1] % 8 == 0 and gamma.dtype == torch.float32:
+        return _BnAct.apply(y, gamma, beta, residual, running_mean, running_var, momentum, relu, stats)
+    z = F.batch_norm(y, running_mean, running_var, gamma, beta, training, momentum, BN_EPS)
+    if residual is not None:
+        z = z + residual
+    return F.relu(z) if relu else z
+
+
+# --------------------------------------------------------------------------- softmax cross-entropy
+class _SoftmaxCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels):
+        lib = _lib()
+        b, c = logits.shape
+        logits = logits.contiguous()
+        loss = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        dlogits = torch.empty_like(logits)
+        _ck(lib.esgd_softmax_ce(logits.data_ptr(), int(logits.dtype == torch.bfloat16), labels.data_ptr(), b, c,
+                                logits.stride(0), 1.0 / b, loss.data_ptr(), None, dlogits.data_ptr(),
+                                _stream(logits)), "softmax_ce")
+        ctx.save_for_backward(dlogits)
+        return loss[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits * g, None
+
+
+def softmax_cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Mean sparse softmax cross-entropy; forward and gradient come out of one kernel."""
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and labels.dtype == torch.int64:
+        return _SoftmaxCE.apply(logits, labels)
+    return F.cross_entropy(logits.float(), labels)
+
+
+# --------------------------------------------------------------------------- pooling
+class _MaxPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, c, h, w = x.shape
+        x2d = nhwc_2d(x)
+        oh, ow = (h + 1) // 2, (w + 1) // 2
+        y2d = torch.empty(n * oh * ow, c, dtype=x.dtype, device=x.device)
+        _ck(_lib().esgd_maxpool3x3s2_fwd(x2d.data_ptr(), y2d.data_ptr(), n, h, w, c, _stream(x)), "maxpool")
+        ctx.save_for_backward(x2d)
+        ctx.dims = (n, c, h, w, oh, ow)
+        return from_2d(y2d, n, oh, ow)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2d,) = ctx.saved_tensors
+        n, c, h, w, oh, ow = ctx.dims
+        dy2d = nhwc_2d(dy)
+        dx2d = torch.empty_like(x2d)
+        _ck(_lib().esgd_maxpool3x3s2_bwd(x2d.data_ptr(), dy2d.data_ptr(), dx2d.data_ptr(), n, h, w, c, _stream(dy)),
+            "maxpool backward")
+        return from_2d(dx2d, n, h, w)
+
+
+def max_pool_3x3_s2(x: torch.Tensor) -> torch.Tensor:
+    if native(x) and x.shape[1] % 8 == 0:
+        return _MaxPool.apply(x)
+    return F.max_pool2d(x, 3, 2, 1)
+
+
+class _AvgPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, c, h, w = x.shape
+        x2d = nhwc_2d(x)
+        y = torch.empty(n, c, dtype=x.dtype, device=x.device)
+        _ck(_lib().esgd_avgpool_fwd(x2d.data_ptr(), y.data_ptr(), n, h * w, c, _stream(x)), "avgpool")
+        ctx.dims = (n, c, h, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, c, h, w = ctx.dims
+        dy = dy.contiguous()
+        dx2d = torch.empty(n * h * w, c, dtype=dy.dtype, device=dy.device)
+        _ck(_lib().esgd_avgpool_bwd(dy.data_ptr(), dx2d.data_ptr(), n, h * w, c, _stream(dy)), "avgpool backward")
+        return from_2d(dx2d, n, h, w)
+
+
+def global_avg_pool(x: torch.Tensor) -> torch.Tensor:
+    """[N, C, H, W] -> [N, C] mean over H, W."""
+    if native(x) and x.shape[1] % 8 == 0:
+        return _AvgPool.apply(x)
+    return torch.flatten(F.adaptive_avg_pool2d(x, 1), 1)

@@ -42,7 +42,8 @@ class TrainStep:
                  compute_dtype=torch.bfloat16, loss_fn=None):
         self.group, self.impl, self.device = group, impl, group.device
         self.compute_dtype = compute_dtype if self.device.type == "cuda" else torch.float32
-        self.loss_fn = loss_fn or F.cross_entropy
+        from ..ops.functional import softmax_cross_entropy
+        self.loss_fn = loss_fn or softmax_cross_entropy
         if impl == "ddp":
             self.model = model.to(self.device)
             if self.device.type == "cuda":
@@ -75,7 +76,7 @@ class TrainStep:
         else:
             logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
                               else x.to(self.compute_dtype))
-        loss = self.loss_fn(logits.float(), y)
+        loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
         loss.backward()
         self.opt.step()
         return loss.detach()

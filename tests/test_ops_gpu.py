@@ -1,0 +1,151 @@
+"""Hand-written NHWC kernels against plain PyTorch fp32 references of the same ops."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cl(x):
+    return x.contiguous(memory_format=torch.channels_last)
+
+
+@pytest.mark.parametrize("n,c,h,w,cout", [(4, 64, 14, 14, 256), (2, 256, 7, 9, 64), (8, 128, 28, 28, 512)])
+def test_conv1x1_forward_backward(n, c, h, w, cout):
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(0)
+    x = _cl(torch.randn(n, c, h, w, device=DEV)).to(torch.bfloat16).requires_grad_()
+    wt = (torch.randn(cout, c, 1, 1, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    y, stats = ops.conv1x1(x, wt, want_stats=True)
+    g = _cl(torch.randn(n, cout, h, w, device=DEV)).to(torch.bfloat16)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), wt.detach().float().requires_grad_()
+    yr = F.conv2d(xr, wr)
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(stats[0], yr.sum((0, 2, 3)), rtol=1e-2, atol=0.5)
+    assert torch.allclose(stats[1], (yr * yr).sum((0, 2, 3)), rtol=1e-2, atol=0.5)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=0.1 * wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("relu,residual", [(True, False), (False, False), (True, True)])
+@pytest.mark.parametrize("c", [64, 264, 2048])
+def test_bn_act(relu, residual, c):
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(1)
+    n, h, w = 4, 6, 5
+    y = _cl(torch.randn(n, c, h, w, device=DEV) * 2 + 0.5).to(torch.bfloat16).requires_grad_()
+    res = _cl(torch.randn(n, c, h, w, device=DEV)).to(torch.bfloat16).requires_grad_() if residual else None
+    gamma = (torch.rand(c, device=DEV) + 0.5).requires_grad_()
+    beta = torch.randn(c, device=DEV).requires_grad_()
+    rm, rv = torch.zeros(c, device=DEV), torch.ones(c, device=DEV)
+    z = ops.bn_act(y, gamma, beta, rm, rv, 0.1, relu, res)
+    g = _cl(torch.randn(n, c, h, w, device=DEV)).to(torch.bfloat16)
+    z.backward(g)
+    yr = y.detach().float().requires_grad_()
+    rr = res.detach().float().requires_grad_() if residual else None
+    gr, br = gamma.detach().clone().requires_grad_(), beta.detach().clone().requires_grad_()
+    rm2, rv2 = torch.zeros(c, device=DEV), torch.ones(c, device=DEV)
+    zr = F.batch_norm(yr, rm2, rv2, gr, br, True, 0.1, 1e-5)
+    if residual:
+        zr = zr + rr
+    if relu:
+        zr = zr.relu()
+    zr.backward(g.float())
+    assert torch.allclose(z.float(), zr, rtol=2e-2, atol=3e-2)
+    assert torch.allclose(rm, rm2, rtol=1e-3, atol=1e-3) and torch.allclose(rv, rv2, rtol=1e-3, atol=1e-3)
+    assert torch.allclose(y.grad.float(), yr.grad, rtol=5e-2, atol=5e-2)
+    assert torch.allclose(gamma.grad, gr.grad, rtol=5e-2, atol=0.3)
+    assert torch.allclose(beta.grad, br.grad, rtol=5e-2, atol=0.3)
+    if residual:
+        assert torch.allclose(res.grad.float(), rr.grad, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("b,c", [(32, 1000), (7, 10), (256, 1001)])
+def test_softmax_cross_entropy(dtype, b, c):
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(2)
+    logits = (torch.randn(b, c, device=DEV) * 3).to(dtype).requires_grad_()
+    labels = torch.randint(0, c, (b,), device=DEV)
+    loss = ops.softmax_cross_entropy(logits, labels)
+    (loss * 2.0).backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = F.cross_entropy(lr, labels)
+    (ref * 2.0).backward()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert abs(loss.item() - ref.item()) < 1e-4 * max(1.0, abs(ref.item())) + tol
+    assert torch.allclose(logits.grad.float(), lr.grad, rtol=tol * 10, atol=tol)
+
+
+@pytest.mark.parametrize("h,w", [(8, 8), (7, 9), (112, 112)])
+def test_max_pool(h, w):
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(3)
+    x = _cl(torch.randn(2, 64, h, w, device=DEV)).relu().to(torch.bfloat16).requires_grad_()  # many ties at zero
+    y = ops.max_pool_3x3_s2(x)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = F.max_pool2d(xr, 3, 2, 1)
+    yr.backward(g.float())
+    assert torch.equal(y.float(), yr)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=1e-2, atol=2e-2)
+
+
+def test_global_avg_pool():
+    from eagersgd_b200.ops import functional as ops
+    x = _cl(torch.randn(4, 2048, 7, 7, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = ops.global_avg_pool(x)
+    g = torch.randn(4, 2048, device=DEV).to(torch.bfloat16)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = xr.mean((2, 3))
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=1e-2, atol=1e-2)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=1e-2, atol=1e-3)
+
+
+def test_linear_layer():
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(4)
+    x = torch.randn(64, 2048, device=DEV).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(1000, 2048, device=DEV) * 0.02).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(1000, device=DEV).to(torch.bfloat16).requires_grad_()
+    y = ops.linear(x, w, b)
+    g = torch.randn(64, 1000, device=DEV)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.linear(xr, wr, br)
+    yr.backward(g)
+    assert y.dtype == torch.float32 and torch.allclose(y, yr, rtol=1e-2, atol=2e-2)
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=2e-2, atol=0.2)
+    assert torch.allclose(b.grad.float(), br.grad, rtol=2e-2, atol=0.1)
+
+
+def test_resnet_native_matches_fp32_reference():
+    """Whole model: native bf16 NHWC path on the GPU vs the same weights in fp32 PyTorch ops."""
+    from eagersgd_b200.models.resnet import imagenet_resnet
+    from eagersgd_b200.train.step import prepare_model
+    torch.manual_seed(5)
+    ref = imagenet_resnet(50, 1, 1000).to(DEV)
+    for m in ref.modules():  # give the zero-initialised gammas a value so every branch carries signal
+        if isinstance(m, torch.nn.BatchNorm2d):
+            torch.nn.init.uniform_(m.weight, 0.5, 1.0)
+    import copy
+    nat = prepare_model(copy.deepcopy(ref), torch.device(DEV))
+    x = torch.randn(8, 3, 64, 64, device=DEV)
+    y = torch.randint(0, 1000, (8,), device=DEV)
+    lr_ = F.cross_entropy(ref(x), y)
+    lr_.backward()
+    from eagersgd_b200.ops.functional import softmax_cross_entropy
+    ln = softmax_cross_entropy(nat(_cl(x).to(torch.bfloat16)), y)
+    ln.backward()
+    assert abs(ln.item() - lr_.item()) < 0.15 * abs(lr_.item())
+    gr = torch.cat([p.grad.flatten() for p in ref.parameters()])
+    gn = torch.cat([p.grad.float().flatten() for p in nat.parameters()])
+    cos = F.cosine_similarity(gr, gn, dim=0).item()
+    assert cos > 0.9, cos
