@@ -106,34 +106,37 @@ __global__ void bn_finalize_kernel(const float* sum, const float* sqsum, const f
   }
 }
 
+// Threads keep a fixed group of 8 channels and walk over rows, so the per-channel
+// coefficients live in registers for the whole kernel.
 __global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __restrict__ y,
                                                        const __nv_bfloat16* __restrict__ res,
                                                        __nv_bfloat16* __restrict__ z, const float* __restrict__ scale,
-                                                       const float* __restrict__ shift, int64_t total_groups, int C,
-                                                       int relu) {
-  const int groups = C / 8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_groups;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int g = (int)(i % groups);
-    float v[8], sc[8], sh[8];
-    ld8(y + i * 8, v);
-    *reinterpret_cast<float4*>(sc) = *reinterpret_cast<const float4*>(scale + g * 8);
-    *reinterpret_cast<float4*>(sc + 4) = *reinterpret_cast<const float4*>(scale + g * 8 + 4);
-    *reinterpret_cast<float4*>(sh) = *reinterpret_cast<const float4*>(shift + g * 8);
-    *reinterpret_cast<float4*>(sh + 4) = *reinterpret_cast<const float4*>(shift + g * 8 + 4);
+                                                       const float* __restrict__ shift, int64_t M, int C, int relu) {
+  const Map mp = make_map(C);
+  const int gl = threadIdx.x % mp.g_per_blk, rl = threadIdx.x / mp.g_per_blk;
+  if (rl >= mp.rows_par) return;
+  for (int g = gl; g < mp.groups; g += mp.g_per_blk) {
+    float sc[8], sh[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) v[q] = v[q] * sc[q] + sh[q];
-    if (res != nullptr) {
-      float r[8];
-      ld8(res + i * 8, r);
+    for (int q = 0; q < 8; ++q) { sc[q] = scale[g * 8 + q]; sh[q] = shift[g * 8 + q]; }
+    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
+      const int64_t off = r * C + g * 8;
+      float v[8];
+      ld8(y + off, v);
 #pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] += r[q];
+      for (int q = 0; q < 8; ++q) v[q] = v[q] * sc[q] + sh[q];
+      if (res != nullptr) {
+        float rr[8];
+        ld8(res + off, rr);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] += rr[q];
+      }
+      if (relu) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = fmaxf(v[q], 0.0f);
+      }
+      st8(z + off, v);
     }
-    if (relu) {
-#pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] = fmaxf(v[q], 0.0f);
-    }
-    st8(z + i * 8, v);
   }
 }
 
@@ -184,42 +187,51 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
   }
 }
 
+// dy = a*g + b*y + c per channel, with a = gamma*invstd, b = -gamma*invstd^2*dgamma/M,
+// c = gamma*invstd*(mean*invstd*dgamma - dbeta)/M held in registers.
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
                     const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
                     const float* __restrict__ invstd, const float* __restrict__ gamma,
                     const float* __restrict__ dbeta, const float* __restrict__ dgamma,
-                    __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dres, int64_t total_groups, int C,
-                    int relu, float inv_count) {
-  const int groups = C / 8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_groups;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int g = (int)(i % groups);
-    float d[8], yy[8];
-    ld8(dz + i * 8, d);
-    ld8(y + i * 8, yy);
-    if (relu) {
-      float zz[8];
-      ld8(z + i * 8, zz);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
-    }
-    if (dres != nullptr) st8(dres + i * 8, d);
-    float o[8];
+                    __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dres, int64_t M, int C, int relu,
+                    float inv_count) {
+  const Map mp = make_map(C);
+  const int gl = threadIdx.x % mp.g_per_blk, rl = threadIdx.x / mp.g_per_blk;
+  if (rl >= mp.rows_par) return;
+  for (int g = gl; g < mp.groups; g += mp.g_per_blk) {
+    float ca[8], cb[8], cc[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const int c = g * 8 + q;
-      const float is = invstd[c];
-      const float xhat = (yy[q] - mean[c]) * is;
-      o[q] = gamma[c] * is * (d[q] - dbeta[c] * inv_count - xhat * dgamma[c] * inv_count);
+      const float is = invstd[c], gm = gamma[c], dg = dgamma[c] * inv_count, db = dbeta[c] * inv_count;
+      ca[q] = gm * is;
+      cb[q] = -gm * is * is * dg;
+      cc[q] = gm * is * (mean[c] * is * dg - db);
     }
-    st8(dy + i * 8, o);
+    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
+      const int64_t off = r * C + g * 8;
+      float d[8], yy[8];
+      ld8(dz + off, d);
+      ld8(y + off, yy);
+      if (relu) {
+        float zz[8];
+        ld8(z + off, zz);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
+      }
+      if (dres != nullptr) st8(dres + off, d);
+      float o[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o[q] = ca[q] * d[q] + cb[q] * yy[q] + cc[q];
+      st8(dy + off, o);
+    }
   }
 }
 
 int blocks_for(int64_t work_items, int per_block) {
   int64_t b = (work_items + per_block - 1) / per_block;
-  const int64_t cap = 148 * 8;
+  const int64_t cap = 148 * 16;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
@@ -252,9 +264,10 @@ int esgd_bn_finalize(const float* sum, const float* sqsum, const float* gamma, c
 int esgd_bn_apply(const void* y, const void* residual, void* z, const float* scale, const float* shift, int64_t M,
                   int C, int relu, void* stream) {
   if (C % 8) return -1;
-  int64_t groups = M * (C / 8);
-  bn_apply_kernel<<<blocks_for(groups, 256 * 4), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, (const __nv_bfloat16*)residual, (__nv_bfloat16*)z, scale, shift, groups, C, relu);
+  int g = C / 8 < 256 ? C / 8 : 256;
+  int rows_par = 256 / g;
+  bn_apply_kernel<<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, (const __nv_bfloat16*)residual, (__nv_bfloat16*)z, scale, shift, M, C, relu);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
@@ -276,10 +289,11 @@ int esgd_bn_bwd_apply(const void* dz, const void* z, const void* y, const float*
                       const float* gamma, const float* dbeta, const float* dgamma, void* dy, void* dres, int64_t M,
                       int C, int relu, void* stream) {
   if (C % 8) return -1;
-  int64_t groups = M * (C / 8);
-  bn_bwd_apply_kernel<<<blocks_for(groups, 256 * 4), 256, 0, (cudaStream_t)stream>>>(
+  int g = C / 8 < 256 ? C / 8 : 256;
+  int rows_par = 256 / g;
+  bn_bwd_apply_kernel<<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, gamma, dbeta,
-      dgamma, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, groups, C, relu, 1.0f / (float)M);
+      dgamma, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, M, C, relu, 1.0f / (float)M);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

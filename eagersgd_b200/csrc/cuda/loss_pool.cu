@@ -88,8 +88,8 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const float v[8]) {
 }
 
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                          __nv_bfloat16* __restrict__ y, int N, int H, int W, int C,
-                                                          int OH, int OW) {
+                                                          __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ idx,
+                                                          int N, int H, int W, int C, int OH, int OW) {
   const int G = C / 8;
   const int64_t total = (int64_t)N * OH * OW * G;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -99,8 +99,9 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const __nv_bfloat16* _
     const int oh = (int)(t % OH);
     const int n = (int)(t / OH);
     float m[8];
+    uint32_t first[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) m[q] = -FLT_MAX;
+    for (int q = 0; q < 8; ++q) { m[q] = -FLT_MAX; first[q] = 0; }
     for (int r = 0; r < 3; ++r) {
       const int h = oh * 2 - 1 + r;
       if (h < 0 || h >= H) continue;
@@ -110,15 +111,22 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const __nv_bfloat16* _
         float v[8];
         ld8(x + (((int64_t)n * H + h) * W + w) * C + g * 8, v);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) m[q] = fmaxf(m[q], v[q]);
+        for (int q = 0; q < 8; ++q)
+          if (v[q] > m[q]) { m[q] = v[q]; first[q] = (uint32_t)(r * 3 + s); }   // first maximum in scan order
       }
     }
     st8(y + i * 8, m);
+    if (idx != nullptr) {
+      uint2 pk;
+      pk.x = first[0] | (first[1] << 8) | (first[2] << 16) | (first[3] << 24);
+      pk.y = first[4] | (first[5] << 8) | (first[6] << 16) | (first[7] << 24);
+      *reinterpret_cast<uint2*>(idx + i * 8) = pk;
+    }
   }
 }
 
-// Gather form: an input pixel receives dy of every window whose first maximum (scan order) it is.
-__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+// Gather form: an input pixel receives dy of every window whose recorded arg-max it is.
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const uint8_t* __restrict__ idx,
                                                           const __nv_bfloat16* __restrict__ dy,
                                                           __nv_bfloat16* __restrict__ dx, int N, int H, int W, int C,
                                                           int OH, int OW) {
@@ -140,33 +148,53 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const __nv_bfloat16* _
       for (int b = 0; b < now; ++b) {
         const int ow = ows[b];
         if (ow >= OW) continue;
-        // position of (h, w) inside the window, in scan order
-        const int my_pos = (h - (oh * 2 - 1)) * 3 + (w - (ow * 2 - 1));
-        float best[8];
-        int first[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) { best[q] = -FLT_MAX; first[q] = -1; }
-        for (int r = 0; r < 3; ++r) {
-          const int hh = oh * 2 - 1 + r;
-          if (hh < 0 || hh >= H) continue;
-          for (int s = 0; s < 3; ++s) {
-            const int ww = ow * 2 - 1 + s;
-            if (ww < 0 || ww >= W) continue;
-            float v[8];
-            ld8(x + (((int64_t)n * H + hh) * W + ww) * C + g * 8, v);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              if (v[q] > best[q]) { best[q] = v[q]; first[q] = r * 3 + s; }
-          }
-        }
+        const uint32_t my_pos = (uint32_t)((h - (oh * 2 - 1)) * 3 + (w - (ow * 2 - 1)));
+        const int64_t o = (((int64_t)n * OH + oh) * OW + ow) * C + g * 8;
+        const uint2 pk = *reinterpret_cast<const uint2*>(idx + o);
         float d[8];
-        ld8(dy + ((((int64_t)n * OH + oh) * OW + ow) * C + g * 8), d);
+        ld8(dy + o, d);
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          if (first[q] == my_pos) acc[q] += d[q];
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t word = q < 4 ? pk.x : pk.y;
+          if (((word >> ((q & 3) * 8)) & 0xffu) == my_pos) acc[q] += d[q];
+        }
       }
     }
     st8(dx + i * 8, acc);
+  }
+}
+
+// ---- 2x spatial subsampling (the gather in front of a strided 1x1 convolution) ---------
+__global__ void __launch_bounds__(256) subsample2_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             __nv_bfloat16* __restrict__ y, int N, int H, int W,
+                                                             int C, int OH, int OW) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * OH * OW * G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    int64_t t = i / G;
+    const int ow = (int)(t % OW); t /= OW;
+    const int oh = (int)(t % OH);
+    const int n = (int)(t / OH);
+    *reinterpret_cast<uint4*>(y + i * 8) =
+        *reinterpret_cast<const uint4*>(x + (((int64_t)n * H + oh * 2) * W + ow * 2) * C + g * 8);
+  }
+}
+__global__ void __launch_bounds__(256) subsample2_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                             __nv_bfloat16* __restrict__ dx, int N, int H, int W,
+                                                             int C, int OH, int OW) {
+  const int G = C / 8;
+  const int64_t total = (int64_t)N * H * W * G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    int64_t t = i / G;
+    const int w = (int)(t % W); t /= W;
+    const int h = (int)(t % H);
+    const int n = (int)(t / H);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (!(h & 1) && !(w & 1))
+      v = *reinterpret_cast<const uint4*>(dy + (((int64_t)n * OH + h / 2) * OW + w / 2) * C + g * 8);
+    *reinterpret_cast<uint4*>(dx + i * 8) = v;
   }
 }
 
@@ -233,20 +261,39 @@ int esgd_softmax_ce(const void* logits, int is_bf16, const int64_t* labels, int 
   return (int)cudaGetLastError();
 }
 
-int esgd_maxpool3x3s2_fwd(const void* x, void* y, int N, int H, int W, int C, void* stream) {
+// idx (optional, one byte per output element) records the arg-max for the backward pass.
+int esgd_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, void* stream) {
   if (C % 8) return -1;
   const int OH = (H + 1) / 2, OW = (W + 1) / 2;
   maxpool_fwd_kernel<<<grid_for((int64_t)N * OH * OW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C, OH, OW);
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)idx, N, H, W, C, OH, OW);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
 
-int esgd_maxpool3x3s2_bwd(const void* x, const void* dy, void* dx, int N, int H, int W, int C, void* stream) {
+int esgd_maxpool3x3s2_bwd(const void* idx, const void* dy, void* dx, int N, int H, int W, int C, void* stream) {
   if (C % 8) return -1;
   const int OH = (H + 1) / 2, OW = (W + 1) / 2;
   maxpool_bwd_kernel<<<grid_for((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, OH, OW);
+      (const uint8_t*)idx, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, OH, OW);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+// y[n, oh, ow, :] = x[n, 2*oh, 2*ow, :]   (OH = ceil(H/2), OW = ceil(W/2))
+int esgd_subsample2_fwd(const void* x, void* y, int N, int H, int W, int C, void* stream) {
+  if (C % 8) return -1;
+  const int OH = (H + 1) / 2, OW = (W + 1) / 2;
+  subsample2_fwd_kernel<<<grid_for((int64_t)N * OH * OW * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C, OH, OW);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+int esgd_subsample2_bwd(const void* dy, void* dx, int N, int H, int W, int C, void* stream) {
+  if (C % 8) return -1;
+  const int OH = (H + 1) / 2, OW = (W + 1) / 2;
+  subsample2_bwd_kernel<<<grid_for((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, OH, OW);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

@@ -1,0 +1,278 @@
+// Persistent warp-specialised tcgen05 pipeline shared by the GEMM and the
+// implicit-GEMM convolution kernels.
+//
+//   warp 0     : TMA producer — the Problem policy issues the loads of one k-block
+//   warp 1     : tcgen05.mma issuer (one thread); two TMEM accumulators so the
+//                epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5 : epilogue — tcgen05.ld, bias / ReLU, bf16 tile staged in shared
+//                memory in the 128-byte-swizzled layout and written with a TMA
+//                store (coalesced, clipped at the tensor edge); per-channel sum and
+//                sum of squares of the stored tile are taken from shared memory and
+//                flushed with one atomic per column per CTA (batch-norm statistics)
+//
+// A tile is 128 rows x BN columns; a k-block is 64 bf16 (one 128-byte swizzle row).
+// Every mbarrier wait is bounded; on expiry the CTA raises an error flag, lets the
+// copies in flight land, frees its tensor memory and returns.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "sm100_primitives.cuh"
+
+namespace umma {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int PANEL_BYTES = BM * 64 * 2;     // one 128 x 64 bf16 output panel
+constexpr int NUM_THREADS = 192;
+
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
+
+struct Epilogue {
+  int out_mode;
+  int relu;
+  int n_total;             // number of valid output columns (channels)
+  const float* bias;       // per column, may be null
+  float* col_sum;          // optional per-column statistics of the stored bf16 values
+  float* col_sqsum;
+  int* error_flag;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * PANEL_BYTES + 1024 + 256;
+};
+
+// Problem policy requirements (all __device__ const):
+//   static constexpr int BN; static constexpr bool A_MN, B_MN;
+//   struct Tile { int kb0, kb1, n0; ... };
+//   bool tile(int it, Tile&)                       enumerate this CTA's tiles
+//   void load(const Tile&, int kb, uint8_t* a, uint8_t* b, uint64_t* bar)
+//   void store_panel(const Tile&, int panel, const void* smem)   TMA store of a 128x64 bf16 panel
+//   bool row_valid(const Tile&, int row)           row is a real output (statistics mask)
+//   void* row_ptr(const Tile&, int row)            fp32 output row pointer (direct modes), or nullptr
+template <class P>
+__device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
+  constexpr int BN = P::BN;
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + STAGES * A_STAGE_BYTES;
+  uint8_t* sC = sB + STAGES * C::B_STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sC + 2 * PANEL_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      typename P::Tile t;
+      for (int it = 0; ok && prob.tile(it, t); ++it) {
+        for (int kb = t.kb0; kb < t.kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], A_STAGE_BYTES + C::B_STAGE_BYTES);
+          prob.load(t, kb, sA + stage * A_STAGE_BYTES, sB + stage * C::B_STAGE_BYTES, &full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, P::A_MN ? 1 : 0, P::B_MN ? 1 : 0);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      typename P::Tile t;
+      for (int it = 0; ok && prob.tile(it, t); ++it) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = t.kb0; kb < t.kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * C::B_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            const uint64_t adesc = P::A_MN ? umma_smem_desc(a_addr + j * 2048, 8192, 1024)
+                                           : umma_smem_desc(a_addr + j * 32, 16, 1024);
+            const uint64_t bdesc = P::B_MN ? umma_smem_desc(b_addr + j * 2048, 8192, 1024)
+                                           : umma_smem_desc(b_addr + j * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > t.kb0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+    const int row = q * 32 + lane;          // tile row owned by this thread
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;                            // staging panel buffer in use
+    bool pending[2] = {false, false};       // a TMA store may still be reading the buffer (thread et == 0)
+    // statistics: thread (cp = et % 32, rq = et / 32) covers columns 2cp, 2cp+1 of each panel, rows 32rq..+32
+    float st_sum[BN / 64][2], st_sq[BN / 64][2];
+#pragma unroll
+    for (int pnl = 0; pnl < BN / 64; ++pnl) { st_sum[pnl][0] = st_sum[pnl][1] = st_sq[pnl][0] = st_sq[pnl][1] = 0.f; }
+    int stats_n0 = -1;
+    bool ok = true;
+    typename P::Tile t;
+    for (int it = 0; ok && prob.tile(it, t); ++it) {
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      stats_n0 = t.n0;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      if (ep.out_mode == OUT_BF16) {
+#pragma unroll 1
+        for (int pnl = 0; pnl < BN / 64; ++pnl) {
+          if (t.n0 + pnl * 64 >= ep.n_total) break;  // uniform across the CTA
+          uint8_t* panel = sC + buf * PANEL_BYTES;
+          if (et == 0 && pending[buf]) { tma_store_wait_read<1>(); pending[buf] = false; }
+          named_barrier_sync(1, 128);                // the buffer is free for everyone
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64 + half * 32), r);
+            tmem_ld_wait();
+            const int col0 = t.n0 + pnl * 64 + half * 32;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[j] = __uint_as_float(r[g * 8 + j]);
+                if (ep.bias != nullptr && col0 + g * 8 + j < ep.n_total) v[j] += __ldg(ep.bias + col0 + g * 8 + j);
+                if (ep.relu) v[j] = fmaxf(v[j], 0.0f);
+              }
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              const int chunk = half * 4 + g;        // 16-byte chunk within the 128-byte row
+              *reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
+            }
+          }
+          fence_proxy_async();
+          named_barrier_sync(1, 128);                // the panel is complete and visible to the TMA engine
+          if (et == 0) {
+            prob.store_panel(t, pnl, panel);
+            tma_store_commit();
+            pending[buf] = true;
+          }
+          if (ep.col_sum != nullptr) {
+            const int cp = et & 31, rq = et >> 5;
+            float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; ++rr) {
+              const int r_ = rq * 32 + rr;
+              if (!prob.row_valid(t, r_)) continue;
+              const int chunk = cp >> 2;
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(panel + r_ * 128 + ((chunk ^ (r_ & 7)) << 4) +
+                                                                    (cp & 3) * 4);
+              __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&w);
+              float2 f = __bfloat1622float2(hv);
+              s0 += f.x; s1 += f.y; q0 += f.x * f.x; q1 += f.y * f.y;
+            }
+            st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
+          }
+          buf ^= 1;
+        }
+      } else {
+        // fp32 outputs (logits, split-K weight gradients): direct stores / atomics from registers
+        float* out_row = reinterpret_cast<float*>(prob.row_ptr(t, row));
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          const int col0 = t.n0 + c * 32;
+          if (out_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < ep.n_total) {
+                float v = __uint_as_float(r[j]);
+                if (ep.bias != nullptr) v += __ldg(ep.bias + col0 + j);
+                if (ep.relu) v = fmaxf(v, 0.0f);
+                if (ep.out_mode == OUT_F32) out_row[col0 + j] = v;
+                else atomicAdd(out_row + col0 + j, v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (ep.col_sum != nullptr && stats_n0 >= 0) {   // one flush per CTA: its tiles share the column range
+      const int cp = et & 31;
+#pragma unroll
+      for (int pnl = 0; pnl < BN / 64; ++pnl) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int col = stats_n0 + pnl * 64 + cp * 2 + k;
+          if (col < ep.n_total) {
+            atomicAdd(ep.col_sum + col, st_sum[pnl][k]);
+            atomicAdd(ep.col_sqsum + col, st_sq[pnl][k]);
+          }
+        }
+      }
+    }
+    if (et == 0) tma_store_wait_all();               // shared memory must outlive the bulk stores
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    __nanosleep(1000000);
+    if (threadIdx.x == 0 && ep.error_flag != nullptr) atomicExch(ep.error_flag, 1);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace umma

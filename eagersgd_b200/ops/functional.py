@@ -30,7 +30,9 @@ def _lib():
         lib.esgd_bn_bwd_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp, vp, vp]
         lib.esgd_bn_bwd_apply.argtypes = [vp] * 10 + [i64, i32, i32, vp]
         lib.esgd_softmax_ce.argtypes = [vp, i32, vp, i32, i32, i32, f32, vp, vp, vp, vp]
-        lib.esgd_maxpool3x3s2_fwd.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        lib.esgd_maxpool3x3s2_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        lib.esgd_subsample2_fwd.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        lib.esgd_subsample2_bwd.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         lib.esgd_maxpool3x3s2_bwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
         lib.esgd_avgpool_fwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
@@ -61,8 +63,23 @@ def from_2d(y2d: torch.Tensor, n: int, h: int, w: int) -> torch.Tensor:
     return y2d.view(n, h, w, y2d.shape[1]).permute(0, 3, 1, 2)
 
 
+_reference_only = False
+
+
+class reference_ops:
+    """Context manager: run every op through its PyTorch restatement (the test oracle)."""
+
+    def __enter__(self):
+        global _reference_only
+        self._prev, _reference_only = _reference_only, True
+
+    def __exit__(self, *a):
+        global _reference_only
+        _reference_only = self._prev
+
+
 def native(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype == torch.bfloat16 and not _reference_only
 
 
 # --------------------------------------------------------------------------- 1x1 convolution / dense
@@ -109,6 +126,28 @@ def conv1x1(x: torch.Tensor, w: torch.Tensor, want_stats: bool = False):
     return y
 
 
+class _Subsample2(torch.autograd.Function):
+    """x[:, :, ::2, ::2] for NHWC tensors, with a one-pass scatter as its gradient."""
+
+    @staticmethod
+    def forward(ctx, x):
+        n, c, h, w = x.shape
+        x2d = nhwc_2d(x)
+        oh, ow = (h + 1) // 2, (w + 1) // 2
+        y2d = torch.empty(n * oh * ow, c, dtype=x.dtype, device=x.device)
+        _ck(_lib().esgd_subsample2_fwd(x2d.data_ptr(), y2d.data_ptr(), n, h, w, c, _stream(x)), "subsample")
+        ctx.dims = (n, c, h, w)
+        return from_2d(y2d, n, oh, ow)
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, c, h, w = ctx.dims
+        dy2d = nhwc_2d(dy)
+        dx2d = torch.empty(n * h * w, c, dtype=dy.dtype, device=dy.device)
+        _ck(_lib().esgd_subsample2_bwd(dy2d.data_ptr(), dx2d.data_ptr(), n, h, w, c, _stream(dy)), "subsample backward")
+        return from_2d(dx2d, n, h, w)
+
+
 def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, want_stats: bool = False):
     """NHWC convolution; returns ``(y, stats)`` (``stats`` is None unless produced by the kernel epilogue).
 
@@ -116,7 +155,9 @@ def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, 
     """
     k = w.shape[2]
     if k == 1 and native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
-        if stride > 1:
+        if stride == 2:
+            x = _Subsample2.apply(x)
+        elif stride > 1:
             x = x[:, :, ::stride, ::stride].contiguous(memory_format=torch.channels_last)
         out = conv1x1(x, w, want_stats)
         return out if want_stats else (out, None)
@@ -229,7 +270,8 @@ class _SoftmaxCE(torch.autograd.Function):
 
 def softmax_cross_entropy(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
     """Mean sparse softmax cross-entropy; forward and gradient come out of one kernel."""
-    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and labels.dtype == torch.int64:
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and labels.dtype == torch.int64 \
+            and not _reference_only:
         return _SoftmaxCE.apply(logits, labels)
     return F.cross_entropy(logits.float(), labels)
 
@@ -242,18 +284,20 @@ class _MaxPool(torch.autograd.Function):
         x2d = nhwc_2d(x)
         oh, ow = (h + 1) // 2, (w + 1) // 2
         y2d = torch.empty(n * oh * ow, c, dtype=x.dtype, device=x.device)
-        _ck(_lib().esgd_maxpool3x3s2_fwd(x2d.data_ptr(), y2d.data_ptr(), n, h, w, c, _stream(x)), "maxpool")
-        ctx.save_for_backward(x2d)
+        idx = torch.empty(n * oh * ow, c, dtype=torch.uint8, device=x.device)
+        _ck(_lib().esgd_maxpool3x3s2_fwd(x2d.data_ptr(), y2d.data_ptr(), idx.data_ptr(), n, h, w, c, _stream(x)),
+            "maxpool")
+        ctx.save_for_backward(idx)
         ctx.dims = (n, c, h, w, oh, ow)
         return from_2d(y2d, n, oh, ow)
 
     @staticmethod
     def backward(ctx, dy):
-        (x2d,) = ctx.saved_tensors
+        (idx,) = ctx.saved_tensors
         n, c, h, w, oh, ow = ctx.dims
         dy2d = nhwc_2d(dy)
-        dx2d = torch.empty_like(x2d)
-        _ck(_lib().esgd_maxpool3x3s2_bwd(x2d.data_ptr(), dy2d.data_ptr(), dx2d.data_ptr(), n, h, w, c, _stream(dy)),
+        dx2d = torch.empty(n * h * w, c, dtype=dy.dtype, device=dy.device)
+        _ck(_lib().esgd_maxpool3x3s2_bwd(idx.data_ptr(), dy2d.data_ptr(), dx2d.data_ptr(), n, h, w, c, _stream(dy)),
             "maxpool backward")
         return from_2d(dx2d, n, h, w)
 

@@ -66,10 +66,28 @@ def test_gemm_epilogue_bias_relu_stats():
     bias = torch.randn(N, device=DEV)
     s = torch.zeros(N, device=DEV)
     s2 = torch.zeros(N, device=DEV)
-    c = gemm(a, b, bias=bias, relu=True, out_dtype=torch.float32, col_sum=s, col_sqsum=s2)
+    c = gemm(a, b, bias=bias, relu=True, out_dtype=torch.float32)
+    cb = gemm(a, b, bias=bias, col_sum=s, col_sqsum=s2)      # bf16 output + statistics of the stored values
     torch.cuda.synchronize()
     check_error(a.device)
     pre = _ref(a, b, True, True) + bias
     assert torch.allclose(c, pre.relu(), rtol=2e-3, atol=2e-2)
-    assert torch.allclose(s, pre.sum(0), rtol=2e-3, atol=0.5)
-    assert torch.allclose(s2, (pre * pre).sum(0), rtol=2e-3, atol=5.0)
+    assert torch.allclose(cb.float(), pre, rtol=1e-2, atol=0.1)
+    assert torch.allclose(s, cb.float().sum(0), rtol=1e-3, atol=0.5)
+    assert torch.allclose(s2, (cb.float() ** 2).sum(0), rtol=1e-3, atol=5.0)
+
+
+@pytest.mark.parametrize("M,N", [(1000, 1000), (130, 72), (802816 // 16, 256), (777, 2048)])
+def test_gemm_stats_tails_and_many_tiles(M, N):
+    from eagersgd_b200.ops.gemm import gemm, check_error
+    torch.manual_seed(M)
+    a, b = _rand((M, 64)), _rand((N, 64))
+    s = torch.zeros(N, device=DEV)
+    s2 = torch.zeros(N, device=DEV)
+    c = gemm(a, b, col_sum=s, col_sqsum=s2)
+    torch.cuda.synchronize()
+    check_error(a.device)
+    ref = _ref(a, b, True, True)
+    assert torch.allclose(c.float(), ref, rtol=2e-2, atol=0.1)
+    assert torch.allclose(s, c.float().sum(0), rtol=2e-3, atol=1.0)
+    assert torch.allclose(s2, (c.float() ** 2).sum(0), rtol=2e-3, atol=10.0)

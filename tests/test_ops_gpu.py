@@ -126,26 +126,62 @@ def test_linear_layer():
     assert torch.allclose(b.grad.float(), br.grad, rtol=2e-2, atol=0.1)
 
 
-def test_resnet_native_matches_fp32_reference():
-    """Whole model: native bf16 NHWC path on the GPU vs the same weights in fp32 PyTorch ops."""
+def test_resnet_native_matches_references():
+    """Whole model: native bf16 NHWC kernels vs (a) the same bf16 model through PyTorch ops and
+    (b) fp32 PyTorch.  The bf16-vs-fp32 gap of PyTorch's own ops calibrates the tolerance."""
+    import copy
     from eagersgd_b200.models.resnet import imagenet_resnet
+    from eagersgd_b200.ops import functional as ops
     from eagersgd_b200.train.step import prepare_model
     torch.manual_seed(5)
-    ref = imagenet_resnet(50, 1, 1000).to(DEV)
+    ref = imagenet_resnet(18, 1, 1000).to(DEV)
     for m in ref.modules():  # give the zero-initialised gammas a value so every branch carries signal
         if isinstance(m, torch.nn.BatchNorm2d):
             torch.nn.init.uniform_(m.weight, 0.5, 1.0)
-    import copy
     nat = prepare_model(copy.deepcopy(ref), torch.device(DEV))
-    x = torch.randn(8, 3, 64, 64, device=DEV)
-    y = torch.randint(0, 1000, (8,), device=DEV)
-    lr_ = F.cross_entropy(ref(x), y)
-    lr_.backward()
-    from eagersgd_b200.ops.functional import softmax_cross_entropy
-    ln = softmax_cross_entropy(nat(_cl(x).to(torch.bfloat16)), y)
+    tor = copy.deepcopy(nat)
+    x = torch.randn(32, 3, 96, 96, device=DEV)
+    y = torch.randint(0, 1000, (32,), device=DEV)
+    F.cross_entropy(ref(x), y).backward()
+    xb = _cl(x).to(torch.bfloat16)
+    ln = ops.softmax_cross_entropy(nat(xb), y)
     ln.backward()
-    assert abs(ln.item() - lr_.item()) < 0.15 * abs(lr_.item())
-    gr = torch.cat([p.grad.flatten() for p in ref.parameters()])
-    gn = torch.cat([p.grad.float().flatten() for p in nat.parameters()])
-    cos = F.cosine_similarity(gr, gn, dim=0).item()
-    assert cos > 0.9, cos
+    with ops.reference_ops():
+        lt = ops.softmax_cross_entropy(tor(xb), y)
+        lt.backward()
+    flat = lambda m: torch.cat([p.grad.float().flatten() for p in m.parameters()])
+    g32, gn, gt = flat(ref), flat(nat), flat(tor)
+    cos_nt = F.cosine_similarity(gn, gt, dim=0).item()
+    cos_t32 = F.cosine_similarity(gt, g32, dim=0).item()
+    cos_n32 = F.cosine_similarity(gn, g32, dim=0).item()
+    print("cos native/torch-bf16 %.4f torch-bf16/fp32 %.4f native/fp32 %.4f" % (cos_nt, cos_t32, cos_n32))
+    assert abs(ln.item() - lt.item()) < 0.05 * abs(lt.item())
+    assert cos_n32 > min(0.97, cos_t32 - 0.03), (cos_nt, cos_t32, cos_n32)
+
+
+def test_bottleneck_block_matches_reference_ops():
+    """One bottleneck block with projection and stride (all conv paths of ResNet-50)."""
+    import copy
+    from eagersgd_b200.models.resnet import _Block
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(6)
+    blk = _Block(64, 32, 2, "bottleneck", 1, True, []).to(DEV)
+    for m in blk.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            torch.nn.init.uniform_(m.weight, 0.5, 1.0)
+        if isinstance(m, torch.nn.Conv2d):
+            m.to(torch.bfloat16)
+    blk2 = copy.deepcopy(blk)
+    x = _cl(torch.randn(8, 64, 16, 16, device=DEV)).to(torch.bfloat16)
+    x1, x2 = x.clone().requires_grad_(), x.clone().requires_grad_()
+    g = _cl(torch.randn(8, 128, 8, 8, device=DEV)).to(torch.bfloat16)
+    z1 = blk(x1)
+    z1.backward(g)
+    with ops.reference_ops():
+        z2 = blk2(x2)
+        z2.backward(g)
+    assert torch.allclose(z1.float(), z2.float(), rtol=5e-2, atol=5e-2)
+    assert F.cosine_similarity(x1.grad.float().flatten(), x2.grad.float().flatten(), dim=0).item() > 0.99
+    for (n1, p1), (_, p2) in zip(blk.named_parameters(), blk2.named_parameters()):
+        c = F.cosine_similarity(p1.grad.float().flatten(), p2.grad.float().flatten(), dim=0).item()
+        assert c > 0.98, (n1, c)
