@@ -38,6 +38,7 @@ struct Epilogue {
   float* col_sum;          // optional per-column statistics of the stored bf16 values
   float* col_sqsum;
   int* error_flag;
+  uint32_t a_tx_bytes;     // bytes one k-block's A loads deliver (0: a full 128 x 64 tile)
 };
 
 template <int BN>
@@ -100,7 +101,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       for (int it = 0; ok && prob.tile(it, t); ++it) {
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[stage], A_STAGE_BYTES + C::B_STAGE_BYTES);
+          mbar_expect_tx(&full[stage], (ep.a_tx_bytes ? ep.a_tx_bytes : (uint32_t)A_STAGE_BYTES) + C::B_STAGE_BYTES);
           prob.load(t, kb, sA + stage * A_STAGE_BYTES, sB + stage * C::B_STAGE_BYTES, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }

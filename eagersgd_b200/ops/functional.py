@@ -36,6 +36,7 @@ def _lib():
         lib.esgd_maxpool3x3s2_bwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
         lib.esgd_avgpool_fwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
+        lib.esgd_conv2d_fwd.argtypes = [vp, vp, vp] + [i32] * 10 + [vp, vp, vp, vp]
         lib._nn_bound = True
     return lib
 
@@ -126,6 +127,59 @@ def conv1x1(x: torch.Tensor, w: torch.Tensor, want_stats: bool = False):
     return y
 
 
+def _conv_native(x2d_src, w_ohwi, n, h, w, cin, cout, r, s, stride, pad, stats):
+    """Launch the implicit-GEMM kernel.  ``x2d_src``: NHWC storage, ``w_ohwi``: [Cout, R, S, Cin] storage."""
+    from .gemm import error_flag
+    ho, wo = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - s) // stride + 1
+    y2d = torch.empty(n * ho * wo, cout, dtype=torch.bfloat16, device=x2d_src.device)
+    _ck(_lib().esgd_conv2d_fwd(x2d_src.data_ptr(), w_ohwi.data_ptr(), y2d.data_ptr(), n, h, w, cin, cout, r, s,
+                               stride, pad, 0, _ptr(stats[0]) if stats is not None else None,
+                               _ptr(stats[1]) if stats is not None else None,
+                               error_flag(x2d_src.device).data_ptr(), _stream(x2d_src)), "conv2d")
+    return y2d, ho, wo
+
+
+class _ConvKxK(torch.autograd.Function):
+    """RxS convolution as an implicit GEMM on the tensor cores (TMA-fed, zero-filled padding)."""
+
+    @staticmethod
+    def forward(ctx, x, w, stride, pad, want_stats):
+        n, cin, h, wd = x.shape
+        cout, _, r, s = w.shape
+        x2d = nhwc_2d(x)
+        w_cl = w.contiguous(memory_format=torch.channels_last)        # [Cout, R, S, Cin] in memory
+        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        y2d, ho, wo = _conv_native(x2d, w_cl, n, h, wd, cin, cout, r, s, stride, pad, stats)
+        ctx.save_for_backward(x, w_cl)
+        ctx.cfg = (stride, pad)
+        y = from_2d(y2d, n, ho, wo)
+        if want_stats:
+            ctx.mark_non_differentiable(stats)
+            return y, stats
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, *unused):
+        x, w = ctx.saved_tensors
+        stride, pad = ctx.cfg
+        n, cin, h, wd = x.shape
+        cout, _, r, s = w.shape
+        dx = dw = None
+        dy_cl = dy.contiguous(memory_format=torch.channels_last)
+        if ctx.needs_input_grad[0]:
+            if stride == 1 and cout % 64 == 0 and cin % 8 == 0:
+                # dx = conv(dy, rot180(w) with in/out channels swapped), padding R-1-pad
+                w_t = w.flip(2, 3).transpose(0, 1).contiguous(memory_format=torch.channels_last)
+                dx2d, _, _ = _conv_native(nhwc_2d(dy_cl), w_t, n, dy.shape[2], dy.shape[3], cout, cin, r, s, 1,
+                                          r - 1 - pad, None)
+                dx = from_2d(dx2d, n, h, wd)
+            else:
+                dx = torch.nn.grad.conv2d_input(x.shape, w, dy_cl, stride=stride, padding=pad)
+        if ctx.needs_input_grad[1]:
+            dw = torch.nn.grad.conv2d_weight(x, w.shape, dy_cl, stride=stride, padding=pad)
+        return dx, dw, None, None, None
+
+
 class _Subsample2(torch.autograd.Function):
     """x[:, :, ::2, ::2] for NHWC tensors, with a one-pass scatter as its gradient."""
 
@@ -160,6 +214,9 @@ def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, 
         elif stride > 1:
             x = x[:, :, ::stride, ::stride].contiguous(memory_format=torch.channels_last)
         out = conv1x1(x, w, want_stats)
+        return out if want_stats else (out, None)
+    if k > 1 and native(x) and x.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and stride in (1, 2):
+        out = _ConvKxK.apply(x, w, stride, padding, want_stats)
         return out if want_stats else (out, None)
     return F.conv2d(x, w, None, stride, padding), None
 

@@ -1,0 +1,60 @@
+"""Implicit-GEMM convolution (tcgen05 + 4-D TMA) against PyTorch fp32 convolution."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cl(x):
+    return x.contiguous(memory_format=torch.channels_last)
+
+
+CASES = [  # n, cin, h, w, cout, k, stride, pad
+    (2, 64, 56, 56, 64, 3, 1, 1),
+    (3, 128, 28, 28, 128, 3, 1, 1),
+    (4, 256, 14, 14, 256, 3, 1, 1),
+    (5, 512, 7, 7, 512, 3, 1, 1),
+    (2, 64, 16, 24, 72, 3, 1, 1),
+    (2, 128, 56, 56, 128, 3, 2, 1),
+    (3, 256, 28, 28, 256, 3, 2, 1),
+    (2, 512, 14, 14, 512, 3, 2, 1),
+    (1, 64, 130, 130, 64, 3, 1, 1),
+    (2, 64, 20, 20, 64, 5, 1, 2),
+]
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", CASES)
+def test_conv_forward(n, cin, h, w, cout, k, stride, pad):
+    from eagersgd_b200.ops import functional as ops
+    from eagersgd_b200.ops.gemm import check_error
+    torch.manual_seed(n * 7 + cin + h)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16)
+    wt = _cl(torch.randn(cout, cin, k, k, device=DEV) * (1.0 / (k * cin ** 0.5))).to(torch.bfloat16)
+    y, stats = ops.conv2d(x, wt, stride, pad, want_stats=True)
+    torch.cuda.synchronize()
+    check_error(x.device)
+    ref = F.conv2d(x.float(), wt.float(), None, stride, pad)
+    assert y.shape == ref.shape
+    err = (y.float() - ref).abs().max().item()
+    assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+    assert stats is not None
+    yf = y.float()
+    assert torch.allclose(stats[0], yf.sum((0, 2, 3)), rtol=1e-3, atol=0.5)
+    assert torch.allclose(stats[1], (yf * yf).sum((0, 2, 3)), rtol=1e-3, atol=0.5)
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", [CASES[0], CASES[2], CASES[3], CASES[5]])
+def test_conv_backward(n, cin, h, w, cout, k, stride, pad):
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(11)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16).requires_grad_()
+    wt = _cl(torch.randn(cout, cin, k, k, device=DEV) * (1.0 / (k * cin ** 0.5))).to(torch.bfloat16).requires_grad_()
+    y, _ = ops.conv2d(x, wt, stride, pad)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), wt.detach().float().requires_grad_()
+    F.conv2d(xr, wr, None, stride, pad).backward(g.float())
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2 * xr.grad.abs().max().item())
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
