@@ -41,6 +41,7 @@ def parse_args():
     ap.add_argument("--imbalance", default="auto", choices=["auto", "none"],
                     help="auto: each step 2 random ranks are delayed by Exp(0.5 x step time) when N > 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of one CUDA graph")
     return ap.parse_args()
 
 
@@ -156,6 +157,10 @@ def main():
         group.barrier()
         torch.cuda.synchronize()
 
+    use_graph = args.impl == "ours" and not args.no_graph
+    if use_graph:
+        step.capture(*dev_batches[0])
+
     # ---- warm-up (untimed), also measures the undisturbed step time ----
     for i in range(max(args.warmup, 3)):
         if i == max(args.warmup, 3) - 2:
@@ -202,7 +207,8 @@ def main():
         clocks = sampler.stop()
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()), clocks, N.launch_count() - launches0, last
+        launched = N.launch_count() - launches0 + args.steps * step.graph_kernel_launches
+        return float(ms.item()), clocks, launched, last
 
     ms_dev, clocks, launches, _ = timed(step.run_device, dev_batches)
     e2e = None
@@ -225,7 +231,7 @@ def main():
             "config": {"model": name, "global_batch": batch * world, "per_gpu_batch": batch, "seq_len": None,
                        "image": [res, res, 3], "classes": classes, "parallelism": "dp%d" % world,
                        "collective": args.mode + "-allreduce" if args.impl == "ours" else "nccl-allreduce",
-                       "bucket_mb": args.bucket_mb, "limiter": args.limiter,
+                       "bucket_mb": args.bucket_mb, "limiter": args.limiter, "cuda_graph": use_graph,
                        "optimizer": "momentum SGD 0.9, wd 1e-4, fp32 master weights",
                        "imbalance": ("2 random ranks/step delayed by Exp(mean 0.5 x %.1f ms)" % (base_step_s * 1e3))
                        if inject else "none (single rank)" if world == 1 else "none",

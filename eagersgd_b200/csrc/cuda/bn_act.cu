@@ -60,11 +60,23 @@ __global__ void __launch_bounds__(256) bn_stats_kernel(const __nv_bfloat16* __re
     const int g = g0 + gl;
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (g < mp.groups && rl < mp.rows_par) {
-      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
-        float v[8];
-        ld8(y + r * C + g * 8, v);
+      const int64_t step = (int64_t)gridDim.x * mp.rows_par;
+      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += 4 * step) {
+        uint4 raw[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) { a[q] += v[q]; b[q] += v[q] * v[q]; }
+        for (int u = 0; u < 4; ++u)
+          if (r + u * step < M) raw[u] = *reinterpret_cast<const uint4*>(y + (r + u * step) * C + g * 8);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (r + u * step < M) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float2 f = __bfloat1622float2(h[q]);
+              a[2 * q] += f.x; a[2 * q + 1] += f.y; b[2 * q] += f.x * f.x; b[2 * q + 1] += f.y * f.y;
+            }
+          }
+        }
       }
     }
 #pragma unroll
@@ -119,23 +131,38 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __re
     float sc[8], sh[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) { sc[q] = scale[g * 8 + q]; sh[q] = shift[g * 8 + q]; }
-    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
-      const int64_t off = r * C + g * 8;
-      float v[8];
-      ld8(y + off, v);
+    const int64_t step = (int64_t)gridDim.x * mp.rows_par;
+    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += 4 * step) {
+      uint4 ry[4], rr_[4];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] = v[q] * sc[q] + sh[q];
-      if (res != nullptr) {
-        float rr[8];
-        ld8(res + off, rr);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) v[q] += rr[q];
+      for (int u = 0; u < 4; ++u) {
+        const int64_t rr = r + u * step;
+        if (rr < M) {
+          ry[u] = *reinterpret_cast<const uint4*>(y + rr * C + g * 8);
+          if (res != nullptr) rr_[u] = *reinterpret_cast<const uint4*>(res + rr * C + g * 8);
+        }
       }
-      if (relu) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) v[q] = fmaxf(v[q], 0.0f);
+      for (int u = 0; u < 4; ++u) {
+        const int64_t rr = r + u * step;
+        if (rr < M) {
+          const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&ry[u]);
+          const __nv_bfloat162* hr = reinterpret_cast<const __nv_bfloat162*>(&rr_[u]);
+          float v[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 f = __bfloat1622float2(hy[q]);
+            v[2 * q] = f.x * sc[2 * q] + sh[2 * q];
+            v[2 * q + 1] = f.y * sc[2 * q + 1] + sh[2 * q + 1];
+            if (res != nullptr) {
+              float2 rf = __bfloat1622float2(hr[q]);
+              v[2 * q] += rf.x; v[2 * q + 1] += rf.y;
+            }
+            if (relu) { v[2 * q] = fmaxf(v[2 * q], 0.0f); v[2 * q + 1] = fmaxf(v[2 * q + 1], 0.0f); }
+          }
+          st8(z + rr * C + g * 8, v);
+        }
       }
-      st8(z + off, v);
     }
   }
 }
@@ -152,22 +179,45 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
     const int g = g0 + gl;
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (g < mp.groups && rl < mp.rows_par) {
-      float mu[8], is[8];
+      float mu[8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) { mu[q] = mean[g * 8 + q]; is[q] = invstd[g * 8 + q]; }
-      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
-        float d[8], yy[8];
-        ld8(dz + r * C + g * 8, d);
-        ld8(y + r * C + g * 8, yy);
-        if (relu) {
-          float zz[8];
-          ld8(z + r * C + g * 8, zz);
+      for (int q = 0; q < 8; ++q) mu[q] = mean[g * 8 + q];
+      const int64_t step = (int64_t)gridDim.x * mp.rows_par;
+      // sum g and g*(y - mean); the 1/std factor is applied once at the end.  Four rows in flight.
+      for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += 4 * step) {
+        uint4 rd[4], ry[4], rz[4];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
+        for (int u = 0; u < 4; ++u) {
+          const int64_t rr = r + u * step;
+          if (rr < M) {
+            const int64_t off = rr * C + g * 8;
+            rd[u] = *reinterpret_cast<const uint4*>(dz + off);
+            ry[u] = *reinterpret_cast<const uint4*>(y + off);
+            if (relu) rz[u] = *reinterpret_cast<const uint4*>(z + off);
+          }
         }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) { a[q] += d[q]; b[q] += d[q] * (yy[q] - mu[q]) * is[q]; }
+        for (int u = 0; u < 4; ++u) {
+          if (r + u * step < M) {
+            const __nv_bfloat162* hd = reinterpret_cast<const __nv_bfloat162*>(&rd[u]);
+            const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&ry[u]);
+            const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&rz[u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float2 d = __bfloat1622float2(hd[q]), yy = __bfloat1622float2(hy[q]);
+              if (relu) {
+                float2 zz = __bfloat1622float2(hz[q]);
+                d.x = zz.x > 0.0f ? d.x : 0.0f;
+                d.y = zz.y > 0.0f ? d.y : 0.0f;
+              }
+              a[2 * q] += d.x; a[2 * q + 1] += d.y;
+              b[2 * q] += d.x * (yy.x - mu[2 * q]); b[2 * q + 1] += d.y * (yy.y - mu[2 * q + 1]);
+            }
+          }
+        }
       }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) b[q] *= invstd[g * 8 + q];
     }
 #pragma unroll
     for (int q = 0; q < 8; ++q) { s_a[threadIdx.x * 8 + q] = a[q]; s_b[threadIdx.x * 8 + q] = b[q]; }
@@ -209,22 +259,44 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* _
       cb[q] = -gm * is * is * dg;
       cc[q] = gm * is * (mean[c] * is * dg - db);
     }
-    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += (int64_t)gridDim.x * mp.rows_par) {
-      const int64_t off = r * C + g * 8;
-      float d[8], yy[8];
-      ld8(dz + off, d);
-      ld8(y + off, yy);
-      if (relu) {
-        float zz[8];
-        ld8(z + off, zz);
+    const int64_t step = (int64_t)gridDim.x * mp.rows_par;
+    for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += 4 * step) {
+      uint4 rd[4], ry[4], rz[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) d[q] = zz[q] > 0.0f ? d[q] : 0.0f;
+      for (int u = 0; u < 4; ++u) {
+        const int64_t rr = r + u * step;
+        if (rr < M) {
+          const int64_t off = rr * C + g * 8;
+          rd[u] = *reinterpret_cast<const uint4*>(dz + off);
+          ry[u] = *reinterpret_cast<const uint4*>(y + off);
+          if (relu) rz[u] = *reinterpret_cast<const uint4*>(z + off);
+        }
       }
-      if (dres != nullptr) st8(dres + off, d);
-      float o[8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) o[q] = ca[q] * d[q] + cb[q] * yy[q] + cc[q];
-      st8(dy + off, o);
+      for (int u = 0; u < 4; ++u) {
+        const int64_t rr = r + u * step;
+        if (rr < M) {
+          const int64_t off = rr * C + g * 8;
+          const __nv_bfloat162* hd = reinterpret_cast<const __nv_bfloat162*>(&rd[u]);
+          const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&ry[u]);
+          const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&rz[u]);
+          float d[8], o[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 dd = __bfloat1622float2(hd[q]), yy = __bfloat1622float2(hy[q]);
+            if (relu) {
+              float2 zz = __bfloat1622float2(hz[q]);
+              dd.x = zz.x > 0.0f ? dd.x : 0.0f;
+              dd.y = zz.y > 0.0f ? dd.y : 0.0f;
+            }
+            d[2 * q] = dd.x; d[2 * q + 1] = dd.y;
+            o[2 * q] = ca[2 * q] * dd.x + cb[2 * q] * yy.x + cc[2 * q];
+            o[2 * q + 1] = ca[2 * q + 1] * dd.y + cb[2 * q + 1] * yy.y + cc[2 * q + 1];
+          }
+          if (dres != nullptr) st8(dres + off, d);
+          st8(dy + off, o);
+        }
+      }
     }
   }
 }

@@ -185,11 +185,20 @@ class EagerOptimizer:
         vals = (float(pg.get("lr", 0.0)), float(pg.get("momentum", 0.0)), float(pg.get("weight_decay", 0.0)),
                 1.0 if pg.get("nesterov", False) else 0.0, float(getattr(self, "grad_scale", 1.0)))
         if force or vals != b.hyper_vals:
+            if torch.cuda.is_current_stream_capturing():
+                return  # a captured step reads the device copy; sync_hyper() refreshes it before a replay
             b.hyper_vals = vals
             for i, v in enumerate(vals):
                 b.hyper_host[i] = v
-            with torch.cuda.stream(self.comm_stream):
-                b.hyper.copy_(b.hyper_host, non_blocking=True)
+            # on the current stream: the side stream waits for it before every launch
+            b.hyper.copy_(b.hyper_host, non_blocking=True)
+
+    def sync_hyper(self):
+        """Push lr / momentum / weight decay to the device copies the fused kernels read.
+        Needed before replaying a CUDA graph that contains ``step()``."""
+        if self.on_gpu:
+            for b in self.buckets:
+                self._refresh_hyper(b)
 
     def _install_hooks(self):
         for b in self.buckets:

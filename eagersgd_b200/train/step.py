@@ -67,8 +67,40 @@ class TrainStep:
             self.opt = cls(inner, group, **kw)
             self.autocast = False
         self._xbuf = self._ybuf = None
+        self._graph = None
+        self.graph_kernel_launches = 0
+
+    def capture(self, x: torch.Tensor, y: torch.Tensor, warmup: int = 2) -> None:
+        """Capture the whole step (forward, backward, bucketed partial allreduce with the
+        fused update on its side stream) into one CUDA graph: a replay costs one launch.
+        ``warmup`` real training steps run first; every rank must call this the same way."""
+        assert self.device.type == "cuda" and self.impl != "ddp"
+        self._gx, self._gy = x.clone(), y.clone()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._step(self._gx, self._gy)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        n0 = N.launch_count()
+        with torch.cuda.graph(graph):
+            self._gloss = self._step(self._gx, self._gy)
+        self.graph_kernel_launches = N.launch_count() - n0   # kernels of this package inside one replay
+        self._graph = graph
 
     def run_device(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        if self._graph is not None:
+            if x.data_ptr() != self._gx.data_ptr():
+                self._gx.copy_(x, non_blocking=True)
+                self._gy.copy_(y, non_blocking=True)
+            self.opt.sync_hyper()
+            self._graph.replay()
+            return self._gloss
+        return self._step(x, y)
+
+    def _step(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         self.opt.zero_grad()
         if self.autocast:
             with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -83,7 +115,9 @@ class TrainStep:
 
     def run_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> float:
         """End to end: pinned host batch in, python float loss out."""
-        if self._xbuf is None or self._xbuf.shape != x_host.shape:
+        if self._graph is not None:
+            self._xbuf, self._ybuf = self._gx, self._gy   # copy straight into the graph's input buffers
+        elif self._xbuf is None or self._xbuf.shape != x_host.shape:
             self._xbuf = torch.empty_like(x_host, device=self.device)
             self._ybuf = torch.empty_like(y_host, device=self.device)
         self._xbuf.copy_(x_host, non_blocking=True)
