@@ -18,16 +18,6 @@
 
 namespace {
 
-__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float v[8]) {
-  uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float2 f = __bfloat1622float2(h[q]);
-    v[2 * q] = f.x;
-    v[2 * q + 1] = f.y;
-  }
-}
 __device__ __forceinline__ void st8(__nv_bfloat16* p, const float v[8]) {
   uint4 raw;
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
@@ -167,10 +157,11 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __re
   }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
                      const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
-                     const float* __restrict__ invstd, int64_t M, int C, int relu, float* __restrict__ dbeta,
+                     const float* __restrict__ invstd, const float* __restrict__ fscale,
+                     const float* __restrict__ fshift, int64_t M, int C, int relu, float* __restrict__ dbeta,
                      float* __restrict__ dgamma) {
   const Map mp = make_map(C);
   __shared__ float s_a[256 * 8], s_b[256 * 8];
@@ -179,9 +170,13 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
     const int g = g0 + gl;
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (g < mp.groups && rl < mp.rows_par) {
-      float mu[8];
+      float mu[8], fsc[8], fsh[8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) mu[q] = mean[g * 8 + q];
+      for (int q = 0; q < 8; ++q) {
+        mu[q] = mean[g * 8 + q];
+        fsc[q] = relu == 2 ? fscale[g * 8 + q] : 0.0f;
+        fsh[q] = relu == 2 ? fshift[g * 8 + q] : 0.0f;
+      }
       const int64_t step = (int64_t)gridDim.x * mp.rows_par;
       // sum g and g*(y - mean); the 1/std factor is applied once at the end.  Four rows in flight.
       for (int64_t r = (int64_t)blockIdx.x * mp.rows_par + rl; r < M; r += 4 * step) {
@@ -193,7 +188,7 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
             const int64_t off = rr * C + g * 8;
             rd[u] = *reinterpret_cast<const uint4*>(dz + off);
             ry[u] = *reinterpret_cast<const uint4*>(y + off);
-            if (relu) rz[u] = *reinterpret_cast<const uint4*>(z + off);
+            if (relu == 1) rz[u] = *reinterpret_cast<const uint4*>(z + off);
           }
         }
 #pragma unroll
@@ -205,10 +200,13 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               float2 d = __bfloat1622float2(hd[q]), yy = __bfloat1622float2(hy[q]);
-              if (relu) {
+              if (relu == 1) {
                 float2 zz = __bfloat1622float2(hz[q]);
                 d.x = zz.x > 0.0f ? d.x : 0.0f;
                 d.y = zz.y > 0.0f ? d.y : 0.0f;
+              } else if (relu == 2) {   // no residual: the sign of the activation follows from y alone
+                d.x = yy.x * fsc[2 * q] + fsh[2 * q] > 0.0f ? d.x : 0.0f;
+                d.y = yy.y * fsc[2 * q + 1] + fsh[2 * q + 1] > 0.0f ? d.y : 0.0f;
               }
               a[2 * q] += d.x; a[2 * q + 1] += d.y;
               b[2 * q] += d.x * (yy.x - mu[2 * q]); b[2 * q + 1] += d.y * (yy.y - mu[2 * q + 1]);
@@ -239,21 +237,24 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
 
 // dy = a*g + b*y + c per channel, with a = gamma*invstd, b = -gamma*invstd^2*dgamma/M,
 // c = gamma*invstd*(mean*invstd*dgamma - dbeta)/M held in registers.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
                     const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
                     const float* __restrict__ invstd, const float* __restrict__ gamma,
                     const float* __restrict__ dbeta, const float* __restrict__ dgamma,
+                    const float* __restrict__ fscale, const float* __restrict__ fshift,
                     __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dres, int64_t M, int C, int relu,
                     float inv_count) {
   const Map mp = make_map(C);
   const int gl = threadIdx.x % mp.g_per_blk, rl = threadIdx.x / mp.g_per_blk;
   if (rl >= mp.rows_par) return;
   for (int g = gl; g < mp.groups; g += mp.g_per_blk) {
-    float ca[8], cb[8], cc[8];
+    float ca[8], cb[8], cc[8], fsc[8], fsh[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const int c = g * 8 + q;
+      fsc[q] = relu == 2 ? fscale[c] : 0.0f;
+      fsh[q] = relu == 2 ? fshift[c] : 0.0f;
       const float is = invstd[c], gm = gamma[c], dg = dgamma[c] * inv_count, db = dbeta[c] * inv_count;
       ca[q] = gm * is;
       cb[q] = -gm * is * is * dg;
@@ -269,7 +270,7 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* _
           const int64_t off = rr * C + g * 8;
           rd[u] = *reinterpret_cast<const uint4*>(dz + off);
           ry[u] = *reinterpret_cast<const uint4*>(y + off);
-          if (relu) rz[u] = *reinterpret_cast<const uint4*>(z + off);
+          if (relu == 1) rz[u] = *reinterpret_cast<const uint4*>(z + off);
         }
       }
 #pragma unroll
@@ -284,10 +285,13 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* _
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             float2 dd = __bfloat1622float2(hd[q]), yy = __bfloat1622float2(hy[q]);
-            if (relu) {
+            if (relu == 1) {
               float2 zz = __bfloat1622float2(hz[q]);
               dd.x = zz.x > 0.0f ? dd.x : 0.0f;
               dd.y = zz.y > 0.0f ? dd.y : 0.0f;
+            } else if (relu == 2) {
+              dd.x = yy.x * fsc[2 * q] + fsh[2 * q] > 0.0f ? dd.x : 0.0f;
+              dd.y = yy.y * fsc[2 * q + 1] + fsh[2 * q + 1] > 0.0f ? dd.y : 0.0f;
             }
             d[2 * q] = dd.x; d[2 * q + 1] = dd.y;
             o[2 * q] = ca[2 * q] * dd.x + cb[2 * q] * yy.x + cc[2 * q];
@@ -345,27 +349,30 @@ int esgd_bn_apply(const void* y, const void* residual, void* z, const float* sca
 }
 
 // dbeta / dgamma must be zeroed by the caller.
+// relu: 0 none, 1 mask from the saved output z (needed with a residual), 2 mask recomputed from y with
+// the forward scale / shift (no read of z).
 int esgd_bn_bwd_reduce(const void* dz, const void* z, const void* y, const float* mean, const float* invstd,
-                       int64_t M, int C, int relu, float* dbeta, float* dgamma, void* stream) {
+                       const float* fscale, const float* fshift, int64_t M, int C, int relu, float* dbeta,
+                       float* dgamma, void* stream) {
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
   bn_bwd_reduce_kernel<<<blocks_for(M, rows_par * 16), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, M, C, relu, dbeta,
-      dgamma);
+      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, fscale, fshift, M, C,
+      relu, dbeta, dgamma);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
 
 int esgd_bn_bwd_apply(const void* dz, const void* z, const void* y, const float* mean, const float* invstd,
-                      const float* gamma, const float* dbeta, const float* dgamma, void* dy, void* dres, int64_t M,
-                      int C, int relu, void* stream) {
+                      const float* gamma, const float* dbeta, const float* dgamma, const float* fscale,
+                      const float* fshift, void* dy, void* dres, int64_t M, int C, int relu, void* stream) {
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
   bn_bwd_apply_kernel<<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, gamma, dbeta,
-      dgamma, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, M, C, relu, 1.0f / (float)M);
+      dgamma, fscale, fshift, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, M, C, relu, 1.0f / (float)M);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

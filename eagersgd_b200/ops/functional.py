@@ -27,8 +27,8 @@ def _lib():
         lib.esgd_bn_stats.argtypes = [vp, i64, i32, vp, vp, vp]
         lib.esgd_bn_finalize.argtypes = [vp] * 10 + [i32, i64, f32, f32, vp]
         lib.esgd_bn_apply.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp]
-        lib.esgd_bn_bwd_reduce.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp, vp, vp]
-        lib.esgd_bn_bwd_apply.argtypes = [vp] * 10 + [i64, i32, i32, vp]
+        lib.esgd_bn_bwd_reduce.argtypes = [vp] * 7 + [i64, i32, i32, vp, vp, vp]
+        lib.esgd_bn_bwd_apply.argtypes = [vp] * 12 + [i64, i32, i32, vp]
         lib.esgd_softmax_ce.argtypes = [vp, i32, vp, i32, i32, i32, f32, vp, vp, vp, vp]
         lib.esgd_maxpool3x3s2_fwd.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
         lib.esgd_subsample2_fwd.argtypes = [vp, vp, i32, i32, i32, i32, vp]
@@ -279,14 +279,17 @@ class _BnAct(torch.autograd.Function):
         m = y2d.shape[0]
         s = _stream(dz)
         red = torch.zeros(2, c, dtype=torch.float32, device=dz.device)  # dbeta, dgamma
+        # ReLU mask: from the saved output when a residual was added, else recomputed from y (z is not read)
+        mode = 0 if not relu else (1 if has_res else 2)
         _ck(lib.esgd_bn_bwd_reduce(dz2d.data_ptr(), z2d.data_ptr(), y2d.data_ptr(), aux[0].data_ptr(),
-                                   aux[1].data_ptr(), m, c, int(relu), red[0].data_ptr(), red[1].data_ptr(), s),
-            "bn_bwd_reduce")
+                                   aux[1].data_ptr(), aux[2].data_ptr(), aux[3].data_ptr(), m, c, mode,
+                                   red[0].data_ptr(), red[1].data_ptr(), s), "bn_bwd_reduce")
         dy2d = torch.empty_like(y2d)
         dres2d = torch.empty_like(y2d) if has_res else None
         _ck(lib.esgd_bn_bwd_apply(dz2d.data_ptr(), z2d.data_ptr(), y2d.data_ptr(), aux[0].data_ptr(),
                                   aux[1].data_ptr(), gamma.data_ptr(), red[0].data_ptr(), red[1].data_ptr(),
-                                  dy2d.data_ptr(), _ptr(dres2d), m, c, int(relu), s), "bn_bwd_apply")
+                                  aux[2].data_ptr(), aux[3].data_ptr(), dy2d.data_ptr(), _ptr(dres2d), m, c, mode,
+                                  s), "bn_bwd_apply")
         dres = from_2d(dres2d, n, h, w) if has_res else None
         return from_2d(dy2d, n, h, w), red[1].to(gamma.dtype), red[0].to(gamma.dtype), dres, None, None, None, None, None
 
