@@ -305,11 +305,12 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* _
   }
 }
 
-int blocks_for(int64_t work_items, int per_block) {
+int blocks_for(int64_t work_items, int per_block, int64_t cap = 148 * 16) {
   int64_t b = (work_items + per_block - 1) / per_block;
-  const int64_t cap = 148 * 16;
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
+// Reductions end with a shared-memory pass and atomics per block: few, long-running blocks.
+constexpr int64_t kReduceGridCap = 148 * 2;
 
 }  // namespace
 
@@ -320,7 +321,7 @@ int esgd_bn_stats(const void* y, int64_t M, int C, float* sum, float* sqsum, voi
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
-  bn_stats_kernel<<<blocks_for(M, rows_par * 16), 256, 0, (cudaStream_t)stream>>>(
+  bn_stats_kernel<<<blocks_for(M, rows_par * 16, kReduceGridCap), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)y, M, C, sum, sqsum);
   esgd::count_launch();
   return (int)cudaGetLastError();
@@ -357,7 +358,7 @@ int esgd_bn_bwd_reduce(const void* dz, const void* z, const void* y, const float
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
-  bn_bwd_reduce_kernel<<<blocks_for(M, rows_par * 16), 256, 0, (cudaStream_t)stream>>>(
+  bn_bwd_reduce_kernel<<<blocks_for(M, rows_par * 16, kReduceGridCap), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, fscale, fshift, M, C,
       relu, dbeta, dgamma);
   esgd::count_launch();

@@ -97,6 +97,22 @@ __global__ void emulated_step_kernel(DevChannel** chans, const uint64_t* delay_n
   if (threadIdx.x == 0) finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
 }
 
+// Stand-alone fused momentum-SGD / weight-decay update over flat buffers (no communication):
+// the same per-element update the reduce kernel applies, with an optional per-tensor LARS
+// trust ratio folded into the learning rate by the caller.
+__global__ void fused_sgd_kernel(const void* grad, int grad_bf16, float* w32, float* mom, __nv_bfloat16* w16,
+                                 uint64_t count, float lr, float mu, float wd, float nesterov, float gscale) {
+  DevChannel ch;
+  ch.w32 = w32; ch.mom = mom; ch.w16 = w16; ch.out = nullptr;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = tid * 8; i < count; i += nth * 8) {
+    float g[8];
+    if (grad_bf16) load8(reinterpret_cast<const __nv_bfloat16*>(grad), i, g);
+    else load8(reinterpret_cast<const float*>(grad), i, g);
+    apply8(&ch, i, g, lr, mu, wd, nesterov, gscale);
+  }
+}
+
 // Bounded busy-wait on the launching stream: the seeded load-imbalance injector
 // (the reference sleeps on the host: resnet_run_loop_solo_imagenet_300.py:288-298).
 __global__ void spin_kernel(uint64_t ns) {
@@ -185,6 +201,17 @@ int esgd_emulated_step(void* chans, void* delay_ns, int world, int flush, void* 
                                               (cudaStream_t)stream);
   count_launch();
   return (int)e;
+}
+
+// count must be a multiple of 8; w16 may be null.
+int esgd_fused_sgd(const void* grad, int grad_bf16, float* w32, float* mom, void* w16, uint64_t count, float lr,
+                   float momentum, float wd, int nesterov, float grad_scale, void* stream) {
+  if (count % 8) return -1;
+  int g = grid_for(count, 148 * 8);
+  fused_sgd_kernel<<<g, 256, 0, (cudaStream_t)stream>>>(grad, grad_bf16, w32, mom, (__nv_bfloat16*)w16, count, lr,
+                                                        momentum, wd, nesterov ? 1.0f : 0.0f, grad_scale);
+  count_launch();
+  return (int)cudaGetLastError();
 }
 
 int esgd_spin(uint64_t ns, void* stream) {

@@ -100,6 +100,8 @@ def cuda():
         lib.esgd_channel_flush.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
         lib.esgd_emulated_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         lib.esgd_spin.argtypes = [C.c_uint64, C.c_void_p]
+        lib.esgd_fused_sgd.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
+                                       C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p]
         lib.esgd_arena_alloc.argtypes = [C.c_uint64, C.POINTER(C.c_void_p), C.c_void_p]
         lib.esgd_arena_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         lib.esgd_arena_close.argtypes = [C.c_void_p]

@@ -1,0 +1,133 @@
+"""Benchmark loggers and throughput hooks.
+
+``BaseBenchmarkLogger`` (stdout) and ``BenchmarkFileLogger`` (``metric.log`` JSON lines plus
+``benchmark_run.log`` with run and machine information) follow official/utils/logs/logger.py:
+57-218; ``ExamplesPerSecondHook`` follows official/utils/logs/hooks.py:28-127 (average and
+current examples/s every N steps); ``LoggingMetricHook`` follows metric_hook.py:24-97; the
+training log line is the reference's formatter (resnet_run_loop_solo_imagenet_300.py:582-623).
+Only rank 0 logs.
+"""
+from __future__ import annotations
+
+import contextlib
+import datetime
+import json
+import os
+import platform
+import time
+from typing import Dict, Optional
+
+import torch
+
+RUN_STATUS_SUCCESS, RUN_STATUS_FAILURE, RUN_STATUS_RUNNING = "success", "failure", "running"
+
+
+class BaseBenchmarkLogger:
+    def log_evaluation_result(self, eval_results: Dict):
+        step = eval_results.get("global_step", 0)
+        for k, v in sorted(eval_results.items()):
+            if k != "global_step":
+                self.log_metric(k, v, global_step=step)
+
+    def log_metric(self, name, value, unit=None, global_step=None, extras=None):
+        print("Benchmark metric:", _metric(name, value, unit, global_step, extras))
+
+    def log_run_info(self, model_name, dataset_name, run_params, test_id=None):
+        print("Benchmark run:", gather_run_info(model_name, dataset_name, run_params, test_id))
+
+    def on_finish(self, status):
+        pass
+
+
+class BenchmarkFileLogger(BaseBenchmarkLogger):
+    def __init__(self, logging_dir: str):
+        self.dir = logging_dir
+        os.makedirs(logging_dir, exist_ok=True)
+        self._f = open(os.path.join(logging_dir, "metric.log"), "a")
+
+    def log_metric(self, name, value, unit=None, global_step=None, extras=None):
+        self._f.write(json.dumps(_metric(name, value, unit, global_step, extras)) + "\n")
+        self._f.flush()
+
+    def log_run_info(self, model_name, dataset_name, run_params, test_id=None):
+        with open(os.path.join(self.dir, "benchmark_run.log"), "w") as f:
+            json.dump(gather_run_info(model_name, dataset_name, run_params, test_id), f)
+            f.write("\n")
+
+    def on_finish(self, status):
+        self._f.flush()
+        self._f.close()
+
+
+def _metric(name, value, unit, global_step, extras):
+    return {"name": name, "value": float(value), "unit": unit, "global_step": global_step,
+            "timestamp": datetime.datetime.utcnow().strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
+            "extras": [{"name": k, "value": str(v)} for k, v in sorted((extras or {}).items())]}
+
+
+def gather_run_info(model_name, dataset_name, run_params, test_id=None) -> dict:
+    info = {"model_name": model_name, "dataset": {"name": dataset_name}, "machine_config": {},
+            "test_id": test_id, "run_date": datetime.datetime.utcnow().strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
+            "torch_version": torch.__version__,
+            "run_parameters": [{"name": k, "value": str(v)} for k, v in sorted((run_params or {}).items())]}
+    info["machine_config"]["cpu_info"] = {"num_cores": os.cpu_count(), "cpu_info": platform.processor()}
+    if torch.cuda.is_available():
+        info["machine_config"]["gpu_info"] = {"count": torch.cuda.device_count(),
+                                              "model": torch.cuda.get_device_name(0)}
+    return info
+
+
+@contextlib.contextmanager
+def benchmark_context(logger: BaseBenchmarkLogger):
+    """Reports success or failure of the run to the logger (logger.py:96-106)."""
+    try:
+        yield
+        logger.on_finish(RUN_STATUS_SUCCESS)
+    except Exception:
+        logger.on_finish(RUN_STATUS_FAILURE)
+        raise
+
+
+class ExamplesPerSecondHook:
+    """Call ``after_step()`` once per training step."""
+
+    def __init__(self, batch_size: int, every_n_steps: int = 100, warm_steps: int = 0,
+                 metric_logger: Optional[BaseBenchmarkLogger] = None):
+        self.batch_size, self.every, self.warm = batch_size, every_n_steps, warm_steps
+        self.logger = metric_logger or BaseBenchmarkLogger()
+        self.step, self.total_time, self.total_steps, self._t = 0, 0.0, 0, None
+
+    def after_step(self):
+        now = time.time()
+        self.step += 1
+        if self._t is None or self.step <= self.warm:
+            self._t = now
+            return None
+        if (self.step - self.warm) % self.every == 0:
+            elapsed = now - self._t
+            self._t = now
+            self.total_time += elapsed
+            self.total_steps += self.every
+            avg = self.batch_size * self.total_steps / self.total_time
+            cur = self.batch_size * self.every / elapsed
+            self.logger.log_metric("average_examples_per_sec", avg, global_step=self.step)
+            self.logger.log_metric("current_examples_per_sec", cur, global_step=self.step)
+            return avg, cur
+        return None
+
+
+class LoggingMetricHook:
+    def __init__(self, metric_logger: BaseBenchmarkLogger, every_n_iter: int = 10):
+        self.logger, self.every, self.step = metric_logger, every_n_iter, 0
+
+    def after_step(self, tensors: Dict[str, float]):
+        self.step += 1
+        if self.step % self.every == 0:
+            for k, v in tensors.items():
+                self.logger.log_metric(k, v, global_step=self.step)
+
+
+def training_log_line(epoch: int, step: int, steps_per_epoch: int, lr: float, loss: float, top1: float,
+                      top5: float) -> str:
+    return ("TRAINING - Epoch: [%d][%d/%d]  LR %.5f  Loss %.4f  Prec@1 %.3f  Prec@5 %.3f"
+            % (epoch, step % max(steps_per_epoch, 1), steps_per_epoch, lr, loss, top1, top5))
