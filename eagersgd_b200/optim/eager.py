@@ -70,6 +70,7 @@ class EagerOptimizer:
         self.overlap = overlap
         self.timeout_s, self.grace_us, self.max_blocks = timeout_s, grace_us, max_blocks
         self.steps = 0
+        self.grad_scale = 1.0   # multiplies every gradient before the update (1 / loss scale)
         params = [p for g in optimizer.param_groups for p in g["params"] if p.requires_grad]
         if not params:
             raise ValueError("optimizer has no trainable parameters")
@@ -249,12 +250,17 @@ class EagerOptimizer:
                 b.launched = False
                 b.pending = len(b.params)
             if not self.fused:
+                if self.grad_scale != 1.0:
+                    for b in self.buckets:
+                        b.grad_flat.mul_(self.grad_scale)
                 self.optimizer.step()
         else:
             applied = False
             for b in self.buckets:
                 out, info = b.channel.step(b.grad_flat, b.out_np)
                 b.grad_flat.copy_(torch.from_numpy(out))
+                if self.grad_scale != 1.0:
+                    b.grad_flat.mul_(self.grad_scale)
                 applied = applied or info.role in (N.ROLE_PARTICIPANT, N.ROLE_DRAIN)
                 b.last_role = info.role
             if applied:

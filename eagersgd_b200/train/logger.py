@@ -61,13 +61,13 @@ class BenchmarkFileLogger(BaseBenchmarkLogger):
 
 def _metric(name, value, unit, global_step, extras):
     return {"name": name, "value": float(value), "unit": unit, "global_step": global_step,
-            "timestamp": datetime.datetime.utcnow().strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
+            "timestamp": datetime.datetime.now(datetime.timezone.utc).strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
             "extras": [{"name": k, "value": str(v)} for k, v in sorted((extras or {}).items())]}
 
 
 def gather_run_info(model_name, dataset_name, run_params, test_id=None) -> dict:
     info = {"model_name": model_name, "dataset": {"name": dataset_name}, "machine_config": {},
-            "test_id": test_id, "run_date": datetime.datetime.utcnow().strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
+            "test_id": test_id, "run_date": datetime.datetime.now(datetime.timezone.utc).strftime("%Y-%m-%dT%H:%M:%S.%fZ"),
             "torch_version": torch.__version__,
             "run_parameters": [{"name": k, "value": str(v)} for k, v in sorted((run_params or {}).items())]}
     info["machine_config"]["cpu_info"] = {"num_cores": os.cpu_count(), "cpu_info": platform.processor()}

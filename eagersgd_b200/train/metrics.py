@@ -1,0 +1,197 @@
+"""Metrics: error norms, device-synchronised wall-clock, accuracy, dataset bias, communication volume.
+
+Counterparts of deep500/utils/metric.py:4-65 (TestMetric protocol), deep500/utils/metrics.py:10-293
+(L1Error, L2Error, MaxError, DiffHeatmap, VarHeatmap, WallclockTime with reruns / avg_over /
+median), deep500/lv2/validation/metrics.py:9-125 (TrainingAccuracy, TestAccuracy, DatasetBias,
+SamplerEventMetric) and deep500/lv3/metrics.py:16-127 (CommunicationVolume, MPIProfiling).
+The reference's WallclockTime reads host time without synchronising the device; here a timed
+region is bracketed by CUDA events on the launching stream.
+"""
+from __future__ import annotations
+
+import statistics
+import time
+from typing import Any, Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+
+
+class TestMetric:
+    __test__ = False  # not a pytest class
+    reruns = 1
+
+    def begin(self, *args): ...
+    def end(self, *args): ...
+
+    def measure(self, inputs, outputs, reference_outputs) -> Any:
+        raise NotImplementedError
+
+    def measure_summary(self, *args) -> Any:
+        return self.measure(*args)
+
+
+def _np(x):
+    return x.detach().float().cpu().numpy() if isinstance(x, torch.Tensor) else np.asarray(x, dtype=np.float64)
+
+
+class L1Error(TestMetric):
+    def measure(self, inputs, outputs, reference_outputs):
+        return float(np.abs(_np(outputs) - _np(reference_outputs)).sum())
+
+
+class L2Error(TestMetric):
+    def measure(self, inputs, outputs, reference_outputs):
+        return float(np.sqrt(((_np(outputs) - _np(reference_outputs)) ** 2).sum()))
+
+
+class MaxError(TestMetric):
+    def measure(self, inputs, outputs, reference_outputs):
+        return float(np.abs(_np(outputs) - _np(reference_outputs)).max())
+
+
+class DiffHeatmap(TestMetric):
+    """Absolute difference map (returned as an array; there is no plotting library here)."""
+
+    def measure(self, inputs, outputs, reference_outputs):
+        return np.abs(_np(outputs) - _np(reference_outputs))
+
+
+class VarHeatmap(TestMetric):
+    """Element-wise variance over reruns."""
+
+    def __init__(self, reruns: int = 10):
+        self.reruns, self.samples = reruns, []
+
+    def measure(self, inputs, outputs, reference_outputs=None):
+        self.samples.append(_np(outputs))
+        return np.var(np.stack(self.samples), axis=0)
+
+
+class WallclockTime(TestMetric):
+    """Median over ``reruns`` of the mean time of ``avg_over`` calls, in milliseconds; CUDA work is
+    timed with events on the current stream."""
+
+    def __init__(self, reruns: int = 100, avg_over: int = 10, device: Optional[torch.device] = None):
+        self.reruns, self.avg_over, self.device = reruns, avg_over, device
+        self.times: List[float] = []
+
+    def time_callable(self, fn: Callable[[], Any], warmup: int = 3) -> float:
+        cuda = self.device is not None and self.device.type == "cuda"
+        for _ in range(warmup):
+            fn()
+        for _ in range(self.reruns):
+            if cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize(self.device)
+                e0.record()
+                for _ in range(self.avg_over):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize(self.device)
+                self.times.append(e0.elapsed_time(e1) / self.avg_over)
+            else:
+                t0 = time.perf_counter()
+                for _ in range(self.avg_over):
+                    fn()
+                self.times.append((time.perf_counter() - t0) * 1e3 / self.avg_over)
+        return statistics.median(self.times)
+
+    def measure(self, inputs=None, outputs=None, reference_outputs=None):
+        return statistics.median(self.times) if self.times else None
+
+
+class TrainingAccuracy(TestMetric):
+    def __init__(self):
+        self.correct = self.total = 0
+
+    def update(self, logits, labels):
+        self.correct += int((_np(logits).argmax(-1) == _np(labels)).sum())
+        self.total += len(_np(labels))
+
+    def measure(self, *a):
+        return self.correct / max(self.total, 1)
+
+
+class TestAccuracy(TrainingAccuracy):
+    pass
+
+
+def topk_accuracy(logits: torch.Tensor, labels: torch.Tensor, ks=(1, 5)) -> List[float]:
+    """Prec@k as logged by the reference run loop (resnet_run_loop_solo_imagenet_300.py:429-448)."""
+    top = logits.float().topk(max(ks), dim=-1).indices
+    hit = top == labels.view(-1, 1)
+    return [float(hit[:, :k].any(-1).float().mean()) for k in ks]
+
+
+class DatasetBias(TestMetric):
+    """Histogram of the labels a sampler produced (detects biased sampling)."""
+
+    def __init__(self, num_classes: int):
+        self.hist = np.zeros(num_classes, dtype=np.int64)
+
+    def after_sampling(self, sampler, batch_size):
+        pass
+
+    def update(self, labels):
+        self.hist += np.bincount(np.asarray(labels), minlength=len(self.hist))
+
+    def measure(self, *a):
+        return self.hist
+
+
+class SamplerEventMetric(TestMetric):
+    """Time spent drawing batches (attach as a sampler event)."""
+
+    def __init__(self):
+        self.times, self._t = [], None
+
+    def before_sampling(self, sampler, batch_size):
+        self._t = time.perf_counter()
+
+    def after_sampling(self, sampler, batch_size):
+        self.times.append(time.perf_counter() - self._t)
+
+    def measure(self, *a):
+        return statistics.median(self.times) if self.times else None
+
+
+class CommunicationVolume(TestMetric):
+    """Bytes this rank moved through the partial allreduce, from the optimizer's own counters
+    (the reference diffs ``ifstat`` output around the run, deep500/lv3/metrics.py:16-92)."""
+
+    def __init__(self, eager_optimizer):
+        self.opt = eager_optimizer
+        self.begin_steps = 0
+
+    def begin(self, *a):
+        self.begin_steps = self.opt.stats()["steps"]
+
+    def measure(self, *a) -> Dict[str, float]:
+        st = self.opt.stats()
+        steps = st["steps"] - self.begin_steps
+        esz = 2 if self.opt.slot_dtype == torch.bfloat16 else 4
+        per_round = sum(b.count for b in self.opt.buckets) * esz
+        contributors = max(st["mean_contributors"], 1.0)
+        return {"steps": steps, "bytes_read_from_peers": steps * per_round * (contributors - 1),
+                "bytes_published": steps * per_round}
+
+
+class CommProfiling(TestMetric):
+    """Device time of the communication stream between ``begin`` and ``end`` (stands where the
+    reference toggles MPI.Pcontrol, deep500/lv3/metrics.py:95-121)."""
+
+    def __init__(self, eager_optimizer):
+        self.opt = eager_optimizer
+
+    def begin(self, *a):
+        self.e0 = torch.cuda.Event(enable_timing=True)
+        self.e0.record(self.opt.comm_stream)
+
+    def end(self, *a):
+        self.e1 = torch.cuda.Event(enable_timing=True)
+        self.e1.record(self.opt.comm_stream)
+
+    def measure(self, *a):
+        self.e1.synchronize()
+        return self.e0.elapsed_time(self.e1)

@@ -1,0 +1,206 @@
+"""ResNet training main: ImageNet and CIFAR-10 with eager-SGD (solo / majority), synchronous
+partial allreduce, or the synchronous NCCL baseline.
+
+    python -m eagersgd_b200.train.resnet_main --dataset imagenet -solo -rs 50 -rv 1 -bs 128 --synthetic
+    torchrun --nproc-per-node 8 -m eagersgd_b200.train.resnet_main --dataset cifar10 --mode majority -rs 32 --synthetic
+
+One program covers what the reference spreads over imagenet_main_eagersgd.py, imagenet_main_hvd.py,
+cifar10_main.py and the run loops resnet_run_loop_{solo_imagenet_300,hvd_imagenet_300,hvd_cifar10}.py:
+identical replicas from a shared seed (:510-513), per-rank model directories (:551-556), the seeded
+imbalance injector (:288-298), learning-rate schedule with warm-up (:164-217), momentum or LARS
+(:366-374), loss scaling (:398-416), rank-0 logging of loss / Prec@1 / Prec@5 (:582-623), train /
+evaluate cycles (:662-684) and the export at the end (:686-690).  Replicas are re-synchronised from
+rank 0 every ``--resync_epochs`` epochs, which the reference does by copying checkpoint directories
+between launches (test_scripts_imagenet/synchm.sh).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+from .. import ckpt
+from ..data import OrderedSampler, ShuffleSampler, SyntheticImageDataset, load_cifar10, partition
+from ..models.resnet import cifar_resnet, imagenet_resnet
+from ..optim.lars import LARS, poly_rate_schedule
+from ..parallel.group import init as init_group, finalize
+from . import flags as F
+from .imbalance import ConstantRanks, ExponentialDelays, FixedRanksSleep, NoImbalance, RandomRankFactor
+from .logger import (BaseBenchmarkLogger, BenchmarkFileLogger, ExamplesPerSecondHook, benchmark_context,
+                     training_log_line)
+from .metrics import topk_accuracy
+from .schedule import cifar10_schedule, imagenet_schedule
+from .step import TrainStep
+
+DATASETS = {
+    "imagenet": dict(train=1281167, val=50000, classes=1001, shape=(3, 224, 224), wd=1e-4, default_size=50),
+    "cifar10": dict(train=50000, val=10000, classes=10, shape=(3, 32, 32), wd=2e-4, default_size=32),
+}
+
+
+def build_model(args, info):
+    if args.dataset == "imagenet":
+        return imagenet_resnet(args.resnet_size, args.resnet_version, info["classes"])
+    return cifar_resnet(args.resnet_size, args.resnet_version, info["classes"])
+
+
+def build_data(args, info, group):
+    if args.use_synthetic_data or args.data_dir is None:
+        n_train = args.synthetic_train_size or info["train"]
+        train = SyntheticImageDataset(n_train, info["shape"], info["classes"], seed=1)
+        val = SyntheticImageDataset(min(info["val"], 4 * args.batch_size), info["shape"], info["classes"], seed=2)
+    elif args.dataset == "cifar10":
+        train, val = load_cifar10(args.data_dir)
+    else:
+        raise SystemExit("ImageNet from disk needs a decoded array dataset; use --synthetic here")
+    shard = partition(train, group.rank, group.world)   # dataset.take(n // num_workers) in the reference (:94-96)
+    return ShuffleSampler(shard, args.batch_size, seed=args.baseseed + 17), OrderedSampler(val, args.batch_size)
+
+
+def make_injector(args, group, step_time):
+    w = group.world
+    return {"none": lambda: NoImbalance(w),
+            "sleep": lambda: FixedRanksSleep(w, args.imbalance_seconds, 2, seed=args.baseseed + 5),
+            "random_rank": lambda: RandomRankFactor(w, step_time, 1.5, seed=args.baseseed + 5),
+            "exponential": lambda: ExponentialDelays(w, step_time, 0.5, 2, seed=args.baseseed + 5),
+            "constant": lambda: ConstantRanks(w, (0, 1), args.imbalance_seconds)}[args.imbalance]()
+
+
+def evaluate(step: TrainStep, sampler, device):
+    model = step.model
+    model.eval()
+    sampler.reset()
+    top1 = top5 = n = 0.0
+    with torch.no_grad():
+        for batch in sampler:
+            x = torch.as_tensor(batch["x"]).to(device)
+            y = torch.as_tensor(batch["y"]).to(device)
+            if device.type == "cuda":
+                x = x.to(step.compute_dtype).contiguous(memory_format=torch.channels_last)
+            a1, a5 = topk_accuracy(model(x), y, (1, min(5, model.fc.out_features)))
+            top1 += a1 * len(y)
+            top5 += a5 * len(y)
+            n += len(y)
+    model.train()
+    return top1 / max(n, 1), top5 / max(n, 1)
+
+
+def main(argv=None):
+    p = F.build_parser(__doc__.split("\n")[0])
+    p.add_argument("--dataset", default="imagenet", choices=sorted(DATASETS))
+    p.add_argument("--synthetic_train_size", type=int, default=None, help="samples per epoch of synthetic data")
+    args = F.resolve(p.parse_args(argv))
+    info = DATASETS[args.dataset]
+    group = init_group()
+    device = group.device
+    torch.manual_seed(args.baseseed)      # identical initial replicas without a broadcast
+    np.random.seed(args.baseseed)
+    if args.clean and group.rank == 0:
+        ckpt.clean(args.model_dir)
+    group.barrier()
+
+    model = build_model(args, info)
+    global_batch = args.batch_size * group.world
+    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // global_batch, 1)
+    if args.dataset == "imagenet":
+        lr_fn = imagenet_schedule(global_batch, info["train"], warmup=not args.disablewarmup, start_epoch=args.start_epoch)
+    else:
+        lr_fn = cifar10_schedule(global_batch, info["train"])
+    step = TrainStep(model, group, impl="ddp" if args.mode == "ddp" else "ours", mode=args.mode if args.mode != "ddp" else "sync",
+                     limiter=args.limiter, bucket_mb=args.bucket_mb, lr=lr_fn(0) * args.lrmult, momentum=0.9,
+                     weight_decay=info["wd"], compute_dtype=getattr(torch, args.torch_dtype),
+                     inner_optimizer=(lambda ps, **kw: LARS(ps, lr=kw["lr"], momentum=0.9, weight_decay=info["wd"]))
+                     if args.lars else None, loss_scale=args.loss_scale)
+    if args.pretrained_model_checkpoint_path:
+        ckpt.import_tf_layout(step.model, args.pretrained_model_checkpoint_path, exclude=("dense",))
+    global_step = ckpt.load(step.model, step.opt if hasattr(step.opt, "state_dict") else None, args.model_dir, group.rank)
+
+    train_sampler, val_sampler = build_data(args, info, group)
+    logger = BenchmarkFileLogger(args.benchmark_log_dir) if (
+        args.benchmark_logger_type == "BenchmarkFileLogger" and args.benchmark_log_dir) else BaseBenchmarkLogger()
+    if group.rank == 0:
+        logger.log_run_info("resnet%d" % args.resnet_size, args.dataset, vars(args), args.benchmark_test_id)
+    eps_hook = ExamplesPerSecondHook(global_batch, every_n_steps=max(args.train_acc_steps, 1), warm_steps=5,
+                                     metric_logger=logger if group.rank == 0 else _Quiet())
+    injector = None
+    t_step = None
+
+    def to_device(batch):
+        x = torch.as_tensor(batch["x"]).pin_memory() if device.type == "cuda" else torch.as_tensor(batch["x"])
+        y = torch.as_tensor(batch["y"])
+        x = x.to(device, non_blocking=True)
+        if device.type == "cuda":
+            x = x.to(step.compute_dtype).contiguous(memory_format=torch.channels_last)
+        return x, y.to(device, non_blocking=True)
+
+    with benchmark_context(logger):
+        epochs = int(np.ceil(args.train_epochs))
+        for epoch in range(args.start_epoch, args.start_epoch + epochs):
+            if args.eval_only:
+                break
+            train_sampler.reset()
+            for batch in train_sampler:
+                if args.max_train_steps is not None and global_step >= args.max_train_steps:
+                    break
+                lr = (poly_rate_schedule(global_step / steps_per_epoch, args.poly_rate, global_batch, epochs)
+                      if args.lars else lr_fn(global_step)) * args.lrmult
+                step.set_lr(lr)
+                if injector is not None:
+                    injector.apply(group.rank, device)
+                t0 = time.perf_counter()
+                x, y = to_device(batch)
+                loss = step.run_device(x, y)
+                global_step += 1
+                eps_hook.after_step()
+                if global_step % max(args.train_acc_steps, 1) == 0:
+                    lv = float(loss)        # synchronises: only every train_acc_steps
+                    if group.rank == 0:
+                        with torch.no_grad():
+                            step.model.eval()
+                            a1, a5 = topk_accuracy(step.model(x), y, (1, min(5, info["classes"])))
+                            step.model.train()
+                        print(training_log_line(epoch, global_step, steps_per_epoch, lr, lv, a1, a5), flush=True)
+                if injector is None and global_step == 5:   # calibrate the delay on undisturbed steps
+                    if device.type == "cuda":
+                        torch.cuda.synchronize()
+                    t_step = time.perf_counter() - t0
+                    injector = make_injector(args, group, max(t_step, 1e-3))
+            if (epoch + 1) % args.epochs_between_evals == 0:
+                a1, a5 = evaluate(step, val_sampler, device)
+                if group.rank == 0:
+                    logger.log_evaluation_result({"accuracy": a1, "accuracy_top_5": a5, "global_step": global_step})
+                if args.stop_threshold is not None and a1 >= args.stop_threshold:
+                    break
+            if args.resync_epochs and (epoch + 1) % args.resync_epochs == 0:
+                ckpt.resync_from_rank0(step.model, step.opt if hasattr(step.opt, "resync_from_rank0") else None, group)
+            ckpt.save(step.model, step.opt if hasattr(step.opt, "state_dict") else None, args.model_dir, group.rank,
+                      global_step)
+            if args.max_train_steps is not None and global_step >= args.max_train_steps:
+                break
+        if hasattr(step.opt, "flush"):
+            step.opt.flush()
+        if args.eval_only:
+            a1, a5 = evaluate(step, val_sampler, device)
+            if group.rank == 0:
+                logger.log_evaluation_result({"accuracy": a1, "accuracy_top_5": a5, "global_step": global_step})
+        if args.export_dir and group.rank == 0:
+            ckpt.export_tf_layout(step.model, os.path.join(args.export_dir, "model.npz"),
+                                  step.opt if hasattr(step.opt, "master_params") else None, global_step)
+    stats = step.stats()
+    if group.rank == 0 and stats:
+        print("eager-SGD counters:", stats)
+    step.close()
+    finalize()
+    return 0
+
+
+class _Quiet(BaseBenchmarkLogger):
+    def log_metric(self, *a, **k):
+        pass
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -39,9 +39,10 @@ def prepare_model(model: nn.Module, device: torch.device, compute_dtype=torch.bf
 class TrainStep:
     def __init__(self, model: nn.Module, group: Group, impl: str = "ours", mode: str = "solo", limiter: int = 32,
                  bucket_mb: float = 25.0, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 1e-4,
-                 compute_dtype=torch.bfloat16, loss_fn=None):
+                 compute_dtype=torch.bfloat16, loss_fn=None, inner_optimizer=None, loss_scale: float = 1.0):
         self.group, self.impl, self.device = group, impl, group.device
         self.compute_dtype = compute_dtype if self.device.type == "cuda" else torch.float32
+        self.loss_scale = float(loss_scale)
         from ..ops.functional import softmax_cross_entropy
         self.loss_fn = loss_fn or softmax_cross_entropy
         if impl == "ddp":
@@ -58,13 +59,17 @@ class TrainStep:
         else:
             self.model = prepare_model(model, self.device, self.compute_dtype)
             self.net = self.model
-            inner = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
+            if inner_optimizer is not None:      # any torch optimizer can be wrapped (LARS, Adam, ...)
+                inner = inner_optimizer(self.model.parameters(), lr=lr)
+            else:
+                inner = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
             cls = {"solo": SoloAllreduceOptimizer, "majority": MajorityAllreduceOptimizer,
                    "sync": SyncAllreduceOptimizer}[mode]
             kw = dict(bucket_mb=bucket_mb)
             if mode != "sync":
                 kw["limiter"] = limiter
             self.opt = cls(inner, group, **kw)
+            self.opt.grad_scale = 1.0 / self.loss_scale   # static loss scaling is undone inside the update
             self.autocast = False
         self._xbuf = self._ybuf = None
         self._graph = None
@@ -109,7 +114,7 @@ class TrainStep:
             logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
                               else x.to(self.compute_dtype))
         loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
-        loss.backward()
+        (loss * self.loss_scale if self.loss_scale != 1.0 else loss).backward()
         self.opt.step()
         return loss.detach()
 
@@ -123,6 +128,10 @@ class TrainStep:
         self._xbuf.copy_(x_host, non_blocking=True)
         self._ybuf.copy_(y_host, non_blocking=True)
         return float(self.run_device(self._xbuf, self._ybuf).item())
+
+    def set_lr(self, lr: float) -> None:
+        for g in self.opt.param_groups:
+            g["lr"] = lr
 
     def inject_delay(self, seconds: float) -> None:
         """Seeded load imbalance: hold this rank's compute stream (GPU) or sleep (CPU)."""

@@ -1,0 +1,171 @@
+"""Trainer, optimizer bases, parity distributed optimizers, schedules, injectors, mains on CPU."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+
+def _toy():
+    from eagersgd_b200.data import NumpyDataset, ShuffleSampler, OrderedSampler
+    rng = np.random.RandomState(0)
+    x = rng.randn(512, 16).astype(np.float32)
+    w = rng.randn(16, 4).astype(np.float32)
+    y = (x @ w).argmax(1).astype(np.int64)
+    ds = NumpyDataset(x, "x", y, "y")
+    return ds, ShuffleSampler(ds, 32, seed=0), OrderedSampler(ds, 64)
+
+
+@pytest.mark.parametrize("opt_name", ["GradientDescent", "MomentumOptimizer", "AdamOptimizer", "AdaGradOptimizer"])
+def test_trainer_with_reference_update_rules(opt_name):
+    from eagersgd_b200.optim import base
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import Trainer
+    from eagersgd_b200.train import events as E
+    torch.manual_seed(0)
+    ds, tr, te = _toy()
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
+    lr = {"GradientDescent": 0.5, "MomentumOptimizer": 0.1, "AdamOptimizer": 0.05, "AdaGradOptimizer": 0.5}[opt_name]
+    opt = getattr(base, opt_name)(ex, learning_rate=lr)
+    stats = Trainer(tr, te, ex, opt).run_loop(4, [E.SummaryGeneratorEvent(), E.AccuracyAbortEvent(0.999)])
+    assert stats.test_summaries[-1].accuracy > 0.85
+    assert stats.train_summaries[-1].mean_loss < stats.train_summaries[0].mean_loss
+
+
+def test_momentum_rule_matches_torch_sgd():
+    from eagersgd_b200.optim.base import MomentumOptimizer
+    from eagersgd_b200.train.executor import GraphExecutor, mse_loss
+    torch.manual_seed(1)
+    m1, m2 = torch.nn.Linear(8, 1), torch.nn.Linear(8, 1)
+    m2.load_state_dict(m1.state_dict())
+    ex = GraphExecutor(m1, lambda o, b: mse_loss(o.squeeze(-1), b))
+    opt = MomentumOptimizer(ex, learning_rate=0.05, momentum=0.9)
+    ref = torch.optim.SGD(m2.parameters(), lr=0.05, momentum=0.9)
+    for k in range(5):
+        x, y = torch.randn(16, 8), torch.randn(16)
+        opt.step({"x": x, "y": y})
+        ref.zero_grad()
+        torch.nn.functional.mse_loss(m2(x).squeeze(-1), y).backward()
+        ref.step()
+    assert torch.allclose(m1.weight, m2.weight, atol=1e-6)
+
+
+def test_events_and_csv(tmp_path):
+    from eagersgd_b200.optim.base import GradientDescent
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import test_training
+    from eagersgd_b200.train import events as E
+    ds, tr, te = _toy()
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
+    opt = GradientDescent(ex, learning_rate=0.1)
+    sched = E.EpochHPSchedule(learning_rate=lambda e: 0.1 * 0.5 ** e)
+    wrongs = E.SaveWrongsEvent()
+    stats = test_training(ex, tr, te, opt, 2, [sched, wrongs, E.CsvWriterEvent(str(tmp_path / "s.csv")),
+                                              E.LossPlotGeneratorEvent(str(tmp_path / "loss")),
+                                              E.TimeAbortAfterTestEvent(1e9)])
+    assert opt.hyper["learning_rate"] == pytest.approx(0.05)
+    assert (tmp_path / "s.csv").exists() and (tmp_path / "loss.json").exists()
+    assert len(wrongs.wrong) == round((1 - stats.test_summaries[-1].accuracy) * 512)
+
+
+def test_lr_schedules():
+    from eagersgd_b200.train.schedule import imagenet_schedule, cifar10_schedule
+    from eagersgd_b200.optim.lars import poly_rate_schedule
+    f = imagenet_schedule(8192, 1281167)
+    bpe = 1281167 / 8192
+    assert f(0) == 0.0 and f(int(bpe * 2.5)) == pytest.approx(3.2 * 0.5, rel=1e-2)   # linear warm-up to 0.1*8192/256
+    assert f(int(bpe * 10)) == pytest.approx(3.2) and f(int(bpe * 31)) == pytest.approx(0.32)
+    assert f(int(bpe * 95)) == pytest.approx(3.2e-4)
+    g = cifar10_schedule(128)
+    assert g(0) == pytest.approx(0.1) and g(int(50000 / 128 * 100)) == pytest.approx(0.01)
+    assert poly_rate_schedule(0, batch_size=8192) == 0 and poly_rate_schedule(90, batch_size=8192, train_epochs=90) == 0
+
+
+def test_injectors_agree_across_ranks():
+    from eagersgd_b200.train.imbalance import FixedRanksSleep, ExponentialDelays, RandomRankFactor
+    a, b = FixedRanksSleep(8, 0.32, 2, seed=5), FixedRanksSleep(8, 0.32, 2, seed=5)
+    for _ in range(20):
+        assert a.delays() == b.delays()
+    d = ExponentialDelays(8, 0.1, 0.5, 2, seed=1).delays()
+    assert sum(1 for v in d if v > 0) in (1, 2) and max(d) <= 0.5
+    d = RandomRankFactor(4, 0.2, 1.5, seed=0).delays()
+    assert sorted(d) == [0, 0, 0, pytest.approx(0.3)]
+
+
+def test_lars_trust_ratio():
+    from eagersgd_b200.optim.lars import LARS
+    w = torch.nn.Parameter(torch.ones(4, 4) * 2.0)
+    b = torch.nn.Parameter(torch.ones(4))
+    opt = LARS([w, b], lr=1.0, momentum=0.0, weight_decay=0.0, eeta=0.1)
+    w.grad, b.grad = torch.ones(4, 4), torch.ones(4)
+    opt.step()
+    trust = 0.1 * (2.0 * 4) / 4.0                      # eeta * ||w|| / ||g||
+    assert torch.allclose(w, torch.full((4, 4), 2.0 - trust))
+    assert torch.allclose(b, torch.zeros(4))           # 1-D tensors are not adapted: plain lr
+
+
+def _parity(rank, world, name):
+    import eagersgd_b200 as es
+    from eagersgd_b200.optim import base, distributed as D
+    from eagersgd_b200.train.executor import GraphExecutor, mse_loss
+    g = es.init(backend="gloo")
+    torch.manual_seed(0)
+    m = torch.nn.Linear(8, 1)
+    ex = GraphExecutor(m, lambda o, b: mse_loss(o.squeeze(-1), b))
+    opt = getattr(D, name)(base.GradientDescent(ex, learning_rate=0.1), g)
+    gen = torch.Generator().manual_seed(3)
+    xs, ys = torch.randn(world, 16, 8, generator=gen), torch.randn(world, 16, generator=gen)
+    if name == "InconsistentParameterServer":
+        if rank == 0:
+            opt.serve(3 * (world - 1))
+        else:
+            for _ in range(3):
+                opt.step({"x": xs[rank], "y": ys[rank]})
+        out = m.weight.detach().clone()
+    else:
+        for _ in range(3):
+            opt.step({"x": xs[rank], "y": ys[rank]})
+        out = m.weight.detach().clone()
+    g.barrier()
+    es.finalize()
+    return out.tolist()   # plain lists travel safely through the result queue
+
+
+@pytest.mark.parametrize("name", ["ConsistentDecentralized", "HorovodStyleOptimizer", "ConsistentParameterServer",
+                                  "ModelAverageDecentralized", "ConsistentNeighbors", "InconsistentParameterServer"])
+def test_parity_distributed_optimizers(name):
+    world = 3
+    outs = [torch.tensor(o) for o in run_ranks(_parity, world, (name,))]
+    if name in ("ConsistentDecentralized", "HorovodStyleOptimizer", "ConsistentParameterServer",
+                "ModelAverageDecentralized", "ConsistentNeighbors"):
+        for o in outs[1:]:
+            assert torch.allclose(o, outs[0], atol=1e-6)   # world 3: ring neighbours cover everyone
+    if name in ("ConsistentDecentralized", "HorovodStyleOptimizer", "ConsistentParameterServer"):
+        torch.manual_seed(0)
+        m = torch.nn.Linear(8, 1)
+        gen = torch.Generator().manual_seed(3)
+        xs, ys = torch.randn(world, 16, 8, generator=gen), torch.randn(world, 16, generator=gen)
+        ref = torch.optim.SGD(m.parameters(), lr=0.1)
+        for _ in range(3):
+            ref.zero_grad()
+            torch.nn.functional.mse_loss(m(xs.view(-1, 8)).squeeze(-1), ys.view(-1)).backward()
+            ref.step()
+        assert torch.allclose(outs[0], m.weight.detach(), atol=1e-5)
+    if name == "InconsistentParameterServer":
+        assert torch.isfinite(outs[0]).all() and not torch.allclose(outs[0], outs[0] * 0)
+
+
+def test_resnet_main_smoke(tmp_path):
+    from eagersgd_b200.train import resnet_main
+    rc = resnet_main.main(["--dataset", "cifar10", "--synthetic", "--synthetic_train_size", "64", "-rs", "8", "-bs", "16",
+                           "--train_epochs", "1", "--max_train_steps", "3", "--mode", "solo", "--dtype", "fp32",
+                           "--model_dir", str(tmp_path / "m"), "--export_dir", str(tmp_path / "e"),
+                           "--train_acc_steps", "2", "--benchmark_logger_type", "BenchmarkFileLogger",
+                           "--benchmark_log_dir", str(tmp_path / "log")])
+    assert rc == 0
+    assert (tmp_path / "m" / "0" / "checkpoint").exists()
+    z = np.load(tmp_path / "e" / "model.npz")
+    assert "resnet_model/conv2d/kernel" in z and "resnet_model/dense/bias" in z
+    assert (tmp_path / "log" / "metric.log").exists()
