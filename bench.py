@@ -94,18 +94,22 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference is TensorFlow 1.x + Horovod + MPI (fflib2 links libmpi, the custom op
-    links tensorflow_framework); none of those exist in this image and nothing can be fetched."""
-    why = None
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    try:
-        import tensorflow  # noqa: F401
-    except Exception:
-        why = "reference needs TensorFlow 1.x, Horovod, mpi4py and an MPI library; none is installed and there is no network"
-    if why is None and not os.path.isdir(ref):
-        why = "baseline/_ref is absent: the reference tree has no installable python project at its root"
-    if why is None:
-        why = "reference run loop requires mpirun with MPI_THREAD_MULTIPLE; no MPI launcher in this image"
+    """The reference's training path is TensorFlow 1.x + Horovod + mpi4py + MPI (fflib2 links libmpi, the
+    custom op links tensorflow_framework); its vendored Deep500 package installs but cannot be imported."""
+    missing = []
+    for mod in ("tensorflow", "horovod", "mpi4py", "onnx"):
+        try:
+            __import__(mod)
+        except Exception:
+            missing.append(mod)
+    import shutil
+    if shutil.which("mpirun") is None and shutil.which("mpiexec") is None:
+        missing.append("an MPI launcher")
+    if missing:
+        why = ("reference cannot run here: missing " + ", ".join(missing) + "; the repository root is not an installable "
+               "project and its vendored deep500 package fails at import (No module named 'onnx'); no network")
+    else:
+        why = "reference run loop needs the Piz Daint SLURM environment; not reproducible on this box"
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
