@@ -129,7 +129,12 @@ def main():
     from eagersgd_b200.parallel import _native as N
     from eagersgd_b200.train.step import TrainStep
 
+    # NCCL announces its version on stdout at the first collective: keep stdout for the one JSON line
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     group = es.init()
+    group.barrier()
     rank, world, dev = group.rank, group.world, group.device
     assert world == args.gpus, "launch with torchrun --nproc-per-node %d (WORLD_SIZE=%d)" % (args.gpus, world)
     torch.backends.cudnn.benchmark = True
@@ -224,6 +229,9 @@ def main():
                "d2h_bytes_per_step": 4, "last_loss": last_loss}
     stats = step.stats()
     step.close()
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
+    os.close(saved_stdout)
 
     if rank == 0:
         out = {

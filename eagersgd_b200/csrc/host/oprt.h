@@ -1,0 +1,94 @@
+/* Host operation runtime: persistent, dependency-triggered operations progressed by one thread
+ * per rank, and collectives built from them.
+ *
+ * It provides what the reference's fflib2 core provides on the host (src/ff.h:100-165,
+ * src/ffop.c, src/ffschedule.c, src/ffprogress.c): operations (send, recv, compute, no-op,
+ * callback) that are created once and posted many times, happens-before edges with AND / OR /
+ * FIRST triggering, schedules with begin / end no-ops, buffers that can be resized between
+ * posts, reduction operators (built-in and user-defined) over int32 / int64 / float / double,
+ * and a recursive-doubling allreduce, an activation broadcast and a bounded-staleness limiter
+ * expressed as schedules.  The transport is an in-process mailbox between the ranks of a
+ * "world" (ranks are threads of one process); the GPU and multi-process paths of this
+ * framework do not use this runtime — they run the one-sided channel protocol instead.
+ */
+#ifndef ESGD_OPRT_H
+#define ESGD_OPRT_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* return codes (ff.h:4-10) */
+#define RT_COMPLETED 1
+#define RT_SUCCESS 0
+#define RT_ERROR (-1)
+#define RT_TIMEOUT (-2)
+
+/* datatypes and operators (ff.h:21-41); every operator is implemented */
+enum { RT_INT32 = 0, RT_INT64 = 1, RT_FLOAT = 2, RT_DOUBLE = 3 };
+enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUSTOM0 = 16 };
+
+/* option bits */
+#define RT_DEP_AND 0x0            /* run when all parents have completed (default) */
+#define RT_DEP_OR 0x1             /* run when any parent completes */
+#define RT_DEP_FIRST 0x2          /* on completion satisfy only ONE dependent, round-robin */
+#define RT_NON_PERSISTENT 0x4     /* runs at most once */
+#define RT_INPLACE ((int64_t)-2)
+#define RT_NONE ((int64_t)-1)
+
+typedef struct rt_world rt_world;
+typedef struct rt_rank rt_rank;
+typedef int64_t rt_op;        /* handle within a rank */
+typedef int64_t rt_buf;
+typedef int64_t rt_sched;
+typedef void (*rt_callback_fn)(rt_op op, void* arg);
+typedef void (*rt_operator_fn)(const void* a, const void* b, void* out, int64_t count, int dtype);
+
+rt_world* rt_world_create(int nranks);
+void rt_world_destroy(rt_world* w);
+rt_rank* rt_world_rank(rt_world* w, int r);
+int rt_rank_id(rt_rank* c);
+int rt_rank_size(rt_rank* c);
+
+/* buffers (ffbuffer_{create,resize,get_size,get_data,delete}) */
+rt_buf rt_buffer_create(rt_rank* c, void* user_ptr, int64_t count, int dtype); /* user_ptr NULL: runtime-owned */
+int rt_buffer_resize(rt_rank* c, rt_buf b, void* user_ptr, int64_t count);
+int64_t rt_buffer_count(rt_rank* c, rt_buf b);
+void* rt_buffer_data(rt_rank* c, rt_buf b);
+
+/* operations */
+rt_op rt_op_nop(rt_rank* c, int options);
+rt_op rt_op_callback(rt_rank* c, rt_callback_fn fn, void* arg, int options);
+rt_op rt_op_comp(rt_rank* c, rt_buf a, rt_buf b, rt_buf out, int op, int options);  /* out = a (op) b */
+rt_op rt_op_send(rt_rank* c, rt_buf b, int peer, int tag, int options);
+rt_op rt_op_recv(rt_rank* c, rt_buf b, int peer, int tag, int options);
+int rt_operator_create(rt_rank* c, rt_operator_fn fn);   /* returns an operator id >= RT_CUSTOM0 */
+int rt_op_hb(rt_rank* c, rt_op first, rt_op second);     /* first happens before second */
+int rt_op_post(rt_rank* c, rt_op op);
+int rt_op_wait(rt_rank* c, rt_op op, double timeout_s);  /* waits for the next completion not yet waited for */
+int rt_op_test(rt_rank* c, rt_op op);
+int64_t rt_op_completions(rt_rank* c, rt_op op);
+
+/* schedules (ffschedule_*) */
+rt_sched rt_schedule_create(rt_rank* c);
+int rt_schedule_add_op(rt_rank* c, rt_sched s, rt_op op);
+int rt_schedule_finalize(rt_rank* c, rt_sched s);        /* link roots to begin and leaves to end */
+rt_op rt_schedule_begin_op(rt_rank* c, rt_sched s);
+rt_op rt_schedule_end_op(rt_rank* c, rt_sched s);
+int rt_schedule_post(rt_rank* c, rt_sched s);
+int rt_schedule_wait(rt_rank* c, rt_sched s, double timeout_s);
+int rt_schedule_test(rt_rank* c, rt_sched s);
+int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap);   /* graphviz DOT */
+
+/* collectives */
+rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op);   /* snd == RT_INPLACE: in place */
+/* activation: any rank posts `activate`; every rank's `joined` op completes once per activation */
+rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined);
+/* limiter: posting `start` fires async[0..n-1] in turn, then sync, round-robin */
+int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op* sync_op);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

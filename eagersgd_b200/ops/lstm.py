@@ -1,0 +1,121 @@
+"""LSTM layer on the hand-written kernels: tensor-core projections + fused cell kernels.
+
+* ``x . W_ih^T`` for every time step is ONE tcgen05 GEMM ([T*B, I] x [4H, I]^T).
+* Per time step the recurrent product runs in swapped form ``W_hh . h_{t-1}^T -> [4H, B]`` so the
+  4H dimension fills the 128-row MMA tile and the small batch is the N dimension; the fused cell
+  kernel adds it to the input projection, applies the gates and updates c and h.
+* Backward keeps only the ``dh`` recurrence sequential (one swapped GEMM + one fused kernel per
+  step); the three weight/input gradients are single large GEMMs over all time steps (split-K).
+
+Stands where the reference calls ``torch.nn.LSTM`` (cuDNN) in its video classifier
+(deep500 samples/ucf101_resnetlstm.py:41-59).  Gate order i, f, g, o; weights are
+``[4H, in]`` as in ``torch.nn.LSTM``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from ..parallel import _native as N
+from .gemm import gemm
+
+
+def _lib():
+    lib = N.cuda()
+    if not getattr(lib, "_lstm_bound", False):
+        vp, i32 = C.c_void_p, C.c_int
+        lib.esgd_lstm_cell_fwd.argtypes = [vp] * 7 + [i32, i32, i32, vp]
+        lib.esgd_lstm_cell_bwd.argtypes = [vp] * 7 + [i32, i32, i32, vp]
+        lib._lstm_bound = True
+    return lib
+
+
+def _ck(rc, what):
+    if rc != 0:
+        raise RuntimeError("%s failed with code %d" % (what, rc))
+
+
+class _LstmLayer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, bias):
+        T, B, I = x.shape
+        H = w_hh.shape[1]
+        lib = _lib()
+        s = torch.cuda.current_stream(x.device).cuda_stream
+        x2d = x.reshape(T * B, I)
+        xproj = gemm(x2d, w_ih)                                          # [T*B, 4H] bf16
+        y = torch.empty(T, B, H, dtype=torch.bfloat16, device=x.device)
+        c = torch.empty(T, B, H, dtype=torch.float32, device=x.device)
+        gates = torch.empty(T, B, 4 * H, dtype=torch.bfloat16, device=x.device)
+        hprojT = torch.empty(4 * H, B, dtype=torch.float32, device=x.device)
+        for t in range(T):
+            hp = None
+            if t > 0:
+                gemm(w_hh, y[t - 1], out=hprojT)                         # W_hh . h^T : [4H, B] fp32
+                hp = hprojT.data_ptr()
+            _ck(lib.esgd_lstm_cell_fwd(xproj[t * B:(t + 1) * B].data_ptr(), hp, bias.data_ptr(),
+                                       c[t - 1].data_ptr() if t > 0 else None, c[t].data_ptr(), y[t].data_ptr(),
+                                       gates[t].data_ptr(), B, H, B, s), "lstm cell forward")
+        ctx.save_for_backward(x2d, w_ih, w_hh, y, c, gates)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w_ih, w_hh, y, c, gates = ctx.saved_tensors
+        T, B, H = y.shape
+        I = w_ih.shape[1]
+        lib = _lib()
+        s = torch.cuda.current_stream(dy.device).cuda_stream
+        dy = dy.contiguous()
+        dG = torch.empty(T, B, 4 * H, dtype=torch.bfloat16, device=dy.device)
+        dc = torch.zeros(B, H, dtype=torch.float32, device=dy.device)
+        dh_recT = torch.empty(H, B, dtype=torch.float32, device=dy.device)
+        for t in range(T - 1, -1, -1):
+            _ck(lib.esgd_lstm_cell_bwd(gates[t].data_ptr(), c[t - 1].data_ptr() if t > 0 else None, c[t].data_ptr(),
+                                       dy[t].data_ptr(), dh_recT.data_ptr() if t < T - 1 else None, dc.data_ptr(),
+                                       dG[t].data_ptr(), B, H, B, s), "lstm cell backward")
+            if t > 0:
+                gemm(w_hh, dG[t], a_kmajor=False, out=dh_recT)           # W_hh^T . dG_t^T : [H, B] fp32
+        dG2d = dG.view(T * B, 4 * H)
+        splits = max(2, min(64, (T * B) // 256))
+        dx = dw_ih = dw_hh = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dG2d, w_ih, b_kmajor=False).view(T, B, I)          # [T*B, 4H] x W_ih[4H(K), I]
+        if ctx.needs_input_grad[1]:
+            dw_ih = gemm(dG2d, x2d, a_kmajor=False, b_kmajor=False, splits=splits).to(w_ih.dtype)
+        if ctx.needs_input_grad[2]:
+            if T > 1:
+                dw_hh = gemm(dG2d[B:], y.view(T * B, H)[:-B], a_kmajor=False, b_kmajor=False,
+                             splits=splits).to(w_hh.dtype)
+            else:
+                dw_hh = torch.zeros_like(w_hh)
+        if ctx.needs_input_grad[3]:
+            db = dG2d.float().sum(0)
+        return dx, dw_ih, dw_hh, db
+
+
+def lstm_layer(x: torch.Tensor, w_ih: torch.Tensor, w_hh: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x: [T, B, I] -> h: [T, B, H], zero initial state.  ``bias`` is b_ih + b_hh (fp32 [4H])."""
+    T, B, I = x.shape
+    H = w_hh.shape[1]
+    if x.is_cuda and x.dtype == torch.bfloat16 and B % 8 == 0 and I % 8 == 0 and H % 8 == 0:
+        return _LstmLayer.apply(x.contiguous(), w_ih, w_hh, bias.float())
+    return lstm_layer_reference(x, w_ih, w_hh, bias)
+
+
+def lstm_layer_reference(x, w_ih, w_hh, bias):
+    """Plain PyTorch restatement (oracle and CPU path)."""
+    T, B, _ = x.shape
+    H = w_hh.shape[1]
+    h = x.new_zeros(B, H)
+    c = x.new_zeros(B, H, dtype=torch.float32)
+    out = []
+    for t in range(T):
+        pre = (x[t] @ w_ih.t() + h @ w_hh.t()).float() + bias.float()
+        i, f, g, o = pre.chunk(4, dim=-1)
+        c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+        h = (torch.sigmoid(o) * torch.tanh(c)).to(x.dtype)
+        out.append(h)
+    return torch.stack(out)

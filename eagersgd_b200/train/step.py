@@ -107,9 +107,16 @@ class TrainStep:
 
     def _step(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
         self.opt.zero_grad()
-        if self.autocast:
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                logits = self.net(x)
+        if self.impl == "ddp":
+            # the baseline arm: PyTorch's own operators (cuDNN / cuBLAS) under bf16 autocast
+            from ..ops.functional import reference_ops
+            with reference_ops():
+                with torch.autocast("cuda", dtype=torch.bfloat16, enabled=self.autocast):
+                    logits = self.net(x.float() if self.device.type != "cuda" else x)
+                loss = torch.nn.functional.cross_entropy(logits.float(), y)
+            loss.backward()
+            self.opt.step()
+            return loss.detach()
         else:
             logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
                               else x.to(self.compute_dtype))

@@ -185,3 +185,26 @@ def test_bottleneck_block_matches_reference_ops():
     for (n1, p1), (_, p2) in zip(blk.named_parameters(), blk2.named_parameters()):
         c = F.cosine_similarity(p1.grad.float().flatten(), p2.grad.float().flatten(), dim=0).item()
         assert c > 0.98, (n1, c)
+
+
+@pytest.mark.parametrize("T,B,I,H", [(5, 16, 64, 128), (12, 8, 256, 256)])
+def test_lstm_layer_forward_backward(T, B, I, H):
+    from eagersgd_b200.ops.lstm import lstm_layer, lstm_layer_reference
+    torch.manual_seed(7)
+    x = (torch.randn(T, B, I, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    k = 1.0 / H ** 0.5
+    w_ih = torch.empty(4 * H, I, device=DEV).uniform_(-k, k).to(torch.bfloat16).requires_grad_()
+    w_hh = torch.empty(4 * H, H, device=DEV).uniform_(-k, k).to(torch.bfloat16).requires_grad_()
+    bias = (torch.randn(4 * H, device=DEV) * 0.1).requires_grad_()
+    y = lstm_layer(x, w_ih, w_hh, bias)
+    g = torch.randn(T, B, H, device=DEV).to(torch.bfloat16)
+    y.backward(g)
+    xr, wi, wh, br = (t.detach().float().requires_grad_() for t in (x, w_ih, w_hh, bias))
+    yr = lstm_layer_reference(xr, wi, wh, br)
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=3e-2, atol=3e-2)
+    for a, b_, name in ((x.grad, xr.grad, "dx"), (w_ih.grad, wi.grad, "dw_ih"), (w_hh.grad, wh.grad, "dw_hh"),
+                        (bias.grad, br.grad, "db")):
+        cos = F.cosine_similarity(a.float().flatten(), b_.flatten(), dim=0).item()
+        assert cos > 0.99, (name, cos)
+        assert (a.float() - b_).abs().max().item() < 0.05 * b_.abs().max().item() + 5e-2, name
