@@ -1,0 +1,218 @@
+"""Host operation runtime: the reference's fflib2 evaluation programs as assertions
+(evaluation/send_recv.c, ping_pong_dep.c, ping_pong_schedule.c, simple_computation.c,
+custom_computation.c, first_dep.c, activation_1.c, activation_tree_multiple.c, limiter.c,
+allreduce.c, allreduce_inplace.c, allreduce_buffers_user_managed*.c)."""
+import threading
+
+import numpy as np
+import pytest
+
+from eagersgd_b200.parallel import oprt as R
+
+
+def _run(world, fn):
+    errs = []
+
+    def wrap(rank):
+        try:
+            fn(rank)
+        except Exception as e:  # noqa
+            import traceback
+            errs.append(traceback.format_exc())
+    th = [threading.Thread(target=wrap, args=(world.ranks[r],)) for r in range(world.n)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errs, errs[0]
+
+
+def test_send_recv():
+    with R.World(2) as w:
+        data = np.arange(64, dtype=np.int32)
+        got = np.zeros(64, dtype=np.int32)
+        r0, r1 = w.ranks
+        s = r0.send(r0.buffer(data), 1, 3)
+        rv = r1.recv(r1.buffer(got), 0, 3)
+        r1.post(rv)
+        r0.post(s)
+        assert r1.wait(rv) == R.SUCCESS and r0.wait(s) == R.SUCCESS
+        assert np.array_equal(got, data)
+
+
+def test_ping_pong_with_dependency_is_persistent():
+    """recv -> send happens-before edge; the same ops are re-posted every iteration."""
+    with R.World(2) as w:
+        r0, r1 = w.ranks
+        ping, pong = np.zeros(8, dtype=np.int64), np.zeros(8, dtype=np.int64)
+        echo = np.zeros(8, dtype=np.int64)
+        s0 = r0.send(r0.buffer(ping), 1, 0)
+        v0 = r0.recv(r0.buffer(pong), 1, 1)
+        v1 = r1.recv(r1.buffer(echo), 0, 0)
+        s1 = r1.send(r1.buffer(echo), 0, 1)
+        r1.hb(v1, s1)                       # the pong is sent once the ping has arrived
+        for it in range(20):
+            ping[:] = it
+            r1.post(v1)
+            r0.post(v0)
+            r0.post(s0)
+            assert r0.wait(v0) == R.SUCCESS
+            assert np.all(pong == it)
+        assert r1.completions(s1) == 20
+
+
+def test_computation_builtin_and_custom_operators():
+    with R.World(1) as w:
+        r = w.ranks[0]
+        a, b, c = np.arange(10, dtype=np.int32), np.arange(10, dtype=np.int32) * 2, np.zeros(10, dtype=np.int32)
+        ba, bb, bc = r.buffer(a), r.buffer(b), r.buffer(c)
+        for op, expect in ((R.SUM, a + b), (R.PROD, a * b), (R.MAX, np.maximum(a, b)), (R.MIN, np.minimum(a, b))):
+            o = r.comp(ba, bb, bc, op)
+            r.post(o)
+            r.wait(o)
+            assert np.array_equal(c, expect)
+        plus_one = r.operator(lambda x, y, out: np.copyto(out, x + y + 1), np.int32)
+        o = r.comp(ba, bb, bc, plus_one)
+        r.post(o)
+        r.wait(o)
+        assert np.array_equal(c, a + b + 1)
+
+
+def test_first_dependency_vs_and_fanout():
+    """DEP_FIRST satisfies one dependent per completion; a plain op satisfies all of them."""
+    deps = 5
+    with R.World(1) as w:
+        r = w.ranks[0]
+        acc = {"first": 0, "all": 0}
+        first = r.nop(R.DEP_FIRST)
+        plain = r.nop()
+        for _ in range(deps):
+            r.hb(first, r.callback(lambda op: acc.__setitem__("first", acc["first"] + 1), R.DEP_OR))
+            r.hb(plain, r.callback(lambda op: acc.__setitem__("all", acc["all"] + 1), R.DEP_OR))
+        done = r.nop()
+        for _ in range(deps):
+            r.post(first)
+            r.wait(first)
+            r.post(plain)
+            r.wait(plain)
+        r.post(done)
+        r.wait(done)
+        import time
+        time.sleep(0.05)
+        assert acc["first"] == deps and acc["all"] == deps * deps
+
+
+def test_or_dependency():
+    n = 50
+    with R.World(1) as w:
+        r = w.ranks[0]
+        count = [0]
+        a, b = r.nop(), r.nop()
+        either = r.callback(lambda op: count.__setitem__(0, count[0] + 1), R.DEP_OR)
+        r.hb(a, either)
+        r.hb(b, either)
+        for i in range(n):
+            r.post(a if i % 2 else b)
+            r.wait(either)
+        assert count[0] == n
+
+
+def test_schedule_and_dot():
+    with R.World(1) as w:
+        r = w.ranks[0]
+        x = np.ones(4, dtype=np.float32)
+        y = np.zeros(4, dtype=np.float32)
+        bx, by = r.buffer(x), r.buffer(y)
+        s = r.schedule()
+        c1 = r.comp(bx, bx, by, R.SUM)          # y = 2
+        c2 = r.comp(by, bx, by, R.SUM)          # y = 3
+        r.hb(c1, c2)
+        r.schedule_add(s, c1)
+        r.schedule_add(s, c2)
+        for _ in range(3):
+            r.schedule_post(s)
+            assert r.schedule_wait(s) == R.SUCCESS
+            assert np.all(y == 3)
+        dot = r.schedule_dot(s)
+        assert dot.startswith("digraph") and "->" in dot and "begin" in dot
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 5, 8])
+def test_allreduce_closed_form_persistent_and_resized(world):
+    """(i + j) * size closed form; the schedule is re-posted with new data and a resized buffer."""
+    with R.World(world) as w:
+        def body(r):
+            n = 33
+            snd, rcv = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+            bs, br = r.buffer(snd), r.buffer(rcv)
+            s = r.allreduce(bs, br, tag=7)
+            for it in range(10):
+                snd[:] = np.arange(n) + it + r.id
+                r.schedule_post(s)
+                assert r.schedule_wait(s) == R.SUCCESS
+                expect = (np.arange(n) + it) * world + sum(range(world))
+                assert np.array_equal(rcv, expect), (r.id, it, rcv[:4], expect[:4])
+            # in place, float, maximum
+            x = np.full(5, float(r.id), dtype=np.float64)
+            bx = r.buffer(x)
+            s2 = r.allreduce(R.INPLACE, bx, tag=9, op=R.MAX)
+            r.schedule_post(s2)
+            r.schedule_wait(s2)
+            assert np.all(x == world - 1)
+        _run(w, body)
+
+
+def test_allreduce_completion_callback():
+    with R.World(2) as w:
+        fired = [0, 0]
+
+        def body(r):
+            x = np.full(4, r.id + 1, dtype=np.int64)
+            s = r.allreduce(R.INPLACE, r.buffer(x), tag=1)
+            cb = r.callback(lambda op: fired.__setitem__(r.id, fired[r.id] + 1), R.DEP_OR)
+            r.hb(r.schedule_end(s), cb)
+            r.schedule_post(s)
+            r.wait(cb)
+            assert np.all(x == 3)
+        _run(w, body)
+        assert fired == [1, 1]
+
+
+def test_activation_from_random_ranks():
+    """Any rank may activate; every rank's join op completes exactly once per activation."""
+    world, n = 4, 30
+    rng = np.random.RandomState(439634)
+    activators = rng.randint(world, size=n)
+    with R.World(world) as w:
+        def body(r):
+            s, act, joined = r.activation(tag=5)
+            for k in range(n):
+                if activators[k] == r.id:
+                    r.post(act)
+                assert r.wait(joined) == R.SUCCESS
+            assert r.completions(joined) == n
+        _run(w, body)
+
+
+def test_limiter_pattern():
+    """15 posts with 3 async slots: A A A S A A A S ... (evaluation/limiter.c prints this)."""
+    with R.World(1) as w:
+        r = w.ranks[0]
+        start, asyncs, sync = r.limiter(3)
+        seq = []
+        for a in asyncs:
+            r.hb(a, r.callback(lambda op: seq.append("A"), R.DEP_OR))
+        end = r.callback(lambda op: seq.append("S"), R.DEP_OR)
+        r.hb(sync, end)
+        for _ in range(15):
+            r.post(start)
+            r.wait(start)
+        import time
+        time.sleep(0.1)
+        assert "".join(seq) == "AAAS" * 3 + "AAA"
+
+
+def test_wait_timeout_reports_instead_of_hanging():
+    with R.World(2) as w:
+        r0 = w.ranks[0]
+        rv = r0.recv(r0.buffer(count=4, dtype=np.int32), 1, 99)
+        r0.post(rv)
+        assert r0.wait(rv, timeout=0.2) == R.TIMEOUT
