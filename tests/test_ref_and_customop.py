@@ -1,0 +1,100 @@
+"""CPU oracles (NumPy and C++) against PyTorch, the operator JIT pipeline, and the validation harness."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from eagersgd_b200.ref import numpy_ops as R
+from eagersgd_b200.ref import cpp_ops as CPP
+
+
+@pytest.mark.parametrize("stride,pad,k", [(1, 1, 3), (2, 1, 3), (2, 3, 7), (1, 0, 1)])
+def test_conv_oracles(stride, pad, k):
+    rng = np.random.RandomState(0)
+    x, w = rng.randn(2, 3, 9, 10).astype(np.float32), rng.randn(4, 3, k, k).astype(np.float32)
+    xt, wt = torch.tensor(x, requires_grad=True), torch.tensor(w, requires_grad=True)
+    yt = F.conv2d(xt, wt, None, stride, pad)
+    dy = rng.randn(*yt.shape).astype(np.float32)
+    yt.backward(torch.tensor(dy))
+    assert np.allclose(R.conv2d(x, w, stride, pad), yt.detach().numpy(), atol=1e-4)
+    assert np.allclose(CPP.conv2d(x, w, stride, pad), yt.detach().numpy(), atol=1e-4)
+    for dx, dw in (R.conv2d_grad(x, w, dy.astype(np.float64), stride, pad), CPP.conv2d_grads(x, w, dy, stride, pad)):
+        assert np.allclose(dx, xt.grad.numpy(), atol=1e-3) and np.allclose(dw, wt.grad.numpy(), atol=1e-3)
+
+
+def test_batchnorm_oracles():
+    rng = np.random.RandomState(1)
+    x = rng.randn(4, 6, 5, 5).astype(np.float32)
+    g, b = rng.rand(6).astype(np.float32) + 0.5, rng.randn(6).astype(np.float32)
+    xt = torch.tensor(x, requires_grad=True)
+    gt, bt = torch.tensor(g, requires_grad=True), torch.tensor(b, requires_grad=True)
+    rm, rv = torch.zeros(6), torch.ones(6)
+    yt = F.batch_norm(xt, rm, rv, gt, bt, True, 0.1, 1e-5)
+    dy = rng.randn(*x.shape).astype(np.float32)
+    yt.backward(torch.tensor(dy))
+    for mod in (R, CPP):
+        y, nrm, nrv, mean, invstd = mod.batchnorm_training(x, g, b, np.zeros(6, np.float32), np.ones(6, np.float32), 0.1)
+        assert np.allclose(y, yt.detach().numpy(), atol=1e-4)
+        assert np.allclose(nrm, rm.numpy(), atol=1e-5) and np.allclose(nrv, rv.numpy(), atol=1e-4)
+        dx, dg, db = mod.batchnorm_training_grad(x, g, mean, invstd, dy)
+        assert np.allclose(dx, xt.grad.numpy(), atol=1e-3)
+        assert np.allclose(dg, gt.grad.numpy(), atol=1e-3) and np.allclose(db, bt.grad.numpy(), atol=1e-3)
+
+
+def test_misc_oracles():
+    rng = np.random.RandomState(2)
+    a, b = rng.randn(5, 7).astype(np.float32), rng.randn(7, 3).astype(np.float32)
+    assert np.allclose(CPP.gemm(a, b), a @ b, atol=1e-4)
+    assert np.allclose(CPP.gemm(a.T.copy(), b.T.copy(), trans_a=True, trans_b=True), a @ b, atol=1e-4)
+    assert np.allclose(R.gemm(a, b, np.ones((5, 3)), 2.0, 0.5), 2 * (a @ b) + 0.5)
+    x = rng.randn(2, 3, 8, 8).astype(np.float32)
+    t = torch.tensor(x)
+    assert np.allclose(R.maxpool(x), F.max_pool2d(t, 3, 2, 1).numpy()) and np.allclose(CPP.maxpool(x), R.maxpool(x))
+    assert np.allclose(R.globalaveragepool(x), CPP.global_avgpool(x), atol=1e-5)
+    assert np.allclose(R.relu(x), CPP.relu(x))
+    logits, labels = rng.randn(6, 10).astype(np.float32), rng.randint(0, 10, 6)
+    lt = torch.tensor(logits, requires_grad=True)
+    F.cross_entropy(lt, torch.tensor(labels)).backward()
+    loss, grad = R.softmax_cross_entropy(logits, labels)
+    assert abs(loss - F.cross_entropy(torch.tensor(logits), torch.tensor(labels)).item()) < 1e-5
+    assert np.allclose(grad, lt.grad.numpy(), atol=1e-6) and np.allclose(CPP.softmax(logits), R.softmax(logits), atol=1e-6)
+    w, acc = R.momentum_sgd(np.ones(3), np.ones(3), np.zeros(3), 0.1, 0.9)
+    assert np.allclose(w, 0.9) and np.allclose(acc, 1.0)
+
+
+SCALE_OP = r'''
+#include <eagersgd/op.h>
+// y = a * x + b, with gradients for x and b
+class ScaleShift : public eagersgd::CustomOperator {
+  int64_t n;
+ public:
+  ScaleShift(const eagersgd::tensor_t* in, int, const eagersgd::tensor_t*, int) : n(in[0].numel()) {}
+  void forward(void** in, void** out) override {
+    const float* x = (const float*)in[0]; const float* b = (const float*)in[1]; float* y = (float*)out[0];
+    for (int64_t i = 0; i < n; ++i) y[i] = SCALE * x[i] + b[i];
+  }
+  void backward(void** g, void**, void**, void** ig) override {
+    const float* dy = (const float*)g[0]; float* dx = (float*)ig[0]; float* db = (float*)ig[1];
+    for (int64_t i = 0; i < n; ++i) { dx[i] = SCALE * dy[i]; db[i] = dy[i]; }
+  }
+  int64_t report(void*) override { return n * 4; }
+};
+ESGD_REGISTER_OP(ScaleShift)
+'''
+
+
+def test_inline_cpp_operator_and_validation(tmp_path):
+    from eagersgd_b200.ops.compile import TensorDescriptor, compile_custom_op, custom_op, custom_python_op
+    from eagersgd_b200.ops.validation import test_op_forward, test_op_gradient
+    d = TensorDescriptor(torch.float32, (3, 4))
+    op = compile_custom_op("scaleshift", SCALE_OP, [d, d], [d], defines={"SCALE": "2.5f"}, output_dir=str(tmp_path))
+    fn = custom_op(op)
+    x, b = torch.randn(3, 4), torch.randn(3, 4)
+    test_op_forward(fn, [x, b], 2.5 * x + b)
+    test_op_gradient(fn, [x, b], eps=1e-2, rtol=1e-2, atol=1e-2)
+    assert op.report() == 48 and not op.supports_cuda
+    sq = custom_python_op(lambda t: t * t, lambda g, ins, outs: (2 * ins[0] * g[0],))
+    test_op_gradient(sq, [torch.randn(5)], eps=1e-3, rtol=1e-2, atol=1e-2)
+    with pytest.raises(AssertionError):
+        bad = custom_python_op(lambda t: t * t, lambda g, ins, outs: (ins[0] * g[0],))
+        test_op_gradient(bad, [torch.randn(5) + 2], eps=1e-3)
