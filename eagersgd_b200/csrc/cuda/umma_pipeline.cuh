@@ -27,6 +27,7 @@ constexpr int BK = 64;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int PANEL_BYTES = BM * 64 * 2;     // one 128 x 64 bf16 output panel
 constexpr int NUM_THREADS = 192;
+constexpr int NUM_PANEL_BUFS = 4;            // output staging ring: up to 3 TMA stores drain while the next panel is built
 
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
 
@@ -44,9 +45,9 @@ struct Epilogue {
 template <int BN>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = BN == 256 ? 3 : (BN == 128 ? 5 : 6);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * PANEL_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_PANEL_BUFS * PANEL_BYTES + 1024 + 256;
 };
 
 // Problem policy requirements (all __device__ const):
@@ -67,7 +68,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
   uint8_t* sA = smem;
   uint8_t* sB = sA + STAGES * A_STAGE_BYTES;
   uint8_t* sC = sB + STAGES * C::B_STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sC + 2 * PANEL_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sC + NUM_PANEL_BUFS * PANEL_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -148,8 +149,8 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     const int row = q * 32 + lane;          // tile row owned by this thread
     int acc = 0;
     uint32_t acc_phase = 0;
-    int buf = 0;                            // staging panel buffer in use
-    bool pending[2] = {false, false};       // a TMA store may still be reading the buffer (thread et == 0)
+    int buf = 0;                            // staging panel buffer in use (ring)
+    int stores_issued = 0;                  // bulk-store groups committed so far (thread et == 0)
     // statistics: thread (cp = et % 32, rq = et / 32) covers columns 2cp, 2cp+1 of each panel, rows 32rq..+32
     float st_sum[BN / 64][2], st_sq[BN / 64][2];
 #pragma unroll
@@ -167,13 +168,16 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
         for (int pnl = 0; pnl < BN / 64; ++pnl) {
           if (t.n0 + pnl * 64 >= ep.n_total) break;  // uniform across the CTA
           uint8_t* panel = sC + buf * PANEL_BYTES;
-          if (et == 0 && pending[buf]) { tma_store_wait_read<1>(); pending[buf] = false; }
+          // the store that used this buffer NUM_PANEL_BUFS panels ago must have read it
+          if (et == 0 && stores_issued >= NUM_PANEL_BUFS) tma_store_wait_read<NUM_PANEL_BUFS - 1>();
+          uint32_t r2[2][32];
+          tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64), r2[0]);       // both halves in flight, one wait
+          tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64 + 32), r2[1]);
+          tmem_ld_wait();
           named_barrier_sync(1, 128);                // the buffer is free for everyone
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64 + half * 32), r);
-            tmem_ld_wait();
+            const uint32_t* r = r2[half];
             const int col0 = t.n0 + pnl * 64 + half * 32;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -197,7 +201,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
           if (et == 0) {
             prob.store_panel(t, pnl, panel);
             tma_store_commit();
-            pending[buf] = true;
+            stores_issued++;
           }
           if (ep.col_sum != nullptr) {
             const int cp = et & 31, rq = et >> 5;
@@ -215,7 +219,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
             }
             st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
           }
-          buf ^= 1;
+          buf = (buf + 1) % NUM_PANEL_BUFS;
         }
       } else {
         // fp32 outputs (logits, split-K weight gradients): direct stores / atomics from registers
