@@ -201,6 +201,24 @@ void esgd_ctl_stats(const void* base, uint64_t* stats) {
   stats[9] = c->stat_last_contrib; stats[10] = c->status; stats[11] = c->latest_round;
 }
 
+// Copy the trace ring, oldest first, as rows of 10 uint64: step, round, t_ns, wait_ns, role, activator,
+// fresh_mask, contrib_mask, is_sync, drain_rounds.  Returns the number of rows written.
+int32_t esgd_ctl_trace(const void* base, uint64_t* rows, int32_t max_rows) {
+  const ChannelCtl* c = (const ChannelCtl*)base;
+  const uint64_t last = c->local_step;
+  const uint64_t first = last > (uint64_t)kTraceRing ? last - kTraceRing + 1 : 1;
+  int32_t n = 0;
+  for (uint64_t k = first; k <= last && n < max_rows; ++k) {
+    const TraceEntry& e = c->trace[k % kTraceRing];
+    if (e.step != k) continue;
+    uint64_t* r = rows + (size_t)n * 10;
+    r[0] = e.step; r[1] = e.round; r[2] = e.t_ns; r[3] = e.wait_ns; r[4] = e.role; r[5] = e.activator;
+    r[6] = e.fresh_mask; r[7] = e.contrib_mask; r[8] = e.is_sync; r[9] = e.drain_rounds;
+    ++n;
+  }
+  return n;
+}
+
 void esgd_ctl_clear_status(void* base) { ((ChannelCtl*)base)->status = 0; }
 
 }  // extern "C"

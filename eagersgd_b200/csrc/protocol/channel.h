@@ -69,6 +69,21 @@ struct alignas(128) RoundDesc {
   uint64_t consumed[kMaxRanks];   // last consumed epoch per rank after this round
 };
 
+// One entry of the per-rank trace ring (the newest kTraceRing steps of this rank).
+constexpr int kTraceRing = 64;
+struct TraceEntry {
+  uint64_t step;          // local post count
+  uint64_t round;         // round applied (participant) or newest round seen (absent)
+  uint64_t t_ns;          // clock at the end of the control step
+  uint64_t wait_ns;       // time spent in this control step (publish, election, waits)
+  uint32_t role;          // Role
+  uint32_t activator;
+  uint32_t fresh_mask;
+  uint32_t contrib_mask;
+  uint32_t is_sync;
+  uint32_t drain_rounds;  // rounds collected from the mailbox (absent ranks)
+};
+
 // One per (channel, rank); lives in that rank's arena; peers read and write it.
 struct alignas(128) ChannelCtl {
   uint64_t pub_epoch[kMaxRanks];          // [j] pushed by rank j: its latest published epoch
@@ -92,6 +107,7 @@ struct alignas(128) ChannelCtl {
   uint64_t stat_wait_ns;                  // time spent in bounded waits
   uint64_t stat_last_round;               // round applied at the last step
   uint64_t stat_last_contrib;
+  TraceEntry trace[kTraceRing];           // ring indexed by local_step % kTraceRing
 };
 
 // What the control step hands to the data phase of the same rank.

@@ -275,7 +275,21 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
     const RoundDesc* dl = &me->desc[rr % kDescRing];
     if (dl->round == rr && dl->consumed[i] + 1 < k) me->stat_dropped_grads++;
   }
-  me->stat_wait_ns += E::now_ns() - t0;
+  const uint64_t t1 = E::now_ns();
+  me->stat_wait_ns += t1 - t0;
+  {
+    TraceEntry* te = &me->trace[k % kTraceRing];
+    te->step = k;
+    te->round = participant ? k : me->stat_last_round;
+    te->t_ns = t1;
+    te->wait_ns = t1 - t0;
+    te->role = (uint32_t)plan->role;
+    te->activator = participant ? d->activator : 0xffffffffu;
+    te->fresh_mask = participant ? d->fresh_mask : 0u;
+    te->contrib_mask = participant ? d->contrib_mask : 0u;
+    te->is_sync = sync_round ? 1u : 0u;
+    te->drain_rounds = (uint32_t)plan->drain_rounds;
+  }
 }
 
 // Called once per rank after its data phase.

@@ -307,6 +307,17 @@ class EagerOptimizer:
             "status": max(p["status"] for p in per), "buckets": len(per),
         }
 
+    def trace(self, bucket: int = 0) -> list:
+        """Per-step trace of one bucket's channel (newest 64 steps): role, round, activator,
+        fresh / contributor masks, time spent waiting."""
+        return self.buckets[bucket].channel.trace()
+
+    def dump_trace(self, path: str) -> None:
+        import json
+        with open(path, "w") as f:
+            json.dump({"rank": self.group.rank, "mode": self.mode,
+                       "buckets": [b.channel.trace() for b in self.buckets], "stats": self.stats()}, f)
+
     def master_params(self):
         """(parameter, fp32 master view) pairs of the fused path; (p, p) otherwise."""
         for b in self.buckets:

@@ -80,6 +80,8 @@ def host():
         lib.esgd_cpu_flush.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.esgd_ctl_stats.argtypes = [C.c_void_p, C.c_void_p]
         lib.esgd_ctl_clear_status.argtypes = [C.c_void_p]
+        lib.esgd_ctl_trace.restype = C.c_int32
+        lib.esgd_ctl_trace.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
         lib.esgd_majority_initiator.restype = C.c_int32
         lib.esgd_majority_initiator.argtypes = [C.c_uint64, C.c_uint64, C.c_int32]
         lib.esgd_limiter_is_sync.restype = C.c_int32
@@ -128,3 +130,19 @@ def parse_stats(raw) -> dict:
 def launch_count() -> int:
     """Kernels launched so far by the CUDA library of this package."""
     return int(cuda().esgd_launch_count())
+
+
+TRACE_FIELDS = ("step", "round", "t_ns", "wait_ns", "role", "activator", "fresh_mask", "contrib_mask", "is_sync",
+                "drain_rounds")
+
+
+def parse_trace(ctl_host_ptr) -> list:
+    """Trace ring of a control block that is readable from the host (CPU segment or a host copy)."""
+    rows = (C.c_uint64 * (64 * 10))()
+    n = host().esgd_ctl_trace(ctl_host_ptr, rows, 64)
+    out = []
+    for i in range(n):
+        e = {f: int(rows[i * 10 + j]) for j, f in enumerate(TRACE_FIELDS)}
+        e["role"] = ROLE_NAMES.get(e["role"], str(e["role"]))
+        out.append(e)
+    return out

@@ -139,6 +139,9 @@ class CpuChannel:
             raise N.ChannelError(st, "cpu rank %d flush" % self.rank)
         return out, self.info
 
+    def trace(self) -> list:
+        return N.parse_trace(C.c_void_p(self._bases[self.rank]))
+
     def stats(self) -> dict:
         raw = (C.c_uint64 * 16)()
         self.lib.esgd_ctl_stats(C.c_void_p(self._bases[self.rank]), raw)

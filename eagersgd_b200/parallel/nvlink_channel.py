@@ -140,6 +140,11 @@ class NvlinkChannel:
         N.host().esgd_ctl_stats(self._ctl_host, raw)
         return N.parse_stats(raw)
 
+    def trace(self) -> list:
+        """The newest (up to 64) steps of this rank: role, round, activator, masks, wait time."""
+        self.stats()   # refreshes the host copy of the control block
+        return N.parse_trace(self._ctl_host)
+
     def check(self, where: str = "") -> None:
         st = self.stats()["status"]
         if st:

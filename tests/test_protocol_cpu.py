@@ -158,3 +158,28 @@ def test_dead_rank_times_out_with_status():
     with pytest.raises(N.ChannelError) as e:
         ch.step(np.ones(count, dtype=np.float32))
     assert e.value.status & 2
+
+
+def test_trace_ring_and_watchdog():
+    """The trace ring records role / round / masks per step; the watchdog turns a status word into an error."""
+    from eagersgd_b200.parallel.watchdog import Watchdog
+    world, count = 2, 16
+    segs = LocalSegments(world, count, np.float32)
+    chans = [CpuChannel(segs.bases, r, world, count, np.float32, mode="sync", limiter=-1, timeout_s=5) for r in range(world)]
+    th = [threading.Thread(target=lambda c=c: [c.step(np.ones(count, dtype=np.float32)) for _ in range(5)]) for c in chans]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    tr = chans[0].trace()
+    assert [e["step"] for e in tr] == [1, 2, 3, 4, 5]
+    assert all(e["role"] == "participant" and e["fresh_mask"] == 3 and e["is_sync"] == 1 for e in tr)
+
+    class FakeOpt:
+        def check(self_inner):
+            raise N.ChannelError(2, "fake")
+    seen = []
+    wd = Watchdog(FakeOpt(), period_s=0.05, on_failure=seen.append).start()
+    time.sleep(0.3)
+    wd.stop()
+    assert seen and seen[0].status == 2
+    with pytest.raises(N.ChannelError):
+        wd.raise_if_failed()
