@@ -30,7 +30,7 @@ namespace {
 template <int BN_>
 struct ConvProblem {
   static constexpr int BN = BN_;
-  static constexpr bool A_MN = false, B_MN = false;
+  static constexpr bool A_MN = false, B_MN = false, kZeroStages = false;
   CUtensorMap tmX, tmW, tmY;
   int N, Ho, Wo, Cout;
   int R, S, stride, pad;
@@ -78,12 +78,72 @@ struct ConvProblem {
   __device__ __forceinline__ void* row_ptr(const Tile&, int) const { return nullptr; }
 };
 
+
+// Weight gradient:  dw[k, r, s, c] = sum over output pixels of dy[pixel, k] * x[pixel shifted by tap (r, s), c].
+// GEMM view per tap: M = Cout, N = Cin, K = pixels.  Both operands are "MN-major" (the pixel dimension is the
+// row of the NHWC storage): a k-block is a box of up to 64 output pixels, loaded once from dy (two 64-channel
+// atoms for the 128 MMA rows) and once from x at the tap's offset (zero-filled outside the image, element
+// strides for stride 2).  Boxes smaller than 64 pixels leave the tail rows of the stage at their initial
+// zeros.  Work is split over taps, channel tiles and pixel ranges (split-K) and meets in fp32 atomics.
+template <int BN_>
+struct ConvWgradProblem {
+  static constexpr int BN = BN_;
+  static constexpr bool A_MN = true, B_MN = true, kZeroStages = true;
+  CUtensorMap tmDY, tmX;
+  int N, Ho, Wo, Cout, Cin;
+  int R, S, stride, pad;
+  int BW, BH, BI, w_tiles, h_tiles, i_tiles;
+  int m_tiles, n_tiles, splits, boxes_total, boxes_per_split;
+  float* dw;   // [Cout][R*S][Cin]
+
+  struct Tile { int kb0, kb1, n0, m0, tap; };
+
+  __device__ __forceinline__ bool tile(int it, Tile& t) const {
+    const int taps = R * S;
+    const int per_split = taps * m_tiles * n_tiles;
+    const int id = blockIdx.x + it * gridDim.x;
+    if (id >= per_split * splits) return false;
+    const int split = id / per_split;       // neighbouring CTAs share a pixel range: the boxes are reused out of L2
+    int rem = id - split * per_split;
+    t.tap = rem % taps; rem /= taps;
+    t.n0 = (rem % n_tiles) * BN;
+    t.m0 = (rem / n_tiles) * BM;
+    t.kb0 = split * boxes_per_split;
+    t.kb1 = min(t.kb0 + boxes_per_split, boxes_total);
+    return true;
+  }
+  __device__ __forceinline__ void load(const Tile& t, int kb, uint8_t* a, uint8_t* b, uint64_t* bar) const {
+    const int w0 = (kb % w_tiles) * BW, h0 = ((kb / w_tiles) % h_tiles) * BH, i0 = (kb / (w_tiles * h_tiles)) * BI;
+    const int r = t.tap / S, s = t.tap - r * S;
+#pragma unroll
+    for (int i = 0; i < BM / 64; ++i) tma_load_4d(a + i * 8192, &tmDY, bar, t.m0 + 64 * i, w0, h0, i0);
+#pragma unroll
+    for (int i = 0; i < BN / 64; ++i)
+      tma_load_4d(b + i * 8192, &tmX, bar, t.n0 + 64 * i, w0 * stride + s - pad, h0 * stride + r - pad, i0);
+  }
+  __device__ __forceinline__ void store_panel(const Tile&, int, const void*) const {}
+  __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < Cout; }
+  __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
+    const int k = t.m0 + row;
+    return k < Cout ? (void*)(dw + ((size_t)k * (R * S) + t.tap) * Cin) : nullptr;
+  }
+};
+
 template <class P>
 __global__ void __launch_bounds__(NUM_THREADS, 1) conv_kernel(const __grid_constant__ P prob, const Epilogue ep) {
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&prob.tmX);
     tma_prefetch_desc(&prob.tmW);
     tma_prefetch_desc(&prob.tmY);
+  }
+  run(prob, ep);
+}
+
+template <class P>
+__global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const __grid_constant__ P prob, const Epilogue ep) {
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&prob.tmX);
+    tma_prefetch_desc(&prob.tmDY);
   }
   run(prob, ep);
 }
@@ -168,8 +228,70 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   } else {
     grid = total < sms ? total : sms;
   }
-  ep.a_tx_bytes = (uint32_t)(p.BW * p.BH * p.BI * 128);
+  ep.tx_bytes = (uint32_t)(p.BW * p.BH * p.BI * 128 + Cfg<BN>::B_STAGE_BYTES);
   conv_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+template <int BN>
+int launch_wgrad(const ConvArgs& a, const void* dy, float* dw, int* error_flag, cudaStream_t stream) {
+  using P = ConvWgradProblem<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(conv_wgrad_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  P p;
+  p.N = a.N; p.Cout = a.Cout; p.Cin = a.Cin; p.R = a.R; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
+  p.Ho = (a.H + 2 * a.pad - a.R) / a.stride + 1;
+  p.Wo = (a.W + 2 * a.pad - a.S) / a.stride + 1;
+  // pixel box of at most 64 rows (one k-block)
+  if (p.Wo >= 64) { p.BW = 64; p.BH = 1; }
+  else {
+    p.BW = p.Wo;
+    p.BH = 1;
+    for (int d = 1; d <= 64 / p.BW && d <= p.Ho; ++d) if (p.Ho % d == 0) p.BH = d;
+  }
+  p.BI = 1;
+  p.w_tiles = (p.Wo + p.BW - 1) / p.BW;
+  p.h_tiles = (p.Ho + p.BH - 1) / p.BH;
+  p.i_tiles = a.N;
+  p.boxes_total = p.w_tiles * p.h_tiles * p.i_tiles;
+  p.m_tiles = (a.Cout + BM - 1) / BM;
+  p.n_tiles = (a.Cin + BN - 1) / BN;
+  const int sms = sm_count();
+  const int base_tiles = a.R * a.S * p.m_tiles * p.n_tiles;
+  int splits = (2 * sms + base_tiles - 1) / base_tiles;
+  if (splits < 1) splits = 1;
+  if (splits > p.boxes_total) splits = p.boxes_total;
+  p.boxes_per_split = (p.boxes_total + splits - 1) / splits;
+  p.splits = (p.boxes_total + p.boxes_per_split - 1) / p.boxes_per_split;
+  p.dw = dw;
+  {
+    uint64_t dims[4] = {(uint64_t)a.Cout, (uint64_t)p.Wo, (uint64_t)p.Ho, (uint64_t)a.N};
+    uint64_t strides[3] = {(uint64_t)a.Cout * 2, (uint64_t)p.Wo * a.Cout * 2, (uint64_t)p.Ho * p.Wo * a.Cout * 2};
+    uint32_t box[4] = {64, (uint32_t)p.BW, (uint32_t)p.BH, 1};
+    int r = esgd::make_tensormap_bf16(&p.tmDY, dy, 4, dims, strides, box, nullptr);
+    if (r != 0) return 1000 + r;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)a.Cin, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N};
+    uint64_t strides[3] = {(uint64_t)a.Cin * 2, (uint64_t)a.W * a.Cin * 2, (uint64_t)a.H * a.W * a.Cin * 2};
+    uint32_t box[4] = {64, (uint32_t)(p.BW * a.stride), (uint32_t)(p.BH * a.stride), 1};
+    uint32_t es[4] = {1, (uint32_t)a.stride, (uint32_t)a.stride, 1};
+    int r = esgd::make_tensormap_bf16(&p.tmX, a.x, 4, dims, strides, box, es);
+    if (r != 0) return 2000 + r;
+  }
+  Epilogue ep;
+  ep.out_mode = OUT_F32_ATOMIC; ep.relu = 0; ep.n_total = a.Cin; ep.bias = nullptr;
+  ep.col_sum = nullptr; ep.col_sqsum = nullptr; ep.error_flag = error_flag;
+  ep.tx_bytes = (uint32_t)(p.BW * p.BH * 128 * (BM / 64 + BN / 64));
+  const int total = base_tiles * p.splits;
+  const int grid = total < sms ? total : sms;
+  conv_wgrad_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
@@ -177,6 +299,19 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
 }  // namespace
 
 extern "C" {
+
+// dw: fp32 [Cout][R][S][Cin], zeroed by the caller (split-K partial sums are added atomically).
+// x: [N,H,W,Cin] bf16, dy: [N,Ho,Wo,Cout] bf16.  Cin % 8 == 0, Cout % 8 == 0.
+int esgd_conv2d_wgrad(const void* x, const void* dy, float* dw, int N, int H, int W, int Cin, int Cout, int R, int S,
+                      int stride, int pad, int* error_flag, void* stream) {
+  if (Cin % 8 || Cout % 8 || stride < 1 || stride > 2) return -1;
+  ConvArgs a{x, nullptr, nullptr, N, H, W, Cin, Cout, R, S, stride, pad};
+  cudaStream_t s = (cudaStream_t)stream;
+  const int BN = Cin <= 64 ? 64 : (Cin <= 128 ? 128 : 256);
+  if (BN == 64) return launch_wgrad<64>(a, dy, dw, error_flag, s);
+  if (BN == 128) return launch_wgrad<128>(a, dy, dw, error_flag, s);
+  return launch_wgrad<256>(a, dy, dw, error_flag, s);
+}
 
 // x: [N,H,W,Cin] bf16, w: [Cout,R,S,Cin] bf16, y: [N,Ho,Wo,Cout] bf16.  Cin % 64 == 0, Cout % 8 == 0.
 // col_sum / col_sqsum (optional, caller-zeroed fp32[Cout]) receive the statistics of the stored y.
@@ -187,7 +322,7 @@ int esgd_conv2d_fwd(const void* x, const void* w, void* y, int N, int H, int W, 
   Epilogue ep;
   ep.out_mode = OUT_BF16; ep.relu = relu; ep.n_total = Cout; ep.bias = nullptr;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
-  ep.a_tx_bytes = 0;
+  ep.tx_bytes = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
   if (BN == 64) return launch<64>(a, ep, s);

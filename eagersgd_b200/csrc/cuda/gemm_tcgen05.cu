@@ -21,7 +21,7 @@ namespace {
 template <int BN_, bool A_MN_, bool B_MN_>
 struct GemmProblem {
   static constexpr int BN = BN_;
-  static constexpr bool A_MN = A_MN_, B_MN = B_MN_;
+  static constexpr bool A_MN = A_MN_, B_MN = B_MN_, kZeroStages = false;
   CUtensorMap tmA, tmB, tmC;
   int M, N, K;
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
@@ -185,7 +185,7 @@ int esgd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   Epilogue ep;
   ep.out_mode = out_mode; ep.relu = relu; ep.n_total = N; ep.bias = bias;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
-  ep.a_tx_bytes = 0;
+  ep.tx_bytes = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
   if (BN == 64) return launch_major<64>(a_mn, b_mn, g, ep, s);

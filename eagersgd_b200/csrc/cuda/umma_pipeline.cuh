@@ -4,7 +4,7 @@
 //   warp 0     : TMA producer — the Problem policy issues the loads of one k-block
 //   warp 1     : tcgen05.mma issuer (one thread); two TMEM accumulators so the
 //                epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2..5 : epilogue — tcgen05.ld, bias / ReLU, bf16 tile staged in shared
+//   warps 2..9 : epilogue — tcgen05.ld, bias / ReLU, bf16 tile staged in shared
 //                memory in the 128-byte-swizzled layout and written with a TMA
 //                store (coalesced, clipped at the tensor edge); per-channel sum and
 //                sum of squares of the stored tile are taken from shared memory and
@@ -26,7 +26,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int PANEL_BYTES = BM * 64 * 2;     // one 128 x 64 bf16 output panel
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_THREADS = 256;         // eight epilogue warps
+constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
 constexpr int NUM_PANEL_BUFS = 4;            // output staging ring: up to 3 TMA stores drain while the next panel is built
 
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
@@ -39,7 +40,7 @@ struct Epilogue {
   float* col_sum;          // optional per-column statistics of the stored bf16 values
   float* col_sqsum;
   int* error_flag;
-  uint32_t a_tx_bytes;     // bytes one k-block's A loads deliver (0: a full 128 x 64 tile)
+  uint32_t tx_bytes;       // bytes the loads of one k-block deliver (0: full A and B stage tiles)
 };
 
 template <int BN>
@@ -51,7 +52,7 @@ struct Cfg {
 };
 
 // Problem policy requirements (all __device__ const):
-//   static constexpr int BN; static constexpr bool A_MN, B_MN;
+//   static constexpr int BN; static constexpr bool A_MN, B_MN, kZeroStages;
 //   struct Tile { int kb0, kb1, n0; ... };
 //   bool tile(int it, Tile&)                       enumerate this CTA's tiles
 //   void load(const Tile&, int kb, uint8_t* a, uint8_t* b, uint64_t* bar)
@@ -79,13 +80,20 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], NUM_EPI_THREADS / 32); }
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
+  }
+  if (P::kZeroStages) {
+    // partial boxes leave the tail rows of a stage untouched: they must read as zeros for ever
+    uint4* p4 = reinterpret_cast<uint4*>(sA);
+    const int n16 = STAGES * (A_STAGE_BYTES + C::B_STAGE_BYTES) / 16;
+    for (int i = threadIdx.x; i < n16; i += NUM_THREADS) p4[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
   }
   tc_fence_before();
   __syncthreads();
@@ -102,7 +110,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       for (int it = 0; ok && prob.tile(it, t); ++it) {
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[stage], (ep.a_tx_bytes ? ep.a_tx_bytes : (uint32_t)A_STAGE_BYTES) + C::B_STAGE_BYTES);
+          mbar_expect_tx(&full[stage], ep.tx_bytes ? ep.tx_bytes : (uint32_t)(A_STAGE_BYTES + C::B_STAGE_BYTES));
           prob.load(t, kb, sA + stage * A_STAGE_BYTES, sB + stage * C::B_STAGE_BYTES, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -143,15 +151,18 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
-    const int q = warp & 3;                 // TMEM lane quarter this warp may access
-    const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+    // ------------------------------------------------------------ epilogue (8 warps)
+    // A warp may only touch TMEM lanes [32*(warp%4), +32): two warps share each lane quarter and
+    // split every 64-column panel into halves.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;       // which 32 columns of a 64-column panel
+    const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
     const int row = q * 32 + lane;          // tile row owned by this thread
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;                            // staging panel buffer in use (ring)
     int stores_issued = 0;                  // bulk-store groups committed so far (thread et == 0)
-    // statistics: thread (cp = et % 32, rq = et / 32) covers columns 2cp, 2cp+1 of each panel, rows 32rq..+32
+    // statistics: thread (cp = et % 32, rg = et / 32) covers columns 2cp, 2cp+1 of each panel, rows 16rg..+16
     float st_sum[BN / 64][2], st_sq[BN / 64][2];
 #pragma unroll
     for (int pnl = 0; pnl < BN / 64; ++pnl) { st_sum[pnl][0] = st_sum[pnl][1] = st_sq[pnl][0] = st_sq[pnl][1] = 0.f; }
@@ -162,74 +173,79 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       stats_n0 = t.n0;
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * 32);
       if (ep.out_mode == OUT_BF16) {
-#pragma unroll 1
-        for (int pnl = 0; pnl < BN / 64; ++pnl) {
-          if (t.n0 + pnl * 64 >= ep.n_total) break;  // uniform across the CTA
-          uint8_t* panel = sC + buf * PANEL_BYTES;
-          // the store that used this buffer NUM_PANEL_BUFS panels ago must have read it
-          if (et == 0 && stores_issued >= NUM_PANEL_BUFS) tma_store_wait_read<NUM_PANEL_BUFS - 1>();
-          uint32_t r2[2][32];
-          tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64), r2[0]);       // both halves in flight, one wait
-          tmem_ld_32x32b_x32(t_row + (uint32_t)(pnl * 64 + 32), r2[1]);
-          tmem_ld_wait();
-          named_barrier_sync(1, 128);                // the buffer is free for everyone
+        const int npan = min(BN / 64, (ep.n_total - t.n0 + 63) / 64);   // uniform across the CTA
+        uint32_t rbuf[2][32];
+        tmem_ld_32x32b_x32(t_row, rbuf[0]);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const uint32_t* r = r2[half];
+        for (int pnl = 0; pnl < BN / 64; ++pnl) {
+          if (pnl < npan) {
+            tmem_ld_wait();
+            if (pnl + 1 < npan)   // the next panel's accumulators travel while this one is converted
+              tmem_ld_32x32b_x32(t_row + (uint32_t)((pnl + 1) * 64), rbuf[(pnl + 1) & 1]);
+            uint8_t* panel = sC + buf * PANEL_BYTES;
+            // the store that used this buffer NUM_PANEL_BUFS panels ago must have read it
+            if (et == 0 && stores_issued >= NUM_PANEL_BUFS) tma_store_wait_read<NUM_PANEL_BUFS - 1>();
+            named_barrier_sync(1, NUM_EPI_THREADS);    // the buffer is free for everyone
+            const uint32_t* r = rbuf[pnl & 1];
             const int col0 = t.n0 + pnl * 64 + half * 32;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float v[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                v[j] = __uint_as_float(r[g * 8 + j]);
-                if (ep.bias != nullptr && col0 + g * 8 + j < ep.n_total) v[j] += __ldg(ep.bias + col0 + g * 8 + j);
-                if (ep.relu) v[j] = fmaxf(v[j], 0.0f);
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+              if (ep.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (col0 + g * 8 + j < ep.n_total) v[j] += __ldg(ep.bias + col0 + g * 8 + j);
+              }
+              if (ep.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
               }
               uint4 pk;
               __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
               for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-              const int chunk = half * 4 + g;        // 16-byte chunk within the 128-byte row
+              const int chunk = half * 4 + g;          // 16-byte chunk within the 128-byte row
               *reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
             }
-          }
-          fence_proxy_async();
-          named_barrier_sync(1, 128);                // the panel is complete and visible to the TMA engine
-          if (et == 0) {
-            prob.store_panel(t, pnl, panel);
-            tma_store_commit();
-            stores_issued++;
-          }
-          if (ep.col_sum != nullptr) {
-            const int cp = et & 31, rq = et >> 5;
-            float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
-#pragma unroll 4
-            for (int rr = 0; rr < 32; ++rr) {
-              const int r_ = rq * 32 + rr;
-              if (!prob.row_valid(t, r_)) continue;
-              const int chunk = cp >> 2;
-              const uint32_t w = *reinterpret_cast<const uint32_t*>(panel + r_ * 128 + ((chunk ^ (r_ & 7)) << 4) +
-                                                                    (cp & 3) * 4);
-              __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&w);
-              float2 f = __bfloat1622float2(hv);
-              s0 += f.x; s1 += f.y; q0 += f.x * f.x; q1 += f.y * f.y;
+            fence_proxy_async();
+            named_barrier_sync(1, NUM_EPI_THREADS);    // the panel is complete and visible to the TMA engine
+            if (et == 0) {
+              prob.store_panel(t, pnl, panel);
+              tma_store_commit();
+              stores_issued++;
             }
-            st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
+            if (ep.col_sum != nullptr) {
+              const int cp = et & 31, rg = et >> 5;
+              float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll 4
+              for (int rr = 0; rr < 16; ++rr) {
+                const int r_ = rg * 16 + rr;
+                if (!prob.row_valid(t, r_)) continue;
+                const int chunk = cp >> 2;
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(panel + r_ * 128 + ((chunk ^ (r_ & 7)) << 4) +
+                                                                      (cp & 3) * 4);
+                __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&w);
+                float2 f = __bfloat1622float2(hv);
+                s0 += f.x; s1 += f.y; q0 += f.x * f.x; q1 += f.y * f.y;
+              }
+              st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
+            }
+            buf = (buf + 1) % NUM_PANEL_BUFS;
           }
-          buf = (buf + 1) % NUM_PANEL_BUFS;
         }
       } else {
         // fp32 outputs (logits, split-K weight gradients): direct stores / atomics from registers
         float* out_row = reinterpret_cast<float*>(prob.row_ptr(t, row));
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < BN / 64; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 32), r);
+          tmem_ld_32x32b_x32(t_row + (uint32_t)(c * 64), r);
           tmem_ld_wait();
-          const int col0 = t.n0 + c * 32;
+          const int col0 = t.n0 + c * 64 + half * 32;
           if (out_row != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {

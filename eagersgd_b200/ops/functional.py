@@ -37,6 +37,7 @@ def _lib():
         lib.esgd_avgpool_fwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_conv2d_fwd.argtypes = [vp, vp, vp] + [i32] * 10 + [vp, vp, vp, vp]
+        lib.esgd_conv2d_wgrad.argtypes = [vp, vp, vp] + [i32] * 9 + [vp, vp]
         lib._nn_bound = True
     return lib
 
@@ -176,7 +177,12 @@ class _ConvKxK(torch.autograd.Function):
             else:
                 dx = torch.nn.grad.conv2d_input(x.shape, w, dy_cl, stride=stride, padding=pad)
         if ctx.needs_input_grad[1]:
-            dw = torch.nn.grad.conv2d_weight(x, w.shape, dy_cl, stride=stride, padding=pad)
+            from .gemm import error_flag
+            dw32 = torch.zeros(cout, r, s, cin, dtype=torch.float32, device=x.device)   # [Cout][R][S][Cin]
+            _ck(_lib().esgd_conv2d_wgrad(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(), dw32.data_ptr(), n, h, wd,
+                                         cin, cout, r, s, stride, pad, error_flag(x.device).data_ptr(), _stream(x)),
+                "conv2d weight gradient")
+            dw = dw32.to(w.dtype).permute(0, 3, 1, 2)
         return dx, dw, None, None, None
 
 
