@@ -162,6 +162,8 @@ struct ConvArgs {
   const void *x, *w;
   void* y;
   int N, H, W, Cin, Cout, R, S, stride, pad;
+  int out_h = 0, out_w = 0;                 // output extent override (0: from the usual formula)
+  int64_t ys_w = 0, ys_h = 0, ys_n = 0;     // output strides in elements (0: dense NHWC)
 };
 
 template <int BN>
@@ -176,8 +178,8 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   }
   P p;
   p.N = a.N; p.Cout = a.Cout; p.R = a.R; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
-  p.Ho = (a.H + 2 * a.pad - a.R) / a.stride + 1;
-  p.Wo = (a.W + 2 * a.pad - a.S) / a.stride + 1;
+  p.Ho = a.out_h ? a.out_h : (a.H + 2 * a.pad - a.R) / a.stride + 1;
+  p.Wo = a.out_w ? a.out_w : (a.W + 2 * a.pad - a.S) / a.stride + 1;
   p.cblks = a.Cin / 64;
   // output-pixel box: whole rows when they fit, as many rows / images as 128 GEMM rows allow
   if (p.Wo >= 128) { p.BW = 128; p.BH = 1; p.BI = 1; }
@@ -213,6 +215,7 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   {
     uint64_t dims[4] = {(uint64_t)a.Cout, (uint64_t)p.Wo, (uint64_t)p.Ho, (uint64_t)a.N};
     uint64_t strides[3] = {(uint64_t)a.Cout * 2, (uint64_t)p.Wo * a.Cout * 2, (uint64_t)p.Ho * p.Wo * a.Cout * 2};
+    if (a.ys_w) { strides[0] = (uint64_t)a.ys_w * 2; strides[1] = (uint64_t)a.ys_h * 2; strides[2] = (uint64_t)a.ys_n * 2; }
     uint32_t box[4] = {64, (uint32_t)p.BW, (uint32_t)p.BH, (uint32_t)p.BI};
     int r = esgd::make_tensormap_bf16(&p.tmY, a.y, 4, dims, strides, box, nullptr);
     if (r != 0) return 3000 + r;
@@ -315,10 +318,25 @@ int esgd_conv2d_wgrad(const void* x, const void* dy, float* dw, int N, int H, in
 
 // x: [N,H,W,Cin] bf16, w: [Cout,R,S,Cin] bf16, y: [N,Ho,Wo,Cout] bf16.  Cin % 64 == 0, Cout % 8 == 0.
 // col_sum / col_sqsum (optional, caller-zeroed fp32[Cout]) receive the statistics of the stored y.
+// out_h / out_w override the output extent (taps that fall outside the input read zeros); ys_w / ys_h / ys_n
+// (elements, 0 = dense) let y be a strided view, e.g. every second pixel of a larger tensor.
+int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int R, int S,
+                       int stride, int pad, int out_h, int out_w, int64_t ys_w, int64_t ys_h, int64_t ys_n, int relu,
+                       float* col_sum, float* col_sqsum, int* error_flag, void* stream);
+
 int esgd_conv2d_fwd(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int R, int S,
                     int stride, int pad, int relu, float* col_sum, float* col_sqsum, int* error_flag, void* stream) {
+  return esgd_conv2d_fwd_ex(x, w, y, N, H, W, Cin, Cout, R, S, stride, pad, 0, 0, 0, 0, 0, relu, col_sum, col_sqsum,
+                            error_flag, stream);
+}
+
+int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int R, int S,
+                       int stride, int pad, int out_h, int out_w, int64_t ys_w, int64_t ys_h, int64_t ys_n, int relu,
+                       float* col_sum, float* col_sqsum, int* error_flag, void* stream) {
   if (Cin % 64 || Cout % 8 || stride < 1 || stride > 2) return -1;
+  if (ys_w && ((ys_w % 8) || (ys_h % 8) || (ys_n % 8))) return -6;
   ConvArgs a{x, w, y, N, H, W, Cin, Cout, R, S, stride, pad};
+  a.out_h = out_h; a.out_w = out_w; a.ys_w = ys_w; a.ys_h = ys_h; a.ys_n = ys_n;
   Epilogue ep;
   ep.out_mode = OUT_BF16; ep.relu = relu; ep.n_total = Cout; ep.bias = nullptr;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;

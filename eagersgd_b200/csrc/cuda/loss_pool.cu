@@ -236,6 +236,38 @@ __global__ void __launch_bounds__(256) avgpool_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
+// im2col for convolutions with very few input channels (the 7x7 / 2 stem on RGB images):
+// col[pixel, k] with k = (r*S + s)*C + c, zero outside the image and for k >= R*S*C (K is padded
+// to a multiple of 64 so that the product runs as a tensor-core GEMM).  One thread per 8 columns.
+__global__ void __launch_bounds__(256) im2col_small_c_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             __nv_bfloat16* __restrict__ col, int N, int H, int W,
+                                                             int C, int R, int S, int stride, int pad, int Ho, int Wo,
+                                                             int Kpad) {
+  const int chunks = Kpad / 8;
+  const int64_t total = (int64_t)N * Ho * Wo * chunks;
+  const int K = R * S * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int ch = (int)(i % chunks);
+    int64_t t = i / chunks;
+    const int q = (int)(t % Wo); t /= Wo;
+    const int p = (int)(t % Ho);
+    const int n = (int)(t / Ho);
+    __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = ch * 8 + j;
+      __nv_bfloat16 val = __float2bfloat16(0.0f);
+      if (k < K) {
+        const int c = k % C, rs = k / C, s = rs % S, r = rs / S;
+        const int h = p * stride + r - pad, w = q * stride + s - pad;
+        if (h >= 0 && h < H && w >= 0 && w < W) val = x[(((int64_t)n * H + h) * W + w) * C + c];
+      }
+      v[j] = val;
+    }
+    *reinterpret_cast<uint4*>(col + i * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
 int grid_for(int64_t items) {
   int64_t b = (items + 255) / 256;
   const int64_t cap = 148 * 16;
@@ -294,6 +326,17 @@ int esgd_subsample2_bwd(const void* dy, void* dx, int N, int H, int W, int C, vo
   const int OH = (H + 1) / 2, OW = (W + 1) / 2;
   subsample2_bwd_kernel<<<grid_for((int64_t)N * H * W * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, OH, OW);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
+// col: [N*Ho*Wo, Kpad] bf16, Kpad a multiple of 8 and >= R*S*C.
+int esgd_im2col_small_c(const void* x, void* col, int N, int H, int W, int C, int R, int S, int stride, int pad,
+                        int Kpad, void* stream) {
+  if (Kpad % 8 || Kpad < R * S * C) return -1;
+  const int Ho = (H + 2 * pad - R) / stride + 1, Wo = (W + 2 * pad - S) / stride + 1;
+  im2col_small_c_kernel<<<grid_for((int64_t)N * Ho * Wo * (Kpad / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, R, S, stride, pad, Ho, Wo, Kpad);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

@@ -37,6 +37,8 @@ def _lib():
         lib.esgd_avgpool_fwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_conv2d_fwd.argtypes = [vp, vp, vp] + [i32] * 10 + [vp, vp, vp, vp]
+        lib.esgd_conv2d_fwd_ex.argtypes = [vp, vp, vp] + [i32] * 11 + [i64, i64, i64, i32, vp, vp, vp, vp]
+        lib.esgd_im2col_small_c.argtypes = [vp, vp] + [i32] * 9 + [vp]
         lib.esgd_conv2d_wgrad.argtypes = [vp, vp, vp] + [i32] * 9 + [vp, vp]
         lib._nn_bound = True
     return lib
@@ -140,6 +142,64 @@ def _conv_native(x2d_src, w_ohwi, n, h, w, cin, cout, r, s, stride, pad, stats):
     return y2d, ho, wo
 
 
+def _dgrad_stride2(dy, w, n, h, wd, cin, cout):
+    """Data gradient of a 3x3 / stride-2 / pad-1 convolution without zero insertion: the four output
+    parities (h%2, w%2) are four small convolutions of dy with 1, 2, 2 and 4 of the nine taps
+    (dx[2i+a] uses rows r with (a+1-r) even), each written into its strided quarter of dx by TMA."""
+    from .gemm import error_flag
+    lib = _lib()
+    dy2d = nhwc_2d(dy)
+    ho, wo = h // 2, wd // 2
+    dx2d = torch.empty(n * h * wd, cin, dtype=torch.bfloat16, device=dy.device)
+    wt = w.permute(1, 0, 2, 3)                                   # [Cin, Cout, R, S]
+    taps = {0: [1], 1: [2, 0]}                                   # parity -> filter indices at offsets 0, +1
+    esz = dx2d.element_size()
+    for a in (0, 1):
+        for b in (0, 1):
+            ws = wt[:, :, taps[a], :][:, :, :, taps[b]].contiguous(memory_format=torch.channels_last)
+            y_ptr = dx2d.data_ptr() + (a * wd + b) * cin * esz
+            _ck(lib.esgd_conv2d_fwd_ex(dy2d.data_ptr(), ws.data_ptr(), y_ptr, n, ho, wo, cout, cin, len(taps[a]),
+                                       len(taps[b]), 1, 0, ho, wo, 2 * cin, 2 * wd * cin, h * wd * cin, 0, None, None,
+                                       error_flag(dy.device).data_ptr(), _stream(dy)), "strided conv data gradient")
+    return from_2d(dx2d, n, h, wd)
+
+
+class _StemConv(torch.autograd.Function):
+    """Convolution with very few input channels (RGB stem): im2col + tensor-core GEMM; the weight
+    gradient is one split-K GEMM over the saved columns.  No input gradient (images are leaves)."""
+
+    @staticmethod
+    def forward(ctx, x, w, stride, pad, want_stats):
+        n, c, h, wd = x.shape
+        cout, _, r, s = w.shape
+        k = r * s * c
+        kpad = (k + 63) // 64 * 64
+        ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - s) // stride + 1
+        col = torch.empty(n * ho * wo, kpad, dtype=torch.bfloat16, device=x.device)
+        _ck(_lib().esgd_im2col_small_c(nhwc_2d(x).data_ptr(), col.data_ptr(), n, h, wd, c, r, s, stride, pad, kpad,
+                                       _stream(x)), "im2col")
+        w2d = torch.zeros(cout, kpad, dtype=torch.bfloat16, device=x.device)
+        w2d[:, :k] = w.permute(0, 2, 3, 1).reshape(cout, k)              # k = (r, s, c)
+        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        y2d = gemm(col, w2d, col_sum=stats[0] if want_stats else None, col_sqsum=stats[1] if want_stats else None)
+        ctx.save_for_backward(col)
+        ctx.cfg = (cout, c, r, s, k)
+        y = from_2d(y2d, n, ho, wo)
+        if want_stats:
+            ctx.mark_non_differentiable(stats)
+            return y, stats
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, *unused):
+        (col,) = ctx.saved_tensors
+        cout, c, r, s, k = ctx.cfg
+        dy2d = nhwc_2d(dy)
+        dw = gemm(dy2d, col, a_kmajor=False, b_kmajor=False, splits=148)        # [Cout, Kpad] fp32
+        dw = dw[:, :k].reshape(cout, r, s, c).permute(0, 3, 1, 2).to(torch.bfloat16)
+        return None, dw, None, None, None
+
+
 class _ConvKxK(torch.autograd.Function):
     """RxS convolution as an implicit GEMM on the tensor cores (TMA-fed, zero-filled padding)."""
 
@@ -174,6 +234,8 @@ class _ConvKxK(torch.autograd.Function):
                 dx2d, _, _ = _conv_native(nhwc_2d(dy_cl), w_t, n, dy.shape[2], dy.shape[3], cout, cin, r, s, 1,
                                           r - 1 - pad, None)
                 dx = from_2d(dx2d, n, h, wd)
+            elif stride == 2 and r == 3 and s == 3 and pad == 1 and h % 2 == 0 and wd % 2 == 0 and cout % 64 == 0:
+                dx = _dgrad_stride2(dy_cl, w, n, h, wd, cin, cout)
             else:
                 dx = torch.nn.grad.conv2d_input(x.shape, w, dy_cl, stride=stride, padding=pad)
         if ctx.needs_input_grad[1]:
@@ -220,6 +282,9 @@ def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, 
         elif stride > 1:
             x = x[:, :, ::stride, ::stride].contiguous(memory_format=torch.channels_last)
         out = conv1x1(x, w, want_stats)
+        return out if want_stats else (out, None)
+    if k > 1 and native(x) and x.shape[1] <= 4 and w.shape[0] % 8 == 0 and not x.requires_grad:
+        out = _StemConv.apply(x, w, stride, padding, want_stats)
         return out if want_stats else (out, None)
     if k > 1 and native(x) and x.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and stride in (1, 2):
         out = _ConvKxK.apply(x, w, stride, padding, want_stats)

@@ -58,3 +58,37 @@ def test_conv_backward(n, cin, h, w, cout, k, stride, pad):
     F.conv2d(xr, wr, None, stride, pad).backward(g.float())
     assert torch.allclose(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2 * xr.grad.abs().max().item())
     assert torch.allclose(wt.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout", [(2, 128, 28, 28, 128), (3, 64, 16, 24, 256)])
+def test_conv_stride2_data_gradient_by_parity(n, cin, h, w, cout):
+    from eagersgd_b200.ops import functional as ops
+    from eagersgd_b200.ops.gemm import check_error
+    torch.manual_seed(3)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16).requires_grad_()
+    wt = _cl(torch.randn(cout, cin, 3, 3, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    y, _ = ops.conv2d(x, wt, 2, 1)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    y.backward(g)
+    torch.cuda.synchronize()
+    check_error(x.device)
+    xr, wr = x.detach().float().requires_grad_(), wt.detach().float().requires_grad_()
+    F.conv2d(xr, wr, None, 2, 1).backward(g.float())
+    assert torch.allclose(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2 * xr.grad.abs().max().item())
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
+
+
+def test_stem_convolution_im2col_gemm():
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(4)
+    x = _cl(torch.randn(4, 3, 64, 64, device=DEV)).to(torch.bfloat16)
+    wt = _cl(torch.randn(64, 3, 7, 7, device=DEV) * 0.1).to(torch.bfloat16).requires_grad_()
+    y, stats = ops.conv2d(x, wt, 2, 3, want_stats=True)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    y.backward(g)
+    wr = wt.detach().float().requires_grad_()
+    yr = F.conv2d(x.float(), wr, None, 2, 3)
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, rtol=3e-2, atol=5e-2)
+    assert torch.allclose(stats[0], y.float().sum((0, 2, 3)), rtol=1e-3, atol=0.5)
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
