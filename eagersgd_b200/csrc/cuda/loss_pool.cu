@@ -236,35 +236,40 @@ __global__ void __launch_bounds__(256) avgpool_bwd_kernel(const __nv_bfloat16* _
   }
 }
 
-// im2col for convolutions with very few input channels (the 7x7 / 2 stem on RGB images):
-// col[pixel, k] with k = (r*S + s)*C + c, zero outside the image and for k >= R*S*C (K is padded
-// to a multiple of 64 so that the product runs as a tensor-core GEMM).  One thread per 8 columns.
+// im2col for convolutions with very few input channels (the 7x7 / 2 stem on RGB images).
+// Column layout per output pixel: R segments of SEG = roundup8(S*C) elements; segment r holds the
+// S*C input values of filter row r — in NHWC they are contiguous in memory — followed by zeros, and the
+// row is zero-padded to Kpad (a multiple of 64, so the product runs as a tensor-core GEMM).
+// One thread per (pixel, segment): no divisions per element, 16-byte stores.
+template <int MAXSEG>
 __global__ void __launch_bounds__(256) im2col_small_c_kernel(const __nv_bfloat16* __restrict__ x,
                                                              __nv_bfloat16* __restrict__ col, int N, int H, int W,
                                                              int C, int R, int S, int stride, int pad, int Ho, int Wo,
-                                                             int Kpad) {
-  const int chunks = Kpad / 8;
-  const int64_t total = (int64_t)N * Ho * Wo * chunks;
-  const int K = R * S * C;
+                                                             int seg, int Kpad) {
+  const int segs = Kpad / seg;              // R real segments + zero segments
+  const int64_t total = (int64_t)N * Ho * Wo * segs;
+  const int sc = S * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int ch = (int)(i % chunks);
-    int64_t t = i / chunks;
+    const int r = (int)(i % segs);
+    int64_t t = i / segs;
     const int q = (int)(t % Wo); t /= Wo;
     const int p = (int)(t % Ho);
     const int n = (int)(t / Ho);
-    __nv_bfloat16 v[8];
+    __align__(16) __nv_bfloat16 v[MAXSEG];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int k = ch * 8 + j;
-      __nv_bfloat16 val = __float2bfloat16(0.0f);
-      if (k < K) {
-        const int c = k % C, rs = k / C, s = rs % S, r = rs / S;
-        const int h = p * stride + r - pad, w = q * stride + s - pad;
-        if (h >= 0 && h < H && w >= 0 && w < W) val = x[(((int64_t)n * H + h) * W + w) * C + c];
-      }
-      v[j] = val;
+    for (int j = 0; j < MAXSEG; ++j) v[j] = __float2bfloat16(0.0f);
+    const int h = p * stride + r - pad;
+    if (r < R && h >= 0 && h < H) {
+      const int w0 = q * stride - pad;
+      const __nv_bfloat16* src = x + (((int64_t)n * H + h) * W + w0) * C;
+      const int lo = w0 < 0 ? -w0 * C : 0;                       // first valid element of the segment
+      const int hi = (w0 + S > W) ? (W - w0) * C : sc;           // one past the last valid element
+#pragma unroll
+      for (int j = 0; j < MAXSEG; ++j)
+        if (j >= lo && j < hi) v[j] = src[j];
     }
-    *reinterpret_cast<uint4*>(col + i * 8) = *reinterpret_cast<const uint4*>(v);
+    __nv_bfloat16* dst = col + (t * 0 + (((int64_t)n * Ho + p) * Wo + q)) * Kpad + (int64_t)r * seg;
+    for (int j = 0; j < seg; j += 8) *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(v + j);
   }
 }
 
@@ -330,13 +335,14 @@ int esgd_subsample2_bwd(const void* dy, void* dx, int N, int H, int W, int C, vo
   return (int)cudaGetLastError();
 }
 
-// col: [N*Ho*Wo, Kpad] bf16, Kpad a multiple of 8 and >= R*S*C.
+// col: [N*Ho*Wo, Kpad] bf16; seg = roundup8(S*C) <= 32; Kpad a multiple of seg with Kpad >= R*seg.
+// Element (r, j) of a row is x[.., h+r, (w0*C + j)] for j < S*C: weights must be laid out the same way.
 int esgd_im2col_small_c(const void* x, void* col, int N, int H, int W, int C, int R, int S, int stride, int pad,
-                        int Kpad, void* stream) {
-  if (Kpad % 8 || Kpad < R * S * C) return -1;
+                        int seg, int Kpad, void* stream) {
+  if (seg % 8 || seg < S * C || seg > 32 || Kpad % seg || Kpad < R * seg) return -1;
   const int Ho = (H + 2 * pad - R) / stride + 1, Wo = (W + 2 * pad - S) / stride + 1;
-  im2col_small_c_kernel<<<grid_for((int64_t)N * Ho * Wo * (Kpad / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, R, S, stride, pad, Ho, Wo, Kpad);
+  im2col_small_c_kernel<32><<<grid_for((int64_t)N * Ho * Wo * (Kpad / seg)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, R, S, stride, pad, Ho, Wo, seg, Kpad);
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

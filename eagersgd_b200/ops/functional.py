@@ -38,7 +38,7 @@ def _lib():
         lib.esgd_avgpool_bwd.argtypes = [vp, vp, i32, i32, i32, vp]
         lib.esgd_conv2d_fwd.argtypes = [vp, vp, vp] + [i32] * 10 + [vp, vp, vp, vp]
         lib.esgd_conv2d_fwd_ex.argtypes = [vp, vp, vp] + [i32] * 11 + [i64, i64, i64, i32, vp, vp, vp, vp]
-        lib.esgd_im2col_small_c.argtypes = [vp, vp] + [i32] * 9 + [vp]
+        lib.esgd_im2col_small_c.argtypes = [vp, vp] + [i32] * 10 + [vp]
         lib.esgd_conv2d_wgrad.argtypes = [vp, vp, vp] + [i32] * 9 + [vp, vp]
         lib._nn_bound = True
     return lib
@@ -152,11 +152,13 @@ def _dgrad_stride2(dy, w, n, h, wd, cin, cout):
     ho, wo = h // 2, wd // 2
     dx2d = torch.empty(n * h * wd, cin, dtype=torch.bfloat16, device=dy.device)
     wt = w.permute(1, 0, 2, 3)                                   # [Cin, Cout, R, S]
+    wf = wt.flip(2, 3)                                           # filter indices 2, 1, 0
     taps = {0: [1], 1: [2, 0]}                                   # parity -> filter indices at offsets 0, +1
+    sel = {0: slice(1, 2), 1: slice(0, 3, 2)}                    # the same selection on the flipped filter
     esz = dx2d.element_size()
     for a in (0, 1):
         for b in (0, 1):
-            ws = wt[:, :, taps[a], :][:, :, :, taps[b]].contiguous(memory_format=torch.channels_last)
+            ws = wf[:, :, sel[a], sel[b]].contiguous(memory_format=torch.channels_last)
             y_ptr = dx2d.data_ptr() + (a * wd + b) * cin * esz
             _ck(lib.esgd_conv2d_fwd_ex(dy2d.data_ptr(), ws.data_ptr(), y_ptr, n, ho, wo, cout, cin, len(taps[a]),
                                        len(taps[b]), 1, 0, ho, wo, 2 * cin, 2 * wd * cin, h * wd * cin, 0, None, None,
@@ -172,18 +174,21 @@ class _StemConv(torch.autograd.Function):
     def forward(ctx, x, w, stride, pad, want_stats):
         n, c, h, wd = x.shape
         cout, _, r, s = w.shape
-        k = r * s * c
-        kpad = (k + 63) // 64 * 64
+        seg = (s * c + 7) // 8 * 8                                       # one filter row, padded to 16 bytes
+        kpad = (r * seg + 63) // 64 * 64
+        while kpad % seg:
+            kpad += 64
         ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - s) // stride + 1
         col = torch.empty(n * ho * wo, kpad, dtype=torch.bfloat16, device=x.device)
-        _ck(_lib().esgd_im2col_small_c(nhwc_2d(x).data_ptr(), col.data_ptr(), n, h, wd, c, r, s, stride, pad, kpad,
-                                       _stream(x)), "im2col")
-        w2d = torch.zeros(cout, kpad, dtype=torch.bfloat16, device=x.device)
-        w2d[:, :k] = w.permute(0, 2, 3, 1).reshape(cout, k)              # k = (r, s, c)
+        _ck(_lib().esgd_im2col_small_c(nhwc_2d(x).data_ptr(), col.data_ptr(), n, h, wd, c, r, s, stride, pad, seg,
+                                       kpad, _stream(x)), "im2col")
+        w2d = torch.zeros(cout, kpad // seg, seg, dtype=torch.bfloat16, device=x.device)
+        w2d[:, :r, :s * c] = w.permute(0, 2, 3, 1).reshape(cout, r, s * c)   # [cout][r][(s, c)]
+        w2d = w2d.view(cout, kpad)
         stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
         y2d = gemm(col, w2d, col_sum=stats[0] if want_stats else None, col_sqsum=stats[1] if want_stats else None)
         ctx.save_for_backward(col)
-        ctx.cfg = (cout, c, r, s, k)
+        ctx.cfg = (cout, c, r, s, seg)
         y = from_2d(y2d, n, ho, wo)
         if want_stats:
             ctx.mark_non_differentiable(stats)
@@ -193,10 +198,10 @@ class _StemConv(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, *unused):
         (col,) = ctx.saved_tensors
-        cout, c, r, s, k = ctx.cfg
+        cout, c, r, s, seg = ctx.cfg
         dy2d = nhwc_2d(dy)
         dw = gemm(dy2d, col, a_kmajor=False, b_kmajor=False, splits=148)        # [Cout, Kpad] fp32
-        dw = dw[:, :k].reshape(cout, r, s, c).permute(0, 3, 1, 2).to(torch.bfloat16)
+        dw = dw.view(cout, -1, seg)[:, :r, :s * c].reshape(cout, r, s, c).permute(0, 3, 1, 2).to(torch.bfloat16)
         return None, dw, None, None, None
 
 
