@@ -33,14 +33,17 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp"])
-    ap.add_argument("--mode", default="solo", choices=["solo", "majority", "sync"])
-    ap.add_argument("--model", default="resnet50", choices=["resnet50", "resnet32"])
+    ap.add_argument("--mode", default=None, choices=["solo", "majority", "sync"],
+                    help="default: solo for resnet50, majority for resnet32 and lstm")
+    ap.add_argument("--model", default="resnet50", choices=["resnet50", "resnet32", "lstm"])
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: 256 / 128)")
     ap.add_argument("--limiter", type=int, default=32)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--imbalance", default="auto", choices=["auto", "none"],
-                    help="auto: each step 2 random ranks are delayed by Exp(0.5 x step time) when N > 1")
+                    help="auto (N > 1): resnet50: 2 random ranks/step delayed by Exp(0.5 x step time); resnet32: one "
+                         "random rank delayed by 1.5 x step time; lstm: none injected (sequence lengths differ per rank)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--max-frames", type=int, default=1800, help="lstm: longest sequence kept by the sampler")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of one CUDA graph")
     return ap.parse_args()
 
@@ -139,25 +142,49 @@ def main():
     assert world == args.gpus, "launch with torchrun --nproc-per-node %d (WORLD_SIZE=%d)" % (args.gpus, world)
     torch.backends.cudnn.benchmark = True
     torch.manual_seed(1234)  # identical replicas through a shared seed
-    if args.model == "resnet50":
-        batch, res, classes = args.batch or 256, 224, 1000
-        model = imagenet_resnet(50, 1, classes)
-        name = "ResNet-50 v1.5"
-    else:
-        batch, res, classes = args.batch or 128, 32, 10
-        model = cifar_resnet(32, 1, classes)
-        name = "ResNet-32 (CIFAR)"
-    step = TrainStep(model, group, impl=args.impl, mode=args.mode, limiter=args.limiter, bucket_mb=args.bucket_mb,
-                     lr=0.01, momentum=0.9, weight_decay=1e-4)
-
-    # synthetic data of the named shape, in pinned host memory (3 distinct batches)
+    from eagersgd_b200.models.lstm import LSTMClassifier
+    if args.mode is None:
+        args.mode = "solo" if args.model == "resnet50" else "majority"
+    unit, loss_fn = "images/s", None
     g = torch.Generator().manual_seed(100 + rank)
     host_batches = []
-    for _ in range(3):
-        x = torch.randn(batch, 3, res, res, generator=g).to(torch.bfloat16)
-        x = x.contiguous(memory_format=torch.channels_last).pin_memory()
-        y = torch.randint(0, classes, (batch,), generator=g).pin_memory()
-        host_batches.append((x, y))
+    if args.model in ("resnet50", "resnet32"):
+        if args.model == "resnet50":
+            batch, res, classes = args.batch or 256, 224, 1000
+            model, name = imagenet_resnet(50, 1, classes), "ResNet-50 v1.5"
+        else:
+            batch, res, classes = args.batch or 128, 32, 10
+            model, name = cifar_resnet(32, 1, classes), "ResNet-32 (CIFAR)"
+        # synthetic data of the named shape, in pinned host memory (3 distinct batches)
+        for _ in range(3):
+            x = torch.randn(batch, 3, res, res, generator=g).to(torch.bfloat16)
+            x = x.contiguous(memory_format=torch.channels_last).pin_memory()
+            y = torch.randint(0, classes, (batch,), generator=g).pin_memory()
+            host_batches.append((x, y))
+        shape_cfg = {"image": [res, res, 3], "classes": classes, "seq_len": None}
+    else:
+        # 2-layer LSTM (hidden 2048) on 2048-d frame features; per-sample length from a clipped log-normal over
+        # 30..1800 frames, length-bucketed batches, left-padded: the per-rank sequence length IS the imbalance
+        import numpy as np
+        from eagersgd_b200.data import BucketSampler, SyntheticSequenceDataset
+        batch, classes, unit = args.batch or 16, 101, "sequences/s"
+        model, name = LSTMClassifier(2048, 2048, 2, classes), "2-layer LSTM classifier (hidden 2048)"
+        ds = SyntheticSequenceDataset(2048, 8, classes, seed=7 + rank)      # lengths / labels only; features below
+        sampler = BucketSampler(ds, batch, ds.lengths, num_buckets=30, max_length=args.max_frames, seed=rank)
+        lengths = []
+        for _ in range(args.steps + max(args.warmup, 3)):
+            b = sampler()
+            if b is None:
+                sampler.reset()
+                b = sampler()
+            lengths.append(int(b["x"].shape[1]))
+            x = torch.randn(batch, lengths[-1], 2048, generator=g).to(torch.bfloat16).pin_memory()
+            host_batches.append((x, torch.as_tensor(b["y"]).pin_memory()))
+        shape_cfg = {"feature_dim": 2048, "classes": classes, "seq_len": "log-normal 30..%d, this rank: min %d max %d"
+                     % (args.max_frames, min(lengths), max(lengths))}
+    step = TrainStep(model, group, impl=args.impl, mode=args.mode, limiter=args.limiter, bucket_mb=args.bucket_mb,
+                     lr=0.01, momentum=0.9, weight_decay=1e-4, loss_fn=loss_fn)
+    nb = len(host_batches)
     dev_batches = [(x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)) for x, y in host_batches]
     torch.cuda.synchronize()
 
@@ -166,7 +193,7 @@ def main():
         group.barrier()
         torch.cuda.synchronize()
 
-    use_graph = args.impl == "ours" and not args.no_graph
+    use_graph = args.impl == "ours" and not args.no_graph and args.model != "lstm"   # sequence length varies
     if use_graph:
         step.capture(*dev_batches[0])
 
@@ -175,7 +202,7 @@ def main():
         if i == max(args.warmup, 3) - 2:
             sync_all()
             t_w = time.perf_counter()
-        step.run_device(*dev_batches[i % 3])
+        step.run_device(*dev_batches[i % nb])
     torch.cuda.synchronize()
     base_step_s = (time.perf_counter() - t_w) / 2.0
     bs = torch.tensor([base_step_s], device=dev)
@@ -183,13 +210,17 @@ def main():
         dist.all_reduce(bs, op=dist.ReduceOp.MAX)
     base_step_s = float(bs.item())
 
-    inject = args.imbalance == "auto" and world > 1
+    inject = args.imbalance == "auto" and world > 1 and args.model != "lstm"
     delay_rng = random.Random(4242)  # same stream on every rank
 
     def delays_for_step():
         if not inject:
             return 0.0
         d = 0.0
+        if args.model == "resnet32":     # one random rank is delayed by 1.5 x its step time
+            if delay_rng.randrange(world) == rank:
+                d = 1.5 * base_step_s
+            return d
         for victim in (delay_rng.randrange(world), delay_rng.randrange(world)):
             e = delay_rng.expovariate(1.0 / (0.5 * base_step_s))
             if victim == rank:
@@ -208,7 +239,7 @@ def main():
             d = delays_for_step()
             if d > 0:
                 step.inject_delay(d)
-            last = fn(*batches[i % 3])
+            last = fn(*batches[(max(args.warmup, 3) + i) % nb])
         e1.record()
         torch.cuda.synchronize()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -223,9 +254,9 @@ def main():
     e2e = None
     if not args.no_e2e:
         ms_e2e, _, _, last_loss = timed(step.run_host, host_batches)
-        e2e = {"value": world * batch * args.steps / (ms_e2e / 1e3), "unit": "images/s",
+        e2e = {"value": world * batch * args.steps / (ms_e2e / 1e3), "unit": unit,
                "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": host_batches[0][0].numel() * 2 + host_batches[0][1].numel() * 8,
+               "h2d_bytes_per_step": int(sum(x.numel() * 2 + y.numel() * 8 for x, y in host_batches) / nb),
                "d2h_bytes_per_step": 4, "last_loss": last_loss}
     stats = step.stats()
     step.close()
@@ -235,18 +266,22 @@ def main():
 
     if rank == 0:
         out = {
-            "metric": "train_images_per_sec_under_injected_imbalance", "impl": args.impl,
-            "value": world * batch * args.steps / (ms_dev / 1e3), "unit": "images/s", "n_gpus": world,
+            "metric": "train_%s_per_sec_under_%s_imbalance" % (unit.split("/")[0],
+                                                                "natural" if args.model == "lstm" else "injected"),
+            "impl": args.impl,
+            "value": world * batch * args.steps / (ms_dev / 1e3), "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic N(0,1) images, uniform labels, random-init weights",
-            "config": {"model": name, "global_batch": batch * world, "per_gpu_batch": batch, "seq_len": None,
-                       "image": [res, res, 3], "classes": classes, "parallelism": "dp%d" % world,
+            "data": "synthetic N(0,1) inputs, uniform labels, random-init weights",
+            "config": {"model": name, "global_batch": batch * world, "per_gpu_batch": batch, **shape_cfg,
+                       "parallelism": "dp%d" % world,
                        "collective": args.mode + "-allreduce" if args.impl == "ours" else "nccl-allreduce",
                        "bucket_mb": args.bucket_mb, "limiter": args.limiter, "cuda_graph": use_graph,
                        "optimizer": "momentum SGD 0.9, wd 1e-4, fp32 master weights",
-                       "imbalance": ("2 random ranks/step delayed by Exp(mean 0.5 x %.1f ms)" % (base_step_s * 1e3))
-                       if inject else "none (single rank)" if world == 1 else "none",
+                       "imbalance": (("one random rank/step delayed by 1.5 x %.1f ms" if args.model == "resnet32" else
+                                      "2 random ranks/step delayed by Exp(mean 0.5 x %.1f ms)") % (base_step_s * 1e3))
+                       if inject else "natural (per-rank sequence lengths)" if args.model == "lstm"
+                       else "none (single rank)" if world == 1 else "none",
                        "l2": "per-step working set (activations + 51 MB gradients) exceeds the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "eager_stats": stats,
         }

@@ -30,6 +30,8 @@ def prepare_model(model: nn.Module, device: torch.device, compute_dtype=torch.bf
     model = model.to(device)
     if device.type == "cuda":
         model = model.to(memory_format=torch.channels_last)
+        if hasattr(model, "compute_dtype_"):        # models with their own parameter containers
+            model.compute_dtype_(compute_dtype)
         for m in model.modules():
             if isinstance(m, (nn.Conv2d, nn.Linear, nn.LSTM)):
                 m.to(compute_dtype)
