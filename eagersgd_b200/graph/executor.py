@@ -1,0 +1,209 @@
+"""Executing a model graph with this framework's operators.
+
+``GraphNetwork`` turns a ``Graph`` into a ``torch.nn.Module`` whose parameters are the graph's
+initializers and whose forward pass visits the operations in topological order, mapping every
+ONNX op type to the hand-written kernels (through ``ops.functional``) or a PyTorch op.  Together
+with ``train.executor.GraphExecutor`` this is the counterpart of the reference's per-framework
+network builders and graph executors (deep500/frameworks/pytorch/pytorch_visitor.py,
+pytorch_network.py, pytorch_graph_executor.py; reference/reference_graph_executor.py:34-47) and
+of its gradient extension ops (extended_operations.py:27-77), which no backend there implements.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as ops
+from .ir import Graph, Operation, Visitor
+
+
+class _Forward(Visitor):
+    def __init__(self, net: "GraphNetwork", feeds: Dict[str, torch.Tensor]):
+        self.net, self.v = net, dict(feeds)
+
+    def begin(self, graph):
+        for name in graph.initializers:
+            self.v[name] = self.net.tensor(name)
+
+    def end(self, graph):
+        return self.v
+
+    def _in(self, op, k):
+        return self.v[op.inputs[k]] if k < len(op.inputs) and op.inputs[k] != "" else None
+
+    def _out(self, op, value):
+        self.v[op.outputs[0]] = value
+
+    def visit_conv(self, op, g):
+        stride = op.attrs.get("strides", [1, 1])[0]
+        pad = op.attrs.get("pads", [0, 0, 0, 0])[0]
+        x, w, b = self._in(op, 0), self._in(op, 1), self._in(op, 2)
+        if b is None:
+            y, _ = ops.conv2d(x, w, stride, pad)
+        else:
+            y = F.conv2d(x, w, b, stride, pad)
+        self._out(op, y)
+
+    def visit_batchnormalization(self, op, g):
+        x, gamma, beta, mean, var = (self._in(op, k) for k in range(5))
+        self._out(op, ops.bn_act(x, gamma, beta, mean, var, 1.0 - op.attrs.get("momentum", 0.9), relu=False,
+                                 training=self.net.training))
+
+    def visit_relu(self, op, g): self._out(op, F.relu(self._in(op, 0)))
+
+    def visit_maxpool(self, op, g):
+        k, s = op.attrs.get("kernel_shape", [2, 2])[0], op.attrs.get("strides", [1, 1])[0]
+        p = op.attrs.get("pads", [0, 0, 0, 0])[0]
+        x = self._in(op, 0)
+        self._out(op, ops.max_pool_3x3_s2(x) if (k, s, p) == (3, 2, 1) else F.max_pool2d(x, k, s, p))
+
+    def visit_averagepool(self, op, g):
+        k, s = op.attrs.get("kernel_shape", [2, 2])[0], op.attrs.get("strides", [1, 1])[0]
+        self._out(op, F.avg_pool2d(self._in(op, 0), k, s, op.attrs.get("pads", [0, 0, 0, 0])[0]))
+
+    def visit_globalaveragepool(self, op, g):
+        y = ops.global_avg_pool(self._in(op, 0))
+        self._out(op, y.view(y.shape[0], y.shape[1], 1, 1))
+
+    def visit_gemm(self, op, g):
+        a, b, c = self._in(op, 0), self._in(op, 1), self._in(op, 2)
+        if op.attrs.get("transA", 0):
+            a = a.t()
+        w = b if op.attrs.get("transB", 0) else b.t()          # ops.linear wants [out, in]
+        self._out(op, ops.linear(a, w.contiguous() if not op.attrs.get("transB", 0) else w, c))
+
+    def visit_matmul(self, op, g): self._out(op, self._in(op, 0) @ self._in(op, 1))
+    def visit_add(self, op, g): self._out(op, self._in(op, 0) + self._in(op, 1))
+    def visit_sum(self, op, g): self._out(op, sum(self.v[i] for i in op.inputs))
+    def visit_flatten(self, op, g): self._out(op, torch.flatten(self._in(op, 0), op.attrs.get("axis", 1)))
+    def visit_reshape(self, op, g): self._out(op, self._in(op, 0).reshape(op.attrs["shape"]))
+    def visit_squeeze(self, op, g): self._out(op, self._in(op, 0).squeeze(*op.attrs.get("axes", [])))
+    def visit_unsqueeze(self, op, g): self._out(op, self._in(op, 0).unsqueeze(op.attrs["axes"][0]))
+    def visit_softmax(self, op, g): self._out(op, F.softmax(self._in(op, 0).float(), op.attrs.get("axis", -1)))
+    def visit_identity(self, op, g): self._out(op, self._in(op, 0))
+    def visit_concat(self, op, g): self._out(op, torch.cat([self.v[i] for i in op.inputs], op.attrs.get("axis", 1)))
+
+    def visit_dropout(self, op, g):
+        self._out(op, F.dropout(self._in(op, 0), op.attrs.get("ratio", 0.5), self.net.training))
+
+    # losses
+    def visit_softmaxcrossentropy(self, op, g):
+        logits = self._in(op, 0)
+        self._out(op, ops.softmax_cross_entropy(logits if logits.dtype == torch.float32 else logits.float(),
+                                                self._in(op, 1)))
+
+    def visit_crossentropy(self, op, g):
+        p = self._in(op, 0).float().clamp_min(1e-12)
+        self._out(op, F.nll_loss(p.log(), self._in(op, 1)))
+
+    def visit_meansquarederror(self, op, g):
+        self._out(op, F.mse_loss(self._in(op, 0).float(), self._in(op, 1).float()))
+
+    # extensions
+    def visit_stopgradient(self, op, g): self._out(op, self._in(op, 0).detach())
+
+    def visit_allreducegradients(self, op, g):
+        """Identity in the forward pass; the gradient flowing back is averaged over the group."""
+        self._out(op, _AllReduceGrad.apply(self._in(op, 0), self.net.group))
+
+
+class _AllReduceGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        if ctx.group is not None and ctx.group.world > 1:
+            g = g.contiguous()
+            ctx.group.sync_all(g, average=True)
+        return g, None
+
+
+class GraphNetwork(nn.Module):
+    def __init__(self, graph: Graph, group=None, trainable_only_used: bool = True):
+        super().__init__()
+        self.graph, self.group = graph, group
+        self._names: Dict[str, str] = {}
+        bn_stats = {op.inputs[k] for op in graph.ops if op.op_type == "BatchNormalization" for k in (3, 4)}
+        for i, (name, value) in enumerate(graph.initializers.items()):
+            t = torch.as_tensor(np.asarray(value))
+            key = "p%d" % i
+            self._names[name] = key
+            if name in bn_stats or not t.is_floating_point():
+                self.register_buffer(key, t.clone())
+            else:
+                self.register_parameter(key, nn.Parameter(t.clone()))
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return getattr(self, self._names[name])
+
+    def forward(self, x, **feeds):
+        values = {self.graph.inputs[0]: x}
+        values.update(feeds)
+        out = self.graph.accept(_Forward(self, values))
+        res = [out[o] for o in self.graph.outputs if o in out]
+        return res[0] if len(res) == 1 else tuple(res)
+
+    def export_initializers(self) -> Dict[str, np.ndarray]:
+        return {n: self.tensor(n).detach().float().cpu().numpy() for n in self.graph.initializers}
+
+
+def from_torch_resnet(model) -> Graph:
+    """Graph of a ``models.resnet.ResNet`` (v1): the creation-order registry gives the node order."""
+    g = Graph("resnet")
+    x = g.add_input("input")
+    cnt = {"conv": 0, "bn": 0}
+
+    def conv(mod, inp):
+        k = cnt["conv"]
+        cnt["conv"] += 1
+        w = g.add_initializer("conv%d.weight" % k, mod.weight.detach().float().numpy())
+        out = "conv%d.out" % k
+        g.add("Conv", [inp, w], [out], strides=[mod.stride[0]] * 2, pads=[mod.padding[0]] * 4,
+              kernel_shape=list(mod.kernel_size))
+        return out
+
+    def bn(mod, inp):
+        k = cnt["bn"]
+        cnt["bn"] += 1
+        names = [g.add_initializer("bn%d.%s" % (k, n), t.detach().float().numpy())
+                 for n, t in (("gamma", mod.weight), ("beta", mod.bias), ("mean", mod.running_mean),
+                              ("var", mod.running_var))]
+        out = "bn%d.out" % k
+        g.add("BatchNormalization", [inp] + names, [out], momentum=1.0 - mod.momentum, epsilon=mod.eps)
+        return out
+
+    def relu(inp):
+        out = inp + ".relu"
+        g.add("Relu", [inp], [out])
+        return out
+
+    assert model.version == 1, "graph export covers the v1 / v1.5 layout"
+    h = relu(bn(model.stem_bn, conv(model.stem, x)))
+    if model.first_pool:
+        g.add("MaxPool", [h], ["pool.out"], kernel_shape=[3, 3], strides=[2, 2], pads=[1, 1, 1, 1])
+        h = "pool.out"
+    for bi, blk in enumerate(model.blocks):
+        sc = h
+        if blk.proj is not None:
+            sc = bn(blk.proj_bn, conv(blk.proj, h))
+        y = h
+        for i, (c, b) in enumerate(zip(blk.convs, blk.bns)):
+            y = bn(b, conv(c, y))
+            if i < len(blk.convs) - 1:
+                y = relu(y)
+        g.add("Add", [y, sc], ["block%d.sum" % bi])
+        h = relu("block%d.sum" % bi)
+    g.add("GlobalAveragePool", [h], ["gap.out"])
+    g.add("Flatten", ["gap.out"], ["flat.out"], axis=1)
+    w = g.add_initializer("fc.weight", model.fc.weight.detach().float().numpy())
+    b = g.add_initializer("fc.bias", model.fc.bias.detach().float().numpy())
+    g.add("Gemm", ["flat.out", w, b], ["logits"], transB=1)
+    g.add_output("logits")
+    return g
