@@ -142,6 +142,23 @@ class AdaGradOptimizer(ThreeStepOptimizer):
             old_param.dtype)
 
 
+class RMSPropOptimizer(ThreeStepOptimizer):
+    """sq = d*sq + (1-d)*g^2 ; p -= lr * g / (sqrt(sq) + eps)  (the RMSProp of the reference's
+    PyTorch backend, deep500/frameworks/pytorch/pytorch_optimizers.py)."""
+
+    def __init__(self, executor, loss="loss", learning_rate=1e-3, decay=0.9, epsilon=1e-8):
+        super().__init__(executor, loss)
+        self.hyper.update(learning_rate=learning_rate, decay=decay, epsilon=epsilon)
+        self.sq: Dict[str, torch.Tensor] = {}
+
+    def update_rule(self, grad, old_param, name):
+        h = self.hyper
+        g = grad.float()
+        sq = self.sq.get(name, torch.zeros_like(g)).mul_(h["decay"]).addcmul_(g, g, value=1 - h["decay"])
+        self.sq[name] = sq
+        return (old_param.float() - h["learning_rate"] * g / (sq.sqrt() + h["epsilon"])).to(old_param.dtype)
+
+
 class TorchOptimizer(FirstOrderOptimizer):
     """Any ``torch.optim`` optimizer (or one of this package's eager-SGD wrappers around it)
     driven through the executor, with the ``gradient_modifier`` hook applied before the step."""

@@ -18,7 +18,7 @@ def _toy():
     return ds, ShuffleSampler(ds, 32, seed=0), OrderedSampler(ds, 64)
 
 
-@pytest.mark.parametrize("opt_name", ["GradientDescent", "MomentumOptimizer", "AdamOptimizer", "AdaGradOptimizer"])
+@pytest.mark.parametrize("opt_name", ["GradientDescent", "MomentumOptimizer", "AdamOptimizer", "AdaGradOptimizer", "RMSPropOptimizer"])
 def test_trainer_with_reference_update_rules(opt_name):
     from eagersgd_b200.optim import base
     from eagersgd_b200.train.executor import GraphExecutor, classification_loss
@@ -27,7 +27,7 @@ def test_trainer_with_reference_update_rules(opt_name):
     torch.manual_seed(0)
     ds, tr, te = _toy()
     ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
-    lr = {"GradientDescent": 0.5, "MomentumOptimizer": 0.1, "AdamOptimizer": 0.05, "AdaGradOptimizer": 0.5}[opt_name]
+    lr = {"GradientDescent": 0.5, "MomentumOptimizer": 0.1, "AdamOptimizer": 0.05, "AdaGradOptimizer": 0.5, "RMSPropOptimizer": 0.02}[opt_name]
     opt = getattr(base, opt_name)(ex, learning_rate=lr)
     stats = Trainer(tr, te, ex, opt).run_loop(4, [E.SummaryGeneratorEvent(), E.AccuracyAbortEvent(0.999)])
     assert stats.test_summaries[-1].accuracy > 0.85
