@@ -2,6 +2,7 @@
 
     python -m eagersgd_b200.ops.bench_ops --op gemm --shape 8192,8192,8192
     python -m eagersgd_b200.ops.bench_ops --op conv --shape 64,128,56,56,128,3,1      (N,Cin,H,W,Cout,k,stride)
+    python -m eagersgd_b200.ops.bench_ops --op conv_wgrad --shape 64,128,28,28,128,3,1
     python -m eagersgd_b200.ops.bench_ops --op bn --shape 256,256,56,56 [--backward]
     python -m eagersgd_b200.ops.bench_ops --op suite
 
@@ -117,6 +118,25 @@ def bench_conv(shape, iters, backward=False):
                 stride=stride, ms=ms, tflops=flops / ms / 1e9, gbs=byts / ms / 1e6, library_ms=ms_lib)
 
 
+def bench_conv_wgrad(shape, iters):
+    """Weight gradient of a k x k convolution (pixels are the reduction dimension)."""
+    from . import functional as ops
+    n, cin, h, w, cout, k, stride = shape
+    x = _cl(torch.randn(n, cin, h, w, device="cuda")).to(torch.bfloat16)
+    wt = _cl(torch.randn(cout, cin, k, k, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    pad = (k - 1) // 2
+    y, _ = ops.conv2d(x, wt, stride, pad)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    ms = timeit(lambda: torch.autograd.grad(y, wt, g, retain_graph=True), iters)
+    with ops.reference_ops():
+        y2, _ = ops.conv2d(x, wt, stride, pad)
+        ms_lib = timeit(lambda: torch.autograd.grad(y2, wt, g, retain_graph=True), iters)
+    flops = 2.0 * n * y.shape[2] * y.shape[3] * cout * cin * k * k
+    byts = 2.0 * (x.numel() + y.numel()) + 4.0 * wt.numel()
+    return dict(op="conv_wgrad", N=n, Cin=cin, H=h, W=w, Cout=cout, k=k, stride=stride, ms=ms,
+                tflops=flops / ms / 1e9, gbs=byts / ms / 1e6, library_ms=ms_lib)
+
+
 def bench_bn(shape, iters, backward=False, residual=False):
     from . import functional as ops
     n, c, h, w = shape
@@ -187,6 +207,8 @@ def run(op, shape, iters, backward=False, residual=False):
         r = bench_gemm(shape, iters, False, False)
     elif op == "conv":
         r = bench_conv(shape, iters, backward)
+    elif op == "conv_wgrad":
+        r = bench_conv_wgrad(shape, iters)
     elif op == "bn":
         r = bench_bn(shape, iters, backward, residual)
     elif op == "ce":
