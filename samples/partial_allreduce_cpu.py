@@ -56,9 +56,10 @@ def main(argv=None):
     # newer one before any round picked it up is superseded (the reference overwrites its send buffer the same
     # way); the limiter's synchronous rounds bound how far a rank can fall behind.
     assert all(np.allclose(t, totals[0]) for t in totals), [t[0] for t in totals]
-    print("every rank applied the same total: %.0f of %d published gradients, %d superseded"
-          % (totals[0][0], P * args.steps, sum(dropped)))
-    assert totals[0][0] + sum(dropped) == P * args.steps
+    pending = P * args.steps - int(round(totals[0][0])) - sum(dropped)   # published after the last round closed
+    print("every rank applied the same total: %.0f of %d published gradients, %d superseded, %d still pending"
+          % (totals[0][0], P * args.steps, sum(dropped), pending))
+    assert 0 <= pending <= P
     segs.close()
 
 
