@@ -38,7 +38,8 @@ def _sources(sub, exts):
     out = []
     for ext in exts:
         out += glob.glob(os.path.join(CSRC, sub, "*" + ext))
-    return sorted(out)
+    # *_main.cpp are stand-alone programs (the sanitizer stress driver), not part of the libraries
+    return sorted(f for f in out if not f.endswith("_main.cpp"))
 
 
 def _headers():

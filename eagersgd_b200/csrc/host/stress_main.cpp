@@ -1,0 +1,113 @@
+// Stress driver for the host control plane, meant to be built with -fsanitize=thread (or address):
+//   g++ -std=c++17 -O1 -g -fsanitize=thread stress_main.cpp cpu_channel.cpp oprt.cpp -lpthread -o stress && ./stress
+// Part 1 runs the partial-allreduce protocol (the very source the CUDA kernels compile) as threads of
+// one process in all three modes with random arrival skew, and checks that every rank applied the same
+// total and that no status bit was raised.  Part 2 posts a persistent allreduce schedule of the
+// operation runtime many times from every rank.  The reference has no sanitizer or race-detection
+// build (fflib2 CMakeLists.txt has only -O3 / -DFFDEBUG); this is the race check of this framework's
+// host code, and because the device kernels share step.h, of their protocol logic too.
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <chrono>
+#include <thread>
+#include <vector>
+#include "oprt.h"
+
+extern "C" {
+struct esgd_step_info {
+  int32_t role, n_contrib, n_fresh, is_sync;
+  uint32_t status;
+  float drain_rounds;
+  uint64_t round, local_step;
+};
+struct esgd_cpu_params {
+  int32_t rank, world, base_mode, include_stale, average, home, dtype, reserved;
+  int64_t limiter;
+  uint64_t seed, timeout_ns, grace_ns, count;
+};
+uint64_t esgd_cpu_segment_bytes(uint64_t count, int dtype);
+uint32_t esgd_cpu_step(void** bases, const esgd_cpu_params* p, const void* grad, void* out, esgd_step_info* info);
+uint32_t esgd_cpu_flush(void** bases, const esgd_cpu_params* p, void* out, esgd_step_info* info);
+}
+
+static int run_channel(int mode, int world, int steps, uint64_t count) {
+  const uint64_t bytes = esgd_cpu_segment_bytes(count, 0);
+  std::vector<void*> bases(world);
+  for (int r = 0; r < world; ++r) {
+    if (posix_memalign(&bases[r], 256, bytes) != 0) return 1;
+    memset(bases[r], 0, bytes);
+  }
+  std::vector<double> totals(world, 0.0);
+  std::vector<uint32_t> status(world, 0);
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r) {
+    th.emplace_back([&, r] {
+      esgd_cpu_params p;
+      memset(&p, 0, sizeof(p));
+      p.rank = r; p.world = world; p.base_mode = mode; p.include_stale = 1; p.average = 2 /* sum */; p.home = 0;
+      p.dtype = 0; p.limiter = 4; p.seed = 6545343; p.timeout_ns = 20ull * 1000000000ull; p.grace_ns = 0; p.count = count;
+      std::vector<float> grad(count), out(count);
+      unsigned seed = 1234u + (unsigned)r;
+      esgd_step_info info;
+      for (int k = 0; k < steps; ++k) {
+        if (rand_r(&seed) % 4 == 0) std::this_thread::sleep_for(std::chrono::microseconds(rand_r(&seed) % 300));
+        for (uint64_t e = 0; e < count; ++e) grad[e] = 1.0f;
+        status[r] |= esgd_cpu_step(bases.data(), &p, grad.data(), out.data(), &info);
+        totals[r] += out[0];
+        for (uint64_t e = 1; e < count; ++e)
+          if (out[e] != out[0]) status[r] |= 0x80000000u;      // a torn result
+      }
+      status[r] |= esgd_cpu_flush(bases.data(), &p, out.data(), &info);
+      totals[r] += out[0];
+    });
+  }
+  for (auto& t : th) t.join();
+  int bad = 0;
+  for (int r = 0; r < world; ++r) {
+    if (status[r] != 0 || totals[r] != totals[0]) {
+      fprintf(stderr, "mode %d rank %d: status %x total %.1f (rank 0: %.1f)\n", mode, r, status[r], totals[r], totals[0]);
+      bad = 1;
+    }
+    free(bases[r]);
+  }
+  printf("channel mode %d: %d ranks x %d steps, total applied %.0f on every rank\n", mode, world, steps, totals[0]);
+  return bad;
+}
+
+static int run_runtime(int world, int posts) {
+  rt_world* w = rt_world_create(world);
+  std::vector<int> bad(world, 0);
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r) {
+    th.emplace_back([&, r] {
+      rt_rank* c = rt_world_rank(w, r);
+      std::vector<int32_t> snd(64), rcv(64);
+      rt_buf bs = rt_buffer_create(c, snd.data(), 64, RT_INT32), br = rt_buffer_create(c, rcv.data(), 64, RT_INT32);
+      rt_sched s = rt_allreduce(c, bs, br, 3, RT_SUM);
+      for (int it = 0; it < posts; ++it) {
+        for (int e = 0; e < 64; ++e) snd[e] = e + it + r;
+        rt_schedule_post(c, s);
+        if (rt_schedule_wait(c, s, 30.0) != RT_SUCCESS) { bad[r] = 1; break; }
+        for (int e = 0; e < 64; ++e)
+          if (rcv[e] != (e + it) * world + world * (world - 1) / 2) bad[r] = 1;
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  rt_world_destroy(w);
+  int any = 0;
+  for (int r = 0; r < world; ++r) any |= bad[r];
+  printf("runtime allreduce: %d ranks x %d posts %s\n", world, posts, any ? "FAILED" : "ok");
+  return any;
+}
+
+int main(int argc, char** argv) {
+  const int world = argc > 1 ? atoi(argv[1]) : 4;
+  const int steps = argc > 2 ? atoi(argv[2]) : 200;
+  int bad = 0;
+  for (int mode = 0; mode < 3; ++mode) bad |= run_channel(mode, world, steps, 1024);
+  bad |= run_runtime(world, steps / 4 + 1);
+  return bad;
+}
