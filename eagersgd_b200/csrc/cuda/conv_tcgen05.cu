@@ -38,6 +38,7 @@ struct ConvProblem {
   int BW, BH, BI;            // output-pixel box of a tile (BW*BH*BI <= 128)
   int w_tiles, h_tiles, i_tiles, n_tiles;
   int fixed_n;
+  int res_kb;                // > 0: the whole filter bank of the CTA's channel range stays in shared memory
 
   struct Tile { int kb0, kb1, n0, w0, h0, i0; };
 
@@ -62,11 +63,17 @@ struct ConvProblem {
     t.kb1 = R * S * cblks;
     return true;
   }
-  __device__ __forceinline__ void load(const Tile& t, int kb, uint8_t* a, uint8_t* b, uint64_t* bar) const {
+  __device__ __forceinline__ void load_a(const Tile& t, int kb, uint8_t* a, uint64_t* bar) const {
     const int tap = kb / cblks, cb = kb - tap * cblks;
     const int r = tap / S, s = tap - r * S;
     tma_load_4d(a, &tmX, bar, cb * 64, t.w0 * stride + s - pad, t.h0 * stride + r - pad, t.i0);
+  }
+  __device__ __forceinline__ void load_b(const Tile& t, int kb, uint8_t* b, uint64_t* bar) const {
     tma_load_2d(b, &tmW, bar, kb * 64, t.n0);
+  }
+  __device__ __forceinline__ void load(const Tile& t, int kb, uint8_t* a, uint8_t* b, uint64_t* bar) const {
+    load_a(t, kb, a, bar);
+    load_b(t, kb, b, bar);
   }
   __device__ __forceinline__ void store_panel(const Tile& t, int panel, const void* smem) const {
     tma_store_4d(&tmY, smem, t.n0 + panel * 64, t.w0, t.h0, t.i0);
@@ -74,6 +81,9 @@ struct ConvProblem {
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const {
     const int wi = row % BW, hi = (row / BW) % BH, ni = row / (BW * BH);
     return ni < BI && t.w0 + wi < Wo && t.h0 + hi < Ho && t.i0 + ni < N;
+  }
+  __device__ __forceinline__ int valid_prefix(const Tile& t) const {   // box inside the tensor: its pixels, in order
+    return (t.w0 + BW <= Wo && t.h0 + BH <= Ho && t.i0 + BI <= N) ? BW * BH * BI : -1;
   }
   __device__ __forceinline__ void* row_ptr(const Tile&, int) const { return nullptr; }
 };
@@ -95,6 +105,7 @@ struct ConvWgradProblem {
   int BW, BH, BI, w_tiles, h_tiles, i_tiles;
   int m_tiles, n_tiles, splits, boxes_total, boxes_per_split;
   float* dw;   // [Cout][R*S][Cin]
+  static constexpr int res_kb = 0;   // both operands change with every k-block
 
   struct Tile { int kb0, kb1, n0, m0, tap; };
 
@@ -121,8 +132,11 @@ struct ConvWgradProblem {
     for (int i = 0; i < BN / 64; ++i)
       tma_load_4d(b + i * 8192, &tmX, bar, t.n0 + 64 * i, w0 * stride + s - pad, h0 * stride + r - pad, i0);
   }
+  __device__ __forceinline__ void load_a(const Tile&, int, uint8_t*, uint64_t*) const {}
+  __device__ __forceinline__ void load_b(const Tile&, int, uint8_t*, uint64_t*) const {}
   __device__ __forceinline__ void store_panel(const Tile&, int, const void*) const {}
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < Cout; }
+  __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, Cout - t.m0); }
   __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
     const int k = t.m0 + row;
     return k < Cout ? (void*)(dw + ((size_t)k * (R * S) + t.tap) * Cin) : nullptr;
@@ -223,7 +237,12 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   const int sms = sm_count();
   const int total = p.w_tiles * p.h_tiles * p.i_tiles * p.n_tiles;
   int grid;
-  p.fixed_n = (ep.col_sum != nullptr) ? 1 : 0;
+  // the filter bank of the CTA's channel range stays in shared memory when it fits beside four input stages
+  const int kb_total = a.R * a.S * p.cblks;
+  const bool resident = resident_enabled() && kb_total <= Cfg<BN>::MAX_RES_KB && p.n_tiles <= sms / 2 &&
+                        total / p.n_tiles >= 2 * (sms / p.n_tiles);
+  p.res_kb = resident ? kb_total : 0;
+  p.fixed_n = (ep.col_sum != nullptr || resident) ? 1 : 0;
   if (p.fixed_n) {
     if (p.n_tiles > sms) return -3;
     grid = (sms / p.n_tiles) * p.n_tiles;
@@ -231,7 +250,8 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   } else {
     grid = total < sms ? total : sms;
   }
-  ep.tx_bytes = (uint32_t)(p.BW * p.BH * p.BI * 128 + Cfg<BN>::B_STAGE_BYTES);
+  ep.tx_bytes_a = (uint32_t)(p.BW * p.BH * p.BI * 128);
+  ep.tx_bytes = ep.tx_bytes_a + (uint32_t)Cfg<BN>::B_STAGE_BYTES;
   conv_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
   esgd::count_launch();
   return (int)cudaGetLastError();
@@ -292,6 +312,7 @@ int launch_wgrad(const ConvArgs& a, const void* dy, float* dw, int* error_flag, 
   ep.out_mode = OUT_F32_ATOMIC; ep.relu = 0; ep.n_total = a.Cin; ep.bias = nullptr;
   ep.col_sum = nullptr; ep.col_sqsum = nullptr; ep.error_flag = error_flag;
   ep.tx_bytes = (uint32_t)(p.BW * p.BH * 128 * (BM / 64 + BN / 64));
+  ep.tx_bytes_a = 0;
   const int total = base_tiles * p.splits;
   const int grid = total < sms ? total : sms;
   conv_wgrad_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
@@ -340,7 +361,7 @@ int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int 
   Epilogue ep;
   ep.out_mode = OUT_BF16; ep.relu = relu; ep.n_total = Cout; ep.bias = nullptr;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
-  ep.tx_bytes = 0;
+  ep.tx_bytes = 0; ep.tx_bytes_a = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
   if (BN == 64) return launch<64>(a, ep, s);

@@ -26,6 +26,7 @@ struct GemmProblem {
   int M, N, K;
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
   int fixed_n;        // every CTA keeps one column range (needed for the per-CTA statistics flush)
+  int res_kb;         // > 0: all k-blocks of B for the CTA's column range stay in shared memory
   float* c_f32;       // fp32 output (direct modes)
   int ldc;
 
@@ -51,7 +52,7 @@ struct GemmProblem {
     t.kb1 = min(t.kb0 + kb_per_split, kb_total);
     return true;
   }
-  __device__ __forceinline__ void load(const Tile& t, int kb, uint8_t* a, uint8_t* b, uint64_t* bar) const {
+  __device__ __forceinline__ void load_a(const Tile& t, int kb, uint8_t* a, uint64_t* bar) const {
     const int k0 = kb * BK;
     if (A_MN) {
 #pragma unroll
@@ -59,6 +60,9 @@ struct GemmProblem {
     } else {
       tma_load_2d(a, &tmA, bar, k0, t.m0);
     }
+  }
+  __device__ __forceinline__ void load_b(const Tile& t, int kb, uint8_t* b, uint64_t* bar) const {
+    const int k0 = kb * BK;
     if (B_MN) {
 #pragma unroll
       for (int i = 0; i < BN / 64; ++i) tma_load_2d(b + i * 8192, &tmB, bar, t.n0 + 64 * i, k0);
@@ -66,10 +70,15 @@ struct GemmProblem {
       tma_load_2d(b, &tmB, bar, k0, t.n0);
     }
   }
+  __device__ __forceinline__ void load(const Tile& t, int kb, uint8_t* a, uint8_t* b, uint64_t* bar) const {
+    load_a(t, kb, a, bar);
+    load_b(t, kb, b, bar);
+  }
   __device__ __forceinline__ void store_panel(const Tile& t, int panel, const void* smem) const {
     tma_store_2d(&tmC, smem, t.n0 + panel * 64, t.m0);
   }
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < M; }
+  __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, M - t.m0); }
   __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
     return (t.m0 + row < M) ? (void*)(c_f32 + (size_t)(t.m0 + row) * ldc) : nullptr;
   }
@@ -144,7 +153,12 @@ int launch(const GemmArgs& g, Epilogue ep, cudaStream_t stream) {
   p.ldc = g.ldc;
   const int sms = sm_count();
   int grid;
-  p.fixed_n = (ep.col_sum != nullptr) ? 1 : 0;
+  // B stays in shared memory when its whole K extent fits beside four A stages and every CTA has several
+  // tiles of one column range to amortise the load over
+  const bool resident = resident_enabled() && p.splits == 1 && p.kb_total <= Cfg<BN>::MAX_RES_KB &&
+                        p.n_tiles <= sms / 2 && p.m_tiles >= 2 * (sms / p.n_tiles);
+  p.res_kb = resident ? p.kb_total : 0;
+  p.fixed_n = (ep.col_sum != nullptr || resident) ? 1 : 0;
   if (p.fixed_n) {
     if (p.splits != 1 || p.n_tiles > sms) return -3;
     const int total = p.m_tiles * p.n_tiles;
@@ -185,7 +199,7 @@ int esgd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   Epilogue ep;
   ep.out_mode = out_mode; ep.relu = relu; ep.n_total = N; ep.bias = bias;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
-  ep.tx_bytes = 0;
+  ep.tx_bytes = 0; ep.tx_bytes_a = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
   if (BN == 64) return launch_major<64>(a_mn, b_mn, g, ep, s);

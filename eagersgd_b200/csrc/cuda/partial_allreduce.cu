@@ -8,6 +8,9 @@
 //                   broadcast the round descriptor, build the Plan
 //   data kernel   : reduce over peer memory + mailbox delivery + fused update;
 //                   the last block signals completion (esgd::finish_step)
+//   gather kernel : large vectors only (two-shot reduction): the data kernel reduced and
+//                   distributed this rank's share; wait for the other shares, apply the
+//                   update from the local gather buffer, signal completion
 //
 // All cross-GPU waits are bounded; when one runs out the kernel records a status
 // bit and returns, leaving the context usable.
@@ -32,10 +35,20 @@ __global__ void pack_kernel(DevChannel* ch) {
   pack_phase(ch, (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
 }
 
+// The data phase is split in two when there is enough data and more than one reducer.  Every
+// participant of a round takes the same decision (same count, same threshold, same descriptor).
+__device__ inline void decide_two_shot(DevChannel* ch) {
+  const Plan& p = ch->plan;
+  ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= 2 && ch->count >= ch->two_shot_min &&
+                       ch->gath[ch->cfg.rank] != nullptr) ? 1 : 0;
+}
+
 __global__ void ctl_kernel(DevChannel* ch) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
   ch->blocks_done = 0;
+  ch->blocks_done2 = 0;
+  ch->plan.two_shot = 0;
   if (me->status & ST_TIMEOUT_SLOT) {  // nothing valid was packed
     me->local_step += 1;
     ch->plan.role = ROLE_ABORT;
@@ -44,6 +57,7 @@ __global__ void ctl_kernel(DevChannel* ch) {
     return;
   }
   ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan);
+  decide_two_shot(ch);
 }
 
 __global__ void flush_ctl_kernel(DevChannel* ch) {
@@ -59,6 +73,25 @@ __global__ void data_kernel(DevChannel* ch) {
   if (threadIdx.x == 0) {
     unsigned old = atomicAdd(&ch->blocks_done, 1u);
     if (old == gridDim.x - 1) {
+      __threadfence_system();
+      if (ch->plan.two_shot) gather_signal(ch);     // completion is signalled by the gather kernel
+      else finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
+    }
+  }
+}
+
+__global__ void gather_kernel(DevChannel* ch) {
+  if (!ch->plan.two_shot) return;
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = gather_wait(ch) ? 1 : 0;
+  __syncthreads();
+  if (ok) data_apply_gathered(ch, (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned old = atomicAdd(&ch->blocks_done2, 1u);
+    if (old == gridDim.x - 1) {
+      if (!ok) ch->view.ctl[ch->cfg.rank]->status |= ST_TIMEOUT_GATHER;
       __threadfence_system();
       finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
     }
@@ -86,14 +119,26 @@ __global__ void emulated_step_kernel(DevChannel** chans, const uint64_t* delay_n
   __syncthreads();
   if (threadIdx.x == 0) {
     if (flush) ctl_flush<DevEnv>(ch->view, ch->cfg, &ch->plan);
-    else if (ok) ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan);
-    else { me->local_step += 1; ch->plan.role = ROLE_ABORT; ch->plan.holds_own_lock = 0; }
+    else if (ok) { ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan); decide_two_shot(ch); }
+    else { me->local_step += 1; ch->plan.role = ROLE_ABORT; ch->plan.holds_own_lock = 0; ch->plan.two_shot = 0; }
   }
   __threadfence();
   __syncthreads();
   data_phase(ch, threadIdx.x, blockDim.x);
   __threadfence_system();
   __syncthreads();
+  if (ch->plan.two_shot) {
+    __shared__ int got;
+    if (threadIdx.x == 0) {
+      gather_signal(ch);
+      got = gather_wait(ch) ? 1 : 0;
+      if (!got) me->status |= ST_TIMEOUT_GATHER;
+    }
+    __syncthreads();
+    if (got) data_apply_gathered(ch, threadIdx.x, blockDim.x);
+    __threadfence_system();
+    __syncthreads();
+  }
   if (threadIdx.x == 0) finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
 }
 
@@ -130,6 +175,7 @@ struct esgd_channel_desc {
   void* slot0[kMaxRanks];
   void* slot1[kMaxRanks];
   void* mbox[kMaxRanks];
+  void* gath[kMaxRanks];          // gather buffers (all null: one-shot reduction only)
   int32_t rank, world, base_mode, include_stale, average, home, slot_bf16, grad_in_bf16;
   int64_t limiter;
   uint64_t seed, timeout_ns, grace_ns, count;
@@ -140,6 +186,7 @@ struct esgd_channel_desc {
   void* out;
   int32_t out_bf16, pad;
   void* hyper;
+  uint64_t two_shot_min;          // element count from which the reduction runs in two shots
 };
 
 uint64_t esgd_dev_channel_bytes(void) { return sizeof(DevChannel); }
@@ -155,7 +202,9 @@ int esgd_channel_configure(void* dch, const esgd_channel_desc* d, void* stream) 
     h.slot[j][0] = d->slot0[j];
     h.slot[j][1] = d->slot1[j];
     h.mbox[j] = (float*)d->mbox[j];
+    h.gath[j] = (float*)d->gath[j];
   }
+  h.two_shot_min = d->two_shot_min;
   h.cfg.rank = d->rank; h.cfg.world = d->world; h.cfg.average_world = d->average; h.cfg.home = d->home;
   h.cfg.timeout_ns = d->timeout_ns; h.cfg.grace_ns = d->grace_ns;
   h.pol.base_mode = d->base_mode; h.pol.include_stale = d->include_stale; h.pol.limiter = d->limiter;
@@ -174,14 +223,17 @@ static inline int grid_for(uint64_t count, int max_blocks) {
   return (int)(need < (uint64_t)max_blocks ? need : (uint64_t)max_blocks);
 }
 
-// One full step of one channel on `stream`.
-int esgd_channel_step(void* dch, uint64_t count, int max_blocks, void* stream) {
+// One full step of one channel on `stream`.  `two_shot`: the channel was configured with gather buffers and
+// `count` reaches its two-shot threshold, so the gather kernel must follow (it returns at once in rounds
+// that were reduced in one shot).
+int esgd_channel_step(void* dch, uint64_t count, int max_blocks, int two_shot, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   int g = grid_for(count, max_blocks);
   pack_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
   ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch);
   data_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
-  count_launch(3);
+  if (two_shot) gather_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
+  count_launch(two_shot ? 4 : 3);
   return (int)cudaGetLastError();
 }
 

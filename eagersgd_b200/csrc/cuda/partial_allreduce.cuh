@@ -12,6 +12,15 @@
 // gradient when a generic optimizer is wrapped.  No NCCL call and no separate
 // elementwise kernel (replaces fflib2 gcomp SUM, components/gcomp/
 // ffop_gcomp_operator.c:8-58, plus TF ApplyMomentum on the reference path).
+//
+// Large vectors with two or more participants use a two-shot form of the same
+// reduction: each participant sums only ITS share of the vector (a reduce-scatter
+// by peer loads), stores the fp32 result into every participant's gather buffer
+// (an all-gather by peer stores) and raises a per-round flag there; a second
+// kernel waits (bounded) for all shares and applies the update from the local
+// gather buffer.  A rank then moves 2(P-1)/P of the vector over NVLink instead of
+// P-1 times the vector, with bit-identical results: the same fp32 sums in the
+// same order, transported in fp32.
 #pragma once
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -27,6 +36,7 @@ struct DevChannel {
   ChannelView view;
   void* slot[kMaxRanks][kSlotDepth];
   float* mbox[kMaxRanks];
+  float* gath[kMaxRanks];    // gather buffers of the two-shot reduction (null: one-shot only)
   StepConfig cfg;
   StepPolicy pol;
   uint64_t count;            // elements; multiple of 8
@@ -42,7 +52,8 @@ struct DevChannel {
   const float* hyper;        // HP_* values in device memory, refreshed by the host
   Plan plan;
   uint32_t blocks_done;
-  uint32_t pad1;
+  uint32_t blocks_done2;     // block counter of the gather kernel
+  uint64_t two_shot_min;     // smallest element count that takes the two-shot path
 };
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, uint64_t i, float v[8]) {
@@ -138,6 +149,84 @@ __device__ void data_participant(const DevChannel* ch, uint64_t tid, uint64_t nt
   }
 }
 
+// Two-shot, first half: reduce this participant's share and deliver it to the gather buffer of every
+// participant (its own included) and to the mailbox of every absent rank.
+template <typename ST>
+__device__ void data_reduce_scatter(const DevChannel* ch, uint64_t tid, uint64_t nthreads) {
+  const Plan& plan = ch->plan;
+  const int n_src = plan.n_src, n_push = plan.n_push;
+  const ST* src[kMaxRanks];
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s)
+    src[s] = s < n_src ? reinterpret_cast<const ST*>(ch->slot[plan.src_rank[s]][plan.src_parity[s]]) : nullptr;
+  float* dst[kMaxRanks];
+  int n_dst = 0;
+  for (int j = 0; j < ch->cfg.world; ++j)
+    if (plan.fresh_mask & (1u << j)) dst[n_dst++] = ch->gath[j];
+  const uint64_t vecs = ch->count / 8;
+  const uint64_t per = (vecs + plan.part_count - 1) / plan.part_count;
+  const uint64_t lo = per * (uint64_t)plan.part_index * 8;
+  const uint64_t hi = min(lo + per * 8, ch->count);
+  const float scale = plan.scale;
+  for (uint64_t i = lo + tid * 8; i < hi; i += nthreads * 8) {
+    float acc[8], v[8];
+    load8(src[0], i, acc);
+    for (int s = 1; s < n_src; ++s) {
+      load8(src[s], i, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += v[q];
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] *= scale;
+    for (int n = 0; n < n_push; ++n) {
+      float* mb = ch->mbox[plan.push_rank[n]];
+      if (plan.push_accum[n]) {
+        load8(mb, i, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] += acc[q];
+        store8(mb, i, v);
+      } else {
+        store8(mb, i, acc);
+      }
+    }
+    for (int d = 0; d < n_dst; ++d) store8(dst[d], i, acc);
+  }
+}
+
+// Two-shot, second half: every share has landed in the local gather buffer; apply it.
+__device__ inline void data_apply_gathered(const DevChannel* ch, uint64_t tid, uint64_t nthreads) {
+  const float* g_in = ch->gath[ch->cfg.rank];
+  const float lr = ch->hyper[HP_LR], mu = ch->hyper[HP_MOMENTUM], wd = ch->hyper[HP_WD];
+  const float nesterov = ch->hyper[HP_NESTEROV], gscale = ch->hyper[HP_GRAD_SCALE];
+  for (uint64_t i = tid * 8; i < ch->count; i += nthreads * 8) {
+    float g[8];
+    load8(g_in, i, g);
+    apply8(ch, i, g, lr, mu, wd, nesterov, gscale);
+  }
+}
+
+// Tell every participant that this rank's share of the round is in its gather buffer.
+__device__ inline void gather_signal(const DevChannel* ch) {
+  const Plan& plan = ch->plan;
+  for (int j = 0; j < ch->cfg.world; ++j)
+    if (plan.fresh_mask & (1u << j)) DevEnv::st_rel64(&ch->view.ctl[j]->gather_round[ch->cfg.rank], plan.round);
+}
+
+// Wait (bounded) until every participant's share of the round has arrived here.
+__device__ inline bool gather_wait(const DevChannel* ch) {
+  const Plan& plan = ch->plan;
+  ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
+  const uint64_t t0 = DevEnv::now_ns();
+  for (int j = 0; j < ch->cfg.world; ++j) {
+    if (!(plan.fresh_mask & (1u << j))) continue;
+    while (DevEnv::ld_acq64(&me->gather_round[j]) < plan.round) {
+      if (DevEnv::now_ns() - t0 > ch->cfg.timeout_ns) return false;
+      DevEnv::pause();
+    }
+  }
+  return true;
+}
+
 __device__ inline void data_drain(const DevChannel* ch, uint64_t tid, uint64_t nthreads) {
   const float* mb = ch->mbox[ch->cfg.rank];
   const float lr = ch->hyper[HP_LR], mu = ch->hyper[HP_MOMENTUM], wd = ch->hyper[HP_WD];
@@ -160,7 +249,10 @@ __device__ inline void data_zero_out(const DevChannel* ch, uint64_t tid, uint64_
 
 __device__ inline void data_phase(const DevChannel* ch, uint64_t tid, uint64_t nthreads) {
   const int role = ch->plan.role;
-  if (role == ROLE_PARTICIPANT) {
+  if (role == ROLE_PARTICIPANT && ch->plan.two_shot) {
+    if (ch->slot_bf16) data_reduce_scatter<__nv_bfloat16>(ch, tid, nthreads);
+    else data_reduce_scatter<float>(ch, tid, nthreads);
+  } else if (role == ROLE_PARTICIPANT) {
     if (ch->slot_bf16) data_participant<__nv_bfloat16>(ch, tid, nthreads);
     else data_participant<float>(ch, tid, nthreads);
   } else if (role == ROLE_DRAIN) {

@@ -50,10 +50,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `kSpinLimit` polls, raises *abort_flag (shared)
 // so that every role of the CTA leaves its loop, and returns false.
-constexpr uint32_t kSpinLimit = 1u << 24;
+// After a few immediate retries the waiter backs off with a short sleep: a warp that spins at full rate
+// takes issue slots from the epilogue warps that share its scheduler.
+constexpr uint32_t kSpinLimit = 1u << 23;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (it >= 4) __nanosleep(48);
     if ((it & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;

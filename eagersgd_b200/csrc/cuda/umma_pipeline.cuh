@@ -10,12 +10,19 @@
 //                sum of squares of the stored tile are taken from shared memory and
 //                flushed with one atomic per column per CTA (batch-norm statistics)
 //
+// B-resident mode: when a CTA keeps one column range for all of its tiles and the whole K
+// extent of B for that range fits beside four A stages, B is loaded ONCE and stays in shared
+// memory; the ring then carries A only (up to eight stages).  Short-K, long-M problems (1x1
+// convolutions over early feature maps, 3x3 over 64 channels) otherwise re-read B from L2 for
+// every tile, which is a quarter of their L2 traffic.
+//
 // A tile is 128 rows x BN columns; a k-block is 64 bf16 (one 128-byte swizzle row).
 // Every mbarrier wait is bounded; on expiry the CTA raises an error flag, lets the
 // copies in flight land, frees its tensor memory and returns.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "sm100_primitives.cuh"
 
 namespace umma {
@@ -28,7 +35,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int PANEL_BYTES = BM * 64 * 2;     // one 128 x 64 bf16 output panel
 constexpr int NUM_EPI_THREADS = 256;         // eight epilogue warps
 constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
-constexpr int NUM_PANEL_BUFS = 4;            // output staging ring: up to 3 TMA stores drain while the next panel is built
+constexpr int NUM_PANEL_BUFS = 4;            // output staging ring (the one-barrier hand-over below needs four)
 
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ATOMIC = 2 };
 
@@ -41,6 +48,7 @@ struct Epilogue {
   float* col_sqsum;
   int* error_flag;
   uint32_t tx_bytes;       // bytes the loads of one k-block deliver (0: full A and B stage tiles)
+  uint32_t tx_bytes_a;     // bytes of the A loads alone (B-resident mode; 0: a full A stage tile)
 };
 
 template <int BN>
@@ -48,16 +56,65 @@ struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGES = BN == 256 ? 3 : (BN == 128 ? 5 : 6);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + NUM_PANEL_BUFS * PANEL_BYTES + 1024 + 256;
+  static constexpr int MAX_STAGES = 8;                 // A-only ring of the B-resident mode
+  static constexpr int STAGE_AREA = 161 * 1024;        // operand stages (ring, or A ring + resident B)
+  static constexpr int SMEM_BYTES = 1024 + STAGE_AREA + NUM_PANEL_BUFS * PANEL_BYTES + 512;
+  static_assert(STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) <= STAGE_AREA, "ring does not fit");
+  static_assert(SMEM_BYTES <= 227 * 1024, "over the shared-memory limit of a CTA");
+  // k-blocks of B that may stay resident: four A stages must still fit
+  static constexpr int MAX_RES_KB = (STAGE_AREA - 4 * A_STAGE_BYTES) / B_STAGE_BYTES;
 };
+
+// ESGD_GEMM_B_RESIDENT=0 in the environment turns the B-resident mode off (for A/B timing).
+inline bool resident_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ESGD_GEMM_B_RESIDENT");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// 32 accumulator columns of one row -> bf16 -> four 16-byte chunks of the swizzled staging panel.
+// kPlain leaves out the bias / ReLU code altogether: as run-time options they would be predicated
+// instructions that still take issue slots in the common case that uses neither.
+template <bool kPlain>
+__device__ __forceinline__ void pack_row_to_panel(const uint32_t* r, uint8_t* panel, int row, int half, int col0,
+                                                  const Epilogue& ep) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+    if (!kPlain) {
+      if (ep.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col0 + g * 8 + j < ep.n_total) v[j] += __ldg(ep.bias + col0 + g * 8 + j);
+      }
+      if (ep.relu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
+      }
+    }
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    const int chunk = half * 4 + g;          // 16-byte chunk within the 128-byte row
+    *reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
+  }
+}
 
 // Problem policy requirements (all __device__ const):
 //   static constexpr int BN; static constexpr bool A_MN, B_MN, kZeroStages;
 //   struct Tile { int kb0, kb1, n0; ... };
 //   bool tile(int it, Tile&)                       enumerate this CTA's tiles
 //   void load(const Tile&, int kb, uint8_t* a, uint8_t* b, uint64_t* bar)
+//   void load_a(...a, bar) / load_b(...b, bar)     the two halves of load(); int res_kb (0: B not resident)
 //   void store_panel(const Tile&, int panel, const void* smem)   TMA store of a 128x64 bf16 panel
 //   bool row_valid(const Tile&, int row)           row is a real output (statistics mask)
+//   int valid_prefix(const Tile&)                  n if exactly rows [0, n) are real outputs, -1 if irregular
 //   void* row_ptr(const Tile&, int row)            fp32 output row pointer (direct modes), or nullptr
 template <class P>
 __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
@@ -66,21 +123,26 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int res_kb = prob.res_kb;            // > 0: B-resident mode
+  const int nstages = res_kb > 0 ? min(C::MAX_STAGES, (C::STAGE_AREA - res_kb * C::B_STAGE_BYTES) / A_STAGE_BYTES)
+                                 : STAGES;
   uint8_t* sA = smem;
-  uint8_t* sB = sA + STAGES * A_STAGE_BYTES;
-  uint8_t* sC = sB + STAGES * C::B_STAGE_BYTES;
+  uint8_t* sB = sA + nstages * A_STAGE_BYTES;
+  uint8_t* sC = smem + C::STAGE_AREA;
   uint64_t* full = reinterpret_cast<uint64_t*>(sC + NUM_PANEL_BUFS * PANEL_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tfull = empty + STAGES;
+  uint64_t* empty = full + C::MAX_STAGES;
+  uint64_t* tfull = empty + C::MAX_STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* bres = tempty + 2;               // the resident B tiles have landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < C::MAX_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], NUM_EPI_THREADS / 32); }
+    mbar_init(bres, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -107,12 +169,23 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       uint32_t phase = 0;
       bool ok = true;
       typename P::Tile t;
+      if (res_kb > 0 && prob.tile(0, t)) {
+        mbar_expect_tx(bres, (uint32_t)(res_kb * C::B_STAGE_BYTES));
+        for (int kb = 0; kb < res_kb; ++kb) prob.load_b(t, kb, sB + kb * C::B_STAGE_BYTES, bres);
+      }
+      const uint32_t tx_a = ep.tx_bytes_a ? ep.tx_bytes_a : (uint32_t)A_STAGE_BYTES;
+      const uint32_t tx_ab = ep.tx_bytes ? ep.tx_bytes : (uint32_t)(A_STAGE_BYTES + C::B_STAGE_BYTES);
       for (int it = 0; ok && prob.tile(it, t); ++it) {
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[stage], ep.tx_bytes ? ep.tx_bytes : (uint32_t)(A_STAGE_BYTES + C::B_STAGE_BYTES));
-          prob.load(t, kb, sA + stage * A_STAGE_BYTES, sB + stage * C::B_STAGE_BYTES, &full[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (res_kb > 0) {
+            mbar_expect_tx(&full[stage], tx_a);
+            prob.load_a(t, kb, sA + stage * A_STAGE_BYTES, &full[stage]);
+          } else {
+            mbar_expect_tx(&full[stage], tx_ab);
+            prob.load(t, kb, sA + stage * A_STAGE_BYTES, sB + stage * C::B_STAGE_BYTES, &full[stage]);
+          }
+          if (++stage == nstages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -124,6 +197,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       typename P::Tile t;
+      if (res_kb > 0 && prob.tile(0, t)) ok = mbar_wait(bres, 0u, abort_flag);
       for (int it = 0; ok && prob.tile(it, t); ++it) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
@@ -132,7 +206,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * C::B_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + (res_kb > 0 ? kb : stage) * C::B_STAGE_BYTES);
 #pragma unroll
           for (int j = 0; j < BK / 16; ++j) {
             const uint64_t adesc = P::A_MN ? umma_smem_desc(a_addr + j * 2048, 8192, 1024)
@@ -142,7 +216,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
             umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > t.kb0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == nstages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&tfull[acc]);
@@ -161,12 +235,12 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;                            // staging panel buffer in use (ring)
-    int stores_issued = 0;                  // bulk-store groups committed so far (thread et == 0)
     // statistics: thread (cp = et % 32, rg = et / 32) covers columns 2cp, 2cp+1 of each panel, rows 16rg..+16
     float st_sum[BN / 64][2], st_sq[BN / 64][2];
 #pragma unroll
     for (int pnl = 0; pnl < BN / 64; ++pnl) { st_sum[pnl][0] = st_sum[pnl][1] = st_sq[pnl][0] = st_sq[pnl][1] = 0.f; }
     int stats_n0 = -1;
+    const bool plain = ep.bias == nullptr && !ep.relu;
     bool ok = true;
     typename P::Tile t;
     for (int it = 0; ok && prob.tile(it, t); ++it) {
@@ -176,6 +250,18 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * 32);
       if (ep.out_mode == OUT_BF16) {
         const int npan = min(BN / 64, (ep.n_total - t.n0 + 63) / 64);   // uniform across the CTA
+        uint32_t row_mask = 0xffffu;          // validity of this thread's 16 statistics rows, once per tile
+        if (ep.col_sum != nullptr) {
+          const int prefix = prob.valid_prefix(t);      // rows [0, prefix) are the real outputs, or -1
+          if (prefix >= 0) {
+            const int mine = min(16, max(0, prefix - (et >> 5) * 16));
+            row_mask = (1u << mine) - 1u;
+          } else {
+            row_mask = 0u;
+            for (int rr = 0; rr < 16; ++rr)
+              if (prob.row_valid(t, (et >> 5) * 16 + rr)) row_mask |= 1u << rr;
+          }
+        }
         uint32_t rbuf[2][32];
         tmem_ld_32x32b_x32(t_row, rbuf[0]);
 #pragma unroll
@@ -185,52 +271,34 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
             if (pnl + 1 < npan)   // the next panel's accumulators travel while this one is converted
               tmem_ld_32x32b_x32(t_row + (uint32_t)((pnl + 1) * 64), rbuf[(pnl + 1) & 1]);
             uint8_t* panel = sC + buf * PANEL_BYTES;
-            // the store that used this buffer NUM_PANEL_BUFS panels ago must have read it
-            if (et == 0 && stores_issued >= NUM_PANEL_BUFS) tma_store_wait_read<NUM_PANEL_BUFS - 1>();
-            named_barrier_sync(1, NUM_EPI_THREADS);    // the buffer is free for everyone
-            const uint32_t* r = rbuf[pnl & 1];
+            // This buffer was last read by the store issued NUM_PANEL_BUFS panels ago; thread 0 waited for
+            // that read before it arrived at the previous panel's barrier (see below), so it is free.
             const int col0 = t.n0 + pnl * 64 + half * 32;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
-              if (ep.bias != nullptr) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (col0 + g * 8 + j < ep.n_total) v[j] += __ldg(ep.bias + col0 + g * 8 + j);
-              }
-              if (ep.relu) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
-              }
-              uint4 pk;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-              const int chunk = half * 4 + g;          // 16-byte chunk within the 128-byte row
-              *reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
-            }
+            if (plain) pack_row_to_panel<true>(rbuf[pnl & 1], panel, row, half, col0, ep);
+            else pack_row_to_panel<false>(rbuf[pnl & 1], panel, row, half, col0, ep);
             fence_proxy_async();
             named_barrier_sync(1, NUM_EPI_THREADS);    // the panel is complete and visible to the TMA engine
             if (et == 0) {
               prob.store_panel(t, pnl, panel);
               tma_store_commit();
-              stores_issued++;
+              // One barrier per panel: before thread 0 reaches the NEXT panel's barrier it makes sure that all
+              // but the two newest stores have read their buffers, so after that barrier everyone may overwrite
+              // the buffer used three panels ago -- the one the panel after next needs.
+              tma_store_wait_read<2>();
             }
             if (ep.col_sum != nullptr) {
+              // thread (cp, rg): columns 2cp, 2cp+1 of the panel, rows 16rg .. 16rg+15, read back as stored
               const int cp = et & 31, rg = et >> 5;
+              const uint8_t* colp = panel + (cp & 3) * 4;
+              const int chunk = cp >> 2;
               float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
-#pragma unroll 4
+#pragma unroll
               for (int rr = 0; rr < 16; ++rr) {
                 const int r_ = rg * 16 + rr;
-                if (!prob.row_valid(t, r_)) continue;
-                const int chunk = cp >> 2;
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(panel + r_ * 128 + ((chunk ^ (r_ & 7)) << 4) +
-                                                                      (cp & 3) * 4);
-                __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&w);
-                float2 f = __bfloat1622float2(hv);
-                s0 += f.x; s1 += f.y; q0 += f.x * f.x; q1 += f.y * f.y;
+                uint32_t w = *reinterpret_cast<const uint32_t*>(colp + r_ * 128 + ((chunk ^ (r_ & 7)) << 4));
+                if (!((row_mask >> rr) & 1u)) w = 0u;        // rows outside the tensor count as zeros
+                const float f0 = __uint_as_float(w << 16), f1 = __uint_as_float(w & 0xffff0000u);
+                s0 += f0; s1 += f1; q0 = fmaf(f0, f0, q0); q1 = fmaf(f1, f1, q1);
               }
               st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
             }

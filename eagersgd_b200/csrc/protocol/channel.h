@@ -52,7 +52,8 @@ enum StatusBits : uint32_t {
   ST_TIMEOUT_DONE = 1u << 3,      // previous round never completed
   ST_DESC_LAPPED = 1u << 4,       // descriptor ring overwritten before it was read
   ST_MBOX_NOT_EMPTY = 1u << 5,    // participant found data in its own mailbox (protocol error)
-  ST_TIMEOUT_SLOT = 1u << 6       // publish slot still being read
+  ST_TIMEOUT_SLOT = 1u << 6,      // publish slot still being read
+  ST_TIMEOUT_GATHER = 1u << 7     // two-shot reduction: a participant's share never arrived
 };
 
 struct alignas(128) RoundDesc {
@@ -93,6 +94,8 @@ struct alignas(128) ChannelCtl {
   alignas(128) uint32_t done_count[kDescRing];  // finishers; only the activator's copy is used
   alignas(128) uint32_t mbox_lock;        // 0 free, else 1 + holder
   uint32_t mbox_count;                    // rounds accumulated since the last drain
+  alignas(128) uint64_t gather_round[kMaxRanks];  // [j] pushed by participant j: its share of that round's result
+                                                  // has landed in this rank's gather buffer (two-shot reduction)
   alignas(128) RoundDesc desc[kDescRing];
   // ---- local only (never touched by peers) ----
   alignas(128) uint64_t local_step;       // posts made so far by the owning rank
@@ -120,6 +123,8 @@ struct alignas(16) Plan {
   int32_t activator;
   int32_t holds_own_lock;         // drain: own mailbox lock is held and must be released
   int32_t is_sync;
+  uint32_t fresh_mask;            // the participants (bit per rank)
+  int32_t two_shot;               // data phase split into reduce-scatter and gather (set by the device front end)
   uint64_t round;
   float scale;                    // 1/contributors or 1/world
   float drain_rounds;             // number of rounds summed in the mailbox (drain)

@@ -170,6 +170,8 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
   plan->n_src = plan->n_push = 0;
   plan->part_index = 0;
   plan->part_count = 1;
+  plan->fresh_mask = 0;
+  plan->two_shot = 0;
   plan->activator = i;
   plan->holds_own_lock = 0;
   plan->round = k;
@@ -216,6 +218,7 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
     plan->role = ROLE_PARTICIPANT;
     plan->activator = (int32_t)d->activator;
     plan->part_count = (int32_t)d->n_fresh;
+    plan->fresh_mask = d->fresh_mask;
     plan->part_index = popc32(d->fresh_mask & (bit_of(i) - 1u));
     plan->scale = cfg.average_world == 1 ? 1.0f / (float)P
                   : cfg.average_world == 2 ? 1.0f : 1.0f / (float)d->n_contrib;
@@ -319,6 +322,8 @@ ESGD_T void ctl_flush(const ChannelView& v, const StepConfig& cfg, Plan* plan) {
   plan->role = ROLE_ABORT;
   plan->n_src = plan->n_push = 0;
   plan->holds_own_lock = 0;
+  plan->two_shot = 0;
+  plan->fresh_mask = 0;
   plan->round = E::ld_acq64(&me->latest_round);
   while (E::ld_acq64(&me->round_done) < plan->round) {
     if (E::now_ns() - t0 > cfg.timeout_ns) { me->status |= ST_TIMEOUT_DONE; return; }

@@ -62,8 +62,9 @@ class EagerOptimizer:
                  limiter: int = 32, seed: int = 6545343, bucket_mb: float = 25.0,
                  average: str = "contributors", include_stale: bool = True, fused: Optional[bool] = None,
                  slot_dtype: Optional[torch.dtype] = None, overlap: bool = True, timeout_s: float = 30.0,
-                 grace_us: float = 50.0, max_blocks: int = 592):
+                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 18):
         self.optimizer = optimizer
+        self.two_shot_min = two_shot_min   # bucket elements from which a round is reduced in two shots (None: never)
         self.group = group if group is not None else init_group()
         self.mode, self.limiter, self.seed = mode, limiter, seed
         self.average, self.include_stale = average, include_stale
@@ -176,7 +177,8 @@ class EagerOptimizer:
                                       slot_dtype=self.slot_dtype, mode=self.mode, limiter=self.limiter,
                                       seed=self.seed, average=self.average,
                                       include_stale=self.include_stale, timeout_s=self.timeout_s,
-                                      grace_us=self.grace_us, hyper=b.hyper, max_blocks=self.max_blocks, **kw)
+                                      grace_us=self.grace_us, hyper=b.hyper, max_blocks=self.max_blocks,
+                                      two_shot_min=self.two_shot_min, **kw)
             self._refresh_hyper(b, force=True)
         torch.cuda.synchronize(self.device)
         g.barrier()

@@ -20,6 +20,7 @@ STATUS_BITS = {
     1 << 4: "round descriptor overwritten before it was read",
     1 << 5: "participant found data in its own mailbox",
     1 << 6: "timeout waiting for a publish slot to be released",
+    1 << 7: "timeout waiting for a participant's share of the reduced vector (two-shot reduction)",
 }
 
 
@@ -50,13 +51,14 @@ class StepInfo(C.Structure):
 
 class ChannelDesc(C.Structure):
     _fields_ = [("ctl", C.c_void_p * MAX_RANKS), ("slot0", C.c_void_p * MAX_RANKS),
-                ("slot1", C.c_void_p * MAX_RANKS), ("mbox", C.c_void_p * MAX_RANKS)] + \
+                ("slot1", C.c_void_p * MAX_RANKS), ("mbox", C.c_void_p * MAX_RANKS),
+                ("gath", C.c_void_p * MAX_RANKS)] + \
                [(n, C.c_int32) for n in
                 "rank world base_mode include_stale average home slot_bf16 grad_in_bf16".split()] + \
                [("limiter", C.c_int64)] + \
                [(n, C.c_uint64) for n in "seed timeout_ns grace_ns count".split()] + \
                [(n, C.c_void_p) for n in "grad_in w32 mom w16 out".split()] + \
-               [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p)]
+               [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p), ("two_shot_min", C.c_uint64)]
 
 
 STAT_NAMES = ("local_step", "participated", "absent", "activated", "sync_rounds", "dropped_grads",
@@ -98,7 +100,7 @@ def cuda():
         lib.esgd_dev_channel_bytes.restype = C.c_uint64
         lib.esgd_dev_ctl_bytes.restype = C.c_uint64
         lib.esgd_channel_configure.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
-        lib.esgd_channel_step.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
+        lib.esgd_channel_step.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_void_p]
         lib.esgd_channel_flush.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
         lib.esgd_emulated_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         lib.esgd_spin.argtypes = [C.c_uint64, C.c_void_p]

@@ -27,7 +27,7 @@ from .group import init as init_group, finalize
 from .nvlink_channel import NvlinkChannel, create_arenas
 
 
-def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused):
+def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False):
     dev = group.device
     esz = 2 if dtype == torch.bfloat16 else 4
     count = max(nbytes // esz // 8 * 8, 8)
@@ -44,7 +44,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused):
         else:
             kw = dict(out=torch.empty(count, dtype=dtype, device=dev))
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=dtype, mode=mode, limiter=-1,
-                           average="world", timeout_s=20.0, grace_us=0.0, **kw)
+                           average="world", timeout_s=20.0, grace_us=0.0,
+                           two_shot_min=None if one_shot else 1 << 18, **kw)
     buf = grad.clone()
     times = []
     for it in range(iters + 3):
@@ -80,7 +81,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused):
     mean_ms, max_ms = float(tsum) / group.world, float(tmax)
     res = dict(mode=mode, bytes=count * esz, dtype=str(dtype).replace("torch.", ""), world=group.world, late=late,
                late_ms=late_ms, fused_update=bool(fused and mode != "nccl"), mean_latency_us=mean_ms * 1e3,
-               max_latency_us=max_ms * 1e3, status=status)
+               max_latency_us=max_ms * 1e3, status=status,
+               two_shot=bool(ch is not None and ch.two_shot))
     if mode in ("sync", "nccl") and late == 0:
         res["bus_gbs"] = 2.0 * (group.world - 1) / max(group.world, 1) * count * esz / (max_ms * 1e-3) / 1e9
     return res
@@ -95,12 +97,14 @@ def main(argv=None):
     ap.add_argument("--late-ms", type=float, default=10.0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fused", action="store_true", help="include the fused momentum-SGD update in our kernels")
+    ap.add_argument("--one-shot", action="store_true", help="never split the reduction into reduce-scatter + gather")
     args = ap.parse_args(argv)
     group = init_group()
     for size in [int(s) for s in args.sizes.split(",")]:
         for dt in args.dtypes.split(","):
             for mode in args.modes.split(","):
-                r = run_case(group, size, getattr(torch, dt), mode, args.late, args.late_ms, args.iters, 1234, args.fused)
+                r = run_case(group, size, getattr(torch, dt), mode, args.late, args.late_ms, args.iters, 1234, args.fused,
+                             args.one_shot)
                 if group.rank == 0:
                     print(json.dumps(r), flush=True)
     finalize()

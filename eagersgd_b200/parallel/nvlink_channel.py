@@ -1,7 +1,7 @@
 """NVLink backend of the partial allreduce: peer-mapped arenas + sm_100a kernels.
 
 Each rank allocates one arena per channel with ``cudaMalloc``
-(``[control block | publish slot 0 | publish slot 1 | fp32 mailbox]``), exports
+(``[control block | publish slot 0 | publish slot 1 | fp32 mailbox | fp32 gather buffer]``), exports
 it with a CUDA IPC handle and maps every peer's arena, so the kernels read and
 write the other GPUs' memory directly over NVLink 5 / NVSwitch.  This replaces
 the reference's buffers, pools and MPI transport (fflib2 src/ffbuffer.c,
@@ -21,6 +21,7 @@ from . import _native as N
 _MODES = {"solo": N.MODE_SOLO, "majority": N.MODE_MAJORITY, "sync": N.MODE_SYNC}
 _AVG = {"contributors": N.AVG_CONTRIBUTORS, "world": N.AVG_WORLD, "sum": N.AVG_SUM}
 HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
+TWO_SHOT_MIN = 1 << 18  # elements from which a round with several reducers is reduced in two shots
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -36,7 +37,8 @@ class ArenaLayout:
         self.slot0 = _align(int(N.cuda().esgd_dev_ctl_bytes()))
         self.slot1 = self.slot0 + _align(count * esz)
         self.mbox = self.slot1 + _align(count * esz)
-        self.total = self.mbox + _align(count * 4)
+        self.gath = self.mbox + _align(count * 4)
+        self.total = self.gath + _align(count * 4)
 
 
 class Arena:
@@ -69,6 +71,10 @@ class NvlinkChannel:
     ``grad_in`` is the flat gradient the backward pass writes.  With ``w32``/
     ``mom`` (and optionally ``w16``) the reduction is fused with the momentum-SGD
     update; otherwise the averaged gradient is written to ``out``.
+
+    Channels of at least ``two_shot_min`` elements reduce in two shots when a round
+    has several participants (each sums its share and stores it into every
+    participant's gather buffer); ``two_shot_min=None`` keeps the one-shot form.
     """
 
     def __init__(self, count: int, rank: int, world: int, bases: List[int], device: torch.device,
@@ -77,7 +83,8 @@ class NvlinkChannel:
                  include_stale: bool = True, timeout_s: float = 20.0, grace_us: float = 50.0, home: int = 0,
                  w32: Optional[torch.Tensor] = None, mom: Optional[torch.Tensor] = None,
                  w16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 hyper: Optional[torch.Tensor] = None, max_blocks: int = 592):
+                 hyper: Optional[torch.Tensor] = None, max_blocks: int = 592,
+                 two_shot_min: Optional[int] = TWO_SHOT_MIN):
         self.lib = N.cuda()
         self.count, self.rank, self.world, self.device = count, rank, world, device
         self.max_blocks = max_blocks
@@ -97,6 +104,9 @@ class NvlinkChannel:
             d.slot0[j] = bases[j] + L.slot0
             d.slot1[j] = bases[j] + L.slot1
             d.mbox[j] = bases[j] + L.mbox
+            d.gath[j] = bases[j] + L.gath if two_shot_min is not None else None
+        d.two_shot_min = int(two_shot_min) if two_shot_min is not None else 0
+        self.two_shot = int(two_shot_min is not None and world > 1 and count >= two_shot_min)
         d.rank, d.world, d.base_mode = rank, world, _MODES[mode]
         d.include_stale, d.average, d.home = int(include_stale), _AVG[average], home
         d.slot_bf16 = int(slot_dtype == torch.bfloat16)
@@ -123,7 +133,8 @@ class NvlinkChannel:
     def step(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         """Enqueue pack + control + reduce/update for one step on ``stream``."""
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
+        N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, self.two_shot,
+                                                s.cuda_stream),
                      "partial allreduce launch")
 
     def flush(self, stream: Optional[torch.cuda.Stream] = None) -> None:

@@ -22,6 +22,8 @@ CASES = [  # n, cin, h, w, cout, k, stride, pad
     (2, 512, 14, 14, 512, 3, 2, 1),
     (1, 64, 130, 130, 64, 3, 1, 1),
     (2, 64, 20, 20, 64, 5, 1, 2),
+    (16, 64, 56, 56, 64, 3, 1, 1),     # enough tiles per CTA for the filter bank to stay in shared memory
+    (20, 64, 112, 112, 64, 3, 2, 1),   # the same with stride 2
 ]
 
 

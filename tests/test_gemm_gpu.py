@@ -91,3 +91,25 @@ def test_gemm_stats_tails_and_many_tiles(M, N):
     assert torch.allclose(c.float(), ref, rtol=2e-2, atol=0.1)
     assert torch.allclose(s, c.float().sum(0), rtol=2e-3, atol=1.0)
     assert torch.allclose(s2, (c.float() ** 2).sum(0), rtol=2e-3, atol=10.0)
+
+
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True)])
+@pytest.mark.parametrize("M,N,K,stats", [(40000, 256, 64, False), (40000, 64, 256, True), (45000, 128, 320, False),
+                                         (80000, 512, 128, True), (39000, 200, 136, False)])
+def test_gemm_resident_b_operand(M, N, K, stats, a_k, b_k):
+    """Long-M, short-K problems keep B in shared memory for all tiles of a CTA: same results as the
+    fp32 product, for every operand storage order, with and without the statistics epilogue."""
+    from eagersgd_b200.ops.gemm import gemm, check_error
+    torch.manual_seed(M + N + K)
+    a = _rand((M, K) if a_k else (K, M), 0.5)
+    b = _rand((N, K) if b_k else (K, N), 0.5)
+    s = torch.zeros(N, device=DEV) if stats else None
+    s2 = torch.zeros(N, device=DEV) if stats else None
+    c = gemm(a, b, a_kmajor=a_k, b_kmajor=b_k, col_sum=s, col_sqsum=s2)
+    torch.cuda.synchronize()
+    check_error(a.device)
+    ref = _ref(a, b, a_k, b_k)
+    assert (c.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-2
+    if stats:
+        assert torch.allclose(s, c.float().sum(0), rtol=2e-3, atol=2.0)
+        assert torch.allclose(s2, (c.float() ** 2).sum(0), rtol=2e-3, atol=20.0)

@@ -172,3 +172,57 @@ def test_missing_rank_is_detected_by_bounded_wait():
         assert ok_first and alive == 24.0
         if r != world - 1:
             assert status != 0     # arrival or round timeout, reported instead of hanging
+
+
+def _two_shot_vs_nccl(rank, world, slot_bf16):
+    """Random gradients through the two-shot data phase (reduce-scatter by peer loads, gather by peer stores)
+    against NCCL's allreduce of the same tensors, plus the one-shot form of the same channel."""
+    es, group = _setup(rank, world)
+    import torch.distributed as dist
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas
+    dev = group.device
+    count = (1 << 20) + 8 * 3
+    sdt = torch.bfloat16 if slot_bf16 else torch.float32
+    outs, arenas, stats, flags = [], [], [], []
+    torch.manual_seed(100 + rank)
+    grads = [torch.randn(count, device=dev) for _ in range(3)]
+    if slot_bf16:
+        grads = [g.to(torch.bfloat16).float() for g in grads]
+    for tsm in (None, 1 << 18):
+        arena, bases = create_arenas(count, sdt, group.rank, group.world, group.exchange)
+        grad = torch.zeros(count, device=dev)
+        out = torch.zeros(count, device=dev)
+        ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=sdt, mode="sync", limiter=-1,
+                           average="world", out=out, timeout_s=5.0, grace_us=0.0, two_shot_min=tsm)
+        res = []
+        for g in grads:
+            grad.copy_(g)
+            ch.step()
+            torch.cuda.synchronize()
+            res.append(out.clone())
+        outs.append(res)
+        stats.append(ch.stats()["status"])
+        flags.append(ch.two_shot)
+        group.barrier()
+        arenas.append(arena)
+    err = 0.0
+    for k, g in enumerate(grads):
+        ref = g.clone()
+        dist.all_reduce(ref)
+        ref /= world
+        err = max(err, (outs[1][k] - ref).abs().max().item())
+    same = all(torch.equal(a, b) for a, b in zip(outs[0], outs[1]))
+    group.barrier()
+    for a in arenas:
+        a.free()
+    es.finalize()
+    return err, same, stats, flags
+
+
+@pytest.mark.parametrize("slot_bf16", [False, True])
+def test_two_shot_matches_nccl_and_one_shot(slot_bf16):
+    for err, same, stats, flags in run_ranks(_two_shot_vs_nccl, _world(), (slot_bf16,)):
+        assert flags == [0, 1]
+        assert stats == [0, 0]
+        assert same, "two-shot and one-shot reductions differ"
+        assert err < 2e-6

@@ -196,3 +196,80 @@ def test_optimizer_wrapper_generic_inner_optimizer():
     for p1, p2 in zip(m1.parameters(), m2.parameters()):
         assert torch.allclose(p1, p2, rtol=1e-5, atol=1e-6)
     o2.close()
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("slot_dtype,fused", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+def test_two_shot_reduction_is_bit_identical_to_one_shot(world, slot_dtype, fused):
+    """Reduce-scatter by peer loads + gather by peer stores gives the very bits of the one-shot reduction:
+    averaged gradients, and fp32 master weights / momentum / bf16 weights after fused updates."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    count = 8 * 1237          # not a multiple of the number of participants
+    gdt = torch.bfloat16 if slot_dtype == torch.bfloat16 else torch.float32
+    worlds = [EmulatedWorld(world, count, _dev(), slot_dtype=slot_dtype, grad_dtype=gdt, fused=fused, mode="sync",
+                            limiter=-1, average="contributors", timeout_s=2.0, two_shot_min=tsm)
+              for tsm in (None, 0)]
+    try:
+        torch.manual_seed(world)
+        for w in worlds:
+            w.hyper[:5] = torch.tensor([0.1, 0.9, 1e-4, 0.0, 1.0])
+            if fused:
+                for r in range(world):
+                    w.w32[r].copy_(torch.linspace(-1, 1, count))
+        for k in range(4):
+            gs = [torch.randn(count, device=_dev()).to(gdt) for _ in range(world)]
+            for w in worlds:
+                for r in range(world):
+                    w.grads[r].copy_(gs[r])
+                w.step()
+            torch.cuda.synchronize()
+            a, b = worlds
+            for r in range(world):
+                if fused:
+                    assert torch.equal(a.w32[r], b.w32[r]) and torch.equal(a.mom[r], b.mom[r])
+                    assert torch.equal(a.w16[r], b.w16[r]) and torch.equal(b.w32[r], b.w32[0])
+                else:
+                    assert torch.equal(a.outs[r], b.outs[r]), (k, r)
+                    ref = torch.stack([g.float() for g in gs]).sum(0) / world
+                    assert torch.allclose(b.outs[r], ref, rtol=1e-5, atol=1e-6)
+        for w in worlds:
+            assert all(c.stats()["status"] == 0 for c in w.channels)
+    finally:
+        for w in worlds:
+            w.close()
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+def test_two_shot_eager_rounds_replicas_agree(mode):
+    """Two-shot data phase under random late arrivals: participants change from round to round, absent ranks
+    collect their mailbox, and every rank ends with the same accumulated total."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    world, count, steps = 6, 8 * 511, 40
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode=mode, limiter=7, average="sum",
+                      timeout_s=2.0, grace_us=0.0, two_shot_min=0)
+    rng = random.Random(17 + len(mode))
+    ramp = torch.arange(count, device=_dev(), dtype=torch.float32) % 13
+    applied = [torch.zeros(count, dtype=torch.float64, device=_dev()) for _ in range(world)]
+    try:
+        for k in range(1, steps + 1):
+            for r in range(world):
+                w.grads[r].copy_(ramp + float((r + 1) * 100 + k))
+            w.step(delays_us=[rng.choice([0, 0, 0, 30, 300]) for _ in range(world)])
+            torch.cuda.synchronize()
+            for r in range(world):
+                applied[r] += w.outs[r].double()
+        w.step(flush=True)
+        torch.cuda.synchronize()
+        for r in range(world):
+            applied[r] += w.outs[r].double()
+        for r in range(1, world):
+            assert torch.equal(applied[r], applied[0])
+        # every element saw the same number of gradients: (total - ramp * n) is constant over the vector
+        n_applied = (applied[0][1] - applied[0][0]).item()        # ramp[1] - ramp[0] = 1 per gradient
+        assert n_applied > 0
+        assert torch.allclose(applied[0] - ramp.double() * n_applied, (applied[0][0]).expand(count), rtol=0, atol=1e-6)
+        sts = [c.stats() for c in w.channels]
+        assert all(s["status"] == 0 for s in sts)
+        assert sum(s["participated"] for s in sts) > steps      # rounds with several participants happened
+    finally:
+        w.close()
