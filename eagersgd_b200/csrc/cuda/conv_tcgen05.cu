@@ -86,6 +86,7 @@ struct ConvProblem {
     return (t.w0 + BW <= Wo && t.h0 + BH <= Ho && t.i0 + BI <= N) ? BW * BH * BI : -1;
   }
   __device__ __forceinline__ void* row_ptr(const Tile&, int) const { return nullptr; }
+  __device__ __forceinline__ void load_res_panel(const Tile&, int, void*, uint64_t*) const {}
 };
 
 
@@ -137,6 +138,7 @@ struct ConvWgradProblem {
   __device__ __forceinline__ void store_panel(const Tile&, int, const void*) const {}
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < Cout; }
   __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, Cout - t.m0); }
+  __device__ __forceinline__ void load_res_panel(const Tile&, int, void*, uint64_t*) const {}
   __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
     const int k = t.m0 + row;
     return k < Cout ? (void*)(dw + ((size_t)k * (R * S) + t.tap) * Cin) : nullptr;
@@ -251,6 +253,7 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
     grid = total < sms ? total : sms;
   }
   ep.tx_bytes_a = (uint32_t)(p.BW * p.BH * p.BI * 128);
+  ep.residual = nullptr; ep.ldr = 0;
   ep.tx_bytes = ep.tx_bytes_a + (uint32_t)Cfg<BN>::B_STAGE_BYTES;
   conv_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
   esgd::count_launch();
@@ -287,7 +290,10 @@ int launch_wgrad(const ConvArgs& a, const void* dy, float* dw, int* error_flag, 
   p.n_tiles = (a.Cin + BN - 1) / BN;
   const int sms = sm_count();
   const int base_tiles = a.R * a.S * p.m_tiles * p.n_tiles;
-  int splits = (2 * sms + base_tiles - 1) / base_tiles;
+  // Every split adds its partial sums with atomics: two waves of tiles when the filter bank is small, one
+  // wave when it is large (the atomics of a 512 x 512 x 9 bank already outnumber its loads).
+  const int waves = base_tiles < 32 ? 2 : 1;
+  int splits = (waves * sms + base_tiles - 1) / base_tiles;
   if (splits < 1) splits = 1;
   if (splits > p.boxes_total) splits = p.boxes_total;
   p.boxes_per_split = (p.boxes_total + splits - 1) / splits;
@@ -312,7 +318,7 @@ int launch_wgrad(const ConvArgs& a, const void* dy, float* dw, int* error_flag, 
   ep.out_mode = OUT_F32_ATOMIC; ep.relu = 0; ep.n_total = a.Cin; ep.bias = nullptr;
   ep.col_sum = nullptr; ep.col_sqsum = nullptr; ep.error_flag = error_flag;
   ep.tx_bytes = (uint32_t)(p.BW * p.BH * 128 * (BM / 64 + BN / 64));
-  ep.tx_bytes_a = 0;
+  ep.tx_bytes_a = 0; ep.residual = nullptr; ep.ldr = 0;
   const int total = base_tiles * p.splits;
   const int grid = total < sms ? total : sms;
   conv_wgrad_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
@@ -361,7 +367,7 @@ int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int 
   Epilogue ep;
   ep.out_mode = OUT_BF16; ep.relu = relu; ep.n_total = Cout; ep.bias = nullptr;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
-  ep.tx_bytes = 0; ep.tx_bytes_a = 0;
+  ep.tx_bytes = 0; ep.tx_bytes_a = 0; ep.residual = nullptr; ep.ldr = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
   if (BN == 64) return launch<64>(a, ep, s);

@@ -22,7 +22,7 @@ template <int BN_, bool A_MN_, bool B_MN_>
 struct GemmProblem {
   static constexpr int BN = BN_;
   static constexpr bool A_MN = A_MN_, B_MN = B_MN_, kZeroStages = false;
-  CUtensorMap tmA, tmB, tmC;
+  CUtensorMap tmA, tmB, tmC, tmR;   // tmR: optional residual, same geometry as the output
   int M, N, K;
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
   int fixed_n;        // every CTA keeps one column range (needed for the per-CTA statistics flush)
@@ -79,6 +79,9 @@ struct GemmProblem {
   }
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < M; }
   __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, M - t.m0); }
+  __device__ __forceinline__ void load_res_panel(const Tile& t, int panel, void* smem, uint64_t* bar) const {
+    tma_load_2d(smem, &tmR, bar, t.n0 + panel * 64, t.m0);
+  }
   __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
     return (t.m0 + row < M) ? (void*)(c_f32 + (size_t)(t.m0 + row) * ldc) : nullptr;
   }
@@ -140,6 +143,13 @@ int launch(const GemmArgs& g, Epilogue ep, cudaStream_t stream) {
   } else {
     p.tmC = p.tmA;  // unused
   }
+  p.tmR = p.tmC;
+  if (ep.residual != nullptr) {
+    dims[0] = (uint64_t)g.N; dims[1] = (uint64_t)g.M; box[0] = 64; box[1] = 128;
+    strides[0] = (uint64_t)ep.ldr * 2;
+    r = esgd::make_tensormap_bf16(&p.tmR, ep.residual, 2, dims, strides, box, nullptr);
+    if (r != 0) return 4000 + r;
+  }
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.m_tiles = (g.M + BM - 1) / BM;
   p.n_tiles = (g.N + BN - 1) / BN;
@@ -190,16 +200,20 @@ extern "C" {
 // out_mode: 0 bf16, 1 fp32, 2 fp32 atomic accumulate (split-K; C must be zeroed by the caller).
 // Requirements: 16-byte aligned bases, lda/ldb/ldc multiples of 8, N multiple of 8.
 // col_sum / col_sqsum (bf16 output only) accumulate into caller-zeroed fp32 arrays of N.
+// residual (bf16 output only): a bf16 [M][N] tensor with row stride ldr (multiple of 8), added before rounding.
 int esgd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
                    int b_mn, int out_mode, const float* bias, int relu, int splits, float* col_sum,
-                   float* col_sqsum, int* error_flag, void* stream) {
+                   float* col_sqsum, const void* residual, int ldr, int* error_flag, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N % 8) || (lda % 8) || (ldb % 8) || (ldc % 8)) return -1;
   if (col_sum != nullptr && out_mode != OUT_BF16) return -4;
+  if (residual != nullptr && (out_mode != OUT_BF16 || (ldr % 8) || ((uintptr_t)residual & 15))) return -5;
+  if (out_mode != OUT_BF16 && (((uintptr_t)C & 15) || ((uintptr_t)bias & 15))) return -6;   // 16-byte fp32 accesses
   GemmArgs g{A, B, C, M, N, K, lda, ldb, ldc, out_mode, splits};
   Epilogue ep;
   ep.out_mode = out_mode; ep.relu = relu; ep.n_total = N; ep.bias = bias;
   ep.col_sum = col_sum; ep.col_sqsum = col_sqsum; ep.error_flag = error_flag;
   ep.tx_bytes = 0; ep.tx_bytes_a = 0;
+  ep.residual = residual; ep.ldr = ldr;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
   if (BN == 64) return launch_major<64>(a_mn, b_mn, g, ep, s);

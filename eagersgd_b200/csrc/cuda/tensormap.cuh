@@ -23,12 +23,24 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// The encode call is a driver entry point and needs a context current in the calling thread.  A thread that has
+// only selected a device (an autograd worker, for instance) gets the primary context bound by its first runtime
+// call that needs one; make sure that has happened, once per thread.
+inline void bind_primary_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 // bf16 tensor of rank `rank` (dims innermost first), 128-byte swizzle, zero fill
 // outside the tensor.  strides_bytes has rank-1 entries (dims 1..rank-1).
 inline int make_tensormap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                                const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return -100;
+  bind_primary_context();
   cuuint64_t d[5], s[5];
   cuuint32_t b[5], e[5];
   for (int i = 0; i < rank; ++i) {

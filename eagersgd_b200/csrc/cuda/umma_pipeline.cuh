@@ -21,6 +21,7 @@
 // copies in flight land, frees its tensor memory and returns.
 #pragma once
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include "sm100_primitives.cuh"
@@ -49,6 +50,8 @@ struct Epilogue {
   int* error_flag;
   uint32_t tx_bytes;       // bytes the loads of one k-block deliver (0: full A and B stage tiles)
   uint32_t tx_bytes_a;     // bytes of the A loads alone (B-resident mode; 0: a full A stage tile)
+  const void* residual;    // optional bf16 tensor added to the product before rounding (same shape as the output)
+  int ldr;                 // its row stride in elements
 };
 
 template <int BN>
@@ -80,13 +83,24 @@ inline bool resident_enabled() {
 // instructions that still take issue slots in the common case that uses neither.
 template <bool kPlain>
 __device__ __forceinline__ void pack_row_to_panel(const uint32_t* r, uint8_t* panel, int row, int half, int col0,
-                                                  const Epilogue& ep) {
+                                                  const Epilogue& ep, bool has_residual) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]);
+    const int chunk = half * 4 + g;          // 16-byte chunk within the 128-byte row
+    uint4* slot = reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4));
     if (!kPlain) {
+      if (has_residual) {     // the residual panel was brought into this very buffer by TMA; add in place
+        const uint4 rv = *slot;
+        const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[2 * j] += __uint_as_float(rw[j] << 16);
+          v[2 * j + 1] += __uint_as_float(rw[j] & 0xffff0000u);
+        }
+      }
       if (ep.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -101,8 +115,7 @@ __device__ __forceinline__ void pack_row_to_panel(const uint32_t* r, uint8_t* pa
     __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
     for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-    const int chunk = half * 4 + g;          // 16-byte chunk within the 128-byte row
-    *reinterpret_cast<uint4*>(panel + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
+    *slot = pk;
   }
 }
 
@@ -114,6 +127,7 @@ __device__ __forceinline__ void pack_row_to_panel(const uint32_t* r, uint8_t* pa
 //   void load_a(...a, bar) / load_b(...b, bar)     the two halves of load(); int res_kb (0: B not resident)
 //   void store_panel(const Tile&, int panel, const void* smem)   TMA store of a 128x64 bf16 panel
 //   bool row_valid(const Tile&, int row)           row is a real output (statistics mask)
+//   void load_res_panel(const Tile&, int panel, void* smem, uint64_t* bar)   TMA load of the residual's panel
 //   int valid_prefix(const Tile&)                  n if exactly rows [0, n) are real outputs, -1 if irregular
 //   void* row_ptr(const Tile&, int row)            fp32 output row pointer (direct modes), or nullptr
 template <class P>
@@ -134,7 +148,8 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
   uint64_t* tfull = empty + C::MAX_STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* bres = tempty + 2;               // the resident B tiles have landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres + 1);
+  uint64_t* rfull = bres + 1;                // residual panel has landed in staging buffer [NUM_PANEL_BUFS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rfull + NUM_PANEL_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,6 +158,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     for (int s = 0; s < C::MAX_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], NUM_EPI_THREADS / 32); }
     mbar_init(bres, 1);
+    for (int b = 0; b < NUM_PANEL_BUFS; ++b) mbar_init(&rfull[b], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -240,7 +256,31 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
 #pragma unroll
     for (int pnl = 0; pnl < BN / 64; ++pnl) { st_sum[pnl][0] = st_sum[pnl][1] = st_sq[pnl][0] = st_sq[pnl][1] = 0.f; }
     int stats_n0 = -1;
-    const bool plain = ep.bias == nullptr && !ep.relu;
+    const bool has_res = ep.residual != nullptr;
+    const bool plain = ep.bias == nullptr && !ep.relu && !has_res;
+    uint32_t gpanel = 0;                    // panels processed so far (all threads count alike)
+    // Residual prefetch (thread 0): the residual's panels are brought into the staging ring by TMA two panels
+    // ahead of the epilogue, which then adds them in place.
+    typename P::Tile pf_t;
+    int pf_it = 0, pf_pnl = 0;
+    uint32_t pf_g = 0;
+    bool pf_valid = false;
+    auto prefetch_residual = [&]() {
+      if (!pf_valid) return;
+      const int b = (int)(pf_g % NUM_PANEL_BUFS);
+      mbar_expect_tx(&rfull[b], (uint32_t)PANEL_BYTES);
+      prob.load_res_panel(pf_t, pf_pnl, sC + b * PANEL_BYTES, &rfull[b]);
+      ++pf_g;
+      if (++pf_pnl >= min(BN / 64, (ep.n_total - pf_t.n0 + 63) / 64)) {
+        pf_pnl = 0;
+        pf_valid = prob.tile(++pf_it, pf_t);
+      }
+    };
+    if (has_res && et == 0) {
+      pf_valid = prob.tile(0, pf_t);
+      prefetch_residual();
+      prefetch_residual();
+    }
     bool ok = true;
     typename P::Tile t;
     for (int it = 0; ok && prob.tile(it, t); ++it) {
@@ -274,8 +314,9 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
             // This buffer was last read by the store issued NUM_PANEL_BUFS panels ago; thread 0 waited for
             // that read before it arrived at the previous panel's barrier (see below), so it is free.
             const int col0 = t.n0 + pnl * 64 + half * 32;
-            if (plain) pack_row_to_panel<true>(rbuf[pnl & 1], panel, row, half, col0, ep);
-            else pack_row_to_panel<false>(rbuf[pnl & 1], panel, row, half, col0, ep);
+            if (has_res && !mbar_wait(&rfull[buf], (gpanel / NUM_PANEL_BUFS) & 1u, abort_flag)) { ok = false; break; }
+            if (plain) pack_row_to_panel<true>(rbuf[pnl & 1], panel, row, half, col0, ep, false);
+            else pack_row_to_panel<false>(rbuf[pnl & 1], panel, row, half, col0, ep, has_res);
             fence_proxy_async();
             named_barrier_sync(1, NUM_EPI_THREADS);    // the panel is complete and visible to the TMA engine
             if (et == 0) {
@@ -285,6 +326,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
               // but the two newest stores have read their buffers, so after that barrier everyone may overwrite
               // the buffer used three panels ago -- the one the panel after next needs.
               tma_store_wait_read<2>();
+              if (has_res) prefetch_residual();       // into the buffer the panel after next will use
             }
             if (ep.col_sum != nullptr) {
               // thread (cp, rg): columns 2cp, 2cp+1 of the panel, rows 16rg .. 16rg+15, read back as stored
@@ -303,8 +345,10 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
               st_sum[pnl][0] += s0; st_sum[pnl][1] += s1; st_sq[pnl][0] += q0; st_sq[pnl][1] += q1;
             }
             buf = (buf + 1) % NUM_PANEL_BUFS;
+            ++gpanel;
           }
         }
+        if (!ok) break;
       } else {
         // fp32 outputs (logits, split-K weight gradients): direct stores / atomics from registers
         float* out_row = reinterpret_cast<float*>(prob.row_ptr(t, row));
@@ -315,14 +359,21 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
           tmem_ld_wait();
           const int col0 = t.n0 + c * 64 + half * 32;
           if (out_row != nullptr) {
+            // four columns at a time (rows are 32-byte aligned and N is a multiple of 8): 16-byte stores, and
+            // 16-byte reductions for the split-K case, a quarter of the atomic instructions
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < ep.n_total) {
-                float v = __uint_as_float(r[j]);
-                if (ep.bias != nullptr) v += __ldg(ep.bias + col0 + j);
-                if (ep.relu) v = fmaxf(v, 0.0f);
-                if (ep.out_mode == OUT_F32) out_row[col0 + j] = v;
-                else atomicAdd(out_row + col0 + j, v);
+            for (int j4 = 0; j4 < 8; ++j4) {
+              if (col0 + j4 * 4 < ep.n_total) {
+                float4 v = make_float4(__uint_as_float(r[j4 * 4]), __uint_as_float(r[j4 * 4 + 1]),
+                                       __uint_as_float(r[j4 * 4 + 2]), __uint_as_float(r[j4 * 4 + 3]));
+                if (ep.bias != nullptr) {
+                  const float4 b4 = __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + j4 * 4));
+                  v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                }
+                if (ep.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+                float4* dst = reinterpret_cast<float4*>(out_row + col0 + j4 * 4);
+                if (ep.out_mode == OUT_F32) *dst = v;
+                else atomicAdd(dst, v);
               }
             }
           }

@@ -56,8 +56,9 @@ class _Conv(nn.Conv2d):
         # variance_scaling_initializer() of the reference: fan-in scaling
         nn.init.kaiming_normal_(self.weight, mode="fan_in", nonlinearity="linear")
 
-    def forward(self, x):  # noqa: D102
-        return ops.conv2d(x, self.weight, self.stride[0], self.padding[0], want_stats=self.training)
+    def forward(self, x, tap_input: bool = False):  # noqa: D102
+        return ops.conv2d(x, self.weight, self.stride[0], self.padding[0], want_stats=self.training,
+                          tap_input=tap_input)
 
 
 class _Block(nn.Module):
@@ -96,13 +97,16 @@ class _Block(nn.Module):
     def forward(self, x):
         n = len(self.convs)
         if self.version == 1:
-            shortcut = x
+            # The shortcut branches off the first convolution's tapped input: both gradients of x then meet
+            # inside that convolution's data-gradient kernel instead of in a separate addition.
+            yc, st, shortcut = self.convs[0](x, tap_input=True)
             if self.proj is not None:
-                ys, st = self.proj(x)
-                shortcut = self.proj_bn(ys, relu=False, stats=st)
+                ys, sts = self.proj(shortcut)
+                shortcut = self.proj_bn(ys, relu=False, stats=sts)
             y = x
             for i in range(n):
-                yc, st = self.convs[i](y)
+                if i > 0:
+                    yc, st = self.convs[i](y)
                 # the last batch norm also adds the shortcut and applies the block's final ReLU
                 y = self.bns[i](yc, relu=True, residual=shortcut if i == n - 1 else None, stats=st)
             return y

@@ -108,7 +108,7 @@ def bench_conv(shape, iters, backward=False):
         fn = lambda: torch.autograd.grad(ops.conv2d(x, wt, stride, pad)[0], x, g)
         with ops.reference_ops():
             lib = lambda: torch.autograd.grad(ops.conv2d(x, wt, stride, pad)[0], x, g)
-            ms_lib = timeit(lib, iters)
+            ms_lib = timeit(lib, iters, graph=False)
         ms = timeit(fn, iters)
         flops *= 2
     else:
@@ -130,7 +130,7 @@ def bench_conv_wgrad(shape, iters):
     ms = timeit(lambda: torch.autograd.grad(y, wt, g, retain_graph=True), iters)
     with ops.reference_ops():
         y2, _ = ops.conv2d(x, wt, stride, pad)
-        ms_lib = timeit(lambda: torch.autograd.grad(y2, wt, g, retain_graph=True), iters)
+        ms_lib = timeit(lambda: torch.autograd.grad(y2, wt, g, retain_graph=True), iters, graph=False)
     flops = 2.0 * n * y.shape[2] * y.shape[3] * cout * cin * k * k
     byts = 2.0 * (x.numel() + y.numel()) + 4.0 * wt.numel()
     return dict(op="conv_wgrad", N=n, Cin=cin, H=h, W=w, Cout=cout, k=k, stride=stride, ms=ms,
@@ -153,7 +153,8 @@ def bench_bn(shape, iters, backward=False, residual=False):
         byts = nb * ((2 + (1 if residual else 0)) + (3 + (2 if residual else 0)))   # reduce reads + apply reads/writes
         with ops.reference_ops():
             z2 = ops.bn_act(y, gamma, beta, rm, rv, 0.1, True, res)
-            ms_lib = timeit(lambda: torch.autograd.grad(z2, (y, gamma, beta), dz, retain_graph=True), iters)
+            ms_lib = timeit(lambda: torch.autograd.grad(z2, (y, gamma, beta), dz, retain_graph=True), iters,
+                            graph=False)
     else:
         ms = timeit(lambda: ops.bn_act(y, gamma, beta, rm, rv, 0.1, True, res), iters)
         byts = nb * (3 + (1 if residual else 0))      # stats read, apply read (+residual), write

@@ -87,11 +87,24 @@ def native(x: torch.Tensor) -> bool:
 
 
 # --------------------------------------------------------------------------- 1x1 convolution / dense
+def wgrad_splits(pixels: int, cout: int, cin: int, sms: int = 148) -> int:
+    """Split-K factor of a weight-gradient GEMM (K = pixels): about one wave of tiles.  Each split adds a
+    full [Cout, Cin] partial result with atomics, so large filter banks take few splits."""
+    bn = 64 if cin <= 64 else (128 if cin <= 128 else 256)
+    out_tiles = -(-cout // 128) * -(-cin // bn)
+    return max(2, min(-(-sms // out_tiles), max(1, (pixels // 64) // 8)))
+
+
 class _Conv1x1(torch.autograd.Function):
-    """y = x (*) w for a 1x1 kernel; optionally also returns per-channel sum / sum-of-squares of y."""
+    """y = x (*) w for a 1x1 kernel; optionally also returns per-channel sum / sum-of-squares of y.
+
+    With ``tap_input`` the input is returned as a last output, too.  A residual block takes its shortcut
+    from that output instead of from ``x`` itself: backward then receives the shortcut's gradient together
+    with dy and adds it in the epilogue of the data-gradient GEMM, instead of autograd summing the two
+    branches of ``x`` with a separate pass over the tensor."""
 
     @staticmethod
-    def forward(ctx, x, w, want_stats: bool):
+    def forward(ctx, x, w, want_stats: bool, tap_input: bool = False):
         n, cin, h, wd = x.shape
         cout = w.shape[0]
         x2d = nhwc_2d(x)
@@ -101,33 +114,45 @@ class _Conv1x1(torch.autograd.Function):
         ctx.save_for_backward(x2d, w2d)
         ctx.dims = (n, h, wd, cin, cout, w.shape)
         ctx.mark_non_differentiable(*( [stats] if want_stats else []))
+        ctx.layout = (want_stats, tap_input)
+        ctx.set_materialize_grads(False)       # an unused tap must not cost a tensor of zeros
         y = from_2d(y2d, n, h, wd)
-        return (y, stats) if want_stats else y
+        outs = (y,) + ((stats,) if want_stats else ()) + ((x.view_as(x),) if tap_input else ())
+        return outs if len(outs) > 1 else y
 
     @staticmethod
-    def backward(ctx, dy, *unused):
+    def backward(ctx, dy, *more):
         x2d, w2d = ctx.saved_tensors
         n, h, wd, cin, cout, wshape = ctx.dims
+        want_stats, tap_input = ctx.layout
+        d_tap = more[-1] if tap_input else None            # gradient that reached the input through the shortcut
+        if dy is None:
+            return d_tap, None, None, None
         dy2d = nhwc_2d(dy)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = from_2d(gemm(dy2d, w2d, b_kmajor=False), n, h, wd)          # [M,Cout] x W[Cout(K),Cin(N)]
+            res = nhwc_2d(d_tap.to(torch.bfloat16)) if d_tap is not None else None
+            dx = from_2d(gemm(dy2d, w2d, b_kmajor=False, residual=res), n, h, wd)   # [M,Cout] x W[Cout(K),Cin(N)]
         if ctx.needs_input_grad[1]:
-            m = dy2d.shape[0]
-            splits = max(1, min(148, (m // 64) // 8))
-            dw32 = gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, splits=max(splits, 2))  # [Cout, Cin] fp32
+            dw32 = gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False,
+                        splits=wgrad_splits(dy2d.shape[0], cout, cin))                      # [Cout, Cin] fp32
             dw = dw32.to(torch.bfloat16).view(wshape)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
-def conv1x1(x: torch.Tensor, w: torch.Tensor, want_stats: bool = False):
+def conv1x1(x: torch.Tensor, w: torch.Tensor, want_stats: bool = False, tap_input: bool = False):
+    """1x1 convolution.  ``tap_input=True`` appends ``x`` itself to the outputs (use it for the shortcut of a
+    residual block: the two gradients of ``x`` are then added inside the data-gradient GEMM)."""
     if native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
-        return _Conv1x1.apply(x, w, want_stats)
+        return _Conv1x1.apply(x, w, want_stats, tap_input)
     y = F.conv2d(x, w)
+    outs = (y,)
     if want_stats:
         yf = y.float()
-        return y, torch.stack([yf.sum((0, 2, 3)), (yf * yf).sum((0, 2, 3))]).detach()
-    return y
+        outs += (torch.stack([yf.sum((0, 2, 3)), (yf * yf).sum((0, 2, 3))]).detach(),)
+    if tap_input:
+        outs += (x,)
+    return outs if len(outs) > 1 else y
 
 
 def _conv_native(x2d_src, w_ohwi, n, h, w, cin, cout, r, s, stride, pad, stats):
@@ -275,11 +300,21 @@ class _Subsample2(torch.autograd.Function):
         return from_2d(dx2d, n, h, w)
 
 
-def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, want_stats: bool = False):
+def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, want_stats: bool = False,
+           tap_input: bool = False):
     """NHWC convolution; returns ``(y, stats)`` (``stats`` is None unless produced by the kernel epilogue).
 
-    1x1 kernels run as tcgen05 GEMMs (a strided 1x1 first gathers the kept pixels).
+    1x1 kernels run as tcgen05 GEMMs (a strided 1x1 first gathers the kept pixels).  With ``tap_input`` a
+    third value is returned: the tensor a residual block should feed its shortcut from (the input itself, or
+    for the fused 1x1 path an alias whose gradient is added inside the data-gradient GEMM).
     """
+    if tap_input:
+        k1 = w.shape[2] == 1 and stride == 1 and native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0
+        if k1 and x.requires_grad and torch.is_grad_enabled():
+            out = conv1x1(x, w, want_stats, tap_input=True)
+            return (out[0], out[1], out[2]) if want_stats else (out[0], None, out[1])
+        y, st = conv2d(x, w, stride, padding, want_stats)
+        return y, st, x
     k = w.shape[2]
     if k == 1 and native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
         if stride == 2:

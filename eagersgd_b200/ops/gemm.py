@@ -25,7 +25,7 @@ def _lib():
     lib = N.cuda()
     if not getattr(lib, "_gemm_bound", False):
         lib.esgd_gemm_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 9 + \
-            [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+            [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         lib._gemm_bound = True
     return lib
 
@@ -46,7 +46,10 @@ def check_error(device: torch.device) -> None:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: bool = True,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          bias: Optional[torch.Tensor] = None, relu: bool = False, splits: int = 1, accumulate: bool = False,
-         col_sum: Optional[torch.Tensor] = None, col_sqsum: Optional[torch.Tensor] = None) -> torch.Tensor:
+         col_sum: Optional[torch.Tensor] = None, col_sqsum: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``residual``: a bf16 ``[M, N]`` tensor added to the product in the epilogue, before the single
+    rounding to bf16 (bf16 output only)."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     if a_kmajor:
@@ -66,12 +69,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_kmajor: bool = True, b_kmajor: b
     mode = 2 if atomic else (0 if out.dtype == torch.bfloat16 else 1)
     if atomic:
         assert out.dtype == torch.float32
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, Nn) and residual.stride(1) == 1 and mode == 0
     stream = torch.cuda.current_stream(a.device).cuda_stream
     rc = _lib().esgd_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0),
                                out.stride(0), int(not a_kmajor), int(not b_kmajor), mode,
                                bias.data_ptr() if bias is not None else None, int(relu), splits,
                                col_sum.data_ptr() if col_sum is not None else None,
                                col_sqsum.data_ptr() if col_sqsum is not None else None,
+                               residual.data_ptr() if residual is not None else None,
+                               residual.stride(0) if residual is not None else 0,
                                error_flag(a.device).data_ptr(), stream)
     if rc != 0:
         raise RuntimeError("esgd_gemm_bf16 failed with code %d (M=%d N=%d K=%d)" % (rc, M, Nn, K))

@@ -113,3 +113,19 @@ def test_gemm_resident_b_operand(M, N, K, stats, a_k, b_k):
     if stats:
         assert torch.allclose(s, c.float().sum(0), rtol=2e-3, atol=2.0)
         assert torch.allclose(s2, (c.float() ** 2).sum(0), rtol=2e-3, atol=20.0)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 72, 64), (4096, 256, 512), (40000, 256, 64), (1000, 520, 96)])
+def test_gemm_residual_added_before_rounding(M, N, K):
+    from eagersgd_b200.ops.gemm import gemm, check_error
+    torch.manual_seed(M + N)
+    a, b = _rand((M, K), 0.5), _rand((K, N), 0.5)
+    res = _rand((M, N), 2.0)
+    c = gemm(a, b, b_kmajor=False, residual=res)
+    torch.cuda.synchronize()
+    check_error(a.device)
+    ref = a.float() @ b.float() + res.float()
+    assert (c.float() - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-2
+    # one rounding: closer to the fp32 sum than rounding the product and the sum separately
+    two = (gemm(a, b, b_kmajor=False) + res).float()
+    assert (c.float() - ref).abs().mean().item() <= (two - ref).abs().mean().item() + 1e-6

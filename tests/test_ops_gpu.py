@@ -208,3 +208,50 @@ def test_lstm_layer_forward_backward(T, B, I, H):
         cos = F.cosine_similarity(a.float().flatten(), b_.flatten(), dim=0).item()
         assert cos > 0.99, (name, cos)
         assert (a.float() - b_).abs().max().item() < 0.05 * b_.abs().max().item() + 5e-2, name
+
+
+def test_conv1x1_tapped_input_adds_shortcut_gradient_in_the_gemm():
+    """The shortcut's gradient reaches x through the tapped output and is added in the data-gradient GEMM."""
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(3)
+    n, c, h, w, cout = 4, 256, 14, 14, 64
+    x = _cl(torch.randn(n, c, h, w, device=DEV)).to(torch.bfloat16).requires_grad_()
+    wt = (torch.randn(cout, c, 1, 1, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    y, stats, tap = ops.conv2d(x, wt, 1, 0, want_stats=True, tap_input=True)
+    assert tap.data_ptr() == x.data_ptr() and stats is not None
+    g = _cl(torch.randn(n, cout, h, w, device=DEV)).to(torch.bfloat16)
+    g2 = _cl(torch.randn(n, c, h, w, device=DEV)).to(torch.bfloat16)
+    torch.autograd.backward([y, tap], [g, g2])
+    xr, wr = x.detach().float().requires_grad_(), wt.detach().float().requires_grad_()
+    F.conv2d(xr, wr).backward(g.float())
+    ref = xr.grad + g2.float()
+    assert torch.allclose(x.grad.float(), ref, rtol=2e-2, atol=3e-2)
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=0.1 * wr.grad.abs().max().item())
+    # an unused tap costs nothing and changes nothing
+    x2 = x.detach().clone().requires_grad_()
+    y2, _, _ = ops.conv2d(x2, wt.detach(), 1, 0, want_stats=False, tap_input=True)
+    y2.backward(g)
+    assert torch.allclose(x2.grad.float(), xr.grad, rtol=2e-2, atol=3e-2)
+
+
+def test_identity_bottleneck_block_matches_reference_ops():
+    import copy
+    from eagersgd_b200.models.resnet import _Block
+    from eagersgd_b200.ops import functional as ops
+    torch.manual_seed(8)
+    blk = _Block(256, 64, 1, "bottleneck", 1, False, []).to(DEV)
+    for m in blk.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            torch.nn.init.uniform_(m.weight, 0.5, 1.0)
+        if isinstance(m, torch.nn.Conv2d):
+            m.to(torch.bfloat16)
+    blk2 = copy.deepcopy(blk)
+    x = _cl(torch.randn(8, 256, 14, 14, device=DEV)).to(torch.bfloat16)
+    x1, x2 = x.clone().requires_grad_(), x.clone().requires_grad_()
+    g = _cl(torch.randn(8, 256, 14, 14, device=DEV)).to(torch.bfloat16)
+    blk(x1).backward(g)
+    with ops.reference_ops():
+        blk2(x2).backward(g)
+    assert F.cosine_similarity(x1.grad.float().flatten(), x2.grad.float().flatten(), dim=0).item() > 0.995
+    rel = (x1.grad.float() - x2.grad.float()).norm() / x2.grad.float().norm()
+    assert rel.item() < 0.05, rel.item()
