@@ -273,6 +273,51 @@ __global__ void __launch_bounds__(256) im2col_small_c_kernel(const __nv_bfloat16
   }
 }
 
+// The same columns, one output row of the image per block: the R input rows that the row's windows touch are
+// staged in shared memory with 16-byte loads between zero guards (the horizontal padding), and every thread
+// assembles 16-byte chunks of the column matrix from them with funnel shifts (a window starts on an even byte,
+// not on a word).  Elements of a segment beyond S*C carry the neighbouring pixels instead of zeros; they meet
+// zero weights.  Writes are the only large traffic (N*Ho*Wo*Kpad*2 bytes) and they are fully coalesced.
+constexpr int kImLeftGuard = 32, kImRightGuard = 64;
+__global__ void __launch_bounds__(256) im2col_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ col, int N, int H, int W, int C,
+                                                          int R, int S, int stride, int pad, int Ho, int Wo, int seg,
+                                                          int Kpad) {
+  extern __shared__ __align__(16) uint8_t im_rows[];
+  const int rowbytes = W * C * 2;
+  const int pitch = kImLeftGuard + rowbytes + kImRightGuard;
+  const int n = blockIdx.x / Ho, p = blockIdx.x % Ho;
+  for (int r = 0; r < R; ++r) {
+    const int h = p * stride + r - pad;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(x) + ((int64_t)n * H + h) * rowbytes;
+    for (int i = threadIdx.x; i < pitch / 16; i += blockDim.x) {
+      const int byte = i * 16 - kImLeftGuard;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h >= 0 && h < H && byte >= 0 && byte < rowbytes) v = __ldg(reinterpret_cast<const uint4*>(src + byte));
+      *reinterpret_cast<uint4*>(im_rows + r * pitch + i * 16) = v;
+    }
+  }
+  __syncthreads();
+  const int chunks_per_seg = seg / 8, chunks_per_pixel = Kpad / 8;
+  __nv_bfloat16* dst_row = col + ((int64_t)n * Ho + p) * Wo * Kpad;
+  for (int ci = threadIdx.x; ci < Wo * chunks_per_pixel; ci += blockDim.x) {
+    const int q = ci / chunks_per_pixel, k8 = ci - q * chunks_per_pixel;
+    const int r = k8 / chunks_per_seg, c = k8 - r * chunks_per_seg;
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (r < R) {
+      const int off = kImLeftGuard + ((q * stride - pad) * C + 8 * c) * 2;
+      const uint32_t* wp = reinterpret_cast<const uint32_t*>(im_rows + r * pitch + (off & ~3));
+      const int sh = (off & 3) * 8;
+      const uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = wp[4];
+      out.x = __funnelshift_r(w0, w1, sh);
+      out.y = __funnelshift_r(w1, w2, sh);
+      out.z = __funnelshift_r(w2, w3, sh);
+      out.w = __funnelshift_r(w3, w4, sh);
+    }
+    *reinterpret_cast<uint4*>(dst_row + (int64_t)ci * 8) = out;
+  }
+}
+
 int grid_for(int64_t items) {
   int64_t b = (items + 255) / 256;
   const int64_t cap = 148 * 16;
@@ -341,6 +386,17 @@ int esgd_im2col_small_c(const void* x, void* col, int N, int H, int W, int C, in
                         int seg, int Kpad, void* stream) {
   if (seg % 8 || seg < S * C || seg > 32 || Kpad % seg || Kpad < R * seg) return -1;
   const int Ho = (H + 2 * pad - R) / stride + 1, Wo = (W + 2 * pad - S) / stride + 1;
+  const int rowbytes = W * C * 2;
+  const int smem = R * (kImLeftGuard + rowbytes + kImRightGuard);
+  // staged-row kernel: rows must be 16-byte multiples on a 16-byte base, the guards must cover the padding and
+  // the over-read of the last window, and the rows must fit in the default shared-memory budget
+  if (rowbytes % 16 == 0 && ((uintptr_t)x & 15) == 0 && pad * C * 2 <= kImLeftGuard &&
+      ((Wo - 1) * stride - pad) * C * 2 + seg * 2 + 8 <= rowbytes + kImRightGuard && smem <= 48 * 1024) {
+    im2col_rows_kernel<<<N * Ho, 256, smem, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, R, S, stride, pad, Ho, Wo, seg, Kpad);
+    esgd::count_launch();
+    return (int)cudaGetLastError();
+  }
   im2col_small_c_kernel<32><<<grid_for((int64_t)N * Ho * Wo * (Kpad / seg)), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, R, S, stride, pad, Ho, Wo, seg, Kpad);
   esgd::count_launch();
