@@ -39,7 +39,8 @@ __global__ void pack_kernel(DevChannel* ch) {
 // participant of a round takes the same decision (same count, same threshold, same descriptor).
 __device__ inline void decide_two_shot(DevChannel* ch) {
   const Plan& p = ch->plan;
-  ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= 2 && ch->count >= ch->two_shot_min &&
+  ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= ch->two_shot_parts && p.part_count >= 2 &&
+                       ch->count >= ch->two_shot_min &&
                        ch->gath[ch->cfg.rank] != nullptr) ? 1 : 0;
 }
 
@@ -187,6 +188,7 @@ struct esgd_channel_desc {
   int32_t out_bf16, pad;
   void* hyper;
   uint64_t two_shot_min;          // element count from which the reduction runs in two shots
+  int32_t two_shot_parts, pad3;   // ... in rounds with at least this many participants
 };
 
 uint64_t esgd_dev_channel_bytes(void) { return sizeof(DevChannel); }
@@ -205,6 +207,7 @@ int esgd_channel_configure(void* dch, const esgd_channel_desc* d, void* stream) 
     h.gath[j] = (float*)d->gath[j];
   }
   h.two_shot_min = d->two_shot_min;
+  h.two_shot_parts = d->two_shot_parts;
   h.cfg.rank = d->rank; h.cfg.world = d->world; h.cfg.average_world = d->average; h.cfg.home = d->home;
   h.cfg.timeout_ns = d->timeout_ns; h.cfg.grace_ns = d->grace_ns;
   h.pol.base_mode = d->base_mode; h.pol.include_stale = d->include_stale; h.pol.limiter = d->limiter;

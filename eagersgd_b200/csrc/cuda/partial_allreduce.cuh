@@ -54,6 +54,8 @@ struct DevChannel {
   uint32_t blocks_done;
   uint32_t blocks_done2;     // block counter of the gather kernel
   uint64_t two_shot_min;     // smallest element count that takes the two-shot path
+  int32_t two_shot_parts;    // fewest participants for which it pays (peer stores are dearer than peer loads)
+  int32_t pad2;
 };
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, uint64_t i, float v[8]) {

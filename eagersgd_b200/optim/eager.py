@@ -62,9 +62,11 @@ class EagerOptimizer:
                  limiter: int = 32, seed: int = 6545343, bucket_mb: float = 25.0,
                  average: str = "contributors", include_stale: bool = True, fused: Optional[bool] = None,
                  slot_dtype: Optional[torch.dtype] = None, overlap: bool = True, timeout_s: float = 30.0,
-                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 18):
+                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 18,
+                 two_shot_parts: int = 5):
         self.optimizer = optimizer
         self.two_shot_min = two_shot_min   # bucket elements from which a round is reduced in two shots (None: never)
+        self.two_shot_parts = two_shot_parts   # ... when at least this many ranks take part in it
         self.group = group if group is not None else init_group()
         self.mode, self.limiter, self.seed = mode, limiter, seed
         self.average, self.include_stale = average, include_stale
@@ -178,7 +180,7 @@ class EagerOptimizer:
                                       seed=self.seed, average=self.average,
                                       include_stale=self.include_stale, timeout_s=self.timeout_s,
                                       grace_us=self.grace_us, hyper=b.hyper, max_blocks=self.max_blocks,
-                                      two_shot_min=self.two_shot_min, **kw)
+                                      two_shot_min=self.two_shot_min, two_shot_parts=self.two_shot_parts, **kw)
             self._refresh_hyper(b, force=True)
         torch.cuda.synchronize(self.device)
         g.barrier()

@@ -58,7 +58,8 @@ class ChannelDesc(C.Structure):
                [("limiter", C.c_int64)] + \
                [(n, C.c_uint64) for n in "seed timeout_ns grace_ns count".split()] + \
                [(n, C.c_void_p) for n in "grad_in w32 mom w16 out".split()] + \
-               [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p), ("two_shot_min", C.c_uint64)]
+               [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p), ("two_shot_min", C.c_uint64),
+                ("two_shot_parts", C.c_int32), ("pad3", C.c_int32)]
 
 
 STAT_NAMES = ("local_step", "participated", "absent", "activated", "sync_rounds", "dropped_grads",

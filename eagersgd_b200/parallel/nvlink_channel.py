@@ -22,6 +22,7 @@ _MODES = {"solo": N.MODE_SOLO, "majority": N.MODE_MAJORITY, "sync": N.MODE_SYNC}
 _AVG = {"contributors": N.AVG_CONTRIBUTORS, "world": N.AVG_WORLD, "sum": N.AVG_SUM}
 HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
 TWO_SHOT_MIN = 1 << 18  # elements from which a round with several reducers is reduced in two shots
+TWO_SHOT_PARTS = 5      # ... when at least this many ranks take part (up to four, one shot moves no more bytes)
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -73,8 +74,8 @@ class NvlinkChannel:
     update; otherwise the averaged gradient is written to ``out``.
 
     Channels of at least ``two_shot_min`` elements reduce in two shots when a round
-    has several participants (each sums its share and stores it into every
-    participant's gather buffer); ``two_shot_min=None`` keeps the one-shot form.
+    has at least ``two_shot_parts`` participants (each sums its share and stores it
+    into every participant's gather buffer); ``two_shot_min=None`` keeps the one-shot form.
     """
 
     def __init__(self, count: int, rank: int, world: int, bases: List[int], device: torch.device,
@@ -84,7 +85,7 @@ class NvlinkChannel:
                  w32: Optional[torch.Tensor] = None, mom: Optional[torch.Tensor] = None,
                  w16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  hyper: Optional[torch.Tensor] = None, max_blocks: int = 592,
-                 two_shot_min: Optional[int] = TWO_SHOT_MIN):
+                 two_shot_min: Optional[int] = TWO_SHOT_MIN, two_shot_parts: int = TWO_SHOT_PARTS):
         self.lib = N.cuda()
         self.count, self.rank, self.world, self.device = count, rank, world, device
         self.max_blocks = max_blocks
@@ -106,7 +107,8 @@ class NvlinkChannel:
             d.mbox[j] = bases[j] + L.mbox
             d.gath[j] = bases[j] + L.gath if two_shot_min is not None else None
         d.two_shot_min = int(two_shot_min) if two_shot_min is not None else 0
-        self.two_shot = int(two_shot_min is not None and world > 1 and count >= two_shot_min)
+        d.two_shot_parts = int(two_shot_parts)
+        self.two_shot = int(two_shot_min is not None and world >= max(2, two_shot_parts) and count >= two_shot_min)
         d.rank, d.world, d.base_mode = rank, world, _MODES[mode]
         d.include_stale, d.average, d.home = int(include_stale), _AVG[average], home
         d.slot_bf16 = int(slot_dtype == torch.bfloat16)

@@ -193,7 +193,7 @@ def _two_shot_vs_nccl(rank, world, slot_bf16):
         grad = torch.zeros(count, device=dev)
         out = torch.zeros(count, device=dev)
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=sdt, mode="sync", limiter=-1,
-                           average="world", out=out, timeout_s=5.0, grace_us=0.0, two_shot_min=tsm)
+                           average="world", out=out, timeout_s=5.0, grace_us=0.0, two_shot_min=tsm, two_shot_parts=2)
         res = []
         for g in grads:
             grad.copy_(g)

@@ -207,7 +207,7 @@ def test_two_shot_reduction_is_bit_identical_to_one_shot(world, slot_dtype, fuse
     count = 8 * 1237          # not a multiple of the number of participants
     gdt = torch.bfloat16 if slot_dtype == torch.bfloat16 else torch.float32
     worlds = [EmulatedWorld(world, count, _dev(), slot_dtype=slot_dtype, grad_dtype=gdt, fused=fused, mode="sync",
-                            limiter=-1, average="contributors", timeout_s=2.0, two_shot_min=tsm)
+                            limiter=-1, average="contributors", timeout_s=2.0, two_shot_min=tsm, two_shot_parts=2)
               for tsm in (None, 0)]
     try:
         torch.manual_seed(world)
@@ -246,7 +246,7 @@ def test_two_shot_eager_rounds_replicas_agree(mode):
     from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
     world, count, steps = 6, 8 * 511, 40
     w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode=mode, limiter=7, average="sum",
-                      timeout_s=2.0, grace_us=0.0, two_shot_min=0)
+                      timeout_s=2.0, grace_us=0.0, two_shot_min=0, two_shot_parts=2)
     rng = random.Random(17 + len(mode))
     ramp = torch.arange(count, device=_dev(), dtype=torch.float32) % 13
     applied = [torch.zeros(count, dtype=torch.float64, device=_dev()) for _ in range(world)]
