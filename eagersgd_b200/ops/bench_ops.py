@@ -59,7 +59,8 @@ def timeit(fn, iters: int, flush: bool = True, graph: bool = True) -> float:
             fn = g.replay
             fn()
             torch.cuda.synchronize()
-        except Exception:
+        except Exception as exc:   # time the plain launches instead, and say so
+            print("graph capture failed, timing eager launches: %s" % str(exc).splitlines()[0], file=sys.stderr)
             torch.cuda.synchronize()
     total = 0.0
     for _ in range(iters):
