@@ -19,6 +19,7 @@
 // conv_op.cpp:291-321.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include "launch_count.cuh"
 #include "tensormap.cuh"
 #include "umma_pipeline.cuh"
@@ -30,7 +31,7 @@ namespace {
 template <int BN_>
 struct ConvProblem {
   static constexpr int BN = BN_;
-  static constexpr bool A_MN = false, B_MN = false, kZeroStages = false;
+  static constexpr bool A_MN = false, B_MN = false, kZeroStages = false, kHalo = false;
   CUtensorMap tmX, tmW, tmY;
   int N, Ho, Wo, Cout;
   int R, S, stride, pad;
@@ -87,6 +88,57 @@ struct ConvProblem {
   }
   __device__ __forceinline__ void* row_ptr(const Tile&, int) const { return nullptr; }
   __device__ __forceinline__ void load_res_panel(const Tile&, int, void*, uint64_t*) const {}
+  __device__ __forceinline__ int out_row(int row) const { return row; }
+};
+
+// Stride-1 convolution whose taps are shifted views of one input box per 64-channel block (halo mode of the
+// pipeline).  A tile is BH full output rows of one image; GEMM row m stands for the pixel (m / PW, m % PW) of
+// the box pitch PW = Wo + S - 1, so the S - 1 margin columns of every row (and the rows past BH * PW) compute
+// values that are dropped: out_row() gives a GEMM row its place in the dense [BH][Wo] tile that is stored.
+template <int BN_>
+struct ConvHaloProblem {
+  static constexpr int BN = BN_;
+  static constexpr bool A_MN = false, B_MN = false, kZeroStages = false, kHalo = true;
+  CUtensorMap tmX, tmW, tmY;
+  int N, Ho, Wo, Cout;
+  int R, S, pad;
+  int cblks;                 // Cin / 64
+  int BH, PW;                // output rows per tile, pixel pitch of the input box
+  int h_tiles, n_tiles;
+  int res_kb;                // > 0: the filter bank of the CTA's channel range is resident
+
+  struct Tile { int kb0, kb1, n0, h0, i0; };
+
+  __device__ __forceinline__ bool tile(int it, Tile& t) const {
+    const int n_idx = blockIdx.x % n_tiles;
+    const int m_idx = blockIdx.x / n_tiles + it * (gridDim.x / n_tiles);
+    if (m_idx >= h_tiles * N) return false;
+    t.h0 = (m_idx % h_tiles) * BH;
+    t.i0 = m_idx / h_tiles;
+    t.n0 = n_idx * BN;
+    t.kb0 = 0;
+    t.kb1 = R * S * cblks;
+    return true;
+  }
+  __device__ __forceinline__ void load_halo(const Tile& t, int cb, void* smem, uint64_t* bar) const {
+    tma_load_4d(smem, &tmX, bar, cb * 64, -pad, t.h0 - pad, t.i0);
+  }
+  __device__ __forceinline__ void load_b(const Tile& t, int kb, uint8_t* b, uint64_t* bar) const {
+    tma_load_2d(b, &tmW, bar, kb * 64, t.n0);
+  }
+  __device__ __forceinline__ void load_a(const Tile&, int, uint8_t*, uint64_t*) const {}
+  __device__ __forceinline__ void load(const Tile&, int, uint8_t*, uint8_t*, uint64_t*) const {}
+  __device__ __forceinline__ void store_panel(const Tile& t, int panel, const void* smem) const {
+    tma_store_4d(&tmY, smem, t.n0 + panel * 64, 0, t.h0, t.i0);
+  }
+  __device__ __forceinline__ int out_row(int row) const {
+    const int hl = row / PW, wl = row - hl * PW;
+    return (hl < BH && wl < Wo) ? hl * Wo + wl : -1;
+  }
+  __device__ __forceinline__ bool row_valid(const Tile&, int row) const { return row < BH * Wo; }
+  __device__ __forceinline__ int valid_prefix(const Tile&) const { return BH * Wo; }
+  __device__ __forceinline__ void* row_ptr(const Tile&, int) const { return nullptr; }
+  __device__ __forceinline__ void load_res_panel(const Tile&, int, void*, uint64_t*) const {}
 };
 
 
@@ -139,6 +191,8 @@ struct ConvWgradProblem {
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < Cout; }
   __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, Cout - t.m0); }
   __device__ __forceinline__ void load_res_panel(const Tile&, int, void*, uint64_t*) const {}
+  __device__ __forceinline__ int out_row(int row) const { return row; }
+  static constexpr bool kHalo = false;
   __device__ __forceinline__ void* row_ptr(const Tile& t, int row) const {
     const int k = t.m0 + row;
     return k < Cout ? (void*)(dw + ((size_t)k * (R * S) + t.tap) * Cin) : nullptr;
@@ -260,6 +314,80 @@ int launch(const ConvArgs& a, Epilogue ep, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
+// Halo mode applies to stride-1 convolutions with full-width tiles: the box (output rows + filter margin, full
+// width + margin, 64 channels) and the rows its most shifted view reaches must fit in one HALO_BYTES slot.
+bool halo_applicable(const ConvArgs& a, int Ho, int Wo, int* bh_out) {
+  if (a.stride != 1 || a.R * a.S < 2 || a.out_h || a.out_w || a.ys_w) return false;
+  const char* e = getenv("ESGD_CONV_HALO");
+  if (e != nullptr && e[0] == '0') return false;
+  const int PW = Wo + a.S - 1;
+  if (PW > 128 || PW != a.W + 2 * a.pad || Ho + a.R - 1 != a.H + 2 * a.pad) return false;
+  int bh = 0;
+  for (int d = 1; d * PW <= BM && d <= Ho; ++d) if (Ho % d == 0) bh = d;
+  if (bh == 0) return false;
+  if (bh * Wo < 64) return false;                                   // too few real rows per tile: keep multi-image tiles
+  const int view_rows = (a.R - 1) * PW + (a.S - 1) + BM;            // rows the last tap's view may touch
+  if (view_rows * 128 > HALO_BYTES || (bh + a.R - 1) * PW * 128 > HALO_BYTES) return false;
+  *bh_out = bh;
+  return true;
+}
+
+template <int BN>
+int launch_halo(const ConvArgs& a, Epilogue ep, int bh, cudaStream_t stream) {
+  using P = ConvHaloProblem<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(conv_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  P p;
+  p.N = a.N; p.Cout = a.Cout; p.R = a.R; p.S = a.S; p.pad = a.pad;
+  p.Ho = a.H + 2 * a.pad - a.R + 1;
+  p.Wo = a.W + 2 * a.pad - a.S + 1;
+  p.cblks = a.Cin / 64;
+  p.BH = bh;
+  p.PW = p.Wo + a.S - 1;
+  p.h_tiles = p.Ho / bh;
+  p.n_tiles = (a.Cout + BN - 1) / BN;
+  {
+    uint64_t dims[4] = {(uint64_t)a.Cin, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N};
+    uint64_t strides[3] = {(uint64_t)a.Cin * 2, (uint64_t)a.W * a.Cin * 2, (uint64_t)a.H * a.W * a.Cin * 2};
+    uint32_t box[4] = {64, (uint32_t)p.PW, (uint32_t)(bh + a.R - 1), 1};
+    int r = esgd::make_tensormap_bf16(&p.tmX, a.x, 4, dims, strides, box, nullptr);
+    if (r != 0) return 1000 + r;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)a.R * a.S * a.Cin, (uint64_t)a.Cout};
+    uint64_t strides[1] = {(uint64_t)a.R * a.S * a.Cin * 2};
+    uint32_t box[2] = {64, (uint32_t)BN};
+    int r = esgd::make_tensormap_bf16(&p.tmW, a.w, 2, dims, strides, box, nullptr);
+    if (r != 0) return 2000 + r;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)a.Cout, (uint64_t)p.Wo, (uint64_t)p.Ho, (uint64_t)a.N};
+    uint64_t strides[3] = {(uint64_t)a.Cout * 2, (uint64_t)p.Wo * a.Cout * 2, (uint64_t)p.Ho * p.Wo * a.Cout * 2};
+    uint32_t box[4] = {64, (uint32_t)p.Wo, (uint32_t)bh, 1};
+    int r = esgd::make_tensormap_bf16(&p.tmY, a.y, 4, dims, strides, box, nullptr);
+    if (r != 0) return 3000 + r;
+  }
+  const int sms = sm_count();
+  if (p.n_tiles > sms) return -3;
+  const int kb_total = a.R * a.S * p.cblks;
+  // resident filter bank: beside two input boxes
+  p.res_kb = (kb_total * Cfg<BN>::B_STAGE_BYTES + 2 * HALO_BYTES <= Cfg<BN>::STAGE_AREA) ? kb_total : 0;
+  const int total = p.h_tiles * a.N * p.n_tiles;
+  int grid = (sms / p.n_tiles) * p.n_tiles;
+  if (grid > total) grid = total;
+  ep.tx_bytes_a = (uint32_t)(p.PW * (bh + a.R - 1) * 128);
+  ep.tx_bytes = 0;
+  ep.residual = nullptr; ep.ldr = 0;
+  conv_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
+  esgd::count_launch();
+  return (int)cudaGetLastError();
+}
+
 template <int BN>
 int launch_wgrad(const ConvArgs& a, const void* dy, float* dw, int* error_flag, cudaStream_t stream) {
   using P = ConvWgradProblem<BN>;
@@ -370,6 +498,9 @@ int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int 
   ep.tx_bytes = 0; ep.tx_bytes_a = 0; ep.residual = nullptr; ep.ldr = 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int BN = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
+  int bh = 0;
+  if (BN <= 128 && halo_applicable(a, (H + 2 * pad - R) / stride + 1, (W + 2 * pad - S) / stride + 1, &bh))
+    return BN == 64 ? launch_halo<64>(a, ep, bh, s) : launch_halo<128>(a, ep, bh, s);
   if (BN == 64) return launch<64>(a, ep, s);
   if (BN == 128) return launch<128>(a, ep, s);
   return launch<256>(a, ep, s);

@@ -21,7 +21,7 @@ namespace {
 template <int BN_, bool A_MN_, bool B_MN_>
 struct GemmProblem {
   static constexpr int BN = BN_;
-  static constexpr bool A_MN = A_MN_, B_MN = B_MN_, kZeroStages = false;
+  static constexpr bool A_MN = A_MN_, B_MN = B_MN_, kZeroStages = false, kHalo = false;
   CUtensorMap tmA, tmB, tmC, tmR;   // tmR: optional residual, same geometry as the output
   int M, N, K;
   int m_tiles, n_tiles, splits, kb_total, kb_per_split;
@@ -78,6 +78,7 @@ struct GemmProblem {
     tma_store_2d(&tmC, smem, t.n0 + panel * 64, t.m0);
   }
   __device__ __forceinline__ bool row_valid(const Tile& t, int row) const { return t.m0 + row < M; }
+  __device__ __forceinline__ int out_row(int row) const { return row; }
   __device__ __forceinline__ int valid_prefix(const Tile& t) const { return min(BM, M - t.m0); }
   __device__ __forceinline__ void load_res_panel(const Tile& t, int panel, void* smem, uint64_t* bar) const {
     tma_load_2d(smem, &tmR, bar, t.n0 + panel * 64, t.m0);

@@ -124,12 +124,17 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1.
 //   K-major operand : rows of 64 bf16 (128 B); 8-row groups 1024 B apart (SBO); LBO unused.
 //   MN-major operand: 64-element (128 B) MN atoms `lbo` bytes apart; 8-row K groups 1024 B apart.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// `base_offset` (bits 49-51) is the phase of the swizzle pattern at the start address when the pattern itself
+// does not start on a 1024-byte boundary; operands whose pattern is 1024-byte aligned pass 0 even when the
+// start address points into the middle of it (K advance by 32 bytes, views shifted by whole rows).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t base_offset = 0) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
+  d |= (uint64_t)(base_offset & 7u) << 49;
   d |= (uint64_t)2 << 61;
   return d;
 }

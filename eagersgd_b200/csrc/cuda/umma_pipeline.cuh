@@ -68,6 +68,17 @@ struct Cfg {
   static constexpr int MAX_RES_KB = (STAGE_AREA - 4 * A_STAGE_BYTES) / B_STAGE_BYTES;
 };
 
+// Halo mode (policies with kHalo): a convolution tile loads, per 64-channel block, ONE box of input pixels
+// that covers all filter taps (the output rows of the tile plus the filter's margin, full width), and the
+// taps are shifted VIEWS of that box: the A descriptor of tap (r, s) starts (r * PW + s) rows of 128 bytes
+// into it (the swizzle is a function of the absolute shared-memory address, so a view that starts in the
+// middle of a 1024-byte pattern reads what TMA wrote there; the descriptor's base-offset field stays 0 --
+// putting the row phase there gives wrong results, as a test run showed).  GEMM rows then run over the box's pixel pitch PW (the margin columns compute values that are
+// never stored), and the input crosses L2 -> SM once instead of once per tap.  The box ring has its own
+// barriers; the operand ring carries the filter tiles only (or nothing, when they are resident).
+constexpr int HALO_BYTES = 32 * 1024;        // one input box (incl. the rows a shifted view may touch past it)
+constexpr int MAX_HALOS = 3;
+
 // ESGD_GEMM_B_RESIDENT=0 in the environment turns the B-resident mode off (for A/B timing).
 inline bool resident_enabled() {
   static int v = -1;
@@ -128,6 +139,8 @@ __device__ __forceinline__ void pack_row_to_panel(const uint32_t* r, uint8_t* pa
 //   void store_panel(const Tile&, int panel, const void* smem)   TMA store of a 128x64 bf16 panel
 //   bool row_valid(const Tile&, int row)           row is a real output (statistics mask)
 //   void load_res_panel(const Tile&, int panel, void* smem, uint64_t* bar)   TMA load of the residual's panel
+//   static constexpr bool kHalo; int out_row(int row)   row of the stored tile for a GEMM row (identity unless kHalo)
+//   kHalo only: int cblks, R, S, PW; void load_halo(const Tile&, int cb, void* smem, uint64_t* bar)
 //   int valid_prefix(const Tile&)                  n if exactly rows [0, n) are real outputs, -1 if irregular
 //   void* row_ptr(const Tile&, int row)            fp32 output row pointer (direct modes), or nullptr
 template <class P>
@@ -138,10 +151,13 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int res_kb = prob.res_kb;            // > 0: B-resident mode
-  const int nstages = res_kb > 0 ? min(C::MAX_STAGES, (C::STAGE_AREA - res_kb * C::B_STAGE_BYTES) / A_STAGE_BYTES)
-                                 : STAGES;
-  uint8_t* sA = smem;
-  uint8_t* sB = sA + nstages * A_STAGE_BYTES;
+  constexpr bool kHalo = P::kHalo;
+  const int nhalo = kHalo ? (res_kb > 0 ? 2 : MAX_HALOS) : 0;
+  const int nstages = kHalo ? (res_kb > 0 ? 1 : min(C::MAX_STAGES, (C::STAGE_AREA - nhalo * HALO_BYTES) / C::B_STAGE_BYTES))
+                            : (res_kb > 0 ? min(C::MAX_STAGES, (C::STAGE_AREA - res_kb * C::B_STAGE_BYTES) / A_STAGE_BYTES)
+                                          : STAGES);
+  uint8_t* sA = smem;                        // halo mode: the input boxes
+  uint8_t* sB = kHalo ? sA + nhalo * HALO_BYTES : sA + nstages * A_STAGE_BYTES;
   uint8_t* sC = smem + C::STAGE_AREA;
   uint64_t* full = reinterpret_cast<uint64_t*>(sC + NUM_PANEL_BUFS * PANEL_BYTES);
   uint64_t* empty = full + C::MAX_STAGES;
@@ -149,7 +165,9 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
   uint64_t* tempty = tfull + 2;
   uint64_t* bres = tempty + 2;               // the resident B tiles have landed
   uint64_t* rfull = bres + 1;                // residual panel has landed in staging buffer [NUM_PANEL_BUFS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rfull + NUM_PANEL_BUFS);
+  uint64_t* hfull = rfull + NUM_PANEL_BUFS;  // halo mode: input box has landed / has been consumed [MAX_HALOS]
+  uint64_t* hempty = hfull + MAX_HALOS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(hempty + MAX_HALOS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,6 +177,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], NUM_EPI_THREADS / 32); }
     mbar_init(bres, 1);
     for (int b = 0; b < NUM_PANEL_BUFS; ++b) mbar_init(&rfull[b], 1);
+    for (int b = 0; b < MAX_HALOS; ++b) { mbar_init(&hfull[b], 1); mbar_init(&hempty[b], 1); }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -191,6 +210,36 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
       }
       const uint32_t tx_a = ep.tx_bytes_a ? ep.tx_bytes_a : (uint32_t)A_STAGE_BYTES;
       const uint32_t tx_ab = ep.tx_bytes ? ep.tx_bytes : (uint32_t)(A_STAGE_BYTES + C::B_STAGE_BYTES);
+      if constexpr (kHalo) {
+        // One input box per (tile, channel block), issued one step ahead of the filter tiles it goes with.
+        const int cblks = prob.cblks, taps = prob.R * prob.S;
+        typename P::Tile tn;                     // box iterator, one (tile, block) ahead
+        int it_n = 0, cb_n = 0, hs_n = 0;
+        uint32_t hph_n = 0;
+        bool more = prob.tile(0, tn);
+        auto issue_box = [&]() -> bool {
+          if (!more) return true;
+          if (!mbar_wait(&hempty[hs_n], hph_n ^ 1u, abort_flag)) return false;
+          mbar_expect_tx(&hfull[hs_n], ep.tx_bytes_a);
+          prob.load_halo(tn, cb_n, sA + hs_n * HALO_BYTES, &hfull[hs_n]);
+          if (++hs_n == nhalo) { hs_n = 0; hph_n ^= 1u; }
+          if (++cb_n == cblks) { cb_n = 0; more = prob.tile(++it_n, tn); }
+          return true;
+        };
+        ok = issue_box();
+        for (int it = 0; ok && prob.tile(it, t); ++it) {
+          for (int cb = 0; ok && cb < cblks; ++cb) {
+            ok = issue_box();                    // the next box travels while this block's filter tiles are fed
+            if (res_kb > 0) continue;
+            for (int tap = 0; ok && tap < taps; ++tap) {
+              if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+              mbar_expect_tx(&full[stage], (uint32_t)C::B_STAGE_BYTES);
+              prob.load_b(t, tap * cblks + cb, sB + stage * C::B_STAGE_BYTES, &full[stage]);
+              if (++stage == nstages) { stage = 0; phase ^= 1u; }
+            }
+          }
+        }
+      } else
       for (int it = 0; ok && prob.tile(it, t); ++it) {
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -209,8 +258,15 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, P::A_MN ? 1 : 0, P::B_MN ? 1 : 0);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      // The issuing thread is one lane with nothing to hide its instruction latency behind: every instruction
+      // between two tcgen05.mma widens the gap between them.  Descriptors are therefore built once and advanced
+      // by adding to their address field (bits 0-13, in 16-byte units; shared memory is < 256 KB, so no carry).
+      constexpr uint64_t kStepA = P::A_MN ? (2048 >> 4) : (32 >> 4);      // K advance of 16 elements
+      constexpr uint64_t kStepB = P::B_MN ? (2048 >> 4) : (32 >> 4);
+      const uint64_t a_desc0 = P::A_MN ? umma_smem_desc(smem_u32(sA), 8192, 1024) : umma_smem_desc(smem_u32(sA), 16, 1024);
+      const uint64_t b_desc0 = P::B_MN ? umma_smem_desc(smem_u32(sB), 8192, 1024) : umma_smem_desc(smem_u32(sB), 16, 1024);
+      int stage = 0, acc = 0, hs = 0;
+      uint32_t phase = 0, acc_phase = 0, hphase = 0;
       bool ok = true;
       typename P::Tile t;
       if (res_kb > 0 && prob.tile(0, t)) ok = mbar_wait(bres, 0u, abort_flag);
@@ -218,18 +274,51 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;                  // the tile's first MMA overwrites the accumulator
+        if constexpr (kHalo) {
+          const int cblks = prob.cblks, R = prob.R, S = prob.S;
+          const uint64_t row_step = (uint64_t)(prob.PW * 8);           // one box row of pixels, in 16-byte units
+          for (int cb = 0; ok && cb < cblks; ++cb) {
+            if (!mbar_wait(&hfull[hs], hphase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            // the window of tap (r, s): the same box, (r * PW + s) pixel rows (128 bytes each) further on
+            uint64_t a_row = a_desc0 + (uint64_t)(hs * (HALO_BYTES >> 4));
+            uint64_t b_tap = b_desc0 + (uint64_t)(cb * (C::B_STAGE_BYTES >> 4));       // resident: k-block tap*cblks+cb
+            const uint64_t b_tap_step = (uint64_t)(cblks * (C::B_STAGE_BYTES >> 4));
+            for (int r = 0; ok && r < R; ++r, a_row += row_step) {
+              uint64_t a_tap = a_row;
+              for (int sx = 0; sx < S; ++sx, a_tap += 8, b_tap += b_tap_step) {
+                uint64_t b_cur = b_tap;
+                if (res_kb == 0) {
+                  if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                  tc_fence_after();
+                  b_cur = b_desc0 + (uint64_t)(stage * (C::B_STAGE_BYTES >> 4));
+                }
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j) {
+                  umma_bf16(d_tmem, a_tap + j * kStepA, b_cur + j * kStepB, idesc, accumulate);
+                  accumulate = 1;
+                }
+                if (res_kb == 0) {
+                  umma_commit(&empty[stage]);
+                  if (++stage == nstages) { stage = 0; phase ^= 1u; }
+                }
+              }
+            }
+            if (!ok) break;
+            umma_commit(&hempty[hs]);
+            if (++hs == nhalo) { hs = 0; hphase ^= 1u; }
+          }
+        } else
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(sB + (res_kb > 0 ? kb : stage) * C::B_STAGE_BYTES);
+          const uint64_t a_cur = a_desc0 + (uint64_t)(stage * (A_STAGE_BYTES >> 4));
+          const uint64_t b_cur = b_desc0 + (uint64_t)((res_kb > 0 ? kb : stage) * (C::B_STAGE_BYTES >> 4));
 #pragma unroll
           for (int j = 0; j < BK / 16; ++j) {
-            const uint64_t adesc = P::A_MN ? umma_smem_desc(a_addr + j * 2048, 8192, 1024)
-                                           : umma_smem_desc(a_addr + j * 32, 16, 1024);
-            const uint64_t bdesc = P::B_MN ? umma_smem_desc(b_addr + j * 2048, 8192, 1024)
-                                           : umma_smem_desc(b_addr + j * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > t.kb0 || j > 0) ? 1u : 0u);
+            umma_bf16(d_tmem, a_cur + j * kStepA, b_cur + j * kStepB, idesc, accumulate);
+            accumulate = 1;
           }
           umma_commit(&empty[stage]);
           if (++stage == nstages) { stage = 0; phase ^= 1u; }
@@ -248,6 +337,7 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
     const int half = (warp - 2) >> 2;       // which 32 columns of a 64-column panel
     const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
     const int row = q * 32 + lane;          // tile row owned by this thread
+    const int drow = prob.out_row(row);     // its row in the stored tile (halo mode: margin rows have none)
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;                            // staging panel buffer in use (ring)
@@ -315,8 +405,10 @@ __device__ __forceinline__ void run(const P& prob, const Epilogue& ep) {
             // that read before it arrived at the previous panel's barrier (see below), so it is free.
             const int col0 = t.n0 + pnl * 64 + half * 32;
             if (has_res && !mbar_wait(&rfull[buf], (gpanel / NUM_PANEL_BUFS) & 1u, abort_flag)) { ok = false; break; }
-            if (plain) pack_row_to_panel<true>(rbuf[pnl & 1], panel, row, half, col0, ep, false);
-            else pack_row_to_panel<false>(rbuf[pnl & 1], panel, row, half, col0, ep, has_res);
+            if (drow >= 0) {
+              if (plain) pack_row_to_panel<true>(rbuf[pnl & 1], panel, drow, half, col0, ep, false);
+              else pack_row_to_panel<false>(rbuf[pnl & 1], panel, drow, half, col0, ep, has_res);
+            }
             fence_proxy_async();
             named_barrier_sync(1, NUM_EPI_THREADS);    // the panel is complete and visible to the TMA engine
             if (et == 0) {

@@ -11,6 +11,8 @@ from __future__ import annotations
 import ctypes as C
 from typing import Optional, Tuple
 
+import contextlib
+
 import torch
 import torch.nn.functional as F
 
@@ -70,6 +72,53 @@ def from_2d(y2d: torch.Tensor, n: int, h: int, w: int) -> torch.Tensor:
 _reference_only = False
 
 
+class _ZeroArena:
+    """One fp32 buffer cleared by a single memset at the start of a training step, from which the operators take
+    their zero-initialised scratch (statistics accumulators, fp32 weight-gradient accumulators) instead of each
+    launching a fill kernel of its own: about 180 fills per ResNet-50 step become one.  Only active inside
+    ``zero_arena()``; slices must not outlive the step (the users here consume them at once)."""
+
+    def __init__(self):
+        self.buf = None
+        self.off = 0
+        self.active = False
+
+    def begin(self, device, numel):
+        if self.buf is None or self.buf.device != device or self.buf.numel() < numel:
+            self.buf = torch.empty(numel, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.off = 0
+        self.active = True
+
+    def take(self, shape, device):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        n_al = (n + 63) // 64 * 64                      # keep every slice 256-byte aligned
+        if not self.active or self.buf.device != device or self.off + n_al > self.buf.numel():
+            return torch.zeros(shape, dtype=torch.float32, device=device)
+        out = self.buf[self.off:self.off + n].view(shape)
+        self.off += n_al
+        return out
+
+
+_arena = _ZeroArena()
+
+
+@contextlib.contextmanager
+def zero_arena(device, numel: int):
+    """Serve the operators' zeroed fp32 scratch from one buffer of ``numel`` floats for the duration of a step."""
+    _arena.begin(torch.device(device), numel)
+    try:
+        yield
+    finally:
+        _arena.active = False
+
+
+def zeros_f32(shape, device):
+    return _arena.take(tuple(shape), torch.device(device) if not isinstance(device, torch.device) else device)
+
+
 class reference_ops:
     """Context manager: run every op through its PyTorch restatement (the test oracle)."""
 
@@ -109,7 +158,7 @@ class _Conv1x1(torch.autograd.Function):
         cout = w.shape[0]
         x2d = nhwc_2d(x)
         w2d = w.reshape(cout, cin)
-        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        stats = zeros_f32((2, cout), x.device) if want_stats else None
         y2d = gemm(x2d, w2d, col_sum=stats[0] if want_stats else None, col_sqsum=stats[1] if want_stats else None)
         ctx.save_for_backward(x2d, w2d)
         ctx.dims = (n, h, wd, cin, cout, w.shape)
@@ -134,8 +183,8 @@ class _Conv1x1(torch.autograd.Function):
             res = nhwc_2d(d_tap.to(torch.bfloat16)) if d_tap is not None else None
             dx = from_2d(gemm(dy2d, w2d, b_kmajor=False, residual=res), n, h, wd)   # [M,Cout] x W[Cout(K),Cin(N)]
         if ctx.needs_input_grad[1]:
-            dw32 = gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False,
-                        splits=wgrad_splits(dy2d.shape[0], cout, cin))                      # [Cout, Cin] fp32
+            dw32 = gemm(dy2d, x2d, a_kmajor=False, b_kmajor=False, splits=wgrad_splits(dy2d.shape[0], cout, cin),
+                        out=zeros_f32((cout, cin), dy2d.device), accumulate=True)            # [Cout, Cin] fp32
             dw = dw32.to(torch.bfloat16).view(wshape)
         return dx, dw, None, None
 
@@ -210,7 +259,7 @@ class _StemConv(torch.autograd.Function):
         w2d = torch.zeros(cout, kpad // seg, seg, dtype=torch.bfloat16, device=x.device)
         w2d[:, :r, :s * c] = w.permute(0, 2, 3, 1).reshape(cout, r, s * c)   # [cout][r][(s, c)]
         w2d = w2d.view(cout, kpad)
-        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        stats = zeros_f32((2, cout), x.device) if want_stats else None
         y2d = gemm(col, w2d, col_sum=stats[0] if want_stats else None, col_sqsum=stats[1] if want_stats else None)
         ctx.save_for_backward(col)
         ctx.cfg = (cout, c, r, s, seg)
@@ -239,7 +288,7 @@ class _ConvKxK(torch.autograd.Function):
         cout, _, r, s = w.shape
         x2d = nhwc_2d(x)
         w_cl = w.contiguous(memory_format=torch.channels_last)        # [Cout, R, S, Cin] in memory
-        stats = torch.zeros(2, cout, dtype=torch.float32, device=x.device) if want_stats else None
+        stats = zeros_f32((2, cout), x.device) if want_stats else None
         y2d, ho, wo = _conv_native(x2d, w_cl, n, h, wd, cin, cout, r, s, stride, pad, stats)
         ctx.save_for_backward(x, w_cl)
         ctx.cfg = (stride, pad)
@@ -270,7 +319,7 @@ class _ConvKxK(torch.autograd.Function):
                 dx = torch.nn.grad.conv2d_input(x.shape, w, dy_cl, stride=stride, padding=pad)
         if ctx.needs_input_grad[1]:
             from .gemm import error_flag
-            dw32 = torch.zeros(cout, r, s, cin, dtype=torch.float32, device=x.device)   # [Cout][R][S][Cin]
+            dw32 = zeros_f32((cout, r, s, cin), x.device)                               # [Cout][R][S][Cin]
             _ck(_lib().esgd_conv2d_wgrad(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(), dw32.data_ptr(), n, h, wd,
                                          cin, cout, r, s, stride, pad, error_flag(x.device).data_ptr(), _stream(x)),
                 "conv2d weight gradient")

@@ -16,6 +16,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import contextlib
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -73,6 +75,8 @@ class TrainStep:
             self.opt = cls(inner, group, **kw)
             self.opt.grad_scale = 1.0 / self.loss_scale   # static loss scaling is undone inside the update
             self.autocast = False
+        n_params = sum(p.numel() for p in self.net.parameters())
+        self._arena_numel = n_params + 64 * (len(list(self.net.parameters())) + 8) + (1 << 20)
         self._xbuf = self._ybuf = None
         self._graph = None
         self.graph_kernel_launches = 0
@@ -119,11 +123,14 @@ class TrainStep:
             loss.backward()
             self.opt.step()
             return loss.detach()
-        else:
+        from ..ops.functional import zero_arena
+        # every operator's zeroed fp32 scratch (statistics, weight-gradient accumulators) comes out of one
+        # buffer cleared by a single memset per step
+        with zero_arena(self.device, self._arena_numel) if self.device.type == "cuda" else contextlib.nullcontext():
             logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
                               else x.to(self.compute_dtype))
-        loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
-        (loss * self.loss_scale if self.loss_scale != 1.0 else loss).backward()
+            loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
+            (loss * self.loss_scale if self.loss_scale != 1.0 else loss).backward()
         self.opt.step()
         return loss.detach()
 
