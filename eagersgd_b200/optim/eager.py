@@ -62,7 +62,7 @@ class EagerOptimizer:
                  limiter: int = 32, seed: int = 6545343, bucket_mb: float = 25.0,
                  average: str = "contributors", include_stale: bool = True, fused: Optional[bool] = None,
                  slot_dtype: Optional[torch.dtype] = None, overlap: bool = True, timeout_s: float = 30.0,
-                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 18,
+                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 26,
                  two_shot_parts: int = 5):
         self.optimizer = optimizer
         self.two_shot_min = two_shot_min   # bucket elements from which a round is reduced in two shots (None: never)

@@ -94,3 +94,27 @@ def test_stem_convolution_im2col_gemm():
     assert torch.allclose(y.float(), yr, rtol=3e-2, atol=5e-2)
     assert torch.allclose(stats[0], y.float().sum((0, 2, 3)), rtol=1e-3, atol=0.5)
     assert torch.allclose(wt.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k", [(8, 64, 56, 56, 64, 3), (6, 128, 28, 28, 128, 3), (4, 128, 14, 14, 64, 3),
+                                              (3, 64, 24, 24, 128, 5)])
+def test_halo_views_match_per_tap_loads(n, cin, h, w, cout, k, monkeypatch):
+    """Stride-1 convolutions read one input box per channel block and take the taps as shifted views of it;
+    the per-tap path (one TMA box per tap) is the same arithmetic in another order of the K steps."""
+    from eagersgd_b200.ops import functional as ops
+    from eagersgd_b200.ops.gemm import check_error
+    torch.manual_seed(n + h)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16)
+    wt = _cl(torch.randn(cout, cin, k, k, device=DEV) * (1.0 / (k * cin ** 0.5))).to(torch.bfloat16)
+    pad = (k - 1) // 2
+    y_halo, st_halo = ops.conv2d(x, wt, 1, pad, want_stats=True)
+    monkeypatch.setenv("ESGD_CONV_HALO", "0")
+    y_tap, st_tap = ops.conv2d(x, wt, 1, pad, want_stats=True)
+    monkeypatch.delenv("ESGD_CONV_HALO")
+    torch.cuda.synchronize()
+    check_error(x.device)
+    ref = F.conv2d(x.float(), wt.float(), None, 1, pad)
+    assert (y_halo.float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
+    assert (y_halo.float() - y_tap.float()).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    assert torch.allclose(st_halo[0], y_halo.float().sum((0, 2, 3)), rtol=1e-3, atol=0.5)
+    assert torch.allclose(st_halo, st_tap, rtol=2e-2, atol=2.0)
