@@ -42,6 +42,7 @@ def _lib():
         lib.esgd_conv2d_fwd_ex.argtypes = [vp, vp, vp] + [i32] * 11 + [i64, i64, i64, i32, vp, vp, vp, vp]
         lib.esgd_im2col_small_c.argtypes = [vp, vp] + [i32] * 10 + [vp]
         lib.esgd_conv2d_wgrad.argtypes = [vp, vp, vp] + [i32] * 9 + [vp, vp]
+        lib.esgd_conv2d_wgrad_halo.argtypes = [vp, vp, vp] + [i32] * 8 + [vp, vp]
         lib._nn_bound = True
     return lib
 
@@ -320,9 +321,17 @@ class _ConvKxK(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             from .gemm import error_flag
             dw32 = zeros_f32((cout, r, s, cin), x.device)                               # [Cout][R][S][Cin]
-            _ck(_lib().esgd_conv2d_wgrad(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(), dw32.data_ptr(), n, h, wd,
-                                         cin, cout, r, s, stride, pad, error_flag(x.device).data_ptr(), _stream(x)),
-                "conv2d weight gradient")
+            rc = -100
+            if stride == 1:      # shared input boxes, taps as shifted views (returns -100 outside its range)
+                rc = _lib().esgd_conv2d_wgrad_halo(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(),
+                                                   dw32.data_ptr(), n, h, wd, cin, cout, r, s, pad,
+                                                   error_flag(x.device).data_ptr(), _stream(x))
+                if rc != -100:
+                    _ck(rc, "conv2d weight gradient (shared boxes)")
+            if rc == -100:
+                _ck(_lib().esgd_conv2d_wgrad(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(), dw32.data_ptr(), n, h,
+                                             wd, cin, cout, r, s, stride, pad, error_flag(x.device).data_ptr(),
+                                             _stream(x)), "conv2d weight gradient")
             dw = dw32.to(w.dtype).permute(0, 3, 1, 2)
         return dx, dw, None, None, None
 

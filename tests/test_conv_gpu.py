@@ -118,3 +118,29 @@ def test_halo_views_match_per_tap_loads(n, cin, h, w, cout, k, monkeypatch):
     assert (y_halo.float() - y_tap.float()).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
     assert torch.allclose(st_halo[0], y_halo.float().sum((0, 2, 3)), rtol=1e-3, atol=0.5)
     assert torch.allclose(st_halo, st_tap, rtol=2e-2, atol=2.0)
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k", [(8, 64, 56, 56, 64, 3), (6, 128, 28, 28, 128, 3), (5, 64, 28, 28, 256, 3),
+                                              (3, 64, 24, 24, 72, 5), (40, 64, 56, 56, 64, 3)])
+def test_weight_gradient_with_shared_boxes(n, cin, h, w, cout, k, monkeypatch):
+    """Weight gradient from one dy box and one x box per block of rows (taps = shifted views) against the fp32
+    reference and against the per-tap kernel."""
+    from eagersgd_b200.ops import functional as ops
+    from eagersgd_b200.ops.gemm import check_error
+    torch.manual_seed(h + cout)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16)
+    wt = _cl(torch.randn(cout, cin, k, k, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    pad = (k - 1) // 2
+    y, _ = ops.conv2d(x, wt, 1, pad)
+    g = _cl(torch.randn_like(y.float()) * 0.1).to(torch.bfloat16)
+    (dw_shared,) = torch.autograd.grad(y, wt, g, retain_graph=True)
+    monkeypatch.setenv("ESGD_CONV_HALO", "0")
+    (dw_tap,) = torch.autograd.grad(y, wt, g, retain_graph=True)
+    monkeypatch.delenv("ESGD_CONV_HALO")
+    torch.cuda.synchronize()
+    check_error(x.device)
+    wr = wt.detach().float().requires_grad_()
+    F.conv2d(x.float(), wr, None, 1, pad).backward(g.float())
+    scale = wr.grad.abs().max().item()
+    assert (dw_shared.float() - wr.grad).abs().max().item() < 2e-2 * scale
+    assert (dw_shared.float() - dw_tap.float()).abs().max().item() < 2e-2 * scale
