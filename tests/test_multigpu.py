@@ -149,12 +149,12 @@ def _absent_rank(rank, world):
     es, group = _setup(rank, world)
     arena, ch, grad, out = _channel(group, 4096, "sync", -1, "sum", timeout_s=1.0)
     grad.fill_(1.0)
-    ch.step()                      # round 1: everyone joins
+    ch.step()                      # first round: everyone joins
     torch.cuda.synchronize()
     ok_first = bool(torch.all(out == float(world)))
     group.barrier()
     status = 0
-    if rank != world - 1:          # the last rank does not join round 2 (it stays alive and idle)
+    if rank != world - 1:          # the last rank does not join the second round (it stays alive and idle)
         ch.step()
         torch.cuda.synchronize()
         status = ch.stats()["status"]
