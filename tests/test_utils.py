@@ -1,0 +1,60 @@
+import os
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_fork_relaunches_script_as_ranks(tmp_path):
+    script = tmp_path / "prog.py"
+    script.write_text(textwrap.dedent('''
+        import os, sys
+        sys.path.insert(0, %r)
+        from eagersgd_b200.utils import fork, rank_env
+        role = fork(2, timeout=300)
+        if role == "child":
+            import torch.distributed as dist, torch
+            dist.init_process_group("gloo")
+            t = torch.tensor([float(rank_env()["rank"] + 1)])
+            dist.all_reduce(t)
+            open(os.path.join(%r, "rank%%d.txt" %% rank_env()["rank"]), "w").write(str(t.item()))
+            dist.destroy_process_group()
+        else:
+            print("parent done")
+    ''' % (ROOT, str(tmp_path))))
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "parent done" in r.stdout
+    assert (tmp_path / "rank0.txt").read_text() == "3.0" and (tmp_path / "rank1.txt").read_text() == "3.0"
+
+
+def test_device_descriptors_and_peaks(tmp_path):
+    import json
+    from eagersgd_b200.utils import CPUDevice, GPUDevice, describe, measured_peaks
+    assert not CPUDevice().is_gpu() and GPUDevice(1).is_gpu() and repr(GPUDevice(1)) == "cuda:1"
+    assert str(CPUDevice().torch_device()) == "cpu"
+    p = tmp_path / "peaks.json"
+    p.write_text(json.dumps({"hbm_gbs": 6000.0, "bf16_tflops": 1500.0}))
+    assert measured_peaks(str(p))["source"] == "measured" and measured_peaks(str(tmp_path / "none.json"))["source"] == "fallback"
+    d = describe()
+    assert d["nominal"]["sms"] == 148 and d["peaks"]["hbm_gbs"] > 0
+
+
+def test_zero_arena_hands_out_aligned_slices_and_falls_back():
+    import torch
+    from eagersgd_b200.ops import functional as ops
+    a = ops.zeros_f32((3, 5), torch.device("cpu"))            # inactive: plain zeros
+    assert a.shape == (3, 5) and float(a.abs().sum()) == 0.0
+    with ops.zero_arena("cpu", 256):
+        b = ops.zeros_f32((2, 10), torch.device("cpu"))
+        c = ops.zeros_f32((7,), torch.device("cpu"))
+        assert b.data_ptr() % 256 == c.data_ptr() % 256       # 64-float granularity
+        assert c.data_ptr() - b.data_ptr() == 64 * 4
+        b.add_(1.0)
+        big = ops.zeros_f32((1000,), torch.device("cpu"))     # does not fit: falls back
+        assert float(big.sum()) == 0.0 and big.numel() == 1000
+    with ops.zero_arena("cpu", 256):                           # a new step starts from zeros again
+        b2 = ops.zeros_f32((2, 10), torch.device("cpu"))
+        assert float(b2.sum()) == 0.0
+    assert float(ops.zeros_f32((4,), torch.device("cpu")).sum()) == 0.0
