@@ -262,14 +262,14 @@ int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, in
 extern "C" {
 
 // Returns -100 when the shape is outside this kernel's range (the caller then uses the per-tap kernel).
-// dw: fp32 [Cout][R][S][Cin], zeroed by the caller.  Stride 1 only; Cin % 64 == 0, Cin <= 128, Cout % 8 == 0.
+// dw: fp32 [Cout][R][S][Cin], zeroed by the caller.  Stride 1 only; Cin % 64 == 0, Cout % 8 == 0.
 int esgd_conv2d_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, int W, int Cin, int Cout, int R,
                            int S, int pad, int* error_flag, void* stream) {
   {
     const char* e = getenv("ESGD_CONV_HALO");          // the same switch as the forward halo mode
     if (e != nullptr && e[0] == '0') return -100;
   }
-  if (Cin % 64 || Cin > 128 || Cout % 8 || R * S < 2) return -100;
+  if (Cin % 64 || Cout % 8 || R * S < 2) return -100;
   const int Ho = H + 2 * pad - R + 1, Wo = W + 2 * pad - S + 1;
   const int PW = Wo + S - 1;
   if (Ho < 1 || Wo < 1 || PW > 128) return -100;
@@ -278,8 +278,11 @@ int esgd_conv2d_wgrad_halo(const void* x, const void* dy, float* dw, int N, int 
   if (bh == 0 || bh * Wo < 48) return -100;
   if (PW > 256 || bh + R - 1 > 256) return -100;
   cudaStream_t s = (cudaStream_t)stream;
-  return Cin <= 64 ? launch_wgrad_halo<64>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s)
-                   : launch_wgrad_halo<128>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
+  int rc;
+  if (Cin <= 64) rc = launch_wgrad_halo<64>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
+  else if (Cin <= 128) rc = launch_wgrad_halo<128>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
+  else rc = launch_wgrad_halo<256>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
+  return rc == -7 ? -100 : rc;          // boxes too large for two stages: the per-tap kernel takes the shape
 }
 
 }  // extern "C"

@@ -121,7 +121,8 @@ def test_halo_views_match_per_tap_loads(n, cin, h, w, cout, k, monkeypatch):
 
 
 @pytest.mark.parametrize("n,cin,h,w,cout,k", [(8, 64, 56, 56, 64, 3), (6, 128, 28, 28, 128, 3), (5, 64, 28, 28, 256, 3),
-                                              (3, 64, 24, 24, 72, 5), (40, 64, 56, 56, 64, 3)])
+                                              (3, 64, 24, 24, 72, 5), (40, 64, 56, 56, 64, 3), (12, 256, 14, 14, 256, 3),
+                                              (16, 512, 7, 7, 512, 3)])
 def test_weight_gradient_with_shared_boxes(n, cin, h, w, cout, k, monkeypatch):
     """Weight gradient from one dy box and one x box per block of rows (taps = shifted views) against the fp32
     reference and against the per-tap kernel."""
