@@ -1,0 +1,73 @@
+"""Micro-benchmark of the host operation runtime: creation, execution and deletion of an allreduce schedule.
+
+    python -m eagersgd_b200.parallel.bench_oprt [--ranks 4] [--count 1024] [--iters 100]
+
+The protocol of the reference's benchmark (fflib2 benchmark/allreduce.c:11-99: int32, 100 timed iterations,
+schedule creation / execution / deletion recorded separately), with ranks as threads of this process and a
+plain numpy sum over the ranks' buffers as the baseline where the reference uses ``MPI_Allreduce``.
+Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import threading
+import time
+
+import numpy as np
+
+from . import oprt as R
+
+
+def run(ranks: int, count: int, iters: int) -> dict:
+    t_create = [0.0] * ranks
+    t_exec = [0.0] * ranks
+    ok = [True] * ranks
+    with R.World(ranks) as w:
+        barrier = threading.Barrier(ranks)
+
+        def body(r):
+            snd = np.zeros(count, dtype=np.int32)
+            rcv = np.zeros(count, dtype=np.int32)
+            t0 = time.perf_counter()
+            s = r.allreduce(r.buffer(snd), r.buffer(rcv), tag=1)
+            t_create[r.id] = time.perf_counter() - t0
+            for it in range(iters + 5):
+                snd[:] = r.id + it
+                barrier.wait()
+                t0 = time.perf_counter()
+                r.schedule_post(s)
+                r.schedule_wait(s)
+                if it >= 5:
+                    t_exec[r.id] += time.perf_counter() - t0
+                ok[r.id] = ok[r.id] and bool(np.all(rcv == it * ranks + ranks * (ranks - 1) // 2))
+        th = [threading.Thread(target=body, args=(w.ranks[i],)) for i in range(ranks)]
+        t0 = time.perf_counter()
+        [t.start() for t in th]
+        [t.join() for t in th]
+        t_total = time.perf_counter() - t0
+        t0 = time.perf_counter()
+    t_delete = time.perf_counter() - t0                       # world (and every schedule in it) torn down
+    bufs = [np.full(count, i, dtype=np.int32) for i in range(ranks)]
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        np.sum(bufs, axis=0)
+    t_numpy = (time.perf_counter() - t0) / iters
+    return {"ranks": ranks, "count": count, "dtype": "int32", "iters": iters, "correct": all(ok),
+            "create_us": 1e6 * max(t_create), "execute_us": 1e6 * max(t_exec) / iters, "delete_us": 1e6 * t_delete,
+            "numpy_sum_us": 1e6 * t_numpy, "wall_s": t_total}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ranks", type=int, default=4)
+    ap.add_argument("--count", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=100)
+    args = ap.parse_args(argv)
+    print(json.dumps(run(args.ranks, args.count, args.iters)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -216,3 +216,9 @@ def test_wait_timeout_reports_instead_of_hanging():
         rv = r0.recv(r0.buffer(count=4, dtype=np.int32), 1, 99)
         r0.post(rv)
         assert r0.wait(rv, timeout=0.2) == R.TIMEOUT
+
+
+def test_runtime_microbenchmark_reports_three_phases():
+    from eagersgd_b200.parallel.bench_oprt import run
+    r = run(ranks=3, count=256, iters=10)
+    assert r["correct"] and r["create_us"] > 0 and r["execute_us"] > 0 and r["delete_us"] >= 0
