@@ -125,7 +125,6 @@ def main():
 
     import torch
     import torch.distributed as dist
-    import torch.nn.functional as F
 
     import eagersgd_b200 as es
     from eagersgd_b200.models.resnet import cifar_resnet, imagenet_resnet
@@ -165,7 +164,6 @@ def main():
     else:
         # 2-layer LSTM (hidden 2048) on 2048-d frame features; per-sample length from a clipped log-normal over
         # 30..1800 frames, length-bucketed batches, left-padded: the per-rank sequence length IS the imbalance
-        import numpy as np
         from eagersgd_b200.data import BucketSampler, SyntheticSequenceDataset
         batch, classes, unit = args.batch or 16, 101, "sequences/s"
         model, name = LSTMClassifier(2048, 2048, 2, classes), "2-layer LSTM classifier (hidden 2048)"

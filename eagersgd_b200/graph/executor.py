@@ -10,7 +10,7 @@ of its gradient extension ops (extended_operations.py:27-77), which no backend t
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import numpy as np
 import torch
@@ -18,7 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
-from .ir import Graph, Operation, Visitor
+from .ir import Graph, Visitor
 
 
 class _Forward(Visitor):

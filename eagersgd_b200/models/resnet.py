@@ -12,11 +12,9 @@ Activations are NHWC (channels_last) bf16 on GPUs.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
-import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops import functional as ops
 

@@ -15,9 +15,8 @@ import hashlib
 import os
 import subprocess
 import tempfile
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
-import numpy as np
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

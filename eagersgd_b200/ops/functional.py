@@ -9,7 +9,7 @@ PyTorch, which is what the CPU tests and oracles use.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
+from typing import Optional
 
 import contextlib
 

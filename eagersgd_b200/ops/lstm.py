@@ -14,7 +14,6 @@ Stands where the reference calls ``torch.nn.LSTM`` (cuDNN) in its video classifi
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
 
 import torch
 

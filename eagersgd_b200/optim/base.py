@@ -13,7 +13,6 @@ from typing import Callable, Dict, Optional
 
 import torch
 
-from ..train.events import StopTraining
 
 
 class Optimizer:

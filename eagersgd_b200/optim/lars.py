@@ -8,7 +8,7 @@ multi-tensor reductions per step.
 """
 from __future__ import annotations
 
-from typing import Callable, Iterable, Optional
+from typing import Callable, Optional
 
 import torch
 

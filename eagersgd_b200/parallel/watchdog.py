@@ -9,7 +9,6 @@ rank hangs the others at the next synchronous round.
 from __future__ import annotations
 
 import threading
-import time
 from typing import Callable, Optional
 
 from ._native import ChannelError

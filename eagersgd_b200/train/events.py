@@ -14,7 +14,7 @@ import csv
 import json
 import sys
 import time
-from typing import Callable, Dict, List, Optional
+from typing import Callable, List, Optional
 
 
 class StopTraining(Exception):

@@ -20,7 +20,6 @@ import contextlib
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..optim.eager import MajorityAllreduceOptimizer, SoloAllreduceOptimizer, SyncAllreduceOptimizer
 from ..parallel import _native as N

@@ -10,7 +10,6 @@ import time
 from typing import Optional, Sequence
 
 import numpy as np
-import torch
 
 from .events import EpochSummary, StopTraining, SummaryGeneratorEvent, TrainingStatistics
 
