@@ -87,6 +87,49 @@ class _Forward(Visitor):
     def visit_identity(self, op, g): self._out(op, self._in(op, 0))
     def visit_concat(self, op, g): self._out(op, torch.cat([self.v[i] for i in op.inputs], op.attrs.get("axis", 1)))
 
+    # elementwise / shape operators of the reference's PyTorch visitor (pytorch_visitor.py) beyond the ResNet set
+    def visit_sub(self, op, g): self._out(op, self._in(op, 0) - self._in(op, 1))
+    def visit_mul(self, op, g): self._out(op, self._in(op, 0) * self._in(op, 1))
+    def visit_div(self, op, g): self._out(op, self._in(op, 0) / self._in(op, 1))
+    def visit_neg(self, op, g): self._out(op, -self._in(op, 0))
+    def visit_abs(self, op, g): self._out(op, self._in(op, 0).abs())
+    def visit_exp(self, op, g): self._out(op, self._in(op, 0).exp())
+    def visit_log(self, op, g): self._out(op, self._in(op, 0).log())
+    def visit_sqrt(self, op, g): self._out(op, self._in(op, 0).sqrt())
+    def visit_pow(self, op, g): self._out(op, self._in(op, 0) ** self._in(op, 1))
+    def visit_sigmoid(self, op, g): self._out(op, torch.sigmoid(self._in(op, 0)))
+    def visit_tanh(self, op, g): self._out(op, torch.tanh(self._in(op, 0)))
+    def visit_leakyrelu(self, op, g): self._out(op, F.leaky_relu(self._in(op, 0), op.attrs.get("alpha", 0.01)))
+    def visit_transpose(self, op, g): self._out(op, self._in(op, 0).permute(*op.attrs["perm"]))
+    def visit_logsoftmax(self, op, g): self._out(op, F.log_softmax(self._in(op, 0).float(), op.attrs.get("axis", -1)))
+
+    def visit_clip(self, op, g):
+        self._out(op, self._in(op, 0).clamp(op.attrs.get("min", None), op.attrs.get("max", None)))
+
+    def visit_reducemean(self, op, g):
+        self._out(op, self._in(op, 0).mean(dim=op.attrs["axes"], keepdim=bool(op.attrs.get("keepdims", 1))))
+
+    def visit_reducesum(self, op, g):
+        self._out(op, self._in(op, 0).sum(dim=op.attrs["axes"], keepdim=bool(op.attrs.get("keepdims", 1))))
+
+    def visit_constant(self, op, g):
+        value = np.asarray(op.attrs["value"])
+        if value.dtype == np.float64:                 # python floats: ONNX constants are float32 unless typed
+            value = value.astype(np.float32)
+        self._out(op, torch.as_tensor(value).to(next(self.net.parameters()).device))
+
+    def visit_pad(self, op, g):
+        pads = op.attrs["pads"]                       # ONNX order: begins of all axes, then ends
+        n = len(pads) // 2
+        torch_pads = []
+        for ax in reversed(range(n)):
+            torch_pads += [pads[ax], pads[ax + n]]
+        self._out(op, F.pad(self._in(op, 0), torch_pads, value=op.attrs.get("value", 0.0)))
+
+    def visit_lrn(self, op, g):
+        self._out(op, F.local_response_norm(self._in(op, 0), op.attrs["size"], op.attrs.get("alpha", 1e-4),
+                                            op.attrs.get("beta", 0.75), op.attrs.get("bias", 1.0)))
+
     def visit_dropout(self, op, g):
         self._out(op, F.dropout(self._in(op, 0), op.attrs.get("ratio", 0.5), self.net.training))
 

@@ -17,7 +17,9 @@ import numpy as np
 
 # op types understood by the executor (ONNX names) plus the reference's extensions
 STANDARD_OPS = ("Conv", "BatchNormalization", "Relu", "MaxPool", "AveragePool", "GlobalAveragePool", "Gemm", "MatMul",
-                "Add", "Sum", "Flatten", "Reshape", "Squeeze", "Unsqueeze", "Softmax", "Dropout", "Identity", "Concat")
+                "Add", "Sum", "Flatten", "Reshape", "Squeeze", "Unsqueeze", "Softmax", "Dropout", "Identity", "Concat",
+                "Sub", "Mul", "Div", "Neg", "Abs", "Exp", "Log", "Sqrt", "Pow", "Sigmoid", "Tanh", "LeakyRelu", "Transpose",
+                "LogSoftmax", "Clip", "ReduceMean", "ReduceSum", "Constant", "Pad", "LRN")
 LOSS_OPS = ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError")
 EXTENSION_OPS = ("StopGradient", "AllReduceGradients")
 

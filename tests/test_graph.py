@@ -59,3 +59,26 @@ def test_graph_training_with_loss_and_extensions():
     g.add_output("frozen")
     outs = GraphNetwork(g)(x, label=y)
     assert not outs[-1].requires_grad
+
+
+def test_elementwise_and_shape_operators():
+    import torch.nn.functional as F
+    g = Graph("misc")
+    g.add_input("x")
+    g.add_initializer("w", np.full((1, 3, 1, 1), 2.0, np.float32))
+    g.add("Mul", ["x", "w"], ["a"])
+    g.add("Constant", [], ["one"], value=[[[[1.0]]]])
+    g.add("Sub", ["a", "one"], ["b"])
+    g.add("LeakyRelu", ["b"], ["c"], alpha=0.1)
+    g.add("Pad", ["c"], ["d"], pads=[0, 0, 1, 2, 0, 0, 3, 4], value=0.0)
+    g.add("ReduceMean", ["d"], ["e"], axes=[2, 3], keepdims=0)
+    g.add("Transpose", ["e"], ["f"], perm=[1, 0])
+    g.add("Tanh", ["f"], ["h"])
+    g.add("Clip", ["h"], ["out"], min=-0.5, max=0.5)
+    g.add_output("out")
+    from eagersgd_b200.graph import STANDARD_OPS
+    assert all(op.op_type in STANDARD_OPS for op in g.ops)
+    x = torch.randn(2, 3, 4, 5)
+    out = GraphNetwork(g)(x)
+    ref = F.pad(F.leaky_relu(x * 2.0 - 1.0, 0.1), [2, 4, 1, 3]).mean((2, 3)).t().tanh().clamp(-0.5, 0.5)
+    assert out.shape == (3, 2) and torch.allclose(out, ref, atol=1e-6)
