@@ -54,7 +54,11 @@ def timeit(fn, iters: int, flush: bool = True, graph: bool = True) -> float:
     if graph:
         try:
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            cur = torch.cuda.current_stream()
+            # Capture on the stream the tensors were created on (main() runs everything on one side stream): a
+            # gradient taken with respect to a leaf created on another stream makes autograd synchronise the two
+            # streams, which is not allowed inside a capture.
+            with (torch.cuda.graph(g, stream=cur) if cur != torch.cuda.default_stream() else torch.cuda.graph(g)):
                 fn()
             fn = g.replay
             fn()
@@ -235,6 +239,11 @@ def main(argv=None):
     ap.add_argument("--residual", action="store_true")
     args = ap.parse_args(argv)
     assert torch.cuda.is_available(), "the kernels need a CUDA device"
+    with torch.cuda.stream(torch.cuda.Stream()):      # tensors, warm-up, capture and replay share this stream
+        return _run_cases(args)
+
+
+def _run_cases(args):
     if args.op == "suite":
         for op, shape in SUITE:
             print(json.dumps(run(op, shape, args.iters)), flush=True)
