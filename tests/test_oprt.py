@@ -222,3 +222,21 @@ def test_runtime_microbenchmark_reports_three_phases():
     from eagersgd_b200.parallel.bench_oprt import run
     r = run(ranks=3, count=256, iters=10)
     assert r["correct"] and r["create_us"] > 0 and r["execute_us"] > 0 and r["delete_us"] >= 0
+
+
+@pytest.mark.parametrize("world", [2, 3, 5, 8])
+def test_activation_stress_300_rounds(world):
+    """The reference loops its activation test 300 times from a shell script (evaluation/test_activation.sh);
+    here 300 activations from shared-seed random ranks run back to back on one persistent schedule."""
+    n = 300
+    rng = np.random.RandomState(1000 + world)
+    activators = rng.randint(world, size=n)
+    with R.World(world) as w:
+        def body(r):
+            s, act, joined = r.activation(tag=9)
+            for k in range(n):
+                if activators[k] == r.id:
+                    r.post(act)
+                assert r.wait(joined, timeout=60.0) == R.SUCCESS
+            assert r.completions(joined) == n
+        _run(w, body)
