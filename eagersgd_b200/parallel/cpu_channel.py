@@ -7,6 +7,7 @@ ffrand_allreduce.c, ffallreduce.c), which is how eager-SGD runs without a GPU.
 """
 from __future__ import annotations
 
+import atexit
 import ctypes as C
 import os
 import uuid
@@ -74,8 +75,13 @@ class SharedSegments:
             self._views.append(view)
             self.bases.append(view.ctypes.data)
         exchange("ready")  # every peer has mapped every segment before anyone proceeds
+        self._closed = False
+        atexit.register(self.close)   # a program that forgets close() still unmaps and unlinks in the right order
 
     def close(self):
+        if getattr(self, "_closed", True):
+            return
+        self._closed = True
         self._views = []
         self.bases = []
         for seg in self._peers:

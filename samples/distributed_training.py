@@ -60,6 +60,8 @@ def main():
             opt.step({"x": x, "y": y})
     group.barrier()
     err = (model.linear.weight.detach().view(-1) - data.w_star).norm() / data.w_star.norm()
+    if hasattr(opt, "close"):
+        opt.close()
     if group.rank == 0:
         print("scheme %s: %d steps in %.2f s (%.1f steps/s), relative error %.4f"
               % (args.scheme, args.steps, time.time() - t0, args.steps / (time.time() - t0), err))
