@@ -33,7 +33,7 @@ def main():
     assert diff < 1e-3
     loaded.add_loss("SoftmaxCrossEntropy", "logits")
     logits, loss = GraphNetwork(loaded).eval()(x, label=torch.randint(0, 10, (4,)))
-    print("with a loss node appended: loss = %.4f" % float(loss))
+    print("with a loss node appended: loss = %.4f" % float(loss.detach()))
 
 
 if __name__ == "__main__":

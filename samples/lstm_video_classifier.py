@@ -58,7 +58,7 @@ def main():
         torch.cuda.synchronize()
     if group.rank == 0:
         print("mode %s: %.1f sequences/s per rank, last loss %.4f, stats %s"
-              % (args.mode, seqs / (time.time() - t0), float(loss), opt.stats()))
+              % (args.mode, seqs / (time.time() - t0), float(loss.detach()), opt.stats()))
     opt.close()
     es.finalize()
 

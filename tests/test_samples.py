@@ -15,6 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("partial_allreduce_cpu.py", ["--mode", "solo", "--steps", "8"]),
     ("partial_allreduce_cpu.py", ["--mode", "majority", "--steps", "8"]),
     ("graph_inference.py", []),
+    ("lstm_video_classifier.py", ["--steps", "2", "--hidden", "32", "--max-length", "20", "--batch", "4"]),
 ])
 def test_sample_runs(script, args):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "samples", script)] + args, capture_output=True, text=True,
