@@ -4,6 +4,7 @@
     python -m eagersgd_b200.ops.bench_ops --op conv --shape 64,128,56,56,128,3,1      (N,Cin,H,W,Cout,k,stride)
     python -m eagersgd_b200.ops.bench_ops --op conv_wgrad --shape 64,128,28,28,128,3,1
     python -m eagersgd_b200.ops.bench_ops --op bn --shape 256,256,56,56 [--backward]
+    python -m eagersgd_b200.ops.bench_ops --op lstm --shape 64,16,2048,2048              (T,B,I,H)
     python -m eagersgd_b200.ops.bench_ops --op suite
 
 Timing: 3 warm-up calls, then ``--iters`` calls between CUDA events on the launching stream with a
@@ -179,6 +180,25 @@ def bench_ce(shape, iters):
     return dict(op="softmax_ce_fwd+grad", B=b, C=c, ms=ms, gbs=3 * b * c * 4.0 / ms / 1e6, library_ms=ms_lib)
 
 
+def bench_lstm(shape, iters):
+    """One LSTM layer, forward + backward: T steps of batch B, input I, hidden H (recurrent GEMM with swapped
+    operands + fused gate kernel per step) against torch.nn.LSTM (cuDNN)."""
+    from .lstm import lstm_layer
+    T, B, I, H = shape
+    x = torch.randn(T, B, I, device="cuda").to(torch.bfloat16).requires_grad_()
+    w_ih = (torch.randn(4 * H, I, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+    w_hh = (torch.randn(4 * H, H, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+    bias = torch.zeros(4 * H, device="cuda", requires_grad=True)
+    g = torch.randn(T, B, H, device="cuda").to(torch.bfloat16)
+    ms = timeit(lambda: torch.autograd.grad(lstm_layer(x, w_ih, w_hh, bias), (x, w_ih, w_hh), g), iters, graph=False)
+    ref = torch.nn.LSTM(I, H).cuda().to(torch.bfloat16)
+    ms_lib = timeit(lambda: torch.autograd.grad(ref(x)[0], (x,) + tuple(ref.parameters()), g), iters, graph=False)
+    flops = 3 * 2.0 * T * B * 4 * H * (I + H)
+    byts = 3 * 2.0 * T * 4 * H * H                      # the recurrent weights are re-read every step, fwd and bwd
+    return dict(op="lstm_layer_fwd+bwd", T=T, B=B, I=I, H=H, ms=ms, tflops=flops / ms / 1e9, gbs=byts / ms / 1e6,
+                library_ms=ms_lib)
+
+
 def bench_update(shape, iters):
     """The fused reduce + momentum-SGD kernel path of a single-rank channel (pack, control, update)."""
     from ..parallel.nvlink_channel import NvlinkChannel, create_arenas
@@ -219,6 +239,8 @@ def run(op, shape, iters, backward=False, residual=False):
         r = bench_bn(shape, iters, backward, residual)
     elif op == "ce":
         r = bench_ce(shape, iters)
+    elif op == "lstm":
+        r = bench_lstm(shape, iters)
     elif op == "update":
         r = bench_update(shape, iters)
     else:
