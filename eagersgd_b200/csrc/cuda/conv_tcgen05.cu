@@ -506,4 +506,30 @@ int esgd_conv2d_fwd_ex(const void* x, const void* w, void* y, int N, int H, int 
   return launch<256>(a, ep, s);
 }
 
+// Host arithmetic of the halo-mode forward / data-gradient launch, without launching (no device needed).
+// out[0..9]: applicable (0/1), BH, PW, BN, resident filter k-blocks (0: streamed), input-box slots, filter stages,
+// bytes of one input box, bytes the most shifted view reaches, stage area used.
+void esgd_conv2d_halo_plan(int N, int H, int W, int Cin, int Cout, int R, int S, int stride, int pad, int* out) {
+  for (int i = 0; i < 10; ++i) out[i] = 0;
+  if (Cin % 64 || Cout % 8) return;
+  ConvArgs a{nullptr, nullptr, nullptr, N, H, W, Cin, Cout, R, S, stride, pad};
+  const int BN = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
+  int bh = 0;
+  if (BN > 128 || stride != 1 || !halo_applicable(a, H + 2 * pad - R + 1, W + 2 * pad - S + 1, &bh)) return;
+  const int PW = W + 2 * pad;
+  const int b_stage = BN * 128, stage_area = BN == 64 ? Cfg<64>::STAGE_AREA : Cfg<128>::STAGE_AREA;
+  const int kb_total = R * S * (Cin / 64);
+  const int res_kb = (kb_total * b_stage + 2 * HALO_BYTES <= stage_area) ? kb_total : 0;
+  const int nhalo = res_kb > 0 ? 2 : MAX_HALOS;
+  int nstages = 1;
+  if (res_kb == 0) {
+    nstages = (stage_area - nhalo * HALO_BYTES) / b_stage;
+    if (nstages > 8) nstages = 8;
+  }
+  out[0] = 1; out[1] = bh; out[2] = PW; out[3] = BN; out[4] = res_kb; out[5] = nhalo; out[6] = nstages;
+  out[7] = PW * (bh + R - 1) * 128;
+  out[8] = ((R - 1) * PW + (S - 1) + BM) * 128;
+  out[9] = nhalo * HALO_BYTES + (res_kb > 0 ? res_kb : nstages) * b_stage;
+}
+
 }  // extern "C"

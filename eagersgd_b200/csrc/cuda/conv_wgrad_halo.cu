@@ -197,16 +197,9 @@ int wg_sm_count() {
   return n;
 }
 
-template <int BN>
-int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, int W, int Cin, int Cout, int R, int S,
-                      int pad, int bh, int* error_flag, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(conv_wgrad_halo_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
-  WgHaloParams p;
+// Geometry of a launch (host arithmetic only, shared by the launcher and by the plan query that the CPU tests
+// sweep): box sizes, stages, tap sets, pixel splits.  Returns -7 when two stages do not fit.
+int wg_plan(WgHaloParams& p, int BN, int N, int H, int W, int Cin, int Cout, int R, int S, int pad, int bh, int sms) {
   p.N = N; p.Cout = Cout; p.Cin = Cin; p.R = R; p.S = S; p.pad = pad;
   p.Ho = H + 2 * pad - R + 1;
   p.Wo = W + 2 * pad - S + 1;
@@ -228,13 +221,40 @@ int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, in
   p.m_tiles = (Cout + 127) / 128;
   p.n_tiles = (Cin + BN - 1) / BN;
   p.boxes_total = p.h_tiles * N;
-  const int sms = wg_sm_count();
   const int base = p.sets * p.m_tiles * p.n_tiles;
   int splits = (2 * sms + base - 1) / base;                   // two waves of CTAs
   if (splits > p.boxes_total) splits = p.boxes_total;
   if (splits < 1) splits = 1;
   p.boxes_per_split = (p.boxes_total + splits - 1) / splits;
   p.splits = (p.boxes_total + p.boxes_per_split - 1) / p.boxes_per_split;
+  return 0;
+}
+
+// Largest number of full output rows whose pitched pixels fit one 128-row K range; 0: outside this kernel's range.
+int wg_pick_bh(int H, int W, int Cin, int Cout, int R, int S, int pad) {
+  if (Cin % 64 || Cout % 8 || R * S < 2) return 0;
+  const int Ho = H + 2 * pad - R + 1, Wo = W + 2 * pad - S + 1;
+  const int PW = Wo + S - 1;
+  if (Ho < 1 || Wo < 1 || PW > 128) return 0;
+  int bh = 0;
+  for (int d = 1; d * PW <= 128 && d <= Ho; ++d) if (Ho % d == 0) bh = d;
+  if (bh == 0 || bh * Wo < 48) return 0;
+  if (bh + R - 1 > 256) return 0;
+  return bh;
+}
+
+template <int BN>
+int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, int W, int Cin, int Cout, int R, int S,
+                      int pad, int bh, int* error_flag, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(conv_wgrad_halo_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, WG_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  WgHaloParams p;
+  const int pr = wg_plan(p, BN, N, H, W, Cin, Cout, R, S, pad, bh, wg_sm_count());
+  if (pr != 0) return pr;
   p.dw = dw;
   p.error_flag = error_flag;
   {
@@ -251,7 +271,7 @@ int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, in
     int r = esgd::make_tensormap_bf16(&p.tmX, x, 4, dims, strides, box, nullptr);
     if (r != 0) return 2000 + r;
   }
-  const int grid = base * p.splits;
+  const int grid = p.sets * p.m_tiles * p.n_tiles * p.splits;
   conv_wgrad_halo_kernel<BN><<<grid, WG_THREADS, WG_SMEM, stream>>>(p);
   esgd::count_launch();
   return (int)cudaGetLastError();
@@ -269,20 +289,30 @@ int esgd_conv2d_wgrad_halo(const void* x, const void* dy, float* dw, int N, int 
     const char* e = getenv("ESGD_CONV_HALO");          // the same switch as the forward halo mode
     if (e != nullptr && e[0] == '0') return -100;
   }
-  if (Cin % 64 || Cout % 8 || R * S < 2) return -100;
-  const int Ho = H + 2 * pad - R + 1, Wo = W + 2 * pad - S + 1;
-  const int PW = Wo + S - 1;
-  if (Ho < 1 || Wo < 1 || PW > 128) return -100;
-  int bh = 0;
-  for (int d = 1; d * PW <= 128 && d <= Ho; ++d) if (Ho % d == 0) bh = d;
-  if (bh == 0 || bh * Wo < 48) return -100;
-  if (PW > 256 || bh + R - 1 > 256) return -100;
+  const int bh = wg_pick_bh(H, W, Cin, Cout, R, S, pad);
+  if (bh == 0) return -100;
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if (Cin <= 64) rc = launch_wgrad_halo<64>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
   else if (Cin <= 128) rc = launch_wgrad_halo<128>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
   else rc = launch_wgrad_halo<256>(x, dy, dw, N, H, W, Cin, Cout, R, S, pad, bh, error_flag, s);
   return rc == -7 ? -100 : rc;          // boxes too large for two stages: the per-tap kernel takes the shape
+}
+
+// Host arithmetic of a launch without launching anything (no device needed).  out[0..11]: applicable (0/1), BH, PW,
+// ksteps, abox, xbox, nstages, sets, taps_per_set, splits, boxes_per_split, grid; out[12] = BN, out[13] = shared
+// memory requested, out[14] = m_tiles, out[15] = n_tiles.
+void esgd_conv2d_wgrad_halo_plan(int N, int H, int W, int Cin, int Cout, int R, int S, int pad, int sms, int* out) {
+  for (int i = 0; i < 16; ++i) out[i] = 0;
+  const int bh = wg_pick_bh(H, W, Cin, Cout, R, S, pad);
+  if (bh == 0) return;
+  const int BN = Cin <= 64 ? 64 : (Cin <= 128 ? 128 : 256);
+  WgHaloParams p;
+  if (wg_plan(p, BN, N, H, W, Cin, Cout, R, S, pad, bh, sms) != 0) return;
+  out[0] = 1; out[1] = p.BH; out[2] = p.PW; out[3] = p.ksteps; out[4] = p.abox; out[5] = p.xbox; out[6] = p.nstages;
+  out[7] = p.sets; out[8] = p.taps_per_set; out[9] = p.splits; out[10] = p.boxes_per_split;
+  out[11] = p.sets * p.m_tiles * p.n_tiles * p.splits; out[12] = BN; out[13] = WG_SMEM; out[14] = p.m_tiles;
+  out[15] = p.n_tiles;
 }
 
 }  // extern "C"
