@@ -82,12 +82,17 @@ class _ZeroArena:
     def __init__(self):
         self.buf = None
         self.off = 0
+        self.dirty = 0          # floats handed out in any step so far: the prefix that has to be cleared again
+        self.cap = 0
+        self.device = None
         self.active = False
 
     def begin(self, device, numel):
-        if self.buf is None or self.buf.device != device or self.buf.numel() < numel:
-            self.buf = torch.empty(numel, dtype=torch.float32, device=device)
-        self.buf.zero_()
+        if self.buf is not None and (self.buf.device != device or self.buf.numel() < numel):
+            self.buf, self.dirty = None, 0
+        self.device, self.cap = device, numel
+        if self.buf is not None and self.dirty > 0:
+            self.buf[:self.dirty].zero_()                # one memset over what earlier steps used
         self.off = 0
         self.active = True
 
@@ -96,10 +101,13 @@ class _ZeroArena:
         for d in shape:
             n *= int(d)
         n_al = (n + 63) // 64 * 64                      # keep every slice 256-byte aligned
-        if not self.active or self.buf.device != device or self.off + n_al > self.buf.numel():
+        if not self.active or self.device != device or self.off + n_al > self.cap:
             return torch.zeros(shape, dtype=torch.float32, device=device)
+        if self.buf is None:                             # first use: models that never ask pay nothing
+            self.buf = torch.zeros(self.cap, dtype=torch.float32, device=device)
         out = self.buf[self.off:self.off + n].view(shape)
         self.off += n_al
+        self.dirty = max(self.dirty, self.off)
         return out
 
 

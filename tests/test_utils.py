@@ -58,3 +58,10 @@ def test_zero_arena_hands_out_aligned_slices_and_falls_back():
         b2 = ops.zeros_f32((2, 10), torch.device("cpu"))
         assert float(b2.sum()) == 0.0
     assert float(ops.zeros_f32((4,), torch.device("cpu")).sum()) == 0.0
+    # the cleared prefix follows the largest use so far, whatever the order of small and large steps
+    for sizes in ([10], [10, 70, 5], [3], [10, 70, 5]):
+        with ops.zero_arena("cpu", 256):
+            got = [ops.zeros_f32((k,), torch.device("cpu")) for k in sizes]
+            assert all(float(t.abs().sum()) == 0.0 for t in got), sizes
+            for t in got:
+                t.fill_(7.0)
