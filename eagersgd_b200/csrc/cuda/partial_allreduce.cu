@@ -1,20 +1,21 @@
 // Kernels and C entry points of the NVLink partial allreduce (solo / majority /
-// synchronous), sm_100a.  Per step and channel, on the communication stream:
+// synchronous), sm_100a.  Per step and channel, two launches on the communication stream:
 //
-//   pack kernel   : wait (bounded) until the publish slot is free, copy/convert
-//                   the flat gradient into slot (epoch % 2)
-//   control kernel: one thread runs esgd::ctl_step — publish the epoch into every
-//                   peer's control block, elect the activator, snapshot arrivals,
-//                   broadcast the round descriptor, build the Plan
-//   data kernel   : reduce over peer memory + mailbox delivery + fused update;
-//                   the last block signals completion (esgd::finish_step)
-//   gather kernel : large vectors only (two-shot reduction): the data kernel reduced and
-//                   distributed this rank's share; wait for the other shares, apply the
-//                   update from the local gather buffer, signal completion
+//   pack + control: every block waits (bounded) until the publish slot is free and copies / converts
+//                   (or folds) its part of the flat gradient into slot (epoch % 2), clearing the flat
+//                   gradient behind it; the LAST block to finish then runs esgd::ctl_step in one thread:
+//                   publish the epoch into every peer's control block, elect the activator, snapshot
+//                   arrivals, broadcast the round descriptor, build the Plan.  No block waits for another.
+//   data          : reduce over peer memory (one shot, or reduce-scatter + pull-gather) + fused update,
+//                   or collect missed rounds from a participant's running sum; the last block signals
+//                   completion (esgd::finish_step)
 //
-// All cross-GPU waits are bounded; when one runs out the kernel records a status
-// bit and returns, leaving the context usable.
+// The kernel boundary is the only grid-wide barrier, so no block ever holds an SM while it waits for
+// another block of its own grid, and long waits (a synchronous round, a late initiator) are spent by a
+// single thread.  All cross-GPU waits are bounded; when one runs out the kernel records a status bit
+// and returns, leaving the context usable.
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdio.h>
 #include <string.h>
 #include "partial_allreduce.cuh"
@@ -26,121 +27,72 @@ using namespace esgd;
 
 namespace {
 
-__global__ void pack_kernel(DevChannel* ch) {
-  __shared__ int ok;
+__device__ inline void control_abort(DevChannel* ch) {
   ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
-  if (threadIdx.x == 0) ok = wait_slot_free<DevEnv>(me, ch->cfg.timeout_ns) ? 1 : 0;
-  __syncthreads();
-  if (!ok) return;
-  pack_phase(ch, (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
-}
-
-// The data phase is split in two when there is enough data and more than one reducer.  Every
-// participant of a round takes the same decision (same count, same threshold, same descriptor).
-__device__ inline void decide_two_shot(DevChannel* ch) {
-  const Plan& p = ch->plan;
-  ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= ch->two_shot_parts && p.part_count >= 2 &&
-                       ch->count >= ch->two_shot_min &&
-                       ch->gath[ch->cfg.rank] != nullptr) ? 1 : 0;
-}
-
-__global__ void ctl_kernel(DevChannel* ch) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
-  ch->blocks_done = 0;
-  ch->blocks_done2 = 0;
+  me->local_step += 1;
+  ch->plan.role = ROLE_ABORT;
+  ch->plan.n_src = ch->plan.n_push = 0;
+  ch->plan.holds_own_lock = 0;
   ch->plan.two_shot = 0;
-  if (me->status & ST_TIMEOUT_SLOT) {  // nothing valid was packed
-    me->local_step += 1;
-    ch->plan.role = ROLE_ABORT;
-    ch->plan.n_src = ch->plan.n_push = 0;
-    ch->plan.holds_own_lock = 0;
+  ch->plan.drain_src = -1;
+  ch->applied = 0;
+}
+
+__device__ inline void control_step(DevChannel* ch, int flush) {
+  ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
+  if (flush) {
+    ctl_flush<DevEnv>(ch->view, ch->cfg, &ch->plan);
+  } else if (me->status & ST_TIMEOUT_SLOT) {   // nothing valid was packed
+    control_abort(ch);
     return;
+  } else {
+    ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan);
   }
-  ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan);
   decide_two_shot(ch);
 }
 
-__global__ void flush_ctl_kernel(DevChannel* ch) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  ch->blocks_done = 0;
-  ctl_flush<DevEnv>(ch->view, ch->cfg, &ch->plan);
-}
-
-__global__ void data_kernel(DevChannel* ch) {
-  data_phase(ch, (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
+__global__ void __launch_bounds__(256) pack_ctl_kernel(DevChannel* ch, int flush) {
+  __shared__ int s_flag;
+  if (!flush) pack_phase(ch, blockIdx.x, gridDim.x, &s_flag);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    unsigned old = atomicAdd(&ch->blocks_done, 1u);
-    if (old == gridDim.x - 1) {
+    if (atomicAdd(&ch->bar_pack, 1u) == gridDim.x - 1) {
+      ch->bar_pack = 0;
       __threadfence_system();
-      if (ch->plan.two_shot) gather_signal(ch);     // completion is signalled by the gather kernel
-      else finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
+      control_step(ch, flush);
     }
   }
 }
 
-__global__ void gather_kernel(DevChannel* ch) {
-  if (!ch->plan.two_shot) return;
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = gather_wait(ch) ? 1 : 0;
-  __syncthreads();
-  if (ok) data_apply_gathered(ch, (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, (uint64_t)gridDim.x * blockDim.x);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    unsigned old = atomicAdd(&ch->blocks_done2, 1u);
-    if (old == gridDim.x - 1) {
-      if (!ok) ch->view.ctl[ch->cfg.rank]->status |= ST_TIMEOUT_GATHER;
-      __threadfence_system();
-      finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
-    }
-  }
+__global__ void __launch_bounds__(256, 4) data_kernel(DevChannel* ch) {
+  __shared__ int s_flag;
+  data_phase(ch, blockIdx.x, gridDim.x, &s_flag);
 }
 
 // All ranks of a (small) world inside ONE launch, one block per rank: used to
 // exercise the multi-rank protocol on a single GPU, where separate launches
 // that wait on one another are not guaranteed to run concurrently.
-__global__ void emulated_step_kernel(DevChannel** chans, const uint64_t* delay_ns, int flush) {
+__global__ void __launch_bounds__(256) emulated_step_kernel(DevChannel** chans, const uint64_t* delay_ns, int flush) {
   DevChannel* ch = chans[blockIdx.x];
-  ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
-  __shared__ int ok;
-  if (threadIdx.x == 0) {
-    ok = 1;
-    if (!flush) {
-      uint64_t t0 = DevEnv::now_ns();
-      while (DevEnv::now_ns() - t0 < delay_ns[blockIdx.x]) __nanosleep(200);
-      ok = wait_slot_free<DevEnv>(me, ch->cfg.timeout_ns) ? 1 : 0;
-    }
+  __shared__ int s_flag;
+  if (threadIdx.x == 0 && !flush) {
+    uint64_t t0 = DevEnv::now_ns();
+    while (DevEnv::now_ns() - t0 < delay_ns[blockIdx.x]) __nanosleep(200);
   }
   __syncthreads();
-  if (!flush && ok) pack_phase(ch, threadIdx.x, blockDim.x);
+  if (!flush) pack_phase(ch, 0, 1, &s_flag);
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    if (flush) ctl_flush<DevEnv>(ch->view, ch->cfg, &ch->plan);
-    else if (ok) { ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan); decide_two_shot(ch); }
-    else { me->local_step += 1; ch->plan.role = ROLE_ABORT; ch->plan.holds_own_lock = 0; ch->plan.two_shot = 0; }
-  }
+  if (threadIdx.x == 0) control_step(ch, flush);
   __threadfence();
   __syncthreads();
-  data_phase(ch, threadIdx.x, blockDim.x);
-  __threadfence_system();
-  __syncthreads();
-  if (ch->plan.two_shot) {
-    __shared__ int got;
-    if (threadIdx.x == 0) {
-      gather_signal(ch);
-      got = gather_wait(ch) ? 1 : 0;
-      if (!got) me->status |= ST_TIMEOUT_GATHER;
-    }
-    __syncthreads();
-    if (got) data_apply_gathered(ch, threadIdx.x, blockDim.x);
-    __threadfence_system();
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
+  data_phase(ch, 0, 1, &s_flag);
+}
+
+__global__ void set_hyper_kernel(float* hyper, float lr, float mu, float wd, float nesterov, float gscale) {
+  hyper[HP_LR] = lr; hyper[HP_MOMENTUM] = mu; hyper[HP_WD] = wd; hyper[HP_NESTEROV] = nesterov;
+  hyper[HP_GRAD_SCALE] = gscale;
 }
 
 // Stand-alone fused momentum-SGD / weight-decay update over flat buffers (no communication):
@@ -175,8 +127,8 @@ struct esgd_channel_desc {
   void* ctl[kMaxRanks];
   void* slot0[kMaxRanks];
   void* slot1[kMaxRanks];
-  void* mbox[kMaxRanks];
-  void* gath[kMaxRanks];          // gather buffers (all null: one-shot reduction only)
+  void* red[kMaxRanks];           // shard buffers, slot element type (all null: one-shot reduction only)
+  void* rsum[kMaxRanks];          // fp32 running sums of round results
   int32_t rank, world, base_mode, include_stale, average, home, slot_bf16, grad_in_bf16;
   int64_t limiter;
   uint64_t seed, timeout_ns, grace_ns, count;
@@ -188,7 +140,10 @@ struct esgd_channel_desc {
   int32_t out_bf16, pad;
   void* hyper;
   uint64_t two_shot_min;          // element count from which the reduction runs in two shots
-  int32_t two_shot_parts, pad3;   // ... in rounds with at least this many participants
+  int32_t accumulate;             // fold a gradient that no round picked up into the next publish of its slot
+  int32_t adaptive_grace;         // the grace window follows the arrival spread (at most grace_ns)
+  int32_t clear_grad;             // zero grad_in behind the copy into the publish slot
+  int32_t pad3;
 };
 
 uint64_t esgd_dev_channel_bytes(void) { return sizeof(DevChannel); }
@@ -196,22 +151,22 @@ uint64_t esgd_dev_ctl_bytes(void) { return sizeof(ChannelCtl); }
 
 // Fill the device-side channel object (a DevChannel in device memory at `dch`).
 int esgd_channel_configure(void* dch, const esgd_channel_desc* d, void* stream) {
-  if (d->count % 8 != 0 || d->world > kMaxRanks) return -1;
+  if (d->count % 8 != 0 || d->world > kMaxRanks || d->world < 1) return -1;
   DevChannel h;
   memset(&h, 0, sizeof(h));
   for (int j = 0; j < d->world; ++j) {
     h.view.ctl[j] = (ChannelCtl*)d->ctl[j];
     h.slot[j][0] = d->slot0[j];
     h.slot[j][1] = d->slot1[j];
-    h.mbox[j] = (float*)d->mbox[j];
-    h.gath[j] = (float*)d->gath[j];
+    h.red[j] = d->red[j];
+    h.rsum[j] = (float*)d->rsum[j];
   }
   h.two_shot_min = d->two_shot_min;
-  h.two_shot_parts = d->two_shot_parts;
+  h.clear_grad = d->clear_grad;
   h.cfg.rank = d->rank; h.cfg.world = d->world; h.cfg.average_world = d->average; h.cfg.home = d->home;
   h.cfg.timeout_ns = d->timeout_ns; h.cfg.grace_ns = d->grace_ns;
   h.pol.base_mode = d->base_mode; h.pol.include_stale = d->include_stale; h.pol.limiter = d->limiter;
-  h.pol.seed = d->seed;
+  h.pol.seed = d->seed; h.pol.accumulate = d->accumulate; h.pol.adaptive_grace = d->adaptive_grace;
   h.count = d->count; h.slot_bf16 = d->slot_bf16; h.grad_in_bf16 = d->grad_in_bf16;
   h.grad_in = d->grad_in; h.w32 = (float*)d->w32; h.mom = (float*)d->mom; h.w16 = (__nv_bfloat16*)d->w16;
   h.out = d->out; h.out_bf16 = d->out_bf16; h.hyper = (const float*)d->hyper;
@@ -226,27 +181,39 @@ static inline int grid_for(uint64_t count, int max_blocks) {
   return (int)(need < (uint64_t)max_blocks ? need : (uint64_t)max_blocks);
 }
 
-// One full step of one channel on `stream`.  `two_shot`: the channel was configured with gather buffers and
-// `count` reaches its two-shot threshold, so the gather kernel must follow (it returns at once in rounds
-// that were reduced in one shot).
-int esgd_channel_step(void* dch, uint64_t count, int max_blocks, int two_shot, void* stream) {
+// One full step of one channel on `stream`: two launches.
+int esgd_channel_step(void* dch, uint64_t count, int max_blocks, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   int g = grid_for(count, max_blocks);
-  pack_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
-  ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch);
+  pack_ctl_kernel<<<g, 256, 0, s>>>((DevChannel*)dch, 0);
   data_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
-  if (two_shot) gather_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
-  count_launch(two_shot ? 4 : 3);
+  count_launch(2);
   return (int)cudaGetLastError();
 }
 
 int esgd_channel_flush(void* dch, uint64_t count, int max_blocks, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   int g = grid_for(count, max_blocks);
-  flush_ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch);
+  pack_ctl_kernel<<<1, 32, 0, s>>>((DevChannel*)dch, 1);
   data_kernel<<<g, 256, 0, s>>>((DevChannel*)dch);
   count_launch(2);
   return (int)cudaGetLastError();
+}
+
+// Learning rate, momentum, weight decay, Nesterov flag and gradient scale travel as launch arguments, so
+// every step reads the values that were current when it was enqueued, however far the host runs ahead.
+int esgd_set_hyper(void* hyper, float lr, float momentum, float wd, int nesterov, float grad_scale, void* stream) {
+  set_hyper_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((float*)hyper, lr, momentum, wd, nesterov ? 1.0f : 0.0f, grad_scale);
+  count_launch();
+  return (int)cudaGetLastError();
+}
+
+// Did the newest step apply anything (participant or drain)?  Synchronises with `stream`.
+int esgd_channel_applied(const void* dch, int* applied, void* stream) {
+  cudaError_t e = cudaMemcpyAsync(applied, (const char*)dch + offsetof(DevChannel, applied), sizeof(int),
+                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize((cudaStream_t)stream);
 }
 
 // `chans`: device array of `world` DevChannel pointers, `delay_ns`: device array.

@@ -73,6 +73,13 @@ void data_participant(void** bases, const SegLayout& L, const Plan& plan, uint64
 }
 
 template <class T>
+void fold_into(void* slot, const void* grad, uint64_t count) {
+  T* s = (T*)slot;
+  const T* g = (const T*)grad;
+  for (uint64_t e = 0; e < count; ++e) s[e] += g[e];
+}
+
+template <class T>
 void run_data(void** bases, int rank, const SegLayout& L, const Plan& plan, uint64_t count, void* out) {
   T* o = (T*)out;
   if (plan.role == ROLE_PARTICIPANT) data_participant<T>(bases, L, plan, count, o);
@@ -96,7 +103,8 @@ struct esgd_step_info {
 };
 
 struct esgd_cpu_params {
-  int32_t rank, world, base_mode, include_stale, average, home, dtype, reserved;
+  int32_t rank, world, base_mode, include_stale, average, home, dtype;
+  int32_t flags;                   // bit 0: fold unconsumed gradients into the next publish; bit 1: adaptive grace
   int64_t limiter;
   uint64_t seed, timeout_ns, grace_ns, count;
 };
@@ -133,12 +141,23 @@ uint32_t esgd_cpu_step(void** bases, const esgd_cpu_params* p, const void* grad,
   cfg.timeout_ns = p->timeout_ns; cfg.grace_ns = p->grace_ns;
   StepPolicy pol;
   pol.base_mode = p->base_mode; pol.include_stale = p->include_stale; pol.limiter = p->limiter; pol.seed = p->seed;
+  pol.accumulate = p->flags & 1; pol.adaptive_grace = (p->flags >> 1) & 1;
 
   Plan plan;
   memset(&plan, 0, sizeof(plan));
   uint64_t k = me->local_step + 1;
-  if (wait_slot_free<HostEnv>(me, p->timeout_ns)) {
-    memcpy((char*)bases[p->rank] + L.slot_off[k % kSlotDepth], grad, p->count * (uint64_t)dtype_size(p->dtype));
+  if (wait_slot_free<HostEnv>(v, cfg, pol, k)) {
+    void* slot = (char*)bases[p->rank] + L.slot_off[k % kSlotDepth];
+    if (slot_fate<HostEnv>(me, pol, k) == SLOT_FOLD) {
+      switch (p->dtype) {   // the gradient of epoch k-2 was never picked up: it rides along with this one
+        case DT_F32: fold_into<float>(slot, grad, p->count); break;
+        case DT_F64: fold_into<double>(slot, grad, p->count); break;
+        case DT_I32: fold_into<int32_t>(slot, grad, p->count); break;
+        default: fold_into<int64_t>(slot, grad, p->count); break;
+      }
+    } else {
+      memcpy(slot, grad, p->count * (uint64_t)dtype_size(p->dtype));
+    }
     ctl_step<HostEnv>(v, cfg, pol, &plan);
   } else {
     me->local_step = k;
@@ -192,13 +211,14 @@ uint32_t esgd_cpu_flush(void** bases, const esgd_cpu_params* p, void* out, esgd_
 }
 
 // stats[0..9]: local_step, participated, absent, activated, sync, dropped,
-// contrib_sum, wait_ns, last_round, last_contrib; [10] status; [11] latest_round
+// contrib_sum, wait_ns, last_round, last_contrib; [10] status; [11] latest_round; [12] folded
 void esgd_ctl_stats(const void* base, uint64_t* stats) {
   const ChannelCtl* c = (const ChannelCtl*)base;
   stats[0] = c->local_step; stats[1] = c->stat_rounds_participated; stats[2] = c->stat_rounds_absent;
   stats[3] = c->stat_rounds_activated; stats[4] = c->stat_sync_rounds; stats[5] = c->stat_dropped_grads;
   stats[6] = c->stat_contrib_sum; stats[7] = c->stat_wait_ns; stats[8] = c->stat_last_round;
   stats[9] = c->stat_last_contrib; stats[10] = c->status; stats[11] = c->latest_round;
+  stats[12] = c->stat_folded_grads;
 }
 
 // Copy the trace ring, oldest first, as rows of 10 uint64: step, round, t_ns, wait_ns, role, activator,

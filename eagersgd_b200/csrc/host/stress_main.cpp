@@ -23,7 +23,7 @@ struct esgd_step_info {
   uint64_t round, local_step;
 };
 struct esgd_cpu_params {
-  int32_t rank, world, base_mode, include_stale, average, home, dtype, reserved;
+  int32_t rank, world, base_mode, include_stale, average, home, dtype, flags;
   int64_t limiter;
   uint64_t seed, timeout_ns, grace_ns, count;
 };
@@ -32,7 +32,7 @@ uint32_t esgd_cpu_step(void** bases, const esgd_cpu_params* p, const void* grad,
 uint32_t esgd_cpu_flush(void** bases, const esgd_cpu_params* p, void* out, esgd_step_info* info);
 }
 
-static int run_channel(int mode, int world, int steps, uint64_t count) {
+static int run_channel(int mode, int world, int steps, uint64_t count, int flags) {
   const uint64_t bytes = esgd_cpu_segment_bytes(count, 0);
   std::vector<void*> bases(world);
   for (int r = 0; r < world; ++r) {
@@ -47,7 +47,7 @@ static int run_channel(int mode, int world, int steps, uint64_t count) {
       esgd_cpu_params p;
       memset(&p, 0, sizeof(p));
       p.rank = r; p.world = world; p.base_mode = mode; p.include_stale = 1; p.average = 2 /* sum */; p.home = 0;
-      p.dtype = 0; p.limiter = 4; p.seed = 6545343; p.timeout_ns = 20ull * 1000000000ull; p.grace_ns = 0; p.count = count;
+      p.dtype = 0; p.flags = flags; p.limiter = 4; p.seed = 6545343; p.timeout_ns = 20ull * 1000000000ull; p.grace_ns = 0; p.count = count;
       std::vector<float> grad(count), out(count);
       unsigned seed = 1234u + (unsigned)r;
       esgd_step_info info;
@@ -107,7 +107,8 @@ int main(int argc, char** argv) {
   const int world = argc > 1 ? atoi(argv[1]) : 4;
   const int steps = argc > 2 ? atoi(argv[2]) : 200;
   int bad = 0;
-  for (int mode = 0; mode < 3; ++mode) bad |= run_channel(mode, world, steps, 1024);
+  for (int mode = 0; mode < 3; ++mode) bad |= run_channel(mode, world, steps, 1024, 2);
+  for (int mode = 0; mode < 2; ++mode) bad |= run_channel(mode, world, steps, 1024, 3);   // folding unconsumed gradients
   bad |= run_runtime(world, steps / 4 + 1);
   return bad;
 }

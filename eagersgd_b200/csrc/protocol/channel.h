@@ -18,7 +18,12 @@
 // What is deliberately different: no message tree (NVSwitch makes every peer one
 // hop, so activation is one descriptor store per peer), a consistent contributor
 // snapshot taken by one elected activator, and a locked per-rank mailbox that
-// accumulates the results of rounds a rank missed, so no round result is lost.
+// counts the rounds a rank missed, so no round result is lost: the CPU backend
+// accumulates the missed results there, the GPU backend lets the late rank pull
+// the difference of a participant's running sum of round results and its own.
+// A gradient that was published but never picked up by a round can be folded into
+// the rank's next publish of the same slot parity instead of being superseded
+// (StepPolicy::accumulate; the reference overwrites, opt_esgd_solo_imagenet_imbalance.py:301-314).
 #pragma once
 #include <stdint.h>
 
@@ -53,7 +58,8 @@ enum StatusBits : uint32_t {
   ST_DESC_LAPPED = 1u << 4,       // descriptor ring overwritten before it was read
   ST_MBOX_NOT_EMPTY = 1u << 5,    // participant found data in its own mailbox (protocol error)
   ST_TIMEOUT_SLOT = 1u << 6,      // publish slot still being read
-  ST_TIMEOUT_GATHER = 1u << 7     // two-shot reduction: a participant's share never arrived
+  ST_TIMEOUT_GATHER = 1u << 7,    // two-shot reduction: a participant's share never arrived
+  ST_TIMEOUT_BARRIER = 1u << 8    // blocks of one rank's kernel did not meet (device only)
 };
 
 struct alignas(128) RoundDesc {
@@ -89,13 +95,18 @@ struct TraceEntry {
 struct alignas(128) ChannelCtl {
   uint64_t pub_epoch[kMaxRanks];          // [j] pushed by rank j: its latest published epoch
   alignas(128) uint64_t owner;            // election word; only the home rank's copy is used
+  alignas(128) uint64_t snap_round;       // home rank's copy: newest round whose activator is past its waits and
+                                          // is taking (or has taken) the snapshot of who contributes what
   alignas(128) uint64_t latest_round;     // newest round whose descriptor is visible here
   alignas(128) uint64_t round_done;       // newest round whose data phase has completed
   alignas(128) uint32_t done_count[kDescRing];  // finishers; only the activator's copy is used
   alignas(128) uint32_t mbox_lock;        // 0 free, else 1 + holder
   uint32_t mbox_count;                    // rounds accumulated since the last drain
-  alignas(128) uint64_t gather_round[kMaxRanks];  // [j] pushed by participant j: its share of that round's result
-                                                  // has landed in this rank's gather buffer (two-shot reduction)
+  alignas(128) uint64_t gather_round[kMaxRanks];  // [j] pushed by participant j: its reduced share of that round is
+                                                  // complete in ITS shard buffer and may be pulled (two-shot reduction)
+  alignas(128) uint64_t taken[kSlotDepth];        // [e % 2] = e: epoch e of this rank was picked up by a round
+                                                  // (written by that round's activator before the descriptor)
+  alignas(128) uint64_t grace_ema_ns;     // home rank's copy: smoothed arrival spread seen by activators
   alignas(128) RoundDesc desc[kDescRing];
   // ---- local only (never touched by peers) ----
   alignas(128) uint64_t local_step;       // posts made so far by the owning rank
@@ -110,6 +121,7 @@ struct alignas(128) ChannelCtl {
   uint64_t stat_wait_ns;                  // time spent in bounded waits
   uint64_t stat_last_round;               // round applied at the last step
   uint64_t stat_last_contrib;
+  uint64_t stat_folded_grads;             // own unconsumed gradients folded into a later publish
   TraceEntry trace[kTraceRing];           // ring indexed by local_step % kTraceRing
 };
 
@@ -125,6 +137,8 @@ struct alignas(16) Plan {
   int32_t is_sync;
   uint32_t fresh_mask;            // the participants (bit per rank)
   int32_t two_shot;               // data phase split into reduce-scatter and gather (set by the device front end)
+  int32_t drain_src;              // drain: a rank whose running sum of round results is complete (device backend)
+  int32_t pad_;
   uint64_t round;
   float scale;                    // 1/contributors or 1/world
   float drain_rounds;             // number of rounds summed in the mailbox (drain)

@@ -40,6 +40,7 @@ struct DevEnv {
     return old;
   }
   static __device__ __forceinline__ void fence() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+  static __device__ __forceinline__ void fence_sc() { asm volatile("fence.sc.sys;" ::: "memory"); }
   static __device__ __forceinline__ uint64_t now_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -22,6 +22,7 @@ struct HostEnv {
   }
   static inline uint32_t add32(uint32_t* p, uint32_t v) { return __atomic_fetch_add(p, v, __ATOMIC_ACQ_REL); }
   static inline void fence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+  static inline void fence_sc() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
   static inline uint64_t now_ns() {
     struct timespec ts;
     clock_gettime(CLOCK_MONOTONIC, &ts);

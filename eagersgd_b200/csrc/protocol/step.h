@@ -2,10 +2,11 @@
 //
 // Env must provide (all at system scope, i.e. visible to every rank):
 //   ld_acq64 / st_rel64 / ld_acq32 / st_rel32, cas64 / cas32 (return the old
-//   value), add32 (returns the old value), fence(), now_ns(), pause().
+//   value), add32 (returns the old value), fence(), fence_sc() (sequentially
+//   consistent: orders an earlier store before a later load), now_ns(), pause().
 //
 // One rank calls, per step and per channel, in this order:
-//   wait_slot_free()  -> write its gradient into publish slot (epoch % 2)
+//   wait_slot_free()  -> write (or fold) its gradient into publish slot (epoch % 2)
 //   ctl_step()        -> publish, elect / wait for the round, build the Plan
 //   <data phase>      -> reduce + update (participant) or apply mailbox (drain)
 //   finish()          -> completion signalling, lock release
@@ -31,7 +32,13 @@ struct StepPolicy {
   int32_t include_stale;   // sum unconsumed gradients of ranks that have not arrived
   int64_t limiter;         // eager rounds between synchronous rounds; < 0: never force
   uint64_t seed;           // majority initiator stream
+  int32_t accumulate;      // fold an own gradient that no round picked up into the next publish of its slot
+  int32_t adaptive_grace;  // the grace window follows the smoothed arrival spread (at most StepConfig::grace_ns)
 };
+
+ESGD_HD bool round_is_sync(const StepPolicy& pol, uint64_t round) {
+  return pol.base_mode == MODE_SYNC || limiter_is_sync(round, pol.limiter);
+}
 
 ESGD_HD uint32_t bit_of(int r) { return 1u << r; }
 ESGD_HD int popc32(uint32_t x) {
@@ -40,17 +47,35 @@ ESGD_HD int popc32(uint32_t x) {
   return c;
 }
 
-// The publish slot for `epoch` was last used for epoch-2.  Its readers belong
-// to a round whose descriptor reached this rank before they started, so the
-// slot is free once every round visible here has completed.
+// What happens to the gradient of epoch k-2, which still sits in the slot that epoch k is about to use.
+enum SlotFate : int32_t { SLOT_CONSUMED = 0, SLOT_FOLD = 1, SLOT_DROP = 2 };
+
+// Valid once wait_slot_free() has returned true for epoch k: a round that picked epoch k-2 up has
+// completed by then, and its activator wrote taken[] before it published the round.
 template <class E>
-ESGD_T bool wait_slot_free(ChannelCtl* me, uint64_t timeout_ns) {
-  uint64_t t0 = E::now_ns();
+ESGD_T int32_t slot_fate(ChannelCtl* me, const StepPolicy& pol, uint64_t k) {
+  if (k < 3) return SLOT_CONSUMED;
+  if (E::ld_acq64(&me->taken[k % kSlotDepth]) == k - 2) return SLOT_CONSUMED;
+  return pol.accumulate ? SLOT_FOLD : SLOT_DROP;
+}
+
+// Before epoch k overwrites publish slot k % 2 (last used for epoch k-2) no round may still read it.
+// An activator announces its round in the home rank's `snap_round`, then (after a sequentially
+// consistent fence) reads every rank's published epoch.  This rank published k-1 a step ago and
+// fences before it reads `snap_round`: a round it does not see there yet will find epoch >= k-1 and
+// never touch the slot of k-2; a round it does see may have picked k-2 up and must complete first.
+// Such a round is past its arrival / grace waits and depends on no rank that is not part of it,
+// so this wait cannot deadlock.
+template <class E>
+ESGD_T bool wait_slot_free(const ChannelView& v, const StepConfig& cfg, const StepPolicy& pol, uint64_t k) {
+  (void)pol;
+  ChannelCtl* me = v.ctl[cfg.rank];
+  const uint64_t t0 = E::now_ns();
+  E::fence_sc();
+  const uint64_t target = E::ld_acq64(&v.ctl[cfg.home]->snap_round);
   for (;;) {
-    uint64_t lr = E::ld_acq64(&me->latest_round);
-    uint64_t rd = E::ld_acq64(&me->round_done);
-    if (rd >= lr) return true;
-    if (E::now_ns() - t0 > timeout_ns) {
+    if (E::ld_acq64(&me->round_done) >= target) return true;
+    if (E::now_ns() - t0 > cfg.timeout_ns) {
       me->status |= ST_TIMEOUT_SLOT;
       return false;
     }
@@ -86,19 +111,38 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
       }
     }
   } else if (cfg.grace_ns > 0) {
-    // Ranks that arrive within the grace window of the first one are still fresh:
-    // without it, near-simultaneous arrivals would all but one count as absent.
+    // Ranks that arrive within the grace window of the first one are still fresh: without it,
+    // near-simultaneous arrivals would all but one count as absent.  The window follows the arrival
+    // spread the activators have seen lately (twice its smoothed value, at most grace_ns); every 16th
+    // round waits the full window so that a growing spread is noticed.
+    ChannelCtl* hm = v.ctl[cfg.home];
+    uint64_t window = cfg.grace_ns, ema = 0;
+    if (pol.adaptive_grace) {
+      ema = E::ld_acq64(&hm->grace_ema_ns);
+      const uint64_t w = 2 * ema + 1000;
+      if ((k & 15u) != 0 && w < window) window = w;
+    }
     const uint64_t tg = E::now_ns();
+    uint64_t last_arrival = 0;
+    int seen = 1;
     for (;;) {
       int arrived = 0;
       for (int j = 0; j < P; ++j) arrived += (E::ld_acq64(&me->pub_epoch[j]) >= k) ? 1 : 0;
-      if (arrived >= P) break;
-      if (E::now_ns() - tg > cfg.grace_ns) break;
+      const uint64_t dt = E::now_ns() - tg;
+      if (arrived > seen) { seen = arrived; last_arrival = dt; }
+      if (arrived >= P || dt > window) break;
       E::pause();
+    }
+    if (pol.adaptive_grace) {   // fast attack, slow decay
+      const uint64_t smooth = (7 * ema + last_arrival) / 8;
+      E::st_rel64(&hm->grace_ema_ns, last_arrival > smooth ? last_arrival : smooth);
     }
   }
 
-  // One consistent snapshot of who has what; every reducer honours it.
+  // One consistent snapshot of who has what; every reducer honours it.  Announced first, so that a
+  // rank about to reuse a publish slot knows that this round may be reading it (wait_slot_free).
+  E::st_rel64(&v.ctl[cfg.home]->snap_round, k);
+  E::fence_sc();
   RoundDesc d;
   d.round = k;
   d.activator = (uint32_t)me_r;
@@ -146,6 +190,11 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
     return st;
   }
 
+  // Tell every contributor which of its epochs this round picks up (it decides from this whether a
+  // later publish must fold an older gradient in), before the round becomes visible anywhere.
+  for (int j = 0; j < P; ++j)
+    if (d.contrib_mask & bit_of(j)) E::st_rel64(&v.ctl[j]->taken[d.read_epoch[j] % kSlotDepth], d.read_epoch[j]);
+
   // Activation = one descriptor store per peer, then the round number.
   E::st_rel32(&me->done_count[k % kDescRing], 0u);
   for (int j = 0; j < P; ++j) {
@@ -156,6 +205,25 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
   for (int j = 0; j < P; ++j) E::st_rel64(&v.ctl[j]->latest_round, k);
   me->stat_rounds_activated++;
   return 0;
+}
+
+// A rank whose record of round results is complete: any participant of the newest completed round
+// (it took part in, or collected, every earlier round before it could post that one).  Called with the
+// caller's own mailbox lock held: no round that lacks the caller can start, and the caller takes part in
+// none, so nothing is in flight and the descriptor ring is stable.  Different late ranks pick different
+// participants.  Returns -1 if the descriptor is gone (protocol error).
+template <class E>
+ESGD_T int32_t pick_drain_source(ChannelCtl* me, int rank) {
+  const uint64_t R = E::ld_acq64(&me->round_done);
+  const RoundDesc* dr = &me->desc[R % kDescRing];
+  if (dr->round != R || dr->n_fresh == 0) return -1;
+  int want = rank % (int)dr->n_fresh;
+  for (int j = 0; j < kMaxRanks; ++j)
+    if (dr->fresh_mask & bit_of(j)) {
+      if (want == 0) return j;
+      --want;
+    }
+  return -1;
 }
 
 template <class E>
@@ -172,14 +240,22 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
   plan->part_count = 1;
   plan->fresh_mask = 0;
   plan->two_shot = 0;
+  plan->drain_src = -1;
   plan->activator = i;
   plan->holds_own_lock = 0;
   plan->round = k;
   plan->scale = 1.0f;
   plan->drain_rounds = 0.0f;
 
-  const bool sync_round = (pol.base_mode == MODE_SYNC) || limiter_is_sync(k, pol.limiter);
+  const bool sync_round = round_is_sync(pol, k);
   plan->is_sync = sync_round ? 1 : 0;
+  // The gradient of epoch k-2 shared this epoch's slot: picked up by a round, folded in, or superseded
+  // (the reference overwrites its send buffer the same way).
+  {
+    const int32_t fate = slot_fate<E>(me, pol, k);
+    if (fate == SLOT_FOLD) me->stat_folded_grads++;
+    else if (fate == SLOT_DROP) me->stat_dropped_grads++;
+  }
   bool may_activate = true;
   if (!sync_round && pol.base_mode == MODE_MAJORITY)
     may_activate = (majority_initiator(pol.seed, k, P) == i);
@@ -269,14 +345,8 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
       plan->role = ROLE_DRAIN;
       plan->holds_own_lock = 1;
       plan->drain_rounds = (float)cnt;
+      plan->drain_src = pick_drain_source<E>(me, i);
     }
-  }
-  // A published gradient that was never consumed and is now superseded is dropped
-  // (the reference overwrites its send buffer the same way).
-  if (k >= 2) {
-    const uint64_t rr = participant ? k - 1 : me->stat_last_round;
-    const RoundDesc* dl = &me->desc[rr % kDescRing];
-    if (dl->round == rr && dl->consumed[i] + 1 < k) me->stat_dropped_grads++;
   }
   const uint64_t t1 = E::now_ns();
   me->stat_wait_ns += t1 - t0;
@@ -323,6 +393,7 @@ ESGD_T void ctl_flush(const ChannelView& v, const StepConfig& cfg, Plan* plan) {
   plan->n_src = plan->n_push = 0;
   plan->holds_own_lock = 0;
   plan->two_shot = 0;
+  plan->drain_src = -1;
   plan->fresh_mask = 0;
   plan->round = E::ld_acq64(&me->latest_round);
   while (E::ld_acq64(&me->round_done) < plan->round) {
@@ -342,6 +413,7 @@ ESGD_T void ctl_flush(const ChannelView& v, const StepConfig& cfg, Plan* plan) {
     plan->role = ROLE_DRAIN;
     plan->holds_own_lock = 1;
     plan->drain_rounds = (float)cnt;
+    plan->drain_src = pick_drain_source<E>(me, cfg.rank);
   }
 }
 

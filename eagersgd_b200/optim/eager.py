@@ -34,10 +34,12 @@ class _Bucket:
         self.launched = False
         self.channel = None
         self.grad_flat = None
-        self.w32 = self.mom = self.w16 = None
+        self.w32 = self.mom = self.w16 = self.g32 = None
+        self.masters = None
         self.hyper = None
-        self.hyper_host = None
         self.hyper_vals = None
+        self.self_clearing = False
+        self.dirty = True
 
     def add(self, p):
         self.params.append(p)
@@ -62,11 +64,14 @@ class EagerOptimizer:
                  limiter: int = 32, seed: int = 6545343, bucket_mb: float = 25.0,
                  average: str = "contributors", include_stale: bool = True, fused: Optional[bool] = None,
                  slot_dtype: Optional[torch.dtype] = None, overlap: bool = True, timeout_s: float = 30.0,
-                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 26,
-                 two_shot_parts: int = 5):
+                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 16,
+                 accumulate: bool = False, adaptive_grace: bool = True):
         self.optimizer = optimizer
         self.two_shot_min = two_shot_min   # bucket elements from which a round is reduced in two shots (None: never)
-        self.two_shot_parts = two_shot_parts   # ... when at least this many ranks take part in it
+        # fold a gradient that no round picked up into this rank's next publish instead of dropping it
+        # (the reference drops it: opt_esgd_solo_imagenet_imbalance.py:311-314 zeroes the send buffer)
+        self.accumulate = accumulate
+        self.adaptive_grace = adaptive_grace
         self.group = group if group is not None else init_group()
         self.mode, self.limiter, self.seed = mode, limiter, seed
         self.average, self.include_stale = average, include_stale
@@ -79,6 +84,13 @@ class EagerOptimizer:
             raise ValueError("optimizer has no trainable parameters")
         self.device = params[0].device
         self.on_gpu = self.device.type == "cuda"
+        if self.on_gpu:
+            bad = sorted({str(p.dtype) for p in params if p.dtype not in (torch.float32, torch.bfloat16)})
+            if bad:
+                raise ValueError("the GPU partial allreduce handles float32 and bfloat16 parameters only (found %s); "
+                                 "use bfloat16 for low-precision compute" % ", ".join(bad))
+            if slot_dtype not in (None, torch.float32, torch.bfloat16):
+                raise ValueError("slot_dtype must be torch.float32 or torch.bfloat16")
         can_fuse = (self.on_gpu and type(optimizer) is torch.optim.SGD and
                     all(g.get("dampening", 0) == 0 and not g.get("maximize", False) for g in optimizer.param_groups))
         self.fused = can_fuse if fused is None else (fused and can_fuse)
@@ -89,8 +101,7 @@ class EagerOptimizer:
         self._hooks = []
         if self.on_gpu:
             self._setup_gpu()
-            if overlap:
-                self._install_hooks()
+            self._install_hooks()
         else:
             self._setup_cpu()
 
@@ -142,7 +153,8 @@ class EagerOptimizer:
             b.channel = CpuChannel(seg.bases, g.rank, g.world, b.count, npdt, mode=self.mode, limiter=self.limiter,
                                    seed=self.seed, average=self.average,
                                    include_stale=self.include_stale, timeout_s=self.timeout_s,
-                                   grace_us=self.grace_us)
+                                   grace_us=self.grace_us, accumulate=self.accumulate,
+                                   adaptive_grace=self.adaptive_grace)
             b.out_np = np.empty(b.count, dtype=npdt)
 
     # ------------------------------------------------------------------ GPU
@@ -151,27 +163,43 @@ class EagerOptimizer:
         g = self.group
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self._arenas = []
+        master_of = {}
         for b in self.buckets:
             dt = b.params[0].dtype
+            low = dt != torch.float32
             b.grad_flat = torch.zeros(b.count, dtype=dt, device=self.device)
             b.hyper = torch.zeros(HYPER_LEN, dtype=torch.float32, device=self.device)
-            b.hyper_host = torch.zeros(HYPER_LEN, dtype=torch.float32).pin_memory()
-            kw = {}
-            if self.fused:
+            b.masters = None
+            if self.fused or low:
+                # fp32 master weights; the model computes on the bucket's own (low-precision) storage
                 b.w32 = torch.zeros(b.count, dtype=torch.float32, device=self.device)
-                b.mom = torch.zeros(b.count, dtype=torch.float32, device=self.device)
-                if dt != torch.float32:
+                if low:
                     b.w16 = torch.zeros(b.count, dtype=dt, device=self.device)
+                store = b.w16 if low else b.w32
                 for p, off in zip(b.params, b.offsets):
                     _view_like(b.w32, off, p).copy_(p.detach().float())
-                    store = b.w16 if b.w16 is not None else b.w32
                     v = _view_like(store, off, p)
-                    if b.w16 is not None:
+                    if low:
                         v.copy_(p.detach())
-                    p.data = v  # the model now computes on the bucket's storage
-                kw = dict(w32=b.w32, mom=b.mom, w16=b.w16)
+                    p.data = v
+            if self.fused:
+                b.mom = torch.zeros(b.count, dtype=torch.float32, device=self.device)
+                kw = dict(w32=b.w32, mom=b.mom, w16=b.w16, clear_grad=True)
+            elif low:
+                # a wrapped optimizer steps the fp32 masters with the averaged gradient in fp32; the
+                # low-precision weights are refreshed from them after every step
+                b.g32 = torch.zeros(b.count, dtype=torch.float32, device=self.device)
+                b.masters = []
+                for p, off in zip(b.params, b.offsets):
+                    m = torch.nn.Parameter(_view_like(b.w32, off, p), requires_grad=True)
+                    m.grad = _view_like(b.g32, off, p)
+                    b.masters.append(m)
+                    master_of[id(p)] = m
+                kw = dict(out=b.g32, clear_grad=True)
             else:
                 kw = dict(out=b.grad_flat)
+            b.self_clearing = bool(kw.get("clear_grad", False))
+            b.dirty = False
             self._point_grads(b)
             arena, bases = create_arenas(b.count, self.slot_dtype, g.rank, g.world, g.exchange)
             self._arenas.append(arena)
@@ -180,23 +208,30 @@ class EagerOptimizer:
                                       seed=self.seed, average=self.average,
                                       include_stale=self.include_stale, timeout_s=self.timeout_s,
                                       grace_us=self.grace_us, hyper=b.hyper, max_blocks=self.max_blocks,
-                                      two_shot_min=self.two_shot_min, two_shot_parts=self.two_shot_parts, **kw)
+                                      two_shot_min=self.two_shot_min, accumulate=self.accumulate,
+                                      adaptive_grace=self.adaptive_grace, **kw)
             self._refresh_hyper(b, force=True)
+        if master_of:
+            if len(self.optimizer.state) != 0:
+                raise ValueError("wrap the optimizer before its first step: its state is keyed by the parameters, "
+                                 "which are replaced by fp32 master copies here")
+            for pg in self.optimizer.param_groups:
+                pg["params"] = [master_of.get(id(p), p) for p in pg["params"]]
         torch.cuda.synchronize(self.device)
         g.barrier()
 
     def _refresh_hyper(self, b: _Bucket, force: bool = False):
         pg = self.optimizer.param_groups[b.group_index]
         vals = (float(pg.get("lr", 0.0)), float(pg.get("momentum", 0.0)), float(pg.get("weight_decay", 0.0)),
-                1.0 if pg.get("nesterov", False) else 0.0, float(getattr(self, "grad_scale", 1.0)))
+                bool(pg.get("nesterov", False)), float(getattr(self, "grad_scale", 1.0)))
         if force or vals != b.hyper_vals:
             if torch.cuda.is_current_stream_capturing():
                 return  # a captured step reads the device copy; sync_hyper() refreshes it before a replay
             b.hyper_vals = vals
-            for i, v in enumerate(vals):
-                b.hyper_host[i] = v
-            # on the current stream: the side stream waits for it before every launch
-            b.hyper.copy_(b.hyper_host, non_blocking=True)
+            # the values travel as launch arguments of a one-thread kernel on the current stream (the side
+            # stream waits for it before every launch): a step always reads what was current when it was
+            # enqueued, however far the host runs ahead of the GPU
+            b.channel.set_hyper(*vals)
 
     def sync_hyper(self):
         """Push lr / momentum / weight decay to the device copies the fused kernels read.
@@ -204,6 +239,19 @@ class EagerOptimizer:
         if self.on_gpu:
             for b in self.buckets:
                 self._refresh_hyper(b)
+
+    def refresh_master_from_params(self):
+        """Re-derive the fp32 master weights (and the low-precision working copies) from the values the
+        parameters hold now.  Call it after writing into the parameters from outside the optimizer — a
+        warm start, a checkpoint without master weights — or the next update starts from the old masters."""
+        if not self.on_gpu:
+            return
+        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        for b in self.buckets:
+            if b.w32 is None:
+                continue
+            for p, off in zip(b.params, b.offsets):
+                _view_like(b.w32, off, p).copy_(p.detach().float())
 
     def _install_hooks(self):
         for b in self.buckets:
@@ -213,8 +261,9 @@ class EagerOptimizer:
 
     def _make_hook(self, b: _Bucket):
         def hook(p):
+            b.dirty = True
             b.pending -= 1
-            if b.pending == 0:
+            if b.pending == 0 and self.overlap:
                 self._launch(b)
         return hook
 
@@ -237,9 +286,14 @@ class EagerOptimizer:
         return self.optimizer.param_groups
 
     def zero_grad(self, set_to_none: bool = False):
-        """Zero the flat gradient buckets (the per-parameter ``.grad`` stay views of them)."""
+        """Zero the flat gradient buckets (the per-parameter ``.grad`` stay views of them).  On the GPU
+        the reduce kernel clears a bucket behind its copy into the publish slot, so after ``step()`` there
+        is nothing left to do here; a fill is launched only for a bucket that backward has written since."""
         for b in self.buckets:
-            b.grad_flat.zero_()
+            if not (self.on_gpu and getattr(b, "self_clearing", False) and not b.dirty):
+                b.grad_flat.zero_()
+                if self.on_gpu:
+                    b.dirty = False
             if any(p.grad is None for p in b.params):
                 self._point_grads(b)
 
@@ -253,11 +307,9 @@ class EagerOptimizer:
             for b in self.buckets:
                 b.launched = False
                 b.pending = len(b.params)
+                b.dirty = not b.self_clearing
             if not self.fused:
-                if self.grad_scale != 1.0:
-                    for b in self.buckets:
-                        b.grad_flat.mul_(self.grad_scale)
-                self.optimizer.step()
+                self._inner_step()
         else:
             applied = False
             for b in self.buckets:
@@ -271,6 +323,23 @@ class EagerOptimizer:
                 self.optimizer.step()
         return loss
 
+    def _inner_step(self):
+        """Step the wrapped optimizer with the averaged gradients the kernels wrote — unless no bucket had
+        anything to apply (the rank missed the round and its mailbox was empty, or a bounded wait ran out):
+        then momentum and weight decay must not move the weights either, as on the CPU path and in the
+        fused kernel.  Reading the flags synchronises with the device; inside stream capture the step is
+        recorded unconditionally."""
+        if not torch.cuda.is_current_stream_capturing():
+            if not any(b.channel.applied() for b in self.buckets):
+                return
+        if self.grad_scale != 1.0:
+            for b in self.buckets:
+                (b.g32 if b.masters is not None else b.grad_flat).mul_(self.grad_scale)
+        self.optimizer.step()
+        for b in self.buckets:
+            if b.masters is not None:
+                b.w16.copy_(b.w32)
+
     def flush(self):
         """Apply the results of rounds that completed after this rank's last step."""
         if self.on_gpu:
@@ -280,7 +349,7 @@ class EagerOptimizer:
                 b.channel.flush(self.comm_stream)
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
             if not self.fused:
-                self.optimizer.step()
+                self._inner_step()
         else:
             applied = False
             for b in self.buckets:
@@ -306,6 +375,7 @@ class EagerOptimizer:
         return {
             "steps": s0["local_step"], "participated": s0["participated"], "absent": s0["absent"],
             "activated": s0["activated"], "forced_sync": s0["sync_rounds"], "dropped_grads": s0["dropped_grads"],
+            "folded_grads": s0.get("folded_grads", 0),
             "mean_contributors": s0["contrib_sum"] / part, "wait_ms": sum(p["wait_ns"] for p in per) / 1e6,
             "staleness": s0["latest_round"] - s0["last_round"] if s0["latest_round"] >= s0["last_round"] else 0,
             "status": max(p["status"] for p in per), "buckets": len(per),
@@ -334,8 +404,8 @@ class EagerOptimizer:
                 if b.mom is not None:
                     yield p, _view_like(b.mom, off, p)
                 else:
-                    st = self.optimizer.state.get(p, {})
-                    yield p, st.get("momentum_buffer")
+                    key = b.masters[b.params.index(p)] if b.masters is not None else p
+                    yield p, self.optimizer.state.get(key, {}).get("momentum_buffer")
 
     def state_dict(self) -> dict:
         sd = {"inner": self.optimizer.state_dict(), "steps": self.steps, "mode": self.mode,
@@ -354,6 +424,8 @@ class EagerOptimizer:
                 b.mom.copy_(m)
                 if b.w16 is not None:
                     b.w16.copy_(b.w32)
+        else:   # a checkpoint without master weights: the parameters as loaded are the truth
+            self.refresh_master_from_params()
 
     def resync_from_rank0(self):
         """Overwrite this replica with rank 0's weights, momentum and (optionally
@@ -371,8 +443,12 @@ class EagerOptimizer:
                 if b.w16 is not None:
                     b.w16.copy_(b.w32)
             else:
-                for p in b.params:
-                    g.bcast(p.data)
+                if b.masters is not None:
+                    g.bcast(b.w32)
+                    b.w16.copy_(b.w32)
+                for p in (b.masters if b.masters is not None else b.params):
+                    if b.masters is None:
+                        g.bcast(p.data)
                     buf = self.optimizer.state.get(p, {}).get("momentum_buffer")
                     if buf is not None:
                         g.bcast(buf)

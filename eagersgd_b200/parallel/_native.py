@@ -21,6 +21,7 @@ STATUS_BITS = {
     1 << 5: "participant found data in its own mailbox",
     1 << 6: "timeout waiting for a publish slot to be released",
     1 << 7: "timeout waiting for a participant's share of the reduced vector (two-shot reduction)",
+    1 << 8: "the blocks of a rank's reduce kernel did not meet at a barrier in time",
 }
 
 
@@ -38,7 +39,7 @@ class ChannelError(RuntimeError):
 
 class CpuParams(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
-                "rank world base_mode include_stale average home dtype reserved".split()] + \
+                "rank world base_mode include_stale average home dtype flags".split()] + \
                [("limiter", C.c_int64)] + \
                [(n, C.c_uint64) for n in "seed timeout_ns grace_ns count".split()]
 
@@ -51,19 +52,20 @@ class StepInfo(C.Structure):
 
 class ChannelDesc(C.Structure):
     _fields_ = [("ctl", C.c_void_p * MAX_RANKS), ("slot0", C.c_void_p * MAX_RANKS),
-                ("slot1", C.c_void_p * MAX_RANKS), ("mbox", C.c_void_p * MAX_RANKS),
-                ("gath", C.c_void_p * MAX_RANKS)] + \
+                ("slot1", C.c_void_p * MAX_RANKS), ("red", C.c_void_p * MAX_RANKS),
+                ("rsum", C.c_void_p * MAX_RANKS)] + \
                [(n, C.c_int32) for n in
                 "rank world base_mode include_stale average home slot_bf16 grad_in_bf16".split()] + \
                [("limiter", C.c_int64)] + \
                [(n, C.c_uint64) for n in "seed timeout_ns grace_ns count".split()] + \
                [(n, C.c_void_p) for n in "grad_in w32 mom w16 out".split()] + \
                [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p), ("two_shot_min", C.c_uint64),
-                ("two_shot_parts", C.c_int32), ("pad3", C.c_int32)]
+                ("accumulate", C.c_int32), ("adaptive_grace", C.c_int32), ("clear_grad", C.c_int32),
+                ("pad3", C.c_int32)]
 
 
 STAT_NAMES = ("local_step", "participated", "absent", "activated", "sync_rounds", "dropped_grads",
-              "contrib_sum", "wait_ns", "last_round", "last_contrib", "status", "latest_round")
+              "contrib_sum", "wait_ns", "last_round", "last_contrib", "status", "latest_round", "folded_grads")
 
 _host = None
 _cuda = None
@@ -101,7 +103,9 @@ def cuda():
         lib.esgd_dev_channel_bytes.restype = C.c_uint64
         lib.esgd_dev_ctl_bytes.restype = C.c_uint64
         lib.esgd_channel_configure.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
-        lib.esgd_channel_step.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_void_p]
+        lib.esgd_channel_step.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
+        lib.esgd_channel_applied.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]
+        lib.esgd_set_hyper.argtypes = [C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p]
         lib.esgd_channel_flush.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
         lib.esgd_emulated_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         lib.esgd_spin.argtypes = [C.c_uint64, C.c_void_p]

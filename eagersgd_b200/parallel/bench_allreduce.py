@@ -45,7 +45,7 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
             kw = dict(out=torch.empty(count, dtype=dtype, device=dev))
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=dtype, mode=mode, limiter=-1,
                            average="world", timeout_s=20.0, grace_us=0.0,
-                           two_shot_min=None if one_shot else 1 << 18, two_shot_parts=2, **kw)
+                           two_shot_min=None if one_shot else 1 << 16, **kw)
     buf = grad.clone()
     times = []
     for it in range(iters + 3):

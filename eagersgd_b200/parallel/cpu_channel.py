@@ -105,7 +105,8 @@ class CpuChannel:
 
     def __init__(self, bases: Sequence[int], rank: int, world: int, count: int, np_dtype=np.float32,
                  mode: str = "solo", limiter: int = 32, seed: int = 6545343, average: str = "contributors",
-                 include_stale: bool = True, timeout_s: float = 60.0, grace_us: float = 0.0, home: int = 0):
+                 include_stale: bool = True, timeout_s: float = 60.0, grace_us: float = 0.0, home: int = 0,
+                 accumulate: bool = False, adaptive_grace: bool = False):
         self.lib = N.host()
         self.rank, self.world, self.count = rank, world, count
         self.np_dtype = np.dtype(np_dtype)
@@ -113,7 +114,8 @@ class CpuChannel:
             raise ValueError("integer buffers support average='sum' only")
         self._bases = (C.c_void_p * world)(*bases)
         self.params = N.CpuParams(rank=rank, world=world, base_mode=_MODES[mode], include_stale=int(include_stale),
-                                  average=_AVG[average], home=home, dtype=_NP_DTYPES[self.np_dtype], reserved=0,
+                                  average=_AVG[average], home=home, dtype=_NP_DTYPES[self.np_dtype],
+                                  flags=int(accumulate) | (int(adaptive_grace) << 1),
                                   limiter=limiter, seed=seed, timeout_ns=int(timeout_s * 1e9),
                                   grace_ns=int(grace_us * 1e3), count=count)
         self.info = N.StepInfo()

@@ -1,7 +1,7 @@
 """NVLink backend of the partial allreduce: peer-mapped arenas + sm_100a kernels.
 
 Each rank allocates one arena per channel with ``cudaMalloc``
-(``[control block | publish slot 0 | publish slot 1 | fp32 mailbox | fp32 gather buffer]``), exports
+(``[control block | publish slot 0 | publish slot 1 | shard buffer | fp32 running sum]``), exports
 it with a CUDA IPC handle and maps every peer's arena, so the kernels read and
 write the other GPUs' memory directly over NVLink 5 / NVSwitch.  This replaces
 the reference's buffers, pools and MPI transport (fflib2 src/ffbuffer.c,
@@ -21,11 +21,17 @@ from . import _native as N
 _MODES = {"solo": N.MODE_SOLO, "majority": N.MODE_MAJORITY, "sync": N.MODE_SYNC}
 _AVG = {"contributors": N.AVG_CONTRIBUTORS, "world": N.AVG_WORLD, "sum": N.AVG_SUM}
 HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
-# Elements from which a round with several reducers is reduced in two shots, and the fewest participants for it.
-# Measured on 8 GPUs (bf16): 25 MiB one-shot 387 us, two-shot 437 us; 256 MiB one-shot 3117 us, two-shot 2753 us --
-# the gather's peer stores cost more per byte than the peer loads they save, so only very large buckets take it.
-TWO_SHOT_MIN = 1 << 26
-TWO_SHOT_PARTS = 5
+# Elements from which a round with several participants and at least three contributors is reduced in two
+# shots (reduce-scatter by peer loads, then every participant pulls the other shares): below it the extra
+# flag round trip costs more than the bytes it saves.
+TWO_SHOT_MIN = 1 << 16
+_FLOAT_DTYPES = (torch.float32, torch.bfloat16)
+
+
+def _check_dtype(t: Optional[torch.Tensor], what: str, allowed=_FLOAT_DTYPES) -> None:
+    if t is not None and t.dtype not in allowed:
+        raise ValueError("%s must be %s, not %s: the kernels of the partial allreduce read and write float32 and "
+                         "bfloat16 only" % (what, " or ".join(str(a) for a in allowed), t.dtype))
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -40,9 +46,9 @@ class ArenaLayout:
         self.ctl = 0
         self.slot0 = _align(int(N.cuda().esgd_dev_ctl_bytes()))
         self.slot1 = self.slot0 + _align(count * esz)
-        self.mbox = self.slot1 + _align(count * esz)
-        self.gath = self.mbox + _align(count * 4)
-        self.total = self.gath + _align(count * 4)
+        self.red = self.slot1 + _align(count * esz)
+        self.rsum = self.red + _align(count * esz)
+        self.total = self.rsum + _align(count * 4)
 
 
 class Arena:
@@ -76,9 +82,12 @@ class NvlinkChannel:
     ``mom`` (and optionally ``w16``) the reduction is fused with the momentum-SGD
     update; otherwise the averaged gradient is written to ``out``.
 
-    Channels of at least ``two_shot_min`` elements reduce in two shots when a round
-    has at least ``two_shot_parts`` participants (each sums its share and stores it
-    into every participant's gather buffer); ``two_shot_min=None`` keeps the one-shot form.
+    Channels of at least ``two_shot_min`` elements reduce in two shots when a round has
+    several participants and at least three contributors (each participant sums its share,
+    then pulls the others' shares); ``two_shot_min=None`` keeps the one-shot form.
+    ``accumulate`` folds a gradient that no round picked up into the rank's next publish of
+    the same slot instead of dropping it; ``clear_grad`` zeroes ``grad_in`` behind the copy
+    into the publish slot, so the caller needs no separate fill before the next backward.
     """
 
     def __init__(self, count: int, rank: int, world: int, bases: List[int], device: torch.device,
@@ -88,7 +97,18 @@ class NvlinkChannel:
                  w32: Optional[torch.Tensor] = None, mom: Optional[torch.Tensor] = None,
                  w16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  hyper: Optional[torch.Tensor] = None, max_blocks: int = 592,
-                 two_shot_min: Optional[int] = TWO_SHOT_MIN, two_shot_parts: int = TWO_SHOT_PARTS):
+                 two_shot_min: Optional[int] = TWO_SHOT_MIN, accumulate: bool = False,
+                 adaptive_grace: bool = True, clear_grad: bool = False):
+        if slot_dtype not in _FLOAT_DTYPES:
+            raise ValueError("slot_dtype must be torch.float32 or torch.bfloat16, not %s" % slot_dtype)
+        _check_dtype(grad_in, "grad_in")
+        _check_dtype(w32, "w32", (torch.float32,))
+        _check_dtype(mom, "mom", (torch.float32,))
+        _check_dtype(w16, "w16", (torch.bfloat16,))
+        _check_dtype(out, "out")
+        for name, t in (("w32", w32), ("mom", mom), ("w16", w16), ("out", out)):
+            if t is not None and (t.numel() != count or not t.is_contiguous()):
+                raise ValueError("%s must be a contiguous tensor of %d elements" % (name, count))
         self.lib = N.cuda()
         self.count, self.rank, self.world, self.device = count, rank, world, device
         self.max_blocks = max_blocks
@@ -107,11 +127,11 @@ class NvlinkChannel:
             d.ctl[j] = bases[j] + L.ctl
             d.slot0[j] = bases[j] + L.slot0
             d.slot1[j] = bases[j] + L.slot1
-            d.mbox[j] = bases[j] + L.mbox
-            d.gath[j] = bases[j] + L.gath if two_shot_min is not None else None
+            d.red[j] = bases[j] + L.red if two_shot_min is not None else None
+            d.rsum[j] = bases[j] + L.rsum
         d.two_shot_min = int(two_shot_min) if two_shot_min is not None else 0
-        d.two_shot_parts = int(two_shot_parts)
-        self.two_shot = int(two_shot_min is not None and world >= max(2, two_shot_parts) and count >= two_shot_min)
+        d.accumulate, d.adaptive_grace, d.clear_grad = int(accumulate), int(adaptive_grace), int(clear_grad)
+        self.two_shot = int(two_shot_min is not None and world >= 2 and count >= two_shot_min)
         d.rank, d.world, d.base_mode = rank, world, _MODES[mode]
         d.include_stale, d.average, d.home = int(include_stale), _AVG[average], home
         d.slot_bf16 = int(slot_dtype == torch.bfloat16)
@@ -136,11 +156,26 @@ class NvlinkChannel:
         return self._dch.data_ptr()
 
     def step(self, stream: Optional[torch.cuda.Stream] = None) -> None:
-        """Enqueue pack + control + reduce/update for one step on ``stream``."""
+        """Enqueue one step on ``stream``: pack + control, then reduce + update."""
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, self.two_shot,
-                                                s.cuda_stream),
+        N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
                      "partial allreduce launch")
+
+    def set_hyper(self, lr: float, momentum: float, weight_decay: float, nesterov: bool, grad_scale: float,
+                  stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Enqueue new hyper-parameters on ``stream``; steps enqueued later on streams that wait for it read them."""
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_set_hyper(self.hyper.data_ptr(), lr, momentum, weight_decay, int(nesterov),
+                                             grad_scale, s.cuda_stream), "hyper-parameter update")
+
+    def applied(self) -> bool:
+        """Whether the newest step applied anything (it took part in a round or collected missed ones).
+        Synchronises with the current stream."""
+        v = C.c_int(0)
+        s = torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_channel_applied(self._dch.data_ptr(), C.byref(v), s.cuda_stream),
+                     "reading the step's outcome")
+        return bool(v.value)
 
     def flush(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)

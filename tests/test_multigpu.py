@@ -175,7 +175,7 @@ def test_missing_rank_is_detected_by_bounded_wait():
 
 
 def _two_shot_vs_nccl(rank, world, slot_bf16):
-    """Random gradients through the two-shot data phase (reduce-scatter by peer loads, gather by peer stores)
+    """Random gradients through the two-shot data phase (reduce-scatter and gather, both by peer loads)
     against NCCL's allreduce of the same tensors, plus the one-shot form of the same channel."""
     es, group = _setup(rank, world)
     import torch.distributed as dist
@@ -193,7 +193,7 @@ def _two_shot_vs_nccl(rank, world, slot_bf16):
         grad = torch.zeros(count, device=dev)
         out = torch.zeros(count, device=dev)
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=sdt, mode="sync", limiter=-1,
-                           average="world", out=out, timeout_s=5.0, grace_us=0.0, two_shot_min=tsm, two_shot_parts=2)
+                           average="world", out=out, timeout_s=5.0, grace_us=0.0, two_shot_min=tsm)
         res = []
         for g in grads:
             grad.copy_(g)
@@ -225,4 +225,4 @@ def test_two_shot_matches_nccl_and_one_shot(slot_bf16):
         assert flags == [0, 1]
         assert stats == [0, 0]
         assert same, "two-shot and one-shot reductions differ"
-        assert err < 2e-6
+        assert err < (2e-2 if slot_bf16 else 2e-6)      # the result is rounded to the slot's element type

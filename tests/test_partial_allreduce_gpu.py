@@ -201,13 +201,14 @@ def test_optimizer_wrapper_generic_inner_optimizer():
 @pytest.mark.parametrize("world", [2, 3, 8])
 @pytest.mark.parametrize("slot_dtype,fused", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 def test_two_shot_reduction_is_bit_identical_to_one_shot(world, slot_dtype, fused):
-    """Reduce-scatter by peer loads + gather by peer stores gives the very bits of the one-shot reduction:
-    averaged gradients, and fp32 master weights / momentum / bf16 weights after fused updates."""
+    """Reduce-scatter + pull-gather (both by peer loads) gives the very bits of the one-shot reduction:
+    averaged gradients, and fp32 master weights / momentum / bf16 weights after fused updates.  The value
+    a round hands out is rounded to the slot's element type in both forms."""
     from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
     count = 8 * 1237          # not a multiple of the number of participants
     gdt = torch.bfloat16 if slot_dtype == torch.bfloat16 else torch.float32
     worlds = [EmulatedWorld(world, count, _dev(), slot_dtype=slot_dtype, grad_dtype=gdt, fused=fused, mode="sync",
-                            limiter=-1, average="contributors", timeout_s=2.0, two_shot_min=tsm, two_shot_parts=2)
+                            limiter=-1, average="contributors", timeout_s=2.0, two_shot_min=tsm)
               for tsm in (None, 0)]
     try:
         torch.manual_seed(world)
@@ -231,7 +232,8 @@ def test_two_shot_reduction_is_bit_identical_to_one_shot(world, slot_dtype, fuse
                 else:
                     assert torch.equal(a.outs[r], b.outs[r]), (k, r)
                     ref = torch.stack([g.float() for g in gs]).sum(0) / world
-                    assert torch.allclose(b.outs[r], ref, rtol=1e-5, atol=1e-6)
+                    tol = dict(rtol=1e-5, atol=1e-6) if slot_dtype == torch.float32 else dict(rtol=8e-3, atol=1e-3)
+                    assert torch.allclose(b.outs[r], ref, **tol)
         for w in worlds:
             assert all(c.stats()["status"] == 0 for c in w.channels)
     finally:
@@ -246,7 +248,7 @@ def test_two_shot_eager_rounds_replicas_agree(mode):
     from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
     world, count, steps = 6, 8 * 511, 40
     w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode=mode, limiter=7, average="sum",
-                      timeout_s=2.0, grace_us=0.0, two_shot_min=0, two_shot_parts=2)
+                      timeout_s=2.0, grace_us=0.0, two_shot_min=0)
     rng = random.Random(17 + len(mode))
     ramp = torch.arange(count, device=_dev(), dtype=torch.float32) % 13
     applied = [torch.zeros(count, dtype=torch.float64, device=_dev()) for _ in range(world)]
@@ -273,3 +275,108 @@ def test_two_shot_eager_rounds_replicas_agree(mode):
         assert sum(s["participated"] for s in sts) > steps      # rounds with several participants happened
     finally:
         w.close()
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+@pytest.mark.parametrize("two_shot_min", [None, 0])
+def test_accumulate_loses_no_gradient(mode, two_shot_min):
+    """With ``accumulate`` a gradient that no round picked up rides along with the rank's next publish of the
+    same slot; after two closing rounds in which everybody is on time, every published gradient has been
+    applied exactly once on every rank and none was dropped."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    world, count, steps = 4, 8 * 129, 36
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.float32, mode=mode, limiter=-1, average="sum",
+                      timeout_s=2.0, grace_us=1000.0, adaptive_grace=False, accumulate=True, two_shot_min=two_shot_min)
+    rng = random.Random(3 + len(mode))
+    applied = [torch.zeros(count, dtype=torch.float64, device=_dev()) for _ in range(world)]
+    try:
+        for k in range(1, steps + 1):
+            for r in range(world):
+                w.grads[r].fill_(float((r + 1) * 100 + k))
+            late = k <= steps - 2       # the last two rounds: everybody inside the grace window
+            w.step(delays_us=[rng.choice([0, 0, 50, 4000]) if late else 0 for _ in range(world)])
+            torch.cuda.synchronize()
+            for r in range(world):
+                applied[r] += w.outs[r].double()
+        w.step(flush=True)
+        torch.cuda.synchronize()
+        for r in range(world):
+            applied[r] += w.outs[r].double()
+        published = float(sum((r + 1) * 100 + k for r in range(world) for k in range(1, steps + 1)))
+        sts = [c.stats() for c in w.channels]
+        for r in range(world):
+            assert torch.all(applied[r] == published), (r, applied[r][0].item(), published)
+            assert sts[r]["status"] == 0 and sts[r]["dropped_grads"] == 0
+        assert sum(s["folded_grads"] for s in sts) > 0
+    finally:
+        w.close()
+
+
+def test_late_ranks_pull_what_they_missed_fused():
+    """Fused update under imbalance with plain SGD (no momentum, no weight decay): whatever order the rounds
+    reach a rank in, participants and late ranks end with the same fp32 master weights up to rounding."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld
+    world, count, steps = 8, 8 * 640, 24
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.bfloat16, grad_dtype=torch.bfloat16, fused=True,
+                      mode="solo", limiter=5, average="contributors", timeout_s=2.0, grace_us=0.0, two_shot_min=0)
+    rng = random.Random(5)
+    try:
+        w.hyper[:5] = torch.tensor([0.05, 0.0, 0.0, 0.0, 1.0])
+        for k in range(steps):
+            for r in range(world):
+                w.grads[r].copy_(torch.randn(count, device=_dev()).to(torch.bfloat16))
+            w.step(delays_us=[rng.choice([0, 0, 0, 40, 400]) for _ in range(world)])
+        w.step(flush=True)
+        torch.cuda.synchronize()
+        sts = [c.stats() for c in w.channels]
+        assert all(s["status"] == 0 for s in sts)
+        assert sum(s["absent"] for s in sts) > 0 and sum(s["participated"] for s in sts) > steps
+        for r in range(1, world):
+            assert torch.allclose(w.w32[r], w.w32[0], rtol=0, atol=2e-5), (r, (w.w32[r] - w.w32[0]).abs().max())
+        assert w.w32[0].abs().max() > 0
+    finally:
+        w.close()
+
+
+def test_half_precision_float16_is_rejected():
+    """The kernels read and write float32 and bfloat16 only: float16 tensors are refused up front
+    instead of being read with the wrong element size."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas
+    dev = _dev()
+    m = torch.nn.Linear(16, 16).to(dev).half()
+    with pytest.raises(ValueError):
+        es.SoloAllreduceOptimizer(torch.optim.SGD(m.parameters(), lr=0.1), es.Group())
+    arena, bases = create_arenas(64, torch.float32, 0, 1)
+    try:
+        with pytest.raises(ValueError):
+            NvlinkChannel(64, 0, 1, bases, dev, torch.zeros(64, dtype=torch.float16, device=dev),
+                          slot_dtype=torch.float32, out=torch.zeros(64, device=dev))
+        with pytest.raises(ValueError):
+            NvlinkChannel(64, 0, 1, bases, dev, torch.zeros(64, device=dev), slot_dtype=torch.float16,
+                          out=torch.zeros(64, device=dev))
+    finally:
+        arena.free()
+
+
+def test_wrapped_optimizer_keeps_fp32_masters_and_skips_idle_steps():
+    """A generic optimizer around bf16 parameters steps fp32 master copies (small updates are not rounded
+    away) and the bf16 weights follow them."""
+    import eagersgd_b200 as es
+    dev = _dev()
+    torch.manual_seed(3)
+    m = torch.nn.Linear(64, 64, bias=False).to(dev).to(torch.bfloat16)
+    w0 = m.weight.detach().float().clone()
+    opt = es.SoloAllreduceOptimizer(torch.optim.Adam(m.parameters(), lr=1e-5), es.Group())
+    assert not opt.fused
+    for _ in range(8):
+        opt.zero_grad()
+        m(torch.randn(8, 64, device=dev, dtype=torch.bfloat16)).float().square().mean().backward()
+        opt.step()
+    torch.cuda.synchronize()
+    (p, master), = list(opt.master_params())
+    assert master.dtype == torch.float32 and p.dtype == torch.bfloat16
+    moved = (master - w0).abs()
+    assert moved.max() > 0 and moved.max() < 2e-4          # eight Adam steps of 1e-5: far below bf16 resolution of O(1) weights
+    assert torch.equal(p.detach(), master.to(torch.bfloat16))
+    opt.close()

@@ -183,3 +183,70 @@ def test_trace_ring_and_watchdog():
     assert seen and seen[0].status == 2
     with pytest.raises(N.ChannelError):
         wd.raise_if_failed()
+
+
+@pytest.mark.parametrize("mode", ["solo", "majority"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_accumulate_loses_no_gradient(mode, world):
+    """With ``accumulate`` a gradient that no round picked up is folded into the rank's next publish of
+    the same slot: after two closing synchronous rounds every published gradient has been applied exactly
+    once on every rank (the reference drops such gradients: opt_esgd_solo_imagenet_imbalance.py:301-314)."""
+    count, steps = 64, 50
+    segs = LocalSegments(world, count, np.int64)
+    applied = [np.zeros(count, dtype=np.int64) for _ in range(world)]
+    stats = [None] * world
+    errors = []
+    phase = threading.Barrier(world)      # every rank changes the channel's mode at the same point
+
+    def worker(r):
+        try:
+            kw = dict(seed=99, average="sum", timeout_s=30, accumulate=True)
+            ch = CpuChannel(segs.bases, r, world, count, np.int64, mode=mode, limiter=-1, **kw)
+            rng = random.Random(7 * world + r)
+            for k in range(1, steps + 1):
+                if rng.random() < 0.4 or r == 0:
+                    time.sleep(rng.random() * 0.003)
+                out, _ = ch.step(np.full(count, (r + 1) * 1000 + k, dtype=np.int64))
+                assert np.all(out == out[0])
+                applied[r] += out
+            phase.wait()
+            closing = CpuChannel(segs.bases, r, world, count, np.int64, mode="sync", limiter=-1, **kw)
+            for _ in range(2):   # both slot parities are flushed
+                out, _ = closing.step(np.zeros(count, dtype=np.int64))
+                applied[r] += out
+            stats[r] = closing.stats()
+        except Exception as e:  # noqa
+            errors.append((r, repr(e)))
+
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errors, errors
+    published = sum((r + 1) * 1000 + k for r in range(world) for k in range(1, steps + 1))
+    for r in range(world):
+        assert applied[r][0] == published, (r, applied[r][0], published)
+        assert stats[r]["status"] == 0 and stats[r]["dropped_grads"] == 0
+    assert sum(s["folded_grads"] for s in stats) > 0      # the case did occur
+
+
+def test_adaptive_grace_window_tracks_arrival_spread():
+    """Ranks arriving within a few hundred microseconds of each other end up in the same round once the
+    activators have learnt the spread; the window never exceeds ``grace_us``."""
+    world, count, steps = 3, 16, 40
+    segs = LocalSegments(world, count, np.float32)
+    fresh = [[] for _ in range(world)]
+    barrier = threading.Barrier(world)
+
+    def worker(r):
+        ch = CpuChannel(segs.bases, r, world, count, np.float32, mode="solo", limiter=-1, timeout_s=30,
+                        grace_us=20000.0, adaptive_grace=True)
+        for k in range(steps):
+            barrier.wait()
+            time.sleep(0.0003 * r)
+            _, info = ch.step(np.ones(count, dtype=np.float32))
+            fresh[r].append(info.n_fresh if info.role == N.ROLE_PARTICIPANT else 0)
+
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert sum(1 for f in fresh[0][20:] if f == world) >= 10
