@@ -145,6 +145,8 @@ def load(model: nn.Module, optimizer, model_dir: str, rank: int) -> int:
                 own[k].copy_(v.to(own[k].device, own[k].dtype))
     if optimizer is not None and "optimizer" in state:
         optimizer.load_state_dict(state["optimizer"])
+    elif optimizer is not None and hasattr(optimizer, "refresh_master_from_params"):
+        optimizer.refresh_master_from_params()   # a model-only checkpoint: master weights follow the parameters
     return int(state["global_step"])
 
 

@@ -142,6 +142,11 @@ int esgd_bn_forward_noalloc(const void* y, const void* residual, void* z, const 
                             float eps, void* stream) {
   if (y == nullptr || z == nullptr || gamma == nullptr || beta == nullptr || M <= 0 || C <= 0 || (C % 8) != 0)
     return ESGD_BN_NOALLOC_BAD_ARGUMENT;
+  // y, residual and z are read and written 16 bytes at a time: a pointer into the middle of a vector
+  // would fault on the device, so it is refused here instead
+  if ((((uintptr_t)y | (uintptr_t)z | (uintptr_t)residual) & 15u) != 0) return ESGD_BN_NOALLOC_BAD_ARGUMENT;
+  if ((((uintptr_t)gamma | (uintptr_t)beta | (uintptr_t)running_mean | (uintptr_t)running_var) & 3u) != 0)
+    return ESGD_BN_NOALLOC_BAD_ARGUMENT;
   if (C > kMaxC) return ESGD_BN_NOALLOC_TOO_MANY_CHANNELS;
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
@@ -173,7 +178,8 @@ const char* esgd_bn_forward_noalloc_strerror(int code) {
   switch (code) {
     case 0: return "success";
     case ESGD_BN_NOALLOC_BAD_ARGUMENT:
-      return "bad argument: pointers must be non-null, M and C positive, C a multiple of 8";
+      return "bad argument: pointers must be non-null, y / residual / z 16-byte aligned, M and C positive, "
+             "C a multiple of 8";
     case ESGD_BN_NOALLOC_TOO_MANY_CHANNELS:
       return "too many channels: the built-in work area holds at most 4096 channels";
     case ESGD_BN_NOALLOC_SETUP_FAILED:

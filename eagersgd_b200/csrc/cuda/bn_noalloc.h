@@ -26,6 +26,9 @@
  *   - Inputs and outputs are still the caller's: y, residual (may be NULL) and z are bf16
  *     [M, C] row-major (NHWC activations), gamma / beta fp32 [C]; running_mean / running_var
  *     (fp32 [C]) may be NULL.  momentum is the weight of the new batch statistic.
+ *   - y, residual and z must start on a 16-byte boundary (the kernels move eight bf16 values
+ *     per access); a pointer that does not is refused with ESGD_BN_NOALLOC_BAD_ARGUMENT, as is
+ *     a channel count that is not a multiple of 8.
  * Returns 0 on success, a negative ESGD_BN_NOALLOC_* code, or a positive cudaError_t.
  */
 #ifndef ESGD_BN_NOALLOC_H

@@ -37,6 +37,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
 }
 
 // One block per sample.  loss_sum accumulates sum_i loss_i * inv_batch; dlogits = (softmax - onehot) * grad_scale.
+// A label outside [0, classes) is never used as an index: that sample gets zero loss and a zero gradient row.
 template <typename T>
 __global__ void __launch_bounds__(256) softmax_ce_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels,
                                                          int classes, int ld, float inv_batch, float grad_scale,
@@ -51,10 +52,12 @@ __global__ void __launch_bounds__(256) softmax_ce_kernel(const T* __restrict__ l
   float se = 0.0f;
   for (int c = threadIdx.x; c < classes; c += blockDim.x) se += __expf(to_f(x[c]) - mx);
   se = block_reduce(se, false, sh);
-  const int label = (int)labels[row];
+  const int64_t raw_label = labels[row];
+  const bool valid = raw_label >= 0 && raw_label < (int64_t)classes;
+  const int label = valid ? (int)raw_label : 0;
   const float lse = mx + __logf(se);
   if (threadIdx.x == 0) {
-    float li = lse - to_f(x[label]);
+    float li = valid ? lse - to_f(x[label]) : 0.0f;
     if (per_sample != nullptr) per_sample[row] = li;
     atomicAdd(loss_sum, li * inv_batch);
   }
@@ -63,7 +66,7 @@ __global__ void __launch_bounds__(256) softmax_ce_kernel(const T* __restrict__ l
     const float inv_se = 1.0f / se;
     for (int c = threadIdx.x; c < classes; c += blockDim.x) {
       float p = __expf(to_f(x[c]) - mx) * inv_se;
-      d[c] = from_f<T>((p - (c == label ? 1.0f : 0.0f)) * grad_scale);
+      d[c] = from_f<T>(valid ? (p - (c == label ? 1.0f : 0.0f)) * grad_scale : 0.0f);
     }
   }
 }

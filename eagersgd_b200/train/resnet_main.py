@@ -116,6 +116,8 @@ def main(argv=None):
                      if args.lars else None, loss_scale=args.loss_scale)
     if args.pretrained_model_checkpoint_path:
         ckpt.import_tf_layout(step.model, args.pretrained_model_checkpoint_path, exclude=("dense",))
+        if hasattr(step.opt, "refresh_master_from_params"):
+            step.opt.refresh_master_from_params()    # the fp32 masters follow the imported weights
     global_step = ckpt.load(step.model, step.opt if hasattr(step.opt, "state_dict") else None, args.model_dir, group.rank)
 
     train_sampler, val_sampler = build_data(args, info, group)
