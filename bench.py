@@ -97,24 +97,33 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference's training path is TensorFlow 1.x + Horovod + mpi4py + MPI (fflib2 links libmpi, the
-    custom op links tensorflow_framework); its vendored Deep500 package installs but cannot be imported."""
+    """The reference's training path is TensorFlow 1.x + Horovod + mpi4py + an MPI library (the custom op
+    links tensorflow_framework; its vendored Deep500 package installs but cannot be imported), so the
+    headline metric has no reference value on this machine.  What of the reference does run here is its
+    communication library: fflib2, built unmodified against a shared-memory MPI subset, driven by its own
+    SGD-loop timing programs (evaluation/ssgd.c, rsgd.c, randomsgd.c).  Their figures ride along in
+    ``fflib2_sgd_loops``; ``python -m eagersgd_b200.parallel.bench_allreduce`` is this framework's
+    counterpart of those loops."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
     missing = []
     for mod in ("tensorflow", "horovod", "mpi4py", "onnx"):
         try:
             __import__(mod)
         except Exception:
             missing.append(mod)
-    import shutil
-    if shutil.which("mpirun") is None and shutil.which("mpiexec") is None:
-        missing.append("an MPI launcher")
-    if missing:
-        why = ("reference cannot run here: missing " + ", ".join(missing) + "; the repository root is not an installable "
-               "project and its vendored deep500 package fails at import (No module named 'onnx'); no network")
-    else:
-        why = "reference run loop needs the Piz Daint SLURM environment; not reproducible on this box"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    why = ("reference training path cannot run here: missing " + ", ".join(missing or ["the Piz Daint SLURM setup"]) +
+           "; the repository root is not an installable project and its vendored deep500 package fails at import; "
+           "no network")
+    out = {"impl": "reference", "unavailable": why}
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import run_reference
+        ranks = sorted({2, max(2, min(args.gpus, 8))})
+        out["fflib2_sgd_loops"] = run_reference.run(ranks=ranks, counts=(1024, 262144, 6553600), iters=12)
+    except Exception as e:  # noqa
+        out["fflib2_sgd_loops"] = {"unavailable": repr(e)[:200]}
+    print(json.dumps(out))
     return 0
 
 

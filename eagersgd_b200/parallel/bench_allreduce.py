@@ -3,9 +3,10 @@
     torchrun --nproc-per-node 8 -m eagersgd_b200.parallel.bench_allreduce --sizes 4096,1048576,268435456 --late 2
 
 For every buffer size and dtype, ``--iters`` rounds are timed on the device: all ranks are aligned
-with a barrier, ``--late`` seeded-random ranks then arrive late by U(0, ``--late-ms``) (a bounded spin
-kernel on their stream), and each rank measures the time from its own arrival to the completion of
-its collective (CUDA events).  Reported per case: mean and max over ranks of the per-rank latency
+with a barrier, every rank holds its stream for ``--hold-us`` with a bounded spin kernel (so that the
+launches that follow are already queued when the clock starts and host launch overhead is not part of
+the figure), ``--late`` seeded-random ranks hold it longer by U(0, ``--late-ms``), and each rank measures
+the time from its own arrival to the completion of its collective (CUDA events).  Reported per case: mean and max over ranks of the per-rank latency
 (the reference's SGD-loop tests print the mean over ranks: fflib2 evaluation/ssgd.c:75-95, rsgd.c:
 90-111, randomsgd.c:90-111) and, for the synchronous variants, the bus bandwidth
 2(P-1)/P * bytes / time.  Same protocol as the reference's allreduce micro-benchmark
@@ -27,7 +28,8 @@ from .group import init as init_group, finalize
 from .nvlink_channel import NvlinkChannel, create_arenas
 
 
-def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False):
+def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False, grace_us=50.0,
+             hold_us=300.0):
     dev = group.device
     esz = 2 if dtype == torch.bfloat16 else 4
     count = max(nbytes // esz // 8 * 8, 8)
@@ -44,7 +46,7 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
         else:
             kw = dict(out=torch.empty(count, dtype=dtype, device=dev))
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=dtype, mode=mode, limiter=-1,
-                           average="world", timeout_s=20.0, grace_us=0.0,
+                           average="world", timeout_s=20.0, grace_us=grace_us,
                            two_shot_min=None if one_shot else 1 << 16, **kw)
     buf = grad.clone()
     times = []
@@ -53,8 +55,9 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
         for _ in range(late):
             delays[rng.randrange(group.world)] = rng.uniform(0, late_ms * 1e-3)
         group.barrier()
-        if delays[group.rank] > 0:
-            N.check_cuda(N.cuda().esgd_spin(int(delays[group.rank] * 1e9), stream.cuda_stream), "delay")
+        hold_ns = int(hold_us * 1e3 + delays[group.rank] * 1e9)
+        if hold_ns > 0:
+            N.check_cuda(N.cuda().esgd_spin(hold_ns, stream.cuda_stream), "delay")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         if mode == "nccl":
@@ -98,13 +101,17 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fused", action="store_true", help="include the fused momentum-SGD update in our kernels")
     ap.add_argument("--one-shot", action="store_true", help="never split the reduction into reduce-scatter + gather")
+    ap.add_argument("--grace-us", type=float, default=50.0,
+                    help="longest time an activator waits for near-simultaneous arrivals (the window adapts below it)")
+    ap.add_argument("--hold-us", type=float, default=300.0,
+                    help="every rank holds its stream this long before the timed region, so the launches are queued")
     args = ap.parse_args(argv)
     group = init_group()
     for size in [int(s) for s in args.sizes.split(",")]:
         for dt in args.dtypes.split(","):
             for mode in args.modes.split(","):
                 r = run_case(group, size, getattr(torch, dt), mode, args.late, args.late_ms, args.iters, 1234, args.fused,
-                             args.one_shot)
+                             args.one_shot, args.grace_us, args.hold_us)
                 if group.rank == 0:
                     print(json.dumps(r), flush=True)
     finalize()
