@@ -40,6 +40,7 @@ __device__ inline void control_abort(DevChannel* ch) {
 
 __device__ inline void control_step(DevChannel* ch, int flush) {
   ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
+  ch->t_phase[1] = DevEnv::now_ns();
   if (flush) {
     ctl_flush<DevEnv>(ch->view, ch->cfg, &ch->plan);
   } else if (me->status & ST_TIMEOUT_SLOT) {   // nothing valid was packed
@@ -49,17 +50,21 @@ __device__ inline void control_step(DevChannel* ch, int flush) {
     ctl_step<DevEnv>(ch->view, ch->cfg, ch->pol, &ch->plan);
   }
   decide_two_shot(ch);
+  ch->t_phase[2] = DevEnv::now_ns();
 }
 
-__global__ void __launch_bounds__(256) pack_ctl_kernel(DevChannel* ch, int flush) {
+__global__ void __launch_bounds__(256, 3) pack_ctl_kernel(DevChannel* ch, int flush) {
   __shared__ int s_flag;
   if (!flush) pack_phase(ch, blockIdx.x, gridDim.x, &s_flag);
-  __threadfence_system();
+  // Device-scope fence per thread, system-scope fence once: the control step fences at system scope before
+  // it publishes the epoch, and that fence carries the other blocks' slot writes with it (they are ordered
+  // before it through this counter).
+  __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(&ch->bar_pack, 1u) == gridDim.x - 1) {
       ch->bar_pack = 0;
-      __threadfence_system();
+      ch->pack_ticket = 0;
       control_step(ch, flush);
     }
   }
@@ -84,7 +89,7 @@ __global__ void __launch_bounds__(256) emulated_step_kernel(DevChannel** chans, 
   if (!flush) pack_phase(ch, 0, 1, &s_flag);
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) control_step(ch, flush);
+  if (threadIdx.x == 0) { ch->pack_ticket = 0; control_step(ch, flush); }
   __threadfence();
   __syncthreads();
   data_phase(ch, 0, 1, &s_flag);
@@ -144,6 +149,10 @@ struct esgd_channel_desc {
   int32_t adaptive_grace;         // the grace window follows the arrival spread (at most grace_ns)
   int32_t clear_grad;             // zero grad_in behind the copy into the publish slot
   int32_t pad3;
+  void* mc_slot0;                 // NVLink multicast addresses of the publish slots and the shard buffer
+  void* mc_slot1;                 // (all null: the arenas have no multicast mapping)
+  void* mc_red;
+  uint64_t mc_min;                // element count from which full rounds go over the switch
 };
 
 uint64_t esgd_dev_channel_bytes(void) { return sizeof(DevChannel); }
@@ -163,6 +172,7 @@ int esgd_channel_configure(void* dch, const esgd_channel_desc* d, void* stream) 
   }
   h.two_shot_min = d->two_shot_min;
   h.clear_grad = d->clear_grad;
+  h.mc_slot[0] = d->mc_slot0; h.mc_slot[1] = d->mc_slot1; h.mc_red = d->mc_red; h.mc_min = d->mc_min;
   h.cfg.rank = d->rank; h.cfg.world = d->world; h.cfg.average_world = d->average; h.cfg.home = d->home;
   h.cfg.timeout_ns = d->timeout_ns; h.cfg.grace_ns = d->grace_ns;
   h.pol.base_mode = d->base_mode; h.pol.include_stale = d->include_stale; h.pol.limiter = d->limiter;
@@ -211,6 +221,15 @@ int esgd_set_hyper(void* hyper, float lr, float momentum, float wd, int nesterov
 // Did the newest step apply anything (participant or drain)?  Synchronises with `stream`.
 int esgd_channel_applied(const void* dch, int* applied, void* stream) {
   cudaError_t e = cudaMemcpyAsync(applied, (const char*)dch + offsetof(DevChannel, applied), sizeof(int),
+                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize((cudaStream_t)stream);
+}
+
+// Device clock (ns) at the phase boundaries of the newest step: first block packing, control start, control
+// end, first data block, own share reduced (two-shot rounds), data end.  Synchronises with `stream`.
+int esgd_channel_times(const void* dch, uint64_t* t8, void* stream) {
+  cudaError_t e = cudaMemcpyAsync(t8, (const char*)dch + offsetof(DevChannel, t_phase), 8 * sizeof(uint64_t),
                                   cudaMemcpyDeviceToHost, (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaStreamSynchronize((cudaStream_t)stream);

@@ -20,6 +20,13 @@
 // gcomp SUM, components/gcomp/ffop_gcomp_operator.c:8-58, plus TF ApplyMomentum
 // on the reference path).
 //
+// When the arenas come from symmetric memory with an NVLink multicast mapping (NVSwitch), a round in which
+// every rank is on time takes a third form: each rank reduces its share with ONE multimem.ld_reduce per
+// vector on the multicast address of the publish slot (the switch sums the eight slots, fp32 accumulate)
+// and broadcasts the rounded result into every rank's shard buffer with multimem.st; the other shares are
+// then read from LOCAL memory.  A rank receives one vector instead of 2(P-1)/P of it.  Rounds that lack
+// somebody, or carry a stale contribution, use the peer-load forms above.
+//
 // Ranks that miss a round get its result later by a pull, not by a push: in a
 // round that lacks somebody every participant adds the round's result to its
 // running sum; a late rank, holding its own mailbox lock (so that no round is in
@@ -42,6 +49,8 @@ struct DevChannel {
   ChannelView view;
   void* slot[kMaxRanks][kSlotDepth];
   void* red[kMaxRanks];      // reduced shares of the running round, slot element type (two-shot form)
+  void* mc_slot[kSlotDepth]; // multicast addresses of the publish slots and of the shard buffer (null: none):
+  void* mc_red;              // a load reduces over every rank's copy, a store lands in every rank's copy
   float* rsum[kMaxRanks];    // running sums of the results of rounds that lacked somebody
   StepConfig cfg;
   StepPolicy pol;
@@ -57,11 +66,17 @@ struct DevChannel {
   int32_t clear_grad;        // zero grad_in once it has been copied into the publish slot
   const float* hyper;        // HP_* values in device memory
   Plan plan;
+  uint32_t pack_ticket;      // the first block to take a ticket checks that the publish slot is free
+  uint32_t pad1;
+  uint64_t pack_word;        // (epoch << 8) | (fate + 2), published by that block for the others
   uint32_t bar_pack;         // blocks that have packed their part (the last one runs the control step)
   uint32_t bar_mid;          // blocks that have reduced their part of this rank's share
   uint32_t bar_end;          // blocks that are done with the data phase
   int32_t applied;           // the last step applied something (participant or drain)
   uint64_t two_shot_min;     // smallest element count that takes the two-shot form
+  uint64_t mc_min;           // smallest element count that goes over the switch when it can
+  uint64_t t_phase[8];       // clock at: first block packing, control start, control end, first data block,
+                             // share reduced (two-shot), data end; for the latency break-down of the benchmarks
 };
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, uint64_t i, float v[8]) {
@@ -175,9 +190,9 @@ __device__ void reduce_range(const DevChannel* ch, uint64_t lo, uint64_t hi, uin
 
 // Two-shot, second half: fetch the share of participant `owner` from its shard buffer and apply it.
 template <typename ST>
-__device__ void pull_share(const DevChannel* ch, int owner, uint64_t lo, uint64_t hi, uint64_t tid,
+__device__ void pull_share(const DevChannel* ch, int from_rank, uint64_t lo, uint64_t hi, uint64_t tid,
                            uint64_t nthreads) {
-  const ST* share = reinterpret_cast<const ST*>(ch->red[owner]);
+  const ST* share = reinterpret_cast<const ST*>(ch->red[from_rank]);
   float* rs = ch->plan.n_push > 0 ? ch->rsum[ch->cfg.rank] : nullptr;
   const Hyper hp(ch->hyper);
   for (uint64_t i = lo + tid * 8; i < hi; i += nthreads * 8) {
@@ -190,6 +205,73 @@ __device__ void pull_share(const DevChannel* ch, int owner, uint64_t lo, uint64_
       store8(rs, i, v);
     }
     apply8(ch, i, g, hp.lr, hp.mu, hp.wd, hp.nesterov, hp.gscale);
+  }
+}
+
+// ---- NVSwitch multicast (multimem) ------------------------------------------------------------------------
+__device__ __forceinline__ void mc_load_sum8(const __nv_bfloat16* mc, uint64_t i, float v[8]) {
+  uint32_t r0, r1, r2, r3;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "l"(mc + i) : "memory");
+  const uint32_t raw[4] = {r0, r1, r2, r3};
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 f = __bfloat1622float2(h[q]);
+    v[2 * q] = f.x;
+    v[2 * q + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void mc_load_sum8(const float* mc, uint64_t i, float v[8]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(mc + i) : "memory");
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(mc + i + 4) : "memory");
+}
+__device__ __forceinline__ void mc_store8(__nv_bfloat16* mc, uint64_t i, const float v[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc + i), "f"(__uint_as_float(raw.x)), "f"(__uint_as_float(raw.y)),
+                  "f"(__uint_as_float(raw.z)), "f"(__uint_as_float(raw.w)) : "memory");
+}
+__device__ __forceinline__ void mc_store8(float* mc, uint64_t i, const float v[8]) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc + i), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc + i + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+
+// Full round over the switch: reduce this rank's share of slot `parity` with in-switch sums, apply it, and
+// broadcast the rounded result into the shard buffer of every rank.
+template <typename ST>
+__device__ void mc_reduce_range(const DevChannel* ch, int parity, uint64_t lo, uint64_t hi, uint64_t tid,
+                                uint64_t nthreads) {
+  const ST* mc_in = reinterpret_cast<const ST*>(ch->mc_slot[parity]);
+  ST* mc_out = reinterpret_cast<ST*>(ch->mc_red);
+  const float scale = ch->plan.scale;
+  const Hyper hp(ch->hyper);
+  constexpr int kUnroll = 2;     // in-switch reductions in flight per thread
+  const uint64_t stride = nthreads * 8;
+  for (uint64_t base = lo + tid * 8; base < hi; base += stride * kUnroll) {
+    float acc[kUnroll][8];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i < hi) mc_load_sum8(mc_in, i, acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i >= hi) break;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[u][q] *= scale;
+      round8(mc_in, acc[u]);
+      mc_store8(mc_out, i, acc[u]);
+      apply8(ch, i, acc[u], hp.lr, hp.mu, hp.wd, hp.nesterov, hp.gscale);
+    }
   }
 }
 
@@ -250,12 +332,15 @@ __device__ void participant_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   }
   uint64_t lo, hi;
   share_of(ch->count, plan.part_count, plan.part_index, &lo, &hi);
-  reduce_range<ST, true>(ch, lo, hi, tid, nth);
-  __threadfence_system();
+  const bool over_switch = plan.two_shot == 2;
+  if (over_switch) mc_reduce_range<ST>(ch, plan.src_parity[0], lo, hi, tid, nth);
+  else reduce_range<ST, true>(ch, lo, hi, tid, nth);
+  __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(&ch->bar_mid, 1u) == nblk - 1) {   // this rank's share is complete: peers may pull it
       ch->bar_mid = 0;
+      ch->t_phase[4] = DevEnv::now_ns();
       __threadfence_system();
       gather_signal(ch);
     }
@@ -275,13 +360,15 @@ __device__ void participant_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
       continue;
     }
     share_of(ch->count, n_own, idx, &lo, &hi);
-    pull_share<ST>(ch, owners[idx], lo, hi, tid, nth);
+    // over the switch the owner has stored its share into this rank's own shard buffer
+    pull_share<ST>(ch, over_switch ? ch->cfg.rank : owners[idx], lo, hi, tid, nth);
   }
 }
 
 __device__ inline void data_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, int* s_flag) {
   const uint64_t tid = (uint64_t)blk * blockDim.x + threadIdx.x, nth = (uint64_t)nblk * blockDim.x;
   const int role = ch->plan.role;
+  if (blk == 0 && threadIdx.x == 0) ch->t_phase[3] = DevEnv::now_ns();
   if (role == ROLE_PARTICIPANT) {
     if (ch->slot_bf16) participant_phase<__nv_bfloat16>(ch, blk, nblk, s_flag);
     else participant_phase<float>(ch, blk, nblk, s_flag);
@@ -290,15 +377,16 @@ __device__ inline void data_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   } else {
     data_zero_out(ch, tid, nth);
   }
-  __threadfence_system();
+  __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(&ch->bar_end, 1u) == nblk - 1) {
       ch->bar_end = 0;
-      __threadfence_system();
+      // finish_step releases at system scope (an acq_rel atomic for a participant, a fence for a drain)
       if (role == ROLE_DRAIN && ch->plan.drain_src < 0)
         atomicOr(&ch->view.ctl[ch->cfg.rank]->status, (uint32_t)ST_DESC_LAPPED);
       finish_step<DevEnv>(ch->view, ch->cfg, &ch->plan);
+      ch->t_phase[5] = DevEnv::now_ns();
     }
   }
 }
@@ -310,8 +398,27 @@ __device__ inline void pack_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   const uint64_t tid = (uint64_t)blk * blockDim.x + threadIdx.x, nthreads = (uint64_t)nblk * blockDim.x;
   ChannelCtl* me = ch->view.ctl[ch->cfg.rank];
   const uint64_t k = me->local_step + 1;
-  if (threadIdx.x == 0)
-    *s_flag = wait_slot_free<DevEnv>(ch->view, ch->cfg, ch->pol, k) ? slot_fate<DevEnv>(me, ch->pol, k) : -1;
+  if (threadIdx.x == 0) {
+    // One block asks (a sequentially consistent fence and a load from the home rank: costly when
+    // hundreds of blocks do it at once); the others read its answer from local memory.  The asking
+    // block is the first to get here, so it is running and waits for no other block.
+    int fate;
+    if (atomicAdd(&ch->pack_ticket, 1u) == 0) {
+      ch->t_phase[0] = DevEnv::now_ns();
+      fate = wait_slot_free<DevEnv>(ch->view, ch->cfg, ch->pol, k) ? slot_fate<DevEnv>(me, ch->pol, k) : -1;
+      __threadfence();
+      *reinterpret_cast<volatile uint64_t*>(&ch->pack_word) = (k << 8) | (uint64_t)(fate + 2);
+    } else {
+      const uint64_t t0 = DevEnv::now_ns();
+      uint64_t w;
+      while (((w = *reinterpret_cast<volatile uint64_t*>(&ch->pack_word)) >> 8) != k) {
+        if (DevEnv::now_ns() - t0 > 2 * ch->cfg.timeout_ns) { w = (k << 8) | 1u; break; }
+        __nanosleep(64);
+      }
+      fate = (int)(w & 0xff) - 2;
+    }
+    *s_flag = fate;
+  }
   __syncthreads();
   const int fate = *s_flag;
   __syncthreads();
@@ -319,21 +426,39 @@ __device__ inline void pack_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   const bool fold = fate == SLOT_FOLD;
   void* dst = ch->slot[ch->cfg.rank][k % kSlotDepth];
   const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (uint64_t i = tid * 8; i < ch->count; i += nthreads * 8) {
-    float v[8], u[8];
-    if (ch->grad_in_bf16) load8(reinterpret_cast<const __nv_bfloat16*>(ch->grad_in), i, v);
-    else load8(reinterpret_cast<const float*>(ch->grad_in), i, v);
-    if (fold) {
-      if (ch->slot_bf16) load8(reinterpret_cast<const __nv_bfloat16*>(dst), i, u);
-      else load8(reinterpret_cast<const float*>(dst), i, u);
+  constexpr int kUnroll = 4;     // independent 16-byte loads in flight per thread
+  const uint64_t stride = nthreads * 8;
+  for (uint64_t base = tid * 8; base < ch->count; base += stride * kUnroll) {
+    float v[kUnroll][8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] += u[q];
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i >= ch->count) break;
+      if (ch->grad_in_bf16) load8(reinterpret_cast<const __nv_bfloat16*>(ch->grad_in), i, v[u]);
+      else load8(reinterpret_cast<const float*>(ch->grad_in), i, v[u]);
     }
-    if (ch->slot_bf16) store8(reinterpret_cast<__nv_bfloat16*>(dst), i, v);
-    else store8(reinterpret_cast<float*>(dst), i, v);
-    if (ch->clear_grad) {
-      if (ch->grad_in_bf16) store8(reinterpret_cast<__nv_bfloat16*>(ch->grad_in), i, z);
-      else store8(reinterpret_cast<float*>(ch->grad_in), i, z);
+    if (fold) {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t i = base + u * stride;
+        if (i >= ch->count) break;
+        float w[8];
+        if (ch->slot_bf16) load8(reinterpret_cast<const __nv_bfloat16*>(dst), i, w);
+        else load8(reinterpret_cast<const float*>(dst), i, w);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[u][q] += w[q];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i >= ch->count) break;
+      if (ch->slot_bf16) store8(reinterpret_cast<__nv_bfloat16*>(dst), i, v[u]);
+      else store8(reinterpret_cast<float*>(dst), i, v[u]);
+      if (ch->clear_grad) {
+        if (ch->grad_in_bf16) store8(reinterpret_cast<__nv_bfloat16*>(ch->grad_in), i, z);
+        else store8(reinterpret_cast<float*>(ch->grad_in), i, z);
+      }
     }
   }
 }
@@ -345,6 +470,14 @@ __device__ inline void decide_two_shot(DevChannel* ch) {
   const Plan& p = ch->plan;
   ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= 2 && p.n_src >= 3 &&
                        ch->count >= ch->two_shot_min && ch->red[ch->cfg.rank] != nullptr) ? 1 : 0;
+  // Over the switch: everybody takes part with this round's own gradient (one slot parity, nothing stale),
+  // which also means that nobody is absent and the running sums stay untouched.
+  if (p.role == ROLE_PARTICIPANT && ch->mc_red != nullptr && p.part_count == ch->cfg.world &&
+      p.n_src == ch->cfg.world && p.part_count >= 2 && ch->count >= ch->mc_min) {
+    bool same = true;
+    for (int s = 1; s < p.n_src; ++s) same = same && (p.src_parity[s] == p.src_parity[0]);
+    if (same && ch->mc_slot[p.src_parity[0]] != nullptr) ch->plan.two_shot = 2;
+  }
   ch->applied = (p.role == ROLE_PARTICIPANT || p.role == ROLE_DRAIN) ? 1 : 0;
 }
 

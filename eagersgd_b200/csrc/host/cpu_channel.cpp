@@ -211,7 +211,8 @@ uint32_t esgd_cpu_flush(void** bases, const esgd_cpu_params* p, void* out, esgd_
 }
 
 // stats[0..9]: local_step, participated, absent, activated, sync, dropped,
-// contrib_sum, wait_ns, last_round, last_contrib; [10] status; [11] latest_round; [12] folded
+// contrib_sum, wait_ns, last_round, last_contrib; [10] status; [11] latest_round; [12] folded;
+// [16..21] clock of the newest control step (ChannelCtl::ctl_t)
 void esgd_ctl_stats(const void* base, uint64_t* stats) {
   const ChannelCtl* c = (const ChannelCtl*)base;
   stats[0] = c->local_step; stats[1] = c->stat_rounds_participated; stats[2] = c->stat_rounds_absent;
@@ -219,6 +220,7 @@ void esgd_ctl_stats(const void* base, uint64_t* stats) {
   stats[6] = c->stat_contrib_sum; stats[7] = c->stat_wait_ns; stats[8] = c->stat_last_round;
   stats[9] = c->stat_last_contrib; stats[10] = c->status; stats[11] = c->latest_round;
   stats[12] = c->stat_folded_grads;
+  for (int q = 0; q < 6; ++q) stats[16 + q] = c->ctl_t[q];
 }
 
 // Copy the trace ring, oldest first, as rows of 10 uint64: step, round, t_ns, wait_ns, role, activator,

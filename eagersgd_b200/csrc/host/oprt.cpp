@@ -23,16 +23,32 @@
 
 namespace {
 
+constexpr double kDefaultWaitSeconds = 600.0;   // what "no timeout" means: ten minutes, then RT_TIMEOUT
+
 size_t dtype_size(int dt) { return (dt == RT_INT32 || dt == RT_FLOAT) ? 4 : 8; }
 
 enum OpType { T_NOP, T_CALLBACK, T_COMP, T_SEND, T_RECV };
 
 struct Buffer {
+  bool alive = true;
   void* ptr = nullptr;
   std::vector<uint8_t> own;
   int64_t count = 0;
   int dtype = RT_FLOAT;
   void* data() { return ptr ? ptr : (void*)own.data(); }
+};
+
+// One happens-before edge.  Plain edges (rt_op_hb) fire whenever the parent completes.  Versioned edges
+// (rt_op_hb_fallback without RT_DEP_IGNORE_VERSION) follow the reference's version rules
+// (fflib2 src/ffop.c:299-401): the parent's n-th completion satisfies the dependent's n-th run only.
+struct Edge {
+  rt_op child = RT_NONE;
+  rt_op fallback = RT_NONE;   // gets the completion when the dependent has already run for this version
+  int options = 0;
+  int count = 0;              // constrained edge: completions it may still pass on
+  int futures = 0;            // completions that arrived ahead of the dependent's version
+  rt_op constrains_op = RT_NONE;   // edge (op, index) whose `count` this edge feeds when it passes one on
+  int constrains_idx = -1;
 };
 
 struct Op {
@@ -42,8 +58,11 @@ struct Op {
   int oper = RT_SUM, peer = -1, tag = 0;
   rt_callback_fn cb = nullptr;
   void* cb_arg = nullptr;
-  std::vector<rt_op> children;
+  std::vector<Edge> edges;    // happens-before edges to dependents, in creation order
+  std::vector<rt_op> parents; // who points here (needed to unlink on free)
   int num_parents = 0;
+  int64_t posted = 0;         // posts so far, explicit or by a parent (the "posted version")
+  bool alive = true;
   int dep_left = 0;           // parents still to complete in this round (AND)
   size_t first_rr = 0;        // round-robin cursor for RT_DEP_FIRST
   int64_t executed = 0;       // times started
@@ -57,9 +76,17 @@ struct Message {
 };
 
 struct Schedule {
+  bool alive = true;
   std::vector<rt_op> ops;
+  std::vector<rt_buf> owned_bufs;   // temporaries a collective created for itself
+  std::vector<rt_sched> parts;      // schedules a composite one is made of (deleted with it)
   rt_op begin = RT_NONE, end = RT_NONE;
   bool finalized = false;
+  // overridable behaviour and a state slot (ffschedule_set_*_fun / ffschedule_{set,get}_state)
+  rt_sched_fn start_fn = nullptr, post_fn = nullptr, test_fn = nullptr, delete_fn = nullptr;
+  rt_sched_wait_fn wait_fn = nullptr;
+  rt_sched_print_fn print_fn = nullptr;
+  void* state = nullptr;
 };
 
 }  // namespace
@@ -83,6 +110,9 @@ struct rt_rank {
   std::deque<rt_op> posted;
   std::vector<rt_op> pending_recvs;
   std::vector<rt_operator_fn> custom_ops;
+  std::vector<rt_op> free_ops;         // recycled handles
+  std::vector<rt_buf> free_bufs;
+  std::vector<rt_sched> free_scheds;
   std::thread progress;
   std::atomic<bool> stop{false};
 };
@@ -126,37 +156,87 @@ void run_comp(rt_rank* c, Op& op) {
 
 void trigger(rt_rank* c, rt_op id);
 
+void post_locked(rt_rank* c, rt_op id) {
+  c->ops[id]->posted++;
+  c->posted.push_back(id);
+}
+
+// One completion of `op` (its `version`-th) travels along edge `e`.  Called with c->mu held.
+void satisfy(rt_rank* c, Op& op, Edge& e, int64_t version) {
+  rt_op target = e.child;
+  if (target == RT_NONE || !c->ops[target] || !c->ops[target]->alive) return;
+  const bool versioned = !(e.options & RT_DEP_IGNORE_VERSION);
+  int64_t tv = c->ops[target]->posted;
+  if (versioned && version <= tv) {            // the dependent already ran for this version
+    if (e.fallback == RT_NONE || !c->ops[e.fallback] || !c->ops[e.fallback]->alive) return;
+    target = e.fallback;
+    tv = c->ops[target]->posted;
+    if (version <= tv) return;
+  }
+  if (versioned && version > tv + 1) {         // ahead of the dependent: remembered until it catches up
+    e.futures++;
+    return;
+  }
+  if (e.options & RT_DEP_NO_AUTOPOST) return;
+  if (e.options & RT_DEP_CONSTRAINED) {
+    if (e.count == 0) return;
+    e.count--;
+  }
+  if (e.constrains_op != RT_NONE && c->ops[e.constrains_op] && e.constrains_idx >= 0)
+    c->ops[e.constrains_op]->edges[e.constrains_idx].count++;
+  (void)op;
+  trigger(c, target);
+}
+
 // Called with c->mu held.
 void complete(rt_rank* c, rt_op id) {
   Op& op = *c->ops[id];
-  op.completed.fetch_add(1);
+  const int64_t version = op.completed.fetch_add(1) + 1;
   c->cv.notify_all();
-  if (op.children.empty()) return;
+  if (op.edges.empty()) return;
   if (op.options & RT_DEP_FIRST) {           // satisfy exactly one dependent, in turn
-    rt_op child = op.children[op.first_rr % op.children.size()];
+    Edge& e = op.edges[op.first_rr % op.edges.size()];
     op.first_rr++;
-    trigger(c, child);
+    satisfy(c, op, e, version);
   } else {
-    for (rt_op child : op.children) trigger(c, child);
+    for (size_t i = 0; i < op.edges.size(); ++i) satisfy(c, op, op.edges[i], version);
   }
 }
 
 // A parent of `id` has completed.  Called with c->mu held.
 void trigger(rt_rank* c, rt_op id) {
   Op& op = *c->ops[id];
-  if ((op.options & RT_NON_PERSISTENT) && op.executed > 0) return;
+  if ((op.options & RT_NON_PERSISTENT) && op.posted > 0) return;
   if (op.options & RT_DEP_OR) {
-    c->posted.push_back(id);
+    post_locked(c, id);
   } else {
     if (op.dep_left <= 0) op.dep_left = op.num_parents;
-    if (--op.dep_left == 0) c->posted.push_back(id);
+    if (--op.dep_left <= 0) {      // an op that is only ever a fall-back has no parent edge of its own
+      op.dep_left = 0;
+      post_locked(c, id);
+    }
+  }
+}
+
+// Completions that arrived before the op reached their version count now.  Called with c->mu held.
+void consume_futures(rt_rank* c, rt_op id) {
+  Op& op = *c->ops[id];
+  for (rt_op pid : op.parents) {
+    if (!c->ops[pid]) continue;
+    for (Edge& e : c->ops[pid]->edges)
+      if (e.child == id && e.futures > 0) {
+        e.futures--;
+        trigger(c, id);
+      }
   }
 }
 
 // Start one operation.  Called with c->mu held; may release it around user callbacks.
 void execute(rt_rank* c, rt_op id, std::unique_lock<std::mutex>& lk) {
+  if (!c->ops[id] || !c->ops[id]->alive) return;
   Op& op = *c->ops[id];
   op.executed++;
+  consume_futures(c, id);
   switch (op.type) {
     case T_NOP: complete(c, id); break;
     case T_CALLBACK: {
@@ -191,6 +271,7 @@ bool poll_recvs(rt_rank* c) {
   bool any = false;
   for (size_t i = 0; i < c->pending_recvs.size();) {
     rt_op id = c->pending_recvs[i];
+    if (!c->ops[id] || !c->ops[id]->alive) { c->pending_recvs.erase(c->pending_recvs.begin() + i); continue; }
     Op& op = *c->ops[id];
     Message m;
     bool got = false;
@@ -232,11 +313,42 @@ void progress_loop(rt_rank* c) {
 
 rt_op new_op(rt_rank* c, OpType t, int options) {
   std::lock_guard<std::mutex> g(c->mu);
-  c->ops.emplace_back(new Op());
-  Op& op = *c->ops.back();
-  op.type = t;
-  op.options = options;
-  return (rt_op)c->ops.size() - 1;
+  rt_op id;
+  if (!c->free_ops.empty()) {          // a freed handle is used again
+    id = c->free_ops.back();
+    c->free_ops.pop_back();
+    c->ops[id].reset(new Op());
+  } else {
+    c->ops.emplace_back(new Op());
+    id = (rt_op)c->ops.size() - 1;
+  }
+  c->ops[id]->type = t;
+  c->ops[id]->options = options;
+  return id;
+}
+
+// Unlink and release one operation.  Called with c->mu held.
+void free_op_locked(rt_rank* c, rt_op id) {
+  if (id < 0 || id >= (rt_op)c->ops.size() || !c->ops[id]) return;
+  Op& op = *c->ops[id];
+  for (Edge& e : op.edges)
+    if (e.child != RT_NONE && e.child != id && c->ops[e.child]) {
+      Op& ch = *c->ops[e.child];
+      for (size_t i = 0; i < ch.parents.size(); ++i)
+        if (ch.parents[i] == id) { ch.parents.erase(ch.parents.begin() + i); ch.num_parents--; break; }
+    }
+  for (rt_op pid : op.parents)
+    if (pid != id && c->ops[pid])
+      for (Edge& e : c->ops[pid]->edges) {
+        if (e.child == id) e.child = RT_NONE;
+        if (e.fallback == id) e.fallback = RT_NONE;
+      }
+  for (size_t i = 0; i < c->posted.size();)
+    if (c->posted[i] == id) c->posted.erase(c->posted.begin() + i); else ++i;
+  for (size_t i = 0; i < c->pending_recvs.size();)
+    if (c->pending_recvs[i] == id) c->pending_recvs.erase(c->pending_recvs.begin() + i); else ++i;
+  c->ops[id].reset();
+  c->free_ops.push_back(id);
 }
 
 }  // namespace
@@ -268,11 +380,29 @@ int rt_rank_size(rt_rank* c) { return c->world->n; }
 
 rt_buf rt_buffer_create(rt_rank* c, void* user_ptr, int64_t count, int dtype) {
   std::lock_guard<std::mutex> g(c->mu);
-  c->bufs.emplace_back();
-  Buffer& b = c->bufs.back();
+  rt_buf id;
+  if (!c->free_bufs.empty()) {
+    id = c->free_bufs.back();
+    c->free_bufs.pop_back();
+    c->bufs[id] = Buffer();
+  } else {
+    c->bufs.emplace_back();
+    id = (rt_buf)c->bufs.size() - 1;
+  }
+  Buffer& b = c->bufs[id];
   b.ptr = user_ptr; b.count = count; b.dtype = dtype;
   if (!user_ptr) b.own.assign((size_t)count * dtype_size(dtype), 0);
-  return (rt_buf)c->bufs.size() - 1;
+  return id;
+}
+
+int rt_buffer_delete(rt_rank* c, rt_buf id) {
+  std::lock_guard<std::mutex> g(c->mu);
+  if (id < 0 || id >= (rt_buf)c->bufs.size() || !c->bufs[id].alive) return RT_ERROR;
+  c->bufs[id] = Buffer();
+  c->bufs[id].alive = false;
+  std::vector<uint8_t>().swap(c->bufs[id].own);
+  c->free_bufs.push_back(id);
+  return RT_SUCCESS;
 }
 
 int rt_buffer_resize(rt_rank* c, rt_buf id, void* user_ptr, int64_t count) {
@@ -326,16 +456,68 @@ int rt_operator_create(rt_rank* c, rt_operator_fn fn) {
   return RT_CUSTOM0 + (int)c->custom_ops.size() - 1;
 }
 
-int rt_op_hb(rt_rank* c, rt_op first, rt_op second) {
+int rt_op_hb_fallback(rt_rank* c, rt_op first, rt_op second, rt_op fallback, int options, rt_dep* dep) {
   std::lock_guard<std::mutex> g(c->mu);
-  c->ops[first]->children.push_back(second);
+  if (first < 0 || second < 0 || !c->ops[first] || !c->ops[second]) return RT_ERROR;
+  Edge e;
+  e.child = second;
+  e.fallback = fallback;
+  e.options = options;
+  c->ops[first]->edges.push_back(e);
+  c->ops[second]->parents.push_back(first);
   c->ops[second]->num_parents++;
+  if (fallback != RT_NONE && c->ops[fallback]) c->ops[fallback]->parents.push_back(first);
+  if (dep) *dep = (first << 20) | (rt_dep)(c->ops[first]->edges.size() - 1);
+  return RT_SUCCESS;
+}
+
+int rt_op_hb(rt_rank* c, rt_op first, rt_op second) {
+  return rt_op_hb_fallback(c, first, second, RT_NONE, RT_DEP_IGNORE_VERSION, nullptr);
+}
+
+// The constrained edge passes a completion on only after the constraining edge has passed one
+// (ffdep_set_parent, fflib2 src/ffop.c:208-216).
+int rt_dep_set_parent(rt_rank* c, rt_dep constrained, rt_dep constraining) {
+  std::lock_guard<std::mutex> g(c->mu);
+  const rt_op o1 = constrained >> 20, o2 = constraining >> 20;
+  const int i1 = (int)(constrained & 0xfffff), i2 = (int)(constraining & 0xfffff);
+  if (!c->ops[o1] || !c->ops[o2] || i1 >= (int)c->ops[o1]->edges.size() || i2 >= (int)c->ops[o2]->edges.size())
+    return RT_ERROR;
+  c->ops[o1]->edges[i1].options |= RT_DEP_CONSTRAINED;
+  c->ops[o2]->edges[i2].constrains_op = o1;
+  c->ops[o2]->edges[i2].constrains_idx = i1;
   return RT_SUCCESS;
 }
 
 int rt_op_post(rt_rank* c, rt_op op) {
-  { std::lock_guard<std::mutex> g(c->mu); c->posted.push_back(op); }
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (op < 0 || op >= (rt_op)c->ops.size() || !c->ops[op]) return RT_ERROR;
+    post_locked(c, op);
+  }
   c->work_cv.notify_all();
+  return RT_SUCCESS;
+}
+
+int rt_op_free(rt_rank* c, rt_op op) {
+  std::lock_guard<std::mutex> g(c->mu);
+  if (op < 0 || op >= (rt_op)c->ops.size() || !c->ops[op]) return RT_ERROR;
+  free_op_locked(c, op);
+  return RT_SUCCESS;
+}
+
+// Withdraw an operation that has been posted but has not completed: it leaves the run queue, a receive
+// stops listening, and its dependency count starts afresh (ffop_cancel, fflib2 src/ffop.c:403-408).
+int rt_op_cancel(rt_rank* c, rt_op id) {
+  std::lock_guard<std::mutex> g(c->mu);
+  if (id < 0 || id >= (rt_op)c->ops.size() || !c->ops[id]) return RT_ERROR;
+  Op& op = *c->ops[id];
+  for (size_t i = 0; i < c->posted.size();)
+    if (c->posted[i] == id) c->posted.erase(c->posted.begin() + i); else ++i;
+  for (size_t i = 0; i < c->pending_recvs.size();)
+    if (c->pending_recvs[i] == id) c->pending_recvs.erase(c->pending_recvs.begin() + i); else ++i;
+  op.in_flight = false;
+  op.dep_left = op.num_parents;
   return RT_SUCCESS;
 }
 
@@ -344,8 +526,8 @@ int rt_op_wait(rt_rank* c, rt_op id, double timeout_s) {
   Op& op = *c->ops[id];
   const int64_t want = op.waited.load() + 1;
   auto pred = [&] { return op.completed.load() >= want; };
-  if (timeout_s <= 0) c->cv.wait(lk, pred);
-  else if (!c->cv.wait_for(lk, std::chrono::duration<double>(timeout_s), pred)) return RT_TIMEOUT;
+  if (timeout_s <= 0) timeout_s = kDefaultWaitSeconds;    // no wait is unbounded
+  if (!c->cv.wait_for(lk, std::chrono::duration<double>(timeout_s), pred)) return RT_TIMEOUT;
   op.waited.store(want);
   return RT_SUCCESS;
 }
@@ -362,10 +544,92 @@ int64_t rt_op_completions(rt_rank* c, rt_op id) { std::lock_guard<std::mutex> g(
 rt_sched rt_schedule_create(rt_rank* c) {
   rt_op b = rt_op_nop(c, 0), e = rt_op_nop(c, 0);
   std::lock_guard<std::mutex> g(c->mu);
-  c->scheds.emplace_back();
-  c->scheds.back().begin = b;
-  c->scheds.back().end = e;
-  return (rt_sched)c->scheds.size() - 1;
+  rt_sched id;
+  if (!c->free_scheds.empty()) {
+    id = c->free_scheds.back();
+    c->free_scheds.pop_back();
+    c->scheds[id] = Schedule();
+  } else {
+    c->scheds.emplace_back();
+    id = (rt_sched)c->scheds.size() - 1;
+  }
+  c->scheds[id].begin = b;
+  c->scheds[id].end = e;
+  return id;
+}
+
+// Release a schedule with everything it owns: its operations, begin / end no-ops, the temporaries a
+// collective made for itself and the schedules a composite one is built from (ffschedule_delete).
+int rt_schedule_delete(rt_rank* c, rt_sched s) {
+  rt_sched_fn custom = nullptr;
+  std::vector<rt_sched> parts;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (s < 0 || s >= (rt_sched)c->scheds.size() || !c->scheds[s].alive) return RT_ERROR;
+    custom = c->scheds[s].delete_fn;
+    c->scheds[s].delete_fn = nullptr;      // the override may call back into the default
+    parts = c->scheds[s].parts;
+  }
+  if (custom) return custom(c, s);
+  for (rt_sched p : parts) rt_schedule_delete(c, p);
+  std::lock_guard<std::mutex> g(c->mu);
+  Schedule& sc = c->scheds[s];
+  for (rt_op id : sc.ops) free_op_locked(c, id);
+  free_op_locked(c, sc.begin);
+  free_op_locked(c, sc.end);
+  for (rt_buf b : sc.owned_bufs)
+    if (b >= 0 && b < (rt_buf)c->bufs.size() && c->bufs[b].alive) {
+      c->bufs[b] = Buffer();
+      c->bufs[b].alive = false;
+      c->free_bufs.push_back(b);
+    }
+  sc = Schedule();
+  sc.alive = false;
+  c->free_scheds.push_back(s);
+  return RT_SUCCESS;
+}
+
+int rt_schedule_add_part(rt_rank* c, rt_sched s, rt_sched part) {
+  std::lock_guard<std::mutex> g(c->mu);
+  c->scheds[s].parts.push_back(part);
+  return RT_SUCCESS;
+}
+
+int rt_schedule_own_buffer(rt_rank* c, rt_sched s, rt_buf b) {
+  std::lock_guard<std::mutex> g(c->mu);
+  c->scheds[s].owned_bufs.push_back(b);
+  return RT_SUCCESS;
+}
+
+int rt_schedule_set_state(rt_rank* c, rt_sched s, void* state) {
+  std::lock_guard<std::mutex> g(c->mu);
+  c->scheds[s].state = state;
+  return RT_SUCCESS;
+}
+void* rt_schedule_get_state(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return c->scheds[s].state; }
+
+int rt_schedule_set_start_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].start_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_post_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].post_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_test_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].test_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_delete_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].delete_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_wait_fun(rt_rank* c, rt_sched s, rt_sched_wait_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].wait_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_print_fun(rt_rank* c, rt_sched s, rt_sched_print_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].print_fn = f; return RT_SUCCESS; }
+
+// The default behaviours, callable from an override (ffschedule_default_*).
+int rt_schedule_default_post(rt_rank* c, rt_sched s) {
+  rt_schedule_finalize(c, s);
+  return rt_op_post(c, rt_schedule_begin_op(c, s));
+}
+int rt_schedule_default_wait(rt_rank* c, rt_sched s, double timeout_s) { return rt_op_wait(c, rt_schedule_end_op(c, s), timeout_s); }
+int rt_schedule_default_test(rt_rank* c, rt_sched s) { return rt_op_test(c, rt_schedule_end_op(c, s)); }
+
+// Arm a schedule once before its first post (a composite schedule posts its listening side here:
+// ffsolo_allreduce.c:97-101).  The default does nothing.
+int rt_schedule_start(rt_rank* c, rt_sched s) {
+  rt_sched_fn f;
+  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].start_fn; }
+  rt_schedule_finalize(c, s);
+  return f ? f(c, s) : RT_SUCCESS;
 }
 
 int rt_schedule_add_op(rt_rank* c, rt_sched s, rt_op op) {
@@ -387,7 +651,7 @@ int rt_schedule_finalize(rt_rank* c, rt_sched s) {
     b = sc.begin; e = sc.end;
     for (rt_op id : sc.ops) {
       if (c->ops[id]->num_parents == 0) roots.push_back(id);
-      if (c->ops[id]->children.empty()) leaves.push_back(id);
+      if (c->ops[id]->edges.empty()) leaves.push_back(id);
     }
   }
   for (rt_op id : roots) rt_op_hb(c, b, id);
@@ -400,14 +664,28 @@ rt_op rt_schedule_begin_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex>
 rt_op rt_schedule_end_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return c->scheds[s].end; }
 
 int rt_schedule_post(rt_rank* c, rt_sched s) {
-  rt_schedule_finalize(c, s);
-  return rt_op_post(c, rt_schedule_begin_op(c, s));
+  rt_sched_fn f;
+  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].post_fn; }
+  return f ? f(c, s) : rt_schedule_default_post(c, s);
 }
-int rt_schedule_wait(rt_rank* c, rt_sched s, double timeout_s) { return rt_op_wait(c, rt_schedule_end_op(c, s), timeout_s); }
-int rt_schedule_test(rt_rank* c, rt_sched s) { return rt_op_test(c, rt_schedule_end_op(c, s)); }
+int rt_schedule_wait(rt_rank* c, rt_sched s, double timeout_s) {
+  rt_sched_wait_fn f;
+  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].wait_fn; }
+  return f ? f(c, s, timeout_s) : rt_schedule_default_wait(c, s, timeout_s);
+}
+int rt_schedule_test(rt_rank* c, rt_sched s) {
+  rt_sched_fn f;
+  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].test_fn; }
+  return f ? f(c, s) : rt_schedule_default_test(c, s);
+}
 
 int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
   static const char* names[] = {"nop", "callback", "comp", "send", "recv"};
+  {
+    rt_sched_print_fn f;
+    { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].print_fn; }
+    if (f) return f(c, s, out, cap);
+  }
   std::lock_guard<std::mutex> g(c->mu);
   Schedule& sc = c->scheds[s];
   std::string dot = "digraph schedule_" + std::to_string(c->id) + "_" + std::to_string(s) + " {\n";
@@ -418,9 +696,12 @@ int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
     Op& op = *c->ops[id];
     dot += "  \"" + std::to_string(id) + "." + std::to_string(c->id) + "\" [label=\"" + names[op.type] +
            (id == sc.begin ? " begin" : id == sc.end ? " end" : "") + "\"];\n";
-    for (rt_op ch : op.children)
+    for (const Edge& ed : op.edges) {
+      const rt_op ch = ed.child;
+      if (ch == RT_NONE) continue;
       dot += "  \"" + std::to_string(id) + "." + std::to_string(c->id) + "\" -> \"" + std::to_string(ch) + "." +
              std::to_string(c->id) + "\";\n";
+    }
   }
   dot += "}\n";
   if ((int64_t)dot.size() + 1 > cap) return RT_ERROR;
@@ -451,12 +732,14 @@ rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper) {
   }
   if (me < extra) {
     rt_buf tmp = rt_buffer_create(c, nullptr, count, dtype);
+    rt_schedule_own_buffer(c, s, tmp);
     chain(rt_op_recv(c, tmp, me + p2, tag, 0));
     chain(rt_op_comp(c, tmp, rcv, rcv, oper, 0));
   }
   for (int mask = 1; mask < p2; mask <<= 1) {
     const int peer = me ^ mask;
     rt_buf tmp = rt_buffer_create(c, nullptr, count, dtype);
+    rt_schedule_own_buffer(c, s, tmp);
     rt_op sd = rt_op_send(c, rcv, peer, tag, 0);
     rt_op rv = rt_op_recv(c, tmp, peer, tag, 0);
     rt_op cp = rt_op_comp(c, tmp, rcv, rcv, oper, 0);
@@ -481,6 +764,7 @@ rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined) {
   const int P = c->world->n, me = c->id;
   rt_sched s = rt_schedule_create(c);
   rt_buf token = rt_buffer_create(c, nullptr, 1, RT_INT32);
+  rt_schedule_own_buffer(c, s, token);
   rt_op act = rt_op_nop(c, 0);
   rt_op join = rt_op_nop(c, RT_DEP_OR);
   rt_schedule_add_op(c, s, act);
@@ -492,7 +776,9 @@ rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined) {
     rt_op_hb(c, act, sd);
     rt_schedule_add_op(c, s, sd);
     // a persistent receive per peer: it re-arms itself after every token
-    rt_op rv = rt_op_recv(c, rt_buffer_create(c, nullptr, 1, RT_INT32), r, tag, RT_DEP_OR);
+    rt_buf rb = rt_buffer_create(c, nullptr, 1, RT_INT32);
+    rt_schedule_own_buffer(c, s, rb);
+    rt_op rv = rt_op_recv(c, rb, r, tag, RT_DEP_OR);
     rt_op_hb(c, rv, join);
     rt_op_hb(c, rv, rv);
     rt_schedule_add_op(c, s, rv);

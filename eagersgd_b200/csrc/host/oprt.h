@@ -34,6 +34,10 @@ enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUST
 #define RT_DEP_OR 0x1             /* run when any parent completes */
 #define RT_DEP_FIRST 0x2          /* on completion satisfy only ONE dependent, round-robin */
 #define RT_NON_PERSISTENT 0x4     /* runs at most once */
+/* options of one happens-before edge (rt_op_hb_fallback; ff.h:50-55) */
+#define RT_DEP_IGNORE_VERSION 0x10   /* every completion of the first op counts (what rt_op_hb uses) */
+#define RT_DEP_NO_AUTOPOST 0x20      /* the edge never posts the second op; it is posted by hand */
+#define RT_DEP_CONSTRAINED 0x40      /* passes a completion on only after its constraining edge has (rt_dep_set_parent) */
 #define RT_INPLACE ((int64_t)-2)
 #define RT_NONE ((int64_t)-1)
 
@@ -42,7 +46,11 @@ typedef struct rt_rank rt_rank;
 typedef int64_t rt_op;        /* handle within a rank */
 typedef int64_t rt_buf;
 typedef int64_t rt_sched;
+typedef int64_t rt_dep;       /* handle of one happens-before edge */
 typedef void (*rt_callback_fn)(rt_op op, void* arg);
+typedef int (*rt_sched_fn)(rt_rank* c, rt_sched s);
+typedef int (*rt_sched_wait_fn)(rt_rank* c, rt_sched s, double timeout_s);
+typedef int (*rt_sched_print_fn)(rt_rank* c, rt_sched s, char* out, int64_t cap);
 typedef void (*rt_operator_fn)(const void* a, const void* b, void* out, int64_t count, int dtype);
 
 rt_world* rt_world_create(int nranks);
@@ -56,6 +64,7 @@ rt_buf rt_buffer_create(rt_rank* c, void* user_ptr, int64_t count, int dtype); /
 int rt_buffer_resize(rt_rank* c, rt_buf b, void* user_ptr, int64_t count);
 int64_t rt_buffer_count(rt_rank* c, rt_buf b);
 void* rt_buffer_data(rt_rank* c, rt_buf b);
+int rt_buffer_delete(rt_rank* c, rt_buf b);
 
 /* operations */
 rt_op rt_op_nop(rt_rank* c, int options);
@@ -65,8 +74,16 @@ rt_op rt_op_send(rt_rank* c, rt_buf b, int peer, int tag, int options);
 rt_op rt_op_recv(rt_rank* c, rt_buf b, int peer, int tag, int options);
 int rt_operator_create(rt_rank* c, rt_operator_fn fn);   /* returns an operator id >= RT_CUSTOM0 */
 int rt_op_hb(rt_rank* c, rt_op first, rt_op second);     /* first happens before second */
+/* Versioned edge: the n-th completion of `first` satisfies the n-th run of `second` only.  A completion that
+ * finds `second` already past that version goes to `fallback` (RT_NONE: it is dropped); one that is ahead of
+ * `second` is remembered and counts when `second` gets there (ffop_hb_fallback, ffop.c:299-401). */
+int rt_op_hb_fallback(rt_rank* c, rt_op first, rt_op second, rt_op fallback, int options, rt_dep* dep);
+int rt_dep_set_parent(rt_rank* c, rt_dep constrained, rt_dep constraining);
 int rt_op_post(rt_rank* c, rt_op op);
-int rt_op_wait(rt_rank* c, rt_op op, double timeout_s);  /* waits for the next completion not yet waited for */
+int rt_op_cancel(rt_rank* c, rt_op op);                  /* withdraw a posted, not yet completed operation */
+int rt_op_free(rt_rank* c, rt_op op);                    /* unlink and release; the handle may be reused */
+/* waits for the next completion not yet waited for; timeout_s <= 0 means the default bound of ten minutes */
+int rt_op_wait(rt_rank* c, rt_op op, double timeout_s);
 int rt_op_test(rt_rank* c, rt_op op);
 int64_t rt_op_completions(rt_rank* c, rt_op op);
 
@@ -76,9 +93,25 @@ int rt_schedule_add_op(rt_rank* c, rt_sched s, rt_op op);
 int rt_schedule_finalize(rt_rank* c, rt_sched s);        /* link roots to begin and leaves to end */
 rt_op rt_schedule_begin_op(rt_rank* c, rt_sched s);
 rt_op rt_schedule_end_op(rt_rank* c, rt_sched s);
+int rt_schedule_start(rt_rank* c, rt_sched s);           /* arm once before the first post (default: nothing) */
 int rt_schedule_post(rt_rank* c, rt_sched s);
 int rt_schedule_wait(rt_rank* c, rt_sched s, double timeout_s);
 int rt_schedule_test(rt_rank* c, rt_sched s);
+int rt_schedule_delete(rt_rank* c, rt_sched s);          /* releases its operations, temporaries and parts */
+int rt_schedule_add_part(rt_rank* c, rt_sched s, rt_sched part);   /* composite schedules: deleted together */
+int rt_schedule_own_buffer(rt_rank* c, rt_sched s, rt_buf b);      /* buffer released with the schedule */
+/* overridable behaviour and a state slot (ffschedule_set_*_fun, ffschedule_{set,get}_state: ff.h:144-159) */
+int rt_schedule_set_start_fun(rt_rank* c, rt_sched s, rt_sched_fn f);
+int rt_schedule_set_post_fun(rt_rank* c, rt_sched s, rt_sched_fn f);
+int rt_schedule_set_wait_fun(rt_rank* c, rt_sched s, rt_sched_wait_fn f);
+int rt_schedule_set_test_fun(rt_rank* c, rt_sched s, rt_sched_fn f);
+int rt_schedule_set_delete_fun(rt_rank* c, rt_sched s, rt_sched_fn f);
+int rt_schedule_set_print_fun(rt_rank* c, rt_sched s, rt_sched_print_fn f);
+int rt_schedule_default_post(rt_rank* c, rt_sched s);
+int rt_schedule_default_wait(rt_rank* c, rt_sched s, double timeout_s);
+int rt_schedule_default_test(rt_rank* c, rt_sched s);
+int rt_schedule_set_state(rt_rank* c, rt_sched s, void* state);
+void* rt_schedule_get_state(rt_rank* c, rt_sched s);
 int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap);   /* graphviz DOT */
 
 /* collectives */

@@ -95,8 +95,8 @@ struct TraceEntry {
 struct alignas(128) ChannelCtl {
   uint64_t pub_epoch[kMaxRanks];          // [j] pushed by rank j: its latest published epoch
   alignas(128) uint64_t owner;            // election word; only the home rank's copy is used
-  alignas(128) uint64_t snap_round;       // home rank's copy: newest round whose activator is past its waits and
-                                          // is taking (or has taken) the snapshot of who contributes what
+  alignas(128) uint64_t snap_round;       // newest round whose activator is past its waits and is taking (or has
+                                          // taken) the snapshot of who contributes what; written into every rank
   alignas(128) uint64_t latest_round;     // newest round whose descriptor is visible here
   alignas(128) uint64_t round_done;       // newest round whose data phase has completed
   alignas(128) uint32_t done_count[kDescRing];  // finishers; only the activator's copy is used
@@ -122,6 +122,8 @@ struct alignas(128) ChannelCtl {
   uint64_t stat_last_round;               // round applied at the last step
   uint64_t stat_last_contrib;
   uint64_t stat_folded_grads;             // own unconsumed gradients folded into a later publish
+  uint64_t ctl_t[6];                      // clock of the newest control step: start, published, election decided,
+                                          // activation waits over, descriptor out (activator only), round visible
   TraceEntry trace[kTraceRing];           // ring indexed by local_step % kTraceRing
 };
 

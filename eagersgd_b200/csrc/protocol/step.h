@@ -1,7 +1,9 @@
 // Control step of the partial allreduce, templated on the execution environment.
 //
 // Env must provide (all at system scope, i.e. visible to every rank):
-//   ld_acq64 / st_rel64 / ld_acq32 / st_rel32, cas64 / cas32 (return the old
+//   ld_acq64 / st_rel64 / ld_acq32 / st_rel32, st_rlx64 / st_rlx32 (relaxed stores:
+//   a group of them behind ONE fence() is as good as a group of release stores and,
+//   over NVLink, costs one round trip instead of one per store), cas64 / cas32 (return the old
 //   value), add32 (returns the old value), fence(), fence_sc() (sequentially
 //   consistent: orders an earlier store before a later load), now_ns(), pause().
 //
@@ -60,7 +62,7 @@ ESGD_T int32_t slot_fate(ChannelCtl* me, const StepPolicy& pol, uint64_t k) {
 }
 
 // Before epoch k overwrites publish slot k % 2 (last used for epoch k-2) no round may still read it.
-// An activator announces its round in the home rank's `snap_round`, then (after a sequentially
+// An activator announces its round in every rank's `snap_round`, then (after a sequentially
 // consistent fence) reads every rank's published epoch.  This rank published k-1 a step ago and
 // fences before it reads `snap_round`: a round it does not see there yet will find epoch >= k-1 and
 // never touch the slot of k-2; a round it does see may have picked k-2 up and must complete first.
@@ -72,7 +74,7 @@ ESGD_T bool wait_slot_free(const ChannelView& v, const StepConfig& cfg, const St
   ChannelCtl* me = v.ctl[cfg.rank];
   const uint64_t t0 = E::now_ns();
   E::fence_sc();
-  const uint64_t target = E::ld_acq64(&v.ctl[cfg.home]->snap_round);
+  const uint64_t target = E::ld_acq64(&me->snap_round);
   for (;;) {
     if (E::ld_acq64(&me->round_done) >= target) return true;
     if (E::now_ns() - t0 > cfg.timeout_ns) {
@@ -135,14 +137,15 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
     }
     if (pol.adaptive_grace) {   // fast attack, slow decay
       const uint64_t smooth = (7 * ema + last_arrival) / 8;
-      E::st_rel64(&hm->grace_ema_ns, last_arrival > smooth ? last_arrival : smooth);
+      E::st_rlx64(&hm->grace_ema_ns, last_arrival > smooth ? last_arrival : smooth);
     }
   }
 
   // One consistent snapshot of who has what; every reducer honours it.  Announced first, so that a
   // rank about to reuse a publish slot knows that this round may be reading it (wait_slot_free).
-  E::st_rel64(&v.ctl[cfg.home]->snap_round, k);
+  for (int j = 0; j < P; ++j) E::st_rlx64(&v.ctl[j]->snap_round, k);
   E::fence_sc();
+  me->ctl_t[3] = E::now_ns();
   RoundDesc d;
   d.round = k;
   d.activator = (uint32_t)me_r;
@@ -178,7 +181,7 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
     locked |= bit_of(j);
     uint32_t cnt = E::ld_acq32(&cj->mbox_count);
     if (cnt > 0) d.accum_mask |= bit_of(j);
-    E::st_rel32(&cj->mbox_count, cnt + 1);
+    E::st_rlx32(&cj->mbox_count, cnt + 1);   // ordered before the descriptor by the fence below
   }
   if (st) {
     for (int j = 0; j < P; ++j)
@@ -193,16 +196,17 @@ ESGD_T uint32_t activate_round(const ChannelView& v, const StepConfig& cfg, cons
   // Tell every contributor which of its epochs this round picks up (it decides from this whether a
   // later publish must fold an older gradient in), before the round becomes visible anywhere.
   for (int j = 0; j < P; ++j)
-    if (d.contrib_mask & bit_of(j)) E::st_rel64(&v.ctl[j]->taken[d.read_epoch[j] % kSlotDepth], d.read_epoch[j]);
+    if (d.contrib_mask & bit_of(j)) E::st_rlx64(&v.ctl[j]->taken[d.read_epoch[j] % kSlotDepth], d.read_epoch[j]);
 
   // Activation = one descriptor store per peer, then the round number.
-  E::st_rel32(&me->done_count[k % kDescRing], 0u);
+  E::st_rlx32(&me->done_count[k % kDescRing], 0u);
   for (int j = 0; j < P; ++j) {
     RoundDesc* dj = &v.ctl[j]->desc[k % kDescRing];
     *dj = d;
   }
   E::fence();
-  for (int j = 0; j < P; ++j) E::st_rel64(&v.ctl[j]->latest_round, k);
+  for (int j = 0; j < P; ++j) E::st_rlx64(&v.ctl[j]->latest_round, k);
+  me->ctl_t[4] = E::now_ns();
   me->stat_rounds_activated++;
   return 0;
 }
@@ -256,13 +260,19 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
     if (fate == SLOT_FOLD) me->stat_folded_grads++;
     else if (fate == SLOT_DROP) me->stat_dropped_grads++;
   }
-  bool may_activate = true;
-  if (!sync_round && pol.base_mode == MODE_MAJORITY)
-    may_activate = (majority_initiator(pol.seed, k, P) == i);
+  // Eager solo rounds elect their activator (first arriver wins a compare-and-swap on the home rank);
+  // majority rounds and synchronous rounds have a designated one, known to every rank without a message:
+  // the shared-seed initiator, and rank (k mod P), which saves the election's round trip.
+  bool may_activate = true, elected = false;
+  if (sync_round) { may_activate = ((int)(k % (uint64_t)P) == i); elected = may_activate; }
+  else if (pol.base_mode == MODE_MAJORITY) may_activate = (majority_initiator(pol.seed, k, P) == i);
 
   // Publish: the gradient is already in slot (k % 2); make it visible, then the epoch.
   E::fence();
-  for (int j = 0; j < P; ++j) E::st_rel64(&v.ctl[j]->pub_epoch[i], k);
+  for (int j = 0; j < P; ++j) E::st_rlx64(&v.ctl[j]->pub_epoch[i], k);
+  me->ctl_t[0] = t0;
+  me->ctl_t[1] = E::now_ns();
+  me->ctl_t[2] = me->ctl_t[3] = me->ctl_t[4] = 0;
 
   bool tried = false;
   uint64_t lr;
@@ -271,7 +281,9 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
     if (lr >= k) break;
     if (may_activate && !tried) {
       tried = true;
-      if (E::cas64(&v.ctl[cfg.home]->owner, k - 1, k) == k - 1) {
+      if (elected) E::st_rlx64(&v.ctl[cfg.home]->owner, k);   // keeps the election word in step for eager rounds
+      if (elected || E::cas64(&v.ctl[cfg.home]->owner, k - 1, k) == k - 1) {
+        me->ctl_t[2] = E::now_ns();
         uint32_t st = activate_round<E>(v, cfg, pol, k, sync_round, t0);
         if (st) { me->status |= st; me->stat_wait_ns += E::now_ns() - t0; return; }
         continue;
@@ -285,6 +297,7 @@ ESGD_T void ctl_step(const ChannelView& v, const StepConfig& cfg, const StepPoli
     E::pause();
   }
 
+  me->ctl_t[5] = E::now_ns();
   const RoundDesc* d = &me->desc[k % kDescRing];
   const bool participant = (lr == k) && (d->round == k) && (d->fresh_mask & bit_of(i));
   if (sync_round) me->stat_sync_rounds++;
@@ -370,13 +383,13 @@ template <class E>
 ESGD_T void finish_step(const ChannelView& v, const StepConfig& cfg, const Plan* plan) {
   ChannelCtl* me = v.ctl[cfg.rank];
   if (plan->role == ROLE_PARTICIPANT) {
-    E::fence();
-    ChannelCtl* act = v.ctl[plan->activator];
+    ChannelCtl* act = v.ctl[plan->activator];   // the atomic below releases this rank's writes and acquires the others'
+
     uint32_t old = E::add32(&act->done_count[plan->round % kDescRing], 1u);
     if ((int32_t)old == plan->part_count - 1) {
       E::fence();
-      for (int n = 0; n < plan->n_push; ++n) E::st_rel32(&v.ctl[plan->push_rank[n]]->mbox_lock, 0u);
-      for (int j = 0; j < cfg.world; ++j) E::st_rel64(&v.ctl[j]->round_done, plan->round);
+      for (int n = 0; n < plan->n_push; ++n) E::st_rlx32(&v.ctl[plan->push_rank[n]]->mbox_lock, 0u);
+      for (int j = 0; j < cfg.world; ++j) E::st_rlx64(&v.ctl[j]->round_done, plan->round);
     }
   } else if (plan->role == ROLE_DRAIN && plan->holds_own_lock) {
     E::fence();

@@ -209,7 +209,7 @@ class EagerOptimizer:
                                       include_stale=self.include_stale, timeout_s=self.timeout_s,
                                       grace_us=self.grace_us, hyper=b.hyper, max_blocks=self.max_blocks,
                                       two_shot_min=self.two_shot_min, accumulate=self.accumulate,
-                                      adaptive_grace=self.adaptive_grace, **kw)
+                                      adaptive_grace=self.adaptive_grace, mc_base=arena.mc_base, **kw)
             self._refresh_hyper(b, force=True)
         if master_of:
             if len(self.optimizer.state) != 0:

@@ -61,7 +61,8 @@ class ChannelDesc(C.Structure):
                [(n, C.c_void_p) for n in "grad_in w32 mom w16 out".split()] + \
                [("out_bf16", C.c_int32), ("pad", C.c_int32), ("hyper", C.c_void_p), ("two_shot_min", C.c_uint64),
                 ("accumulate", C.c_int32), ("adaptive_grace", C.c_int32), ("clear_grad", C.c_int32),
-                ("pad3", C.c_int32)]
+                ("pad3", C.c_int32), ("mc_slot0", C.c_void_p), ("mc_slot1", C.c_void_p), ("mc_red", C.c_void_p),
+                ("mc_min", C.c_uint64)]
 
 
 STAT_NAMES = ("local_step", "participated", "absent", "activated", "sync_rounds", "dropped_grads",
@@ -105,6 +106,7 @@ def cuda():
         lib.esgd_channel_configure.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         lib.esgd_channel_step.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
         lib.esgd_channel_applied.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_void_p]
+        lib.esgd_channel_times.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         lib.esgd_set_hyper.argtypes = [C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p]
         lib.esgd_channel_flush.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
         lib.esgd_emulated_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
@@ -131,7 +133,14 @@ def check_cuda(code: int, what: str) -> None:
 
 
 def parse_stats(raw) -> dict:
-    return {n: int(raw[i]) for i, n in enumerate(STAT_NAMES)}
+    d = {n: int(raw[i]) for i, n in enumerate(STAT_NAMES)}
+    t = [int(raw[16 + q]) for q in range(6)]
+    us = lambda a, b: (t[b] - t[a]) / 1e3 if t[a] and t[b] else None
+    # newest control step: publishing, the election, the activator's waits and its descriptor broadcast, and
+    # the time until the round was visible here
+    d["control_us"] = {"publish": us(0, 1), "elect": us(1, 2), "activate_wait": us(2, 3), "describe": us(3, 4),
+                       "visible": us(0, 5)}
+    return d
 
 
 def launch_count() -> int:

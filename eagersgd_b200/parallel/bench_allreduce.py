@@ -29,7 +29,7 @@ from .nvlink_channel import NvlinkChannel, create_arenas
 
 
 def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False, grace_us=50.0,
-             hold_us=300.0):
+             hold_us=300.0, multicast=True):
     dev = group.device
     esz = 2 if dtype == torch.bfloat16 else 4
     count = max(nbytes // esz // 8 * 8, 8)
@@ -38,7 +38,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
     rng = random.Random(seed)
     ch = arena = None
     if mode != "nccl":
-        arena, bases = create_arenas(count, dtype, group.rank, group.world, group.exchange)
+        arena, bases = create_arenas(count, dtype, group.rank, group.world, group.exchange,
+                                     multicast=None if multicast else False)
         kw = {}
         if fused:
             kw = dict(w32=torch.zeros(count, device=dev), mom=torch.zeros(count, device=dev),
@@ -47,9 +48,9 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
             kw = dict(out=torch.empty(count, dtype=dtype, device=dev))
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=dtype, mode=mode, limiter=-1,
                            average="world", timeout_s=20.0, grace_us=grace_us,
-                           two_shot_min=None if one_shot else 1 << 16, **kw)
+                           two_shot_min=None if one_shot else 1 << 16, mc_base=arena.mc_base, **kw)
     buf = grad.clone()
-    times = []
+    times, phases = [], {}
     for it in range(iters + 3):
         delays = [0.0] * group.world
         for _ in range(late):
@@ -69,23 +70,32 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
         torch.cuda.synchronize()
         if it >= 3:
             times.append(e0.elapsed_time(e1))
+            if ch is not None:
+                for kk, vv in ch.phase_times_us().items():
+                    if vv is not None:
+                        phases.setdefault(kk, []).append(vv)
     t = torch.tensor([sum(times) / len(times)], device=dev)
     tmax, tsum = t.clone(), t.clone()
     if group.world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dist.all_reduce(tsum)
-    status = 0
+    status, control_us = 0, None
     if ch is not None:
         ch.flush()
         torch.cuda.synchronize()
-        status = ch.stats()["status"]
+        st = ch.stats()
+        status, control_us = st["status"], st.get("control_us")
         group.barrier()
         arena.free()
     mean_ms, max_ms = float(tsum) / group.world, float(tmax)
     res = dict(mode=mode, bytes=count * esz, dtype=str(dtype).replace("torch.", ""), world=group.world, late=late,
                late_ms=late_ms, fused_update=bool(fused and mode != "nccl"), mean_latency_us=mean_ms * 1e3,
                max_latency_us=max_ms * 1e3, status=status,
-               two_shot=bool(ch is not None and ch.two_shot))
+               two_shot=bool(ch is not None and ch.two_shot), multicast=bool(ch is not None and ch.multicast))
+    if control_us is not None:
+        res["control_us_last"] = control_us
+    if phases:   # this rank's device-side break-down of its steps
+        res["phases_us"] = {kk: round(sum(vv) / len(vv), 1) for kk, vv in phases.items()}
     if mode in ("sync", "nccl") and late == 0:
         res["bus_gbs"] = 2.0 * (group.world - 1) / max(group.world, 1) * count * esz / (max_ms * 1e-3) / 1e9
     return res
@@ -101,6 +111,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fused", action="store_true", help="include the fused momentum-SGD update in our kernels")
     ap.add_argument("--one-shot", action="store_true", help="never split the reduction into reduce-scatter + gather")
+    ap.add_argument("--no-multicast", action="store_true",
+                    help="plain peer loads only: no in-switch (multimem) reduction of rounds in which all are on time")
     ap.add_argument("--grace-us", type=float, default=50.0,
                     help="longest time an activator waits for near-simultaneous arrivals (the window adapts below it)")
     ap.add_argument("--hold-us", type=float, default=300.0,
@@ -111,7 +123,7 @@ def main(argv=None):
         for dt in args.dtypes.split(","):
             for mode in args.modes.split(","):
                 r = run_case(group, size, getattr(torch, dt), mode, args.late, args.late_ms, args.iters, 1234, args.fused,
-                             args.one_shot, args.grace_us, args.hold_us)
+                             args.one_shot, args.grace_us, args.hold_us, not args.no_multicast)
                 if group.rank == 0:
                     print(json.dumps(r), flush=True)
     finalize()

@@ -151,6 +151,6 @@ class CpuChannel:
         return N.parse_trace(C.c_void_p(self._bases[self.rank]))
 
     def stats(self) -> dict:
-        raw = (C.c_uint64 * 16)()
+        raw = (C.c_uint64 * 24)()
         self.lib.esgd_ctl_stats(C.c_void_p(self._bases[self.rank]), raw)
         return N.parse_stats(raw)

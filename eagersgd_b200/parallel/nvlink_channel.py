@@ -25,6 +25,9 @@ HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
 # shots (reduce-scatter by peer loads, then every participant pulls the other shares): below it the extra
 # flag round trip costs more than the bytes it saves.
 TWO_SHOT_MIN = 1 << 16
+# Elements from which a round with every rank on time is reduced inside the NVSwitch (multimem), when the
+# arenas have a multicast mapping.
+MULTICAST_MIN = 1 << 12
 _FLOAT_DTYPES = (torch.float32, torch.bfloat16)
 
 
@@ -55,6 +58,7 @@ class Arena:
     """One cudaMalloc'd, zeroed, IPC-exportable allocation on the current device."""
 
     def __init__(self, nbytes: int, export: bool = True):
+        self.mc_base = 0
         self.ptr = C.c_void_p()
         self.handle = (C.c_ubyte * 64)()
         N.check_cuda(N.cuda().esgd_arena_alloc(nbytes, C.byref(self.ptr), self.handle if export else None),
@@ -66,6 +70,36 @@ class Arena:
         if self.ptr:
             N.cuda().esgd_arena_free(self.ptr)
             self.ptr = C.c_void_p()
+
+
+class SymmetricArena:
+    """An arena in symmetric memory with an NVLink multicast mapping (NVSwitch): ``bases`` are the ranks'
+    peer-mapped addresses of it and ``mc_base`` is ONE address whose loads reduce over, and whose stores
+    land in, every rank's copy (``multimem`` instructions).  Allocation, handle exchange and the multicast
+    binding are PyTorch's symmetric-memory plumbing; every kernel that touches the memory is this package's."""
+
+    def __init__(self, nbytes: int, device: torch.device, group_name: str):
+        import torch.distributed._symmetric_memory as symm
+        self.tensor = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.tensor.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm.rendezvous(self.tensor, group_name)
+        self.bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.mc_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.nbytes = nbytes
+        self.base = int(self.tensor.data_ptr())
+
+    def free(self):
+        self.handle = None
+        self.tensor = None
+
+
+def multicast_wanted() -> bool:
+    """NVSwitch multicast is used unless it is switched off: ``ESGD_MULTICAST=0``, or ``NCCL_NVLS_ENABLE=0``
+    (one switch for every library of a job — tests in which a rank leaves a running job set it, because memory
+    bound to a multicast object must not lose its owner)."""
+    import os
+    return os.environ.get("ESGD_MULTICAST", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
 
 
 def open_peer(handle_bytes: bytes) -> int:
@@ -85,6 +119,8 @@ class NvlinkChannel:
     Channels of at least ``two_shot_min`` elements reduce in two shots when a round has
     several participants and at least three contributors (each participant sums its share,
     then pulls the others' shares); ``two_shot_min=None`` keeps the one-shot form.
+    With ``mc_base`` (the multicast address of arenas from ``create_arenas``) rounds in which every rank is
+    on time are reduced inside the NVSwitch from ``mc_min`` elements up.
     ``accumulate`` folds a gradient that no round picked up into the rank's next publish of
     the same slot instead of dropping it; ``clear_grad`` zeroes ``grad_in`` behind the copy
     into the publish slot, so the caller needs no separate fill before the next backward.
@@ -98,7 +134,8 @@ class NvlinkChannel:
                  w16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  hyper: Optional[torch.Tensor] = None, max_blocks: int = 592,
                  two_shot_min: Optional[int] = TWO_SHOT_MIN, accumulate: bool = False,
-                 adaptive_grace: bool = True, clear_grad: bool = False):
+                 adaptive_grace: bool = True, clear_grad: bool = False, mc_base: int = 0,
+                 mc_min: int = MULTICAST_MIN):
         if slot_dtype not in _FLOAT_DTYPES:
             raise ValueError("slot_dtype must be torch.float32 or torch.bfloat16, not %s" % slot_dtype)
         _check_dtype(grad_in, "grad_in")
@@ -129,6 +166,10 @@ class NvlinkChannel:
             d.slot1[j] = bases[j] + L.slot1
             d.red[j] = bases[j] + L.red if two_shot_min is not None else None
             d.rsum[j] = bases[j] + L.rsum
+        if mc_base and two_shot_min is not None and world > 1:
+            d.mc_slot0, d.mc_slot1, d.mc_red = mc_base + L.slot0, mc_base + L.slot1, mc_base + L.red
+            d.mc_min = int(mc_min)
+        self.multicast = bool(mc_base and two_shot_min is not None and world > 1)
         d.two_shot_min = int(two_shot_min) if two_shot_min is not None else 0
         d.accumulate, d.adaptive_grace, d.clear_grad = int(accumulate), int(adaptive_grace), int(clear_grad)
         self.two_shot = int(two_shot_min is not None and world >= 2 and count >= two_shot_min)
@@ -177,6 +218,16 @@ class NvlinkChannel:
                      "reading the step's outcome")
         return bool(v.value)
 
+    def phase_times_us(self) -> dict:
+        """Where the newest step spent its time on the device (microseconds): packing, the control step
+        (publish, election, waits, descriptor), the gap to the data kernel, the data phase.  Synchronises."""
+        t = (C.c_uint64 * 8)()
+        s = torch.cuda.current_stream(self.device)
+        N.check_cuda(self.lib.esgd_channel_times(self._dch.data_ptr(), t, s.cuda_stream), "reading phase clocks")
+        us = lambda a, b: (int(t[b]) - int(t[a])) / 1e3
+        return {"pack": us(0, 1), "control": us(1, 2), "launch_gap": us(2, 3), "data": us(3, 5),
+                "own_share": us(3, 4) if t[4] >= t[3] else None}
+
     def flush(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         N.check_cuda(self.lib.esgd_channel_flush(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
@@ -187,7 +238,7 @@ class NvlinkChannel:
         s = torch.cuda.current_stream(self.device)
         N.check_cuda(self.lib.esgd_memcpy_d2h(self._ctl_host, C.c_void_p(self.bases[self.rank] + self.layout.ctl),
                                               len(self._ctl_host), s.cuda_stream), "reading channel counters")
-        raw = (C.c_uint64 * 16)()
+        raw = (C.c_uint64 * 24)()
         N.host().esgd_ctl_stats(self._ctl_host, raw)
         return N.parse_stats(raw)
 
@@ -203,12 +254,37 @@ class NvlinkChannel:
 
 
 def create_arenas(count: int, slot_dtype: torch.dtype, rank: int, world: int,
-                  exchange: Optional[Callable] = None):
-    """Allocate this rank's arena and map the peers'.  Returns (own Arena, bases)."""
+                  exchange: Optional[Callable] = None, multicast: Optional[bool] = None):
+    """Allocate this rank's arena and map the peers'.  Returns (own arena, bases); ``arena.mc_base`` is the
+    arena's NVLink multicast address, or 0.  With ``multicast`` (default: ``multicast_wanted()``) and an
+    initialised NCCL process group the arena comes from symmetric memory; if any rank cannot get that, all
+    ranks fall back to ``cudaMalloc`` + CUDA IPC."""
     layout = ArenaLayout(count, slot_dtype)
-    arena = Arena(layout.total, export=world > 1)
     if world == 1:
+        arena = Arena(layout.total, export=False)
         return arena, [arena.base]
+    import torch.distributed as dist
+    if multicast is None:
+        multicast = multicast_wanted()
+    want = bool(multicast and dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl" and
+                dist.get_world_size() == world)
+    if all(exchange(want)):
+        arena, err = None, ""
+        try:
+            arena = SymmetricArena(layout.total, torch.device("cuda", torch.cuda.current_device()),
+                                   dist.group.WORLD.group_name)
+        except Exception as e:  # noqa
+            err = repr(e)[:200]
+        oks = exchange(arena is not None and arena.mc_base != 0)
+        if all(oks):
+            exchange("mapped")
+            return arena, arena.bases
+        if arena is not None:
+            arena.free()
+        if rank == 0:
+            import warnings
+            warnings.warn("no NVLink multicast arena (%s): using CUDA IPC arenas" % (err or "a rank has none"))
+    arena = Arena(layout.total, export=True)
     handles = exchange(bytes(arena.handle))
     bases = [arena.base if r == rank else open_peer(h) for r, h in enumerate(handles)]
     exchange("mapped")

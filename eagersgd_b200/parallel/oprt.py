@@ -19,6 +19,10 @@ _DT = {np.dtype("int32"): INT32, np.dtype("int64"): INT64, np.dtype("float32"): 
 
 CALLBACK = C.CFUNCTYPE(None, C.c_int64, C.c_void_p)
 OPERATOR = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int)
+SCHED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64)
+SCHED_WAIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_double)
+DEP_IGNORE_VERSION, DEP_NO_AUTOPOST, DEP_CONSTRAINED = 0x10, 0x20, 0x40
+NONE = -1
 
 _lib = None
 
@@ -58,6 +62,24 @@ def lib():
         l.rt_schedule_wait.argtypes = [vp, i64, C.c_double]
         l.rt_schedule_test.argtypes = [vp, i64]
         l.rt_schedule_print.argtypes = [vp, i64, C.c_char_p, i64]
+        l.rt_buffer_delete.argtypes = [vp, i64]
+        l.rt_op_hb_fallback.argtypes = [vp, i64, i64, i64, i32, C.POINTER(i64)]
+        l.rt_dep_set_parent.argtypes = [vp, i64, i64]
+        l.rt_op_cancel.argtypes = [vp, i64]
+        l.rt_op_free.argtypes = [vp, i64]
+        l.rt_schedule_start.argtypes = [vp, i64]
+        l.rt_schedule_delete.argtypes = [vp, i64]
+        l.rt_schedule_add_part.argtypes = [vp, i64, i64]
+        l.rt_schedule_own_buffer.argtypes = [vp, i64, i64]
+        for nm in ("start", "post", "test", "delete"):
+            getattr(l, "rt_schedule_set_%s_fun" % nm).argtypes = [vp, i64, SCHED_FN]
+        l.rt_schedule_set_wait_fun.argtypes = [vp, i64, SCHED_WAIT_FN]
+        for nm in ("post", "test"):
+            getattr(l, "rt_schedule_default_" + nm).argtypes = [vp, i64]
+        l.rt_schedule_default_wait.argtypes = [vp, i64, C.c_double]
+        l.rt_schedule_set_state.argtypes = [vp, i64, vp]
+        l.rt_schedule_get_state.restype = vp
+        l.rt_schedule_get_state.argtypes = [vp, i64]
         l.rt_activation.restype = i64
         l.rt_activation.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64)]
         l.rt_limiter.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]
@@ -114,6 +136,17 @@ class Rank:
         return lib().rt_operator_create(self.h, cb)
 
     def hb(self, first, second): return lib().rt_op_hb(self.h, first, second)
+    def hb_fallback(self, first, second, fallback=NONE, options=0) -> int:
+        """Versioned edge (the n-th completion of ``first`` feeds the n-th run of ``second``; a completion that
+        comes too late goes to ``fallback``).  Returns the edge handle."""
+        d = C.c_int64()
+        lib().rt_op_hb_fallback(self.h, first, second, fallback, options, C.byref(d))
+        return d.value
+
+    def dep_set_parent(self, constrained: int, constraining: int): return lib().rt_dep_set_parent(self.h, constrained, constraining)
+    def cancel(self, op): return lib().rt_op_cancel(self.h, op)
+    def free(self, op): return lib().rt_op_free(self.h, op)
+    def buffer_delete(self, buf): return lib().rt_buffer_delete(self.h, buf)
     def post(self, op): return lib().rt_op_post(self.h, op)
     def wait(self, op, timeout=30.0): return lib().rt_op_wait(self.h, op, timeout)
     def test(self, op): return lib().rt_op_test(self.h, op)
@@ -122,6 +155,29 @@ class Rank:
     # schedules
     def schedule(self): return lib().rt_schedule_create(self.h)
     def schedule_add(self, s, op): return lib().rt_schedule_add_op(self.h, s, op)
+    def schedule_start(self, s): return lib().rt_schedule_start(self.h, s)
+    def schedule_delete(self, s): return lib().rt_schedule_delete(self.h, s)
+    def schedule_add_part(self, s, part): return lib().rt_schedule_add_part(self.h, s, part)
+
+    def schedule_override(self, s, start=None, post=None, wait=None, test=None, delete=None):
+        """Replace what start / post / wait / test / delete of schedule ``s`` do (composite schedules).  The
+        callables get the schedule handle (``wait`` also the timeout) and return a runtime code; the defaults
+        stay reachable as ``schedule_default_post / _wait / _test``."""
+        keep = self._keep
+        for name, fn, proto in (("start", start, SCHED_FN), ("post", post, SCHED_FN), ("test", test, SCHED_FN),
+                                ("delete", delete, SCHED_FN)):
+            if fn is not None:
+                cb = proto(lambda c, sid, fn=fn: int(fn(sid) or 0))
+                keep.append(cb)
+                getattr(lib(), "rt_schedule_set_%s_fun" % name)(self.h, s, cb)
+        if wait is not None:
+            cb = SCHED_WAIT_FN(lambda c, sid, t, fn=wait: int(fn(sid, t) or 0))
+            keep.append(cb)
+            lib().rt_schedule_set_wait_fun(self.h, s, cb)
+
+    def schedule_default_post(self, s): return lib().rt_schedule_default_post(self.h, s)
+    def schedule_default_wait(self, s, timeout=30.0): return lib().rt_schedule_default_wait(self.h, s, timeout)
+    def schedule_default_test(self, s): return lib().rt_schedule_default_test(self.h, s)
     def schedule_post(self, s): return lib().rt_schedule_post(self.h, s)
     def schedule_wait(self, s, timeout=30.0): return lib().rt_schedule_wait(self.h, s, timeout)
     def schedule_test(self, s): return lib().rt_schedule_test(self.h, s)

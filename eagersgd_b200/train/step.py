@@ -42,7 +42,8 @@ def prepare_model(model: nn.Module, device: torch.device, compute_dtype=torch.bf
 class TrainStep:
     def __init__(self, model: nn.Module, group: Group, impl: str = "ours", mode: str = "solo", limiter: int = 32,
                  bucket_mb: float = 25.0, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 1e-4,
-                 compute_dtype=torch.bfloat16, loss_fn=None, inner_optimizer=None, loss_scale: float = 1.0):
+                 compute_dtype=torch.bfloat16, loss_fn=None, inner_optimizer=None, loss_scale: float = 1.0,
+                 accumulate: bool = False):
         self.group, self.impl, self.device = group, impl, group.device
         self.compute_dtype = compute_dtype if self.device.type == "cuda" else torch.float32
         self.loss_scale = float(loss_scale)
@@ -68,7 +69,7 @@ class TrainStep:
                 inner = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
             cls = {"solo": SoloAllreduceOptimizer, "majority": MajorityAllreduceOptimizer,
                    "sync": SyncAllreduceOptimizer}[mode]
-            kw = dict(bucket_mb=bucket_mb)
+            kw = dict(bucket_mb=bucket_mb, accumulate=accumulate)
             if mode != "sync":
                 kw["limiter"] = limiter
             self.opt = cls(inner, group, **kw)

