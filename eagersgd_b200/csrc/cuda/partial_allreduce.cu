@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(256, 3) pack_ctl_kernel(DevChannel* ch, int fl
   }
 }
 
-__global__ void __launch_bounds__(256, 4) data_kernel(DevChannel* ch) {
+__global__ void __launch_bounds__(256, 3) data_kernel(DevChannel* ch) {
   __shared__ int s_flag;
   data_phase(ch, blockIdx.x, gridDim.x, &s_flag);
 }
@@ -185,9 +185,27 @@ int esgd_channel_configure(void* dch, const esgd_channel_desc* d, void* stream) 
   return (int)cudaStreamSynchronize((cudaStream_t)stream);
 }
 
+// The blocks of the data kernel wait for one another's shares, so all of them must be able to be resident at
+// once: the grid never exceeds what the occupancy calculator gives for the current device.
+static int resident_cap() {
+  static int cap[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (cap[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, data_kernel, 256, 0);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cap[dev] = per_sm > 0 && sms > 0 ? per_sm * sms : 148;
+  }
+  return cap[dev];
+}
+
 static inline int grid_for(uint64_t count, int max_blocks) {
   uint64_t need = (count / 8 + 255) / 256;
   if (need < 1) need = 1;
+  const int cap = resident_cap();
+  if (max_blocks > cap) max_blocks = cap;
   return (int)(need < (uint64_t)max_blocks ? need : (uint64_t)max_blocks);
 }
 

@@ -21,11 +21,13 @@
 // on the reference path).
 //
 // When the arenas come from symmetric memory with an NVLink multicast mapping (NVSwitch), a round in which
-// every rank is on time takes a third form: each rank reduces its share with ONE multimem.ld_reduce per
-// vector on the multicast address of the publish slot (the switch sums the eight slots, fp32 accumulate)
-// and broadcasts the rounded result into every rank's shard buffer with multimem.st; the other shares are
-// then read from LOCAL memory.  A rank receives one vector instead of 2(P-1)/P of it.  Rounds that lack
-// somebody, or carry a stale contribution, use the peer-load forms above.
+// every rank is on time takes a third form: each rank reduces its share with peer loads as above and
+// broadcasts the rounded result into every rank's shard buffer with multimem.st (one store, replicated by
+// the switch); the other shares are then read from LOCAL memory.  The gather half of the exchange costs a
+// rank 1/P of the vector outbound instead of (P-1)/P inbound.  (Reducing the share with
+// multimem.ld_reduce as well was measured and is slower than peer loads here: 57 vs 87 GB/s of reduced
+// output per GPU on eight GPUs at 256 MiB, so the reduction stays on peer loads.)  Rounds that lack
+// somebody use the peer-load forms for both halves.
 //
 // Ranks that miss a round get its result later by a pull, not by a push: in a
 // round that lacks somebody every participant adds the round's result to its
@@ -50,14 +52,14 @@ struct DevChannel {
   void* slot[kMaxRanks][kSlotDepth];
   void* red[kMaxRanks];      // reduced shares of the running round, slot element type (two-shot form)
   void* mc_slot[kSlotDepth]; // multicast addresses of the publish slots and of the shard buffer (null: none):
-  void* mc_red;              // a load reduces over every rank's copy, a store lands in every rank's copy
+  void* mc_red;              // a store to one lands in every rank's copy
   float* rsum[kMaxRanks];    // running sums of the results of rounds that lacked somebody
   StepConfig cfg;
   StepPolicy pol;
   uint64_t count;            // elements; multiple of 8
   int32_t slot_bf16;         // publish-slot element type: 1 bf16, 0 fp32
   int32_t grad_in_bf16;
-  void* grad_in;             // flat gradient written by backward
+  void* grad_in;             // flat gradient written by backward (null: the caller fills the publish slot directly)
   float* w32;                // fused update: fp32 master weights (null: plain mode)
   float* mom;                // momentum buffer
   __nv_bfloat16* w16;        // optional bf16 copy of the weights used by the model
@@ -152,9 +154,16 @@ __device__ __forceinline__ void share_of(uint64_t count, int parts, int index, u
   *hi = a + per * 8 < count ? a + per * 8 : count;
 }
 
-// Sum the contributors' slots over [lo, hi), scale, round, apply; optionally keep the result in this
-// rank's shard buffer (two-shot form) and add it to the running sum (rounds that lack somebody).
-template <typename ST, bool kKeepShare>
+__device__ __forceinline__ void mc_store8(__nv_bfloat16* mc, uint64_t i, const float v[8]);
+__device__ __forceinline__ void mc_store8(float* mc, uint64_t i, const float v[8]);
+
+enum ShareMode { SHARE_APPLY = 0, SHARE_KEEP = 1, SHARE_MULTICAST = 2 };
+
+// Sum the contributors' slots over [lo, hi), scale and round.  One-shot form (SHARE_APPLY): apply the result,
+// and add it to the running sum in rounds that lack somebody.  Two-shot forms: leave the result in this
+// rank's shard buffer (SHARE_KEEP) or store it into every rank's shard buffer through the switch
+// (SHARE_MULTICAST); everything is applied from the shard buffers afterwards.
+template <typename ST, int kKeepShare>
 __device__ void reduce_range(const DevChannel* ch, uint64_t lo, uint64_t hi, uint64_t tid, uint64_t nthreads) {
   const Plan& plan = ch->plan;
   const int n_src = plan.n_src;
@@ -162,7 +171,7 @@ __device__ void reduce_range(const DevChannel* ch, uint64_t lo, uint64_t hi, uin
 #pragma unroll
   for (int s = 0; s < kMaxRanks; ++s)
     src[s] = s < n_src ? reinterpret_cast<const ST*>(ch->slot[plan.src_rank[s]][plan.src_parity[s]]) : nullptr;
-  ST* share = reinterpret_cast<ST*>(ch->red[ch->cfg.rank]);
+  ST* share = reinterpret_cast<ST*>(kKeepShare == SHARE_MULTICAST ? ch->mc_red : ch->red[ch->cfg.rank]);
   float* rs = plan.n_push > 0 ? ch->rsum[ch->cfg.rank] : nullptr;
   const float scale = plan.scale;
   const Hyper hp(ch->hyper);
@@ -177,7 +186,14 @@ __device__ void reduce_range(const DevChannel* ch, uint64_t lo, uint64_t hi, uin
 #pragma unroll
     for (int q = 0; q < 8; ++q) acc[q] *= scale;
     round8(src[0], acc);
-    if (kKeepShare) store8(share, i, acc);
+    if (kKeepShare == SHARE_KEEP) {
+      store8(share, i, acc);
+      continue;
+    }
+    if (kKeepShare == SHARE_MULTICAST) {
+      mc_store8(share, i, acc);
+      continue;
+    }
     if (rs != nullptr) {
       load8(rs, i, v);
 #pragma unroll
@@ -188,46 +204,39 @@ __device__ void reduce_range(const DevChannel* ch, uint64_t lo, uint64_t hi, uin
   }
 }
 
-// Two-shot, second half: fetch the share of participant `owner` from its shard buffer and apply it.
+// Two-shot, second half: fetch one share of the result from the shard buffer of `from_rank` and apply it.
 template <typename ST>
 __device__ void pull_share(const DevChannel* ch, int from_rank, uint64_t lo, uint64_t hi, uint64_t tid,
                            uint64_t nthreads) {
   const ST* share = reinterpret_cast<const ST*>(ch->red[from_rank]);
   float* rs = ch->plan.n_push > 0 ? ch->rsum[ch->cfg.rank] : nullptr;
   const Hyper hp(ch->hyper);
-  for (uint64_t i = lo + tid * 8; i < hi; i += nthreads * 8) {
-    float g[8], v[8];
-    load8(share, i, g);
-    if (rs != nullptr) {
-      load8(rs, i, v);
+  constexpr int kUnroll = 4;     // independent loads in flight per thread
+  const uint64_t stride = nthreads * 8;
+  for (uint64_t base = lo + tid * 8; base < hi; base += stride * kUnroll) {
+    float g[kUnroll][8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] += g[q];
-      store8(rs, i, v);
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i < hi) load8(share, i, g[u]);
     }
-    apply8(ch, i, g, hp.lr, hp.mu, hp.wd, hp.nesterov, hp.gscale);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t i = base + u * stride;
+      if (i >= hi) break;
+      if (rs != nullptr) {
+        float v[8];
+        load8(rs, i, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] += g[u][q];
+        store8(rs, i, v);
+      }
+      apply8(ch, i, g[u], hp.lr, hp.mu, hp.wd, hp.nesterov, hp.gscale);
+    }
   }
 }
 
 // ---- NVSwitch multicast (multimem) ------------------------------------------------------------------------
-__device__ __forceinline__ void mc_load_sum8(const __nv_bfloat16* mc, uint64_t i, float v[8]) {
-  uint32_t r0, r1, r2, r3;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "l"(mc + i) : "memory");
-  const uint32_t raw[4] = {r0, r1, r2, r3};
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(raw);
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float2 f = __bfloat1622float2(h[q]);
-    v[2 * q] = f.x;
-    v[2 * q + 1] = f.y;
-  }
-}
-__device__ __forceinline__ void mc_load_sum8(const float* mc, uint64_t i, float v[8]) {
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(mc + i) : "memory");
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(mc + i + 4) : "memory");
-}
 __device__ __forceinline__ void mc_store8(__nv_bfloat16* mc, uint64_t i, const float v[8]) {
   uint4 raw;
   __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
@@ -242,37 +251,6 @@ __device__ __forceinline__ void mc_store8(float* mc, uint64_t i, const float v[8
                :: "l"(mc + i), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
                :: "l"(mc + i + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
-}
-
-// Full round over the switch: reduce this rank's share of slot `parity` with in-switch sums, apply it, and
-// broadcast the rounded result into the shard buffer of every rank.
-template <typename ST>
-__device__ void mc_reduce_range(const DevChannel* ch, int parity, uint64_t lo, uint64_t hi, uint64_t tid,
-                                uint64_t nthreads) {
-  const ST* mc_in = reinterpret_cast<const ST*>(ch->mc_slot[parity]);
-  ST* mc_out = reinterpret_cast<ST*>(ch->mc_red);
-  const float scale = ch->plan.scale;
-  const Hyper hp(ch->hyper);
-  constexpr int kUnroll = 2;     // in-switch reductions in flight per thread
-  const uint64_t stride = nthreads * 8;
-  for (uint64_t base = lo + tid * 8; base < hi; base += stride * kUnroll) {
-    float acc[kUnroll][8];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const uint64_t i = base + u * stride;
-      if (i < hi) mc_load_sum8(mc_in, i, acc[u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const uint64_t i = base + u * stride;
-      if (i >= hi) break;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) acc[u][q] *= scale;
-      round8(mc_in, acc[u]);
-      mc_store8(mc_out, i, acc[u]);
-      apply8(ch, i, acc[u], hp.lr, hp.mu, hp.wd, hp.nesterov, hp.gscale);
-    }
-  }
 }
 
 // Tell every participant that this rank's share of the round is complete in its shard buffer.
@@ -327,14 +305,14 @@ __device__ void participant_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   const uint64_t tid = (uint64_t)blk * blockDim.x + threadIdx.x, nth = (uint64_t)nblk * blockDim.x;
   const Plan& plan = ch->plan;
   if (!plan.two_shot) {
-    reduce_range<ST, false>(ch, 0, ch->count, tid, nth);
+    reduce_range<ST, SHARE_APPLY>(ch, 0, ch->count, tid, nth);
     return;
   }
   uint64_t lo, hi;
   share_of(ch->count, plan.part_count, plan.part_index, &lo, &hi);
   const bool over_switch = plan.two_shot == 2;
-  if (over_switch) mc_reduce_range<ST>(ch, plan.src_parity[0], lo, hi, tid, nth);
-  else reduce_range<ST, true>(ch, lo, hi, tid, nth);
+  if (over_switch) reduce_range<ST, SHARE_MULTICAST>(ch, lo, hi, tid, nth);
+  else reduce_range<ST, SHARE_KEEP>(ch, lo, hi, tid, nth);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -345,22 +323,28 @@ __device__ void participant_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
       gather_signal(ch);
     }
   }
-  // the other shares, in an order that differs from rank to rank
+  // Every share, this rank's own included (its flag is raised by the last of this rank's blocks, so waiting
+  // for it is also the barrier between the blocks that wrote the share and the blocks that read it).  All
+  // blocks of the grid must be able to run at once: the launcher sizes the grid by the kernel's occupancy.
   int owners[kMaxRanks], n_own = 0;
   for (int j = 0; j < ch->cfg.world; ++j)
     if (plan.fresh_mask & (1u << j)) owners[n_own++] = j;
-  for (int step = 1; step < n_own; ++step) {
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int j = 0; j < n_own && ok; ++j) ok = gather_wait(ch, owners[j]) ? 1 : 0;
+    *s_flag = ok;
+  }
+  __syncthreads();
+  const int ok = *s_flag;
+  __syncthreads();
+  if (!ok) {
+    if (threadIdx.x == 0) atomicOr(&ch->view.ctl[ch->cfg.rank]->status, (uint32_t)ST_TIMEOUT_GATHER);
+    return;
+  }
+  for (int step = 0; step < n_own; ++step) {       // no barrier between the shares: loads of several are in flight
     const int idx = (plan.part_index + step) % n_own;
-    if (threadIdx.x == 0) *s_flag = gather_wait(ch, owners[idx]) ? 1 : 0;
-    __syncthreads();
-    const int ok = *s_flag;
-    __syncthreads();
-    if (!ok) {
-      if (threadIdx.x == 0) atomicOr(&ch->view.ctl[ch->cfg.rank]->status, (uint32_t)ST_TIMEOUT_GATHER);
-      continue;
-    }
     share_of(ch->count, n_own, idx, &lo, &hi);
-    // over the switch the owner has stored its share into this rank's own shard buffer
+    // over the switch every owner has stored its share into this rank's own shard buffer
     pull_share<ST>(ch, over_switch ? ch->cfg.rank : owners[idx], lo, hi, tid, nth);
   }
 }
@@ -423,6 +407,7 @@ __device__ inline void pack_phase(DevChannel* ch, uint32_t blk, uint32_t nblk, i
   const int fate = *s_flag;
   __syncthreads();
   if (fate < 0) return;
+  if (ch->grad_in == nullptr) return;      // the caller has written this epoch's gradient into the slot itself
   const bool fold = fate == SLOT_FOLD;
   void* dst = ch->slot[ch->cfg.rank][k % kSlotDepth];
   const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -470,14 +455,13 @@ __device__ inline void decide_two_shot(DevChannel* ch) {
   const Plan& p = ch->plan;
   ch->plan.two_shot = (p.role == ROLE_PARTICIPANT && p.part_count >= 2 && p.n_src >= 3 &&
                        ch->count >= ch->two_shot_min && ch->red[ch->cfg.rank] != nullptr) ? 1 : 0;
-  // Over the switch: everybody takes part with this round's own gradient (one slot parity, nothing stale),
-  // which also means that nobody is absent and the running sums stay untouched.
-  if (p.role == ROLE_PARTICIPANT && ch->mc_red != nullptr && p.part_count == ch->cfg.world &&
-      p.n_src == ch->cfg.world && p.part_count >= 2 && ch->count >= ch->mc_min) {
-    bool same = true;
-    for (int s = 1; s < p.n_src; ++s) same = same && (p.src_parity[s] == p.src_parity[0]);
-    if (same && ch->mc_slot[p.src_parity[0]] != nullptr) ch->plan.two_shot = 2;
-  }
+  // Over the switch: everybody takes part, so every rank's shard buffer is a destination of the broadcast
+  // (and nobody is absent: the running sums stay untouched).
+  // From four ranks up: with two, a rank's share is half the vector and storing it through the switch was
+  // measured slower (215 GB/s) than the peer's pulling it (620 GB/s).
+  if (p.role == ROLE_PARTICIPANT && ch->mc_red != nullptr && p.part_count == ch->cfg.world && p.part_count >= 4 &&
+      ch->count >= ch->mc_min)
+    ch->plan.two_shot = 2;
   ch->applied = (p.role == ROLE_PARTICIPANT || p.role == ROLE_DRAIN) ? 1 : 0;
 }
 

@@ -29,7 +29,7 @@ from .nvlink_channel import NvlinkChannel, create_arenas
 
 
 def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False, grace_us=50.0,
-             hold_us=300.0, multicast=True):
+             hold_us=300.0, multicast=True, zero_copy=False):
     dev = group.device
     esz = 2 if dtype == torch.bfloat16 else 4
     count = max(nbytes // esz // 8 * 8, 8)
@@ -46,7 +46,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
                       w16=torch.zeros(count, dtype=torch.bfloat16, device=dev) if dtype == torch.bfloat16 else None)
         else:
             kw = dict(out=torch.empty(count, dtype=dtype, device=dev))
-        ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=dtype, mode=mode, limiter=-1,
+        ch = NvlinkChannel(count, group.rank, group.world, bases, dev, None if zero_copy else grad, slot_dtype=dtype,
+                           mode=mode, limiter=-1,
                            average="world", timeout_s=20.0, grace_us=grace_us,
                            two_shot_min=None if one_shot else 1 << 16, mc_base=arena.mc_base, **kw)
     buf = grad.clone()
@@ -55,6 +56,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
         delays = [0.0] * group.world
         for _ in range(late):
             delays[rng.randrange(group.world)] = rng.uniform(0, late_ms * 1e-3)
+        if ch is not None and zero_copy:
+            ch.publish_view().copy_(grad)      # outside the timed region, like filling NCCL's buffer
         group.barrier()
         hold_ns = int(hold_us * 1e3 + delays[group.rank] * 1e9)
         if hold_ns > 0:
@@ -91,7 +94,8 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
     res = dict(mode=mode, bytes=count * esz, dtype=str(dtype).replace("torch.", ""), world=group.world, late=late,
                late_ms=late_ms, fused_update=bool(fused and mode != "nccl"), mean_latency_us=mean_ms * 1e3,
                max_latency_us=max_ms * 1e3, status=status,
-               two_shot=bool(ch is not None and ch.two_shot), multicast=bool(ch is not None and ch.multicast))
+               two_shot=bool(ch is not None and ch.two_shot), multicast=bool(ch is not None and ch.multicast),
+               zero_copy=bool(zero_copy and ch is not None))
     if control_us is not None:
         res["control_us_last"] = control_us
     if phases:   # this rank's device-side break-down of its steps
@@ -111,6 +115,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--fused", action="store_true", help="include the fused momentum-SGD update in our kernels")
     ap.add_argument("--one-shot", action="store_true", help="never split the reduction into reduce-scatter + gather")
+    ap.add_argument("--zero-copy", action="store_true",
+                    help="write the gradient straight into the publish slot (no staging copy inside the timed step)")
     ap.add_argument("--no-multicast", action="store_true",
                     help="plain peer loads only: no in-switch (multimem) reduction of rounds in which all are on time")
     ap.add_argument("--grace-us", type=float, default=50.0,
@@ -123,7 +129,8 @@ def main(argv=None):
         for dt in args.dtypes.split(","):
             for mode in args.modes.split(","):
                 r = run_case(group, size, getattr(torch, dt), mode, args.late, args.late_ms, args.iters, 1234, args.fused,
-                             args.one_shot, args.grace_us, args.hold_us, not args.no_multicast)
+                             args.one_shot, args.grace_us, args.hold_us, not args.no_multicast,
+                             args.zero_copy)
                 if group.rank == 0:
                     print(json.dumps(r), flush=True)
     finalize()

@@ -72,6 +72,20 @@ class Arena:
             self.ptr = C.c_void_p()
 
 
+class _DevicePointer:
+    """Lets ``torch.as_tensor`` wrap device memory this package allocated itself (CUDA array interface)."""
+
+    def __init__(self, ptr: int, count: int, dtype: torch.dtype, keep=None):
+        typestr = {torch.float32: "<f4", torch.bfloat16: "<u2", torch.uint8: "|u1"}[dtype]
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False), "version": 3}
+        self.keep = keep
+
+
+def device_view(ptr: int, count: int, dtype: torch.dtype, device: torch.device, keep=None) -> torch.Tensor:
+    t = torch.as_tensor(_DevicePointer(ptr, count, dtype, keep), device=device)
+    return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+
 class SymmetricArena:
     """An arena in symmetric memory with an NVLink multicast mapping (NVSwitch): ``bases`` are the ranks'
     peer-mapped addresses of it and ``mc_base`` is ONE address whose loads reduce over, and whose stores
@@ -112,7 +126,9 @@ def open_peer(handle_bytes: bytes) -> int:
 class NvlinkChannel:
     """One persistent partial-allreduce channel of ``count`` elements on this GPU.
 
-    ``grad_in`` is the flat gradient the backward pass writes.  With ``w32``/
+    ``grad_in`` is the flat gradient the backward pass writes; ``None`` selects zero-copy publishing: the
+    caller writes each step's gradient straight into ``publish_view()`` (this rank's publish slot of the
+    coming epoch, in peer-mapped memory) and no staging copy runs.  With ``w32``/
     ``mom`` (and optionally ``w16``) the reduction is fused with the momentum-SGD
     update; otherwise the averaged gradient is written to ``out``.
 
@@ -139,6 +155,8 @@ class NvlinkChannel:
         if slot_dtype not in _FLOAT_DTYPES:
             raise ValueError("slot_dtype must be torch.float32 or torch.bfloat16, not %s" % slot_dtype)
         _check_dtype(grad_in, "grad_in")
+        if grad_in is None and accumulate:
+            raise ValueError("zero-copy publishing overwrites the slot: it cannot fold an older gradient in")
         _check_dtype(w32, "w32", (torch.float32,))
         _check_dtype(mom, "mom", (torch.float32,))
         _check_dtype(w16, "w16", (torch.bfloat16,))
@@ -156,7 +174,9 @@ class NvlinkChannel:
             hyper = torch.zeros(HYPER_LEN, dtype=torch.float32, device=device)
             hyper[4] = 1.0
         self.hyper = hyper
-        assert grad_in.numel() == count and grad_in.is_contiguous()
+        assert grad_in is None or (grad_in.numel() == count and grad_in.is_contiguous())
+        self.slot_dtype = slot_dtype
+        self._steps = 0
         self._dch = torch.zeros(int(self.lib.esgd_dev_channel_bytes()), dtype=torch.uint8, device=device)
         d = N.ChannelDesc()
         L = self.layout
@@ -176,10 +196,10 @@ class NvlinkChannel:
         d.rank, d.world, d.base_mode = rank, world, _MODES[mode]
         d.include_stale, d.average, d.home = int(include_stale), _AVG[average], home
         d.slot_bf16 = int(slot_dtype == torch.bfloat16)
-        d.grad_in_bf16 = int(grad_in.dtype == torch.bfloat16)
+        d.grad_in_bf16 = int(grad_in is not None and grad_in.dtype == torch.bfloat16)
         d.limiter, d.seed = limiter, seed
         d.timeout_ns, d.grace_ns, d.count = int(timeout_s * 1e9), int(grace_us * 1e3), count
-        d.grad_in = grad_in.data_ptr()
+        d.grad_in = grad_in.data_ptr() if grad_in is not None else None
         d.w32 = w32.data_ptr() if w32 is not None else None
         d.mom = mom.data_ptr() if mom is not None else None
         d.w16 = w16.data_ptr() if w16 is not None else None
@@ -201,6 +221,15 @@ class NvlinkChannel:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         N.check_cuda(self.lib.esgd_channel_step(self._dch.data_ptr(), self.count, self.max_blocks, s.cuda_stream),
                      "partial allreduce launch")
+        self._steps += 1
+
+    def publish_view(self) -> torch.Tensor:
+        """This rank's publish slot of the coming step as a tensor (zero-copy publishing: fill it, then ``step()``).
+        Slots alternate from step to step; a slot is free again once the step after next is being prepared, which
+        ``step()`` checks on the device — do not write into a view obtained before the previous ``step()``."""
+        parity = (self._steps + 1) % 2
+        off = self.layout.slot0 if parity == 0 else self.layout.slot1
+        return device_view(self.bases[self.rank] + off, self.count, self.slot_dtype, self.device)
 
     def set_hyper(self, lr: float, momentum: float, weight_decay: float, nesterov: bool, grad_scale: float,
                   stream: Optional[torch.cuda.Stream] = None) -> None:

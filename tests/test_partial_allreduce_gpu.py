@@ -380,3 +380,31 @@ def test_wrapped_optimizer_keeps_fp32_masters_and_skips_idle_steps():
     assert moved.max() > 0 and moved.max() < 2e-4          # eight Adam steps of 1e-5: far below bf16 resolution of O(1) weights
     assert torch.equal(p.detach(), master.to(torch.bfloat16))
     opt.close()
+
+
+def test_zero_copy_publishing_matches_the_staged_path():
+    """Writing the gradient straight into the publish slot gives the same result as handing it over in a
+    separate buffer (which the kernel copies into the slot)."""
+    from eagersgd_b200.parallel.nvlink_channel import NvlinkChannel, create_arenas
+    dev = _dev()
+    count = 8 * 300
+    outs = []
+    for zero_copy in (False, True):
+        arena, bases = create_arenas(count, torch.bfloat16, 0, 1)
+        grad = torch.zeros(count, dtype=torch.bfloat16, device=dev)
+        out = torch.zeros(count, device=dev)
+        ch = NvlinkChannel(count, 0, 1, bases, dev, None if zero_copy else grad, slot_dtype=torch.bfloat16, mode="solo",
+                           limiter=-1, average="world", out=out, timeout_s=2.0)
+        res = []
+        torch.manual_seed(9)
+        for k in range(5):
+            g = torch.randn(count, device=dev).to(torch.bfloat16)
+            (ch.publish_view() if zero_copy else grad).copy_(g)
+            ch.step()
+            torch.cuda.synchronize()
+            res.append(out.clone())
+            assert torch.equal(out, g.float())
+        assert ch.stats()["status"] == 0
+        outs.append(res)
+        arena.free()
+    assert all(torch.equal(a, b) for a, b in zip(*outs))
