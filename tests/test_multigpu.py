@@ -280,3 +280,63 @@ def test_full_rounds_over_the_switch_match_nccl(slot_bf16):
     for err, same, st, used in res:
         assert st == 0 and same
         assert err < (2e-2 if slot_bf16 else 2e-6)
+
+
+def _train_resnet32(rank, world, mode, accumulate, steps):
+    """ResNet-32 on a learnable synthetic task (every class has a fixed random low-frequency template, an image
+    is half its class template plus unit noise), one random rank per step delayed by 1.5 x the step time:
+    returns the loss curve of this rank and the optimizer's counters."""
+    es, group = _setup(rank, world)
+    from eagersgd_b200.models.resnet import cifar_resnet
+    from eagersgd_b200.train.imbalance import RandomRankFactor
+    from eagersgd_b200.train.step import TrainStep
+    dev = group.device
+    torch.manual_seed(11)                                   # same initial replica and same teacher everywhere
+    model = cifar_resnet(32, 1, 10)
+    teacher = torch.randn(10, 3, 4, 4).repeat_interleave(8, 2).repeat_interleave(8, 3).to(dev)   # low-frequency templates
+    step = TrainStep(model, group, mode=mode, limiter=8, bucket_mb=1.0, lr=0.1, momentum=0.9, weight_decay=1e-4,
+                     accumulate=accumulate)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)     # every rank sees its own data
+    inj = RandomRankFactor(world, 0.005, 1.5, seed=77)
+    losses = []
+    for k in range(steps):
+        y = torch.randint(0, 10, (128,), device=dev, generator=g)
+        x = torch.randn(128, 3, 32, 32, device=dev, generator=g) + 0.5 * teacher[y]
+        xb = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        d = inj.delays()[rank]
+        if d > 0 and mode is not None:
+            step.inject_delay(d)
+        losses.append(step.run_device(xb, y))
+    torch.cuda.synchronize()
+    curve = [float(l) for l in losses]
+    st = step.stats()
+    group.barrier()
+    step.close()
+    es.finalize()
+    return curve, st
+
+
+def test_eager_training_converges_like_synchronous_sgd():
+    """Solo and majority eager-SGD under injected imbalance reach the loss of synchronous SGD on the same task
+    (the reference's claim, README.md:4-6), no gradient is dropped when unconsumed gradients are folded into
+    the next publish, and no rank falls further behind than the limiter allows."""
+    world, steps = _world(), 300
+    tail = lambda c: sum(c[-30:]) / 30.0
+    curves, final = {}, {}
+    for mode in ("sync", "solo", "majority"):
+        res = run_ranks(_train_resnet32, world, (mode, mode != "sync", steps), timeout=600)
+        curves[mode] = [sum(r[0][k] for r in res) / world for k in range(steps)]      # mean over ranks per step
+        final[mode] = tail(curves[mode])
+        for curve, st in res:
+            assert st["status"] == 0
+            assert st["dropped_grads"] == 0
+            assert st["staleness"] <= 8 + 1
+    out_dir = os.environ.get("ESGD_CURVES_DIR")
+    if out_dir:
+        import json
+        with open(os.path.join(out_dir, "convergence_resnet32_%dgpu.json" % world), "w") as f:
+            json.dump({"world": world, "steps": steps, "final": final,
+                       "curves": {m: [round(v, 4) for v in c[::5]] for m, c in curves.items()}}, f)
+    assert final["sync"] < 0.7 * curves["sync"][0], final            # the task is learnable and was learnt
+    for mode in ("solo", "majority"):
+        assert final[mode] <= 1.10 * final["sync"] + 0.02, final
