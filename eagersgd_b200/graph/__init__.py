@@ -1,3 +1,4 @@
 """Model graphs (ONNX-shaped object model, visitors) and their execution with this framework's operators."""
 from .ir import Graph, Operation, Visitor, OpCounter, STANDARD_OPS, LOSS_OPS, EXTENSION_OPS  # noqa: F401
 from .executor import GraphNetwork, from_torch_resnet  # noqa: F401
+from .onnx_io import load_onnx, save_onnx, parse_onnx, dump_onnx  # noqa: F401

@@ -1,4 +1,5 @@
 import numpy as np
+import pytest
 import torch
 
 from eagersgd_b200.graph import Graph, GraphNetwork, OpCounter, from_torch_resnet
@@ -82,3 +83,74 @@ def test_elementwise_and_shape_operators():
     out = GraphNetwork(g)(x)
     ref = F.pad(F.leaky_relu(x * 2.0 - 1.0, 0.1), [2, 4, 1, 3]).mean((2, 3)).t().tanh().clamp(-0.5, 0.5)
     assert out.shape == (3, 2) and torch.allclose(out, ref, atol=1e-6)
+
+
+def test_onnx_file_round_trip(tmp_path):
+    """A graph written as a .onnx file (protobuf wire format, no onnx package) reads back with the same
+    nodes, attributes of every kind, initializers and inputs / outputs."""
+    import numpy as np
+    from eagersgd_b200.graph.ir import Graph
+    from eagersgd_b200.graph.onnx_io import load_onnx, save_onnx
+    g = Graph("net")
+    g.add_input("x")
+    g.add_initializer("w", np.random.randn(4, 3, 3, 3).astype(np.float32))
+    g.add_initializer("idx", np.arange(6, dtype=np.int64).reshape(2, 3))
+    g.add("Conv", ["x", "w"], ["y"], kernel_shape=[3, 3], pads=[1, 1, 1, 1], strides=[2, 2], group=1, auto_pad="NOTSET")
+    g.add("LeakyRelu", ["y"], ["z"], alpha=0.25)
+    g.add("Constant", [], ["c"], value=np.array([1.5, -2.0], dtype=np.float32))
+    g.add("Pad", ["z"], ["out"], pads=[0, 0, 1, 1, 0, 0, 1, 1], mode="constant", scales=[1.0, 0.5])
+    g.add_output("out")
+    path = str(tmp_path / "net.onnx")
+    save_onnx(g, path)
+    h = load_onnx(path)
+    assert h.name == "net" and h.inputs == ["x"] and h.outputs == ["out"]
+    assert [o.op_type for o in h.ops] == ["Conv", "LeakyRelu", "Constant", "Pad"]
+    assert h.ops[0].attrs["pads"] == [1, 1, 1, 1] and h.ops[0].attrs["auto_pad"] == "NOTSET" and h.ops[0].attrs["group"] == 1
+    assert abs(h.ops[1].attrs["alpha"] - 0.25) < 1e-7 and h.ops[3].attrs["scales"] == [1.0, 0.5]
+    assert np.array_equal(h.ops[2].attrs["value"], np.array([1.5, -2.0], dtype=np.float32))
+    assert np.array_equal(h.initializers["w"], g.initializers["w"]) and h.initializers["idx"].dtype == np.int64
+    assert h.meta["opsets"][""] == 13
+
+
+def test_onnx_file_from_the_torch_exporter_runs_on_the_executor(tmp_path):
+    """A model exported by PyTorch's own ONNX exporter is parsed and gives the exporter model's outputs."""
+    import numpy as np
+    import torch
+    from eagersgd_b200.graph.executor import GraphNetwork
+    from eagersgd_b200.graph.onnx_io import load_onnx
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU(),
+                            torch.nn.MaxPool2d(2), torch.nn.Flatten(), torch.nn.Linear(8 * 4 * 4, 5)).eval()
+    x = torch.randn(2, 3, 8, 8)
+    path = str(tmp_path / "m.onnx")
+    try:
+        torch.onnx.export(m, (x,), path, input_names=["x"], output_names=["y"], opset_version=13, dynamo=False)
+    except Exception as e:   # noqa
+        pytest.skip("this PyTorch cannot export without extra packages: %s" % str(e)[:80])
+    g = load_onnx(path)
+    assert g.inputs == ["x"] and g.outputs == ["y"] and any(o.op_type == "Conv" for o in g.ops)
+    net = GraphNetwork(g).eval()
+    with torch.no_grad():
+        got = net(x)
+        ref = m(x)
+    got = got[0] if isinstance(got, (list, tuple)) else got
+    assert torch.allclose(got.float(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_resnet_graph_survives_an_onnx_file(tmp_path):
+    """Model -> graph -> .onnx file -> graph -> executor: same logits as the model."""
+    from eagersgd_b200.graph import load_onnx, save_onnx
+    torch.manual_seed(3)
+    model = cifar_resnet(8, 1, 10).eval()
+    g = from_torch_resnet(model)
+    path = str(tmp_path / "resnet8.onnx")
+    save_onnx(g, path)
+    h = load_onnx(path)
+    assert len(h.ops) == len(g.ops) and sorted(h.initializers) == sorted(g.initializers)
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        a = GraphNetwork(g).eval()(x)
+        b = GraphNetwork(h).eval()(x)
+    a = a[0] if isinstance(a, (list, tuple)) else a
+    b = b[0] if isinstance(b, (list, tuple)) else b
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
