@@ -98,3 +98,72 @@ def test_inline_cpp_operator_and_validation(tmp_path):
     with pytest.raises(AssertionError):
         bad = custom_python_op(lambda t: t * t, lambda g, ins, outs: (ins[0] * g[0],))
         test_op_gradient(bad, [torch.randn(5) + 2], eps=1e-3)
+
+
+def test_cpp_oracles_with_backward_match_autograd():
+    """Every C++ oracle added for parity with the reference's operator set, forward and backward, against
+    PyTorch autograd in double precision."""
+    import numpy as np
+    import torch
+    import torch.nn.functional as F
+    from eagersgd_b200.ref import cpp_ops as R
+    rng = np.random.RandomState(0)
+    t = lambda a: torch.tensor(a, dtype=torch.float64, requires_grad=True)
+    close = lambda a, b: np.allclose(a, b.detach().numpy() if hasattr(b, "detach") else b, rtol=1e-4, atol=1e-5)
+
+    a, b = rng.randn(3, 5).astype(np.float32), rng.randn(3, 5).astype(np.float32)
+    assert close(R.add(a, b), a + b) and all(close(g, np.ones_like(a) * 2) for g in R.add_grad(np.full_like(a, 2)))
+    assert close(R.sum_n([a, b, a]), a + b + a) and len(R.sum_n_grad(a, 3)) == 3
+    assert close(R.reshape(a, (5, 3)), a.reshape(5, 3)) and close(R.reshape_grad(a.reshape(5, 3), (3, 5)), a)
+    assert close(R.relu_grad(a, b), b * (a > 0))
+
+    A, B, dY = rng.randn(4, 6).astype(np.float32), rng.randn(6, 3).astype(np.float32), rng.randn(4, 3).astype(np.float32)
+    ta, tb = t(A), t(B)
+    (ta @ tb).backward(torch.tensor(dY, dtype=torch.float64))
+    assert close(R.matmul(A, B), A @ B)
+    da, db = R.matmul_grad(A, B, dY)
+    assert close(da, ta.grad) and close(db, tb.grad)
+    for trans_a in (False, True):
+        for trans_b in (False, True):
+            Ag = rng.randn(6, 4).astype(np.float32) if trans_a else A
+            Bg = rng.randn(3, 6).astype(np.float32) if trans_b else B
+            ta, tb = t(Ag), t(Bg)
+            y = 0.5 * (ta.t() if trans_a else ta) @ (tb.t() if trans_b else tb)
+            y.backward(torch.tensor(dY, dtype=torch.float64))
+            da, db, dc = R.gemm_grad(Ag, Bg, dY, alpha=0.5, beta=2.0, trans_a=trans_a, trans_b=trans_b)
+            assert close(da, ta.grad) and close(db, tb.grad) and close(dc, 2.0 * dY)
+
+    x = rng.randn(5, 7).astype(np.float32)
+    tx = t(x)
+    ty = torch.softmax(tx, 1)
+    g = rng.randn(5, 7).astype(np.float32)
+    ty.backward(torch.tensor(g, dtype=torch.float64))
+    assert close(R.softmax_grad(R.softmax(x), g), tx.grad)
+
+    x4 = rng.randn(2, 3, 7, 6).astype(np.float32)
+    for k, s, p in ((3, 2, 1), (2, 2, 0), (3, 1, 1)):
+        tx = t(x4)
+        y = F.max_pool2d(tx, k, s, p)
+        g = rng.randn(*y.shape).astype(np.float32)
+        y.backward(torch.tensor(g, dtype=torch.float64))
+        assert close(R.maxpool(x4, k, s, p), y) and close(R.maxpool_grad(x4, g, k, s, p), tx.grad)
+        for inc in (False, True):
+            tx = t(x4)
+            y = F.avg_pool2d(tx, k, s, p, count_include_pad=inc)
+            y.backward(torch.tensor(g, dtype=torch.float64))
+            assert close(R.avgpool(x4, k, s, p, inc), y) and close(R.avgpool_grad(g, x4.shape, k, s, p, inc), tx.grad)
+    tx = t(x4)
+    y = tx.mean((2, 3))
+    g = rng.randn(2, 3).astype(np.float32)
+    y.backward(torch.tensor(g, dtype=torch.float64))
+    assert close(R.global_avgpool_grad(g, x4.shape), tx.grad)
+
+    gamma, beta = rng.rand(3).astype(np.float32) + 0.5, rng.randn(3).astype(np.float32)
+    mean, var = rng.randn(3).astype(np.float32), rng.rand(3).astype(np.float32) + 0.1
+    tx, tg, tb2 = t(x4), t(gamma), t(beta)
+    y = F.batch_norm(tx, torch.tensor(mean, dtype=torch.float64), torch.tensor(var, dtype=torch.float64), tg, tb2, False, 0.0, 1e-5)
+    g = rng.randn(*x4.shape).astype(np.float32)
+    y.backward(torch.tensor(g, dtype=torch.float64))
+    assert close(R.batchnorm_inference(x4, gamma, beta, mean, var), y)
+    dx, dg, db = R.batchnorm_inference_grad(x4, gamma, mean, var, g)
+    assert close(dx, tx.grad) and close(dg, tg.grad) and close(db, tb2.grad)
