@@ -154,3 +154,35 @@ def test_resnet_graph_survives_an_onnx_file(tmp_path):
     a = a[0] if isinstance(a, (list, tuple)) else a
     b = b[0] if isinstance(b, (list, tuple)) else b
     assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("use_cpp", [True, False])
+def test_reference_executor_matches_native_executor(use_cpp):
+    """The same ResNet graph on the CPU oracles (numpy / compiled C++) and on the native executor: logits,
+    loss and the gradient of every weight agree."""
+    from eagersgd_b200.graph import ReferenceGraphExecutor
+    torch.manual_seed(4)
+    model = cifar_resnet(8, 1, 10).train()
+    for m in model.modules():                     # give the zero-initialised gammas a value: every path carries gradient
+        if isinstance(m, torch.nn.BatchNorm2d):
+            torch.nn.init.uniform_(m.weight, 0.5, 1.5)
+    g = from_torch_resnet(model)
+    g.add_loss("SoftmaxCrossEntropy", g.outputs[0])
+    x = torch.randn(4, 3, 32, 32)
+    y = torch.randint(0, 10, (4,))
+    net = GraphNetwork(g).train()
+    outs = net(x, label=y)
+    outs[-1].backward()
+    ref = ReferenceGraphExecutor(g, use_cpp=use_cpp)
+    r_outs = ref.inference_and_backprop({g.inputs[0]: x.numpy(), "label": y.numpy()})
+    assert np.allclose(r_outs[0], outs[0].detach().numpy(), rtol=1e-3, atol=1e-3)
+    assert abs(float(r_outs[-1]) - float(outs[-1])) < 1e-3
+    checked = 0
+    for name in g.get_params():
+        p = net.tensor(name)
+        if p.grad is None or name not in ref.gradients:
+            continue
+        a, b = ref.gradients[name], p.grad.numpy()
+        assert np.allclose(a, b, rtol=2e-2, atol=2e-3 * max(1.0, float(np.abs(b).max()))), name
+        checked += 1
+    assert checked >= 20
