@@ -118,7 +118,7 @@ def collate_sequences(seqs: List[np.ndarray], labels: np.ndarray) -> Dict[str, n
     """Left-zero-pad to the longest sequence of the batch (the reference pads on the left too,
     deep500/datasets/ucf101.py:92-109) and return the true lengths."""
     t = max(len(s) for s in seqs)
-    out = np.zeros((len(seqs), t, seqs[0].shape[1]), dtype=seqs[0].dtype)
+    out = np.zeros((len(seqs), t) + tuple(seqs[0].shape[1:]), dtype=seqs[0].dtype)   # frames of any rank
     for i, s in enumerate(seqs):
         out[i, t - len(s):] = s
     return {"x": out, "y": np.asarray(labels), "lengths": np.asarray([len(s) for s in seqs], dtype=np.int64)}

@@ -39,11 +39,15 @@ class LSTMClassifier(nn.Module):
         self.fc.to(dtype)
         return self
 
-    def forward(self, x):
-        """x: [B, T, input_dim] (batch first, left-padded) -> logits [B, classes]."""
+    def hidden_states(self, x):
+        """x: [B, T, input_dim] (batch first, left-padded) -> the top layer's hidden states [T, B, hidden]."""
         h = x.transpose(0, 1).contiguous()                 # [T, B, I]
         for l in range(self.layers):
             h = lstm_layer(h, self.w_ih[l], self.w_hh[l], self.bias[l])
             if self.dropout > 0 and self.training and l < self.layers - 1:
                 h = torch.nn.functional.dropout(h, self.dropout)
-        return ops.linear(h[-1], self.fc.weight, self.fc.bias)
+        return h
+
+    def forward(self, x):
+        """x: [B, T, input_dim] -> logits [B, classes] from the last hidden state."""
+        return ops.linear(self.hidden_states(x)[-1], self.fc.weight, self.fc.bias)

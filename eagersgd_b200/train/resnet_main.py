@@ -55,7 +55,15 @@ def build_data(args, info, group):
     elif args.dataset == "cifar10":
         train, val = load_cifar10(args.data_dir)
     else:
-        raise SystemExit("ImageNet from disk needs a decoded array dataset; use --synthetic here")
+        # <data_dir>/{train,val}/<wnid>/*.JPEG, or the shards build_shards() packs from it
+        from ..data.imagenet import ImageNetFolder, ShardedImageDataset
+        if any(f.startswith("train-") and f.endswith(".npz") for f in os.listdir(args.data_dir)):
+            train = ShardedImageDataset(args.data_dir, "train", seed=args.baseseed)
+            val = ShardedImageDataset(args.data_dir, "val", seed=args.baseseed)
+        else:
+            train = ImageNetFolder(args.data_dir, "train", seed=args.baseseed)
+            val = ImageNetFolder(args.data_dir, "val", seed=args.baseseed)
+        info["train"], info["val"] = len(train), len(val)
     shard = partition(train, group.rank, group.world)   # dataset.take(n // num_workers) in the reference (:94-96)
     return ShuffleSampler(shard, args.batch_size, seed=args.baseseed + 17), OrderedSampler(val, args.batch_size)
 

@@ -61,3 +61,72 @@ def test_synthetic_image_dataset_is_deterministic():
     assert np.array_equal(a["x"], b["x"]) and a["y"] == b["y"]
     batch = ds[np.array([1, 2, 3])]
     assert batch["x"].shape == (3, 3, 8, 8) and batch["y"].shape == (3,)
+
+
+def test_video_loader_follows_the_reference_pipeline(tmp_path):
+    """Left zero-padding to the longest clip, [:max_length:skip] sub-sampling, 1/255 scaling, channels first
+    (deep500/datasets/ucf101.py:92-109), and the UCF101 list files."""
+    import numpy as np
+    from eagersgd_b200.data import BucketSampler, VideoFolderDataset, VideoLoader, read_split, write_synthetic_ucf101
+    root = write_synthetic_ucf101(str(tmp_path / "ucf"), classes=3, clips_per_class=4, frames=(12, 30), size=(16, 24))
+    paths, labels, classes = read_split(root, "trainlist01.txt")
+    assert len(classes) == 3 and len(paths) == len(labels) > 0 and all(p.endswith(".npy") for p in paths)
+    loader = VideoLoader(normalize=False, max_length=25, skip_frames=3)
+    a, b = np.load(paths[0]), np.load(paths[1])
+    batch = loader([paths[0], paths[1]])
+    longest = max(len(a), len(b))
+    expect_t = len(range(0, min(longest, 25), 3))
+    assert batch.shape == (2, expect_t, 3, 16, 24)
+    short, n_short = (0, len(a)) if len(a) < len(b) else (1, len(b))
+    padded = np.concatenate([np.zeros((longest - n_short, 16, 24, 3), np.float32), (a if short == 0 else b).astype(np.float32)])
+    assert np.allclose(batch[short], np.moveaxis(padded[:25:3] / 255.0, -1, -3))
+    ds = VideoFolderDataset(root, "trainlist01.txt", loader)
+    s = BucketSampler(ds, 2, ds.lengths, num_buckets=4, max_length=50, seed=0)
+    got = s()
+    assert got["x"].ndim == 5 and got["x"].shape[0] == 2 and got["x"].shape[2] == 3
+
+
+def test_resnet_lstm_video_model_runs_on_cpu():
+    import torch
+    from eagersgd_b200.models.resnet import cifar_resnet
+    from eagersgd_b200.models.video import ResNetLSTM
+    torch.manual_seed(0)
+    net = cifar_resnet(8, 1, 10)
+    m = ResNetLSTM(5, hidden=16, frame_net=net, feature_dim=net.fc.in_features, frame_chunk=7)
+    x = torch.randn(2, 6, 3, 16, 16)
+    out = m(x)
+    assert out.shape == (2, 5)
+    out.sum().backward()
+    assert m.rnn.w_hh[0].grad is not None and next(net.parameters()).grad is not None
+
+
+def test_imagenet_from_disk_folder_shards_and_preprocessing(tmp_path):
+    """The folder layout and the packed shards give the same images and labels; evaluation pre-processing is the
+    aspect-preserving resize + central crop with the channel means subtracted, training pre-processing a random
+    crop / flip of the right size (official/resnet/imagenet_preprocessing.py)."""
+    import numpy as np
+    from eagersgd_b200.data import (CHANNEL_MEANS, ImageNetFolder, ShardedImageDataset, build_shards, decode_image,
+                                    preprocess_image, random_crop_box, write_synthetic_imagenet)
+    root = write_synthetic_imagenet(str(tmp_path / "inet"), classes=3, per_class=4)
+    val = ImageNetFolder(root, "val")
+    assert len(val) == 3 * 2 and len(val.classes) == 3 and not val.is_training
+    one = val[0]
+    assert one["x"].shape == (3, 224, 224) and one["x"].dtype == np.float32 and one["y"] == 0
+    raw = decode_image(val.files[0])
+    h, w = raw.shape[:2]
+    assert np.allclose(preprocess_image(raw, False), one["x"])
+    assert one["x"].min() >= -max(CHANNEL_MEANS) - 1e-3 and one["x"].max() <= 255.0
+    train = ImageNetFolder(root, "train", seed=3, label_offset=1)
+    b = train[[0, 5, 9]]
+    assert b["x"].shape == (3, 3, 224, 224) and list(b["y"]) == [1, 2, 3]          # 1001-class convention
+    rng = np.random.default_rng(0)
+    for _ in range(50):
+        t, l, ch, cw = random_crop_box(60, 80, rng)
+        assert 0 <= t and 0 <= l and t + ch <= 60 and l + cw <= 80 and 0.74 <= cw / ch <= 1.35 or (ch, cw) == (60, 80)
+    shards = build_shards(root, "val", str(tmp_path / "shards"), shard_size=4)
+    assert len(shards) == 2
+    sv = ShardedImageDataset(str(tmp_path / "shards"), "val")
+    assert len(sv) == len(val) and sorted(sv.labels.tolist()) == sorted(val.labels.tolist())
+    by_label = {int(l): i for i, l in enumerate(sv.labels)}
+    i_sh = by_label[int(val.labels[-1])]
+    assert sv[i_sh]["x"].shape == (3, 224, 224)
