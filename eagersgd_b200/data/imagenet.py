@@ -96,9 +96,12 @@ def list_folder(root: str, split: str) -> Tuple[List[str], np.ndarray, List[str]
 class _ImageDataset(Dataset):
     data_node, label_node = "x", "y"
 
+    num_parallel_calls = 1      # threads that decode and pre-process the images of one batch
+
     def _init_common(self, is_training, size, seed, label_offset):
         self.is_training, self.size, self.label_offset = is_training, size, label_offset
         self.rng = np.random.default_rng(seed)
+        self._pool = None
 
     def _raw(self, i: int):
         raise NotImplementedError
@@ -108,8 +111,17 @@ class _ImageDataset(Dataset):
             return {"x": preprocess_image(decode_image(self._raw(int(index))), self.is_training, self.rng, self.size),
                     "y": self.labels[index] + self.label_offset}
         idx = list(range(*index.indices(len(self)))) if isinstance(index, slice) else list(index)
-        x = np.stack([preprocess_image(decode_image(self._raw(int(i))), self.is_training, self.rng, self.size)
-                      for i in idx])
+        if self.num_parallel_calls > 1:       # like dataset.map(parse_record, num_parallel_calls=n) in the reference
+            if self._pool is None:
+                from concurrent.futures import ThreadPoolExecutor
+                self._pool = ThreadPoolExecutor(self.num_parallel_calls)
+            seeds = self.rng.integers(1 << 62, size=len(idx))
+            x = np.stack(list(self._pool.map(
+                lambda a: preprocess_image(decode_image(self._raw(int(a[0]))), self.is_training,
+                                           np.random.default_rng(int(a[1])), self.size), zip(idx, seeds))))
+        else:
+            x = np.stack([preprocess_image(decode_image(self._raw(int(i))), self.is_training, self.rng, self.size)
+                          for i in idx])
         return {"x": x, "y": self.labels[idx] + self.label_offset}
 
 

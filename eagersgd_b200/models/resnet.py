@@ -30,7 +30,18 @@ IMAGENET_BLOCKS = {
 class BatchNormAct(nn.BatchNorm2d):
     """Batch norm fused with an optional residual add and ReLU (one kernel pass each way)."""
 
+    # Ghost batch norm: statistics over consecutive groups of this many samples instead of the whole batch
+    # (the reference's --virtual_batch_size, official/resnet/resnet_model.py:45-60); None: the whole batch.
+    virtual_batch_size = None
+
     def forward(self, y, relu: bool = True, residual=None, stats=None):  # noqa: D102
+        v = self.virtual_batch_size
+        if v and self.training and y.shape[0] > v:
+            import torch
+            outs = [ops.bn_act(y[i:i + v], self.weight, self.bias, self.running_mean, self.running_var, self.momentum,
+                               relu, None if residual is None else residual[i:i + v], None, True)
+                    for i in range(0, y.shape[0], v)]
+            return torch.cat(outs)
         return ops.bn_act(y, self.weight, self.bias, self.running_mean, self.running_var, self.momentum, relu,
                           residual, stats, self.training)
 

@@ -116,6 +116,60 @@ class ExamplesPerSecondHook:
         return None
 
 
+class ProfilerHook:
+    """Every ``save_steps`` steps, profile one training step and write a Chrome trace
+    (``timeline-<step>.json``) into ``output_dir`` — the reference's ProfilerHook
+    (official/utils/logs/hooks_helper.py:98-110: tf.train.ProfilerHook(save_steps=1000)).
+    Use ``with hook.step(global_step):`` around the training step."""
+
+    def __init__(self, output_dir: str, save_steps: int = 1000, first_step: int = 10):
+        self.dir, self.every, self.first = output_dir, max(int(save_steps), 1), first_step
+        self.written = []
+
+    def step(self, global_step: int):
+        import contextlib
+        if global_step != self.first and (global_step == 0 or global_step % self.every != 0):
+            return contextlib.nullcontext()
+        return self._profiled(global_step)
+
+    def _profiled(self, global_step: int):
+        import contextlib
+        import os
+        import torch
+
+        @contextlib.contextmanager
+        def ctx():
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if torch.cuda.is_available():
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            with torch.profiler.profile(activities=acts) as prof:
+                yield
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+            os.makedirs(self.dir, exist_ok=True)
+            path = os.path.join(self.dir, "timeline-%d.json" % global_step)
+            prof.export_chrome_trace(path)
+            self.written.append(path)
+        return ctx()
+
+
+HOOKS = ("LoggingTensorHook", "ExamplesPerSecondHook", "ProfilerHook", "LoggingMetricHook")
+
+
+def parse_hooks(spec: str):
+    """``--hooks`` value -> the set of hook names (case-insensitive, as hooks_helper.get_train_hooks accepts)."""
+    by_lower = {h.lower(): h for h in HOOKS}
+    out = set()
+    for name in (spec or "").split(","):
+        name = name.strip().lower()
+        if not name:
+            continue
+        if name not in by_lower:
+            raise ValueError("unknown hook %r: choose from %s" % (name, ", ".join(HOOKS)))
+        out.add(by_lower[name])
+    return out
+
+
 class LoggingMetricHook:
     def __init__(self, metric_logger: BaseBenchmarkLogger, every_n_iter: int = 10):
         self.logger, self.every, self.step = metric_logger, every_n_iter, 0

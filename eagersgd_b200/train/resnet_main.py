@@ -15,6 +15,7 @@ between launches (test_scripts_imagenet/synchm.sh).
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import sys
 import time
@@ -23,13 +24,14 @@ import numpy as np
 import torch
 
 from .. import ckpt
-from ..data import OrderedSampler, ShuffleSampler, SyntheticImageDataset, load_cifar10, partition
+from ..data import OrderedSampler, ReplicateBatch, ShuffleSampler, SyntheticImageDataset, load_cifar10, partition
 from ..models.resnet import cifar_resnet, imagenet_resnet
 from ..optim.lars import LARS, poly_rate_schedule
 from ..parallel.group import init as init_group, finalize
 from . import flags as F
 from .imbalance import ConstantRanks, ExponentialDelays, FixedRanksSleep, NoImbalance, RandomRankFactor
-from .logger import (BaseBenchmarkLogger, BenchmarkFileLogger, ExamplesPerSecondHook, benchmark_context,
+from .logger import (BaseBenchmarkLogger, BenchmarkFileLogger, ExamplesPerSecondHook, ProfilerHook, benchmark_context,
+                     parse_hooks,
                      training_log_line)
 from .metrics import topk_accuracy
 from .schedule import cifar10_schedule, imagenet_schedule
@@ -64,6 +66,7 @@ def build_data(args, info, group):
             train = ImageNetFolder(args.data_dir, "train", seed=args.baseseed)
             val = ImageNetFolder(args.data_dir, "val", seed=args.baseseed)
         info["train"], info["val"] = len(train), len(val)
+        train.num_parallel_calls = val.num_parallel_calls = max(int(args.num_parallel_calls), 1)
     shard = partition(train, group.rank, group.world)   # dataset.take(n // num_workers) in the reference (:94-96)
     return ShuffleSampler(shard, args.batch_size, seed=args.baseseed + 17), OrderedSampler(val, args.batch_size)
 
@@ -111,6 +114,15 @@ def main(argv=None):
     group.barrier()
 
     model = build_model(args, info)
+    if args.virtual_batch_size:                  # ghost batch norm (resnet_model.py:45-60)
+        from ..models.resnet import BatchNormAct
+        for m in model.modules():
+            if isinstance(m, BatchNormAct):
+                m.virtual_batch_size = int(args.virtual_batch_size)
+    if args.fine_tune:                           # only the dense layer learns (run loop :404-416)
+        for name, p_ in model.named_parameters():
+            p_.requires_grad_(name.startswith("fc."))
+    hooks = parse_hooks(args.hooks)
     global_batch = args.batch_size * group.world
     steps_per_epoch = max((args.synthetic_train_size or info["train"]) // global_batch, 1)
     if args.dataset == "imagenet":
@@ -129,14 +141,18 @@ def main(argv=None):
     global_step = ckpt.load(step.model, step.opt if hasattr(step.opt, "state_dict") else None, args.model_dir, group.rank)
 
     train_sampler, val_sampler = build_data(args, info, group)
+    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // global_batch, 1)   # a data set read from disk knows its size
     logger = BenchmarkFileLogger(args.benchmark_log_dir) if (
         args.benchmark_logger_type == "BenchmarkFileLogger" and args.benchmark_log_dir) else BaseBenchmarkLogger()
     if group.rank == 0:
         logger.log_run_info("resnet%d" % args.resnet_size, args.dataset, vars(args), args.benchmark_test_id)
     eps_hook = ExamplesPerSecondHook(global_batch, every_n_steps=max(args.train_acc_steps, 1), warm_steps=5,
                                      metric_logger=logger if group.rank == 0 else _Quiet())
+    profiler = ProfilerHook(os.path.join(args.model_dir, str(group.rank))) if "ProfilerHook" in hooks else None
+    replicate = ReplicateBatch(args.batchaug) if args.batchaug and args.batchaug > 1 else None
     injector = None
     t_step = None
+    captured = False
 
     def to_device(batch):
         x = torch.as_tensor(batch["x"]).pin_memory() if device.type == "cuda" else torch.as_tensor(batch["x"])
@@ -161,11 +177,19 @@ def main(argv=None):
                 if injector is not None:
                     injector.apply(group.rank, device)
                 t0 = time.perf_counter()
+                if replicate is not None:            # batch augmentation: every sample several times per step
+                    batch = replicate(batch)
                 x, y = to_device(batch)
-                loss = step.run_device(x, y)
+                if args.cuda_graph and not captured and device.type == "cuda" and args.mode != "ddp" \
+                        and len(y) == args.batch_size * max(args.batchaug, 1):
+                    step.capture(x, y)               # the whole step becomes one graph launch from here on
+                    captured = True
+                with (profiler.step(global_step) if profiler is not None else contextlib.nullcontext()):
+                    loss = step.run_device(x, y)
                 global_step += 1
-                eps_hook.after_step()
-                if global_step % max(args.train_acc_steps, 1) == 0:
+                if "ExamplesPerSecondHook" in hooks:
+                    eps_hook.after_step()
+                if "LoggingTensorHook" in hooks and global_step % max(args.train_acc_steps, 1) == 0:
                     lv = float(loss)        # synchronises: only every train_acc_steps
                     if group.rank == 0:
                         with torch.no_grad():

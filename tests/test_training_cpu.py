@@ -169,3 +169,45 @@ def test_resnet_main_smoke(tmp_path):
     z = np.load(tmp_path / "e" / "model.npz")
     assert "resnet_model/conv2d/kernel" in z and "resnet_model/dense/bias" in z
     assert (tmp_path / "log" / "metric.log").exists()
+
+
+def test_flags_that_change_behaviour(tmp_path):
+    """--hooks (profiler trace), --fine_tune (only the dense layer moves), --virtual_batch_size (ghost batch
+    norm) and --batchaug (replicated batch) are read by the run loop, not just parsed."""
+    import numpy as np
+    import torch
+    from eagersgd_b200.models.resnet import BatchNormAct, cifar_resnet
+    from eagersgd_b200.train.logger import ProfilerHook, parse_hooks
+    assert parse_hooks("profilerhook, ExamplesPerSecondHook") == {"ProfilerHook", "ExamplesPerSecondHook"}
+    with pytest.raises(ValueError):
+        parse_hooks("NoSuchHook")
+    hook = ProfilerHook(str(tmp_path), save_steps=2, first_step=1)
+    for step in range(3):
+        with hook.step(step):
+            torch.randn(8, 8) @ torch.randn(8, 8)
+    assert len(hook.written) == 2 and all(p.endswith(".json") for p in hook.written)
+    # ghost batch norm: statistics per group of 2 samples differ from statistics over the batch of 4
+    torch.manual_seed(0)
+    bn = BatchNormAct(4)
+    x = torch.randn(4, 4, 3, 3) * torch.tensor([1.0, 2.0, 3.0, 4.0]).view(4, 1, 1, 1)
+    full = bn(x, relu=False)
+    bn.virtual_batch_size = 2
+    ghost = bn(x, relu=False)
+    assert not torch.allclose(full, ghost)
+    ref = torch.cat([torch.nn.functional.batch_norm(x[i:i + 2], None, None, bn.weight, bn.bias, True, 0.0, bn.eps)
+                     for i in (0, 2)])
+    assert torch.allclose(ghost, ref, atol=1e-5)
+    # the main program with --fine_tune leaves everything but the dense layer untouched
+    from eagersgd_b200.train import resnet_main
+    before = cifar_resnet(8, 1, 10)
+    torch.manual_seed(0)
+    rc = resnet_main.main(["--dataset", "cifar10", "--synthetic", "--synthetic_train_size", "8", "--resnet_size", "8",
+                           "--batch_size", "4", "--max_train_steps", "2", "--train_epochs", "1", "--dtype", "fp32",
+                           "--model_dir", str(tmp_path / "md"), "--fine_tune", "--batchaug", "2", "--hooks",
+                           "ExamplesPerSecondHook"])
+    assert rc == 0
+    state = torch.load(str(tmp_path / "md" / "0" / "ckpt-2.pt"), weights_only=False)["model"]
+    torch.manual_seed(0)
+    fresh = cifar_resnet(8, 1, 10).state_dict()
+    moved = [k for k in fresh if fresh[k].dtype.is_floating_point and "running" not in k and not torch.equal(fresh[k], state[k])]
+    assert moved and all(k.startswith("fc.") for k in moved), moved
