@@ -16,6 +16,17 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("partial_allreduce_cpu.py", ["--mode", "majority", "--steps", "8"]),
     ("graph_inference.py", []),
     ("lstm_video_classifier.py", ["--steps", "2", "--hidden", "32", "--max-length", "20", "--batch", "4"]),
+    ("ucf101_resnetlstm.py", ["--resnet-size", "8", "--hidden", "16", "--max-steps", "2", "--skip-frames", "4"]),
+    ("train_until.py", ["80", "--max-epochs", "3", "--train-size", "512"]),
+    ("accelegrad.py", ["--epochs", "1", "--train-size", "512"]),
+    ("dataset_latency.py", ["--batches", "2"]),
+    ("mnist_bias.py", []),
+    ("network_inference.py", []),
+    ("network_inference.py", ["reference"]),
+    ("onnxtest.py", ["all"]),
+    ("synthetic_dataset.py", ["--resnet-size", "8", "--size", "32", "--batch", "8", "--steps", "2"]),
+    ("deepbench/gemm_overhead.py", ["--limit", "2", "--reruns", "2"]),
+    ("deepbench/conv_overhead.py", ["--limit", "1", "--reruns", "2"]),
 ])
 def test_sample_runs(script, args):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "samples", script)] + args, capture_output=True, text=True,
