@@ -189,8 +189,29 @@ def load_cuda() -> ctypes.CDLL:
         return _cache["cuda"]
 
 
-if __name__ == "__main__":
-    import sys
+def write_pkgconfig() -> str:
+    """Write ``_lib/pkgconfig/esgd_host.pc`` so that C and C++ programs can compile and link against the host
+    library (operation runtime ``host/oprt.h``, CPU channel) with ``pkg-config --cflags --libs esgd_host`` —
+    what the reference's ``fflib.pc`` does for ``libfflib.so`` (fflib2 CMakeLists.txt:83-96, fflib.pc.in)."""
+    d = os.path.join(LIBDIR, "pkgconfig")
+    os.makedirs(d, exist_ok=True)
+    path = os.path.join(d, "esgd_host.pc")
+    with open(path, "w") as f:
+        f.write("prefix=%s\nlibdir=%s\nincludedir=%s\n\nName: esgd_host\nDescription: eager-SGD host runtime "
+                "(persistent dependency-triggered operations, schedules, CPU partial allreduce)\nVersion: 0.2.0\n"
+                "Libs: -L${libdir} -lesgd_host -Wl,-rpath,${libdir} -pthread\nCflags: -I${includedir}\n"
+                % (os.path.dirname(LIBDIR), LIBDIR, CSRC))
+    return path
 
-    build_all(force="--force" in sys.argv, verbose=True)
+
+def main(argv=None) -> int:
+    import sys
+    argv = sys.argv[1:] if argv is None else argv
+    build_all(force="--force" in argv, verbose=True)
     print("built", HOST_LIB, CUDA_LIB)
+    print("pkg-config file:", write_pkgconfig())
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

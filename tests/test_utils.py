@@ -1,3 +1,4 @@
+import pytest
 import os
 import subprocess
 import sys
@@ -65,3 +66,57 @@ def test_zero_arena_hands_out_aligned_slices_and_falls_back():
             assert all(float(t.abs().sum()) == 0.0 for t in got), sizes
             for t in got:
                 t.fill_(7.0)
+
+
+def test_host_library_links_from_c_through_pkgconfig(tmp_path):
+    """A C program includes host/oprt.h, links libesgd_host through the generated pkg-config file and runs a
+    two-rank allreduce of the operation runtime."""
+    import os
+    import shutil
+    import subprocess
+    from eagersgd_b200 import _build
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    _build.build_host()
+    pc = _build.write_pkgconfig()
+    text = open(pc).read()
+    flags = {}
+    for line in text.splitlines():
+        if "=" in line and ":" not in line.split("=")[0]:
+            k, v = line.split("=", 1)
+            flags[k] = v
+    expand = lambda s: s.replace("${libdir}", flags["libdir"]).replace("${includedir}", flags["includedir"])
+    cflags = expand([l for l in text.splitlines() if l.startswith("Cflags:")][0].split(":", 1)[1]).split()
+    libs = expand([l for l in text.splitlines() if l.startswith("Libs:")][0].split(":", 1)[1]).split()
+    src = tmp_path / "prog.c"
+    src.write_text("""
+#include <stdio.h>
+#include <pthread.h>
+#include "host/oprt.h"
+static rt_world* w;
+static int ok[2];
+static void* body(void* arg) {
+  int r = (int)(long)arg;
+  rt_rank* c = rt_world_rank(w, r);
+  int snd[4] = {r + 1, 2, 3, 4}, rcv[4] = {0, 0, 0, 0};
+  rt_buf bs = rt_buffer_create(c, snd, 4, RT_INT32), br = rt_buffer_create(c, rcv, 4, RT_INT32);
+  rt_sched s = rt_allreduce(c, bs, br, 1, RT_SUM);
+  rt_schedule_post(c, s);
+  ok[r] = rt_schedule_wait(c, s, 10.0) == RT_SUCCESS && rcv[0] == 3 && rcv[3] == 8;
+  rt_schedule_delete(c, s);
+  return 0;
+}
+int main(void) {
+  pthread_t t[2];
+  w = rt_world_create(2);
+  for (long r = 0; r < 2; ++r) pthread_create(&t[r], 0, body, (void*)r);
+  for (int r = 0; r < 2; ++r) pthread_join(t[r], 0);
+  rt_world_destroy(w);
+  printf(ok[0] && ok[1] ? "PASSED\\n" : "FAILED\\n");
+  return !(ok[0] && ok[1]);
+}
+""")
+    exe = str(tmp_path / "prog")
+    subprocess.run(["gcc", "-O1", str(src), "-o", exe] + cflags + libs, check=True)
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0 and "PASSED" in out.stdout, out.stdout + out.stderr
