@@ -13,6 +13,8 @@
 // blocks, partial sums meet in shared memory and then in fp32 global atomics.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <stdint.h>
 #include "launch_count.cuh"
 
@@ -110,7 +112,8 @@ __global__ void bn_finalize_kernel(const float* sum, const float* sqsum, const f
 
 // Threads keep a fixed group of 8 channels and walk over rows, so the per-channel
 // coefficients live in registers for the whole kernel.
-__global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __restrict__ y,
+template <int kMinBlocks>
+__global__ void __launch_bounds__(256, kMinBlocks) bn_apply_kernel(const __nv_bfloat16* __restrict__ y,
                                                        const __nv_bfloat16* __restrict__ res,
                                                        __nv_bfloat16* __restrict__ z, const float* __restrict__ scale,
                                                        const float* __restrict__ shift, int64_t M, int C, int relu) {
@@ -157,7 +160,8 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const __nv_bfloat16* __re
   }
 }
 
-__global__ void __launch_bounds__(256, 2)
+template <int kMinBlocks>
+__global__ void __launch_bounds__(256, kMinBlocks)
 bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
                      const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
                      const float* __restrict__ invstd, const float* __restrict__ fscale,
@@ -237,7 +241,8 @@ bn_bwd_reduce_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* 
 
 // dy = a*g + b*y + c per channel, with a = gamma*invstd, b = -gamma*invstd^2*dgamma/M,
 // c = gamma*invstd*(mean*invstd*dgamma - dbeta)/M held in registers.
-__global__ void __launch_bounds__(256, 2)
+template <int kMinBlocks>
+__global__ void __launch_bounds__(256, kMinBlocks)
 bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ z,
                     const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean,
                     const float* __restrict__ invstd, const float* __restrict__ gamma,
@@ -314,6 +319,18 @@ constexpr int64_t kReduceGridCap = 148 * 2;
 
 }  // namespace
 
+// Resident blocks per SM the three bandwidth-bound kernels are compiled for (a register budget): chosen by
+// measurement, overridable for experiments with ESGD_BN_OCC="apply,reduce,bwd_apply" (each 2, 3 or 4).
+static int occupancy_choice(int which) {
+  static int choice[3] = {0, 0, 0};
+  if (choice[0] == 0) {
+    int c[3] = {2, 2, 2};
+    if (const char* e = getenv("ESGD_BN_OCC")) sscanf(e, "%d,%d,%d", &c[0], &c[1], &c[2]);
+    for (int i = 2; i >= 0; --i) choice[i] = c[i] >= 2 && c[i] <= 4 ? c[i] : 2;
+  }
+  return choice[which];
+}
+
 extern "C" {
 
 // sum / sqsum must be zeroed by the caller (they accumulate).
@@ -343,8 +360,14 @@ int esgd_bn_apply(const void* y, const void* residual, void* z, const float* sca
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
-  bn_apply_kernel<<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, (const __nv_bfloat16*)residual, (__nv_bfloat16*)z, scale, shift, M, C, relu);
+#define ESGD_BN_APPLY(MB)                                                                          \
+  bn_apply_kernel<MB><<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(             \
+      (const __nv_bfloat16*)y, (const __nv_bfloat16*)residual, (__nv_bfloat16*)z, scale, shift, M, C, relu)
+  switch (occupancy_choice(0)) {
+    case 3: ESGD_BN_APPLY(3); break;
+    case 4: ESGD_BN_APPLY(4); break;
+    default: ESGD_BN_APPLY(2); break;
+  }
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
@@ -358,9 +381,14 @@ int esgd_bn_bwd_reduce(const void* dz, const void* z, const void* y, const float
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
-  bn_bwd_reduce_kernel<<<blocks_for(M, rows_par * 16, kReduceGridCap), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, fscale, fshift, M, C,
-      relu, dbeta, dgamma);
+#define ESGD_BN_REDUCE(MB)                                                                                     \
+  bn_bwd_reduce_kernel<MB><<<blocks_for(M, rows_par * 16, kReduceGridCap), 256, 0, (cudaStream_t)stream>>>(   \
+      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, fscale, fshift, M, C, \
+      relu, dbeta, dgamma)
+  switch (occupancy_choice(1)) {
+    case 3: ESGD_BN_REDUCE(3); break;
+    default: ESGD_BN_REDUCE(2); break;
+  }
   esgd::count_launch();
   return (int)cudaGetLastError();
 }
@@ -371,9 +399,15 @@ int esgd_bn_bwd_apply(const void* dz, const void* z, const void* y, const float*
   if (C % 8) return -1;
   int g = C / 8 < 256 ? C / 8 : 256;
   int rows_par = 256 / g;
-  bn_bwd_apply_kernel<<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, gamma, dbeta,
-      dgamma, fscale, fshift, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, M, C, relu, 1.0f / (float)M);
+#define ESGD_BN_BWD_APPLY(MB)                                                                              \
+  bn_bwd_apply_kernel<MB><<<blocks_for(M, rows_par * 8), 256, 0, (cudaStream_t)stream>>>(                   \
+      (const __nv_bfloat16*)dz, (const __nv_bfloat16*)z, (const __nv_bfloat16*)y, mean, invstd, gamma, dbeta, \
+      dgamma, fscale, fshift, (__nv_bfloat16*)dy, (__nv_bfloat16*)dres, M, C, relu, 1.0f / (float)M)
+  switch (occupancy_choice(2)) {
+    case 3: ESGD_BN_BWD_APPLY(3); break;
+    case 4: ESGD_BN_BWD_APPLY(4); break;
+    default: ESGD_BN_BWD_APPLY(2); break;
+  }
   esgd::count_launch();
   return (int)cudaGetLastError();
 }

@@ -25,7 +25,10 @@ namespace {
 
 constexpr double kDefaultWaitSeconds = 600.0;   // what "no timeout" means: ten minutes, then RT_TIMEOUT
 
-size_t dtype_size(int dt) { return (dt == RT_INT32 || dt == RT_FLOAT) ? 4 : 8; }
+size_t dtype_size(int dt) { return dt == RT_CHAR ? 1 : (dt == RT_INT32 || dt == RT_FLOAT) ? 4 : 8; }
+
+// Shadow-tagged messages live in a tag space of their own.
+int wire_tag(int tag, int options) { return (options & RT_SHADOW_TAG) ? (tag | 0x40000000) : tag; }
 
 enum OpType { T_NOP, T_CALLBACK, T_COMP, T_SEND, T_RECV };
 
@@ -149,6 +152,7 @@ void run_comp(rt_rank* c, Op& op) {
   switch (A.dtype) {
     case RT_INT32: reduce_typed((const int32_t*)A.data(), (const int32_t*)B.data(), (int32_t*)O.data(), n, op.oper); break;
     case RT_INT64: reduce_typed((const int64_t*)A.data(), (const int64_t*)B.data(), (int64_t*)O.data(), n, op.oper); break;
+    case RT_CHAR: reduce_typed((const signed char*)A.data(), (const signed char*)B.data(), (signed char*)O.data(), n, op.oper); break;
     case RT_FLOAT: reduce_typed((const float*)A.data(), (const float*)B.data(), (float*)O.data(), n, op.oper); break;
     default: reduce_typed((const double*)A.data(), (const double*)B.data(), (double*)O.data(), n, op.oper); break;
   }
@@ -255,7 +259,7 @@ void execute(rt_rank* c, rt_op id, std::unique_lock<std::mutex>& lk) {
       m.data.assign((uint8_t*)b.data(), (uint8_t*)b.data() + (size_t)b.count * dtype_size(b.dtype));
       {
         std::lock_guard<std::mutex> g(c->world->mail_mu);
-        c->world->mail[std::make_tuple(c->id, op.peer, op.tag)].push_back(std::move(m));
+        c->world->mail[std::make_tuple(c->id, op.peer, wire_tag(op.tag, op.options))].push_back(std::move(m));
       }
       rt_rank* dst = c->world->ranks[op.peer].get();
       dst->work_cv.notify_all();
@@ -277,7 +281,7 @@ bool poll_recvs(rt_rank* c) {
     bool got = false;
     {
       std::lock_guard<std::mutex> g(c->world->mail_mu);
-      auto it = c->world->mail.find(std::make_tuple(op.peer, c->id, op.tag));
+      auto it = c->world->mail.find(std::make_tuple(op.peer, c->id, wire_tag(op.tag, op.options)));
       if (it != c->world->mail.end() && !it->second.empty()) {
         m = std::move(it->second.front());
         it->second.pop_front();
@@ -512,6 +516,10 @@ int rt_op_cancel(rt_rank* c, rt_op id) {
   std::lock_guard<std::mutex> g(c->mu);
   if (id < 0 || id >= (rt_op)c->ops.size() || !c->ops[id]) return RT_ERROR;
   Op& op = *c->ops[id];
+  if (op.options & RT_OP_COMPLETE_BEFORE_CANCELLING) {   // what has been posted runs to completion
+    op.dep_left = op.num_parents;
+    return RT_SUCCESS;
+  }
   for (size_t i = 0; i < c->posted.size();)
     if (c->posted[i] == id) c->posted.erase(c->posted.begin() + i); else ++i;
   for (size_t i = 0; i < c->pending_recvs.size();)

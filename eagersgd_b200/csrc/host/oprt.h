@@ -26,7 +26,7 @@ extern "C" {
 #define RT_TIMEOUT (-2)
 
 /* datatypes and operators (ff.h:21-41); every operator is implemented */
-enum { RT_INT32 = 0, RT_INT64 = 1, RT_FLOAT = 2, RT_DOUBLE = 3 };
+enum { RT_INT32 = 0, RT_INT64 = 1, RT_FLOAT = 2, RT_DOUBLE = 3, RT_CHAR = 4 };
 enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUSTOM0 = 16 };
 
 /* option bits */
@@ -38,6 +38,14 @@ enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUST
 #define RT_DEP_IGNORE_VERSION 0x10   /* every completion of the first op counts (what rt_op_hb uses) */
 #define RT_DEP_NO_AUTOPOST 0x20      /* the edge never posts the second op; it is posted by hand */
 #define RT_DEP_CONSTRAINED 0x40      /* passes a completion on only after its constraining edge has (rt_dep_set_parent) */
+/* more operation options (ff.h:44-57) */
+#define RT_SHADOW_TAG 0x100          /* send / recv: a second tag space, so that control tokens never match data */
+#define RT_OP_COMPLETE_BEFORE_CANCELLING 0x200   /* rt_op_cancel lets a posted instance finish instead of withdrawing it */
+#define RT_COMP_DEST_ATOMIC 0x400    /* compute op: the destination is updated atomically with respect to other
+                                        compute ops of the rank.  Always true here (one progress thread per rank
+                                        runs them one at a time); the bit is accepted for source compatibility. */
+/* Buffers are always handles into the rank's table (the reference's FFBUFFER_IDX); a handle made around user memory
+ * is its FFBUFFER_PTR, and every collective takes handles, so user-managed buffers (FFCOLL_BUFFERS) are the rule. */
 #define RT_INPLACE ((int64_t)-2)
 #define RT_NONE ((int64_t)-1)
 

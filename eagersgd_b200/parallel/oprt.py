@@ -10,12 +10,13 @@ import numpy as np
 
 from .. import _build
 
-INT32, INT64, FLOAT, DOUBLE = 0, 1, 2, 3
+INT32, INT64, FLOAT, DOUBLE, CHAR = 0, 1, 2, 3, 4
+SHADOW_TAG, COMPLETE_BEFORE_CANCELLING, COMP_DEST_ATOMIC = 0x100, 0x200, 0x400
 SUM, PROD, MAX, MIN, IDENTITY = 0, 1, 2, 3, 4
 DEP_AND, DEP_OR, DEP_FIRST, NON_PERSISTENT = 0, 1, 2, 4
 INPLACE, NONE = -2, -1
 COMPLETED, SUCCESS, ERROR, TIMEOUT = 1, 0, -1, -2
-_DT = {np.dtype("int32"): INT32, np.dtype("int64"): INT64, np.dtype("float32"): FLOAT, np.dtype("float64"): DOUBLE}
+_DT = {np.dtype("int8"): CHAR, np.dtype("int32"): INT32, np.dtype("int64"): INT64, np.dtype("float32"): FLOAT, np.dtype("float64"): DOUBLE}
 
 CALLBACK = C.CFUNCTYPE(None, C.c_int64, C.c_void_p)
 OPERATOR = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int)

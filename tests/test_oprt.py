@@ -419,3 +419,30 @@ def test_wait_without_timeout_is_still_bounded():
         a = rk.nop()
         rk.post(a)
         assert rk.wait(a, 0.0) == R.SUCCESS
+
+
+def test_shadow_tags_char_buffers_and_complete_before_cancelling():
+    """A shadow-tagged message never matches a receive with the plain tag of the same number; int8 buffers
+    reduce; an operation created with COMPLETE_BEFORE_CANCELLING finishes what was posted when cancelled."""
+    with R.World(2) as w:
+        a, b = w.ranks
+        data = np.array([1, 2, 3, 4], dtype=np.int8)
+        ctrl = np.array([9, 9, 9, 9], dtype=np.int8)
+        got_data, got_ctrl = np.zeros(4, np.int8), np.zeros(4, np.int8)
+        a.post(a.send(a.buffer(ctrl), 1, 5, R.SHADOW_TAG))       # control token first, same tag number
+        a.post(a.send(a.buffer(data), 1, 5))
+        r_data = b.recv(b.buffer(got_data), 0, 5)
+        r_ctrl = b.recv(b.buffer(got_ctrl), 0, 5, R.SHADOW_TAG)
+        b.post(r_data)
+        b.post(r_ctrl)
+        assert b.wait(r_data, 5.0) == R.SUCCESS and b.wait(r_ctrl, 5.0) == R.SUCCESS
+        assert got_data.tolist() == [1, 2, 3, 4] and got_ctrl.tolist() == [9, 9, 9, 9]
+        x, y, z = np.array([1, -2, 3], np.int8), np.array([10, 20, 30], np.int8), np.zeros(3, np.int8)
+        c = a.comp(a.buffer(x), a.buffer(y), a.buffer(z), R.SUM, R.COMP_DEST_ATOMIC)
+        a.post(c)
+        assert a.wait(c, 5.0) == R.SUCCESS and z.tolist() == [11, 18, 33]
+        hits = []
+        keep = a.callback(lambda op: hits.append(1), R.COMPLETE_BEFORE_CANCELLING)
+        a.post(keep)
+        a.cancel(keep)
+        assert a.wait(keep, 5.0) == R.SUCCESS and hits == [1]
