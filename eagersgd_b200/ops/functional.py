@@ -13,6 +13,8 @@ from typing import Optional
 
 import contextlib
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -295,10 +297,18 @@ class _ConvKxK(torch.autograd.Function):
     def forward(ctx, x, w, stride, pad, want_stats):
         n, cin, h, wd = x.shape
         cout, _, r, s = w.shape
-        x2d = nhwc_2d(x)
         w_cl = w.contiguous(memory_format=torch.channels_last)        # [Cout, R, S, Cin] in memory
+        # Narrow layers (16 / 32 input channels): the kernel's K blocks are 64 channels wide, so the input and
+        # the filters are zero-padded to 64 channels here; the padded input is what backward needs too.
+        pin = (-cin) % 64
+        if pin:
+            x = _pad_channels(x, pin)
+            w_f = F.pad(w_cl, (0, 0, 0, 0, 0, pin)).contiguous(memory_format=torch.channels_last)
+        else:
+            w_f = w_cl
+        x2d = nhwc_2d(x)
         stats = zeros_f32((2, cout), x.device) if want_stats else None
-        y2d, ho, wo = _conv_native(x2d, w_cl, n, h, wd, cin, cout, r, s, stride, pad, stats)
+        y2d, ho, wo = _conv_native(x2d, w_f, n, h, wd, cin + pin, cout, r, s, stride, pad, stats)
         ctx.save_for_backward(x, w_cl)
         ctx.cfg = (stride, pad)
         y = from_2d(y2d, n, ho, wo)
@@ -309,12 +319,17 @@ class _ConvKxK(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, *unused):
-        x, w = ctx.saved_tensors
+        x, w = ctx.saved_tensors             # x carries the forward pass's channel padding, w does not
         stride, pad = ctx.cfg
-        n, cin, h, wd = x.shape
-        cout, _, r, s = w.shape
+        n, cin_x, h, wd = x.shape
+        cout, cin, r, s = w.shape
         dx = dw = None
         dy_cl = dy.contiguous(memory_format=torch.channels_last)
+        pout = (-cout) % 64
+        if pout:        # the output channels are the reduction dimension of both gradients: pad them with zeros
+            dy_cl = _pad_channels(dy_cl, pout)
+            w = F.pad(w, (0, 0, 0, 0, 0, 0, 0, pout)).contiguous(memory_format=torch.channels_last)
+            cout += pout
         if ctx.needs_input_grad[0]:
             if stride == 1 and cout % 64 == 0 and cin % 8 == 0:
                 # dx = conv(dy, rot180(w) with in/out channels swapped), padding R-1-pad
@@ -325,9 +340,10 @@ class _ConvKxK(torch.autograd.Function):
             elif stride == 2 and r == 3 and s == 3 and pad == 1 and h % 2 == 0 and wd % 2 == 0 and cout % 64 == 0:
                 dx = _dgrad_stride2(dy_cl, w, n, h, wd, cin, cout)
             else:
-                dx = torch.nn.grad.conv2d_input(x.shape, w, dy_cl, stride=stride, padding=pad)
+                dx = torch.nn.grad.conv2d_input((n, cin, h, wd), w, dy_cl, stride=stride, padding=pad)
         if ctx.needs_input_grad[1]:
             from .gemm import error_flag
+            cin_w, cin = cin, cin_x            # the weight gradient is taken against the padded input
             dw32 = zeros_f32((cout, r, s, cin), x.device)                               # [Cout][R][S][Cin]
             rc = -100
             if stride == 1:      # shared input boxes, taps as shifted views (returns -100 outside its range)
@@ -340,8 +356,21 @@ class _ConvKxK(torch.autograd.Function):
                 _ck(_lib().esgd_conv2d_wgrad(nhwc_2d(x).data_ptr(), nhwc_2d(dy_cl).data_ptr(), dw32.data_ptr(), n, h,
                                              wd, cin, cout, r, s, stride, pad, error_flag(x.device).data_ptr(),
                                              _stream(x)), "conv2d weight gradient")
+            if pout or cin_w != cin:
+                dw32 = dw32[:cout - pout, :, :, :cin_w]
             dw = dw32.to(w.dtype).permute(0, 3, 1, 2)
         return dx, dw, None, None, None
+
+
+# Narrow convolutions on the tensor-core path by channel padding (ESGD_SMALL_CHANNELS=library keeps them on
+# PyTorch's convolution instead).
+_SMALL_CHANNELS_NATIVE = os.environ.get("ESGD_SMALL_CHANNELS", "native") != "library"
+
+
+def _pad_channels(x: torch.Tensor, extra: int) -> torch.Tensor:
+    if extra == 0:
+        return x
+    return F.pad(x, (0, 0, 0, 0, 0, extra)).contiguous(memory_format=torch.channels_last)
 
 
 class _Subsample2(torch.autograd.Function):
@@ -395,6 +424,11 @@ def conv2d(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, 
     if k > 1 and native(x) and x.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and stride in (1, 2):
         out = _ConvKxK.apply(x, w, stride, padding, want_stats)
         return out if want_stats else (out, None)
+    if k > 1 and native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and stride in (1, 2) and \
+            _SMALL_CHANNELS_NATIVE:
+        # narrow layers (the 16- and 32-channel stages of the CIFAR ResNets): channel-padded inside the operator
+        out = _ConvKxK.apply(x, w, stride, padding, want_stats)
+        return out if want_stats else (out, None)
     return F.conv2d(x, w, None, stride, padding), None
 
 
@@ -420,6 +454,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -
     """Dense layer; fp32 logits out of bf16 operands on the native path."""
     if native(x) and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
         return _Linear.apply(x.contiguous(), w, b)
+    if native(x) and x.shape[1] % 8 == 0 and _SMALL_CHANNELS_NATIVE:
+        # a class count that is not a multiple of 8 (10 CIFAR classes, 101 video classes): zero rows are added
+        # to the weight so that the tensor-core GEMM can take it, and cut off the logits again
+        extra = (-w.shape[0]) % 8
+        wp = F.pad(w, (0, 0, 0, extra))
+        bp = F.pad(b, (0, extra)) if b is not None else None
+        return _Linear.apply(x.contiguous(), wp, bp)[:, :w.shape[0]]
     return F.linear(x, w, b)
 
 

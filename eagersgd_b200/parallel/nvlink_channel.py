@@ -28,6 +28,8 @@ TWO_SHOT_MIN = 1 << 16
 # Elements from which a round with every rank on time is reduced inside the NVSwitch (multimem), when the
 # arenas have a multicast mapping.
 MULTICAST_MIN = 1 << 12
+GUARD_BYTES = 256
+GUARD_VALUE = 0xA5
 _FLOAT_DTYPES = (torch.float32, torch.bfloat16)
 
 
@@ -46,12 +48,32 @@ class ArenaLayout:
         if count % 8:
             raise ValueError("channel element count must be a multiple of 8")
         esz = 2 if slot_dtype == torch.bfloat16 else 4
+        # [control | guard | slot 0 | guard | slot 1 | guard | shard buffer | guard | running sum | guard]: the
+        # guards hold a fixed pattern that no kernel ever writes; check_canaries() finds an overrun of a
+        # neighbouring region (the debugging aid that stands in for a memory checker on shared GPUs)
+        self.guards = []
+        off = _align(int(N.cuda().esgd_dev_ctl_bytes()))
+
+        def guard():
+            nonlocal off
+            self.guards.append(off)
+            off += GUARD_BYTES
+
         self.ctl = 0
-        self.slot0 = _align(int(N.cuda().esgd_dev_ctl_bytes()))
-        self.slot1 = self.slot0 + _align(count * esz)
-        self.red = self.slot1 + _align(count * esz)
-        self.rsum = self.red + _align(count * esz)
-        self.total = self.rsum + _align(count * 4)
+        guard()
+        self.slot0 = off
+        off += _align(count * esz)
+        guard()
+        self.slot1 = off
+        off += _align(count * esz)
+        guard()
+        self.red = off
+        off += _align(count * esz)
+        guard()
+        self.rsum = off
+        off += _align(count * 4)
+        guard()
+        self.total = off
 
 
 class Arena:
@@ -211,6 +233,8 @@ class NvlinkChannel:
         N.check_cuda(self.lib.esgd_channel_configure(self._dch.data_ptr(), C.byref(d), stream.cuda_stream),
                      "channel configuration")
         self._ctl_host = (C.c_ubyte * int(self.lib.esgd_dev_ctl_bytes()))()
+        for g in self.layout.guards:     # this rank's own arena; peers paint theirs
+            device_view(self.bases[self.rank] + g, GUARD_BYTES, torch.uint8, device).fill_(GUARD_VALUE)
 
     @property
     def dev_ptr(self) -> int:
@@ -237,6 +261,18 @@ class NvlinkChannel:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         N.check_cuda(self.lib.esgd_set_hyper(self.hyper.data_ptr(), lr, momentum, weight_decay, int(nesterov),
                                              grad_scale, s.cuda_stream), "hyper-parameter update")
+
+    def check_canaries(self) -> None:
+        """Raise if any guard region between the sections of this rank's arena no longer holds its pattern: some
+        kernel, local or on a peer, wrote past the end (or before the start) of a slot, the shard buffer or the
+        running sum.  Synchronises with the device."""
+        torch.cuda.synchronize(self.device)
+        for k, g in enumerate(self.layout.guards):
+            v = device_view(self.bases[self.rank] + g, GUARD_BYTES, torch.uint8, self.device)
+            if not bool((v == GUARD_VALUE).all()):
+                bad = int((v != GUARD_VALUE).nonzero()[0])
+                raise RuntimeError("arena guard %d of rank %d was overwritten at byte %d: a kernel wrote outside its "
+                                   "region" % (k, self.rank, bad))
 
     def applied(self) -> bool:
         """Whether the newest step applied anything (it took part in a round or collected missed ones).

@@ -145,3 +145,48 @@ def test_weight_gradient_with_shared_boxes(n, cin, h, w, cout, k, monkeypatch):
     scale = wr.grad.abs().max().item()
     assert (dw_shared.float() - wr.grad).abs().max().item() < 2e-2 * scale
     assert (dw_shared.float() - dw_tap.float()).abs().max().item() < 2e-2 * scale
+
+
+# ---- small shapes, every geometry the kernels accept, against the compiled C++ oracle ----------------------------
+def _small_cases():
+    cases = []
+    for n in (1, 2):
+        for (h, w) in ((5, 5), (8, 9), (9, 6)):
+            for (cin, cout) in ((64, 64), (128, 64), (64, 72)):
+                for (k, stride, pad) in ((3, 1, 1), (3, 1, 0), (3, 2, 1), (1, 1, 0), (1, 2, 0), (5, 1, 2), (3, 1, 2)):
+                    if (h + 2 * pad - k) // stride + 1 < 1 or (w + 2 * pad - k) // stride + 1 < 1:
+                        continue
+                    cases.append((n, cin, h, w, cout, k, stride, pad))
+    # the narrow layers of the CIFAR ResNets (channel-padded around the kernel)
+    for (cin, cout, stride) in ((16, 16, 1), (16, 32, 2), (32, 32, 1), (32, 64, 2)):
+        cases.append((2, cin, 8, 8, cout, 3, stride, 1))
+        cases.append((1, cin, 7, 9, cout, 3, stride, 1))
+    return cases
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", _small_cases())
+def test_small_shapes_forward_dgrad_wgrad_against_cpp_oracle(n, cin, h, w, cout, k, stride, pad):
+    """Forward, data gradient and weight gradient of small, odd-sized problems, element by element against the
+    plain-loop C++ convolution (ref/cpp/ops.cpp) on the same bf16-rounded operands: every element within 1 % of
+    the tensor's largest magnitude.  A dropped filter tap at an image border, a wrong halo or a mis-strided
+    gradient shows up here as an error of the size of the values themselves."""
+    from eagersgd_b200.ops import functional as ops
+    from eagersgd_b200.ops.gemm import check_error
+    from eagersgd_b200.ref import cpp_ops as R
+    torch.manual_seed(n * 1000 + cin + 7 * h + w + k + stride)
+    x = _cl(torch.randn(n, cin, h, w, device=DEV)).to(torch.bfloat16).requires_grad_()
+    wt = _cl(torch.randn(cout, cin, k, k, device=DEV) * (1.0 / (k * cin ** 0.5))).to(torch.bfloat16).requires_grad_()
+    y, _ = ops.conv2d(x, wt, stride, pad)
+    g = _cl(torch.randn_like(y.float())).to(torch.bfloat16)
+    y.backward(g)
+    torch.cuda.synchronize()
+    check_error(x.device)
+    xn, wn, gn = x.detach().float().cpu().numpy(), wt.detach().float().cpu().numpy(), g.float().cpu().numpy()
+    y_ref = R.conv2d(xn, wn, stride, pad)
+    dx_ref, dw_ref = R.conv2d_grads(xn, wn, gn, stride, pad)
+    for name, got, ref in (("y", y, y_ref), ("dx", x.grad, dx_ref), ("dw", wt.grad, dw_ref)):
+        got = got.detach().float().cpu().numpy()
+        assert got.shape == ref.shape, name
+        tol = 1e-2 * max(float(abs(ref).max()), 1e-6)
+        worst = float(abs(got - ref).max())
+        assert worst <= tol, (name, worst, tol)

@@ -27,7 +27,7 @@ def test_conv1x1_forward_backward(n, c, h, w, cout):
     assert torch.allclose(stats[0], yr.sum((0, 2, 3)), rtol=1e-2, atol=0.5)
     assert torch.allclose(stats[1], (yr * yr).sum((0, 2, 3)), rtol=1e-2, atol=0.5)
     assert torch.allclose(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
-    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=0.1 * wr.grad.abs().max().item())
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=2e-2 * wr.grad.abs().max().item())
 
 
 @pytest.mark.parametrize("relu,residual", [(True, False), (False, False), (True, True)])
@@ -226,7 +226,7 @@ def test_conv1x1_tapped_input_adds_shortcut_gradient_in_the_gemm():
     F.conv2d(xr, wr).backward(g.float())
     ref = xr.grad + g2.float()
     assert torch.allclose(x.grad.float(), ref, rtol=2e-2, atol=3e-2)
-    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=0.1 * wr.grad.abs().max().item())
+    assert torch.allclose(wt.grad.float(), wr.grad, rtol=2e-2, atol=2e-2 * wr.grad.abs().max().item())
     # an unused tap costs nothing and changes nothing
     x2 = x.detach().clone().requires_grad_()
     y2, _, _ = ops.conv2d(x2, wt.detach(), 1, 0, want_stats=False, tap_input=True)
@@ -255,3 +255,28 @@ def test_identity_bottleneck_block_matches_reference_ops():
     assert F.cosine_similarity(x1.grad.float().flatten(), x2.grad.float().flatten(), dim=0).item() > 0.995
     rel = (x1.grad.float() - x2.grad.float()).norm() / x2.grad.float().norm()
     assert rel.item() < 0.05, rel.item()
+
+
+def test_cifar_resnet_step_launches_no_library_convolution_or_gemm():
+    """The ResNet-32 training step, narrow 16- and 32-channel layers included, runs its convolutions and
+    dense layer on this package's kernels: no cuDNN, cuBLAS or CUTLASS kernel shows up in the profile."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.models.resnet import cifar_resnet
+    from eagersgd_b200.train.step import TrainStep
+    torch.manual_seed(0)
+    step = TrainStep(cifar_resnet(32, 1, 10), es.Group(), mode="solo", lr=0.05)
+    x = _cl(torch.randn(32, 3, 32, 32, device=DEV)).to(torch.bfloat16)
+    y = torch.randint(0, 10, (32,), device=DEV)
+    l0 = float(step.run_device(x, y))
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            loss = step.run_device(x, y)
+        torch.cuda.synchronize()
+    names = {e.key for e in prof.key_averages() if getattr(e, "device_time_total", 0) > 0 or "kernel" in e.key.lower()}
+    library = [n for n in names if any(t in n.lower() for t in ("cudnn", "cublas", "cutlass", "xmma", "implicit_convolve",
+                                                               "sgemm", "gemv", "wgrad", "dgrad"))
+               and "conv_wgrad" not in n and "esgd" not in n and "anonymous namespace" not in n]
+    assert not library, library
+    assert any("conv_kernel" in n or "gemm_kernel" in n for n in names), sorted(names)[:20]
+    assert float(loss) < l0          # and it learns the batch
+    step.close()

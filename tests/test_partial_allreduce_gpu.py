@@ -408,3 +408,27 @@ def test_zero_copy_publishing_matches_the_staged_path():
         outs.append(res)
         arena.free()
     assert all(torch.equal(a, b) for a, b in zip(*outs))
+
+
+def test_arena_guards_stay_intact_and_catch_an_overrun():
+    """The guard regions between the sections of an arena survive real traffic (one-shot, two-shot, drains) and
+    report a write that strays into them."""
+    from eagersgd_b200.parallel.nvlink_channel import EmulatedWorld, device_view
+    world, count = 4, 8 * 77
+    w = EmulatedWorld(world, count, _dev(), slot_dtype=torch.bfloat16, grad_dtype=torch.bfloat16, mode="solo", limiter=3,
+                      average="world", timeout_s=2.0, grace_us=0.0, two_shot_min=0)
+    rng = random.Random(1)
+    try:
+        for k in range(12):
+            for r in range(world):
+                w.grads[r].copy_(torch.randn(count, device=_dev()).to(torch.bfloat16))
+            w.step(delays_us=[rng.choice([0, 0, 50, 300]) for _ in range(world)])
+        w.step(flush=True)
+        for c in w.channels:
+            c.check_canaries()
+        ch = w.channels[2]
+        device_view(ch.bases[2] + ch.layout.slot1 - 3, 1, torch.uint8, _dev()).fill_(0)    # one byte before slot 1
+        with pytest.raises(RuntimeError, match="guard 1"):
+            ch.check_canaries()
+    finally:
+        w.close()
