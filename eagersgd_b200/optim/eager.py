@@ -94,6 +94,9 @@ class EagerOptimizer:
         can_fuse = (self.on_gpu and type(optimizer) is torch.optim.SGD and
                     all(g.get("dampening", 0) == 0 and not g.get("maximize", False) for g in optimizer.param_groups))
         self.fused = can_fuse if fused is None else (fused and can_fuse)
+        # LARS is the other optimizer the reference wraps (resnet_run_loop_solo_imagenet_300.py:366-374): on
+        # GPUs its step runs as two kernels over the buckets' flat buffers instead of a Python loop over tensors
+        self.lars = bool(self.on_gpu and type(optimizer).__name__ == "LARS" and not self.fused)
         if slot_dtype is None:
             slot_dtype = torch.bfloat16 if params[0].dtype == torch.bfloat16 else torch.float32
         self.slot_dtype = slot_dtype
@@ -170,7 +173,7 @@ class EagerOptimizer:
             b.grad_flat = torch.zeros(b.count, dtype=dt, device=self.device)
             b.hyper = torch.zeros(HYPER_LEN, dtype=torch.float32, device=self.device)
             b.masters = None
-            if self.fused or low:
+            if self.fused or low or self.lars:
                 # fp32 master weights; the model computes on the bucket's own (low-precision) storage
                 b.w32 = torch.zeros(b.count, dtype=torch.float32, device=self.device)
                 if low:
@@ -185,6 +188,11 @@ class EagerOptimizer:
             if self.fused:
                 b.mom = torch.zeros(b.count, dtype=torch.float32, device=self.device)
                 kw = dict(w32=b.w32, mom=b.mom, w16=b.w16, clear_grad=True)
+            elif self.lars:
+                b.g32 = torch.zeros(b.count, dtype=torch.float32, device=self.device)
+                b.mom = torch.zeros(b.count, dtype=torch.float32, device=self.device)
+                self._lars_tables(b)
+                kw = dict(out=b.g32, clear_grad=True)
             elif low:
                 # a wrapped optimizer steps the fp32 masters with the averaged gradient in fp32; the
                 # low-precision weights are refreshed from them after every step
@@ -219,6 +227,37 @@ class EagerOptimizer:
                 pg["params"] = [master_of.get(id(p), p) for p in pg["params"]]
         torch.cuda.synchronize(self.device)
         g.barrier()
+
+    def _lars_tables(self, b: _Bucket):
+        """Chunk records (start, length, tensor) of one bucket for the fused LARS kernels: chunks never straddle
+        a tensor; tensors the optimizer does not adapt (biases, batch-norm scale / shift) carry a negative index."""
+        import ctypes as C
+        lib = N.cuda()
+        lib.esgd_lars_step.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_float, C.c_float,
+                                       C.c_float, C.c_void_p]
+        chunk = int(lib.esgd_lars_chunk_elems())
+        rec = []
+        for t, (p, off) in enumerate(zip(b.params, b.offsets)):
+            padded = (p.numel() + _PAD - 1) // _PAD * _PAD
+            for s0 in range(0, padded, chunk):
+                rec.append((off + s0, min(chunk, padded - s0), (-1 - t) if self.optimizer.skip(p) else t))
+        arr = np.zeros(len(rec), dtype=np.dtype([("start", "<i8"), ("len", "<i4"), ("tensor", "<i4")]))
+        for i, r in enumerate(rec):
+            arr[i] = r
+        b.lars_chunks = torch.from_numpy(arr.view(np.uint8).copy()).to(self.device)
+        b.lars_num_chunks = len(rec)
+        b.lars_sq = torch.zeros(2 * len(b.params), dtype=torch.float32, device=self.device)
+
+    def _lars_step(self):
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        for b in self.buckets:
+            pg = self.optimizer.param_groups[b.group_index]
+            N.check_cuda(N.cuda().esgd_lars_step(
+                b.lars_chunks.data_ptr(), b.lars_num_chunks, len(b.params), b.lars_sq.data_ptr(), b.g32.data_ptr(), 0,
+                float(self.grad_scale), b.w32.data_ptr(), b.mom.data_ptr(),
+                b.w16.data_ptr() if b.w16 is not None else None, float(pg["lr"]), float(pg["momentum"]),
+                float(pg["weight_decay"]), float(pg["eeta"]), float(pg["epsilon"]), s), "fused LARS step")
 
     def _refresh_hyper(self, b: _Bucket, force: bool = False):
         pg = self.optimizer.param_groups[b.group_index]
@@ -332,6 +371,8 @@ class EagerOptimizer:
         if not torch.cuda.is_current_stream_capturing():
             if not any(b.channel.applied() for b in self.buckets):
                 return
+        if self.lars:
+            return self._lars_step()
         if self.grad_scale != 1.0:
             for b in self.buckets:
                 (b.g32 if b.masters is not None else b.grad_flat).mul_(self.grad_scale)
@@ -410,7 +451,7 @@ class EagerOptimizer:
     def state_dict(self) -> dict:
         sd = {"inner": self.optimizer.state_dict(), "steps": self.steps, "mode": self.mode,
               "limiter": self.limiter, "seed": self.seed}
-        if self.fused:
+        if self.fused or self.lars:
             sd["fused_master"] = [b.w32.detach().cpu() for b in self.buckets]
             sd["fused_momentum"] = [b.mom.detach().cpu() for b in self.buckets]
         return sd
@@ -418,7 +459,7 @@ class EagerOptimizer:
     def load_state_dict(self, sd: dict):
         self.optimizer.load_state_dict(sd["inner"])
         self.steps = sd.get("steps", 0)
-        if self.fused and "fused_master" in sd:
+        if (self.fused or self.lars) and "fused_master" in sd:
             for b, w, m in zip(self.buckets, sd["fused_master"], sd["fused_momentum"]):
                 b.w32.copy_(w)
                 b.mom.copy_(m)
@@ -437,7 +478,7 @@ class EagerOptimizer:
         if self.on_gpu:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         for b in self.buckets:
-            if self.fused:
+            if self.fused or self.lars:
                 g.bcast(b.w32)
                 g.bcast(b.mom)
                 if b.w16 is not None:

@@ -280,3 +280,32 @@ def test_cifar_resnet_step_launches_no_library_convolution_or_gemm():
     assert any("conv_kernel" in n or "gemm_kernel" in n for n in names), sorted(names)[:20]
     assert float(loss) < l0          # and it learns the batch
     step.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_lars_matches_the_per_tensor_reference(dtype):
+    """Two launches for all tensors: per-tensor trust ratios, momentum on the scaled gradient, fp32 master
+    weights — against the per-tensor PyTorch implementation of the same rule on fp32 copies."""
+    from eagersgd_b200.optim.lars import LARS, FusedLARS
+    torch.manual_seed(0)
+    shapes = [(64, 32, 3, 3), (64,), (10, 64), (10,), (300, 77)]
+    ref_params = [torch.nn.Parameter(torch.randn(s, device=DEV) * 0.1) for s in shapes]
+    fused_params = [torch.nn.Parameter(p.detach().clone().to(dtype)) for p in ref_params]
+    if dtype == torch.bfloat16:
+        for p, q in zip(ref_params, fused_params):
+            p.data.copy_(q.detach().float())
+    ref = LARS(ref_params, lr=0.5, momentum=0.9, weight_decay=1e-3, eeta=0.01)
+    fused = FusedLARS(fused_params, lr=0.5, momentum=0.9, weight_decay=1e-3, eeta=0.01)
+    for k in range(5):
+        fused.zero_grad()
+        for p, q in zip(ref_params, fused_params):
+            g = torch.randn_like(p).to(dtype)
+            p.grad = g.float()
+            q.grad.copy_(g)
+        ref.step()
+        fused.step()
+    torch.cuda.synchronize()
+    for p, q, off in zip(ref_params, fused_params, fused.offsets):
+        master = fused.w32[off:off + p.numel()].view(p.shape)
+        assert torch.allclose(master, p.detach(), rtol=2e-4, atol=2e-6), (p.shape, (master - p).abs().max())
+        assert torch.equal(q.detach().float(), master.to(dtype).float())
