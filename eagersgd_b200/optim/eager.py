@@ -19,6 +19,7 @@ import torch
 
 from ..parallel import _native as N
 from ..parallel.group import Group, init as init_group
+from ..parallel.nvlink_channel import TWO_SHOT_MIN
 
 _PAD = 64  # elements; keeps every parameter 128-byte aligned inside a bucket
 
@@ -64,7 +65,7 @@ class EagerOptimizer:
                  limiter: int = 32, seed: int = 6545343, bucket_mb: float = 25.0,
                  average: str = "contributors", include_stale: bool = True, fused: Optional[bool] = None,
                  slot_dtype: Optional[torch.dtype] = None, overlap: bool = True, timeout_s: float = 30.0,
-                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = 1 << 16,
+                 grace_us: float = 50.0, max_blocks: int = 592, two_shot_min: Optional[int] = TWO_SHOT_MIN,
                  accumulate: bool = False, adaptive_grace: bool = True):
         self.optimizer = optimizer
         self.two_shot_min = two_shot_min   # bucket elements from which a round is reduced in two shots (None: never)

@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from . import _native as N
 from .group import init as init_group, finalize
-from .nvlink_channel import NvlinkChannel, create_arenas
+from .nvlink_channel import NvlinkChannel, TWO_SHOT_MIN, create_arenas
 
 
 def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_shot=False, grace_us=50.0,
@@ -49,7 +49,7 @@ def run_case(group, nbytes, dtype, mode, late, late_ms, iters, seed, fused, one_
         ch = NvlinkChannel(count, group.rank, group.world, bases, dev, None if zero_copy else grad, slot_dtype=dtype,
                            mode=mode, limiter=-1,
                            average="world", timeout_s=20.0, grace_us=grace_us,
-                           two_shot_min=None if one_shot else 1 << 16, mc_base=arena.mc_base, **kw)
+                           two_shot_min=None if one_shot else TWO_SHOT_MIN, mc_base=arena.mc_base, **kw)
     buf = grad.clone()
     times, phases = [], {}
     for it in range(iters + 3):

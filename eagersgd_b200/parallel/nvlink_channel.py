@@ -24,10 +24,13 @@ HYPER_LEN = 8  # lr, momentum, weight_decay, nesterov, grad_scale, pad...
 # Elements from which a round with several participants and at least three contributors is reduced in two
 # shots (reduce-scatter by peer loads, then every participant pulls the other shares): below it the extra
 # flag round trip costs more than the bytes it saves.
-TWO_SHOT_MIN = 1 << 16
+TWO_SHOT_MIN = 1 << 20
 # Elements from which a round with every rank on time is reduced inside the NVSwitch (multimem), when the
 # arenas have a multicast mapping.
 MULTICAST_MIN = 1 << 12
+# Bytes of a channel above which the multicast broadcast is not used: stores through the switch into eight arenas
+# ran at 340 GB/s, so from here peer loads are the faster gather (8 GPUs, 256 MiB: 776 against 899 us).
+MULTICAST_MAX_BYTES = 64 << 20
 GUARD_BYTES = 256
 GUARD_VALUE = 0xA5
 _FLOAT_DTYPES = (torch.float32, torch.bfloat16)
@@ -208,9 +211,11 @@ class NvlinkChannel:
             d.slot1[j] = bases[j] + L.slot1
             d.red[j] = bases[j] + L.red if two_shot_min is not None else None
             d.rsum[j] = bases[j] + L.rsum
+        if mc_base and count * (2 if slot_dtype == torch.bfloat16 else 4) > MULTICAST_MAX_BYTES:
+            mc_base = 0
         if mc_base and two_shot_min is not None and world > 1:
             d.mc_slot0, d.mc_slot1, d.mc_red = mc_base + L.slot0, mc_base + L.slot1, mc_base + L.red
-            d.mc_min = int(mc_min)
+            d.mc_min = max(int(mc_min), int(two_shot_min))      # never where one shot is the faster form
         self.multicast = bool(mc_base and two_shot_min is not None and world > 1)
         d.two_shot_min = int(two_shot_min) if two_shot_min is not None else 0
         d.accumulate, d.adaptive_grace, d.clear_grad = int(accumulate), int(adaptive_grace), int(clear_grad)

@@ -246,7 +246,7 @@ def _multicast_round(rank, world, slot_bf16):
     grad = torch.zeros(count, device=dev)
     out = torch.zeros(count, device=dev)
     ch = NvlinkChannel(count, group.rank, group.world, bases, dev, grad, slot_dtype=sdt, mode="sync", limiter=-1,
-                       average="world", out=out, timeout_s=5.0, mc_base=arena.mc_base)
+                       average="world", out=out, timeout_s=5.0, mc_base=arena.mc_base, two_shot_min=1 << 16)
     torch.manual_seed(200 + rank)
     err, same = 0.0, True
     for k in range(4):
@@ -340,3 +340,83 @@ def test_eager_training_converges_like_synchronous_sgd():
     assert final["sync"] < 0.7 * curves["sync"][0], final            # the task is learnable and was learnt
     for mode in ("solo", "majority"):
         assert final[mode] <= 1.10 * final["sync"] + 0.02, final
+
+
+def _peer_collectives(rank, world):
+    """Every classic collective on this package's kernels, against closed forms; then the same calls through
+    the Group API with the native path switched on."""
+    os.environ["ESGD_NATIVE_COLLECTIVES"] = "1"
+    es, group = _setup(rank, world)
+    dev = group.device
+    pc = group.peer_collectives(stage_mb=1.0)
+    n = 300_001                                    # odd byte counts and more than one stage of 1 MiB (fp32: 1.2 MB)
+    res = {}
+    t = torch.full((n,), float(rank), device=dev) + torch.arange(n, device=dev) % 7
+    ref = (torch.arange(n, device=dev) % 7).float()
+    # broadcast from the last rank
+    b = t.clone()
+    pc.bcast(b, world - 1)
+    res["bcast"] = bool(torch.equal(b, ref + (world - 1)))
+    # all-gather and gather (uint8 payload of odd length)
+    u = (torch.arange(1001, device=dev) % 251).to(torch.uint8) + rank
+    ag = pc.allgather(u)
+    res["allgather"] = all(bool(torch.equal(ag[j], (torch.arange(1001, device=dev) % 251).to(torch.uint8) + j))
+                           for j in range(world))
+    g = pc.gather(t, 1 % world)
+    res["gather"] = (g is None) if rank != 1 % world else all(bool(torch.equal(g[j], ref + j)) for j in range(world))
+    # all-reduce: bits equal on every rank and equal to the rank-ordered fp32 sum
+    a = (torch.randn(1 << 18, device=dev, generator=torch.Generator(dev).manual_seed(rank)))
+    parts = pc.allgather(a)
+    expect = torch.zeros_like(a)
+    for j in range(world):
+        expect += parts[j]
+    s = a.clone()
+    pc.allreduce(s)
+    res["allreduce_f32"] = bool(torch.equal(s, expect))
+    h = a.to(torch.bfloat16)
+    hp = pc.allgather(h)
+    eh = torch.zeros_like(a)
+    for j in range(world):
+        eh += hp[j].float()
+    pc.allreduce(h)
+    res["allreduce_bf16"] = bool(torch.equal(h, eh.to(torch.bfloat16)))
+    # ring of sends: rank r sends to r+1, receives from r-1 (even ranks send first)
+    x = torch.full((4097,), float(rank), device=dev)
+    y = torch.empty_like(x)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    pc.send(x, nxt)                                # a send returns once the stage holds the data: no deadlock
+    pc.recv(y, prv)
+    res["sendrecv"] = bool(torch.all(y == float(prv)))
+    # whichever rank sends first: all send one word to rank 0
+    if rank == 0:
+        seen = sorted(int(pc.recv_any(y[:4]) ) for _ in range(world - 1))
+        res["recv_any"] = seen == list(range(1, world))
+    else:
+        pc.send(x[:4], 0)
+        res["recv_any"] = True
+    # ring-neighbour sum
+    z = torch.full((1024,), float(rank + 1), device=dev)
+    pc.reduce_from_neighbours(z)
+    res["neighbours"] = bool(torch.all(z == float(rank + 1 + prv + 1 + nxt + 1)))
+    pc.barrier()
+    pc.check()
+    # the Group API on the native path
+    w = torch.full((64,), float(rank), device=dev)
+    group.bcast(w, 0)
+    v = torch.ones(64, device=dev)
+    group.allreduce(v)
+    res["group_api"] = bool(torch.all(w == 0)) and bool(torch.all(v == world))
+    torch.cuda.synchronize()
+    import eagersgd_b200.parallel._native as N
+    res["launches"] = N.launch_count() > 20
+    group.barrier()
+    es.finalize()
+    return res
+
+
+def test_classic_collectives_on_peer_memory():
+    world = _world()
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    for r, res in enumerate(run_ranks(_peer_collectives, world, timeout=240)):
+        assert all(res.values()), (r, res)

@@ -460,3 +460,55 @@ def test_wrapped_lars_runs_as_fused_kernels_and_matches_the_python_optimizer():
         assert torch.allclose(p, q, rtol=1e-4, atol=1e-6), (p - q).abs().max()
     assert es.parallel._native.launch_count() - n0 == 5 * len(o.buckets) * 4      # 2 collective + 2 LARS launches per bucket
     o.close()
+
+
+@pytest.mark.parametrize("world", [2, 3, 5, 8])
+def test_classic_collectives_emulated_on_one_gpu(world):
+    """Broadcast, gather, all-gather, all-reduce, send / receive, ring sum and barrier of the peer-memory
+    collectives, all ranks on one GPU in one cooperative launch per operation, against closed forms."""
+    from eagersgd_b200.parallel.peer_collectives import EmulatedCollectives
+    dev = _dev()
+    ec = EmulatedCollectives(world, dev)
+    n = 10_007
+    base = torch.arange(n, device=dev) % 13
+    ts = [(base + r).float() for r in range(world)]
+    ec.bcast(ts, world - 1)
+    assert all(torch.equal(t, (base + world - 1).float()) for t in ts)
+    us = [((torch.arange(1001, device=dev) % 251) + r).to(torch.uint8) for r in range(world)]
+    outs = ec.allgather(us)
+    for r in range(world):
+        for j in range(world):
+            assert torch.equal(outs[r][j], us[j])
+    g = ec.gather(us, 1)
+    assert all(torch.equal(g[j], us[j]) for j in range(world))
+    torch.manual_seed(world)
+    for dt in (torch.float32, torch.bfloat16):
+        xs = [torch.randn(4096, device=dev).to(dt) for _ in range(world)]
+        expect = torch.zeros(4096, device=dev)
+        for x in xs:
+            expect += x.float()
+        ec.allreduce(xs)
+        assert all(torch.equal(x, expect.to(dt)) for x in xs)
+    a, b = torch.full((333,), 7.0, device=dev), torch.zeros(333, device=dev)
+    ec.send_recv(a, world - 1, b, 0)
+    assert torch.equal(a, b)
+    if world >= 3:
+        zs = [torch.full((64,), float(r + 1), device=dev) for r in range(world)]
+        ec.neighbours(zs)
+        for r in range(world):
+            assert torch.all(zs[r] == float((r + 1) + ((r - 1) % world + 1) + ((r + 1) % world + 1)))
+    ec.barrier()
+    assert ec.status() == [0] * world
+
+
+def test_collective_wait_for_a_silent_rank_runs_out_with_a_status():
+    """A receive from a rank that never sends: the bounded wait ends, the status says which wait it was, the
+    destination is untouched and the context keeps working."""
+    from eagersgd_b200.parallel.peer_collectives import EmulatedCollectives, RED_NONE
+    dev = _dev()
+    ec = EmulatedCollectives(2, dev, timeout_s=0.2)
+    b = torch.full((16,), 3.0, device=dev)
+    ops = [(0, 0, 0, 0, 0, 0, RED_NONE, -1), (0, 1, 64, 0, b.data_ptr(), 0, RED_NONE, -1)]   # rank 1 reads, nobody writes
+    ec._run(ops)
+    assert ec.status() == [0, 2] and torch.all(b == 3.0)
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
