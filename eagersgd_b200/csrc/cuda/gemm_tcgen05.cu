@@ -29,6 +29,7 @@ struct GemmProblem {
   int res_kb;         // > 0: all k-blocks of B for the CTA's column range stay in shared memory
   float* c_f32;       // fp32 output (direct modes)
   int ldc;
+  int chained;        // launched with programmatic stream serialization: wait for the previous kernel in the kernel
 
   struct Tile { int kb0, kb1, n0, m0; };
 
@@ -94,8 +95,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_kernel(const __grid_const
     tma_prefetch_desc(&prob.tmA);
     tma_prefetch_desc(&prob.tmB);
   }
+  if (prob.chained) {
+    // This grid was allowed to start while the kernel before it in the stream was still running (its launch
+    // latency is hidden that way): nothing of that kernel's output may be touched before this returns.  The
+    // kernel after this one may be scheduled now; it waits for this grid in the same way.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   run(prob, ep);
 }
+
+// Set by callers that issue a chain of dependent launches (the LSTM time loop) around their calls.
+thread_local int g_chained = 0;
 
 int sm_count() {
   static int n = 0;
@@ -179,8 +190,22 @@ int launch(const GemmArgs& g, Epilogue ep, cudaStream_t stream) {
     const int total = p.m_tiles * p.n_tiles * p.splits;
     grid = total < sms ? total : sms;
   }
-  gemm_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
+  p.chained = g_chained;
   esgd::count_launch();
+  if (p.chained) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<BN>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_kernel<P>, p, ep);
+  }
+  gemm_kernel<P><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(p, ep);
   return (int)cudaGetLastError();
 }
 
@@ -221,5 +246,8 @@ int esgd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, i
   if (BN == 128) return launch_major<128>(a_mn, b_mn, g, ep, s);
   return launch_major<256>(a_mn, b_mn, g, ep, s);
 }
+
+// Launches of this thread from now on are links of a chain of dependent kernels (1) or ordinary launches (0).
+void esgd_gemm_set_chained(int on) { g_chained = on; }
 
 }  // extern "C"

@@ -187,7 +187,7 @@ def test_bottleneck_block_matches_reference_ops():
         assert c > 0.98, (n1, c)
 
 
-@pytest.mark.parametrize("T,B,I,H", [(5, 16, 64, 128), (12, 8, 256, 256)])
+@pytest.mark.parametrize("T,B,I,H", [(5, 16, 64, 128), (12, 8, 256, 256), (6, 16, 512, 1024), (3, 40, 64, 128)])
 def test_lstm_layer_forward_backward(T, B, I, H):
     from eagersgd_b200.ops.lstm import lstm_layer, lstm_layer_reference
     torch.manual_seed(7)
