@@ -98,7 +98,7 @@ lstm_cell_bwd_kernel(const __nv_bfloat16* __restrict__ gates,   // [B, 4H] saved
 // while everything else is [B, H] (unit fastest): a block takes kJT hidden units x all B batch rows, moves its part
 // of the transposed product through shared memory with contiguous accesses (and zeroes it behind itself for the next
 // step's split-K sums), then works unit-fastest.  B <= kMaxTileB.
-constexpr int kJT = 32;
+constexpr int kJT = 16;
 constexpr int kMaxTileB = 32;
 
 __global__ void __launch_bounds__(256)

@@ -218,6 +218,30 @@ def bench_update(shape, iters):
     return dict(op="publish+reduce+fused_sgd(world=1)", count=count, ms=ms, gbs=byts / ms / 1e6)
 
 
+def bench_lars(shape, iters):
+    """Fused LARS (per-tensor norms kernel + trust-ratio update kernel) over the parameter tensors of ResNet-50,
+    bf16 parameters with fp32 masters, against the per-tensor PyTorch LARS on fp32 copies."""
+    from ..models.resnet import imagenet_resnet
+    from ..optim.lars import LARS, FusedLARS
+    (depth,) = shape
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = imagenet_resnet(depth).to(dev)
+    ref = [torch.nn.Parameter(p.detach().clone()) for p in model.parameters()]
+    for p in model.parameters():
+        p.data = p.data.to(torch.bfloat16)
+    params = list(model.parameters())
+    fused = FusedLARS(params, lr=0.1, momentum=0.9, weight_decay=1e-4, eeta=0.001)
+    plain = LARS(ref, lr=0.1, momentum=0.9, weight_decay=1e-4, eeta=0.001)
+    for p, q in zip(params, ref):
+        p.grad.normal_() if p.grad is not None else None
+        q.grad = torch.randn_like(q)
+    count = sum(p.numel() for p in params)
+    ms = timeit(lambda: fused.step(), iters, graph=False)
+    ms_lib = timeit(lambda: plain.step(), iters, graph=False)
+    byts = count * (2 + 4 + 2 + 4 + 4 + 4 + 4 + 2.0)    # norms: grad + w32; update: grad, w32 / momentum read + write, bf16 copy
+    return dict(op="fused_lars", tensors=len(params), count=count, ms=ms, gbs=byts / ms / 1e6, library_ms=ms_lib)
+
+
 SUITE = [("gemm", (8192, 8192, 8192)), ("gemm", (4096, 4096, 4096)), ("gemm", (802816, 64, 256)),
          ("gemm", (802816, 256, 64)), ("gemm", (200704, 512, 128)), ("gemm", (50176, 1024, 256)),
          ("gemm", (12544, 2048, 512)), ("conv", (256, 64, 56, 56, 64, 3, 1)), ("conv", (256, 128, 28, 28, 128, 3, 1)),
@@ -243,6 +267,8 @@ def run(op, shape, iters, backward=False, residual=False):
         r = bench_lstm(shape, iters)
     elif op == "update":
         r = bench_update(shape, iters)
+    elif op == "lars":
+        r = bench_lars(shape, iters)
     else:
         raise SystemExit("unknown op " + op)
     p = peaks()

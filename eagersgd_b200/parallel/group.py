@@ -75,7 +75,7 @@ class Group:
     def _native(self, t: torch.Tensor, summed: bool = False) -> bool:
         """Whether a collective on ``t`` runs on this package's kernels: CUDA tensors of a multi-rank group, unless
         ``ESGD_NATIVE_COLLECTIVES=0``; sums only for float32 / bfloat16 in 16-byte units."""
-        if self.world == 1 or not t.is_cuda or not t.is_contiguous() or os.environ.get("ESGD_NATIVE_COLLECTIVES", "0") == "0":
+        if self.world == 1 or not t.is_cuda or not t.is_contiguous() or os.environ.get("ESGD_NATIVE_COLLECTIVES", "1") == "0":
             return False
         if summed and (t.dtype not in (torch.float32, torch.bfloat16) or (t.numel() * t.element_size()) % 16
                        or t.data_ptr() % 16):
