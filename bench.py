@@ -246,7 +246,7 @@ def run_arm(args, group, host_batches, batch, classes, impl, mode, inject, steps
                 d += e
         return min(d, 5.0 * base_step_s)
 
-    def timed(fn, batches):
+    def timed(fn, batches, stream_api=False):
         sampler = ClockSampler(dev.index)
         launches0 = N.launch_count()
         sync_all()
@@ -254,12 +254,24 @@ def run_arm(args, group, host_batches, batch, classes, impl, mode, inject, steps
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         last, total_delay = None, 0.0
-        for i in range(steps):
-            d = delay_for_step()
-            if d > 0:
-                step.inject_delay(d)
-                total_delay += d
-            last = fn(*batches[(warm + i) % nb])
+        if stream_api:
+            # the public end-to-end loop: pinned host batches in, one python float per step out; it overlaps the
+            # next batch's host-to-device copy and the previous loss's read-back with the running step
+            def before(i):
+                nonlocal total_delay
+                d = delay_for_step()
+                if d > 0:
+                    step.inject_delay(d)
+                    total_delay += d
+            for last in fn((batches[(warm + i) % nb] for i in range(steps)), before_step=before):
+                pass
+        else:
+            for i in range(steps):
+                d = delay_for_step()
+                if d > 0:
+                    step.inject_delay(d)
+                    total_delay += d
+                last = fn(*batches[(warm + i) % nb])
         e1.record()
         torch.cuda.synchronize()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -281,7 +293,7 @@ def run_arm(args, group, host_batches, batch, classes, impl, mode, inject, steps
            "undisturbed_ms_per_step": float(own.item()) * 1e3, "base_step_s": base_step_s,
            "injected_ms_per_step": injected[0], "clocks": clocks, "gpu_launches": launches, "e2e": None}
     if with_e2e:
-        ms_e2e, _, _, last_loss = timed(step.run_host, host_batches)
+        ms_e2e, _, _, last_loss = timed(step.run_host_stream, host_batches, stream_api=True)
         out["e2e"] = {"value": world * batch * steps / (ms_e2e / 1e3), "ms_per_step": ms_e2e / steps,
                       "h2d_bytes_per_step": int(sum(x.numel() * 2 + y.numel() * 8 for x, y in host_batches) / nb),
                       "d2h_bytes_per_step": 4, "last_loss": last_loss, "injected_ms_per_step": injected[1]}

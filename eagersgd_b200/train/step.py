@@ -145,6 +145,83 @@ class TrainStep:
         self._ybuf.copy_(y_host, non_blocking=True)
         return float(self.run_device(self._xbuf, self._ybuf).item())
 
+    def run_host_stream(self, batches, before_step=None):
+        """End to end over a stream of pinned host batches, pipelined: yields every step's loss as a python float, in
+        order.  The host-to-device copy of batch k+1 runs on a copy stream while step k computes (two staging buffers
+        on the device), and the loss of step k is read back (asynchronous copy into pinned memory) only after step
+        k+1 has been launched, so neither transfer leaves the GPU idle.  ``before_step(k)`` is called right before
+        step k is launched (the benchmark injects its delays there).  On a CPU device this is ``run_host`` in a loop."""
+        if self.device.type != "cuda":
+            for k, (xh, yh) in enumerate(batches):
+                if before_step is not None:
+                    before_step(k)
+                yield self.run_host(xh, yh)
+            return
+        dev = self.device
+        main = torch.cuda.current_stream(dev)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(device=dev)
+            self._stage = [None, None]
+            self._loss_pin = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        copy = self._copy_stream
+        h2d_done = [torch.cuda.Event() for _ in range(2)]
+        stage_free = [torch.cuda.Event() for _ in range(2)]
+        loss_done = [torch.cuda.Event() for _ in range(2)]
+
+        def prefetch(k, xh, yh):
+            b = k % 2
+            st = self._stage[b]
+            if st is None or st[0].shape != xh.shape or st[0].dtype != xh.dtype or st[1].shape != yh.shape:
+                # From the copy stream's pool, and marked as used by the compute stream: memory that the compute
+                # stream has freed but whose kernels are still queued must not be written by an early copy, and a
+                # staging buffer dropped here must not be handed out again before the step that reads it is done.
+                with torch.cuda.stream(copy):
+                    st = self._stage[b] = (torch.empty_like(xh, device=dev), torch.empty_like(yh, device=dev))
+                for t in st:
+                    t.record_stream(main)
+            if k >= 2:
+                copy.wait_event(stage_free[b])           # the step that read this buffer two batches ago is past it
+            else:
+                copy.wait_stream(main)
+            with torch.cuda.stream(copy):
+                st[0].copy_(xh, non_blocking=True)
+                st[1].copy_(yh, non_blocking=True)
+                h2d_done[b].record(copy)
+
+        it = iter(batches)
+        nxt = next(it, None)
+        if nxt is None:
+            return
+        prefetch(0, *nxt)
+        k = 0
+        while nxt is not None:
+            b = k % 2
+            main.wait_event(h2d_done[b])
+            x, y = self._stage[b]
+            if self._graph is not None:                  # the graph reads fixed buffers: one device copy into them
+                self._gx.copy_(x, non_blocking=True)
+                self._gy.copy_(y, non_blocking=True)
+                stage_free[b].record(main)
+                x, y = self._gx, self._gy
+            nxt = next(it, None)
+            if nxt is not None and self._graph is not None:
+                prefetch(k + 1, *nxt)
+            if before_step is not None:
+                before_step(k)
+            loss = self.run_device(x, y)
+            if self._graph is None:
+                stage_free[b].record(main)
+                if nxt is not None:
+                    prefetch(k + 1, *nxt)
+            self._loss_pin[b].copy_(loss.detach().reshape(1).float(), non_blocking=True)
+            loss_done[b].record(main)
+            if k > 0:
+                loss_done[1 - b].synchronize()
+                yield float(self._loss_pin[1 - b][0])
+            k += 1
+        loss_done[(k - 1) % 2].synchronize()
+        yield float(self._loss_pin[(k - 1) % 2][0])
+
     def set_lr(self, lr: float) -> None:
         for g in self.opt.param_groups:
             g["lr"] = lr

@@ -309,3 +309,55 @@ def test_fused_lars_matches_the_per_tensor_reference(dtype):
         master = fused.w32[off:off + p.numel()].view(p.shape)
         assert torch.allclose(master, p.detach(), rtol=2e-4, atol=2e-6), (p.shape, (master - p).abs().max())
         assert torch.equal(q.detach().float(), master.to(dtype).float())
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_pipelined_host_loop_gives_the_losses_of_the_plain_one(graph):
+    """``run_host_stream`` (next batch copied while the step runs, loss read one step late) returns, in order,
+    the losses that ``run_host`` returns for the same batches from the same start."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.models.resnet import cifar_resnet
+    from eagersgd_b200.train.step import TrainStep
+    batches = []
+    g = torch.Generator().manual_seed(5)
+    for _ in range(6):
+        x = torch.randn(16, 32, 32, 3, generator=g).permute(0, 3, 1, 2).to(torch.bfloat16).pin_memory()
+        batches.append((x, torch.randint(0, 10, (16,), generator=g).pin_memory()))
+    out = []
+    for stream in (False, True):
+        torch.manual_seed(1)
+        step = TrainStep(cifar_resnet(8, 1, 10), es.Group(), mode="solo", lr=0.05)
+        if graph:
+            step.capture(batches[0][0].to(DEV), batches[0][1].to(DEV), warmup=0)
+        if stream:
+            out.append(list(step.run_host_stream(iter(batches))))
+        else:
+            out.append([step.run_host(x, y) for x, y in batches])
+        step.close()
+    assert len(out[1]) == len(batches)
+    for a, b in zip(*out):
+        assert abs(a - b) <= 2e-2 * max(1.0, abs(a)), out      # fp32 atomics in the weight gradients: not bit-equal
+    assert out[0][-1] != out[0][0]
+
+
+def test_pipelined_host_loop_with_batches_of_changing_shape():
+    """Variable-length sequence batches make the loop re-allocate its staging buffers: the early copy of the next
+    batch must never land in memory that queued kernels of the running step still use."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.models import create_model
+    from eagersgd_b200.train.step import TrainStep
+    g = torch.Generator().manual_seed(3)
+    batches = []
+    for _ in range(8):
+        T = int(torch.randint(5, 60, (1,), generator=g))
+        batches.append((torch.randn(16, T, 64, generator=g).to(torch.bfloat16).pin_memory(),
+                        torch.randint(0, 7, (16,), generator=g).pin_memory()))
+    out = []
+    for stream in (True, False):
+        torch.manual_seed(0)
+        step = TrainStep(create_model("lstm", input_dim=64, hidden=128, layers=2, num_classes=7), es.Group(), mode="solo",
+                         lr=0.05)
+        out.append(list(step.run_host_stream(iter(batches))) if stream else [step.run_host(x, y) for x, y in batches])
+        step.close()
+    for a, b in zip(*out):
+        assert a == a and abs(a - b) <= 1e-2 * max(1.0, abs(a)), out
