@@ -339,6 +339,20 @@ class _ConvKxK(torch.autograd.Function):
                 dx = from_2d(dx2d, n, h, wd)
             elif stride == 2 and r == 3 and s == 3 and pad == 1 and h % 2 == 0 and wd % 2 == 0 and cout % 64 == 0:
                 dx = _dgrad_stride2(dy_cl, w, n, h, wd, cin, cout)
+            elif pad <= min(r, s) - 1 and cout % 64 == 0 and cin % 8 == 0:
+                # Any other stride / size: the gradient is spread out with (stride - 1) zeros between its pixels
+                # (plus the rows and columns at the far edge that no window reached) and then goes through the
+                # stride-1 form above.  stride^2 times the multiply-adds of a dedicated kernel, but on this
+                # package's tensor-core path for every geometry.
+                ho, wo = dy_cl.shape[2], dy_cl.shape[3]
+                eh, ew = (h + 2 * pad - r) % stride, (wd + 2 * pad - s) % stride
+                spread = torch.zeros((n, cout, (ho - 1) * stride + 1 + eh, (wo - 1) * stride + 1 + ew), dtype=dy_cl.dtype,
+                                     device=dy_cl.device).contiguous(memory_format=torch.channels_last)
+                spread[:, :, :(ho - 1) * stride + 1:stride, :(wo - 1) * stride + 1:stride] = dy_cl
+                w_t = w.flip(2, 3).transpose(0, 1).contiguous(memory_format=torch.channels_last)
+                dx2d, _, _ = _conv_native(nhwc_2d(spread), w_t, n, spread.shape[2], spread.shape[3], cout, cin, r, s, 1,
+                                          r - 1 - pad, None)
+                dx = from_2d(dx2d, n, h, wd)
             else:
                 dx = torch.nn.grad.conv2d_input((n, cin, h, wd), w, dy_cl, stride=stride, padding=pad)
         if ctx.needs_input_grad[1]:

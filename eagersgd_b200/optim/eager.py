@@ -20,6 +20,7 @@ import torch
 from ..parallel import _native as N
 from ..parallel.group import Group, init as init_group
 from ..parallel.nvlink_channel import TWO_SHOT_MIN
+from ..utils.nvtx import nvtx_range
 
 _PAD = 64  # elements; keeps every parameter 128-byte aligned inside a bucket
 
@@ -317,7 +318,8 @@ class EagerOptimizer:
                 p.grad = _view_like(b.grad_flat, off, p)
         self._refresh_hyper(b)
         self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
-        b.channel.step(self.comm_stream)
+        with nvtx_range("partial_allreduce"):
+            b.channel.step(self.comm_stream)
         b.launched = True
 
     # ------------------------------------------------------------------ API

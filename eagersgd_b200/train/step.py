@@ -24,6 +24,7 @@ import torch.nn as nn
 from ..optim.eager import MajorityAllreduceOptimizer, SoloAllreduceOptimizer, SyncAllreduceOptimizer
 from ..parallel import _native as N
 from ..parallel.group import Group
+from ..utils.nvtx import nvtx_range
 
 
 def prepare_model(model: nn.Module, device: torch.device, compute_dtype=torch.bfloat16) -> nn.Module:
@@ -127,11 +128,14 @@ class TrainStep:
         # every operator's zeroed fp32 scratch (statistics, weight-gradient accumulators) comes out of one
         # buffer cleared by a single memset per step
         with zero_arena(self.device, self._arena_numel) if self.device.type == "cuda" else contextlib.nullcontext():
-            logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
-                              else x.to(self.compute_dtype))
-            loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
-            (loss * self.loss_scale if self.loss_scale != 1.0 else loss).backward()
-        self.opt.step()
+            with nvtx_range("forward"):
+                logits = self.net(x if x.dtype == self.compute_dtype or not x.is_floating_point()
+                                  else x.to(self.compute_dtype))
+                loss = self.loss_fn(logits if logits.dtype == torch.float32 else logits.float(), y)
+            with nvtx_range("backward"):
+                (loss * self.loss_scale if self.loss_scale != 1.0 else loss).backward()
+        with nvtx_range("optimizer"):
+            self.opt.step()
         return loss.detach()
 
     def run_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> float:

@@ -153,7 +153,7 @@ def _small_cases():
     for n in (1, 2):
         for (h, w) in ((5, 5), (8, 9), (9, 6)):
             for (cin, cout) in ((64, 64), (128, 64), (64, 72)):
-                for (k, stride, pad) in ((3, 1, 1), (3, 1, 0), (3, 2, 1), (1, 1, 0), (1, 2, 0), (5, 1, 2), (3, 1, 2)):
+                for (k, stride, pad) in ((3, 1, 1), (3, 1, 0), (3, 2, 1), (3, 2, 0), (5, 2, 2), (1, 1, 0), (1, 2, 0), (5, 1, 2), (3, 1, 2)):
                     if (h + 2 * pad - k) // stride + 1 < 1 or (w + 2 * pad - k) // stride + 1 < 1:
                         continue
                     cases.append((n, cin, h, w, cout, k, stride, pad))

@@ -120,3 +120,18 @@ int main(void) {
     subprocess.run(["gcc", "-O1", str(src), "-o", exe] + cflags + libs, check=True)
     out = subprocess.run([exe], capture_output=True, text=True, timeout=60)
     assert out.returncode == 0 and "PASSED" in out.stdout, out.stdout + out.stderr
+
+
+def test_nvtx_ranges_are_free_when_off(monkeypatch):
+    """``nvtx_range`` hands out one shared no-op context unless ESGD_NVTX=1."""
+    import eagersgd_b200.utils.nvtx as nv
+    monkeypatch.setattr(nv, "_ON", None)
+    monkeypatch.setenv("ESGD_NVTX", "0")
+    a, b = nv.nvtx_range("x"), nv.nvtx_range("y")
+    assert a is b and not nv.nvtx_enabled()
+    with a:
+        pass
+    monkeypatch.setattr(nv, "_ON", None)
+    monkeypatch.setenv("ESGD_NVTX", "1")
+    assert nv.nvtx_enabled() and nv.nvtx_range("x") is not a
+    monkeypatch.setattr(nv, "_ON", None)
