@@ -6,8 +6,11 @@
 // and of CommunicationNetwork (deep500/lv3/communication.py:14-119).  No message is ever sent: a source copies
 // its data into its own stage buffer and raises a counter in every destination; a destination waits for the
 // counter, pulls the bytes with 16-byte peer loads over NVLink, and acknowledges in the source's memory so the
-// stage can be reused.  Counters are per ordered pair (source, destination), so point-to-point traffic between
-// two ranks does not involve the others, and matching is by order, as with MPI tags on one communicator.
+// stage can be reused.  Counters are per ordered pair (source, destination) and per class of traffic (collectives /
+// point-to-point), so point-to-point traffic between two ranks does not involve the others, a receive from
+// "whichever rank sends first" can never pick up a peer's next collective, and matching within a class is by order.
+// A rank has one message in flight at a time (one stage buffer): a send returns as soon as the stage holds the data,
+// and the next publish of that rank waits until everybody the previous one was meant for has read it.
 //
 // Every wait is bounded: when it runs out the kernel sets a status bit, skips its copies and returns.
 #include <cuda_bf16.h>
@@ -30,9 +33,10 @@ enum CollStatus : uint32_t {
 };
 
 // Peer-visible words of one rank (start of its arena; the stage follows at `stage_off`).
+constexpr int kClasses = 2;      // 0: collectives, 1: point-to-point
 struct CollCtl {
-  uint64_t ready[kMaxRanks];   // ready[j]: number of messages rank j has published for this rank
-  uint64_t ack[kMaxRanks];     // ack[j]:   number of this rank's messages that rank j has finished reading
+  uint64_t ready[kClasses][kMaxRanks];   // ready[c][j]: number of class-c messages rank j has published for this rank
+  uint64_t ack[kClasses][kMaxRanks];     // ack[c][j]: number of this rank's class-c messages that rank j has read
 };
 
 // This rank's private state and its view of the peers (device memory of this GPU).
@@ -41,8 +45,8 @@ struct CollRank {
   uint64_t timeout_ns;
   CollCtl* ctl[kMaxRanks];
   uint8_t* stage[kMaxRanks];
-  uint64_t sent[kMaxRanks];    // messages published to j
-  uint64_t recvd[kMaxRanks];   // messages consumed from j
+  uint64_t sent[kClasses][kMaxRanks];    // messages published to j
+  uint64_t recvd[kClasses][kMaxRanks];   // messages consumed from j
   uint32_t ticket[2];          // last-block-done counters of the two phases
   uint32_t status;
   int32_t any_src;             // result of a probe for "whichever rank sends first"
@@ -57,6 +61,8 @@ struct Op {
   int64_t out_stride;          // bytes between the outputs of source j and j+1 (0: all to `out`)
   int32_t reduce;              // Reduce
   int32_t self_slot;           // >= 0: copy / include the own contribution at that slot
+  int32_t cls;                 // class of traffic: 0 collective, 1 point-to-point
+  int32_t pad_;
 };
 
 __device__ __forceinline__ uint4 ld_peer16(const uint8_t* p) {
@@ -120,8 +126,9 @@ __device__ void publish_phase(CollRank* me, const Op& op, int blk, int nblk) {
   if (op.dst_mask == 0) return;
   // the stage is single-buffered: everything published before must have been read
   bool ok = wait_block(me, CS_TIMEOUT_ACK, [&] {
-    for (int d = 0; d < me->world; ++d)
-      if (me->sent[d] && DevEnv::ld_acq64(&me->ctl[me->rank]->ack[d]) < me->sent[d]) return false;
+    for (int c = 0; c < kClasses; ++c)
+      for (int d = 0; d < me->world; ++d)
+        if (me->sent[c][d] && DevEnv::ld_acq64(&me->ctl[me->rank]->ack[c][d]) < me->sent[c][d]) return false;
     return true;
   });
   if (ok) copy_bytes(me->stage[me->rank], op.in, op.bytes, blk, nblk, false);
@@ -130,8 +137,8 @@ __device__ void publish_phase(CollRank* me, const Op& op, int blk, int nblk) {
       DevEnv::fence();
       for (int d = 0; d < me->world; ++d)
         if (op.dst_mask >> d & 1) {
-          me->sent[d] += 1;
-          DevEnv::st_rlx64(&me->ctl[d]->ready[me->rank], me->sent[d]);
+          me->sent[op.cls][d] += 1;
+          DevEnv::st_rlx64(&me->ctl[d]->ready[op.cls][me->rank], me->sent[op.cls][d]);
         }
     }
   }
@@ -183,7 +190,8 @@ __device__ void pull_phase(CollRank* me, const Op& op, int blk, int nblk) {
   if (op.src_mask == 0 && op.self_slot < 0) return;
   bool ok = wait_block(me, CS_TIMEOUT_READY, [&] {
     for (int j = 0; j < me->world; ++j)
-      if ((op.src_mask >> j & 1) && DevEnv::ld_acq64(&me->ctl[me->rank]->ready[j]) <= me->recvd[j]) return false;
+      if ((op.src_mask >> j & 1) && DevEnv::ld_acq64(&me->ctl[me->rank]->ready[op.cls][j]) <= me->recvd[op.cls][j])
+        return false;
     return true;
   });
   if (ok) {
@@ -206,8 +214,8 @@ __device__ void pull_phase(CollRank* me, const Op& op, int blk, int nblk) {
     DevEnv::fence();
     for (int j = 0; j < me->world; ++j)
       if (op.src_mask >> j & 1) {
-        me->recvd[j] += 1;
-        DevEnv::st_rlx64(&me->ctl[j]->ack[me->rank], me->recvd[j]);
+        me->recvd[op.cls][j] += 1;
+        DevEnv::st_rlx64(&me->ctl[j]->ack[op.cls][me->rank], me->recvd[op.cls][j]);
       }
   }
 }
@@ -224,13 +232,13 @@ __global__ void __launch_bounds__(256) coll_emulated_kernel(CollRank** ranks, co
   pull_phase(me, op, 0, 1);
 }
 
-// Which rank of `mask` has a message waiting (bounded); -1 when the wait runs out.
+// Which rank of `mask` has a point-to-point message waiting (bounded); -1 when the wait runs out.
 __global__ void coll_probe_kernel(CollRank* me, uint32_t mask) {
   uint64_t t0 = DevEnv::now_ns();
   me->any_src = -1;
   for (;;) {
     for (int j = 0; j < me->world; ++j)
-      if ((mask >> j & 1) && DevEnv::ld_acq64(&me->ctl[me->rank]->ready[j]) > me->recvd[j]) {
+      if ((mask >> j & 1) && DevEnv::ld_acq64(&me->ctl[me->rank]->ready[1][j]) > me->recvd[1][j]) {
         me->any_src = j;
         return;
       }
@@ -272,12 +280,12 @@ int esgd_coll_init(void* rank_desc, int rank, int world, const uint64_t* bases, 
 
 // One exchange: publish `in` to the ranks of dst_mask, read from the ranks of src_mask.
 int esgd_coll_exchange(void* rank_desc, uint32_t dst_mask, uint32_t src_mask, int64_t bytes, const void* in, void* out,
-                       int64_t out_stride, int reduce, int self_slot, cudaStream_t stream) {
-  if (bytes < 0 || (reduce != RED_NONE && (bytes & 15))) return cudaErrorInvalidValue;
+                       int64_t out_stride, int reduce, int self_slot, int cls, cudaStream_t stream) {
+  if (bytes < 0 || (reduce != RED_NONE && (bytes & 15)) || cls < 0 || cls >= kClasses) return cudaErrorInvalidValue;
   if (reduce != RED_NONE && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15))
     return cudaErrorMisalignedAddress;
   Op op = {dst_mask, src_mask, bytes, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), out_stride, reduce,
-           self_slot};
+           self_slot, cls, 0};
   CollRank* me = static_cast<CollRank*>(rank_desc);
   int grid = grid_for(bytes);
   if (dst_mask) {
@@ -302,9 +310,9 @@ uint64_t esgd_coll_op_bytes(void) { return sizeof(Op); }
 
 // Host-side packing of one Op record (for the emulated launch, whose ops live in a device array).
 void esgd_coll_pack_op(void* dst_host, uint32_t dst_mask, uint32_t src_mask, int64_t bytes, const void* in, void* out,
-                       int64_t out_stride, int reduce, int self_slot) {
+                       int64_t out_stride, int reduce, int self_slot, int cls) {
   Op op = {dst_mask, src_mask, bytes, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), out_stride, reduce,
-           self_slot};
+           self_slot, cls, 0};
   *static_cast<Op*>(dst_host) = op;
 }
 

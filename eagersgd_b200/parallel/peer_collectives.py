@@ -22,6 +22,7 @@ from . import _native as N
 from .nvlink_channel import Arena, _align, open_peer
 
 RED_NONE, RED_SUM_F32, RED_SUM_BF16 = 0, 1, 2
+COLLECTIVE, POINT_TO_POINT = 0, 1      # classes of traffic: each has its own message counters per pair of ranks
 _STATUS = {1: "a destination never acknowledged the previous message", 2: "a source never published"}
 
 
@@ -38,10 +39,10 @@ def _lib():
         lib.esgd_coll_init.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint64), C.c_uint64, C.c_double,
                                        C.c_void_p]
         lib.esgd_coll_exchange.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_int64, C.c_void_p, C.c_void_p,
-                                           C.c_int64, C.c_int, C.c_int, C.c_void_p]
+                                           C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]
         lib.esgd_coll_exchange_emulated.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         lib.esgd_coll_pack_op.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_int64, C.c_void_p, C.c_void_p,
-                                          C.c_int64, C.c_int, C.c_int]
+                                          C.c_int64, C.c_int, C.c_int, C.c_int]
         lib.esgd_coll_probe.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
         lib.esgd_coll_state.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_void_p]
         lib._coll_ready = True
@@ -117,7 +118,7 @@ class PeerCollectives:
 
     # ---- one exchange, in pieces no larger than the stage ---------------------------------------------------
     def _exchange(self, dst: int, src: int, t_in: Optional[torch.Tensor], t_out: Optional[torch.Tensor], nbytes: int,
-                  out_stride: int = 0, reduce: int = RED_NONE, self_slot: int = -1) -> None:
+                  out_stride: int = 0, reduce: int = RED_NONE, self_slot: int = -1, cls: int = COLLECTIVE) -> None:
         lib = _lib()
         step = self.stage_bytes
         off = 0
@@ -126,7 +127,7 @@ class PeerCollectives:
             pin = t_in.data_ptr() + off if t_in is not None else 0
             pout = t_out.data_ptr() + off if t_out is not None else 0
             N.check_cuda(lib.esgd_coll_exchange(self.desc.data_ptr(), dst, src, n, pin, pout, out_stride, reduce,
-                                                self_slot, _stream()), "peer collective")
+                                                self_slot, cls, _stream()), "peer collective")
             off += n
             if off >= nbytes:
                 break
@@ -168,19 +169,21 @@ class PeerCollectives:
             m = min(self.stage_bytes, n - off)
             N.check_cuda(lib.esgd_coll_exchange(self.desc.data_ptr(), dst, src, m, b.data_ptr() + off,
                                                 ob.data_ptr() + off if ob is not None else 0, n, RED_NONE, slot,
-                                                _stream()), "peer gather")
+                                                COLLECTIVE, _stream()), "peer gather")
 
     def send(self, t: torch.Tensor, dst: int) -> None:
         b = _flat(t)
-        self._exchange(1 << dst, 0, b, None, b.numel())
+        self._exchange(1 << dst, 0, b, None, b.numel(), cls=POINT_TO_POINT)
 
     def recv(self, t: torch.Tensor, src: int) -> int:
         b = _flat(t)
-        self._exchange(0, 1 << src, None, b, b.numel())
+        self._exchange(0, 1 << src, None, b, b.numel(), cls=POINT_TO_POINT)
         return src
 
     def recv_any(self, t: torch.Tensor) -> int:
-        """Receive from whichever rank has sent first; returns its rank.  Synchronises the stream."""
+        """Receive from whichever rank has sent (point-to-point) first; returns its rank.  Synchronises the stream.
+        Only ``send`` traffic is looked at, so a peer that has gone on to its next collective is never mistaken
+        for a sender."""
         lib = _lib()
         N.check_cuda(lib.esgd_coll_probe(self.desc.data_ptr(), self.plan.others, _stream()), "probe")
         status, src = self._state()
@@ -258,13 +261,13 @@ class EmulatedCollectives:
         self.op_bytes = int(lib.esgd_coll_op_bytes())
 
     def _run(self, ops: Sequence[tuple]) -> None:
-        """ops[r] = (dst_mask, src_mask, nbytes, in_ptr, out_ptr, out_stride, reduce, self_slot)"""
+        """ops[r] = (dst_mask, src_mask, nbytes, in_ptr, out_ptr, out_stride, reduce, self_slot[, class])"""
         lib = _lib()
         host = (C.c_ubyte * (self.op_bytes * self.world))()
         for r, o in enumerate(ops):
             if o[2] > self.stage_bytes:
                 raise ValueError("message larger than the emulated stage")
-            lib.esgd_coll_pack_op(C.byref(host, r * self.op_bytes), *o)
+            lib.esgd_coll_pack_op(C.byref(host, r * self.op_bytes), *(tuple(o) + (COLLECTIVE,))[:9])
         dev = torch.frombuffer(bytearray(host), dtype=torch.uint8).to(self.device)
         N.check_cuda(lib.esgd_coll_exchange_emulated(self.desc_ptrs.data_ptr(), dev.data_ptr(), self.world, _stream()),
                      "emulated collective")
@@ -309,8 +312,8 @@ class EmulatedCollectives:
     def send_recv(self, t_src: torch.Tensor, src: int, t_dst: torch.Tensor, dst: int) -> None:
         ops = [(0, 0, 0, 0, 0, 0, RED_NONE, -1)] * self.world
         a, b = _flat(t_src), _flat(t_dst)
-        ops[src] = (1 << dst, 0, a.numel(), a.data_ptr(), 0, 0, RED_NONE, -1)
-        ops[dst] = (0, 1 << src, b.numel(), 0, b.data_ptr(), 0, RED_NONE, -1)
+        ops[src] = (1 << dst, 0, a.numel(), a.data_ptr(), 0, 0, RED_NONE, -1, POINT_TO_POINT)
+        ops[dst] = (0, 1 << src, b.numel(), 0, b.data_ptr(), 0, RED_NONE, -1, POINT_TO_POINT)
         self._run(ops)
 
     def neighbours(self, ts: List[torch.Tensor]) -> None:
