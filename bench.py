@@ -247,6 +247,7 @@ def run_arm(args, group, host_batches, batch, classes, impl, mode, inject, steps
         return min(d, 5.0 * base_step_s)
 
     def timed(fn, batches, stream_api=False):
+        delay_rng.seed(4242)                 # the device-timed and the end-to-end loop see the same delays
         sampler = ClockSampler(dev.index)
         launches0 = N.launch_count()
         sync_all()
