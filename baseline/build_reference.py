@@ -20,7 +20,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
 SHIM = os.path.join(HERE, "mpi_shim")
-DEFAULT_SOURCE = "/root/reference/eager-SGD-modules/fflib2"
+# where the reference's fflib2 sources are: ESGD_REFERENCE_FFLIB2, else a checkout named "reference" beside this repository
+DEFAULT_SOURCE = os.environ.get("ESGD_REFERENCE_FFLIB2") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference", "eager-SGD-modules", "fflib2")
 # the programs the comparison uses, plus the correctness programs that double as a check of the shim
 PROGRAMS = ["ssgd", "rsgd", "randomsgd", "allreduce", "allreduce_inplace", "solo_allreduce_correctness",
             "rand_allreduce_correctness", "activation_tree_multiple", "send_recv", "ping_pong_dep", "first_dep",

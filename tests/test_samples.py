@@ -32,3 +32,11 @@ def test_sample_runs(script, args):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "samples", script)] + args, capture_output=True, text=True,
                        timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+def test_peer_collectives_sample_runs_emulated_on_one_gpu():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "samples", "peer_collectives.py"), "--emulate", "4"],
+                       capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "expected 6.0" in r.stdout and "[6.0, 6.0]" in r.stdout and "status words: [0, 0, 0, 0]" in r.stdout

@@ -135,3 +135,23 @@ def test_nvtx_ranges_are_free_when_off(monkeypatch):
     monkeypatch.setenv("ESGD_NVTX", "1")
     assert nv.nvtx_enabled() and nv.nvtx_range("x") is not a
     monkeypatch.setattr(nv, "_ON", None)
+
+
+def test_collective_plans_pair_every_sender_with_a_reader():
+    """The masks of the peer-memory collectives, for every rank of worlds of 2 to 8: whoever a rank publishes to
+    reads from it and vice versa (an unmatched side would wait until its time limit on a GPU)."""
+    from eagersgd_b200.parallel.peer_collectives import _Plan
+    for world in range(2, 9):
+        plans = [_Plan(r, world) for r in range(world)]
+        for name, args in (("bcast", (0,)), ("bcast", (world - 1,)), ("gather", (1 % world,)), ("allgather", ()),
+                           ("neighbours", ())):
+            masks = [getattr(p, name)(*args) for p in plans]
+            for a in range(world):
+                dst_a, src_a, slot_a = masks[a]
+                assert not dst_a >> a & 1 and not src_a >> a & 1            # nobody sends to itself
+                for b in range(world):
+                    if a != b:
+                        assert bool(dst_a >> b & 1) == bool(masks[b][1] >> a & 1), (name, world, a, b)
+        root = 1 % world
+        assert [p.gather(root)[2] for p in plans] == [r if r == root else -1 for r in range(world)]
+        assert all(p.allgather()[2] == r for r, p in enumerate(plans))
