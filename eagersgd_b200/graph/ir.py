@@ -5,7 +5,8 @@
 per node in topological order.  It is the object model the reference builds from ONNX protobufs
 (deep500/utils/onnx_interop/onnx_objects.py, generated_operators.py, onnx_base_visitor.py,
 operations_visitor.py, losses.py, extended_operations.py) without the protobuf dependency: graphs
-are built programmatically or loaded from a JSON + NPZ pair in the same schema.
+are built programmatically, read from ``.onnx`` files (onnx_io.py) or loaded from a JSON + NPZ pair in the
+same schema.  Nodes of standard operators are instances of that operator's class (onnx_ops.py).
 """
 from __future__ import annotations
 
@@ -60,7 +61,8 @@ class Graph:
         return name
 
     def add(self, op_type: str, inputs: Sequence[str], outputs: Sequence[str], **attrs) -> Operation:
-        op = Operation(op_type, inputs, outputs, **attrs)
+        from .onnx_ops import make_operation
+        op = make_operation(op_type, inputs, outputs, **attrs)     # the operator's own class where ONNX defines it
         self.ops.append(op)
         return op
 
@@ -121,7 +123,8 @@ class Graph:
         g = Graph(d["name"])
         g.inputs, g.outputs = d["inputs"], d["outputs"]
         for o in d["ops"]:
-            g.ops.append(Operation(o["op_type"], o["inputs"], o["outputs"], o["name"], **o["attrs"]))
+            from .onnx_ops import make_operation
+            g.ops.append(make_operation(o["op_type"], o["inputs"], o["outputs"], o["name"], **o["attrs"]))
         z = np.load(base + ".npz")
         g.initializers = {k: z[k] for k in z.files}
         return g

@@ -196,7 +196,8 @@ def _parse_node(buf: bytes) -> Operation:
         elif num == 5:
             k, v = _parse_attribute(val)
             attrs[k] = v
-    return Operation(op_type, inputs, outputs, name, **attrs)
+    from .onnx_ops import make_operation
+    return make_operation(op_type, inputs, outputs, name, **attrs)
 
 
 def _value_info_name_shape(buf: bytes) -> Tuple[str, Optional[List[Any]]]:

@@ -186,3 +186,37 @@ def test_reference_executor_matches_native_executor(use_cpp):
         assert np.allclose(a, b, rtol=2e-2, atol=2e-3 * max(1.0, float(np.abs(b).max()))), name
         checked += 1
     assert checked >= 20
+
+
+def test_onnx_operator_classes():
+    """Every standard operator has a class with its attributes and defaults; nodes of graphs built in code and of
+    parsed files are instances of them; validation names what is wrong."""
+    from eagersgd_b200.graph import Graph, operator_class, operator_names
+    from eagersgd_b200.graph.ir import Operation
+    names = operator_names()
+    assert len(names) >= 150 and {"Conv", "BatchNormalization", "LSTM", "Einsum", "Resize", "TopK"} <= set(names)
+    g = Graph("t")
+    g.add_input("x")
+    g.add_initializer("w", np.zeros((4, 3, 3, 3), np.float32))
+    conv = g.add("Conv", ["x", "w"], ["y"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    assert isinstance(conv, operator_class("Conv")) and isinstance(conv, Operation)
+    assert conv.group == 1 and conv.auto_pad == "NOTSET" and conv.pads == [1, 1, 1, 1] and conv.strides is None
+    conv.validate()
+    pool = g.add("MaxPool", ["y"], ["z"])
+    with pytest.raises(ValueError, match="kernel_shape"):
+        pool.validate()
+    with pytest.raises(AttributeError):
+        pool.kernel_shape
+    bad = g.add("Relu", ["z", "z"], ["r"], slope=0.1)
+    with pytest.raises(ValueError, match="slope"):
+        bad.validate()
+    bad.attrs.clear()
+    with pytest.raises(ValueError, match="inputs"):
+        bad.validate()
+    custom = g.add("MyOwnOp", ["r"], ["s"], anything=1)
+    assert type(custom) is Operation and operator_class("MyOwnOp") is None
+    counts = g.accept(OpCounter())                                  # visitor dispatch is unchanged
+    assert counts["Conv"] == 1 and counts["MyOwnOp"] == 1
+    for n in names:                                                 # every class can be made and validated
+        cls = operator_class(n)
+        assert cls.__name__ == n and cls.MIN_INPUTS <= cls.MAX_INPUTS
