@@ -154,6 +154,33 @@ class _Forward(Visitor):
         self._out(op, _AllReduceGrad.apply(self._in(op, 0), self.net.group))
 
 
+    def visit_consistentparameterservergradients(self, op, g):
+        """Identity forward; backward the gradients of all ranks meet at rank 0, are averaged there and sent back
+        (extended_operations.py:27-77 declares the operation; no backend of the reference implements it)."""
+        self._out(op, _ParameterServerGrad.apply(self._in(op, 0), self.net.group))
+
+    def visit_inconsistentparameterservergradients(self, op, g):
+        """Identity in both directions: with an inconsistent parameter server every rank applies its own
+        gradient and the exchange happens in the optimizer (``optim.distributed.InconsistentParameterServer``)."""
+        self._out(op, self._in(op, 0).view_as(self._in(op, 0)))
+
+
+class _ParameterServerGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        gr = ctx.group
+        if gr is not None and gr.world > 1:
+            g = g.contiguous()
+            gr.sync_all_at_root(g, average=True)
+            gr.bcast(g, 0)
+        return g, None
+
+
 class _AllReduceGrad(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):

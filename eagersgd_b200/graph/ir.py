@@ -22,7 +22,8 @@ STANDARD_OPS = ("Conv", "BatchNormalization", "Relu", "MaxPool", "AveragePool", 
                 "Sub", "Mul", "Div", "Neg", "Abs", "Exp", "Log", "Sqrt", "Pow", "Sigmoid", "Tanh", "LeakyRelu", "Transpose",
                 "LogSoftmax", "Clip", "ReduceMean", "ReduceSum", "Constant", "Pad", "LRN")
 LOSS_OPS = ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError")
-EXTENSION_OPS = ("StopGradient", "AllReduceGradients")
+EXTENSION_OPS = ("StopGradient", "AllReduceGradients", "ConsistentParameterServerGradients",
+                 "InconsistentParameterServerGradients")
 
 
 class Operation:

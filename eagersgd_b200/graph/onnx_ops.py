@@ -160,6 +160,8 @@ for _n in ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError"):
     _op(_n, 2, 2)
 _op("StopGradient", 1, 1)
 _op("AllReduceGradients", 1, 1)
+_op("ConsistentParameterServerGradients", 1, 1)
+_op("InconsistentParameterServerGradients", 1, 1)
 
 _CLASSES: Dict[str, type] = {}
 

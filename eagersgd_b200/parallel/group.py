@@ -102,6 +102,21 @@ class Group:
 
     allreduce = sync_all
 
+    def sync_all_at_root(self, t: torch.Tensor, average: bool = False) -> torch.Tensor:
+        """Sum over every rank, delivered to rank 0 only (``sync_all_at_root``, communication.py: a reduce);
+        the other ranks' tensors are left as they are."""
+        if self.world == 1:
+            return t.div_(1) if average else t
+        if self._native(t):
+            parts = self.peer_collectives().gather(t, 0)
+            if parts is not None:
+                t.copy_(parts.sum(0) if t.is_floating_point() else parts.sum(0).to(t.dtype))
+        else:
+            dist.reduce(t, dst=0)
+        if average and self.rank == 0:
+            t.div_(self.world)
+        return t
+
     def gather_at_root(self, t: torch.Tensor) -> Optional[List[torch.Tensor]]:
         if self.world == 1:
             return [t.clone()]

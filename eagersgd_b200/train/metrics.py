@@ -117,6 +117,30 @@ class TestAccuracy(TrainingAccuracy):
     pass
 
 
+class DatasetAccuracy(TestMetric):
+    """Accuracy of an executor over a whole sampler / data set, measured on demand
+    (deep500/lv2/validation/metrics.py: ``DatasetAccuracy``).  ``executor`` is anything with
+    ``inference(batch_dict) -> {name: array}`` (the graph executors) or a callable on a batch tensor."""
+
+    def __init__(self, sampler, output: str = None, input_name: str = "x", max_batches: int = None):
+        self.sampler, self.output, self.input_name, self.max_batches = sampler, output, input_name, max_batches
+
+    def measure(self, executor=None, *a):
+        correct = total = 0
+        for k, (x, y) in enumerate(self.sampler):
+            if self.max_batches is not None and k >= self.max_batches:
+                break
+            if hasattr(executor, "inference"):
+                out = executor.inference({self.input_name: x})
+                logits = out[self.output] if self.output is not None else next(iter(out.values()))
+            else:
+                with torch.no_grad():
+                    logits = executor(x if torch.is_tensor(x) else torch.as_tensor(x))
+            correct += int((_np(logits).argmax(-1) == _np(y)).sum())
+            total += len(_np(y))
+        return correct / max(total, 1)
+
+
 def topk_accuracy(logits: torch.Tensor, labels: torch.Tensor, ks=(1, 5)) -> List[float]:
     """Prec@k as logged by the reference run loop (resnet_run_loop_solo_imagenet_300.py:429-448)."""
     top = logits.float().topk(max(ks), dim=-1).indices

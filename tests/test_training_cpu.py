@@ -211,3 +211,16 @@ def test_flags_that_change_behaviour(tmp_path):
     fresh = cifar_resnet(8, 1, 10).state_dict()
     moved = [k for k in fresh if fresh[k].dtype.is_floating_point and "running" not in k and not torch.equal(fresh[k], state[k])]
     assert moved and all(k.startswith("fc.") for k in moved), moved
+
+
+def test_dataset_accuracy_metric():
+    """Accuracy of a model over a sampler, measured on demand."""
+    import numpy as np
+    from eagersgd_b200.train.metrics import DatasetAccuracy
+    xs = np.eye(4, dtype=np.float32)
+    batches = [(torch.from_numpy(xs[:2]), torch.tensor([0, 1])), (torch.from_numpy(xs[2:]), torch.tensor([2, 0]))]
+    model = torch.nn.Linear(4, 4, bias=False)
+    with torch.no_grad():
+        model.weight.copy_(torch.eye(4))
+    assert DatasetAccuracy(batches).measure(model) == 0.75
+    assert DatasetAccuracy(batches, max_batches=1).measure(model) == 1.0
