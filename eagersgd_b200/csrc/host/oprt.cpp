@@ -717,6 +717,35 @@ int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
   return (int)dot.size();
 }
 
+// The same graph as two JSON arrays for vis.js network views (ffschedule.c:111-161 prints both forms):
+// {"nodes": [{"id": "7.0", "label": "send"}, ...], "edges": [{"from": "7.0", "to": "9.0"}, ...]}
+int rt_schedule_print_visjs(rt_rank* c, rt_sched s, char* out, int64_t cap) {
+  static const char* names[] = {"nop", "callback", "comp", "send", "recv"};
+  std::lock_guard<std::mutex> g(c->mu);
+  Schedule& sc = c->scheds[s];
+  std::vector<rt_op> all = sc.ops;
+  all.push_back(sc.begin);
+  all.push_back(sc.end);
+  const std::string r = "." + std::to_string(c->id);
+  std::string nodes, edges;
+  for (rt_op id : all) {
+    Op& op = *c->ops[id];
+    if (!nodes.empty()) nodes += ", ";
+    nodes += "{\"id\": \"" + std::to_string(id) + r + "\", \"label\": \"" + names[op.type] +
+             (id == sc.begin ? " begin" : id == sc.end ? " end" : "") + "\"}";
+    for (const Edge& ed : op.edges) {
+      if (ed.child == RT_NONE) continue;
+      if (!edges.empty()) edges += ", ";
+      edges += "{\"from\": \"" + std::to_string(id) + r + "\", \"to\": \"" + std::to_string(ed.child) + r +
+               "\", \"arrows\": \"to\"}";
+    }
+  }
+  const std::string js = "{\"nodes\": [" + nodes + "], \"edges\": [" + edges + "]}\n";
+  if ((int64_t)js.size() + 1 > cap) return RT_ERROR;
+  memcpy(out, js.c_str(), js.size() + 1);
+  return (int)js.size();
+}
+
 // Recursive doubling for any P: ranks beyond the largest power of two first fold into a
 // partner, the power-of-two core exchanges in log2 rounds, and the result is sent back.
 rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper) {

@@ -38,6 +38,9 @@ enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUST
 #define RT_DEP_IGNORE_VERSION 0x10   /* every completion of the first op counts (what rt_op_hb uses) */
 #define RT_DEP_NO_AUTOPOST 0x20      /* the edge never posts the second op; it is posted by hand */
 #define RT_DEP_CONSTRAINED 0x40      /* passes a completion on only after its constraining edge has (rt_dep_set_parent) */
+#define RT_DEP_SKIP_OLD_VERSIONS 0x80 /* accepted and without effect, as in the reference (its code for the bit is commented
+                                         out, ffop.c:347-356): a completion that is ahead of the second op is always kept
+                                         as a future */
 /* more operation options (ff.h:44-57) */
 #define RT_SHADOW_TAG 0x100          /* send / recv: a second tag space, so that control tokens never match data */
 #define RT_OP_COMPLETE_BEFORE_CANCELLING 0x200   /* rt_op_cancel lets a posted instance finish instead of withdrawing it */
@@ -121,6 +124,7 @@ int rt_schedule_default_test(rt_rank* c, rt_sched s);
 int rt_schedule_set_state(rt_rank* c, rt_sched s, void* state);
 void* rt_schedule_get_state(rt_rank* c, rt_sched s);
 int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap);   /* graphviz DOT */
+int rt_schedule_print_visjs(rt_rank* c, rt_sched s, char* out, int64_t cap);   /* {"nodes": [...], "edges": [...]} */
 
 /* collectives */
 rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op);   /* snd == RT_INPLACE: in place */

@@ -22,7 +22,7 @@ CALLBACK = C.CFUNCTYPE(None, C.c_int64, C.c_void_p)
 OPERATOR = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int)
 SCHED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64)
 SCHED_WAIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_double)
-DEP_IGNORE_VERSION, DEP_NO_AUTOPOST, DEP_CONSTRAINED = 0x10, 0x20, 0x40
+DEP_IGNORE_VERSION, DEP_NO_AUTOPOST, DEP_CONSTRAINED, DEP_SKIP_OLD_VERSIONS = 0x10, 0x20, 0x40, 0x80
 NONE = -1
 
 _lib = None
@@ -63,6 +63,7 @@ def lib():
         l.rt_schedule_wait.argtypes = [vp, i64, C.c_double]
         l.rt_schedule_test.argtypes = [vp, i64]
         l.rt_schedule_print.argtypes = [vp, i64, C.c_char_p, i64]
+        l.rt_schedule_print_visjs.argtypes = [vp, i64, C.c_char_p, i64]
         l.rt_buffer_delete.argtypes = [vp, i64]
         l.rt_op_hb_fallback.argtypes = [vp, i64, i64, i64, i32, C.POINTER(i64)]
         l.rt_dep_set_parent.argtypes = [vp, i64, i64]
@@ -188,6 +189,13 @@ class Rank:
         buf = C.create_string_buffer(1 << 16)
         n = lib().rt_schedule_print(self.h, s, buf, len(buf))
         return buf.value.decode() if n >= 0 else ""
+
+    def schedule_visjs(self, s) -> dict:
+        """The schedule as ``{"nodes": [...], "edges": [...]}`` for a vis.js network view."""
+        import json
+        buf = C.create_string_buffer(1 << 17)
+        n = lib().rt_schedule_print_visjs(self.h, s, buf, len(buf))
+        return json.loads(buf.value.decode()) if n >= 0 else {}
 
     # collectives
     def allreduce(self, snd: int, rcv: int, tag: int, op=SUM) -> int:

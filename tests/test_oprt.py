@@ -134,6 +134,11 @@ def test_schedule_and_dot():
             assert np.all(y == 3)
         dot = r.schedule_dot(s)
         assert dot.startswith("digraph") and "->" in dot and "begin" in dot
+        vis = r.schedule_visjs(s)                 # the same graph for a vis.js network view
+        labels = sorted(n["label"] for n in vis["nodes"])
+        assert labels == ["comp", "comp", "nop begin", "nop end"]
+        ids = {n["id"] for n in vis["nodes"]}
+        assert len(vis["edges"]) == dot.count("->") and all(e["from"] in ids and e["to"] in ids for e in vis["edges"])
 
 
 @pytest.mark.parametrize("world", [1, 2, 3, 4, 5, 8])
