@@ -223,6 +223,14 @@ def main(argv=None):
         if args.export_dir and group.rank == 0:
             ckpt.export_tf_layout(step.model, os.path.join(args.export_dir, "model.npz"),
                                   step.opt if hasattr(step.opt, "master_params") else None, global_step)
+            # and the servable form: the inference graph with its weights as one .onnx file
+            from ..graph import from_torch_resnet, save_onnx
+            try:
+                import copy
+                frozen = copy.deepcopy(step.model).float().cpu().eval()
+                save_onnx(from_torch_resnet(frozen), os.path.join(args.export_dir, "model.onnx"))
+            except (TypeError, ValueError, AttributeError) as e:    # a model the graph builder does not cover
+                print("no .onnx export for this model: %s" % e)
     stats = step.stats()
     if group.rank == 0 and stats:
         print("eager-SGD counters:", stats)

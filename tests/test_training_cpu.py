@@ -169,6 +169,12 @@ def test_resnet_main_smoke(tmp_path):
     z = np.load(tmp_path / "e" / "model.npz")
     assert "resnet_model/conv2d/kernel" in z and "resnet_model/dense/bias" in z
     assert (tmp_path / "log" / "metric.log").exists()
+    from eagersgd_b200.graph import GraphNetwork, load_onnx          # the exported inference graph loads and runs
+    net = GraphNetwork(load_onnx(str(tmp_path / "e" / "model.onnx"))).eval()
+    with torch.no_grad():
+        out = net(torch.randn(2, 3, 32, 32))
+    out = out[0] if isinstance(out, (list, tuple)) else out
+    assert out.shape == (2, 10) and torch.isfinite(out).all()
 
 
 def test_flags_that_change_behaviour(tmp_path):
