@@ -16,5 +16,6 @@ ref/       CPU oracles (numpy / C++) for every kernel
 __version__ = "0.1.0"
 
 from .parallel.group import Group, init, finalize, rank, world_size  # noqa: F401
+from .parallel.partial_allreduce import PartialAllreduce  # noqa: F401
 from .optim.eager import (EagerOptimizer, SoloAllreduceOptimizer, MajorityAllreduceOptimizer,  # noqa: F401
                           SyncAllreduceOptimizer)

@@ -74,3 +74,60 @@ def test_parameter_server_gradient_operations_in_a_graph():
     for gx, gx2 in res:
         assert gx == [2.0] * 4
         assert gx2 == [2.0 * 1.5] * 4
+
+
+def _partial_allreduce_object(rank, world):
+    """The schedule-like life cycle on CPU ranks: start, post / wait and post / test, in place and out of place,
+    a completion callback, resize, describe, close."""
+    import time
+    import eagersgd_b200 as es
+    g = es.init()
+    seen = []
+    t = torch.zeros(10)
+    ar = es.PartialAllreduce(t, g, mode="sync", average="sum", on_complete=seen.append).start()
+    ok = True
+    for k in range(1, 4):
+        t.fill_(float(rank + k))
+        ar.post()
+        info = ar.wait()
+        ok = ok and bool(torch.all(t == sum(r + k for r in range(world)))) and info["role"] == "participant" \
+            and info["contributors"] == world and info["sync"]
+    out = torch.zeros(10)
+    ar.resize(torch.full((10,), 2.0), out)                 # out of place after a resize
+    ar.post()
+    while not ar.test():
+        time.sleep(0.001)
+    ok = ok and bool(torch.all(out == 2.0 * world)) and len(seen) == 4 and "sync" in ar.describe()
+    ar.close()
+    # solo: every post returns without waiting for the others; whoever misses a round gets it at the next step or flush
+    x = torch.ones(16) * (rank + 1)
+    with es.PartialAllreduce(x, g, mode="solo", limiter=4, average="world") as solo:
+        for k in range(6):
+            if rank == 1:
+                time.sleep(0.01)
+            solo.post()
+            solo.wait()
+        st = solo.flush()
+    ok = ok and st["status"] == 0 and st["steps"] == 6
+    es.finalize()
+    return ok, st["forced_sync"]
+
+
+def test_partial_allreduce_object_on_cpu_ranks():
+    res = run_ranks(_partial_allreduce_object, 3)
+    assert all(r[0] for r in res), res
+    assert all(r[1] >= 1 for r in res)                     # the limiter forced a synchronous round
+
+
+def test_partial_allreduce_object_single_rank():
+    import eagersgd_b200 as es
+    g = es.Group()
+    t = torch.arange(5, dtype=torch.float64)
+    with es.PartialAllreduce(t, g, mode="majority") as ar:
+        ar.post()
+        info = ar.wait()
+        assert info["applied"] and torch.equal(t, torch.arange(5, dtype=torch.float64))
+        assert not ar.test() is False
+    import pytest
+    with pytest.raises(RuntimeError):
+        es.PartialAllreduce(torch.zeros(3), g).post()

@@ -420,3 +420,37 @@ def test_classic_collectives_on_peer_memory():
         pytest.skip("needs 2 GPUs")
     for r, res in enumerate(run_ranks(_peer_collectives, world, timeout=240)):
         assert all(res.values()), (r, res)
+
+
+def _partial_allreduce_object(rank, world):
+    """The stand-alone collective object across GPUs: synchronous closed form, then solo with a late rank."""
+    es, group = _setup(rank, world)
+    dev = group.device
+    t = torch.zeros(1 << 16, device=dev)
+    ok = True
+    with es.PartialAllreduce(t, group, mode="sync", average="sum") as ar:
+        for k in range(1, 4):
+            t.fill_(float(rank + k))
+            ar.post()
+            info = ar.wait()
+            ok = ok and bool(torch.all(t == float(sum(r + k for r in range(world))))) and info["contributors"] == world
+    x = torch.ones(1000, device=dev, dtype=torch.bfloat16) * (rank + 1)     # not a multiple of eight: padded inside
+    out = torch.zeros(1000, device=dev, dtype=torch.bfloat16)
+    with es.PartialAllreduce(x, group, mode="solo", limiter=3, average="world", out=out, timeout_s=10.0) as solo:
+        for k in range(8):
+            if rank == world - 1:
+                torch.cuda._sleep(20_000_000)               # this rank's stream is late every step
+            solo.post()
+            solo.wait()
+        st = solo.flush()
+    ok = ok and st["status"] == 0 and st["steps"] == 8 and st["forced_sync"] >= 1 and bool(torch.isfinite(out.float()).all())
+    es.finalize()
+    return ok, st
+
+
+def test_partial_allreduce_object_across_gpus():
+    world = _world()
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    for ok, st in run_ranks(_partial_allreduce_object, world, timeout=240):
+        assert ok, st

@@ -512,3 +512,28 @@ def test_collective_wait_for_a_silent_rank_runs_out_with_a_status():
     ec._run(ops)
     assert ec.status() == [0, 2] and torch.all(b == 3.0)
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
+
+
+@pytest.mark.parametrize("dtype,n", [(torch.float32, 4096), (torch.bfloat16, 1003), (torch.float32, 77)])
+def test_partial_allreduce_object_on_one_gpu(dtype, n):
+    """The schedule-like object on a CUDA tensor (world of one): post returns at once, wait delivers the average in
+    place or into ``out``, sizes that are no multiple of eight are padded inside, the counters count."""
+    import eagersgd_b200 as es
+    dev = _dev()
+    g = es.Group()
+    t = (torch.arange(n, device=dev, dtype=torch.float32) % 17 - 8).to(dtype)
+    ref = t.clone()
+    seen = []
+    with es.PartialAllreduce(t, g, mode="solo", limiter=2, on_complete=seen.append) as ar:
+        for k in range(4):
+            ar.post()
+            info = ar.wait()
+            assert info["applied"] and info["role"] == "participant" and info["contributors"] == 1
+            assert torch.equal(t, ref)                      # the average over one rank is the tensor itself
+        out = torch.zeros(n, device=dev, dtype=dtype)
+        ar.resize(t, out)
+        ar.post()
+        assert ar.wait()["applied"] and torch.equal(out, ref)
+        st = ar.stats()
+        assert st["steps"] == 1 and st["status"] == 0 and "NVLink" in ar.describe()
+    assert len(seen) == 5
