@@ -95,6 +95,13 @@ class SharedSegments:
         except BufferError:
             pass
         try:
+            # ranks started by one parent share its resource tracker, and a peer's unregister (above) has then
+            # removed this segment's entry as well: put it back so that unlink() finds what it takes out
+            from multiprocessing import resource_tracker
+            resource_tracker.register(self._own._name, "shared_memory")
+        except Exception:
+            pass
+        try:
             self._own.unlink()
         except FileNotFoundError:
             pass
