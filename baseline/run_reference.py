@@ -51,6 +51,21 @@ def run_one(program: str, ranks: int, count: int, iters: int, timeout: float = 3
     return 1e6 * sum(vals) / len(vals)
 
 
+def allreduce_cycle_us(ranks: int, count: int = 1024, timeout: float = 90.0):
+    """Microseconds per create + post + wait + delete of a synchronous allreduce schedule: wall time of the
+    reference's evaluation/allreduce.c (2048 fresh schedules on int32 vectors, checked against the closed form)
+    divided by 2048.  Includes the start of the processes (about 10 ms, i.e. 5 us per cycle)."""
+    import time
+    t0 = time.perf_counter()
+    try:
+        r = subprocess.run([os.path.join(BIN, "shimrun"), "-n", str(ranks), os.path.join(BIN, "allreduce"), str(count)],
+                           capture_output=True, text=True, timeout=timeout, cwd=BIN)
+    except subprocess.TimeoutExpired:
+        return None
+    dt = time.perf_counter() - t0
+    return 1e6 * dt / 2048 if r.returncode == 0 and "PASSED" in r.stdout else None
+
+
 def run(ranks=(2, 4, 8), counts=(1024, 262144, 6553600), iters: int = 12) -> dict:
     why = available()
     if why:
@@ -65,8 +80,13 @@ def run(ranks=(2, 4, 8), counts=(1024, 262144, 6553600), iters: int = 12) -> dic
                 except subprocess.TimeoutExpired:
                     row[prog + "_us"] = None
             rows.append(row)
+    cycles = {}
+    if os.path.exists(os.path.join(BIN, "allreduce")):
+        for p in ranks:
+            if p <= (os.cpu_count() or 1):
+                cycles[str(p)] = allreduce_cycle_us(p)
     return {"programs": PROGRAMS, "iters": iters, "transport": "shared-memory MPI subset (baseline/mpi_shim)",
-            "rows": rows}
+            "rows": rows, "allreduce_schedule_cycle_us": cycles}
 
 
 if __name__ == "__main__":

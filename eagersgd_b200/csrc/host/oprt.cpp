@@ -11,6 +11,7 @@
 #include <chrono>
 #include <condition_variable>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <map>
@@ -24,6 +25,12 @@
 namespace {
 
 constexpr double kDefaultWaitSeconds = 600.0;   // what "no timeout" means: ten minutes, then RT_TIMEOUT
+// How long an idle progress thread / a waiter spins before it sleeps (ESGD_RT_SPIN_US overrides; 0 = sleep at once).
+int spin_micros() {
+  static const int v = [] { const char* e = getenv("ESGD_RT_SPIN_US"); return e ? atoi(e) : 50; }();
+  return v;
+}
+#define kSpinMicros spin_micros()
 
 size_t dtype_size(int dt) { return dt == RT_CHAR ? 1 : (dt == RT_INT32 || dt == RT_FLOAT) ? 4 : 8; }
 
@@ -118,6 +125,7 @@ struct rt_rank {
   std::vector<rt_sched> free_scheds;
   std::thread progress;
   std::atomic<bool> stop{false};
+  std::atomic<uint64_t> signals{0};    // bumped with every wake-up of the progress thread (a spinning one sees it)
 };
 
 namespace {
@@ -262,6 +270,7 @@ void execute(rt_rank* c, rt_op id, std::unique_lock<std::mutex>& lk) {
         c->world->mail[std::make_tuple(c->id, op.peer, wire_tag(op.tag, op.options))].push_back(std::move(m));
       }
       rt_rank* dst = c->world->ranks[op.peer].get();
+      dst->signals.fetch_add(1, std::memory_order_release);
       dst->work_cv.notify_all();
       complete(c, id);
       break;
@@ -311,7 +320,24 @@ void progress_loop(rt_rank* c) {
       did = true;
     }
     if (poll_recvs(c)) did = true;
-    if (!did) c->work_cv.wait_for(lk, std::chrono::microseconds(200));
+    if (!did) {
+      // A dependency chain across ranks is a sequence of wake-ups; a condition variable costs tens of
+      // microseconds each.  So the thread first spins for a short while (lock released) on the counter that every
+      // waker bumps, and only then goes to sleep.
+      const uint64_t seen = c->signals.load(std::memory_order_acquire);
+      lk.unlock();
+      const auto t0 = std::chrono::steady_clock::now();
+      int polls = 0;
+      while (c->signals.load(std::memory_order_acquire) == seen && !c->stop.load()) {
+        if ((++polls & 63) == 0) {
+          if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(kSpinMicros)) break;
+          std::this_thread::yield();
+        }
+      }
+      lk.lock();
+      if (c->signals.load(std::memory_order_acquire) == seen && !c->stop.load())
+        c->work_cv.wait_for(lk, std::chrono::microseconds(200));
+    }
   }
 }
 
@@ -499,6 +525,7 @@ int rt_op_post(rt_rank* c, rt_op op) {
     if (op < 0 || op >= (rt_op)c->ops.size() || !c->ops[op]) return RT_ERROR;
     post_locked(c, op);
   }
+  c->signals.fetch_add(1, std::memory_order_release);
   c->work_cv.notify_all();
   return RT_SUCCESS;
 }
@@ -535,6 +562,18 @@ int rt_op_wait(rt_rank* c, rt_op id, double timeout_s) {
   const int64_t want = op.waited.load() + 1;
   auto pred = [&] { return op.completed.load() >= want; };
   if (timeout_s <= 0) timeout_s = kDefaultWaitSeconds;    // no wait is unbounded
+  if (!pred()) {                                          // spin briefly before sleeping (see progress_loop)
+    lk.unlock();
+    const auto t0 = std::chrono::steady_clock::now();
+    int polls = 0;
+    while (!pred()) {
+      if ((++polls & 63) == 0) {
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(kSpinMicros)) break;
+        std::this_thread::yield();
+      }
+    }
+    lk.lock();
+  }
   if (!c->cv.wait_for(lk, std::chrono::duration<double>(timeout_s), pred)) return RT_TIMEOUT;
   op.waited.store(want);
   return RT_SUCCESS;
@@ -835,6 +874,55 @@ int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op*
   *sync_op = rt_op_nop(c, RT_DEP_OR);
   rt_op_hb(c, st, *sync_op);
   *start = st;
+  return RT_SUCCESS;
+}
+
+// Micro-benchmark of the runtime by itself (no interpreter in the loop): `ranks` native threads run the protocol
+// of the reference's allreduce programs on int32 vectors of `count` elements, checked against the closed form.
+//   fresh = 1: a new schedule per iteration — create, post, wait, delete (evaluation/allreduce.c:44-72);
+//   fresh = 0: one persistent schedule posted `iters` times (evaluation/allreduce_inplace.c, benchmark/allreduce.c).
+// out_us[0] = mean microseconds per iteration (slowest rank), out_us[1] = creation of the first schedule,
+// out_us[2] = 1.0 if every result was right.
+int rt_bench_allreduce(int ranks, int64_t count, int iters, int fresh, double* out_us) {
+  if (ranks < 1 || count < 1 || iters < 1) return RT_ERROR;
+  rt_world* w = rt_world_create(ranks);
+  std::vector<double> per(ranks, 0.0), create(ranks, 0.0);
+  std::vector<int> ok(ranks, 1);
+  std::atomic<int> arrived{0};
+  auto body = [&](int r) {
+    rt_rank* c = rt_world_rank(w, r);
+    std::vector<int32_t> snd(count), rcv(count);
+    rt_buf bs = rt_buffer_create(c, snd.data(), count, RT_INT32), br = rt_buffer_create(c, rcv.data(), count, RT_INT32);
+    auto t0 = std::chrono::steady_clock::now();
+    rt_sched s = rt_allreduce(c, bs, br, 0, RT_SUM);
+    create[r] = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+    arrived.fetch_add(1);
+    while (arrived.load() < ranks) std::this_thread::yield();
+    const int warm = 5;
+    std::chrono::steady_clock::time_point start;
+    for (int it = 0; it < iters + warm; ++it) {
+      if (it == warm) start = std::chrono::steady_clock::now();
+      for (int64_t j = 0; j < count; ++j) { snd[j] = (int32_t)(it + j); rcv[j] = 0; }
+      if (fresh && it > 0) s = rt_allreduce(c, bs, br, it & 0x7f, RT_SUM);
+      rt_schedule_post(c, s);
+      if (rt_schedule_wait(c, s, 30.0) != RT_SUCCESS) { ok[r] = 0; break; }
+      for (int64_t j = 0; j < count; ++j)
+        if (rcv[j] != (int32_t)((it + j) * ranks)) { ok[r] = 0; break; }
+      if (fresh) rt_schedule_delete(c, s);
+    }
+    per[r] = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - start).count() / iters;
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < ranks; ++r) th.emplace_back(body, r);
+  for (auto& t : th) t.join();
+  rt_world_destroy(w);
+  double worst = 0, cr = 0, good = 1;
+  for (int r = 0; r < ranks; ++r) {
+    if (per[r] > worst) worst = per[r];
+    if (create[r] > cr) cr = create[r];
+    if (!ok[r]) good = 0;
+  }
+  out_us[0] = worst; out_us[1] = cr; out_us[2] = good;
   return RT_SUCCESS;
 }
 

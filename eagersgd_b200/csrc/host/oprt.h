@@ -133,6 +133,9 @@ rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined);
 /* limiter: posting `start` fires async[0..n-1] in turn, then sync, round-robin */
 int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op* sync_op);
 
+/* native micro-benchmark (threads of this process as ranks); out_us: per-iteration, first creation, all-correct flag */
+int rt_bench_allreduce(int ranks, int64_t count, int iters, int fresh, double* out_us);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,6 @@
 """Micro-benchmark of the host operation runtime: creation, execution and deletion of an allreduce schedule.
 
-    python -m eagersgd_b200.parallel.bench_oprt [--ranks 4] [--count 1024] [--iters 100]
+    python -m eagersgd_b200.parallel.bench_oprt [--ranks 4] [--count 1024] [--iters 100] [--python-threads]
 
 The protocol of the reference's benchmark (fflib2 benchmark/allreduce.c:11-99: int32, 100 timed iterations,
 schedule creation / execution / deletion recorded separately), with ranks as threads of this process and a
@@ -59,13 +59,36 @@ def run(ranks: int, count: int, iters: int) -> dict:
             "numpy_sum_us": 1e6 * t_numpy, "wall_s": t_total}
 
 
+def run_native(ranks: int, count: int, iters: int) -> dict:
+    """The same protocol with native threads as ranks (no interpreter in the loop): microseconds per post + wait of
+    a persistent schedule, and per create + post + wait + delete of a fresh one (the reference's
+    evaluation/allreduce.c cycle)."""
+    import ctypes as C
+    lib = R.lib()
+    lib.rt_bench_allreduce.argtypes = [C.c_int, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_double)]
+    out = {}
+    for name, fresh, n in (("persistent", 0, iters), ("fresh", 1, max(iters, 256))):
+        v = (C.c_double * 3)()
+        if lib.rt_bench_allreduce(ranks, count, n, fresh, v) != 0:
+            raise RuntimeError("native benchmark failed")
+        out[name + "_us"] = v[0]
+        out["correct"] = out.get("correct", True) and v[2] == 1.0
+        if not fresh:
+            out["first_create_us"] = v[1]
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--count", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=100)
+    ap.add_argument("--python-threads", action="store_true",
+                    help="drive the ranks from Python threads (measures the binding and the interpreter as well)")
     args = ap.parse_args(argv)
-    print(json.dumps(run(args.ranks, args.count, args.iters)))
+    res = run(args.ranks, args.count, args.iters) if args.python_threads else \
+        dict(ranks=args.ranks, count=args.count, dtype="int32", iters=args.iters, native=run_native(args.ranks, args.count, args.iters))
+    print(json.dumps(res))
     return 0
 
 

@@ -230,6 +230,14 @@ def test_runtime_microbenchmark_reports_three_phases():
     assert r["correct"] and r["create_us"] > 0 and r["execute_us"] > 0 and r["delete_us"] >= 0
 
 
+def test_native_microbenchmark_checks_its_results():
+    """Native threads as ranks: persistent reposts and fresh create / post / wait / delete cycles, both checked
+    against the closed form inside the loop."""
+    from eagersgd_b200.parallel.bench_oprt import run_native
+    r = run_native(ranks=3, count=257, iters=40)
+    assert r["correct"] and 0 < r["persistent_us"] < 1e5 and 0 < r["fresh_us"] < 1e5
+
+
 @pytest.mark.parametrize("world", [2, 3, 5, 8])
 def test_activation_stress_300_rounds(world):
     """The reference loops its activation test 300 times from a shell script (evaluation/test_activation.sh);
