@@ -250,3 +250,12 @@ def test_adaptive_grace_window_tracks_arrival_spread():
     [t.start() for t in th]
     [t.join() for t in th]
     assert sum(1 for f in fresh[0][20:] if f == world) >= 10
+
+
+def test_cpu_channel_benchmark_runs_the_skewed_loop():
+    """The SGD-loop protocol of the reference's timing programs on the CPU backend: a late rank costs the solo
+    collective nothing, the synchronous one its lateness."""
+    from eagersgd_b200.parallel.bench_cpu_channel import run
+    solo = run(2, 1024, "solo", iters=6)
+    sync = run(2, 1024, "sync", iters=6)
+    assert 0 < solo < sync and sync > 300.0      # rank 1 sleeps 1 ms: the mean wait of two ranks is about 500 us
