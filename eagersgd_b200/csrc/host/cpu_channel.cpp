@@ -9,6 +9,8 @@
 #include <stdint.h>
 #include <string.h>
 #include <stdlib.h>
+#include <thread>
+#include <vector>
 #include "../protocol/channel.h"
 #include "../protocol/step.h"
 #include "../protocol/env_host.h"
@@ -43,47 +45,86 @@ template <class T> struct IsFloat { static const bool v = false; };
 template <> struct IsFloat<float> { static const bool v = true; };
 template <> struct IsFloat<double> { static const bool v = true; };
 
+// Large vectors are worked on by a few threads of the rank: one core does not reach the memory bandwidth of the
+// host.  ESGD_CPU_THREADS sets the number (default: the cores divided among the ranks of the world, at most 4);
+// ranges below 256 K elements per thread stay on the calling thread.
+int data_threads(int world) {
+  static const int forced = [] { const char* e = getenv("ESGD_CPU_THREADS"); return e ? atoi(e) : 0; }();
+  if (forced > 0) return forced;
+  int hw = (int)std::thread::hardware_concurrency();
+  int t = hw / (world > 0 ? world : 1);
+  return t < 1 ? 1 : (t > 4 ? 4 : t);
+}
+
+template <class F>
+void parallel_ranges(uint64_t lo, uint64_t hi, int world, F fn) {
+  const uint64_t n = hi > lo ? hi - lo : 0;
+  int t = data_threads(world);
+  const uint64_t kMinPerThread = 1u << 18;
+  if ((uint64_t)t > n / kMinPerThread) t = (int)(n / kMinPerThread);
+  if (t <= 1) { fn(lo, hi); return; }
+  const uint64_t per = ((n + t - 1) / t + 1023) / 1024 * 1024;      // whole blocks of the reduction loop
+  std::vector<std::thread> th;
+  for (int i = 1; i < t; ++i) {
+    const uint64_t a = lo + per * i, b = a + per < hi ? a + per : hi;
+    if (a < hi) th.emplace_back([=] { fn(a, b); });
+  }
+  fn(lo, lo + per < hi ? lo + per : hi);
+  for (auto& x : th) x.join();
+}
+
 // Participant: out = scale * sum(contributor slots); this participant's share of
 // the vector is also delivered to the mailbox of every absent rank.
 template <class T>
-void data_participant(void** bases, const SegLayout& L, const Plan& plan, uint64_t count, T* out) {
+void data_participant(void** bases, const SegLayout& L, const Plan& plan, uint64_t count, T* out, int world) {
   const T* src[kMaxRanks];
   for (int s = 0; s < plan.n_src; ++s)
     src[s] = (const T*)((char*)bases[plan.src_rank[s]] + L.slot_off[plan.src_parity[s]]);
   const T scale = IsFloat<T>::v ? (T)plan.scale : (T)1;
-  const uint64_t BLK = 1024;
-  for (uint64_t b = 0; b < count; b += BLK) {
-    uint64_t n = count - b < BLK ? count - b : BLK;
-    T acc[BLK];
-    for (uint64_t e = 0; e < n; ++e) acc[e] = src[0][b + e];
-    for (int s = 1; s < plan.n_src; ++s)
-      for (uint64_t e = 0; e < n; ++e) acc[e] += src[s][b + e];
-    for (uint64_t e = 0; e < n; ++e) out[b + e] = acc[e] * scale;
-  }
+  const int n_src = plan.n_src;
+  parallel_ranges(0, count, world, [&](uint64_t lo, uint64_t hi) {
+    const uint64_t BLK = 1024;
+    for (uint64_t b = lo; b < hi; b += BLK) {      // the same blocks and the same order of additions on any thread count
+      uint64_t n = hi - b < BLK ? hi - b : BLK;
+      T acc[BLK];
+      for (uint64_t e = 0; e < n; ++e) acc[e] = src[0][b + e];
+      for (int s = 1; s < n_src; ++s)
+        for (uint64_t e = 0; e < n; ++e) acc[e] += src[s][b + e];
+      for (uint64_t e = 0; e < n; ++e) out[b + e] = acc[e] * scale;
+    }
+  });
   if (plan.n_push > 0) {
     uint64_t per = (count + plan.part_count - 1) / plan.part_count;
     uint64_t lo = per * (uint64_t)plan.part_index;
     uint64_t hi = lo + per < count ? lo + per : count;
     for (int n = 0; n < plan.n_push; ++n) {
       T* mb = (T*)((char*)bases[plan.push_rank[n]] + L.mbox_off);
-      if (plan.push_accum[n]) for (uint64_t e = lo; e < hi; ++e) mb[e] += out[e];
-      else for (uint64_t e = lo; e < hi; ++e) mb[e] = out[e];
+      const bool accum = plan.push_accum[n];
+      parallel_ranges(lo, hi, world, [&](uint64_t a, uint64_t b) {
+        if (accum) for (uint64_t e = a; e < b; ++e) mb[e] += out[e];
+        else for (uint64_t e = a; e < b; ++e) mb[e] = out[e];
+      });
     }
   }
 }
 
 template <class T>
-void fold_into(void* slot, const void* grad, uint64_t count) {
+void fold_into(void* slot, const void* grad, uint64_t count, int world) {
   T* s = (T*)slot;
   const T* g = (const T*)grad;
-  for (uint64_t e = 0; e < count; ++e) s[e] += g[e];
+  parallel_ranges(0, count, world, [&](uint64_t a, uint64_t b) { for (uint64_t e = a; e < b; ++e) s[e] += g[e]; });
+}
+
+void parallel_copy(void* dst, const void* src, uint64_t bytes, int world) {
+  parallel_ranges(0, bytes / 4, world, [&](uint64_t a, uint64_t b) { memcpy((char*)dst + a * 4, (const char*)src + a * 4, (b - a) * 4); });
+  if (bytes % 4) memcpy((char*)dst + bytes / 4 * 4, (const char*)src + bytes / 4 * 4, bytes % 4);
 }
 
 template <class T>
-void run_data(void** bases, int rank, const SegLayout& L, const Plan& plan, uint64_t count, void* out) {
+void run_data(void** bases, int rank, const SegLayout& L, const Plan& plan, uint64_t count, void* out, int world) {
   T* o = (T*)out;
-  if (plan.role == ROLE_PARTICIPANT) data_participant<T>(bases, L, plan, count, o);
-  else if (plan.role == ROLE_DRAIN) memcpy(o, (char*)bases[rank] + L.mbox_off, count * sizeof(T));
+  if (plan.role == ROLE_PARTICIPANT) data_participant<T>(bases, L, plan, count, o, world);
+  else if (plan.role == ROLE_DRAIN) parallel_copy(o, (char*)bases[rank] + L.mbox_off, count * sizeof(T), world);
   else memset(o, 0, count * sizeof(T));
 }
 
@@ -150,13 +191,13 @@ uint32_t esgd_cpu_step(void** bases, const esgd_cpu_params* p, const void* grad,
     void* slot = (char*)bases[p->rank] + L.slot_off[k % kSlotDepth];
     if (slot_fate<HostEnv>(me, pol, k) == SLOT_FOLD) {
       switch (p->dtype) {   // the gradient of epoch k-2 was never picked up: it rides along with this one
-        case DT_F32: fold_into<float>(slot, grad, p->count); break;
-        case DT_F64: fold_into<double>(slot, grad, p->count); break;
-        case DT_I32: fold_into<int32_t>(slot, grad, p->count); break;
-        default: fold_into<int64_t>(slot, grad, p->count); break;
+        case DT_F32: fold_into<float>(slot, grad, p->count, p->world); break;
+        case DT_F64: fold_into<double>(slot, grad, p->count, p->world); break;
+        case DT_I32: fold_into<int32_t>(slot, grad, p->count, p->world); break;
+        default: fold_into<int64_t>(slot, grad, p->count, p->world); break;
       }
     } else {
-      memcpy(slot, grad, p->count * (uint64_t)dtype_size(p->dtype));
+      parallel_copy(slot, grad, p->count * (uint64_t)dtype_size(p->dtype), p->world);
     }
     ctl_step<HostEnv>(v, cfg, pol, &plan);
   } else {
@@ -164,10 +205,10 @@ uint32_t esgd_cpu_step(void** bases, const esgd_cpu_params* p, const void* grad,
     plan.role = ROLE_ABORT;
   }
   switch (p->dtype) {
-    case DT_F32: run_data<float>(bases, p->rank, L, plan, p->count, out); break;
-    case DT_F64: run_data<double>(bases, p->rank, L, plan, p->count, out); break;
-    case DT_I32: run_data<int32_t>(bases, p->rank, L, plan, p->count, out); break;
-    default: run_data<int64_t>(bases, p->rank, L, plan, p->count, out); break;
+    case DT_F32: run_data<float>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    case DT_F64: run_data<double>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    case DT_I32: run_data<int32_t>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    default: run_data<int64_t>(bases, p->rank, L, plan, p->count, out, p->world); break;
   }
   finish_step<HostEnv>(v, cfg, &plan);
   if (info) {
@@ -196,10 +237,10 @@ uint32_t esgd_cpu_flush(void** bases, const esgd_cpu_params* p, void* out, esgd_
   memset(&plan, 0, sizeof(plan));
   ctl_flush<HostEnv>(v, cfg, &plan);
   switch (p->dtype) {
-    case DT_F32: run_data<float>(bases, p->rank, L, plan, p->count, out); break;
-    case DT_F64: run_data<double>(bases, p->rank, L, plan, p->count, out); break;
-    case DT_I32: run_data<int32_t>(bases, p->rank, L, plan, p->count, out); break;
-    default: run_data<int64_t>(bases, p->rank, L, plan, p->count, out); break;
+    case DT_F32: run_data<float>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    case DT_F64: run_data<double>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    case DT_I32: run_data<int32_t>(bases, p->rank, L, plan, p->count, out, p->world); break;
+    default: run_data<int64_t>(bases, p->rank, L, plan, p->count, out, p->world); break;
   }
   finish_step<HostEnv>(v, cfg, &plan);
   if (info) {

@@ -259,3 +259,39 @@ def test_cpu_channel_benchmark_runs_the_skewed_loop():
     solo = run(2, 1024, "solo", iters=6)
     sync = run(2, 1024, "sync", iters=6)
     assert 0 < solo < sync and sync > 300.0      # rank 1 sleeps 1 ms: the mean wait of two ranks is about 500 us
+
+
+@pytest.mark.parametrize("mode", ["sync", "solo"])
+def test_large_vectors_on_several_threads_per_rank(mode):
+    """Vectors large enough for the rank's helper threads (from 256 K elements per thread), with a length that is
+    no multiple of the reduction block: position-dependent values come out summed element by element, replicas
+    agree in the eager mode, nothing is torn at the thread boundaries."""
+    world, count, steps = 2, (1 << 20) + 12345, 4
+    segs = LocalSegments(world, count, np.float32)
+    base = (np.arange(count) % 97).astype(np.float32)
+    applied = [np.zeros(count, dtype=np.float64) for _ in range(world)]
+    errors = []
+
+    def worker(r):
+        try:
+            ch = CpuChannel(segs.bases, r, world, count, np.float32, mode=mode, limiter=2, average="sum", timeout_s=60)
+            for k in range(1, steps + 1):
+                if mode == "solo" and r == 1:
+                    time.sleep(0.003)
+                out, info = ch.step(base * (r + 1) + k)
+                applied[r] += out
+            out, _ = ch.flush()
+            applied[r] += out
+        except Exception as e:  # noqa
+            errors.append((r, repr(e)))
+
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errors, errors
+    total = sum(base.astype(np.float64) * (r + 1) * steps + sum(range(1, steps + 1)) for r in range(world))
+    if mode == "sync":
+        assert np.array_equal(applied[0], total) and np.array_equal(applied[1], total)
+    else:
+        assert np.array_equal(applied[0], applied[1])               # every replica applied the same total
+        assert np.all(applied[0] <= total + 1e-6) and applied[0].sum() > 0
