@@ -230,3 +230,25 @@ def test_dataset_accuracy_metric():
         model.weight.copy_(torch.eye(4))
     assert DatasetAccuracy(batches).measure(model) == 0.75
     assert DatasetAccuracy(batches, max_batches=1).measure(model) == 1.0
+
+
+def test_update_rule_optimizer_of_the_tutorial():
+    """The optimizer written in docs/custom_optimizer.md: one overridden method, driven by an executor."""
+    from eagersgd_b200.optim.base import UpdateRuleOptimizer
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+
+    class SignSGD(UpdateRuleOptimizer):
+        def __init__(self, executor, loss="loss", learning_rate=0.01):
+            super().__init__(executor, loss)
+            self.hyper["learning_rate"] = learning_rate
+
+        def update_rule(self, grad, old_param, name):
+            return old_param - self.hyper["learning_rate"] * grad.sign()
+
+    torch.manual_seed(0)
+    opt = SignSGD(GraphExecutor(torch.nn.Linear(4, 2), loss_fn=classification_loss))
+    batch = {"x": torch.randn(8, 4), "y": torch.randint(0, 2, (8,))}
+    first = float(opt.step(batch)["loss"])
+    for _ in range(30):
+        last = float(opt.step(batch)["loss"])
+    assert last < first
