@@ -130,3 +130,52 @@ def test_imagenet_from_disk_folder_shards_and_preprocessing(tmp_path):
     by_label = {int(l): i for i, l in enumerate(sv.labels)}
     i_sh = by_label[int(val.labels[-1])]
     assert sv[i_sh]["x"].shape == (3, 224, 224)
+
+
+def test_download_helpers_against_a_mirror_on_disk(tmp_path):
+    """``real_download`` and the MNIST helper against a ``file://`` mirror (no network here): files arrive once, are
+    kept on a second call, load as a data set; a wrong checksum removes the file; a missing file leaves nothing
+    behind; archives unpack inside their folder only."""
+    import gzip
+    import os
+    import struct
+    import tarfile
+    import pytest
+    from eagersgd_b200.data.dataset import load_mnist
+    from eagersgd_b200.utils import download as D
+    mirror = tmp_path / "mirror"
+    mirror.mkdir()
+
+    def idx(arr):
+        arr = np.asarray(arr, dtype=np.uint8)
+        return struct.pack(">I", 0x0800 | arr.ndim) + struct.pack(">" + "I" * arr.ndim, *arr.shape) + arr.tobytes()
+
+    rng = np.random.RandomState(0)
+    for stem, arr in (("train-images-idx3-ubyte", rng.randint(0, 255, (12, 28, 28))), ("train-labels-idx1-ubyte", np.arange(12) % 10),
+                      ("t10k-images-idx3-ubyte", rng.randint(0, 255, (4, 28, 28))), ("t10k-labels-idx1-ubyte", np.arange(4))):
+        with gzip.open(mirror / (stem + ".gz"), "wb") as f:
+            f.write(idx(arr))
+    cache = tmp_path / "cache"
+    paths = D.download_mnist_and_get_file_paths(str(cache), base_url="file://" + str(mirror) + "/")
+    assert set(paths) == {"train_images", "train_labels", "test_images", "test_labels"}
+    stamp = os.path.getmtime(paths["train_images"])
+    assert D.download_mnist_and_get_file_paths(str(cache), base_url="file:///nowhere/") == paths     # kept, not fetched again
+    assert os.path.getmtime(paths["train_images"]) == stamp
+    train, test = load_mnist(os.path.dirname(paths["train_images"]))
+    assert len(train) == 12 and len(test) == 4
+    name = "train-labels-idx1-ubyte.gz"
+    with pytest.raises(IOError, match="checksum"):
+        D.real_download("file://" + str(mirror), [name], "other", str(cache), sha256={name: "0" * 64})
+    assert not (cache / "other" / name).exists()
+    with pytest.raises(IOError):
+        D.real_download("file://" + str(mirror), ["missing.bin"], "other", str(cache))
+    assert list((cache / "other").iterdir()) == []
+    good = D.real_download("file://" + str(mirror), [name], "other", str(cache), sha256={name: D.sha256_of(str(mirror / name))})
+    assert D.unpack(good[name]).endswith("train-labels-idx1-ubyte")
+    evil = tmp_path / "evil.tar.gz"
+    with tarfile.open(evil, "w:gz") as t:
+        info = tarfile.TarInfo("../escaped.txt")
+        info.size = 0
+        t.addfile(info)
+    with pytest.raises(IOError, match="escapes"):
+        D.unpack(str(evil), str(tmp_path / "x"))
