@@ -21,8 +21,7 @@ MNIST_FILES = {"train_images": "train-images-idx3-ubyte.gz", "train_labels": "tr
                "test_images": "t10k-images-idx3-ubyte.gz", "test_labels": "t10k-labels-idx1-ubyte.gz"}
 MNIST_URL = "http://yann.lecun.com/exdb/mnist/"
 FASHION_MNIST_URL = "http://fashion-mnist.s3-website.eu-central-1.amazonaws.com/"
-CIFAR10_URL, CIFAR10_FILE = "https://www.cs.toronto.edu/~kriz/", "cifar-10-binary.tar.gz"
-CIFAR100_FILE = "cifar-100-binary.tar.gz"
+CIFAR10_URL, CIFAR10_FILE = "https://www.cs.toronto.edu/~kriz/", "cifar-10-python.tar.gz"   # what load_cifar10 reads
 
 
 def default_cache_dir(sub_folder: str = "") -> str:
@@ -119,8 +118,9 @@ def download_fashion_mnist_and_get_file_paths(folder: str = "", base_url: str = 
 
 
 def download_cifar10_and_get_folder(folder: str = "", base_url: str = CIFAR10_URL) -> str:
-    """The CIFAR-10 binary batches, fetched and unpacked; returns the folder that holds ``data_batch_*.bin``."""
+    """The CIFAR-10 python batches, fetched and unpacked; returns the folder that holds ``data_batch_1`` ...
+    ``test_batch`` (the argument of ``data.dataset.load_cifar10``)."""
     got = real_download(base_url, [CIFAR10_FILE], "cifar10", folder)
     root = unpack(got[CIFAR10_FILE])
-    sub = os.path.join(root, "cifar-10-batches-bin")
+    sub = os.path.join(root, "cifar-10-batches-py")
     return sub if os.path.isdir(sub) else root
