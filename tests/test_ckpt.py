@@ -93,3 +93,21 @@ def test_block_names_match_golden_checkpoints(cfg):
     assert last_conv + "/kernel" in names and last_bn + "/gamma" in names
     nxt = lambda s: s.rsplit("_", 1)[0] + "_%d" % (int(s.rsplit("_", 1)[1]) + 1)
     assert nxt(last_conv) + "/kernel" not in names and nxt(last_bn) + "/gamma" not in names
+
+
+def test_rank_directories_become_copies_of_rank_zero(tmp_path):
+    """Between two jobs of a chained run (the reference's synchm.sh): ranks 1.. get rank 0's files, stale files go."""
+    from eagersgd_b200.ckpt.sync_dirs import main, sync_dirs
+    for r in range(3):
+        d = tmp_path / str(r)
+        d.mkdir()
+        (d / "checkpoint").write_text("rank %d" % r)
+    (tmp_path / "2" / "stale.bin").write_text("old")
+    (tmp_path / "0" / "sub").mkdir()
+    (tmp_path / "0" / "sub" / "weights.npz").write_text("w")
+    assert sync_dirs(str(tmp_path)) == 2
+    for r in (1, 2):
+        assert (tmp_path / str(r) / "checkpoint").read_text() == "rank 0"
+        assert (tmp_path / str(r) / "sub" / "weights.npz").read_text() == "w"
+    assert not (tmp_path / "2" / "stale.bin").exists()
+    assert main([str(tmp_path), "--world", "4"]) == 0 and (tmp_path / "3" / "checkpoint").read_text() == "rank 0"
