@@ -57,6 +57,9 @@ def define_resnet(p, default_size=50, sizes=(18, 34, 50, 101, 152, 200)):
     g.add_argument("--horovod", "-hvd", action="store_true", help="same as --mode ddp (synchronous NCCL baseline)")
     g.add_argument("--limiter", type=int, default=32)
     g.add_argument("--bucket_mb", type=float, default=25.0)
+    g.add_argument("--accumulate", action="store_true",
+                   help="fold a gradient that no round picked up into the rank's next one (default: it is superseded, "
+                        "as in the reference)")
     g.add_argument("--baseseed", type=int, default=0)
     g.add_argument("--lrmult", type=float, default=1.0)
     g.add_argument("--disablewarmup", action="store_true")

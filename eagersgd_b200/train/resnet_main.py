@@ -133,7 +133,7 @@ def main(argv=None):
                      limiter=args.limiter, bucket_mb=args.bucket_mb, lr=lr_fn(0) * args.lrmult, momentum=0.9,
                      weight_decay=info["wd"], compute_dtype=getattr(torch, args.torch_dtype),
                      inner_optimizer=(lambda ps, **kw: LARS(ps, lr=kw["lr"], momentum=0.9, weight_decay=info["wd"]))
-                     if args.lars else None, loss_scale=args.loss_scale)
+                     if args.lars else None, loss_scale=args.loss_scale, accumulate=args.accumulate)
     if args.pretrained_model_checkpoint_path:
         ckpt.import_tf_layout(step.model, args.pretrained_model_checkpoint_path, exclude=("dense",))
         if hasattr(step.opt, "refresh_master_from_params"):
