@@ -23,6 +23,7 @@ import time
 import numpy as np
 import torch
 
+from .model_helpers import past_stop_threshold
 from .. import ckpt
 from ..data import OrderedSampler, ReplicateBatch, ShuffleSampler, SyntheticImageDataset, load_cifar10, partition
 from ..models.resnet import cifar_resnet, imagenet_resnet
@@ -206,7 +207,7 @@ def main(argv=None):
                 a1, a5 = evaluate(step, val_sampler, device)
                 if group.rank == 0:
                     logger.log_evaluation_result({"accuracy": a1, "accuracy_top_5": a5, "global_step": global_step})
-                if args.stop_threshold is not None and a1 >= args.stop_threshold:
+                if past_stop_threshold(args.stop_threshold, a1):
                     break
             if args.resync_epochs and (epoch + 1) % args.resync_epochs == 0:
                 ckpt.resync_from_rank0(step.model, step.opt if hasattr(step.opt, "resync_from_rank0") else None, group)

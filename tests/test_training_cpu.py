@@ -252,3 +252,28 @@ def test_update_rule_optimizer_of_the_tutorial():
     for _ in range(30):
         last = float(opt.step(batch)["loss"])
     assert last < first
+
+
+def test_model_helpers_and_the_synthetic_integration_run(tmp_path):
+    from eagersgd_b200.train import resnet_main
+    from eagersgd_b200.train.model_helpers import (MockBenchmarkLogger, apply_clean, generate_synthetic_data,
+                                                   past_stop_threshold, run_synthetic)
+    assert not past_stop_threshold(None, 0.9) and past_stop_threshold(0.5, 0.5) and not past_stop_threshold(0.5, 0.4)
+    with pytest.raises(ValueError):
+        past_stop_threshold("high", 0.1)
+    it = generate_synthetic_data((2, 3), 1.5, label_shape=(2,), label_value=7, batches=3)
+    batches = list(it)
+    assert len(batches) == 3 and torch.all(batches[0][0] == 1.5) and torch.all(batches[2][1] == 7)
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "x").write_text("1")
+    apply_clean(False, str(d))
+    assert d.exists()
+    apply_clean(True, str(d))
+    assert not d.exists()
+    log = MockBenchmarkLogger()
+    log.log_evaluation_result({"accuracy": 0.5, "global_step": 3})
+    assert log.logged_metric == [{"name": "accuracy", "value": 0.5, "unit": None, "global_step": 3, "extras": None}]
+    rc = run_synthetic(resnet_main.main, str(tmp_path), ["--dataset", "cifar10", "-rs", "8", "-bs", "8", "--dtype", "fp32",
+                                                          "--synthetic_train_size", "16"], max_train=1)
+    assert rc == 0 and [p for p in tmp_path.iterdir() if p.is_dir()] == []      # the scratch directory is gone
