@@ -25,6 +25,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("network_inference.py", ["reference"]),
     ("onnxtest.py", ["all"]),
     ("synthetic_dataset.py", ["--resnet-size", "8", "--size", "32", "--batch", "8", "--steps", "2"]),
+    ("imbalance_modes_cpu.py", ["--ranks", "3", "--steps", "15", "--buckets", "2"]),
     ("deepbench/gemm_overhead.py", ["--limit", "2", "--reruns", "2"]),
     ("deepbench/conv_overhead.py", ["--limit", "1", "--reruns", "2"]),
 ])
