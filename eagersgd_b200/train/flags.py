@@ -61,6 +61,11 @@ def define_resnet(p, default_size=50, sizes=(18, 34, 50, 101, 152, 200)):
                    help="fold a gradient that no round picked up into the rank's next one (default: it is superseded, "
                         "as in the reference)")
     g.add_argument("--baseseed", type=int, default=0)
+    g.add_argument("--shuffleaug", "-saug", type=int, default=1,
+                   help="groups of this many consecutive ranks read the same samples in the same order (each with its own "
+                        "augmentation); the data are divided among world / shuffleaug groups")
+    g.add_argument("--regime", "-fr", type=int, default=0, choices=[0, 1, 2],
+                   help="ImageNet learning-rate boundaries: 0 = 30/60/80/90 epochs, 1 = 30/35/39/40, 2 = 15/20/22/30")
     g.add_argument("--lrmult", type=float, default=1.0)
     g.add_argument("--disablewarmup", action="store_true")
     g.add_argument("--start_epoch", type=int, default=0)

@@ -68,8 +68,13 @@ def build_data(args, info, group):
             val = ImageNetFolder(args.data_dir, "val", seed=args.baseseed)
         info["train"], info["val"] = len(train), len(val)
         train.num_parallel_calls = val.num_parallel_calls = max(int(args.num_parallel_calls), 1)
-    shard = partition(train, group.rank, group.world)   # dataset.take(n // num_workers) in the reference (:94-96)
-    return ShuffleSampler(shard, args.batch_size, seed=args.baseseed + 17), OrderedSampler(val, args.batch_size)
+    # dataset.take(n // num_workers) in the reference (:94-96); with --shuffleaug M the workers are groups of M
+    # consecutive ranks that share a part of the data and a shuffle seed (:82-88, :494-507)
+    m = max(int(getattr(args, "shuffleaug", 1)), 1)
+    workers = max(group.world // m, 1)
+    shard = partition(train, min(group.rank // m, workers - 1), workers)
+    seed = args.baseseed + 17 + (group.rank // m if m > 1 else 0)
+    return ShuffleSampler(shard, args.batch_size, seed=seed), OrderedSampler(val, args.batch_size)
 
 
 def make_injector(args, group, step_time):
@@ -125,9 +130,12 @@ def main(argv=None):
             p_.requires_grad_(name.startswith("fc."))
     hooks = parse_hooks(args.hooks)
     global_batch = args.batch_size * group.world
-    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // global_batch, 1)
+    # an epoch is one pass of the groups of ranks that read different data (all ranks unless --shuffleaug)
+    epoch_batch = args.batch_size * max(group.world // max(int(args.shuffleaug), 1), 1)
+    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // epoch_batch, 1)
     if args.dataset == "imagenet":
-        lr_fn = imagenet_schedule(global_batch, info["train"], warmup=not args.disablewarmup, start_epoch=args.start_epoch)
+        lr_fn = imagenet_schedule(global_batch, info["train"], warmup=not args.disablewarmup, start_epoch=args.start_epoch,
+                                  regime=args.regime)
     else:
         lr_fn = cifar10_schedule(global_batch, info["train"])
     step = TrainStep(model, group, impl="ddp" if args.mode == "ddp" else "ours", mode=args.mode if args.mode != "ddp" else "sync",
@@ -142,7 +150,7 @@ def main(argv=None):
     global_step = ckpt.load(step.model, step.opt if hasattr(step.opt, "state_dict") else None, args.model_dir, group.rank)
 
     train_sampler, val_sampler = build_data(args, info, group)
-    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // global_batch, 1)   # a data set read from disk knows its size
+    steps_per_epoch = max((args.synthetic_train_size or info["train"]) // epoch_batch, 1)   # a data set read from disk knows its size
     logger = BenchmarkFileLogger(args.benchmark_log_dir) if (
         args.benchmark_logger_type == "BenchmarkFileLogger" and args.benchmark_log_dir) else BaseBenchmarkLogger()
     if group.rank == 0:

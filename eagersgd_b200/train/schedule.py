@@ -33,8 +33,13 @@ def learning_rate_with_decay(batch_size: int, batch_denom: int, num_images: int,
     return lr
 
 
-def imagenet_schedule(batch_size: int, num_images: int = 1281167, warmup: bool = True, start_epoch: int = 0):
-    return learning_rate_with_decay(batch_size, 256, num_images, [30, 60, 80, 90], [1, 0.1, 0.01, 0.001, 1e-4],
+# learning-rate boundaries (epochs) by --regime (imagenet_main_eagersgd.py:333-340): the full 90-epoch run and two short ones
+IMAGENET_REGIMES = {0: [30, 60, 80, 90], 1: [30, 35, 39, 40], 2: [15, 20, 22, 30]}
+
+
+def imagenet_schedule(batch_size: int, num_images: int = 1281167, warmup: bool = True, start_epoch: int = 0,
+                      regime: int = 0):
+    return learning_rate_with_decay(batch_size, 256, num_images, IMAGENET_REGIMES[regime], [1, 0.1, 0.01, 0.001, 1e-4],
                                     warmup=warmup, start_epoch=start_epoch)
 
 

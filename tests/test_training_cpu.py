@@ -277,3 +277,28 @@ def test_model_helpers_and_the_synthetic_integration_run(tmp_path):
     rc = run_synthetic(resnet_main.main, str(tmp_path), ["--dataset", "cifar10", "-rs", "8", "-bs", "8", "--dtype", "fp32",
                                                           "--synthetic_train_size", "16"], max_train=1)
     assert rc == 0 and [p for p in tmp_path.iterdir() if p.is_dir()] == []      # the scratch directory is gone
+
+
+def test_shuffleaug_groups_share_data_and_regime_moves_the_boundaries():
+    """--shuffleaug 2 on four ranks: ranks 0,1 and ranks 2,3 read the same samples in the same order, the two groups
+    different halves of the data; --regime selects the ImageNet learning-rate boundaries."""
+    from types import SimpleNamespace
+    from eagersgd_b200.train import resnet_main
+    from eagersgd_b200.train import flags as F
+    from eagersgd_b200.train.schedule import imagenet_schedule
+    p = F.build_parser("t")
+    p.add_argument("--synthetic_train_size", type=int, default=None)
+    args = F.resolve(p.parse_args(["--synthetic", "--synthetic_train_size", "64", "-bs", "4", "--shuffleaug", "2"]))
+    args.dataset = "cifar10"
+    info = dict(resnet_main.DATASETS["cifar10"])
+    firsts = []
+    for rank in range(4):
+        train, _ = resnet_main.build_data(args, info, SimpleNamespace(rank=rank, world=4))
+        b = next(iter(train))
+        x, y = (b["x"], b["y"]) if isinstance(b, dict) else b
+        firsts.append((len(train.dataset), np.asarray(y).tolist(), float(np.asarray(x, dtype=np.float64).sum())))
+    assert firsts[0] == firsts[1] and firsts[2] == firsts[3] and firsts[0] != firsts[2]
+    assert firsts[0][0] == 32                                   # two groups: half of the 64 samples each
+    lr0, lr2 = imagenet_schedule(256, 2560, warmup=False), imagenet_schedule(256, 2560, warmup=False, regime=2)
+    steps = 2560 // 256                                         # batches per epoch
+    assert lr0(steps * 16) == pytest.approx(0.1) and lr2(steps * 16) == pytest.approx(0.01)
