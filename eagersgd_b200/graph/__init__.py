@@ -4,3 +4,4 @@ from .executor import GraphNetwork, from_torch_resnet  # noqa: F401
 from .onnx_io import load_onnx, save_onnx, parse_onnx, dump_onnx  # noqa: F401
 from .reference_executor import ReferenceGraphExecutor  # noqa: F401
 from .onnx_ops import operator_class, operator_names, make_operation  # noqa: F401
+from .from_torch import from_torch_module, export_network  # noqa: F401

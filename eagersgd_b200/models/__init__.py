@@ -18,3 +18,9 @@ def create_model(name: str, **kw):
         depth = kw.pop("depth", 50 if dataset == "imagenet" else 32)
         return (imagenet_resnet if dataset == "imagenet" else cifar_resnet)(depth, **kw)
     return _FACTORIES[name](**kw)
+
+
+def export_network(name: str, file_path: str, **kw) -> str:
+    """Write a network of this zoo as an ``.onnx`` file and return the path (deep500/networks/__init__.py:6-21)."""
+    from ..graph.from_torch import export_network as _export
+    return _export(name, file_path, **kw)

@@ -220,3 +220,43 @@ def test_onnx_operator_classes():
     for n in names:                                                 # every class can be made and validated
         cls = operator_class(n)
         assert cls.__name__ == n and cls.MIN_INPUTS <= cls.MAX_INPUTS
+
+
+@pytest.mark.parametrize("name,kw,shape", [("simple_mnist", {}, (3, 1, 28, 28)), ("deep_mnist", {}, (2, 1, 28, 28)),
+                                           ("wide_resnet", dict(depth=10, widen=1), (2, 3, 32, 32))])
+def test_any_traceable_module_becomes_a_graph_and_an_onnx_file(name, kw, shape, tmp_path):
+    """``torch.fx`` trace -> model graph -> .onnx file -> graph -> executor: the outputs of the module."""
+    from eagersgd_b200.graph import GraphNetwork, export_network, from_torch_module, load_onnx
+    from eagersgd_b200.models import create_model
+    torch.manual_seed(5)
+    m = create_model(name, **kw).eval()
+    for mod in m.modules():
+        if isinstance(mod, torch.nn.BatchNorm2d):
+            mod.running_mean.normal_(0, 0.2)
+            mod.running_var.uniform_(0.5, 1.5)
+    x = torch.randn(*shape)
+    g = from_torch_module(m)
+    for op in g.ops:
+        if hasattr(op, "validate"):
+            op.validate()                                   # every node is a well-formed standard operator
+    with torch.no_grad():
+        want = m(x)
+        got = GraphNetwork(g).eval()(x)
+    got = got[0] if isinstance(got, (list, tuple)) else got
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-4)
+    path = export_network(m, str(tmp_path / (name + ".onnx")))
+    with torch.no_grad():
+        again = GraphNetwork(load_onnx(path)).eval()(x)
+    again = again[0] if isinstance(again, (list, tuple)) else again
+    assert torch.allclose(again, want, rtol=1e-4, atol=1e-4)
+
+
+def test_untraceable_operations_are_named():
+    from eagersgd_b200.graph import from_torch_module
+
+    class Odd(torch.nn.Module):
+        def forward(self, x):
+            return torch.erf(x)
+
+    with pytest.raises(NotImplementedError, match="erf"):
+        from_torch_module(Odd())
