@@ -18,10 +18,11 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
+from .executor_ops import MoreOperators, _ints
 from .ir import Graph, Visitor
 
 
-class _Forward(Visitor):
+class _Forward(MoreOperators, Visitor):
     def __init__(self, net: "GraphNetwork", feeds: Dict[str, torch.Tensor]):
         self.net, self.v = net, dict(feeds)
 
@@ -80,9 +81,24 @@ class _Forward(Visitor):
     def visit_add(self, op, g): self._out(op, self._in(op, 0) + self._in(op, 1))
     def visit_sum(self, op, g): self._out(op, sum(self.v[i] for i in op.inputs))
     def visit_flatten(self, op, g): self._out(op, torch.flatten(self._in(op, 0), op.attrs.get("axis", 1)))
-    def visit_reshape(self, op, g): self._out(op, self._in(op, 0).reshape(op.attrs["shape"]))
-    def visit_squeeze(self, op, g): self._out(op, self._in(op, 0).squeeze(*op.attrs.get("axes", [])))
-    def visit_unsqueeze(self, op, g): self._out(op, self._in(op, 0).unsqueeze(op.attrs["axes"][0]))
+    def visit_reshape(self, op, g):
+        x, shape = self._in(op, 0), (_ints(self._in(op, 1)) if self._in(op, 1) is not None else list(op.attrs["shape"]))
+        shape = [x.shape[i] if d == 0 and not op.attrs.get("allowzero", 0) else d for i, d in enumerate(shape)]
+        self._out(op, x.reshape(shape))
+
+    def visit_squeeze(self, op, g):
+        x, axes = self._in(op, 0), self._axes(op)
+        if axes is None:
+            return self._out(op, x.squeeze())
+        for a in sorted((a % x.dim() for a in axes), reverse=True):
+            x = x.squeeze(a)
+        self._out(op, x)
+
+    def visit_unsqueeze(self, op, g):
+        x, axes = self._in(op, 0), self._axes(op)
+        for a in sorted(a % (x.dim() + len(axes)) for a in axes):
+            x = x.unsqueeze(a)
+        self._out(op, x)
     def visit_softmax(self, op, g): self._out(op, F.softmax(self._in(op, 0).float(), op.attrs.get("axis", -1)))
     def visit_identity(self, op, g): self._out(op, self._in(op, 0))
     def visit_concat(self, op, g): self._out(op, torch.cat([self.v[i] for i in op.inputs], op.attrs.get("axis", 1)))
@@ -106,11 +122,8 @@ class _Forward(Visitor):
     def visit_clip(self, op, g):
         self._out(op, self._in(op, 0).clamp(op.attrs.get("min", None), op.attrs.get("max", None)))
 
-    def visit_reducemean(self, op, g):
-        self._out(op, self._in(op, 0).mean(dim=op.attrs["axes"], keepdim=bool(op.attrs.get("keepdims", 1))))
-
-    def visit_reducesum(self, op, g):
-        self._out(op, self._in(op, 0).sum(dim=op.attrs["axes"], keepdim=bool(op.attrs.get("keepdims", 1))))
+    def visit_reducemean(self, op, g): self._reduce(op, lambda x, a, k: x.mean(dim=a, keepdim=k))
+    def visit_reducesum(self, op, g): self._reduce(op, lambda x, a, k: x.sum(dim=a, keepdim=k))
 
     def visit_constant(self, op, g):
         value = np.asarray(op.attrs["value"])

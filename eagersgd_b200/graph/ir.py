@@ -20,7 +20,21 @@ import numpy as np
 STANDARD_OPS = ("Conv", "BatchNormalization", "Relu", "MaxPool", "AveragePool", "GlobalAveragePool", "Gemm", "MatMul",
                 "Add", "Sum", "Flatten", "Reshape", "Squeeze", "Unsqueeze", "Softmax", "Dropout", "Identity", "Concat",
                 "Sub", "Mul", "Div", "Neg", "Abs", "Exp", "Log", "Sqrt", "Pow", "Sigmoid", "Tanh", "LeakyRelu", "Transpose",
-                "LogSoftmax", "Clip", "ReduceMean", "ReduceSum", "Constant", "Pad", "LRN")
+                "LogSoftmax", "Clip", "ReduceMean", "ReduceSum", "Constant", "Pad", "LRN",
+                # comparisons, logic and selection
+                "Equal", "Greater", "GreaterOrEqual", "Less", "LessOrEqual", "And", "Or", "Xor", "Not", "Where", "IsNaN",
+                "Max", "Min", "Mean",
+                # the rest of the unary maths and activations
+                "Floor", "Ceil", "Round", "Sign", "Reciprocal", "Erf", "Sin", "Cos", "Softplus", "Softsign", "Elu", "Selu",
+                "HardSigmoid", "PRelu", "ThresholdedRelu", "Cast",
+                # reductions and selection by value
+                "ReduceMax", "ReduceMin", "ReduceProd", "ReduceL1", "ReduceL2", "ReduceSumSquare", "ReduceLogSumExp",
+                "ArgMax", "ArgMin", "TopK", "CumSum",
+                # shapes and data movement
+                "Shape", "Size", "Expand", "Tile", "Gather", "Slice", "Split", "DepthToSpace", "SpaceToDepth",
+                "ConstantOfShape", "Range", "OneHot",
+                # layers
+                "ConvTranspose", "InstanceNormalization", "GlobalMaxPool", "LpNormalization", "Resize", "Upsample")
 LOSS_OPS = ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError")
 EXTENSION_OPS = ("StopGradient", "AllReduceGradients", "ConsistentParameterServerGradients",
                  "InconsistentParameterServerGradients")
