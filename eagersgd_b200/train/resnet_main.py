@@ -190,7 +190,7 @@ def main(argv=None):
                     batch = replicate(batch)
                 x, y = to_device(batch)
                 if args.cuda_graph and not captured and device.type == "cuda" and args.mode != "ddp" \
-                        and len(y) == args.batch_size * max(args.batchaug, 1):
+                        and getattr(step.opt, "fused", False) and len(y) == args.batch_size * max(args.batchaug, 1):
                     step.capture(x, y)               # the whole step becomes one graph launch from here on
                     captured = True
                 with (profiler.step(global_step) if profiler is not None else contextlib.nullcontext()):

@@ -87,6 +87,11 @@ class TrainStep:
         fused update on its side stream) into one CUDA graph: a replay costs one launch.
         ``warmup`` real training steps run first; every rank must call this the same way."""
         assert self.device.type == "cuda" and self.impl != "ddp"
+        if not getattr(self.opt, "fused", False):
+            # A wrapped optimizer (LARS, Adam, ...) takes its learning rate as a host value at every step and is
+            # skipped on the host when the rank applied nothing: neither survives being recorded once.
+            raise NotImplementedError("only the fused momentum-SGD path can be captured in a CUDA graph; "
+                                      "run a wrapped optimizer without capture")
         self._gx, self._gy = x.clone(), y.clone()
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
