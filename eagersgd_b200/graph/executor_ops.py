@@ -3,7 +3,7 @@ reductions, shape and data movement, transposed convolution, instance normalisat
 
 The reference's TensorFlow visitor maps 69 ONNX operators and its PyTorch visitor 32
 (deep500/frameworks/tensorflow/tf_visitor_impl.py, frameworks/pytorch/pytorch_visitor.py); with this mix-in the
-executor here runs 105 (the loss and gradient-exchange extensions included).  Each method reads its inputs with ``self._in(op, k)`` (None for an absent optional input) and
+executor here runs 106 (the loss and gradient-exchange extensions included).  Each method reads its inputs with ``self._in(op, k)`` (None for an absent optional input) and
 attributes from ``op.attrs`` with the ONNX defaults; semantics follow the ONNX operator specification, opset 13,
 with the attribute forms of older opsets (``axes`` / ``split`` / ``pads`` as attributes) accepted as well.
 """
@@ -234,3 +234,24 @@ class MoreOperators:
         sc = self._in(op, 1)
         sc = [float(v) for v in sc.flatten().tolist()] if sc is not None else [float(v) for v in op.attrs["scales"]]
         self._out(op, F.interpolate(self._in(op, 0), scale_factor=sc[2:], mode=op.attrs.get("mode", "nearest")))
+
+    def visit_lstm(self, op, g):
+        """ONNX LSTM, forward direction, zero initial state, full-length sequences: runs on this package's LSTM layer
+        (tensor-core projections and the native time loop on a GPU).  ONNX orders the gates i, o, f, c and splits the
+        bias into an input and a recurrent half; the layer wants i, f, g, o and their sum."""
+        from ..ops.lstm import lstm_layer
+        x, w, r, b = (self._in(op, k) for k in range(4))
+        if op.attrs.get("direction", "forward") != "forward" or any(self._in(op, k) is not None for k in (4, 5, 6, 7)):
+            raise NotImplementedError("LSTM: only the forward direction with zero initial state and no sequence_lens")
+        if op.attrs.get("layout", 0) != 0:
+            raise NotImplementedError("LSTM: batch-major layout")
+        h = r.shape[-1]
+        order = torch.cat([torch.arange(0, h), torch.arange(2 * h, 3 * h), torch.arange(3 * h, 4 * h), torch.arange(h, 2 * h)]).to(w.device)
+        w_ih, w_hh = w[0].index_select(0, order), r[0].index_select(0, order)
+        bias = (b[0, :4 * h] + b[0, 4 * h:]).index_select(0, order) if b is not None else torch.zeros(4 * h, device=w.device)
+        y = lstm_layer(x, w_ih.to(x.dtype).contiguous(), w_hh.to(x.dtype).contiguous(), bias.float())      # [T, B, H]
+        outs = [y.unsqueeze(1), y[-1].unsqueeze(0)]
+        if len(op.outputs) > 2 and op.outputs[2] != "":
+            raise NotImplementedError("LSTM: the final cell state is not an output of the layer")
+        self._outs(op, outs)
+

@@ -34,7 +34,8 @@ STANDARD_OPS = ("Conv", "BatchNormalization", "Relu", "MaxPool", "AveragePool", 
                 "Shape", "Size", "Expand", "Tile", "Gather", "Slice", "Split", "DepthToSpace", "SpaceToDepth",
                 "ConstantOfShape", "Range", "OneHot",
                 # layers
-                "ConvTranspose", "InstanceNormalization", "GlobalMaxPool", "LpNormalization", "Resize", "Upsample")
+                "ConvTranspose", "InstanceNormalization", "GlobalMaxPool", "LpNormalization", "Resize", "Upsample",
+                "LSTM")
 LOSS_OPS = ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError")
 EXTENSION_OPS = ("StopGradient", "AllReduceGradients", "ConsistentParameterServerGradients",
                  "InconsistentParameterServerGradients")

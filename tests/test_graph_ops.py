@@ -134,3 +134,19 @@ def test_layers():
     assert torch.equal(up, F.interpolate(x, scale_factor=2.0, mode="nearest"))
     up = _run("Upsample", [("x", x, False), ("sc", np.asarray([1, 1, 2, 2], np.float32), True)])
     assert up.shape == (2, 4, 10, 10)
+
+
+def test_onnx_lstm_runs_on_the_lstm_layer():
+    """An ONNX LSTM node (gates ordered i, o, f, c; split bias) against torch.nn.LSTM with the same weights."""
+    torch.manual_seed(1)
+    T, B, I, H = 5, 3, 8, 16
+    ref = torch.nn.LSTM(I, H)
+    x = torch.randn(T, B, I)
+    to_onnx = torch.cat([torch.arange(0, H), torch.arange(3 * H, 4 * H), torch.arange(H, 2 * H), torch.arange(2 * H, 3 * H)])
+    w = ref.weight_ih_l0.detach()[to_onnx].unsqueeze(0).numpy()
+    r = ref.weight_hh_l0.detach()[to_onnx].unsqueeze(0).numpy()
+    b = torch.cat([ref.bias_ih_l0.detach()[to_onnx], ref.bias_hh_l0.detach()[to_onnx]]).unsqueeze(0).numpy()
+    y, y_h = _run("LSTM", [("x", x, False), ("w", w, True), ("r", r, True), ("b", b, True)], n_out=2, hidden_size=H)
+    want, (h_n, _) = ref(x)
+    assert y.shape == (T, 1, B, H) and torch.allclose(y[:, 0], want, atol=1e-5)
+    assert torch.allclose(y_h, h_n, atol=1e-5)
