@@ -155,3 +155,34 @@ def test_collective_plans_pair_every_sender_with_a_reader():
         root = 1 % world
         assert [p.gather(root)[2] for p in plans] == [r if r == root else -1 for r in range(world)]
         assert all(p.allgather()[2] == r for r, p in enumerate(plans))
+
+
+def test_bench_clock_sampler_parses_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The bench's clock record: median SM clock, maximum, and the throttle reasons seen during the timed region,
+    from the lines ``nvidia-smi -lms`` prints (here a stand-in script, so that the parsing is tested without a GPU)."""
+    import importlib.util
+    import os
+    import stat
+    import time
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/bash\n"
+                    "echo '1965, 1965, 400.1, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo '1410, 1965, 998.0, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '1400, 1965, 999.5, Not Active, Not Active, Not Active, Active'\n"
+                    "echo 'garbage line'\n"
+                    "sleep 5\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    s = bench.ClockSampler(0)
+    s.start()
+    time.sleep(0.5)
+    rec = s.stop()
+    assert rec == {"sm_mhz": 1410.0, "sm_max_mhz": 1965.0, "samples": 3, "reasons": ["sw_power_cap"]}
+    monkeypatch.setenv("PATH", str(tmp_path / "nothing"))
+    s = bench.ClockSampler(0)
+    s.start()
+    assert s.stop()["reasons"] == ["nvidia-smi unavailable"]
