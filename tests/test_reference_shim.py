@@ -59,3 +59,23 @@ def test_sgd_loop_figures_are_parsed(ref_bin):
     res = run_reference.run(ranks=(2,), counts=(1024,), iters=6)
     row = res["rows"][0]
     assert all(row[k] is not None and row[k] > 0 for k in ("ssgd_us", "rsgd_us", "randomsgd_us")), row
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    """``bench.py --impl reference`` on any machine: one JSON line that says why the training path of the reference
+    is unavailable and carries the figures of its own fflib2 loops."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "1"], capture_output=True, text=True, timeout=900, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and "tensorflow" in rec["unavailable"]
+    loops = rec.get("fflib2_sgd_loops", {})
+    if "rows" in loops:                                   # the library was built here: its loops ran
+        assert all(row["rsgd_us"] is None or row["rsgd_us"] > 0 for row in loops["rows"])
