@@ -14,6 +14,7 @@
 #include "../protocol/channel.h"
 #include "../protocol/step.h"
 #include "../protocol/env_host.h"
+#include "esgd_channel.h"
 
 using namespace esgd;
 
@@ -130,25 +131,15 @@ void run_data(void** bases, int rank, const SegLayout& L, const Plan& plan, uint
 
 }  // namespace
 
+// the public C interface: parameter and result records, enumerations, prototypes
+static_assert((int)MODE_SOLO == ESGD_MODE_SOLO && (int)MODE_MAJORITY == ESGD_MODE_MAJORITY && (int)MODE_SYNC == ESGD_MODE_SYNC,
+              "modes of the header and of the protocol differ");
+static_assert((int)ROLE_ABORT == ESGD_ROLE_ABORT && (int)ROLE_PARTICIPANT == ESGD_ROLE_PARTICIPANT &&
+              (int)ROLE_DRAIN == ESGD_ROLE_DRAIN && (int)ROLE_IDLE == ESGD_ROLE_IDLE, "roles differ");
+static_assert((int)DT_F32 == ESGD_F32 && (int)DT_F64 == ESGD_F64 && (int)DT_I32 == ESGD_I32 && (int)DT_I64 == ESGD_I64,
+              "element types differ");
+
 extern "C" {
-
-struct esgd_step_info {
-  int32_t role;
-  int32_t n_contrib;
-  int32_t n_fresh;
-  int32_t is_sync;
-  uint32_t status;
-  float drain_rounds;
-  uint64_t round;
-  uint64_t local_step;
-};
-
-struct esgd_cpu_params {
-  int32_t rank, world, base_mode, include_stale, average, home, dtype;
-  int32_t flags;                   // bit 0: fold unconsumed gradients into the next publish; bit 1: adaptive grace
-  int64_t limiter;
-  uint64_t seed, timeout_ns, grace_ns, count;
-};
 
 uint64_t esgd_ctl_bytes(void) { return sizeof(ChannelCtl); }
 

@@ -186,3 +186,27 @@ def test_bench_clock_sampler_parses_a_fake_nvidia_smi(tmp_path, monkeypatch):
     s = bench.ClockSampler(0)
     s.start()
     assert s.stop()["reasons"] == ["nvidia-smi unavailable"]
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_c_sample_of_the_partial_allreduce(tmp_path, mode):
+    """samples/c/solo_allreduce.c — the reference's rsgd.c loop written against host/esgd_channel.h — compiles with
+    the flags of the pkg-config file and passes its own checks in solo, majority and synchronous mode."""
+    import os
+    import shutil
+    import subprocess
+    from eagersgd_b200 import _build
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    _build.build_host()
+    text = open(_build.write_pkgconfig()).read()
+    var = dict(l.split("=", 1) for l in text.splitlines() if "=" in l and ":" not in l.split("=")[0])
+    expand = lambda s: s.replace("${libdir}", var["libdir"]).replace("${includedir}", var["includedir"])
+    cflags = expand([l for l in text.splitlines() if l.startswith("Cflags:")][0].split(":", 1)[1]).split()
+    libs = expand([l for l in text.splitlines() if l.startswith("Libs:")][0].split(":", 1)[1]).split()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "solo_allreduce")
+    subprocess.run(["gcc", "-O2", "-Wall", "-Werror", os.path.join(root, "samples", "c", "solo_allreduce.c")] + cflags + libs +
+                   ["-o", exe], check=True, capture_output=True, text=True)
+    r = subprocess.run([exe, "3", "2048", "6", str(mode)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "PASSED" in r.stdout and "replicas agree" in r.stdout, r.stdout + r.stderr
