@@ -295,3 +295,66 @@ def test_large_vectors_on_several_threads_per_rank(mode):
     else:
         assert np.array_equal(applied[0], applied[1])               # every replica applied the same total
         assert np.all(applied[0] <= total + 1e-6) and applied[0].sum() > 0
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_randomised_schedules_keep_the_invariants(seed):
+    """Random worlds, modes, limiters, grace windows, staleness policies and delay patterns: every rank's result is
+    untorn, no wait runs out, every replica has applied the same total once the channel is flushed, nothing is
+    counted twice, and with accumulation plus two closing synchronous rounds nothing is lost."""
+    cfg = random.Random(1000 + seed)
+    world = cfg.choice([2, 3, 4, 5, 6])
+    mode = cfg.choice(["solo", "majority"])
+    limiter = cfg.choice([-1, 1, 3, 8])
+    accumulate = cfg.random() < 0.5
+    kw = dict(seed=cfg.randrange(1 << 30), average="sum", timeout_s=30, accumulate=accumulate,
+              include_stale=cfg.random() < 0.7, grace_us=cfg.choice([0.0, 200.0]), adaptive_grace=cfg.random() < 0.5)
+    p_delay = [cfg.choice([0.0, 0.2, 0.6, 1.0]) for _ in range(world)]
+    scale = cfg.choice([0.0005, 0.002, 0.004])
+    count, steps = 32, 30
+    segs = LocalSegments(world, count, np.int64)
+    applied = [0] * world
+    stats = [None] * world
+    errors = []
+    phase = threading.Barrier(world)
+
+    def worker(r):
+        try:
+            ch = CpuChannel(segs.bases, r, world, count, np.int64, mode=mode, limiter=limiter, **kw)
+            rng = random.Random(seed * 977 + r)
+            for k in range(1, steps + 1):
+                if rng.random() < p_delay[r]:
+                    time.sleep(rng.random() * scale)
+                out, _ = ch.step(np.full(count, (r + 1) * 1000 + k, dtype=np.int64))
+                assert np.all(out == out[0]), "torn result"
+                applied[r] += int(out[0])
+            phase.wait()
+            if accumulate:
+                closing = CpuChannel(segs.bases, r, world, count, np.int64, mode="sync", limiter=-1, **kw)
+                for _ in range(2):
+                    out, _ = closing.step(np.zeros(count, dtype=np.int64))
+                    applied[r] += int(out[0])
+                stats[r] = closing.stats()
+            else:
+                out, _ = ch.flush()
+                applied[r] += int(out[0])
+                stats[r] = ch.stats()
+        except Exception as e:  # noqa
+            errors.append((r, repr(e)))
+            try:
+                phase.abort()
+            except Exception:
+                pass
+
+    th = [threading.Thread(target=worker, args=(r,)) for r in range(world)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    desc = dict(world=world, mode=mode, limiter=limiter, accumulate=accumulate, kw=kw, p_delay=p_delay, scale=scale)
+    assert not errors, (errors, desc)
+    published = sum((r + 1) * 1000 + k for r in range(world) for k in range(1, steps + 1))
+    assert all(s["status"] == 0 for s in stats), (stats, desc)
+    assert len(set(applied)) == 1, (applied, desc)                  # replicas agree
+    assert applied[0] <= published, (applied[0], published, desc)    # nothing twice
+    if accumulate:
+        assert applied[0] == published, (applied[0], published, desc)
+        assert all(s["dropped_grads"] == 0 for s in stats), (stats, desc)
