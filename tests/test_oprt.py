@@ -459,3 +459,38 @@ def test_shadow_tags_char_buffers_and_complete_before_cancelling():
         a.post(keep)
         a.cancel(keep)
         assert a.wait(keep, 5.0) == R.SUCCESS and hits == [1]
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_dependency_graphs_compute_in_dependency_order(seed):
+    """Random DAGs of compute operations (each adds the results of two earlier nodes, edges as happens-before
+    relations) inside one schedule, posted several times with new leaf values: every node ends up with the value a
+    topological evaluation gives, on every post — a node that ran before one of its parents would not."""
+    rng = np.random.RandomState(seed)
+    n_leaf, n_node = 3, int(rng.randint(5, 40))
+    with R.World(1) as w:
+        r = w.ranks[0]
+        arrays = [np.zeros(4, dtype=np.int64) for _ in range(n_leaf + n_node)]
+        bufs = [r.buffer(a) for a in arrays]
+        s = r.schedule()
+        ops, parents = {}, {}
+        for i in range(n_leaf, n_leaf + n_node):
+            a, b = (int(v) for v in rng.randint(0, i, size=2))
+            parents[i] = (a, b)
+            ops[i] = r.comp(bufs[a], bufs[b], bufs[i], R.SUM)
+            for p in (a, b):
+                if p in ops:
+                    r.hb(ops[p], ops[i])
+            r.schedule_add(s, ops[i])
+        for rep in range(3):
+            for k in range(n_leaf):
+                arrays[k][:] = rng.randint(-5, 6, size=4)
+            for i in range(n_leaf, n_leaf + n_node):
+                arrays[i][:] = -999                                  # stale values must not survive
+            want = [a.copy() for a in arrays[:n_leaf]]
+            for i in range(n_leaf, n_leaf + n_node):
+                want.append(want[parents[i][0]] + want[parents[i][1]])
+            r.schedule_post(s)
+            assert r.schedule_wait(s, timeout=20.0) == R.SUCCESS
+            for i in range(n_leaf, n_leaf + n_node):
+                assert np.array_equal(arrays[i], want[i]), (seed, rep, i, parents[i])
