@@ -294,7 +294,7 @@ def load_onnx(path: str) -> Graph:
 
 # ---- encoding ------------------------------------------------------------------------------------------------------
 def _enc_tensor(name: str, arr: np.ndarray) -> bytes:
-    arr = np.ascontiguousarray(arr)
+    arr = np.asarray(arr, order="C")          # not ascontiguousarray: that turns a scalar into a vector of one
     if arr.dtype not in _DTYPE_IDS:
         arr = arr.astype(np.float32)
     out = b"".join(_enc_int(1, int(d)) for d in arr.shape)

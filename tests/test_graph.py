@@ -260,3 +260,68 @@ def test_untraceable_operations_are_named():
 
     with pytest.raises(NotImplementedError, match="erf"):
         from_torch_module(Odd())
+
+
+def test_onnx_round_trip_of_random_graphs():
+    """Property test of the .onnx writer and reader: graphs with random node attributes (negative and large
+    integers, floats, unicode strings, lists, tensors of several element types and ranks, empty lists) and random
+    initializers come back equal."""
+    import tempfile
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from hypothesis.extra import numpy as hnp
+    from eagersgd_b200.graph.ir import Graph
+    from eagersgd_b200.graph.onnx_io import load_onnx, save_onnx
+
+    f32 = st.floats(width=32, allow_nan=False, allow_infinity=False)
+    i64 = st.integers(min_value=-(1 << 62), max_value=(1 << 62))
+    tensors = st.one_of(
+        hnp.arrays(np.float32, hnp.array_shapes(min_dims=0, max_dims=3, max_side=4), elements=f32),
+        hnp.arrays(np.int64, hnp.array_shapes(min_dims=1, max_dims=2, max_side=5), elements=i64),
+        hnp.arrays(np.float64, hnp.array_shapes(min_dims=1, max_dims=2, max_side=3),
+                   elements=st.floats(allow_nan=False, allow_infinity=False, width=64)),
+        hnp.arrays(np.int32, hnp.array_shapes(min_dims=1, max_dims=2, max_side=4),
+                   elements=st.integers(-(1 << 31), (1 << 31) - 1)),
+        hnp.arrays(np.uint8, hnp.array_shapes(min_dims=1, max_dims=2, max_side=6), elements=st.integers(0, 255)),
+        hnp.arrays(np.bool_, hnp.array_shapes(min_dims=1, max_dims=1, max_side=6)))
+    attr = st.one_of(i64, f32, st.text(max_size=12), st.lists(i64, max_size=5), st.lists(f32, min_size=1, max_size=5), tensors)
+    names = st.text(alphabet="abcdefghij_", min_size=1, max_size=6)
+    attrs = st.dictionaries(names, attr, max_size=4)
+    nodes = st.lists(st.tuples(st.sampled_from(["Relu", "Conv", "MyOp", "Add"]), attrs), min_size=1, max_size=4)
+
+    @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(nodes=nodes, inits=st.lists(tensors, max_size=3))
+    def check(nodes, inits):
+        g = Graph("g")
+        g.add_input("x")
+        prev = "x"
+        for k, t in enumerate(inits):
+            g.add_initializer("w%d" % k, t)
+        for k, (op_type, a) in enumerate(nodes):
+            out = "t%d" % k
+            g.add(op_type, [prev], [out], **a)
+            prev = out
+        g.add_output(prev)
+        with tempfile.TemporaryDirectory() as d:
+            path = d + "/g.onnx"
+            save_onnx(g, path)
+            h = load_onnx(path)
+        assert [o.op_type for o in h.ops] == [o.op_type for o in g.ops]
+        assert h.inputs == g.inputs and h.outputs == g.outputs
+        for a, b in zip(g.ops, h.ops):
+            assert a.inputs == b.inputs and a.outputs == b.outputs and set(a.attrs) == set(b.attrs), (a.attrs, b.attrs)
+            for key, v in a.attrs.items():
+                w = b.attrs[key]
+                if isinstance(v, np.ndarray):
+                    assert isinstance(w, np.ndarray) and w.dtype == v.dtype and w.shape == v.shape and np.array_equal(w, v), (key, v, w)
+                elif isinstance(v, float):
+                    assert w == pytest.approx(v, rel=1e-6, abs=1e-38), (key, v, w)
+                elif isinstance(v, list) and v and isinstance(v[0], float):
+                    assert w == pytest.approx(v, rel=1e-6, abs=1e-38), (key, v, w)
+                else:
+                    assert w == v, (key, v, w)
+        for k, t in enumerate(inits):
+            w = h.initializers["w%d" % k]
+            assert w.dtype == t.dtype and w.shape == t.shape and np.array_equal(w, t)
+
+    check()
