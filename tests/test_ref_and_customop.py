@@ -167,3 +167,65 @@ def test_cpp_oracles_with_backward_match_autograd():
     assert close(R.batchnorm_inference(x4, gamma, beta, mean, var), y)
     dx, dg, db = R.batchnorm_inference_grad(x4, gamma, mean, var, g)
     assert close(dx, tx.grad) and close(dg, tg.grad) and close(db, tb2.grad)
+
+
+def test_cpp_oracles_against_autograd_on_random_geometries():
+    """Property test of the C++ oracles the GPU kernels are checked against: convolution (forward, data and weight
+    gradient), max pooling, average pooling and GEMM with random sizes, strides, paddings and transpositions agree
+    with PyTorch's fp32 operators and their autograd."""
+    import torch
+    import torch.nn.functional as F
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.ref import cpp_ops as R
+
+    close = lambda a, b: np.allclose(a, b, rtol=2e-4, atol=2e-4)
+
+    @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(n=st.integers(1, 3), cin=st.integers(1, 5), cout=st.integers(1, 5), h=st.integers(3, 9), w=st.integers(3, 9),
+           k=st.sampled_from([1, 2, 3, 5]), stride=st.integers(1, 3), pad=st.integers(0, 2), seed=st.integers(0, 10 ** 6))
+    def conv(n, cin, cout, h, w, k, stride, pad, seed):
+        if h + 2 * pad < k or w + 2 * pad < k or pad >= k:
+            return
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(n, cin, h, w, generator=g, requires_grad=True)
+        wt = torch.randn(cout, cin, k, k, generator=g, requires_grad=True)
+        y = F.conv2d(x, wt, None, stride, pad)
+        dy = torch.randn(y.shape, generator=g)
+        y.backward(dy)
+        assert close(R.conv2d(x.detach().numpy(), wt.detach().numpy(), stride, pad), y.detach().numpy())
+        dx, dw = R.conv2d_grads(x.detach().numpy(), wt.detach().numpy(), dy.numpy(), stride, pad)
+        assert close(dx, x.grad.numpy()) and close(dw, wt.grad.numpy())
+
+    @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(n=st.integers(1, 3), c=st.integers(1, 4), h=st.integers(4, 10), w=st.integers(4, 10), k=st.sampled_from([2, 3]),
+           stride=st.integers(1, 3), pad=st.integers(0, 1), seed=st.integers(0, 10 ** 6), include=st.booleans())
+    def pools(n, c, h, w, k, stride, pad, seed, include):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(n, c, h, w, generator=g, requires_grad=True)
+        y = F.max_pool2d(x, k, stride, pad)
+        dy = torch.randn(y.shape, generator=g)
+        y.backward(dy)
+        assert close(R.maxpool(x.detach().numpy(), k, stride, pad), y.detach().numpy())
+        assert close(R.maxpool_grad(x.detach().numpy(), dy.numpy(), k, stride, pad), x.grad.numpy())
+        x.grad = None
+        y = F.avg_pool2d(x, k, stride, pad, count_include_pad=include)
+        dy = torch.randn(y.shape, generator=g)
+        y.backward(dy)
+        assert close(R.avgpool(x.detach().numpy(), k, stride, pad, include), y.detach().numpy())
+        assert close(R.avgpool_grad(dy.numpy(), tuple(x.shape), k, stride, pad, include), x.grad.numpy())
+
+    @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(m=st.integers(1, 7), n=st.integers(1, 7), kk=st.integers(1, 7), ta=st.booleans(), tb=st.booleans(),
+           alpha=st.sampled_from([1.0, 0.5, -2.0]), beta=st.sampled_from([0.0, 1.0, 0.25]), seed=st.integers(0, 10 ** 6))
+    def gemm(m, n, kk, ta, tb, alpha, beta, seed):
+        g = torch.Generator().manual_seed(seed)
+        a = torch.randn((kk, m) if ta else (m, kk), generator=g)
+        b = torch.randn((n, kk) if tb else (kk, n), generator=g)
+        c = torch.randn(m, n, generator=g)
+        want = alpha * ((a.t() if ta else a) @ (b.t() if tb else b)) + beta * c
+        assert close(R.gemm(a.numpy(), b.numpy(), c.numpy(), alpha, beta, ta, tb), want.numpy())
+
+    conv()
+    pools()
+    gemm()
