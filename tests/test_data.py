@@ -179,3 +179,61 @@ def test_download_helpers_against_a_mirror_on_disk(tmp_path):
         t.addfile(info)
     with pytest.raises(IOError, match="escapes"):
         D.unpack(str(evil), str(tmp_path / "x"))
+
+
+def test_sampler_invariants_over_random_sizes():
+    """Property test of the samplers: an epoch of the ordered and the shuffling sampler visits every sample at most
+    once and all of them unless the ragged last batch is dropped; the bucket sampler's batches stay inside one length
+    bucket, visit every sequence once, and pad on the left to the longest sequence of the batch."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.data.dataset import NumpyDataset
+    from eagersgd_b200.data.sampler import BucketSampler, OrderedSampler, ShuffleSampler
+
+    @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(n=st.integers(1, 70), bs=st.integers(1, 12), drop=st.booleans(), seed=st.integers(0, 1000))
+    def plain(n, bs, drop, seed):
+        ds = NumpyDataset(np.arange(n, dtype=np.float32).reshape(n, 1), "x", np.arange(n), "y")
+        for cls in (OrderedSampler, ShuffleSampler):
+            s = cls(ds, bs, seed=seed, drop_last_batch=drop)
+            for _ in range(2):                                   # two epochs
+                seen = np.concatenate([b["y"] for b in s] or [np.zeros(0, np.int64)])
+                assert len(seen) == len(set(seen.tolist()))
+                assert len(seen) == ((n // bs) * bs if drop else n)
+                assert len(s) == (n // bs if drop else -(-n // bs))
+                s.reset()
+
+    class Seqs:
+        data_node, label_node = "x", "y"
+
+        def __init__(self, lengths):
+            self.seqs = [np.full((int(l), 2), i, dtype=np.float32) for i, l in enumerate(lengths)]
+
+        def __len__(self):
+            return len(self.seqs)
+
+        def __getitem__(self, i):
+            return {"x": self.seqs[i], "y": i}
+
+    @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(lengths=st.lists(st.integers(1, 50), min_size=1, max_size=40), bs=st.integers(1, 6), nb=st.integers(1, 8),
+           seed=st.integers(0, 1000))
+    def buckets(lengths, bs, nb, seed):
+        ds = Seqs(lengths)
+        s = BucketSampler(ds, bs, np.asarray(lengths), num_buckets=nb, seed=seed, drop_last_batch=False)
+        width = max(lengths) / nb
+        seen = []
+        for b in s:
+            ids = b["y"].tolist()
+            seen += ids
+            lens = [lengths[i] for i in ids]
+            assert b["x"].shape[1] == max(lens) and b["lengths"].tolist() == lens
+            for row, i in zip(b["x"], ids):                      # left padding: zeros, then the sequence
+                pad = b["x"].shape[1] - lengths[i]
+                assert np.all(row[:pad] == 0) and np.all(row[pad:] == i)
+            which = {min(int(np.ceil(l / width)) - 1, nb - 1) if l > 0 else 0 for l in lens}
+            assert len(which) == 1 or max(lens) - min(lens) <= width + 1e-9, (lens, width)
+        assert sorted(seen) == list(range(len(lengths)))
+
+    plain()
+    buckets()
