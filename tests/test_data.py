@@ -237,3 +237,26 @@ def test_sampler_invariants_over_random_sizes():
 
     plain()
     buckets()
+
+
+def test_imagenet_preprocessing_over_random_image_sizes():
+    """Images of any size, tiny and extreme aspect ratios included, come out as float32 [3, 224, 224] in both the
+    training and the evaluation path; the random crop always lies inside the image."""
+    pytest = __import__("pytest")
+    pytest.importorskip("PIL")
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.data.imagenet import preprocess_image, random_crop_box
+
+    @settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(h=st.integers(1, 400), w=st.integers(1, 400), seed=st.integers(0, 10 ** 6), train=st.booleans())
+    def check(h, w, seed, train):
+        rng = np.random.default_rng(seed)
+        t, l, ch, cw = random_crop_box(h, w, rng)
+        assert 0 <= t and 0 <= l and ch >= 1 and cw >= 1 and t + ch <= h and l + cw <= w
+        img = rng.integers(0, 256, size=(h, w, 3), dtype=np.uint8)
+        out = preprocess_image(img, train, rng)
+        assert out.shape == (3, 224, 224) and out.dtype == np.float32 and np.isfinite(out).all()
+        assert out.min() >= -130.0 and out.max() <= 160.0          # 0..255 minus channel means of 104..124
+
+    check()
