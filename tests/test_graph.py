@@ -325,3 +325,68 @@ def test_onnx_round_trip_of_random_graphs():
             assert w.dtype == t.dtype and w.shape == t.shape and np.array_equal(w, t)
 
     check()
+
+
+def test_random_sequential_networks_survive_tracing_and_an_onnx_file():
+    """Property test: random small convolutional networks (kernel sizes, strides, paddings, biases, normalisation,
+    activations, pooling, a dense head) give the same outputs as a graph and after a trip through an .onnx file."""
+    import tempfile
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.graph import GraphNetwork, from_torch_module, load_onnx, save_onnx
+
+    layer = st.one_of(
+        st.tuples(st.just("conv"), st.integers(1, 6), st.sampled_from([1, 3]), st.integers(1, 2), st.integers(0, 1), st.booleans()),
+        st.tuples(st.just("bn")), st.tuples(st.just("relu")), st.tuples(st.just("leaky"), st.sampled_from([0.01, 0.2])),
+        st.tuples(st.just("sigmoid")), st.tuples(st.just("tanh")),
+        st.tuples(st.just("maxpool"), st.sampled_from([2, 3]), st.integers(1, 2)),
+        st.tuples(st.just("avgpool"), st.sampled_from([2]), st.integers(1, 2)))
+
+    @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(layers=st.lists(layer, min_size=1, max_size=6), cin=st.integers(1, 3), classes=st.integers(1, 5),
+           seed=st.integers(0, 10 ** 6))
+    def check(layers, cin, classes, seed):
+        torch.manual_seed(seed)
+        mods, c, size = [], cin, 12
+        for spec in layers:
+            kind = spec[0]
+            if kind == "conv":
+                _, co, k, s, p, bias = spec
+                if size + 2 * p < k:
+                    continue
+                mods.append(torch.nn.Conv2d(c, co, k, s, p, bias=bias))
+                c, size = co, (size + 2 * p - k) // s + 1
+            elif kind == "bn":
+                bn = torch.nn.BatchNorm2d(c)
+                bn.running_mean.normal_(0, 0.3)
+                bn.running_var.uniform_(0.5, 2.0)
+                mods.append(bn)
+            elif kind == "relu":
+                mods.append(torch.nn.ReLU())
+            elif kind == "leaky":
+                mods.append(torch.nn.LeakyReLU(spec[1]))
+            elif kind == "sigmoid":
+                mods.append(torch.nn.Sigmoid())
+            elif kind == "tanh":
+                mods.append(torch.nn.Tanh())
+            elif kind in ("maxpool", "avgpool"):
+                _, k, s = spec
+                if size < k:
+                    continue
+                mods.append((torch.nn.MaxPool2d if kind == "maxpool" else torch.nn.AvgPool2d)(k, s))
+                size = (size - k) // s + 1
+        mods += [torch.nn.Flatten(), torch.nn.Linear(c * size * size, classes)]
+        m = torch.nn.Sequential(*mods).eval()
+        x = torch.randn(2, cin, 12, 12)
+        with torch.no_grad():
+            want = m(x)
+            g = from_torch_module(m)
+            got = GraphNetwork(g).eval()(x)
+            with tempfile.TemporaryDirectory() as d:
+                save_onnx(g, d + "/m.onnx")
+                again = GraphNetwork(load_onnx(d + "/m.onnx")).eval()(x)
+        for y in (got, again):
+            y = y[0] if isinstance(y, (list, tuple)) else y
+            assert torch.allclose(y, want, rtol=1e-4, atol=1e-4), (layers, (y - want).abs().max())
+
+    check()
