@@ -390,3 +390,64 @@ def test_random_sequential_networks_survive_tracing_and_an_onnx_file():
             assert torch.allclose(y, want, rtol=1e-4, atol=1e-4), (layers, (y - want).abs().max())
 
     check()
+
+
+@pytest.mark.parametrize("use_cpp", [True, False])
+def test_reference_executor_gradients_on_random_networks(use_cpp):
+    """Property test of the CPU reference executor (numpy and compiled C++ operators, forward and backward): on
+    random small networks with a softmax-cross-entropy loss its logits, loss and every weight gradient agree with
+    the native executor's autograd."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.graph import GraphNetwork, ReferenceGraphExecutor, from_torch_module
+
+    layer = st.one_of(
+        st.tuples(st.just("conv"), st.integers(1, 5), st.sampled_from([1, 3]), st.integers(1, 2), st.integers(0, 1), st.booleans()),
+        st.tuples(st.just("bn")), st.tuples(st.just("relu")),
+        st.tuples(st.just("maxpool"), st.sampled_from([2, 3]), st.integers(1, 2)),
+        st.tuples(st.just("avgpool"), st.just(2), st.integers(1, 2)))
+
+    @settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(layers=st.lists(layer, min_size=1, max_size=5), cin=st.integers(1, 3), classes=st.integers(2, 5),
+           seed=st.integers(0, 10 ** 6))
+    def check(layers, cin, classes, seed):
+        torch.manual_seed(seed)
+        mods, c, size = [], cin, 10
+        for spec in layers:
+            kind = spec[0]
+            if kind == "conv":
+                _, co, k, s, p, bias = spec
+                if size + 2 * p < k:
+                    continue
+                mods.append(torch.nn.Conv2d(c, co, k, s, p, bias=bias))
+                c, size = co, (size + 2 * p - k) // s + 1
+            elif kind == "bn":
+                mods.append(torch.nn.BatchNorm2d(c))
+            elif kind == "relu":
+                mods.append(torch.nn.ReLU())
+            else:
+                _, k, s = spec
+                if size < k:
+                    continue
+                mods.append((torch.nn.MaxPool2d if kind == "maxpool" else torch.nn.AvgPool2d)(k, s))
+                size = (size - k) // s + 1
+        mods += [torch.nn.Flatten(), torch.nn.Linear(c * size * size, classes)]
+        g = from_torch_module(torch.nn.Sequential(*mods))
+        g.add_loss("SoftmaxCrossEntropy", g.outputs[0])
+        x = torch.randn(4, cin, 10, 10)
+        y = torch.randint(0, classes, (4,))
+        net = GraphNetwork(g).train()
+        outs = net(x, label=y)
+        outs[-1].backward()
+        ref = ReferenceGraphExecutor(g, use_cpp=use_cpp)
+        r_outs = ref.inference_and_backprop({g.inputs[0]: x.numpy(), "label": y.numpy()})
+        assert np.allclose(r_outs[0], outs[0].detach().numpy(), rtol=1e-3, atol=1e-3), layers
+        assert abs(float(r_outs[-1]) - float(outs[-1].detach())) < 1e-3
+        for name in g.get_params():
+            p = net.tensor(name)
+            if p.grad is None or name not in ref.gradients:
+                continue
+            a, b = ref.gradients[name], p.grad.numpy()
+            assert np.allclose(a, b, rtol=2e-2, atol=2e-3 * max(1.0, float(np.abs(b).max()))), (name, layers)
+
+    check()
