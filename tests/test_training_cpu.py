@@ -302,3 +302,47 @@ def test_shuffleaug_groups_share_data_and_regime_moves_the_boundaries():
     lr0, lr2 = imagenet_schedule(256, 2560, warmup=False), imagenet_schedule(256, 2560, warmup=False, regime=2)
     steps = 2560 // 256                                         # batches per epoch
     assert lr0(steps * 16) == pytest.approx(0.1) and lr2(steps * 16) == pytest.approx(0.01)
+
+
+def test_update_rule_optimizers_follow_torch_optim_over_random_hyperparameters():
+    """Property test: the update-rule optimizers (gradient descent, momentum with weight decay, Adam, AdaGrad,
+    RMSProp) take the same six steps as their torch.optim counterparts from the same start, for random
+    hyper-parameters."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+    from eagersgd_b200.optim import base as B
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+
+    lr = st.floats(1e-3, 0.5)
+
+    @settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(kind=st.sampled_from(["gd", "momentum", "adam", "adagrad", "rmsprop"]), lr=lr, a=st.floats(0.5, 0.99),
+           b=st.floats(0.9, 0.9999), wd=st.sampled_from([0.0, 1e-3, 1e-1]), seed=st.integers(0, 10 ** 6))
+    def check(kind, lr, a, b, wd, seed):
+        torch.manual_seed(seed)
+        m1 = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.Tanh(), torch.nn.Linear(7, 3))
+        m2 = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.Tanh(), torch.nn.Linear(7, 3))
+        m2.load_state_dict(m1.state_dict())
+        ex = GraphExecutor(m1, loss_fn=classification_loss)
+        ours, theirs = {
+            "gd": lambda: (B.GradientDescent(ex, learning_rate=lr), torch.optim.SGD(m2.parameters(), lr=lr)),
+            "momentum": lambda: (B.MomentumOptimizer(ex, learning_rate=lr, momentum=a, weight_decay=wd),
+                                 torch.optim.SGD(m2.parameters(), lr=lr, momentum=a, weight_decay=wd)),
+            "adam": lambda: (B.AdamOptimizer(ex, learning_rate=lr * 0.1, beta1=a, beta2=b, epsilon=1e-8),
+                             torch.optim.Adam(m2.parameters(), lr=lr * 0.1, betas=(a, b), eps=1e-8)),
+            "adagrad": lambda: (B.AdaGradOptimizer(ex, learning_rate=lr, epsilon=1e-10),
+                                torch.optim.Adagrad(m2.parameters(), lr=lr, eps=1e-10)),
+            "rmsprop": lambda: (B.RMSPropOptimizer(ex, learning_rate=lr * 0.1, decay=a, epsilon=1e-8),
+                                torch.optim.RMSprop(m2.parameters(), lr=lr * 0.1, alpha=a, eps=1e-8)),
+        }[kind]()
+        g = torch.Generator().manual_seed(seed)
+        for _ in range(6):
+            x, y = torch.randn(8, 5, generator=g), torch.randint(0, 3, (8,), generator=g)
+            ours.step({"x": x, "y": y})
+            theirs.zero_grad()
+            torch.nn.functional.cross_entropy(m2(x), y).backward()
+            theirs.step()
+        for p, q in zip(m1.parameters(), m2.parameters()):
+            assert torch.allclose(p, q, rtol=1e-4, atol=1e-5), (kind, (p - q).abs().max())
+
+    check()
