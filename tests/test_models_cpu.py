@@ -37,3 +37,30 @@ def test_lstm_classifier_trains_on_cpu():
         opt.step()
         first = first or loss.item()
     assert loss.item() < first
+
+
+@pytest.mark.parametrize("size,version,params", [
+    (18, 1, 11_689_512 + 4_224), (34, 1, 21_797_672 + 4_224), (50, 1, 25_557_032), (101, 1, 44_549_160), (152, 1, 60_192_808),
+    (200, 1, 64_673_832), (18, 2, None), (50, 2, None), (200, 2, None)])
+def test_imagenet_resnets_of_every_size(size, version, params, tmp_path):
+    """Every ImageNet ResNet size (the reference's imagenet_test.py runs all sizes and versions): the v1 models have
+    the parameter counts of the published architectures (1000 classes; the two building-block sizes carry 4,224 more
+    because the first block of EVERY stage has a projection shortcut here, as in resnet_model.py:block_layer, where
+    the common PyTorch definition leaves the first stage's out), a forward pass gives [N, classes], the variable
+    layout exports and imports without loss."""
+    import torch
+    from eagersgd_b200 import ckpt
+    from eagersgd_b200.models.resnet import imagenet_resnet
+    torch.manual_seed(0)
+    m = imagenet_resnet(size, version, 1000).eval()
+    if params is not None:
+        assert sum(p.numel() for p in m.parameters()) == params
+    with torch.no_grad():
+        y = m(torch.randn(1, 3, 64, 64))
+    assert y.shape == (1, 1000) and torch.isfinite(y).all()
+    path = str(tmp_path / "m.npz")
+    ckpt.export_tf_layout(m, path)
+    m2 = imagenet_resnet(size, version, 1000).eval()
+    assert ckpt.import_tf_layout(m2, path) == 0               # the global step the file carries
+    with torch.no_grad():
+        assert torch.equal(m2(torch.ones(1, 3, 64, 64)), m(torch.ones(1, 3, 64, 64)))
