@@ -103,6 +103,18 @@ static int run_runtime(int world, int posts) {
   return any;
 }
 
+// Fresh schedules every iteration: create, post, wait, delete (handles and temporaries are recycled), and the
+// persistent form, through the runtime's own native benchmark; the results are checked inside.
+static int run_schedule_cycles(int world) {
+  double out[3] = {0, 0, 0};
+  int bad = 0;
+  for (int fresh = 0; fresh < 2; ++fresh) {
+    if (rt_bench_allreduce(world, 96, 48, fresh, out) != RT_SUCCESS || out[2] != 1.0) bad = 1;
+  }
+  printf("runtime schedule cycles: %d ranks %s\n", world, bad ? "FAILED" : "ok");
+  return bad;
+}
+
 int main(int argc, char** argv) {
   const int world = argc > 1 ? atoi(argv[1]) : 4;
   const int steps = argc > 2 ? atoi(argv[2]) : 200;
@@ -110,5 +122,9 @@ int main(int argc, char** argv) {
   for (int mode = 0; mode < 3; ++mode) bad |= run_channel(mode, world, steps, 1024, 2);
   for (int mode = 0; mode < 2; ++mode) bad |= run_channel(mode, world, steps, 1024, 3);   // folding unconsumed gradients
   bad |= run_runtime(world, steps / 4 + 1);
+  bad |= run_schedule_cycles(world);
+  // vectors long enough for a rank's helper threads (from 256 K elements each), with a ragged length
+  bad |= run_channel(2, 2, 3, (1u << 20) + 1234, 0);
+  bad |= run_channel(0, 2, 3, (1u << 20) + 1234, 1);
   return bad;
 }

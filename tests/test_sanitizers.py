@@ -24,4 +24,5 @@ def test_stress_driver_is_clean(tmp_path, flags, needle):
     out = run.stdout + run.stderr
     assert run.returncode == 0, out[-3000:]
     assert needle not in out, out[-3000:]
-    assert out.count("on every rank") == 5 and "runtime allreduce: 4 ranks" in out
+    assert out.count("on every rank") == 7 and "runtime allreduce: 4 ranks" in out
+    assert "runtime schedule cycles: 4 ranks ok" in out
