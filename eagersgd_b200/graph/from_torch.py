@@ -5,8 +5,10 @@ the executor and the file writer know.  This stands where the reference exports 
 ``torch.onnx.export`` (deep500/networks/__init__.py:6-21, pytorch_mnist.py, pytorch_deep_mnist.py,
 pytorch_wide_resnet.py: ``export_network(name, batch_size, file_path=...)``) — the ``onnx`` package that exporter needs
 is not assumed here.  Covered: convolutions, dense layers, batch norm, ReLU / sigmoid / tanh / leaky ReLU, max / average
-/ adaptive-average pooling to 1x1, flatten / view(batch, -1), dropout, softmax / log-softmax, add / sub / mul /
-concatenation, written as modules or as ``torch.nn.functional`` calls.  Anything else raises with the node's name.
+/ adaptive-average pooling to 1x1, flatten / view(batch, -1), permute / transpose, dropout, softmax / log-softmax,
+add / sub / mul / concatenation, stacks of unidirectional LSTM layers (as ONNX LSTM nodes, which the executor runs on
+this package's LSTM layer), written as modules or as ``torch.nn.functional`` calls.  Anything else raises with the
+node's name.
 The ResNets of this package have their own builder (``from_torch_resnet``): their blocks fuse operations in ways a
 tracer cannot see through.
 """
@@ -33,10 +35,13 @@ def _pads(p) -> List[int]:
 
 
 class _Builder:
-    def __init__(self, module: nn.Module, name: str):
+    def __init__(self, module: nn.Module, name: str, example_inputs=None):
         import torch.fx as fx
         self.module = module
         self.traced = fx.symbolic_trace(module)
+        if example_inputs is not None:            # shapes of every intermediate value: needed where an operator's
+            from torch.fx.passes.shape_prop import ShapeProp     # ONNX form depends on the rank (transpose)
+            ShapeProp(self.traced).propagate(*example_inputs)
         self.g = Graph(name)
         self.names: Dict[str, str] = {}           # fx node name -> graph tensor name
         self.k = 0
@@ -98,8 +103,40 @@ class _Builder:
             self.emit(node, "Softmax", [x], axis=int(m.dim if m.dim is not None else -1))
         elif isinstance(m, nn.LogSoftmax):
             self.emit(node, "LogSoftmax", [x], axis=int(m.dim if m.dim is not None else -1))
+        elif isinstance(m, nn.LSTM):
+            self.lstm(node, m, x, q)
         else:
             raise NotImplementedError("no graph operator for module %s (%s)" % (node.target, type(m).__name__))
+
+    def lstm(self, node, m: nn.LSTM, x: str, q: str) -> None:
+        """A stack of unidirectional LSTM layers as ONNX LSTM nodes (gates re-ordered from i, f, g, o to ONNX's
+        i, o, f, c; the two bias vectors side by side).  The node's value is the pair (outputs, final hidden state
+        of the top layer); ``lstm(x)[0]`` picks the outputs."""
+        if m.bidirectional or getattr(m, "proj_size", 0) or m.dropout:
+            raise NotImplementedError("bidirectional, projected or dropout LSTM at %s" % node.target)
+        h = m.hidden_size
+        order = torch.cat([torch.arange(0, h), torch.arange(3 * h, 4 * h), torch.arange(h, 2 * h), torch.arange(2 * h, 3 * h)])
+        cur = x
+        if m.batch_first:
+            cur = self.fresh("transpose")
+            self.g.add("Transpose", [x], [cur], perm=[1, 0, 2])
+        y_h = None
+        for l in range(m.num_layers):
+            w = getattr(m, "weight_ih_l%d" % l).detach()[order].unsqueeze(0)
+            r = getattr(m, "weight_hh_l%d" % l).detach()[order].unsqueeze(0)
+            ins = [cur, self.init("%s.W%d" % (q, l), w), self.init("%s.R%d" % (q, l), r)]
+            if m.bias:
+                b = torch.cat([getattr(m, "bias_ih_l%d" % l).detach()[order], getattr(m, "bias_hh_l%d" % l).detach()[order]])
+                ins.append(self.init("%s.B%d" % (q, l), b.unsqueeze(0)))
+            y4, y_h = self.fresh("lstm_y"), self.fresh("lstm_h")
+            self.g.add("LSTM", ins, [y4, y_h], hidden_size=int(h))
+            cur = self.fresh("squeeze")
+            self.g.add("Squeeze", [y4], [cur], axes=[1])           # [T, 1, B, H] -> [T, B, H]
+        if m.batch_first:
+            out = self.fresh("transpose")
+            self.g.add("Transpose", [cur], [out], perm=[1, 0, 2])
+            cur = out
+        self.names[node.name] = (cur, y_h)
 
     def pool(self, node, op_type, x, k, s, p) -> None:
         self.emit(node, op_type, [x], kernel_shape=_pair(k), strides=_pair(s if s is not None else k), pads=_pads(p))
@@ -113,7 +150,7 @@ class _Builder:
     def function_node(self, node) -> None:
         t, a, kw = node.target, node.args, node.kwargs
         arg = lambda i, key, default=None: a[i] if len(a) > i else kw.get(key, default)
-        x = self.src(a[0]) if a and hasattr(a[0], "name") else None
+        x = self.src(a[0]) if a and hasattr(a[0], "name") and isinstance(self.names.get(a[0].name), str) else None
         if t in (F.relu, torch.relu):
             self.emit(node, "Relu", [x])
         elif t in (torch.sigmoid, F.sigmoid):
@@ -141,6 +178,16 @@ class _Builder:
             self.emit(node, kind, [self.operand(v) for v in a[:2]])
         elif t is torch.cat:
             self.emit(node, "Concat", [self.src(v) for v in a[0]], axis=int(arg(1, "dim", 0)))
+        elif t is operator.getitem and isinstance(self.names.get(a[0].name), tuple):
+            picked = self.names[a[0].name][a[1]] if isinstance(a[1], int) else None
+            if picked is None:
+                raise NotImplementedError("only lstm(x)[0] and lstm(x)[1] are known at %s" % node.name)
+            self.names[node.name] = picked if isinstance(picked, str) else (picked,)
+        elif t is operator.getitem and isinstance(a[1], int) and a[1] < 0 and x is not None:
+            # x[-1] on the leading axis (the last time step of [T, B, H])
+            idx = self.fresh("const")
+            self.g.add("Constant", [], [idx], value=np.asarray(a[1], dtype=np.int64))
+            self.emit(node, "Gather", [x, idx], axis=0)
         else:
             raise NotImplementedError("no graph operator for the call %s at %s" % (getattr(t, "__name__", t), node.name))
 
@@ -161,6 +208,17 @@ class _Builder:
             self.emit(node, node.target.capitalize(), [x])
         elif node.target in ("contiguous", "float", "detach"):
             self.names[node.name] = x
+        elif node.target == "permute":
+            dims = node.args[1] if isinstance(node.args[1], (tuple, list)) else node.args[1:]
+            self.emit(node, "Transpose", [x], perm=[int(d) for d in dims])
+        elif node.target == "transpose":
+            meta = node.args[0].meta.get("tensor_meta") if hasattr(node.args[0], "meta") else None
+            if meta is None:
+                raise NotImplementedError("x.transpose() at %s needs the rank of x: pass example_inputs" % node.name)
+            perm = list(range(len(meta.shape)))
+            d0, d1 = int(node.args[1]) % len(perm), int(node.args[2]) % len(perm)
+            perm[d0], perm[d1] = perm[d1], perm[d0]
+            self.emit(node, "Transpose", [x], perm=perm)
         else:
             raise NotImplementedError("no graph operator for the method .%s() at %s" % (node.target, node.name))
 
@@ -187,12 +245,13 @@ class _Builder:
         return self.g
 
 
-def from_torch_module(module: nn.Module, name: Optional[str] = None) -> Graph:
-    """The forward pass of ``module`` as a graph whose initializers are the module's current weights."""
-    return _Builder(module, name or type(module).__name__).build()
+def from_torch_module(module: nn.Module, name: Optional[str] = None, example_inputs=None) -> Graph:
+    """The forward pass of ``module`` as a graph whose initializers are the module's current weights.
+    ``example_inputs`` (a tuple of tensors) lets the tracer know every intermediate shape; a few operators need it."""
+    return _Builder(module, name or type(module).__name__, example_inputs).build()
 
 
-def export_network(name_or_module, file_path: str, **kwargs) -> str:
+def export_network(name_or_module, file_path: str, example_inputs=None, **kwargs) -> str:
     """Write a network as an ``.onnx`` file and return the path: ``name_or_module`` is a module or a name that
     ``models.create_model`` knows ("simple_mnist", "deep_mnist", "wide_resnet", "resnet"); keyword arguments go to the
     constructor."""
@@ -208,6 +267,6 @@ def export_network(name_or_module, file_path: str, **kwargs) -> str:
         from .executor import from_torch_resnet
         g = from_torch_resnet(module)
     else:
-        g = from_torch_module(module)
+        g = from_torch_module(module, example_inputs=example_inputs)
     save_onnx(g, file_path)
     return file_path

@@ -451,3 +451,33 @@ def test_reference_executor_gradients_on_random_networks(use_cpp):
             assert np.allclose(a, b, rtol=2e-2, atol=2e-3 * max(1.0, float(np.abs(b).max()))), (name, layers)
 
     check()
+
+
+@pytest.mark.parametrize("batch_first,layers", [(False, 1), (True, 2)])
+def test_torch_lstm_models_become_onnx_lstm_nodes(batch_first, layers, tmp_path):
+    """A sequence classifier around torch.nn.LSTM (outputs of the last step into a dense layer) traced into ONNX LSTM
+    nodes, run by the executor on this package's LSTM layer, and once more from an .onnx file."""
+    from eagersgd_b200.graph import GraphNetwork, export_network, from_torch_module, load_onnx
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lstm = torch.nn.LSTM(6, 8, num_layers=layers, batch_first=batch_first)
+            self.fc = torch.nn.Linear(8, 3)
+
+        def forward(self, x):
+            out = self.lstm(x)[0]
+            last = out.transpose(0, 1)[-1] if batch_first else out[-1]
+            return self.fc(last)
+
+    torch.manual_seed(0)
+    m = Net().eval()
+    x = torch.randn(4, 5, 6) if batch_first else torch.randn(5, 4, 6)
+    g = from_torch_module(m, example_inputs=(x,))
+    assert [o.op_type for o in g.ops].count("LSTM") == layers
+    with torch.no_grad():
+        want = m(x)
+        got = GraphNetwork(g).eval()(x)
+        path = export_network(m, str(tmp_path / "lstm.onnx"), example_inputs=(x,))
+        again = GraphNetwork(load_onnx(path)).eval()(x)
+    assert torch.allclose(got, want, atol=1e-5) and torch.allclose(again, want, atol=1e-5)
