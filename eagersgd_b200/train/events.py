@@ -143,7 +143,16 @@ class TimeAbortAfterTestEvent(TrainingEvent):
             raise StopTraining("time budget used up")
 
 
-class TimeAbortImmediateEvent(TimeAbortAfterTestEvent):
+class TimeAbortImmediateEvent(TrainingEvent):
+    """Ends the run after the first optimizer step past the time budget; test passes are not cut short
+    (deep500/lv2/events/stopping_conditions.py:35-47)."""
+
+    def __init__(self, seconds: float):
+        self.seconds, self.t0 = seconds, None
+
+    def before_training(self, runner, training_stats):
+        self.t0 = time.time()
+
     def after_training_step(self, executor, optimizer, outputs, loss):
         if time.time() - self.t0 > self.seconds:
             raise StopTraining("time budget used up")

@@ -202,20 +202,31 @@ class CommunicationVolume(TestMetric):
 
 
 class CommProfiling(TestMetric):
-    """Device time of the communication stream between ``begin`` and ``end`` (stands where the
-    reference toggles MPI.Pcontrol, deep500/lv3/metrics.py:95-121)."""
+    """Time of the communication stream between ``begin`` and ``end``, in milliseconds (stands where the
+    reference toggles MPI.Pcontrol, deep500/lv3/metrics.py:95-121).  On GPUs it is device time between two
+    events on the optimizer's communication stream; for a CPU optimizer it is the growth of the channels'
+    own wait counters, that is the time this rank spent inside the collective waiting for peers."""
 
     def __init__(self, eager_optimizer):
         self.opt = eager_optimizer
+        self.gpu = bool(getattr(eager_optimizer, "on_gpu", False))
 
     def begin(self, *a):
-        self.e0 = torch.cuda.Event(enable_timing=True)
-        self.e0.record(self.opt.comm_stream)
+        if self.gpu:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record(self.opt.comm_stream)
+        else:
+            self.w0 = self.w1 = self.opt.stats()["wait_ms"]
 
     def end(self, *a):
-        self.e1 = torch.cuda.Event(enable_timing=True)
-        self.e1.record(self.opt.comm_stream)
+        if self.gpu:
+            self.e1 = torch.cuda.Event(enable_timing=True)
+            self.e1.record(self.opt.comm_stream)
+        else:
+            self.w1 = self.opt.stats()["wait_ms"]
 
     def measure(self, *a):
-        self.e1.synchronize()
-        return self.e0.elapsed_time(self.e1)
+        if self.gpu:
+            self.e1.synchronize()
+            return self.e0.elapsed_time(self.e1)
+        return self.w1 - self.w0

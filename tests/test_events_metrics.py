@@ -1,0 +1,157 @@
+"""Events and metrics of the training loop: every class does what its name says, on CPU.
+
+The reference's counterparts are deep500/lv2/events/*.py (terminal bar, time aborts, hyper-parameter
+schedules, plot generators) and deep500/lv0..lv3 metrics (norm errors, heatmaps, accuracies, sampler time,
+communication volume)."""
+import io
+import json
+import time
+
+import numpy as np
+import pytest
+import torch
+
+
+def _toy(events=None):
+    from eagersgd_b200.data import NumpyDataset, OrderedSampler, ShuffleSampler
+    rng = np.random.RandomState(0)
+    x = rng.randn(256, 16).astype(np.float32)
+    w = rng.randn(16, 4).astype(np.float32)
+    y = (x @ w).argmax(1).astype(np.int64)
+    ds = NumpyDataset(x, "x", y, "y")
+    return ds, ShuffleSampler(ds, 32, seed=0, events=events), OrderedSampler(ds, 64)
+
+
+def _trainer(lr=0.1, events=None):
+    from eagersgd_b200.optim.base import GradientDescent
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import Trainer
+    torch.manual_seed(0)
+    ds, tr, te = _toy(events)
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
+    opt = GradientDescent(ex, learning_rate=lr)
+    return Trainer(tr, te, ex, opt), opt
+
+
+def test_terminal_bar_prints_one_line_per_epoch():
+    from eagersgd_b200.train import events as E
+    out = io.StringIO()
+    tr, _ = _trainer()
+    stats = tr.run_loop(2, [E.SummaryGeneratorEvent(), E.TerminalBarEvent(out)])
+    lines = [l for l in out.getvalue().replace("\r", "\n").split("\n") if l.startswith("epoch ") and "loss" in l and "train-acc" in l]
+    assert len(lines) == 2
+    assert lines[1].startswith("epoch 1: loss %.4f" % stats.train_summaries[1].mean_loss)
+
+
+def test_time_abort_immediate_stops_inside_the_epoch():
+    from eagersgd_b200.train import events as E
+    tr, _ = _trainer()
+    ev = E.TimeAbortImmediateEvent(-1.0)                       # the budget is already used up
+    stats = tr.run_loop(3, [ev])
+    assert len(stats.train_summaries) == 1 and len(stats.train_summaries[0].losses) == 1
+    assert len(stats.test_summaries) == 1                       # only the pass before training ran
+    tr2, _ = _trainer()
+    after = E.TimeAbortAfterTestEvent(-1.0)                     # the same budget, checked after a test pass only
+    s2 = tr2.run_loop(3, [after])
+    assert len(s2.train_summaries) == 0 and len(s2.test_summaries) == 1
+
+
+def test_step_schedule_sets_the_rate_before_every_step():
+    from eagersgd_b200.train import events as E
+    seen = []
+
+    class Spy(E.TrainingEvent):
+        def after_optimizer_step(self, executor, optimizer, loss):
+            seen.append(optimizer.hyper["learning_rate"])
+
+    tr, opt = _trainer()
+    tr.run_loop(2, [E.StepHPSchedule(learning_rate=lambda k: 0.1 / (1 + k)), Spy()])
+    assert seen == pytest.approx([0.1 / (1 + k) for k in range(16)])   # 8 steps an epoch, the count runs on
+
+
+def test_box_plot_quartiles(tmp_path):
+    from eagersgd_b200.train import events as E
+    tr, _ = _trainer()
+    stats = tr.run_loop(2, [E.BoxPlotGeneratorEvent(str(tmp_path / "box"))])
+    q = json.load(open(tmp_path / "box.json"))["loss_quartiles_per_epoch"]
+    assert len(q) == 2
+    for quart, s in zip(q, stats.train_summaries):
+        assert quart[0] == pytest.approx(min(s.losses)) and quart[4] == pytest.approx(max(s.losses))
+        assert quart[2] == pytest.approx(float(np.median(s.losses)))
+        assert quart == sorted(quart)
+
+
+def test_norm_errors_and_heatmaps():
+    from eagersgd_b200.train import metrics as M
+    a = torch.tensor([[1.0, -2.0], [3.0, 4.0]])
+    b = np.array([[0.0, 0.0], [0.0, 1.0]])
+    assert M.L1Error().measure(None, a, b) == pytest.approx(9.0)
+    assert M.L2Error().measure(None, a, b) == pytest.approx(np.sqrt(1 + 4 + 9 + 9))
+    assert M.MaxError().measure(None, a, b) == pytest.approx(3.0)
+    assert M.MaxError().measure(None, a.bfloat16(), b) == pytest.approx(3.0)     # low-precision outputs are widened
+    np.testing.assert_allclose(M.DiffHeatmap().measure(None, a, b), [[1, 2], [3, 3]])
+    v = M.VarHeatmap()
+    for k in range(4):
+        var = v.measure(None, torch.full((2, 3), float(k)))
+    np.testing.assert_allclose(var, np.full((2, 3), np.var([0, 1, 2, 3])))
+
+
+def test_accuracy_metrics_accumulate_over_batches():
+    from eagersgd_b200.train import metrics as M
+    for cls in (M.TrainingAccuracy, M.TestAccuracy):
+        m = cls()
+        assert m.measure() == 0.0
+        m.update(torch.tensor([[0.1, 0.9], [0.8, 0.2]]), torch.tensor([1, 1]))
+        m.update(np.array([[0.3, 0.7], [0.3, 0.7], [0.9, 0.1]]), [1, 1, 0])
+        assert m.measure() == pytest.approx(4 / 5)
+    l = torch.tensor([[0.1, 0.5, 0.4], [0.7, 0.2, 0.1]])
+    assert M.topk_accuracy(l, torch.tensor([2, 1]), ks=(1, 2)) == pytest.approx([0.0, 1.0])
+
+
+def test_sampler_event_metric_times_every_draw():
+    from eagersgd_b200.train import metrics as M
+    m = M.SamplerEventMetric()
+    bias = M.DatasetBias(4)
+    assert m.measure() is None
+    ds, tr, _ = _toy([m])
+    n = 0
+    while True:
+        b = tr()
+        if b is None:
+            break
+        bias.update(b["y"])
+        n += 1
+    assert n == 8 and len(m.times) in (8, 9)                    # the draw that finds the epoch over may be timed too
+    assert 0 <= m.measure() < 1.0
+    labels = np.concatenate([ds[i]["y"].reshape(-1) for i in range(len(ds))])
+    assert (bias.measure() == np.bincount(labels, minlength=4)).all()      # one epoch saw every sample once
+
+
+def test_wallclock_time_takes_the_median_of_reruns():
+    from eagersgd_b200.train import metrics as M
+    w = M.WallclockTime(reruns=5, avg_over=1, device=torch.device("cpu"))
+    t = w.time_callable(lambda: time.sleep(0.002), warmup=1)
+    assert 1.5 < t < 50 and w.measure() == pytest.approx(t) and len(w.times) == 5       # milliseconds
+
+
+def test_communication_metrics_follow_the_optimizer_counters():
+    import eagersgd_b200 as es
+    from eagersgd_b200.train import metrics as M
+    torch.manual_seed(0)
+    m = torch.nn.Linear(8, 4)
+    o = es.SoloAllreduceOptimizer(torch.optim.SGD(m.parameters(), lr=0.1), es.Group())
+    try:
+        for _ in range(2):                                      # steps before begin() are not counted
+            o.zero_grad(); m(torch.randn(2, 8)).sum().backward(); o.step()
+        vol, prof = M.CommunicationVolume(o), M.CommProfiling(o)
+        vol.begin(); prof.begin()
+        for _ in range(3):
+            o.zero_grad(); m(torch.randn(2, 8)).sum().backward(); o.step()
+        prof.end()
+        r = vol.measure()
+        per_round = sum(b.count for b in o.buckets) * 4
+        assert r["steps"] == 3 and r["bytes_published"] == 3 * per_round and per_round >= 36 * 4
+        assert r["bytes_read_from_peers"] == 0                  # one rank: nothing crosses
+        assert 0 <= prof.measure() < 1000
+    finally:
+        o.close()
