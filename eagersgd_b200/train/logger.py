@@ -55,8 +55,15 @@ class BenchmarkFileLogger(BaseBenchmarkLogger):
             f.write("\n")
 
     def on_finish(self, status):
-        self._f.flush()
-        self._f.close()
+        """Close the metric file and leave the run's final status beside it (the reference keeps the status in
+        its BigQuery run-status table, logger.py:293-300; with no such service here it is a one-line file)."""
+        self.status = status
+        if not self._f.closed:
+            self._f.flush()
+            self._f.close()
+        with open(os.path.join(self.dir, "run_status.log"), "w") as f:
+            json.dump({"run_status": status}, f)
+            f.write("\n")
 
 
 def _metric(name, value, unit, global_step, extras):
@@ -74,6 +81,15 @@ def gather_run_info(model_name, dataset_name, run_params, test_id=None) -> dict:
     if torch.cuda.is_available():
         info["machine_config"]["gpu_info"] = {"count": torch.cuda.device_count(),
                                               "model": torch.cuda.get_device_name(0)}
+    try:                                      # memory of the host, when psutil is there (logger.py:407-416)
+        import psutil
+        vm = psutil.virtual_memory()
+        info["machine_config"]["memory_total"], info["machine_config"]["memory_available"] = vm.total, vm.available
+    except ImportError:
+        pass
+    # the switches of this framework and of its libraries that were set for the run (logger.py:361-366 lists TF_*)
+    info["environment_variables"] = [{"name": k, "value": v} for k, v in sorted(os.environ.items())
+                                     if k.startswith(("ESGD_", "NCCL_", "CUDA_", "OMP_"))]
     return info
 
 
