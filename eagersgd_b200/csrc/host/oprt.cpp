@@ -14,6 +14,8 @@
 #include <cstdlib>
 #include <cstring>
 #include <deque>
+#include <initializer_list>
+#include <limits>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -24,6 +26,10 @@
 
 namespace {
 
+constexpr size_t kDirectBytes = 16 << 10;         // bodies from this size on are copied straight into a listening receive
+constexpr size_t kPooledBodyBytes = 64 << 10;     // message bodies from this size on are recycled
+constexpr size_t kMaxSpareBodies = 64;
+constexpr size_t kMaxSpareBytes = 512u << 20;
 constexpr double kDefaultWaitSeconds = 600.0;   // what "no timeout" means: ten minutes, then RT_TIMEOUT
 // How long an idle progress thread / a waiter spins before it sleeps (ESGD_RT_SPIN_US overrides; 0 = sleep at once).
 int spin_micros() {
@@ -31,6 +37,7 @@ int spin_micros() {
   return v;
 }
 #define kSpinMicros spin_micros()
+constexpr int kBusySpinFactor = 20;   // the window of a thread that has reason to expect an event soon
 
 size_t dtype_size(int dt) { return dt == RT_CHAR ? 1 : (dt == RT_INT32 || dt == RT_FLOAT) ? 4 : 8; }
 
@@ -99,6 +106,8 @@ struct Schedule {
   void* state = nullptr;
 };
 
+struct Partial;   // state of one solo / majority allreduce (defined with the collectives)
+
 }  // namespace
 
 struct rt_world {
@@ -106,6 +115,11 @@ struct rt_world {
   std::vector<std::unique_ptr<rt_rank>> ranks;
   std::mutex mail_mu;
   std::map<std::tuple<int, int, int>, std::deque<Message>> mail;  // (src, dst, tag) -> FIFO
+  // Message bodies that have been delivered, kept for the next sends: a fresh allocation of a large body is
+  // fresh pages from the kernel every time, which costs more than the copy itself.  Guarded by mail_mu.
+  std::vector<std::vector<uint8_t>> spare_bodies;
+  size_t spare_bytes = 0;
+  std::atomic<int64_t> direct_bodies{0}, queued_bodies{0};   // how message bodies travelled (rt_world_stats)
 };
 
 struct rt_rank {
@@ -126,6 +140,10 @@ struct rt_rank {
   std::thread progress;
   std::atomic<bool> stop{false};
   std::atomic<uint64_t> signals{0};    // bumped with every wake-up of the progress thread (a spinning one sees it)
+  rt_op in_callback = RT_NONE;         // the callback operation that is running with the lock released
+  std::map<rt_sched, Partial*> partials;   // state of the partial allreduces that have not been deleted
+  std::map<int, int64_t> partial_generation;   // per tag: how many partial allreduces this rank has created
+  ~rt_rank();
 };
 
 namespace {
@@ -167,6 +185,7 @@ void run_comp(rt_rank* c, Op& op) {
 }
 
 void trigger(rt_rank* c, rt_op id);
+void free_op_locked(rt_rank* c, rt_op id);
 
 void post_locked(rt_rank* c, rt_op id) {
   c->ops[id]->posted++;
@@ -254,22 +273,93 @@ void execute(rt_rank* c, rt_op id, std::unique_lock<std::mutex>& lk) {
     case T_CALLBACK: {
       rt_callback_fn fn = op.cb;
       void* arg = op.cb_arg;
+      c->in_callback = id;
       lk.unlock();
       if (fn) fn(id, arg);
       lk.lock();
+      c->in_callback = RT_NONE;
+      if (!op.alive) {                 // freed while its callback ran
+        free_op_locked(c, id);
+        c->cv.notify_all();
+        break;
+      }
       complete(c, id);
       break;
     }
     case T_COMP: run_comp(c, op); complete(c, id); break;
     case T_SEND: {
       Buffer& b = c->bufs[op.a];
+      const size_t bytes = (size_t)b.count * dtype_size(b.dtype);
+      rt_rank* dst = c->world->ranks[op.peer].get();
+      if (bytes >= kDirectBytes && dst != c) {
+        // A large body goes straight into the buffer of a receive that is already listening: one copy instead of
+        // two.  The sender's own lock is released meanwhile (two partners that send to each other at the same moment,
+        // as in every round of the allreduce, would otherwise both find the other's lock taken), and the receiver's
+        // is only tried: when it is busy, or no receive is listening yet, the body is queued as usual.
+        const void* src = b.data();
+        const int key_tag = wire_tag(op.tag, op.options);
+        const auto key = std::make_tuple(c->id, op.peer, key_tag);
+        bool delivered = false;
+        c->in_callback = id;                            // keeps the operation alive while the lock is released
+        lk.unlock();
+        {
+          std::unique_lock<std::mutex> dl(dst->mu, std::try_to_lock);
+          if (dl.owns_lock()) {
+            bool nothing_queued;                        // an earlier body of this (source, tag) must not be overtaken
+            {
+              std::lock_guard<std::mutex> g(c->world->mail_mu);
+              auto it = c->world->mail.find(key);
+              nothing_queued = it == c->world->mail.end() || it->second.empty();
+            }
+            for (size_t i = 0; nothing_queued && i < dst->pending_recvs.size(); ++i) {
+              const rt_op rid = dst->pending_recvs[i];
+              if (!dst->ops[rid] || !dst->ops[rid]->alive) continue;
+              Op& ro = *dst->ops[rid];
+              if (ro.peer != c->id || wire_tag(ro.tag, ro.options) != key_tag) continue;
+              Buffer& rb = dst->bufs[ro.a];
+              const size_t cap = (size_t)rb.count * dtype_size(rb.dtype);
+              memcpy(rb.data(), src, bytes < cap ? bytes : cap);
+              ro.in_flight = false;
+              dst->pending_recvs.erase(dst->pending_recvs.begin() + i);
+              complete(dst, rid);
+              delivered = true;
+              break;
+            }
+          }
+        }
+        if (delivered) {
+          dst->signals.fetch_add(1, std::memory_order_release);
+          dst->work_cv.notify_all();
+        }
+        lk.lock();
+        c->in_callback = RT_NONE;
+        if (!op.alive) {                                // freed meanwhile
+          free_op_locked(c, id);
+          c->cv.notify_all();
+          break;
+        }
+        if (delivered) { c->world->direct_bodies.fetch_add(1, std::memory_order_relaxed); complete(c, id); break; }
+      }
+      c->world->queued_bodies.fetch_add(1, std::memory_order_relaxed);
       Message m;
-      m.data.assign((uint8_t*)b.data(), (uint8_t*)b.data() + (size_t)b.count * dtype_size(b.dtype));
+      if (bytes >= kPooledBodyBytes) {                  // take a delivered body of sufficient capacity, if there is one
+        std::lock_guard<std::mutex> g(c->world->mail_mu);
+        auto& pool = c->world->spare_bodies;
+        for (size_t i = 0; i < pool.size(); ++i)
+          if (pool[i].capacity() >= bytes) {
+            c->world->spare_bytes -= pool[i].capacity();
+            m.data = std::move(pool[i]);
+            pool[i] = std::move(pool.back());
+            pool.pop_back();
+            break;
+          }
+      }
+      m.data.resize(bytes);
+      memcpy(m.data.data(), b.data(), bytes);
       {
         std::lock_guard<std::mutex> g(c->world->mail_mu);
         c->world->mail[std::make_tuple(c->id, op.peer, wire_tag(op.tag, op.options))].push_back(std::move(m));
       }
-      rt_rank* dst = c->world->ranks[op.peer].get();
       dst->signals.fetch_add(1, std::memory_order_release);
       dst->work_cv.notify_all();
       complete(c, id);
@@ -301,6 +391,13 @@ bool poll_recvs(rt_rank* c) {
     Buffer& b = c->bufs[op.a];
     size_t cap = (size_t)b.count * dtype_size(b.dtype);
     memcpy(b.data(), m.data.data(), m.data.size() < cap ? m.data.size() : cap);
+    if (m.data.capacity() >= kPooledBodyBytes) {         // keep the body for a later send
+      std::lock_guard<std::mutex> g(c->world->mail_mu);
+      if (c->world->spare_bodies.size() < kMaxSpareBodies && c->world->spare_bytes + m.data.capacity() <= kMaxSpareBytes) {
+        c->world->spare_bytes += m.data.capacity();
+        c->world->spare_bodies.push_back(std::move(m.data));
+      }
+    }
     op.in_flight = false;
     c->pending_recvs.erase(c->pending_recvs.begin() + i);
     complete(c, id);
@@ -325,12 +422,15 @@ void progress_loop(rt_rank* c) {
       // microseconds each.  So the thread first spins for a short while (lock released) on the counter that every
       // waker bumps, and only then goes to sleep.
       const uint64_t seen = c->signals.load(std::memory_order_acquire);
+      // a rank that is listening for a message expects one soon (its peer is copying a body right now, which for a
+      // large body takes longer than the plain window): it spins longer before it pays for a sleep and a wake-up
+      const int window = c->pending_recvs.empty() ? kSpinMicros : kSpinMicros * kBusySpinFactor;
       lk.unlock();
       const auto t0 = std::chrono::steady_clock::now();
       int polls = 0;
       while (c->signals.load(std::memory_order_acquire) == seen && !c->stop.load()) {
         if ((++polls & 63) == 0) {
-          if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(kSpinMicros)) break;
+          if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(window)) break;
           std::this_thread::yield();
         }
       }
@@ -361,6 +461,10 @@ rt_op new_op(rt_rank* c, OpType t, int options) {
 void free_op_locked(rt_rank* c, rt_op id) {
   if (id < 0 || id >= (rt_op)c->ops.size() || !c->ops[id]) return;
   Op& op = *c->ops[id];
+  if (c->in_callback == id) {          // its callback is running right now: execute() frees it when that returns
+    op.alive = false;
+    return;
+  }
   for (Edge& e : op.edges)
     if (e.child != RT_NONE && e.child != id && c->ops[e.child]) {
       Op& ch = *c->ops[e.child];
@@ -405,6 +509,10 @@ void rt_world_destroy(rt_world* w) {
 }
 
 rt_rank* rt_world_rank(rt_world* w, int r) { return w->ranks[r].get(); }
+int rt_world_stats(rt_world* w, int64_t* out) {
+  out[0] = w->direct_bodies.load(); out[1] = w->queued_bodies.load();
+  return RT_SUCCESS;
+}
 int rt_rank_id(rt_rank* c) { return c->id; }
 int rt_rank_size(rt_rank* c) { return c->world->n; }
 
@@ -563,12 +671,13 @@ int rt_op_wait(rt_rank* c, rt_op id, double timeout_s) {
   auto pred = [&] { return op.completed.load() >= want; };
   if (timeout_s <= 0) timeout_s = kDefaultWaitSeconds;    // no wait is unbounded
   if (!pred()) {                                          // spin briefly before sleeping (see progress_loop)
+    const int window = (c->pending_recvs.empty() && c->posted.empty()) ? kSpinMicros : kSpinMicros * kBusySpinFactor;
     lk.unlock();
     const auto t0 = std::chrono::steady_clock::now();
     int polls = 0;
     while (!pred()) {
       if ((++polls & 63) == 0) {
-        if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(kSpinMicros)) break;
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(window)) break;
         std::this_thread::yield();
       }
     }
@@ -819,8 +928,8 @@ rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper) {
     rt_op sd = rt_op_send(c, rcv, peer, tag, 0);
     rt_op rv = rt_op_recv(c, tmp, peer, tag, 0);
     rt_op cp = rt_op_comp(c, tmp, rcv, rcv, oper, 0);
-    rt_op_hb(c, last, sd);              // send what has been reduced so far ...
-    rt_op_hb(c, last, rv);              // ... while the partner's data arrives
+    rt_op_hb(c, last, rv);              // listen first: a partner that sends now can copy straight into tmp ...
+    rt_op_hb(c, last, sd);              // ... then send what has been reduced so far
     rt_op_hb(c, sd, cp);
     rt_op_hb(c, rv, cp);
     rt_schedule_add_op(c, s, sd);
@@ -877,6 +986,363 @@ int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op*
   return RT_SUCCESS;
 }
 
+}  // extern "C"
+
+// ---- partial allreduces as schedules of this runtime ------------------------------------------------------------------
+// The reference builds its solo and majority allreduces from an activation schedule, two allreduce schedules and a
+// limiter, glued by version-checked edges (fflib2 src/colls/ffsolo_allreduce.c:21-148, ffrand_allreduce.c:27-128,
+// ffactivation.c:11-106).  Here the rounds are numbered instead: a rank's j-th post belongs to round j, the token
+// that activates a round carries its number, and every rank runs every round in order.  A post that finds its round
+// already begun (another rank activated it) has nothing left to start; what it staged goes into the next round.
+namespace {
+
+struct TokenArg;
+
+struct Partial {
+  rt_rank* c = nullptr;
+  rt_sched self = RT_NONE, ar_data = RT_NONE, ar_cnt = RT_NONE;
+  rt_buf snd = RT_NONE, rcv = RT_NONE, stage = RT_NONE, work = RT_NONE, flag = RT_NONE, tok_out = RT_NONE;
+  std::vector<rt_buf> tok_in;
+  std::vector<rt_op> sends, recvs, tok_cbs;
+  rt_op cb_post = RT_NONE, cb_begin = RT_NONE, cb_end = RT_NONE;
+  int mode = 0;            // 0: solo (whoever posts first activates), 1: majority (one drawn rank per round activates)
+  int oper = RT_SUM, dtype = RT_FLOAT, tag = 0, options = 0;
+  int token_tag = 0;       // tag of the activation tokens: the user's tag and which schedule of that tag this is, so that a
+                           // schedule which is about to be deleted never swallows a token meant for its successor
+  int64_t count = 0, limiter = -1;
+  uint64_t seed = 0;
+  bool started_flag = false;
+  std::vector<TokenArg*> token_args;
+  // everything below is guarded by mu
+  std::mutex mu;
+  bool fresh = false;      // the stage holds a contribution that no round has taken yet
+  int64_t posts = 0, posted_by_user = 0, started = 0, begun = 0, done = 0, queued = 0;
+  bool running = false;
+  int64_t activated = 0, late = 0, sync_rounds = 0, overwritten = 0, last_contributors = 0, last_round = -1;
+
+  bool is_sync(int64_t j) const { return limiter >= 0 && (j % (limiter + 1)) == limiter; }
+  int activator(int64_t j) const {           // the same draw on every rank (ffrand_allreduce.c:88 uses rand_r)
+    uint64_t z = seed + 0x9e3779b97f4a7c15ULL * (uint64_t)(j + 1);
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+    z ^= z >> 31;
+    return (int)(z % (uint64_t)c->world->n);
+  }
+};
+
+struct TokenArg { Partial* st; int peer; };
+
+template <class T>
+void fill_typed(T* p, int64_t n, int oper) {
+  T v = T(0);
+  if (oper == RT_PROD) v = T(1);
+  else if (oper == RT_MAX) v = std::numeric_limits<T>::lowest();
+  else if (oper == RT_MIN) v = std::numeric_limits<T>::max();
+  for (int64_t i = 0; i < n; ++i) p[i] = v;
+}
+
+// The neutral element of a built-in operator: what a rank without a fresh contribution puts into a round.
+void fill_neutral(void* p, int64_t n, int dtype, int oper) {
+  switch (dtype) {
+    case RT_INT32: fill_typed((int32_t*)p, n, oper); break;
+    case RT_INT64: fill_typed((int64_t*)p, n, oper); break;
+    case RT_CHAR: fill_typed((signed char*)p, n, oper); break;
+    case RT_FLOAT: fill_typed((float*)p, n, oper); break;
+    default: fill_typed((double*)p, n, oper); break;
+  }
+}
+
+// Ask for every round up to j.  Returns how many times cb_begin has to be posted now (0 or 1).  Called with st->mu held.
+int request_upto_locked(Partial* st, int64_t j) {
+  int post_now = 0;
+  while (st->started <= j) {
+    st->started++;
+    if (st->running) st->queued++;
+    else { st->running = true; post_now = 1; }
+  }
+  return post_now;
+}
+
+// The user's post has reached the progress thread.
+void partial_on_post(rt_op, void* arg) {
+  Partial* st = (Partial*)arg;
+  bool activate = false;
+  int post_now = 0;
+  int64_t j;
+  {
+    std::lock_guard<std::mutex> g(st->mu);
+    j = st->posts++;
+    const bool sync = st->is_sync(j);
+    if (st->started <= j) {
+      if (sync) post_now = request_upto_locked(st, j);
+      else if (st->mode == 0 || st->activator(j) == st->c->id) {
+        activate = true;
+        st->activated++;
+        post_now = request_upto_locked(st, j);
+      }
+    } else if (!sync) {
+      st->late++;
+    }
+  }
+  if (activate) {
+    *(int64_t*)rt_buffer_data(st->c, st->tok_out) = j;
+    for (rt_op sd : st->sends) rt_op_post(st->c, sd);    // they run before the round begins: the queue is FIFO
+  }
+  if (post_now) rt_op_post(st->c, st->cb_begin);
+}
+
+// A token from a peer: it names the newest round that peer has activated.
+void partial_on_token(rt_op, void* arg) {
+  TokenArg* ta = (TokenArg*)arg;
+  Partial* st = ta->st;
+  const int64_t t = *(int64_t*)rt_buffer_data(st->c, st->tok_in[ta->peer]);
+  int post_now = 0;
+  {
+    std::lock_guard<std::mutex> g(st->mu);
+    if (t >= st->started) post_now = request_upto_locked(st, t);
+  }
+  if (post_now) rt_op_post(st->c, st->cb_begin);
+}
+
+// A round begins on this rank: its contribution is what the user staged since the last round, or nothing.
+void partial_on_begin(rt_op, void* arg) {
+  Partial* st = (Partial*)arg;
+  int32_t* flag = (int32_t*)rt_buffer_data(st->c, st->flag);
+  const size_t bytes = (size_t)st->count * dtype_size(st->dtype);
+  const bool keeps_last = (st->options & RT_PARTIAL_STALE) || st->oper >= RT_CUSTOM0;
+  std::lock_guard<std::mutex> g(st->mu);
+  const int64_t round = st->begun++;
+  if (st->is_sync(round)) st->sync_rounds++;
+  if (st->fresh && !keeps_last) {
+    // the staged contribution becomes the round's working vector by exchanging the two buffers' storage: the
+    // stage is rewritten by the next post anyway
+    std::lock_guard<std::mutex> gc(st->c->mu);
+    std::swap(st->c->bufs[st->stage].own, st->c->bufs[st->work].own);
+    st->fresh = false;
+    *flag = 1;
+    return;
+  }
+  void* work = rt_buffer_data(st->c, st->work);
+  void* stage = rt_buffer_data(st->c, st->stage);
+  if (st->fresh) {
+    memcpy(work, stage, bytes);
+    st->fresh = false;
+    *flag = 1;
+  } else {
+    *flag = 0;
+    if (keeps_last) memcpy(work, stage, bytes);          // its last contribution again
+    else fill_neutral(work, st->count, st->dtype, st->oper);
+  }
+}
+
+// The round has ended everywhere it matters for this rank: hand the result over and begin the next one if asked.
+void partial_on_end(rt_op, void* arg) {
+  Partial* st = (Partial*)arg;
+  void* rcv = rt_buffer_data(st->c, st->rcv);
+  const int32_t contributors = *(int32_t*)rt_buffer_data(st->c, st->flag);
+  int post_now = 0;
+  {
+    std::lock_guard<std::mutex> g(st->mu);
+    const void* work = rt_buffer_data(st->c, st->work);
+    memcpy(rcv, work, (size_t)st->count * dtype_size(st->dtype));
+    st->last_contributors = contributors;
+    st->last_round = st->done++;
+    st->running = false;
+    if (st->queued > 0) { st->queued--; st->running = true; post_now = 1; }
+  }
+  if (post_now) rt_op_post(st->c, st->cb_begin);
+}
+
+int partial_start(rt_rank* c, rt_sched s) {
+  Partial* st = (Partial*)rt_schedule_get_state(c, s);
+  if (!st) return RT_ERROR;
+  if (st->started_flag) return RT_SUCCESS;
+  st->started_flag = true;
+  for (rt_op rv : st->recvs) rt_op_post(c, rv);          // listen for tokens from now on
+  return RT_SUCCESS;
+}
+
+// Runs in the caller's thread: the contribution is taken here, so the caller may reuse its buffer at once.
+int partial_post(rt_rank* c, rt_sched s) {
+  Partial* st = (Partial*)rt_schedule_get_state(c, s);
+  if (!st || !st->started_flag) return RT_ERROR;
+  const void* snd = rt_buffer_data(c, st->snd);
+  {
+    std::lock_guard<std::mutex> g(st->mu);
+    void* stage = rt_buffer_data(c, st->stage);          // under the lock: a round that begins exchanges stage and work
+    if (st->fresh && (st->options & RT_PARTIAL_ACCUMULATE) && st->oper < RT_CUSTOM0 && st->oper != RT_IDENTITY) {
+      // what no round has taken yet is combined with the new contribution instead of being replaced by it
+      switch (st->dtype) {
+        case RT_INT32: reduce_typed((const int32_t*)stage, (const int32_t*)snd, (int32_t*)stage, st->count, st->oper); break;
+        case RT_INT64: reduce_typed((const int64_t*)stage, (const int64_t*)snd, (int64_t*)stage, st->count, st->oper); break;
+        case RT_CHAR: reduce_typed((const signed char*)stage, (const signed char*)snd, (signed char*)stage, st->count, st->oper); break;
+        case RT_FLOAT: reduce_typed((const float*)stage, (const float*)snd, (float*)stage, st->count, st->oper); break;
+        default: reduce_typed((const double*)stage, (const double*)snd, (double*)stage, st->count, st->oper); break;
+      }
+    } else {
+      if (st->fresh) st->overwritten++;                  // the reference's behaviour: the older contribution is lost
+      memcpy(stage, snd, (size_t)st->count * dtype_size(st->dtype));
+    }
+    st->fresh = true;
+    st->posted_by_user++;
+  }
+  return rt_op_post(c, st->cb_post);
+}
+
+int partial_delete(rt_rank* c, rt_sched s) {
+  Partial* st = (Partial*)rt_schedule_get_state(c, s);
+  if (!st) return RT_ERROR;
+  std::vector<rt_op> cbs = st->tok_cbs;
+  cbs.push_back(st->cb_post); cbs.push_back(st->cb_begin); cbs.push_back(st->cb_end);
+  {                                    // tokens of concurrent activators that nobody will read any more
+    std::lock_guard<std::mutex> g(c->world->mail_mu);
+    for (int r = 0; r < c->world->n; ++r) c->world->mail.erase(std::make_tuple(r, c->id, wire_tag(st->token_tag, RT_SHADOW_TAG)));
+  }
+  const int rc = rt_schedule_delete(c, s);               // the default: operations, parts, owned buffers
+  for (int spins = 0; spins < 2000000; ++spins) {        // a callback of this schedule may still be returning
+    {
+      std::lock_guard<std::mutex> g(c->mu);
+      bool busy = false;
+      for (rt_op id : cbs) busy = busy || c->in_callback == id;
+      if (!busy) break;
+    }
+    std::this_thread::yield();
+  }
+  { std::lock_guard<std::mutex> g(c->mu); c->partials.erase(s); }
+  for (TokenArg* ta : st->token_args) delete ta;
+  delete st;
+  return rc;
+}
+
+int partial_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
+  Partial* st = (Partial*)rt_schedule_get_state(c, s);
+  if (!st || cap < 1) return RT_ERROR;
+  int64_t used = 0;
+  for (rt_sched part : {st->ar_data, st->ar_cnt}) {      // the parts first, as ffsolo_allreduce_print does
+    const int n = rt_schedule_print(c, part, out + used, cap - used);
+    if (n < 0) return RT_ERROR;
+    used += n;
+  }
+  rt_sched_print_fn self = nullptr;
+  { std::lock_guard<std::mutex> g(c->mu); self = c->scheds[s].print_fn; c->scheds[s].print_fn = nullptr; }
+  const int n = rt_schedule_print(c, s, out + used, cap - used);
+  { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].print_fn = self; }
+  return n < 0 ? RT_ERROR : (int)(used + n);
+}
+
+rt_sched make_partial(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper, int mode, uint64_t seed, int limiter,
+                      int options) {
+  const int P = c->world->n, me = c->id;
+  int64_t count;
+  int dtype;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (snd < 0 || rcv < 0 || snd >= (rt_buf)c->bufs.size() || rcv >= (rt_buf)c->bufs.size()) return RT_ERROR;
+    count = c->bufs[rcv].count; dtype = c->bufs[rcv].dtype;
+    if (c->bufs[snd].count != count || c->bufs[snd].dtype != dtype) return RT_ERROR;
+  }
+  Partial* st = new Partial();
+  st->c = c; st->snd = snd; st->rcv = rcv; st->tag = tag; st->oper = oper; st->mode = mode; st->seed = seed;
+  st->limiter = limiter; st->options = options; st->count = count; st->dtype = dtype;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    st->token_tag = (tag & 0xffff) | (int)((c->partial_generation[tag]++ & 0x3ff) << 16);
+  }
+  rt_sched s = rt_schedule_create(c);
+  st->self = s;
+  auto own = [&](int64_t n, int dt) { rt_buf b = rt_buffer_create(c, nullptr, n, dt); rt_schedule_own_buffer(c, s, b); return b; };
+  st->stage = own(count, dtype);
+  st->work = own(count, dtype);
+  st->flag = own(1, RT_INT32);
+  st->tok_out = own(1, RT_INT64);
+  if (!(options & RT_PARTIAL_STALE) && oper < RT_CUSTOM0)
+    fill_neutral(rt_buffer_data(c, st->stage), count, dtype, oper);
+  st->ar_data = rt_allreduce(c, RT_INPLACE, st->work, tag, oper);
+  st->ar_cnt = rt_allreduce(c, RT_INPLACE, st->flag, tag, RT_SUM);   // how many ranks put something fresh into the round
+  rt_schedule_add_part(c, s, st->ar_data);
+  rt_schedule_add_part(c, s, st->ar_cnt);
+  auto add = [&](rt_op op) { rt_schedule_add_op(c, s, op); return op; };
+  st->cb_post = add(rt_op_callback(c, partial_on_post, st, RT_DEP_OR));
+  st->cb_begin = add(rt_op_callback(c, partial_on_begin, st, RT_DEP_OR));
+  st->cb_end = add(rt_op_callback(c, partial_on_end, st, RT_DEP_OR));
+  rt_op_hb(c, st->cb_begin, rt_schedule_begin_op(c, st->ar_data));
+  rt_op_hb(c, rt_schedule_end_op(c, st->ar_data), rt_schedule_begin_op(c, st->ar_cnt));
+  rt_op_hb(c, rt_schedule_end_op(c, st->ar_cnt), st->cb_end);
+  rt_op_hb(c, st->cb_end, rt_schedule_end_op(c, s));      // the schedule's end completes once per round
+  rt_op_hb(c, rt_schedule_begin_op(c, s), st->cb_post);
+  st->tok_in.assign(P, RT_NONE);
+  for (int r = 0; r < P; ++r) {
+    if (r == me) continue;
+    st->sends.push_back(add(rt_op_send(c, st->tok_out, r, st->token_tag, RT_SHADOW_TAG | RT_DEP_OR)));
+    st->tok_in[r] = own(1, RT_INT64);
+    rt_op rv = add(rt_op_recv(c, st->tok_in[r], r, st->token_tag, RT_SHADOW_TAG | RT_DEP_OR));
+    TokenArg* ta = new TokenArg{st, r};
+    st->token_args.push_back(ta);
+    rt_op cb = add(rt_op_callback(c, partial_on_token, ta, RT_DEP_OR));
+    rt_op_hb(c, rv, cb);                                  // read the token, then listen again
+    rt_op_hb(c, cb, rv);
+    st->recvs.push_back(rv);
+    st->tok_cbs.push_back(cb);
+  }
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    c->scheds[s].finalized = true;                        // wired by hand: no automatic begin / end links
+    c->scheds[s].state = st;
+    c->scheds[s].start_fn = partial_start;
+    c->scheds[s].post_fn = partial_post;
+    c->scheds[s].delete_fn = partial_delete;
+    c->scheds[s].print_fn = partial_print;
+    c->partials[s] = st;
+  }
+  return s;
+}
+
+}  // namespace
+
+rt_rank::~rt_rank() {                  // partial allreduces that were never deleted
+  for (auto& kv : partials) {
+    for (TokenArg* ta : kv.second->token_args) delete ta;
+    delete kv.second;
+  }
+}
+
+extern "C" {
+
+rt_sched rt_solo_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op, int limiter, int options) {
+  return make_partial(c, snd, rcv, tag, op, 0, 0, limiter, options);
+}
+
+rt_sched rt_rand_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op, int seed, int limiter, int options) {
+  return make_partial(c, snd, rcv, tag, op, 1, (uint64_t)(uint32_t)seed, limiter, options);
+}
+
+int rt_partial_info(rt_rank* c, rt_sched s, int64_t* out) {
+  Partial* st;
+  { std::lock_guard<std::mutex> g(c->mu); auto it = c->partials.find(s); if (it == c->partials.end()) return RT_ERROR; st = it->second; }
+  std::lock_guard<std::mutex> g(st->mu);
+  out[0] = st->posted_by_user; out[1] = st->done; out[2] = st->activated; out[3] = st->late; out[4] = st->sync_rounds;
+  out[5] = st->last_contributors; out[6] = st->last_round; out[7] = st->overwritten; out[8] = st->fresh ? 1 : 0;
+  return RT_SUCCESS;
+}
+
+int rt_partial_read(rt_rank* c, rt_sched s, void* out, int64_t* contributors, int64_t* round) {
+  Partial* st;
+  { std::lock_guard<std::mutex> g(c->mu); auto it = c->partials.find(s); if (it == c->partials.end()) return RT_ERROR; st = it->second; }
+  const void* rcv = rt_buffer_data(c, st->rcv);
+  std::lock_guard<std::mutex> g(st->mu);
+  if (out) memcpy(out, rcv, (size_t)st->count * dtype_size(st->dtype));
+  if (contributors) *contributors = st->last_contributors;
+  if (round) *round = st->last_round;
+  return RT_SUCCESS;
+}
+
+int rt_partial_activator(rt_rank* c, rt_sched s, int64_t round) {
+  Partial* st;
+  { std::lock_guard<std::mutex> g(c->mu); auto it = c->partials.find(s); if (it == c->partials.end()) return RT_ERROR; st = it->second; }
+  if (st->mode != 1 || st->is_sync(round)) return -1;
+  return st->activator(round);
+}
+
 // Micro-benchmark of the runtime by itself (no interpreter in the loop): `ranks` native threads run the protocol
 // of the reference's allreduce programs on int32 vectors of `count` elements, checked against the closed form.
 //   fresh = 1: a new schedule per iteration — create, post, wait, delete (evaluation/allreduce.c:44-72);
@@ -923,6 +1389,61 @@ int rt_bench_allreduce(int ranks, int64_t count, int iters, int fresh, double* o
     if (!ok[r]) good = 0;
   }
   out_us[0] = worst; out_us[1] = cr; out_us[2] = good;
+  return RT_SUCCESS;
+}
+
+// The reference's SGD-loop timing programs on this runtime (evaluation/ssgd.c:63-97, rsgd.c:77-113,
+// randomsgd.c:78-113): every iteration rank r first sleeps r * skew_us, fills its vector with ones, times post + wait
+// of the persistent collective, clears the vector, and meets the others at a barrier.  mode 0: synchronous allreduce,
+// 1: solo, 2: majority (limiter 1024 as in those programs).  out[0]: microseconds per post + wait, averaged over
+// ranks and over the iterations after the second (the figure those programs print); out[1]: mean number of fresh
+// contributors per round as the ranks saw it after their waits; out[2]: 1.0 if every result read was a whole number
+// between 0 and the number of ranks.
+int rt_bench_partial(int ranks, int64_t count, int iters, int mode, int skew_us, double* out) {
+  if (ranks < 1 || count < 1 || iters < 3 || mode < 0 || mode > 2) return RT_ERROR;
+  rt_world* w = rt_world_create(ranks);
+  std::vector<double> per(ranks, 0.0), contrib(ranks, 0.0);
+  std::vector<int> ok(ranks, 1);
+  std::atomic<int64_t> arrived{0};
+  auto barrier = [&](int64_t generation) {
+    arrived.fetch_add(1);
+    int polls = 0;
+    while (arrived.load() < generation * ranks)
+      if ((++polls & 255) == 0) std::this_thread::sleep_for(std::chrono::microseconds(20)); else std::this_thread::yield();
+  };
+  auto body = [&](int r) {
+    rt_rank* c = rt_world_rank(w, r);
+    std::vector<float> snd(count, 0.f), rcv(count, 0.f), res(count, 0.f);
+    rt_buf bs = rt_buffer_create(c, snd.data(), count, RT_FLOAT), br = rt_buffer_create(c, rcv.data(), count, RT_FLOAT);
+    rt_sched s = mode == 0 ? rt_allreduce(c, bs, br, 0, RT_SUM)
+               : mode == 1 ? rt_solo_allreduce(c, bs, br, 0, RT_SUM, 1024, 0)
+                           : rt_rand_allreduce(c, bs, br, 0, RT_SUM, 1234, 1024, 0);
+    rt_schedule_start(c, s);
+    barrier(1);
+    for (int it = 0; it < iters; ++it) {
+      if (skew_us > 0 && r > 0) std::this_thread::sleep_for(std::chrono::microseconds((int64_t)r * skew_us));
+      for (int64_t j = 0; j < count; ++j) snd[j] = 1.f;
+      const auto t0 = std::chrono::steady_clock::now();
+      rt_schedule_post(c, s);
+      if (rt_schedule_wait(c, s, 30.0) != RT_SUCCESS) { ok[r] = 0; break; }
+      const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      int64_t k = ranks, rnd = 0;
+      if (mode == 0) { res[0] = rcv[0]; res[count - 1] = rcv[count - 1]; }
+      else rt_partial_read(c, s, res.data(), &k, &rnd);
+      if (res[0] < 0.f || res[0] > (float)ranks || res[0] != (float)(int)res[0] || res[count - 1] != res[0]) ok[r] = 0;
+      if (it >= 2) { per[r] += us; contrib[r] += (double)k; }
+      for (int64_t j = 0; j < count; ++j) snd[j] = 0.f;
+      barrier(it + 2);
+    }
+    rt_schedule_delete(c, s);
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < ranks; ++r) th.emplace_back(body, r);
+  for (auto& t : th) t.join();
+  rt_world_destroy(w);
+  double us = 0, k = 0, good = 1;
+  for (int r = 0; r < ranks; ++r) { us += per[r]; k += contrib[r]; if (!ok[r]) good = 0; }
+  out[0] = us / ranks / (iters - 2); out[1] = k / ranks / (iters - 2); out[2] = good;
   return RT_SUCCESS;
 }
 

@@ -47,6 +47,12 @@ enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUST
 #define RT_COMP_DEST_ATOMIC 0x400    /* compute op: the destination is updated atomically with respect to other
                                         compute ops of the rank.  Always true here (one progress thread per rank
                                         runs them one at a time); the bit is accepted for source compatibility. */
+/* options of the partial allreduces (rt_solo_allreduce, rt_rand_allreduce) */
+#define RT_PARTIAL_STALE 0x800       /* a rank with nothing new puts its previous contribution into the round again (what the
+                                        reference does when the caller leaves its send buffer alone); default: the operator's
+                                        neutral element, so that only fresh contributions count */
+#define RT_PARTIAL_ACCUMULATE 0x1000 /* a contribution that no round has taken yet is combined with the next one instead of
+                                        being replaced by it: nothing a rank posts is lost */
 /* Buffers are always handles into the rank's table (the reference's FFBUFFER_IDX); a handle made around user memory
  * is its FFBUFFER_PTR, and every collective takes handles, so user-managed buffers (FFCOLL_BUFFERS) are the rule. */
 #define RT_INPLACE ((int64_t)-2)
@@ -67,6 +73,8 @@ typedef void (*rt_operator_fn)(const void* a, const void* b, void* out, int64_t 
 rt_world* rt_world_create(int nranks);
 void rt_world_destroy(rt_world* w);
 rt_rank* rt_world_rank(rt_world* w, int r);
+/* out[2]: message bodies copied straight into a listening receive, and bodies queued in the mailbox */
+int rt_world_stats(rt_world* w, int64_t* out);
 int rt_rank_id(rt_rank* c);
 int rt_rank_size(rt_rank* c);
 
@@ -133,8 +141,30 @@ rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined);
 /* limiter: posting `start` fires async[0..n-1] in turn, then sync, round-robin */
 int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op* sync_op);
 
+/* Partial allreduces (ffsolo_allreduce / ffrand_allreduce, ff.h:161-165): persistent schedules with start / post / wait /
+ * test / delete / print like any other.  A rank's j-th post belongs to round j.  In a solo allreduce the first rank to post j
+ * activates the round on every rank; in a majority ("rand") allreduce only the rank drawn for round j (the same draw everywhere,
+ * from `seed`) does.  A rank takes part in every round with what it has posted since the previous one, or with nothing; its
+ * j-th wait returns when round j has completed, which may be long before its own j-th post.  With limiter L >= 0 every
+ * (L+1)-th round is synchronous: it begins on a rank only with that rank's own post (L < 0: never).  The contribution is
+ * copied inside post, so the send buffer may be reused at once; the result buffer is rewritten by every round
+ * (rt_partial_read copies it together with the number of fresh contributors without tearing).  Every rank creates the
+ * schedule with the same arguments and posts it the same number of times.  Tags are 16 bits wide (as the reference's);
+ * schedules that reuse a tag must be created in the same order on every rank. */
+rt_sched rt_solo_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op, int limiter, int options);
+rt_sched rt_rand_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op, int seed, int limiter, int options);
+/* out[9]: posts, rounds completed, rounds this rank activated, posts that found their round already begun, synchronous
+ * rounds, fresh contributors of the newest round, its number, contributions replaced before any round took them,
+ * 1 if a contribution is waiting for a round */
+int rt_partial_info(rt_rank* c, rt_sched s, int64_t* out);
+int rt_partial_read(rt_rank* c, rt_sched s, void* out, int64_t* contributors, int64_t* round);
+int rt_partial_activator(rt_rank* c, rt_sched s, int64_t round);   /* majority: the rank drawn for a round (-1: synchronous) */
+
 /* native micro-benchmark (threads of this process as ranks); out_us: per-iteration, first creation, all-correct flag */
 int rt_bench_allreduce(int ranks, int64_t count, int iters, int fresh, double* out_us);
+/* the skewed SGD loop of the reference's ssgd.c / rsgd.c / randomsgd.c (mode 0 / 1 / 2): rank r sleeps r * skew_us before
+ * every post; out[0]: mean microseconds per post + wait, out[1]: mean fresh contributors per round, out[2]: all-sane flag */
+int rt_bench_partial(int ranks, int64_t count, int iters, int mode, int skew_us, double* out);
 
 #ifdef __cplusplus
 }

@@ -115,6 +115,74 @@ static int run_schedule_cycles(int world) {
   return bad;
 }
 
+// Solo and majority allreduce as runtime schedules: ranks arrive with random skew, an observer on the schedule's end
+// records every round, schedules are created and deleted in cycles with one tag.  Checked: every rank ran every round,
+// the rounds agree across ranks, and with accumulation on and a synchronous last round no post was lost.
+struct RoundLog { std::vector<int64_t> value, contributors, scratch; rt_rank* c; rt_sched s; int torn = 0; };
+static void observe_round(rt_op, void* arg) {
+  RoundLog* log = (RoundLog*)arg;
+  int64_t k = 0, rnd = 0;
+  if (rt_partial_read(log->c, log->s, log->scratch.data(), &k, &rnd) != RT_SUCCESS) return;
+  if (log->scratch.front() != log->scratch.back()) log->torn = 1;
+  log->value.push_back(log->scratch[0]);
+  log->contributors.push_back(k);
+}
+
+static int run_partial(int world, int cycles, int steps, int64_t count) {
+  rt_world* w = rt_world_create(world);
+  std::vector<int> bad(world, 0);
+  std::vector<std::vector<RoundLog>> logs(world, std::vector<RoundLog>(cycles));
+  std::vector<std::thread> th;
+  const int limiter = 3;                              // steps is a multiple of 4: the last round is synchronous
+  for (int r = 0; r < world; ++r) {
+    th.emplace_back([&, r] {
+      rt_rank* c = rt_world_rank(w, r);
+      uint64_t rng = 0x243f6a8885a308d3ULL * (uint64_t)(r + 1);
+      for (int cy = 0; cy < cycles && !bad[r]; ++cy) {
+        std::vector<int64_t> snd(count, r + 1), rcv(count, 0);
+        rt_buf bs = rt_buffer_create(c, snd.data(), count, RT_INT64), br = rt_buffer_create(c, rcv.data(), count, RT_INT64);
+        rt_sched s = (cy & 1) ? rt_rand_allreduce(c, bs, br, 11, RT_SUM, cy, limiter, RT_PARTIAL_ACCUMULATE)
+                              : rt_solo_allreduce(c, bs, br, 11, RT_SUM, limiter, RT_PARTIAL_ACCUMULATE);
+        RoundLog& log = logs[r][cy];
+        log.c = c; log.s = s; log.scratch.assign(count, 0);
+        rt_op obs = rt_op_callback(c, observe_round, &log, RT_DEP_OR);
+        rt_op_hb(c, rt_schedule_end_op(c, s), obs);
+        rt_schedule_start(c, s);
+        for (int it = 0; it < steps; ++it) {
+          rng = rng * 6364136223846793005ULL + 1442695040888963407ULL;
+          if (((rng >> 33) & 3) == 0) std::this_thread::sleep_for(std::chrono::microseconds((rng >> 40) & 255));
+          if (rt_schedule_post(c, s) != RT_SUCCESS || rt_schedule_wait(c, s, 30.0) != RT_SUCCESS) { bad[r] = 1; break; }
+        }
+        for (int spin = 0; spin < 200000 && rt_op_completions(c, obs) < steps; ++spin) std::this_thread::yield();
+        if (rt_op_completions(c, obs) != steps || log.torn) bad[r] = 1;
+        int64_t info[9];
+        if (rt_partial_info(c, s, info) != RT_SUCCESS || info[1] != steps || info[7] != 0 || info[8] != 0) bad[r] = 1;
+        rt_schedule_delete(c, s);
+        rt_op_free(c, obs);
+        rt_buffer_delete(c, bs);
+        rt_buffer_delete(c, br);
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  rt_world_destroy(w);
+  int any = 0;
+  for (int r = 0; r < world; ++r) any |= bad[r];
+  for (int cy = 0; cy < cycles && !any; ++cy) {
+    int64_t total = 0;
+    for (int it = 0; it < steps; ++it) {
+      for (int r = 1; r < world; ++r)
+        if (logs[r][cy].value[it] != logs[0][cy].value[it] || logs[r][cy].contributors[it] != logs[0][cy].contributors[it]) any = 1;
+      total += logs[0][cy].value[it];
+    }
+    if (logs[0][cy].contributors[steps - 1] != world) any = 1;
+    if (total != (int64_t)steps * world * (world + 1) / 2) any = 1;
+  }
+  printf("runtime partial allreduce: %d ranks x %d cycles x %d posts of %ld elements %s\n", world, cycles, steps, (long)count,
+         any ? "FAILED" : "ok");
+  return any;
+}
+
 int main(int argc, char** argv) {
   const int world = argc > 1 ? atoi(argv[1]) : 4;
   const int steps = argc > 2 ? atoi(argv[2]) : 200;
@@ -123,6 +191,8 @@ int main(int argc, char** argv) {
   for (int mode = 0; mode < 2; ++mode) bad |= run_channel(mode, world, steps, 1024, 3);   // folding unconsumed gradients
   bad |= run_runtime(world, steps / 4 + 1);
   bad |= run_schedule_cycles(world);
+  bad |= run_partial(world, 6, 16, 8);
+  bad |= run_partial(world, 2, 8, 8192);               // bodies large enough to be copied straight into a listening receive
   // vectors long enough for a rank's helper threads (from 256 K elements each), with a ragged length
   bad |= run_channel(2, 2, 3, (1u << 20) + 1234, 0);
   bad |= run_channel(0, 2, 3, (1u << 20) + 1234, 1);

@@ -9,7 +9,7 @@ PyTorch or a GPU, which is the point: it is the independent check for the native
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 

@@ -78,6 +78,23 @@ def run_native(ranks: int, count: int, iters: int) -> dict:
     return out
 
 
+def run_sgd_loops(ranks: int, count: int, iters: int, skew_us: int = 1000) -> dict:
+    """The reference's skewed SGD-loop programs (fflib2 evaluation/ssgd.c, rsgd.c, randomsgd.c) on this runtime's
+    synchronous, solo and majority allreduce schedules: microseconds per post + wait, averaged over ranks, with
+    rank r arriving r * skew_us late in every iteration; and how many ranks put something fresh into a round."""
+    import ctypes as C
+    lib = R.lib()
+    lib.rt_bench_partial.argtypes = [C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
+    out = {"ranks": ranks, "floats": count, "iters": iters, "skew": "rank * %d us per iteration" % skew_us}
+    for mode, name in enumerate(("ssgd", "rsgd", "randomsgd")):
+        v = (C.c_double * 3)()
+        if lib.rt_bench_partial(ranks, count, iters, mode, skew_us, v) != 0:
+            raise RuntimeError("native benchmark failed")
+        out[name + "_us"], out[name + "_contributors"] = v[0], v[1]
+        out["sane"] = out.get("sane", True) and v[2] == 1.0
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--ranks", type=int, default=4)
@@ -85,7 +102,13 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--python-threads", action="store_true",
                     help="drive the ranks from Python threads (measures the binding and the interpreter as well)")
+    ap.add_argument("--sgd-loops", action="store_true",
+                    help="the skewed SGD loops of the reference (synchronous / solo / majority allreduce schedules)")
+    ap.add_argument("--skew-us", type=int, default=1000)
     args = ap.parse_args(argv)
+    if args.sgd_loops:
+        print(json.dumps(run_sgd_loops(args.ranks, args.count, args.iters, args.skew_us)))
+        return 0
     res = run(args.ranks, args.count, args.iters) if args.python_threads else \
         dict(ranks=args.ranks, count=args.count, dtype="int32", iters=args.iters, native=run_native(args.ranks, args.count, args.iters))
     print(json.dumps(res))

@@ -23,6 +23,7 @@ OPERATOR = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_
 SCHED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64)
 SCHED_WAIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_double)
 DEP_IGNORE_VERSION, DEP_NO_AUTOPOST, DEP_CONSTRAINED, DEP_SKIP_OLD_VERSIONS = 0x10, 0x20, 0x40, 0x80
+PARTIAL_STALE, PARTIAL_ACCUMULATE = 0x800, 0x1000
 NONE = -1
 
 _lib = None
@@ -85,6 +86,13 @@ def lib():
         l.rt_activation.restype = i64
         l.rt_activation.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64)]
         l.rt_limiter.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]
+        l.rt_solo_allreduce.restype = i64
+        l.rt_solo_allreduce.argtypes = [vp, i64, i64, i32, i32, i32, i32]
+        l.rt_rand_allreduce.restype = i64
+        l.rt_rand_allreduce.argtypes = [vp, i64, i64, i32, i32, i32, i32, i32]
+        l.rt_partial_info.argtypes = [vp, i64, C.POINTER(i64)]
+        l.rt_partial_read.argtypes = [vp, i64, vp, C.POINTER(i64), C.POINTER(i64)]
+        l.rt_partial_activator.argtypes = [vp, i64, i64]
         _lib = l
     return _lib
 
@@ -211,6 +219,33 @@ class Rank:
         arr = (C.c_int64 * num_async)()
         lib().rt_limiter(self.h, num_async, C.byref(st), arr, C.byref(sy))
         return st.value, list(arr), sy.value
+
+    # partial allreduces as schedules (ffsolo_allreduce / ffrand_allreduce, fflib2 src/ff.h:161-165)
+    def solo_allreduce(self, snd: int, rcv: int, tag: int, op=SUM, limiter: int = -1, options: int = 0) -> int:
+        """The first rank to post round j activates it on every rank; ``limiter`` >= 0 makes every (limiter+1)-th
+        round synchronous.  Drive the returned schedule with ``schedule_start / _post / _wait / _test / _delete``."""
+        return lib().rt_solo_allreduce(self.h, snd, rcv, tag, op, limiter, options)
+
+    def rand_allreduce(self, snd: int, rcv: int, tag: int, op=SUM, seed: int = 0, limiter: int = -1, options: int = 0) -> int:
+        """Majority allreduce: the rank drawn for round j (the same draw on every rank) activates it."""
+        return lib().rt_rand_allreduce(self.h, snd, rcv, tag, op, seed, limiter, options)
+
+    def partial_info(self, s: int) -> dict:
+        out = (C.c_int64 * 9)()
+        if lib().rt_partial_info(self.h, s, out) != SUCCESS:
+            raise ValueError("not a live partial allreduce")
+        keys = ("posts", "rounds", "activated", "late", "sync_rounds", "contributors", "round", "overwritten", "pending")
+        return dict(zip(keys, list(out)))
+
+    def partial_read(self, s: int, out: np.ndarray) -> Tuple[int, int]:
+        """Copy the newest result into ``out`` together with (fresh contributors, round number), without tearing."""
+        k, r = C.c_int64(), C.c_int64()
+        if lib().rt_partial_read(self.h, s, out.ctypes.data_as(C.c_void_p), C.byref(k), C.byref(r)) != SUCCESS:
+            raise ValueError("not a live partial allreduce")
+        return k.value, r.value
+
+    def partial_activator(self, s: int, round_: int) -> int:
+        return lib().rt_partial_activator(self.h, s, round_)
 
 
 class World:

@@ -1,0 +1,316 @@
+"""Solo and majority allreduce as schedules of the host runtime (fflib2 src/colls/ffsolo_allreduce.c,
+ffrand_allreduce.c; driven like evaluation/rsgd.c and randomsgd.c: start once, then post / wait per step).
+
+Ranks are threads.  A rank contributes ``rank + 1`` in every element, so a round's value names its contributors:
+it is the sum of ``r + 1`` over the ranks that put something fresh in, and the runtime's own count of fresh
+contributors has to agree with it."""
+import itertools
+import threading
+import time
+
+import numpy as np
+import pytest
+
+from eagersgd_b200.parallel import oprt as R
+
+
+def _run(world, fn):
+    errs = []
+
+    def wrap(rank):
+        try:
+            fn(rank)
+        except Exception:  # noqa
+            import traceback
+            errs.append(traceback.format_exc())
+    th = [threading.Thread(target=wrap, args=(world.ranks[r],)) for r in range(world.n)]
+    [t.start() for t in th]
+    [t.join() for t in th]
+    assert not errs, errs[0]
+
+
+def _subset_sums(world):
+    """value -> set of possible contributor counts, for contributions r + 1."""
+    out = {}
+    for k in range(world + 1):
+        for sub in itertools.combinations(range(world), k):
+            out.setdefault(sum(r + 1 for r in sub), set()).add(k)
+    return out
+
+
+def _observe(r, s, rcv, log):
+    """Record (round, value, contributors) at every round end, on the progress thread, before the next round."""
+    def seen(op):
+        k, rnd = r.partial_read(s, rcv_copy)
+        assert np.all(rcv_copy == rcv_copy[0]), rcv_copy           # one round, not a mix of two
+        log.append((rnd, int(rcv_copy[0]), k))
+    rcv_copy = np.zeros_like(rcv)
+    cb = r.callback(seen, R.DEP_OR)
+    r.hb(r.schedule_end(s), cb)
+
+    def settled(rounds):                                            # the observer runs after the wait has returned
+        t0 = time.time()
+        while r.completions(cb) < rounds and time.time() - t0 < 20:
+            time.sleep(0.001)
+        assert r.completions(cb) == rounds
+    return settled
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 5])
+def test_solo_rounds_agree_on_every_rank_and_lose_nothing(world):
+    """Every rank sees the same value and contributor count for every round; with accumulation on and a synchronous
+    last round, the rounds together contain every post exactly once."""
+    steps, limiter, n = 24, 5, 17                                   # rounds 5, 11, 17, 23 are synchronous
+    logs = [[] for _ in range(world)]
+    infos = [None] * world
+    rng = np.random.RandomState(world)
+    naps = rng.uniform(0, 0.002, size=(world, steps))
+    with R.World(world) as w:
+        def body(r):
+            snd, rcv = np.full(n, r.id + 1, dtype=np.int64), np.zeros(n, dtype=np.int64)
+            s = r.solo_allreduce(r.buffer(snd), r.buffer(rcv), tag=3, limiter=limiter, options=R.PARTIAL_ACCUMULATE)
+            assert s >= 0
+            settled = _observe(r, s, rcv, logs[r.id])
+            assert r.schedule_post(s) == R.ERROR                    # not started yet
+            assert r.schedule_start(s) == R.SUCCESS
+            for k in range(steps):
+                time.sleep(naps[r.id, k])
+                assert r.schedule_post(s) == R.SUCCESS
+                snd[:] = -1000                                      # the contribution was taken inside post
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                snd[:] = r.id + 1
+            settled(steps)
+            w_barrier.wait()
+            infos[r.id] = r.partial_info(s)
+            assert r.schedule_delete(s) == R.SUCCESS
+            with pytest.raises(ValueError):
+                r.partial_info(s)
+        w_barrier = threading.Barrier(world)
+        _run(w, body)
+    for log in logs:
+        assert [e[0] for e in log] == list(range(steps))            # every rank ran every round, in order
+    for rnd in range(steps):
+        vals = {(log[rnd][1], log[rnd][2]) for log in logs}
+        assert len(vals) == 1, (rnd, vals)
+        value, k = vals.pop()
+        assert 1 <= k <= world and value >= k                       # somebody activated it; accumulated posts may add up
+        if rnd % (limiter + 1) == limiter:
+            assert k == world                                       # a synchronous round has everybody
+    assert sum(e[1] for e in logs[0]) == steps * sum(range(1, world + 1))
+    for i in infos:
+        assert i["posts"] == steps and i["rounds"] == steps and i["sync_rounds"] == 4 and i["pending"] == 0
+        assert i["overwritten"] == 0
+    assert sum(i["activated"] for i in infos) >= steps - 4          # each eager round had at least one activator
+
+
+def test_solo_does_not_wait_for_a_slow_rank_and_the_limiter_does():
+    world, steps, nap = 4, 12, 0.03
+    waits = [0.0] * world
+    infos = [None] * world
+    logs = [[] for _ in range(world)]
+    with R.World(world) as w:
+        done = threading.Barrier(world)
+
+        def body(r):
+            snd, rcv = np.full(8, float(1 << r.id), dtype=np.float32), np.zeros(8, dtype=np.float32)   # a bit per rank
+            s = r.solo_allreduce(r.buffer(snd), r.buffer(rcv), tag=1, limiter=-1)
+            settled = _observe(r, s, rcv, logs[r.id])
+            r.schedule_start(s)
+            for k in range(steps):
+                if r.id == 3:
+                    time.sleep(nap)
+                r.schedule_post(s)
+                t0 = time.perf_counter()
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                waits[r.id] += time.perf_counter() - t0
+            settled(steps)
+            done.wait()
+            infos[r.id] = r.partial_info(s)
+            r.schedule_delete(s)
+        t0 = time.perf_counter()
+        _run(w, body)
+    assert max(waits[:3]) < 0.5 * steps * nap, waits               # the on-time ranks never sat out a nap
+    for rnd in range(steps):
+        assert len({(log[rnd][1], log[rnd][2]) for log in logs}) == 1
+        assert bin(logs[0][rnd][1]).count("1") == logs[0][rnd][2] >= 1, logs[0][rnd]   # the value names its contributors
+    assert infos[3]["late"] >= steps - 2 and infos[3]["activated"] <= 2   # the slow rank found its rounds begun
+    assert sum(1 for e in logs[0] if e[1] & 7) == steps             # every round had one of the on-time ranks
+    for q in range(world):                                          # a post is taken by a round, replaced, or left over
+        taken = sum(1 for e in logs[0] if e[1] & (1 << q))
+        assert taken + infos[q]["overwritten"] + infos[q]["pending"] == steps, (q, taken, infos[q])
+    assert sum(1 for e in logs[0] if e[1] & 8) <= steps // 2        # the slow rank is in few rounds, if any
+    # the same loop with a limiter of 0 is a synchronous allreduce: everybody waits for the slow rank
+    waits2 = [0.0] * world
+    with R.World(world) as w:
+        def body2(r):
+            x, y = np.full(8, float(r.id + 1), dtype=np.float32), np.zeros(8, dtype=np.float32)
+            s = r.solo_allreduce(r.buffer(x), r.buffer(y), tag=1, limiter=0)
+            r.schedule_start(s)
+            for k in range(4):
+                if r.id == 3:
+                    time.sleep(nap)
+                r.schedule_post(s)
+                t0 = time.perf_counter()
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                waits2[r.id] += time.perf_counter() - t0
+                assert np.all(y == 10.0)                            # 1 + 2 + 3 + 4: nobody is missing
+            r.schedule_delete(s)
+        _run(w, body2)
+    assert min(waits2[:3]) > 0.5 * 4 * nap, waits2
+
+
+def test_majority_waits_for_the_drawn_rank_only():
+    world, steps, seed = 4, 16, 77
+    logs = [[] for _ in range(world)]
+    infos = [None] * world
+    draws = [None] * world
+    with R.World(world) as w:
+        done = threading.Barrier(world)
+
+        def body(r):
+            snd, rcv = np.full(4, r.id + 1, dtype=np.int32), np.zeros(4, dtype=np.int32)
+            s = r.rand_allreduce(r.buffer(snd), r.buffer(rcv), tag=2, seed=seed, limiter=7)
+            draws[r.id] = [r.partial_activator(s, k) for k in range(steps)]
+            settled = _observe(r, s, rcv, logs[r.id])
+            r.schedule_start(s)
+            for k in range(steps):
+                time.sleep(0.001 * r.id)
+                r.schedule_post(s)
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+            settled(steps)
+            done.wait()
+            infos[r.id] = r.partial_info(s)
+            r.schedule_delete(s)
+        _run(w, body)
+    assert draws[0] == draws[1] == draws[2] == draws[3]             # one draw, known to everybody
+    assert draws[0][7] == -1 and draws[0][15] == -1 and len(set(draws[0]) - {-1}) > 1
+    for rank, i in enumerate(infos):
+        assert i["activated"] <= sum(1 for d in draws[0] if d == rank)
+        assert i["rounds"] == steps and i["sync_rounds"] == 2
+    for rnd in range(steps):
+        assert len({(log[rnd][1], log[rnd][2]) for log in logs}) == 1
+        if draws[0][rnd] >= 0:                                      # the drawn rank's own contribution is in its round
+            value, k = logs[0][rnd][1], logs[0][rnd][2]
+            assert any(draws[0][rnd] in sub and sum(q + 1 for q in sub) == value
+                       for sub in itertools.combinations(range(world), k)), (rnd, value, k)
+
+
+def test_neutral_element_stale_option_and_other_operators():
+    """A rank with nothing new contributes the operator's neutral element (maximum: the lowest value), or with
+    PARTIAL_STALE its previous contribution once more."""
+    out = {}
+    with R.World(2) as w:
+        gate = threading.Barrier(2)
+
+        def body(r):
+            snd = np.full(3, 10.0 * (r.id + 1))
+            scheds = {"max": r.solo_allreduce(r.buffer(snd), r.buffer(np.zeros(3)), tag=4, op=R.MAX),
+                      "stale": r.solo_allreduce(r.buffer(snd), r.buffer(np.zeros(3)), tag=5, options=R.PARTIAL_STALE)}
+            res = np.zeros(3)
+
+            def alone(key, rnd):                                    # rank 0 activates a round; rank 1's user is elsewhere
+                if r.id == 0:
+                    r.schedule_post(scheds[key])
+                    assert r.schedule_wait(scheds[key], 20.0) == R.SUCCESS
+                    k, got = r.partial_read(scheds[key], res)
+                    assert got == rnd
+                    out[key, rnd] = (res[0], k)
+
+            def catch_up(key, n):                                   # rank 1 posts rounds that are over already
+                if r.id == 1:
+                    for _ in range(n):
+                        r.schedule_post(scheds[key])
+                        assert r.schedule_wait(scheds[key], 1.0) == R.SUCCESS
+
+            for q in scheds.values():
+                r.schedule_start(q)
+            gate.wait()
+            for key in scheds:
+                alone(key, 0)                                       # rank 1 has posted nothing yet
+            gate.wait()
+            for key in scheds:
+                catch_up(key, 1)                                    # its contribution of 20 now waits for a round
+            gate.wait()
+            for key in scheds:
+                alone(key, 1)                                       # takes the 20
+                alone(key, 2)                                       # nothing new from rank 1
+            gate.wait()
+            for key in scheds:
+                catch_up(key, 2)
+            gate.wait()
+            for key, q in scheds.items():
+                i = r.partial_info(q)
+                assert i["rounds"] == 3 and i["posts"] == 3
+                if r.id == 1:
+                    assert i["late"] == 3 and i["activated"] == 0 and i["overwritten"] == 1 and i["pending"] == 1
+                else:
+                    assert i["late"] == 0 and i["activated"] == 3
+                r.schedule_delete(q)
+        _run(w, body)
+    assert out["max", 0] == (10.0, 1) and out["stale", 0] == (10.0, 1)
+    assert out["max", 1] == (20.0, 2) and out["stale", 1] == (30.0, 2)
+    assert out["max", 2] == (10.0, 1)                                # the lowest value stood in for rank 1, not 0 or 20
+    assert out["stale", 2] == (30.0, 1)                              # its 20 counted again, though only one was fresh
+
+
+def test_create_delete_cycles_reuse_the_tag_and_a_missing_rank_times_out():
+    with R.World(3) as w:
+        def body(r):
+            for cycle in range(40):
+                x, y, res = np.full(2, r.id + 1, dtype=np.int32), np.zeros(2, dtype=np.int32), np.zeros(2, dtype=np.int32)
+                bx, by = r.buffer(x), r.buffer(y)
+                s = r.solo_allreduce(bx, by, tag=9, limiter=1)
+                r.schedule_start(s)
+                for k in range(4):
+                    r.schedule_post(s)
+                    assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                    if k % 2 == 1:                                  # a synchronous round; a peer may have begun the next
+                        contributors, rnd = r.partial_read(s, res)  # one already, so ask which round the buffer holds
+                        if rnd == k:
+                            assert np.all(res == 6) and contributors == 3
+                assert np.all(y == 6)                               # nothing follows the last round
+                assert r.schedule_delete(s) == R.SUCCESS
+                m = r.rand_allreduce(bx, by, tag=9, seed=cycle, limiter=3)    # the same tag again, another collective
+                r.schedule_start(m)
+                for k in range(4):
+                    r.schedule_post(m)
+                    assert r.schedule_wait(m, 20.0) == R.SUCCESS
+                assert np.all(y == 6) and r.partial_info(m)["rounds"] == 4
+                assert r.schedule_delete(m) == R.SUCCESS
+                r.buffer_delete(bx)
+                r.buffer_delete(by)
+        _run(w, body)
+    with R.World(2) as w:
+        def body(r):
+            x, y = np.ones(2, dtype=np.int32), np.zeros(2, dtype=np.int32)
+            s = r.solo_allreduce(r.buffer(x), r.buffer(y), tag=1, limiter=0)
+            r.schedule_start(s)
+            if r.id == 0:                                           # rank 1 never posts the synchronous round
+                r.schedule_post(s)
+                t0 = time.perf_counter()
+                assert r.schedule_wait(s, 0.3) == R.TIMEOUT
+                assert time.perf_counter() - t0 < 5.0
+                assert r.schedule_test(s) == R.SUCCESS              # still not complete, and nothing hangs
+        _run(w, body)
+
+
+def test_print_shows_the_parts():
+    with R.World(2) as w:
+        def body(r):
+            x, y = np.ones(2, dtype=np.float32), np.zeros(2, dtype=np.float32)
+            s = r.solo_allreduce(r.buffer(x), r.buffer(y), tag=1)
+            dot = r.schedule_dot(s)
+            assert dot.count("digraph") == 3 and dot.count("callback") >= 4 and "send" in dot and "recv" in dot
+            r.schedule_delete(s)
+        _run(w, body)
+
+
+def test_sgd_loop_benchmark_shows_the_three_behaviours():
+    """The reference's ssgd / rsgd / randomsgd loops on this runtime: with rank r arriving r ms late, the synchronous
+    allreduce costs the ranks about the mean lateness, the solo allreduce next to nothing, the majority one lies between."""
+    from eagersgd_b200.parallel.bench_oprt import run_sgd_loops
+    r = run_sgd_loops(ranks=4, count=512, iters=42, skew_us=1000)
+    assert r["sane"]
+    assert r["ssgd_contributors"] == 4.0 and r["rsgd_contributors"] >= 1.0
+    assert r["rsgd_us"] < 0.5 * r["ssgd_us"], r
+    assert r["rsgd_us"] < r["randomsgd_us"] < 1.25 * r["ssgd_us"], r

@@ -26,3 +26,5 @@ def test_stress_driver_is_clean(tmp_path, flags, needle):
     assert needle not in out, out[-3000:]
     assert out.count("on every rank") == 7 and "runtime allreduce: 4 ranks" in out
     assert "runtime schedule cycles: 4 ranks ok" in out
+    assert "runtime partial allreduce: 4 ranks x 6 cycles x 16 posts of 8 elements ok" in out
+    assert "runtime partial allreduce: 4 ranks x 2 cycles x 8 posts of 8192 elements ok" in out
