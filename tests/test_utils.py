@@ -210,3 +210,27 @@ def test_c_sample_of_the_partial_allreduce(tmp_path, mode):
                    ["-o", exe], check=True, capture_output=True, text=True)
     r = subprocess.run([exe, "3", "2048", "6", str(mode)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "PASSED" in r.stdout and "replicas agree" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_c_sample_of_the_runtime_partial_allreduce(tmp_path, mode):
+    """samples/c/rt_partial_allreduce.c — the reference's rsgd.c / randomsgd.c loop on the operation runtime's solo and
+    majority allreduce schedules, from plain C — builds with the pkg-config flags and passes its own conservation check."""
+    import os
+    import shutil
+    import subprocess
+    from eagersgd_b200 import _build
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    _build.build_host()
+    text = open(_build.write_pkgconfig()).read()
+    var = dict(l.split("=", 1) for l in text.splitlines() if "=" in l and ":" not in l.split("=")[0])
+    expand = lambda s: s.replace("${libdir}", var["libdir"]).replace("${includedir}", var["includedir"])
+    cflags = expand([l for l in text.splitlines() if l.startswith("Cflags:")][0].split(":", 1)[1]).split()
+    libs = expand([l for l in text.splitlines() if l.startswith("Libs:")][0].split(":", 1)[1]).split()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "rt_partial_allreduce")
+    subprocess.run(["gcc", "-O2", "-Wall", "-Werror", os.path.join(root, "samples", "c", "rt_partial_allreduce.c")] + cflags +
+                   libs + ["-lpthread", "-o", exe], check=True, capture_output=True, text=True)
+    r = subprocess.run([exe, "4", "4096", "12", str(mode), "5"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "PASSED" in r.stdout and "2 synchronous" in r.stdout, r.stdout + r.stderr
