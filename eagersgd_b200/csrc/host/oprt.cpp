@@ -172,7 +172,8 @@ void run_comp(rt_rank* c, Op& op) {
   if (B.count < n) n = B.count;
   if (O.count < n) n = O.count;
   if (op.oper >= RT_CUSTOM0) {
-    c->custom_ops[op.oper - RT_CUSTOM0](A.data(), B.data(), O.data(), n, A.dtype);
+    rt_operator_fn fn = c->custom_ops[op.oper - RT_CUSTOM0];
+    if (fn) fn(A.data(), B.data(), O.data(), n, A.dtype);
     return;
   }
   switch (A.dtype) {
@@ -590,8 +591,41 @@ rt_op rt_op_recv(rt_rank* c, rt_buf b, int peer, int tag, int options) {
 
 int rt_operator_create(rt_rank* c, rt_operator_fn fn) {
   std::lock_guard<std::mutex> g(c->mu);
+  for (size_t i = 0; i < c->custom_ops.size(); ++i)      // a deleted operator's number is given out again
+    if (!c->custom_ops[i]) { c->custom_ops[i] = fn; return RT_CUSTOM0 + (int)i; }
   c->custom_ops.push_back(fn);
   return RT_CUSTOM0 + (int)c->custom_ops.size() - 1;
+}
+
+// ffcomp_operator_delete: compute operations that still name the operator must not run afterwards.
+int rt_operator_delete(rt_rank* c, int oper) {
+  std::lock_guard<std::mutex> g(c->mu);
+  const int i = oper - RT_CUSTOM0;
+  if (i < 0 || i >= (int)c->custom_ops.size() || !c->custom_ops[i]) return RT_ERROR;
+  c->custom_ops[i] = nullptr;
+  return RT_SUCCESS;
+}
+
+// One line on an operation: what it is, whom it talks to, how often it was posted / started / completed, how many
+// dependents it has (ffop_tostring).
+int rt_op_tostring(rt_rank* c, rt_op id, char* out, int64_t cap) {
+  static const char* names[] = {"nop", "callback", "comp", "send", "recv"};
+  std::lock_guard<std::mutex> g(c->mu);
+  if (id < 0 || id >= (rt_op)c->ops.size() || !c->ops[id] || cap < 1) return RT_ERROR;
+  const Op& op = *c->ops[id];
+  std::string t = std::string("[") + std::to_string(id) + "." + std::to_string(c->id) + "] " + names[op.type];
+  if (op.type == T_SEND || op.type == T_RECV)
+    t += std::string(op.type == T_SEND ? " to " : " from ") + std::to_string(op.peer) + " tag " + std::to_string(op.tag) +
+         ((op.options & RT_SHADOW_TAG) ? " (shadow)" : "");
+  if (op.type == T_COMP) t += " operator " + std::to_string(op.oper);
+  t += std::string(" deps ") + ((op.options & RT_DEP_OR) ? "or" : (op.options & RT_DEP_FIRST) ? "first" : "and");
+  if (op.options & RT_NON_PERSISTENT) t += " once";
+  t += " posted " + std::to_string(op.posted) + " started " + std::to_string(op.executed) + " completed " +
+       std::to_string(op.completed.load()) + " parents " + std::to_string(op.num_parents) + " dependents " +
+       std::to_string(op.edges.size()) + (op.in_flight ? " listening" : "");
+  if ((int64_t)t.size() + 1 > cap) return RT_ERROR;
+  memcpy(out, t.c_str(), t.size() + 1);
+  return (int)t.size();
 }
 
 int rt_op_hb_fallback(rt_rank* c, rt_op first, rt_op second, rt_op fallback, int options, rt_dep* dep) {
@@ -778,6 +812,28 @@ int rt_schedule_default_post(rt_rank* c, rt_sched s) {
 }
 int rt_schedule_default_wait(rt_rank* c, rt_sched s, double timeout_s) { return rt_op_wait(c, rt_schedule_end_op(c, s), timeout_s); }
 int rt_schedule_default_test(rt_rank* c, rt_sched s) { return rt_op_test(c, rt_schedule_end_op(c, s)); }
+
+// ffschedule_default_delete / ffschedule_default_print: what an override calls for the schedule's own part.
+int rt_schedule_default_delete(rt_rank* c, rt_sched s) {
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (s < 0 || s >= (rt_sched)c->scheds.size() || !c->scheds[s].alive) return RT_ERROR;
+    c->scheds[s].delete_fn = nullptr;
+  }
+  return rt_schedule_delete(c, s);
+}
+int rt_schedule_default_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
+  rt_sched_print_fn custom = nullptr;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (s < 0 || s >= (rt_sched)c->scheds.size() || !c->scheds[s].alive) return RT_ERROR;
+    custom = c->scheds[s].print_fn;
+    c->scheds[s].print_fn = nullptr;
+  }
+  const int n = rt_schedule_print(c, s, out, cap);
+  { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].print_fn = custom; }
+  return n;
+}
 
 // Arm a schedule once before its first post (a composite schedule posts its listening side here:
 // ffsolo_allreduce.c:97-101).  The default does nothing.
@@ -1198,7 +1254,7 @@ int partial_delete(rt_rank* c, rt_sched s) {
     std::lock_guard<std::mutex> g(c->world->mail_mu);
     for (int r = 0; r < c->world->n; ++r) c->world->mail.erase(std::make_tuple(r, c->id, wire_tag(st->token_tag, RT_SHADOW_TAG)));
   }
-  const int rc = rt_schedule_delete(c, s);               // the default: operations, parts, owned buffers
+  const int rc = rt_schedule_default_delete(c, s);       // operations, parts, owned buffers
   for (int spins = 0; spins < 2000000; ++spins) {        // a callback of this schedule may still be returning
     {
       std::lock_guard<std::mutex> g(c->mu);
@@ -1223,10 +1279,7 @@ int partial_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
     if (n < 0) return RT_ERROR;
     used += n;
   }
-  rt_sched_print_fn self = nullptr;
-  { std::lock_guard<std::mutex> g(c->mu); self = c->scheds[s].print_fn; c->scheds[s].print_fn = nullptr; }
-  const int n = rt_schedule_print(c, s, out + used, cap - used);
-  { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].print_fn = self; }
+  const int n = rt_schedule_default_print(c, s, out + used, cap - used);
   return n < 0 ? RT_ERROR : (int)(used + n);
 }
 

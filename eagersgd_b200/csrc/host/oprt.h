@@ -92,6 +92,8 @@ rt_op rt_op_comp(rt_rank* c, rt_buf a, rt_buf b, rt_buf out, int op, int options
 rt_op rt_op_send(rt_rank* c, rt_buf b, int peer, int tag, int options);
 rt_op rt_op_recv(rt_rank* c, rt_buf b, int peer, int tag, int options);
 int rt_operator_create(rt_rank* c, rt_operator_fn fn);   /* returns an operator id >= RT_CUSTOM0 */
+int rt_operator_delete(rt_rank* c, int op);              /* the id may be given out again */
+int rt_op_tostring(rt_rank* c, rt_op op, char* out, int64_t cap);   /* one line on an operation; returns its length */
 int rt_op_hb(rt_rank* c, rt_op first, rt_op second);     /* first happens before second */
 /* Versioned edge: the n-th completion of `first` satisfies the n-th run of `second` only.  A completion that
  * finds `second` already past that version goes to `fallback` (RT_NONE: it is dropped); one that is ahead of
@@ -129,6 +131,8 @@ int rt_schedule_set_print_fun(rt_rank* c, rt_sched s, rt_sched_print_fn f);
 int rt_schedule_default_post(rt_rank* c, rt_sched s);
 int rt_schedule_default_wait(rt_rank* c, rt_sched s, double timeout_s);
 int rt_schedule_default_test(rt_rank* c, rt_sched s);
+int rt_schedule_default_delete(rt_rank* c, rt_sched s);
+int rt_schedule_default_print(rt_rank* c, rt_sched s, char* out, int64_t cap);
 int rt_schedule_set_state(rt_rank* c, rt_sched s, void* state);
 void* rt_schedule_get_state(rt_rank* c, rt_sched s);
 int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap);   /* graphviz DOT */

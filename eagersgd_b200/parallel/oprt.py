@@ -86,6 +86,10 @@ def lib():
         l.rt_activation.restype = i64
         l.rt_activation.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64)]
         l.rt_limiter.argtypes = [vp, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]
+        l.rt_op_tostring.argtypes = [vp, i64, C.c_char_p, i64]
+        l.rt_operator_delete.argtypes = [vp, i32]
+        l.rt_schedule_default_delete.argtypes = [vp, i64]
+        l.rt_schedule_default_print.argtypes = [vp, i64, C.c_char_p, i64]
         l.rt_solo_allreduce.restype = i64
         l.rt_solo_allreduce.argtypes = [vp, i64, i64, i32, i32, i32, i32]
         l.rt_rand_allreduce.restype = i64
@@ -144,6 +148,13 @@ class Rank:
         cb = OPERATOR(tramp)
         self._keep.append(cb)
         return lib().rt_operator_create(self.h, cb)
+
+    def operator_delete(self, oper: int): return lib().rt_operator_delete(self.h, oper)
+
+    def describe(self, op: int) -> str:
+        """One line on an operation (``ffop_tostring``)."""
+        buf = C.create_string_buffer(512)
+        return buf.value.decode() if lib().rt_op_tostring(self.h, op, buf, len(buf)) >= 0 else ""
 
     def hb(self, first, second): return lib().rt_op_hb(self.h, first, second)
     def hb_fallback(self, first, second, fallback=NONE, options=0) -> int:

@@ -494,3 +494,52 @@ def test_random_dependency_graphs_compute_in_dependency_order(seed):
             assert r.schedule_wait(s, timeout=20.0) == R.SUCCESS
             for i in range(n_leaf, n_leaf + n_node):
                 assert np.array_equal(arrays[i], want[i]), (seed, rep, i, parents[i])
+
+
+def test_operation_description_operator_delete_and_default_schedule_functions():
+    """ffop_tostring, ffcomp_operator_delete, ffschedule_default_delete / _print (fflib2 src/ff.h:112-159)."""
+    with R.World(2) as w:
+        r = w.ranks[0]
+        x = np.arange(4, dtype=np.int32)
+        bx = r.buffer(x)
+        sd = r.send(bx, 1, 9, R.SHADOW_TAG)
+        rv = r.recv(bx, 1, 4, R.DEP_OR)
+        assert r.describe(sd).startswith("[%d.0] send to 1 tag 9 (shadow) deps and posted 0" % sd)
+        r.post(rv)
+        for _ in range(200):
+            if "listening" in r.describe(rv):
+                break
+            time.sleep(0.001)
+        assert "recv from 1 tag 4 deps or posted 1 started 1 completed 0" in r.describe(rv) and r.describe(rv).endswith("listening")
+        assert r.describe(10 ** 6) == ""
+        # a deleted operator's number is handed out again; a compute op that still names a deleted one does nothing
+        first = r.operator(lambda a, b, o: np.copyto(o, a - b))
+        second = r.operator(lambda a, b, o: np.copyto(o, a * b + 1))
+        assert second == first + 1
+        y, z = np.full(4, 10, dtype=np.int32), np.zeros(4, dtype=np.int32)
+        by, bz = r.buffer(y), r.buffer(z)
+        c1 = r.comp(by, bx, bz, first)
+        r.post(c1)
+        assert r.wait(c1) == R.SUCCESS and z.tolist() == [10, 9, 8, 7]
+        assert "comp operator %d" % first in r.describe(c1) and "completed 1" in r.describe(c1)
+        assert r.operator_delete(first) == R.SUCCESS and r.operator_delete(first) == R.ERROR
+        z[:] = -1
+        r.post(c1)
+        assert r.wait(c1) == R.SUCCESS and z.tolist() == [-1] * 4
+        assert r.operator(lambda a, b, o: np.copyto(o, a + b)) == first
+        r.post(c1)
+        assert r.wait(c1) == R.SUCCESS and z.tolist() == [10, 11, 12, 13]
+        # an overriding delete / print reaches the schedule's own part through the default functions
+        s = r.schedule()
+        r.schedule_add(s, r.nop())
+        calls = []
+
+        def my_delete(sched):
+            calls.append("delete")
+            return R.lib().rt_schedule_default_delete(r.h, sched)
+        r.schedule_override(s, delete=my_delete)
+        import ctypes as C
+        buf = C.create_string_buffer(4096)
+        assert R.lib().rt_schedule_default_print(r.h, s, buf, len(buf)) > 0 and b"digraph" in buf.value
+        assert r.schedule_delete(s) == R.SUCCESS and calls == ["delete"]
+        assert r.schedule_delete(s) == R.ERROR
