@@ -95,6 +95,56 @@ class MoreOperators:
 
     def visit_cast(self, op, g): self._out(op, self._in(op, 0).to(_ONNX_DTYPES[int(op.attrs["to"])]))
 
+    # ---- the experimental operators of early ONNX releases (the reference has classes for them) -----------------------
+    def visit_affine(self, op, g): self._out(op, op.attrs.get("alpha", 1.0) * self._in(op, 0) + op.attrs.get("beta", 0.0))
+
+    def visit_scale(self, op, g): self._out(op, self._in(op, 0) * op.attrs.get("scale", 1.0))
+
+    def visit_scaledtanh(self, op, g):
+        self._out(op, op.attrs.get("alpha", 1.0) * torch.tanh(op.attrs.get("beta", 1.0) * self._in(op, 0)))
+
+    def visit_parametricsoftplus(self, op, g):
+        a, b = op.attrs.get("alpha", 1.0), op.attrs.get("beta", 1.0)
+        self._out(op, a * torch.nn.functional.softplus(b * self._in(op, 0)))
+
+    def visit_imagescaler(self, op, g):
+        x = self._in(op, 0)
+        y = x * op.attrs.get("scale", 1.0)
+        bias = op.attrs.get("bias")
+        if bias is not None:
+            y = y + torch.as_tensor(np.asarray(bias, dtype=np.float32), device=x.device).to(x.dtype).view(1, -1, 1, 1)
+        self._out(op, y)
+
+    def visit_crop(self, op, g):
+        x = self._in(op, 0)
+        left, top, right, bottom = [int(v) for v in op.attrs["border"]]
+        scale = op.attrs.get("scale")
+        if scale is not None:                            # the size of the crop instead of its right / bottom border
+            h, w = int(scale[0]), int(scale[1])
+            self._out(op, x[..., top:top + h, left:left + w])
+        else:
+            self._out(op, x[..., top:x.shape[-2] - bottom, left:x.shape[-1] - right])
+
+    def _device(self):
+        return next(self.net.parameters()).device
+
+    def _fill_shape(self, op):
+        if int(op.attrs.get("input_as_shape", 0)):
+            shape = _ints(self._in(op, 0))
+        elif op.inputs and op.inputs[0] != "":
+            shape = list(self._in(op, 0).shape)
+        else:
+            shape = [int(v) for v in (op.attrs.get("shape") or [])]
+        return shape + [int(v) for v in (op.attrs.get("extra_shape") or [])]
+
+    def visit_constantfill(self, op, g):
+        dt = _ONNX_DTYPES[int(op.attrs.get("dtype", 1))]
+        self._out(op, torch.full(self._fill_shape(op), op.attrs.get("value", 0.0), dtype=dt, device=self._device()))
+
+    def visit_giventensorfill(self, op, g):
+        v = torch.as_tensor(np.asarray(op.attrs.get("values") or [], dtype=np.float32), device=self._device())
+        self._out(op, v.reshape(self._fill_shape(op)))
+
     # ---- reductions ---------------------------------------------------------------------------------------------------
     def _reduce(self, op, fn):
         x, axes = self._in(op, 0), self._axes(op)

@@ -158,10 +158,25 @@ SCHEMA["SequenceEmpty"] = ({"dtype": None}, 0, 0)
 # ---- this framework's additions (losses and gradient extensions of the reference's object model) ---------------------
 for _n in ("SoftmaxCrossEntropy", "CrossEntropy", "MeanSquaredError"):
     _op(_n, 2, 2)
+# ---- the experimental operators of the ONNX release the reference generated its classes from (deep500/utils/
+# onnx_interop/generated_operators.py has a class for each; later ONNX releases dropped them) -------------------------
+_op("Affine", 1, 1, alpha=1.0, beta=0.0)                        # alpha * x + beta
+_op("Scale", 1, 1, scale=1.0)
+_op("ScaledTanh", 1, 1, alpha=1.0, beta=1.0)                    # alpha * tanh(beta * x)
+_op("ParametricSoftplus", 1, 1, alpha=1.0, beta=1.0)            # alpha * log(exp(beta * x) + 1)
+_op("ImageScaler", 1, 1, bias=None, scale=1.0)                  # x * scale + bias[channel]
+_op("Crop", 1, 1, border=None, scale=None)                      # border = left, top, right, bottom; or scale = height, width
+_op("ConstantFill", 0, 1, dtype=1, extra_shape=None, input_as_shape=0, shape=None, value=0.0)
+_op("GivenTensorFill", 0, 1, extra_shape=None, input_as_shape=0, shape=None, values=None)
+_op("GRUUnit", 4, 4, drop_states=0)                             # hidden_prev, gates, seq_lengths, t
+_op("LoopIndexTensor", 2, 2, axis=0)
 _op("StopGradient", 1, 1)
 _op("AllReduceGradients", 1, 1)
 _op("ConsistentParameterServerGradients", 1, 1)
 _op("InconsistentParameterServerGradients", 1, 1)
+
+_op("ATen", 0, INF, operator=None)                              # a call into the exporting framework: any attributes
+ANY_ATTRIBUTES = {"ATen"}
 
 _CLASSES: Dict[str, type] = {}
 
@@ -169,10 +184,11 @@ _CLASSES: Dict[str, type] = {}
 def _make_class(op_type: str):
     from .ir import Operation
     attrs, lo, hi = SCHEMA[op_type]
+    open_ended = op_type in ANY_ATTRIBUTES
 
     def validate(self) -> None:
         unknown = sorted(set(self.attrs) - set(attrs))
-        if unknown:
+        if unknown and not open_ended:
             raise ValueError("%s has no attribute %s (it has: %s)" % (op_type, ", ".join(unknown), ", ".join(sorted(attrs)) or "none"))
         missing = sorted(a for a, d in attrs.items() if d is REQUIRED and a not in self.attrs)
         if missing:

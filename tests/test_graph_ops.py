@@ -150,3 +150,32 @@ def test_onnx_lstm_runs_on_the_lstm_layer():
     want, (h_n, _) = ref(x)
     assert y.shape == (T, 1, B, H) and torch.allclose(y[:, 0], want, atol=1e-5)
     assert torch.allclose(y_h, h_n, atol=1e-5)
+
+
+def test_experimental_operators_of_early_onnx():
+    """Affine, Scale, ScaledTanh, ParametricSoftplus, ImageScaler, Crop, ConstantFill, GivenTensorFill: the operator
+    classes the reference generated from its ONNX release (deep500/utils/onnx_interop/generated_operators.py)."""
+    from eagersgd_b200.graph import onnx_ops
+    for name in ("ATen", "Affine", "ConstantFill", "Crop", "GRUUnit", "GivenTensorFill", "ImageScaler", "LoopIndexTensor",
+                 "ParametricSoftplus", "Scale", "ScaledTanh"):
+        assert onnx_ops.operator_class(name) is not None, name
+    assert torch.allclose(_run("Affine", [("x", X, False)], alpha=2.0, beta=-1.0), 2 * X - 1)
+    assert torch.allclose(_run("Scale", [("x", X, False)], scale=0.5), X / 2)
+    assert torch.allclose(_run("ScaledTanh", [("x", X, False)], alpha=1.5, beta=0.5), 1.5 * torch.tanh(0.5 * X))
+    assert torch.allclose(_run("ParametricSoftplus", [("x", X, False)], alpha=2.0, beta=3.0), 2 * torch.log(torch.exp(3 * X) + 1),
+                          atol=1e-6)
+    img = torch.arange(2 * 3 * 4 * 5, dtype=torch.float32).reshape(2, 3, 4, 5)
+    got = _run("ImageScaler", [("x", img, False)], scale=0.1, bias=[1.0, 2.0, 3.0])
+    assert torch.allclose(got, img * 0.1 + torch.tensor([1.0, 2.0, 3.0]).view(1, 3, 1, 1))
+    assert torch.equal(_run("Crop", [("x", img, False)], border=[1, 0, 2, 1]), img[:, :, 0:3, 1:3])
+    assert torch.equal(_run("Crop", [("x", img, False)], border=[1, 1, 0, 0], scale=[2, 3]), img[:, :, 1:3, 1:4])
+    got = _run("ConstantFill", [("x", X, False)], value=2.5)
+    assert got.shape == X.shape and torch.all(got == 2.5)
+    got = _run("ConstantFill", [("s", I64(2, 3), False)], input_as_shape=1, extra_shape=[4], value=7, dtype=7)
+    assert got.shape == (2, 3, 4) and got.dtype == torch.int64 and torch.all(got == 7)
+    got = _run("GivenTensorFill", [("x", torch.zeros(2, 2), False)], values=[1.0, 2.0, 3.0, 4.0])
+    assert torch.equal(got, torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    op = onnx_ops.make_operation("ATen", ["a", "b"], ["c"], operator="index_select", dim=1)      # any attribute is allowed
+    op.validate()
+    with pytest.raises(ValueError, match="no attribute"):
+        onnx_ops.make_operation("Affine", ["a"], ["b"], gamma=1.0).validate()
