@@ -92,8 +92,64 @@ def test_executor_backprop(executor, batch, reference_grads: Dict[str, np.ndarra
     return res
 
 
-def test_optimizer(optimizer, sampler, steps: int = 10, device: Optional[torch.device] = None) -> Dict[str, float]:
-    """Run ``steps`` steps; returns the median step time (ms) and the loss trajectory ends."""
+class OneInputDataset:
+    """A data set of one batch that is handed out again and again: what ``test_optimizer`` makes of a plain dictionary
+    of inputs, or of an (inputs, labels) pair (deep500/lv2/validation/optimizer.py:11-27)."""
+
+    def __init__(self, inputs: Dict[str, np.ndarray], labels: Optional[Dict[str, np.ndarray]] = None):
+        self.batch = dict(inputs)
+        self.batch.update(labels or {})
+        names = list(inputs)
+        self.data_node = names[0] if names else "x"
+        self.label_node = next(iter(labels), "y") if labels else "y"
+
+    def __len__(self):
+        return 1
+
+    def __getitem__(self, index):
+        return self.batch
+
+
+class _OneBatchSampler:
+    def __init__(self, dataset: OneInputDataset):
+        self.dataset, self.batch_size = dataset, 1
+
+    def __call__(self):
+        return self.dataset[0]
+
+    def reset(self): ...
+
+
+def test_optimizer(optimizer, sampler, steps: int = 10, device: Optional[torch.device] = None,
+                   expected_params=None, rtol: float = 1e-4, atol: float = 1e-6) -> Dict[str, float]:
+    """Run ``steps`` steps; returns the median step time (ms) and the loss trajectory ends.
+
+    ``sampler`` may be a sampler, a data set (batches of one sample are drawn from it in order), a dictionary of
+    input arrays, or an (inputs, labels) pair of dictionaries.  With ``expected_params`` (name -> array, or a list in
+    parameter order) exactly one step is taken and the parameters are compared with them: the L2 distance per
+    parameter is returned and a mismatch raises (deep500/lv2/validation/optimizer.py:29-93)."""
+    if isinstance(sampler, dict):
+        sampler = _OneBatchSampler(OneInputDataset(sampler))
+    elif isinstance(sampler, tuple) and len(sampler) == 2 and all(isinstance(d, dict) for d in sampler):
+        sampler = _OneBatchSampler(OneInputDataset(*sampler))
+    elif not callable(sampler):
+        if not (hasattr(sampler, "__len__") and hasattr(sampler, "__getitem__")):
+            raise ValueError("test_optimizer takes a sampler, a data set, a dictionary of inputs or an (inputs, labels) pair")
+        from ..data.sampler import OrderedSampler
+        sampler = OrderedSampler(sampler, 1)
+    if expected_params is not None:
+        batch = sampler()
+        out = optimizer.step(batch)
+        net = optimizer.executor.network
+        names = net.get_params()
+        expect = expected_params if isinstance(expected_params, dict) else dict(zip(names, expected_params))
+        res = {"loss": float(out["loss"])}
+        for name, ref in expect.items():
+            got = net.fetch_tensor(name)
+            res[name] = L2Error().measure(None, got, np.asarray(ref))
+            if not np.allclose(got, np.asarray(ref), rtol=rtol, atol=atol):
+                raise AssertionError("parameter %s after one step differs from the expected value: L2 distance %g" % (name, res[name]))
+        return res
     losses = []
     timer = WallclockTime(reruns=1, avg_over=1, device=device)
 

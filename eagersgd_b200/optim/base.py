@@ -183,3 +183,35 @@ class TorchOptimizer(FirstOrderOptimizer):
                         p.grad.copy_(g)
         self.opt.step()
         return out
+
+
+class LBFGSOptimizer(TorchOptimizer):
+    """``torch.optim.LBFGS`` through the executor: one ``step`` evaluates the loss and its gradients as often as the
+    line search asks (deep500/frameworks/pytorch/pytorch_optimizers.py:136-152)."""
+
+    def __init__(self, executor, loss="loss", learning_rate: float = 1.0, max_iter: int = 20, max_eval: Optional[int] = None,
+                 tolerance_grad: float = 1e-5, tolerance_change: float = 1e-9, history_size: int = 100, line_search_fn=None):
+        params = [p for p in executor.module.parameters() if p.requires_grad]
+        super().__init__(executor, torch.optim.LBFGS(params, lr=learning_rate, max_iter=max_iter, max_eval=max_eval,
+                                                     tolerance_grad=tolerance_grad, tolerance_change=tolerance_change,
+                                                     history_size=history_size, line_search_fn=line_search_fn), loss)
+        self.evaluations = 0
+
+    def step(self, inputs):
+        last = {}
+
+        def closure():
+            self.opt.zero_grad()
+            out = self.executor.inference_and_backprop(inputs, self.loss)
+            if self.gradient_modifier is not None:
+                with torch.no_grad():
+                    for name, p, g in self._grads():
+                        if g is not p.grad:
+                            p.grad.copy_(g)
+            self.evaluations += 1
+            if not last:
+                last.update(out)                         # what the step started from, like the other optimizers return
+            return out[self.loss]
+
+        self.opt.step(closure)
+        return last

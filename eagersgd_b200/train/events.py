@@ -53,6 +53,8 @@ class EpochSummary:
         self.wrong_batches: List = []
         self.time = 0.0
         self.lr: Optional[float] = None
+        self.time_used_inference: List[float] = []     # filled by SummaryGeneratorInferenceEvent
+        self.time_used_optimizing: List[float] = []
 
     @property
     def mean_loss(self):
@@ -119,6 +121,47 @@ class SummaryGeneratorEvent(TrainingEvent):
 
     def after_epoch(self, epoch, runner, training_stats):
         training_stats.train_summaries[-1].time = time.time() - self._t
+
+
+class SummaryGeneratorInferenceEvent(SummaryGeneratorEvent):
+    """Adds the seconds spent in every forward pass and in every optimizer step to the epoch summaries
+    (deep500/lv2/events/summary_generator.py:113-133).  The forward times come from the executor's own hooks, so the
+    event has to be in the executor's event list as well as in the trainer's."""
+
+    def __init__(self):
+        super().__init__()
+        self._fwd0 = self._opt0 = None
+        self._testing = False
+
+    def _summary(self):
+        if self.stats is None:
+            return None
+        pool = self.stats.test_summaries if self._testing else self.stats.train_summaries
+        return pool[-1] if pool else None
+
+    def before_test_set(self, runner, training_stats, sampler):
+        self.stats, self._testing = training_stats, True
+
+    def after_test_set(self, runner, training_stats, sampler):
+        self._testing = False
+
+    def before_executor(self, inputs):
+        self._fwd0 = time.perf_counter()
+
+    def after_inference(self, outputs):
+        s = self._summary()
+        if s is not None and self._fwd0 is not None and not self._testing:
+            s.time_used_inference.append(time.perf_counter() - self._fwd0)
+        self._fwd0 = None
+
+    def before_optimizer_step(self, executor, optimizer, inputs):
+        self._opt0 = time.perf_counter()
+
+    def after_optimizer_step(self, executor, optimizer, loss):
+        s = self._summary()
+        if s is not None and self._opt0 is not None:
+            s.time_used_optimizing.append(time.perf_counter() - self._opt0)
+        self._opt0 = None
 
 
 class AccuracyAbortEvent(TrainingEvent):

@@ -35,19 +35,37 @@ def _np(x):
     return x.detach().float().cpu().numpy() if isinstance(x, torch.Tensor) else np.asarray(x, dtype=np.float64)
 
 
-class L1Error(TestMetric):
+class NormDifference(TestMetric):
+    """Norm of the difference between outputs and reference outputs; ``ord`` as in ``numpy.linalg.norm``.  A list of
+    outputs gives a list of norms (deep500/utils/metrics.py:10-26)."""
+
+    def __init__(self, ord=2):
+        self.ord = ord
+
+    def _one(self, o, r):
+        return float(np.linalg.norm((_np(o).astype(np.float64) - _np(r).astype(np.float64)).ravel(), ord=self.ord))
+
     def measure(self, inputs, outputs, reference_outputs):
-        return float(np.abs(_np(outputs) - _np(reference_outputs)).sum())
+        if isinstance(outputs, (list, tuple)):
+            if len(outputs) != len(reference_outputs):
+                raise ValueError("outputs and reference outputs differ in number")
+            return [self._one(o, r) for o, r in zip(outputs, reference_outputs)]
+        return self._one(outputs, reference_outputs)
 
 
-class L2Error(TestMetric):
-    def measure(self, inputs, outputs, reference_outputs):
-        return float(np.sqrt(((_np(outputs) - _np(reference_outputs)) ** 2).sum()))
+class L1Error(NormDifference):
+    def __init__(self):
+        super().__init__(1)
 
 
-class MaxError(TestMetric):
-    def measure(self, inputs, outputs, reference_outputs):
-        return float(np.abs(_np(outputs) - _np(reference_outputs)).max())
+class L2Error(NormDifference):
+    def __init__(self):
+        super().__init__(2)
+
+
+class MaxError(NormDifference):
+    def __init__(self):
+        super().__init__(np.inf)
 
 
 class DiffHeatmap(TestMetric):

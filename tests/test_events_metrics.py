@@ -155,3 +155,31 @@ def test_communication_metrics_follow_the_optimizer_counters():
         assert 0 <= prof.measure() < 1000
     finally:
         o.close()
+
+
+def test_inference_summary_event_times_forward_passes_and_steps():
+    from eagersgd_b200.optim.base import GradientDescent
+    from eagersgd_b200.train import events as E
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import Trainer
+    torch.manual_seed(0)
+    ds, tr, te = _toy()
+    ev = E.SummaryGeneratorInferenceEvent()
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss, events=[ev])      # the executor's hooks time the forward
+    stats = Trainer(tr, te, ex, GradientDescent(ex, learning_rate=0.1)).run_loop(2, [ev])
+    for s in stats.train_summaries:
+        assert len(s.losses) == len(s.time_used_inference) == len(s.time_used_optimizing) == 8
+        assert all(0 < a <= b for a, b in zip(s.time_used_inference, s.time_used_optimizing))   # a step contains its forward
+    assert all(s.time_used_optimizing == [] for s in stats.test_summaries)
+
+
+def test_norm_difference_over_lists_and_orders():
+    from eagersgd_b200.train import metrics as M
+    a, b = np.array([3.0, -4.0]), np.zeros(2)
+    assert M.NormDifference(2).measure(None, a, b) == pytest.approx(5.0)
+    assert M.NormDifference(1).measure(None, a, b) == pytest.approx(7.0)
+    assert M.NormDifference(np.inf).measure(None, a, b) == pytest.approx(4.0)
+    assert M.L2Error().measure(None, [a, 2 * a], [b, b]) == pytest.approx([5.0, 10.0])
+    with pytest.raises(ValueError):
+        M.L1Error().measure(None, [a], [b, b])
+    assert isinstance(M.MaxError(), M.NormDifference) and M.MaxError().ord == np.inf

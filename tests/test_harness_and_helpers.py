@@ -233,3 +233,35 @@ def test_status_words_segments_and_switches(monkeypatch):
     monkeypatch.setenv("NCCL_NVLS_ENABLE", "1")
     monkeypatch.setenv("ESGD_MULTICAST", "0")
     assert not multicast_wanted()
+
+
+def test_optimizer_harness_with_expected_parameters_and_lbfgs():
+    """One step of gradient descent on a linear layer has a closed form; ``test_optimizer`` takes plain dictionaries
+    of inputs and compares the parameters after the step with it (deep500/lv2/validation/optimizer.py:29-93).  L-BFGS,
+    the one optimizer that needs the loss re-evaluated inside a step, solves the least-squares problem outright."""
+    from eagersgd_b200.ops.validation import OneInputDataset, test_optimizer
+    from eagersgd_b200.optim.base import GradientDescent, LBFGSOptimizer
+    rng = np.random.RandomState(0)
+    x, y = rng.randn(8, 6).astype(np.float32), rng.randn(8, 3).astype(np.float32)
+    ex = _executor()
+    w, b = ex.network.fetch_tensor("weight").copy(), ex.network.fetch_tensor("bias").copy()
+    d = 2 * (x @ w.T + b - y) / y.size
+    expect = {"weight": w - 0.25 * d.T @ x, "bias": b - 0.25 * d.sum(0)}
+    res = test_optimizer(GradientDescent(ex, learning_rate=0.25), ({"x": x}, {"y": y}), expected_params=expect)
+    assert res["weight"] < 1e-5 and res["bias"] < 1e-5 and res["loss"] == pytest.approx(float(((x @ w.T + b - y) ** 2).mean()), rel=1e-5)
+    with pytest.raises(AssertionError, match="weight"):
+        test_optimizer(GradientDescent(_executor(), learning_rate=0.25), {"x": x, "y": y}, expected_params=[w, b])
+    with pytest.raises(ValueError):
+        test_optimizer(GradientDescent(_executor(), learning_rate=0.25), 3)
+    ds = OneInputDataset({"x": x}, {"y": y})
+    assert len(ds) == 1 and set(ds[0]) == {"x", "y"} and ds.data_node == "x" and ds.label_node == "y"
+    ex2 = _executor()
+    opt = LBFGSOptimizer(ex2, learning_rate=1.0, max_iter=50, history_size=20, line_search_fn="strong_wolfe")
+    first = opt.step({"x": x, "y": y})
+    assert opt.evaluations > 1                                      # the line search re-evaluated the loss
+    A = np.concatenate([x, np.ones((8, 1), np.float32)], 1)
+    best = float(((A @ np.linalg.lstsq(A, y, rcond=None)[0] - y) ** 2).mean())
+    after = float(ex2.inference({"x": x, "y": y})["loss"])
+    assert after < float(first["loss"]) and after == pytest.approx(best, abs=1e-4)
+    opt.set_parameter("learning_rate", 0.5)
+    assert opt.opt.param_groups[0]["lr"] == 0.5
