@@ -14,6 +14,7 @@ import datetime
 import json
 import os
 import platform
+import threading
 import time
 from typing import Dict, Optional
 
@@ -64,6 +65,33 @@ class BenchmarkFileLogger(BaseBenchmarkLogger):
         with open(os.path.join(self.dir, "run_status.log"), "w") as f:
             json.dump({"run_status": status}, f)
             f.write("\n")
+
+
+_benchmark_logger: Optional[BaseBenchmarkLogger] = None
+_logger_lock = threading.Lock()
+
+
+def config_benchmark_logger(flag_obj=None) -> BaseBenchmarkLogger:
+    """Set the process-wide benchmark logger from a flags object (``benchmark_logger_type``, ``benchmark_log_dir``);
+    without one, or with the base type, metrics go to standard output (logger.py:56-86).  The reference's third type
+    uploads to BigQuery; with no network here a request for it is an error like any unknown type."""
+    global _benchmark_logger
+    with _logger_lock:
+        kind = getattr(flag_obj, "benchmark_logger_type", None) or "BaseBenchmarkLogger"
+        if kind == "BaseBenchmarkLogger":
+            _benchmark_logger = BaseBenchmarkLogger()
+        elif kind == "BenchmarkFileLogger":
+            _benchmark_logger = BenchmarkFileLogger(flag_obj.benchmark_log_dir)
+        else:
+            raise ValueError("Unrecognized benchmark_logger_type: %s" % kind)
+        return _benchmark_logger
+
+
+def get_benchmark_logger() -> BaseBenchmarkLogger:
+    """The process-wide logger (a standard-output one if nothing was configured)."""
+    if _benchmark_logger is None:
+        config_benchmark_logger()
+    return _benchmark_logger
 
 
 def _metric(name, value, unit, global_step, extras):

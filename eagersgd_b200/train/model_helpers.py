@@ -27,6 +27,18 @@ def past_stop_threshold(stop_threshold, eval_metric) -> bool:
     return eval_metric >= stop_threshold
 
 
+def per_device_batch_size(batch_size: int, num_gpus: int) -> int:
+    """The batch of one GPU when ``batch_size`` is the global one: it has to divide evenly
+    (official/utils/misc/distribution_utils.py:50-79)."""
+    if num_gpus <= 1:
+        return batch_size
+    if batch_size % num_gpus:
+        raise ValueError("When running with multiple GPUs, batch size must be a multiple of the number of available GPUs. "
+                         "Found %d GPUs with a batch size of %d; try --batch_size=%d instead."
+                         % (num_gpus, batch_size, batch_size - batch_size % num_gpus))
+    return batch_size // num_gpus
+
+
 def generate_synthetic_data(input_shape: Sequence[int], input_value=0, input_dtype=torch.float32,
                             label_shape: Optional[Sequence[int]] = None, label_value=0, label_dtype=torch.int64,
                             batches: Optional[int] = None):

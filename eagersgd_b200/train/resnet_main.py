@@ -31,9 +31,8 @@ from ..optim.lars import LARS, poly_rate_schedule
 from ..parallel.group import init as init_group, finalize
 from . import flags as F
 from .imbalance import ConstantRanks, ExponentialDelays, FixedRanksSleep, NoImbalance, RandomRankFactor
-from .logger import (BaseBenchmarkLogger, BenchmarkFileLogger, ExamplesPerSecondHook, ProfilerHook, benchmark_context,
-                     parse_hooks,
-                     training_log_line)
+from .logger import (BaseBenchmarkLogger, ExamplesPerSecondHook, ProfilerHook, benchmark_context, config_benchmark_logger,
+                     parse_hooks, training_log_line)
 from .metrics import topk_accuracy
 from .schedule import cifar10_schedule, imagenet_schedule
 from .step import TrainStep
@@ -151,8 +150,9 @@ def main(argv=None):
 
     train_sampler, val_sampler = build_data(args, info, group)
     steps_per_epoch = max((args.synthetic_train_size or info["train"]) // epoch_batch, 1)   # a data set read from disk knows its size
-    logger = BenchmarkFileLogger(args.benchmark_log_dir) if (
-        args.benchmark_logger_type == "BenchmarkFileLogger" and args.benchmark_log_dir) else BaseBenchmarkLogger()
+    if args.benchmark_logger_type == "BenchmarkFileLogger" and not args.benchmark_log_dir:
+        args.benchmark_logger_type = "BaseBenchmarkLogger"           # nowhere to write files to
+    logger = config_benchmark_logger(args)                           # also what get_benchmark_logger() returns from now on
     if group.rank == 0:
         logger.log_run_info("resnet%d" % args.resnet_size, args.dataset, vars(args), args.benchmark_test_id)
     eps_hook = ExamplesPerSecondHook(global_batch, every_n_steps=max(args.train_acc_steps, 1), warm_steps=5,

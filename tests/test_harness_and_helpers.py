@@ -265,3 +265,21 @@ def test_optimizer_harness_with_expected_parameters_and_lbfgs():
     assert after < float(first["loss"]) and after == pytest.approx(best, abs=1e-4)
     opt.set_parameter("learning_rate", 0.5)
     assert opt.opt.param_groups[0]["lr"] == 0.5
+
+
+def test_process_wide_logger_and_per_device_batch(tmp_path):
+    import types
+    from eagersgd_b200.train import logger as L
+    from eagersgd_b200.train.model_helpers import per_device_batch_size
+    assert isinstance(L.get_benchmark_logger(), L.BaseBenchmarkLogger)
+    flags = types.SimpleNamespace(benchmark_logger_type="BenchmarkFileLogger", benchmark_log_dir=str(tmp_path / "logs"))
+    log = L.config_benchmark_logger(flags)
+    assert isinstance(log, L.BenchmarkFileLogger) and L.get_benchmark_logger() is log
+    L.get_benchmark_logger().log_metric("accuracy", 0.5, global_step=3)
+    assert json.loads(open(tmp_path / "logs" / "metric.log").readline())["name"] == "accuracy"
+    with pytest.raises(ValueError, match="Unrecognized benchmark_logger_type"):
+        L.config_benchmark_logger(types.SimpleNamespace(benchmark_logger_type="BenchmarkBigQueryLogger"))
+    assert type(L.config_benchmark_logger()) is L.BaseBenchmarkLogger          # back to standard output
+    assert per_device_batch_size(256, 1) == 256 and per_device_batch_size(256, 8) == 32
+    with pytest.raises(ValueError, match="try --batch_size=96"):
+        per_device_batch_size(100, 8)
