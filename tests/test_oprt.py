@@ -1,7 +1,8 @@
 """Host operation runtime: the reference's fflib2 evaluation programs as assertions
 (evaluation/send_recv.c, ping_pong_dep.c, ping_pong_schedule.c, simple_computation.c,
 custom_computation.c, first_dep.c, activation_1.c, activation_tree_multiple.c, limiter.c,
-allreduce.c, allreduce_inplace.c, allreduce_buffers_user_managed*.c)."""
+allreduce.c, allreduce_inplace.c, allreduce_buffers_user_managed*.c, allreduce_buffers_fflib_managed*.c,
+ping_modify_pong.c, activation_tree.c).  The solo / majority programs are in test_oprt_partial.py."""
 import threading
 import time
 
@@ -543,3 +544,73 @@ def test_operation_description_operator_delete_and_default_schedule_functions():
         assert R.lib().rt_schedule_default_print(r.h, s, buf, len(buf)) > 0 and b"digraph" in buf.value
         assert r.schedule_delete(s) == R.SUCCESS and calls == ["delete"]
         assert r.schedule_delete(s) == R.ERROR
+
+
+def test_ping_modify_pong_a_dependent_operation_needs_no_post():
+    """evaluation/ping_modify_pong.c: rank 1's send hangs off its receive, so only the receive is posted; the pong
+    carries what the ping brought."""
+    n = 257
+    with R.World(2) as w:
+        def body(r):
+            ping, pong = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+            if r.id == 0:
+                ping[:] = np.arange(n)
+                a, b = r.send(r.buffer(ping), 1, 0), r.recv(r.buffer(pong), 1, 0)
+                r.post(a)
+                r.post(b)
+                assert r.wait(b) == R.SUCCESS and np.array_equal(pong, np.arange(n))
+            else:
+                bp = r.buffer(ping)
+                a, b = r.recv(bp, 0, 0), r.send(bp, 0, 0)
+                r.hb(a, b)
+                r.post(a)                                       # b is never posted by hand
+                assert r.wait(b) == R.SUCCESS and np.array_equal(ping, np.arange(n))
+            for op in (a, b):
+                assert r.free(op) == R.SUCCESS
+        _run(w, body)
+
+
+@pytest.mark.parametrize("inplace", [False, True])
+def test_allreduce_on_buffers_the_runtime_owns(inplace):
+    """evaluation/allreduce_buffers_fflib_managed.c and _inplace.c: buffers created without user memory, resized to a
+    random count before every post, filled and read through the runtime's own pointer; closed form (i + j) * size."""
+    world, rounds = 3, 12
+    counts = np.random.RandomState(7).randint(1, 300, size=rounds)
+    with R.World(world) as w:
+        def body(r):
+            rcv = r.buffer(count=300, dtype=np.float32)
+            snd = R.INPLACE if inplace else r.buffer(count=300, dtype=np.float32)
+            s = r.allreduce(snd, rcv, tag=0)
+            for i, count in enumerate(int(c) for c in counts):
+                r.resize(rcv, count=count)
+                if not inplace:
+                    r.resize(snd, count=count)
+                src = r.buffer_array(rcv if inplace else snd, np.float32)
+                assert src.shape == (count,)
+                src[:] = np.arange(count) + i
+                assert r.schedule_post(s) == R.SUCCESS and r.schedule_wait(s) == R.SUCCESS
+                assert np.array_equal(r.buffer_array(rcv, np.float32), (np.arange(count) + i) * world), (r.id, i)
+            assert r.schedule_delete(s) == R.SUCCESS and r.buffer_delete(rcv) == R.SUCCESS
+        _run(w, body)
+
+
+def test_activation_feeds_a_computation_on_every_rank():
+    """evaluation/activation_tree.c: a compute operation (acc += 1) hangs off the activation's join; whoever the
+    activator is, every rank's accumulator goes up by exactly one per activation."""
+    world = 5
+    activators = np.random.RandomState(4535).randint(world, size=6)
+    with R.World(world) as w:
+        def body(r):
+            acc, inc = np.zeros(1, dtype=np.int32), np.ones(1, dtype=np.int32)
+            ba, bi = r.buffer(acc), r.buffer(inc)
+            s, act, joined = r.activation(tag=0)
+            add = r.comp(ba, bi, ba, R.SUM)
+            r.hb(joined, add)
+            for k, who in enumerate(activators):
+                if who == r.id:
+                    r.post(act)
+                assert r.wait(add) == R.SUCCESS and acc[0] >= k + 1    # the next activator may be ahead already
+            gate.wait()
+            assert acc[0] == len(activators) and r.completions(add) == len(activators)
+        gate = threading.Barrier(world)
+        _run(w, body)

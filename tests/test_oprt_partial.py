@@ -314,3 +314,68 @@ def test_sgd_loop_benchmark_shows_the_three_behaviours():
     assert r["ssgd_contributors"] == 4.0 and r["rsgd_contributors"] >= 1.0
     assert r["rsgd_us"] < 0.5 * r["ssgd_us"], r
     assert r["rsgd_us"] < r["randomsgd_us"] < 1.25 * r["ssgd_us"], r
+
+
+def test_one_random_slow_rank_with_a_limiter_of_twenty():
+    """evaluation/solo_allreduce_single.c / solo_allreduce_multiple.c: every rank increments its vector before each
+    post, one rank drawn from a shared seed sleeps before its posts, limiter 20; nobody but that rank waits, and
+    what arrives is always a whole round."""
+    world, iters, n = 4, 25, 33
+    slow = int(np.random.RandomState(434656342 % (2 ** 31)).randint(world))
+    waits = [0.0] * world
+    infos = [None] * world
+    with R.World(world) as w:
+        done = threading.Barrier(world)
+
+        def body(r):
+            to_reduce, reduced, res = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+            s = r.solo_allreduce(r.buffer(to_reduce), r.buffer(reduced), tag=0, limiter=20)
+            if r.id == 0:
+                assert r.schedule_dot(s).count("digraph") == 3             # the program prints the schedule first
+            r.schedule_start(s)
+            for it in range(iters):
+                to_reduce += 1
+                if r.id == slow:
+                    time.sleep(0.01)
+                r.schedule_post(s)
+                t0 = time.perf_counter()
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                waits[r.id] += time.perf_counter() - t0
+                k, rnd = r.partial_read(s, res)
+                assert np.all(res == res[0]) and 0 <= k <= world and rnd >= it
+            done.wait()
+            infos[r.id] = r.partial_info(s)
+            r.schedule_delete(s)
+        _run(w, body)
+    for q in range(world):
+        assert infos[q]["rounds"] == iters and infos[q]["sync_rounds"] == 1        # round 20
+    others = [waits[q] for q in range(world) if q != slow]
+    assert infos[slow]["late"] >= iters - 6                         # the slow rank found nearly all of its rounds begun
+    assert max(others) < 0.25 + 0.01 * 22                           # the others waited for it in the synchronous round only
+
+
+@pytest.mark.parametrize("kind", ["solo", "majority"])
+def test_several_collectives_side_by_side_on_balanced_ranks(kind):
+    """evaluation/rsgd_synch_send.c, rsgd_synch_recv.c and their ssgd twins: N persistent schedules with tags 0..N-1,
+    posted and waited for one after the other in every iteration; with nobody late every round has everybody."""
+    world, N, iters, n = 3, 3, 10, 64
+    with R.World(world) as w:
+        def body(r):
+            snd = [np.zeros(n, dtype=np.float32) for _ in range(N)]
+            rcv = [np.zeros(n, dtype=np.float32) for _ in range(N)]
+            make = (lambda i: r.solo_allreduce(r.buffer(snd[i]), r.buffer(rcv[i]), tag=i, limiter=0)) if kind == "solo" else \
+                   (lambda i: r.rand_allreduce(r.buffer(snd[i]), r.buffer(rcv[i]), tag=i, seed=6545343, limiter=0))
+            scheds = [make(i) for i in range(N)]
+            for s in scheds:
+                r.schedule_start(s)
+            for it in range(iters):
+                for i, s in enumerate(scheds):
+                    snd[i][:] = 1.0 + i
+                    r.schedule_post(s)
+                    assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                    assert np.all(rcv[i] == world * (1.0 + i)), (it, i, rcv[i][:3])   # limiter 0: every round has all ranks
+                    snd[i][:] = 0.0
+            for s in scheds:
+                assert r.partial_info(s)["rounds"] == iters
+                r.schedule_delete(s)
+        _run(w, body)
