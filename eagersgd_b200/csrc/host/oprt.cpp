@@ -998,6 +998,23 @@ rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper) {
   return s;
 }
 
+// The listening side of an activation schedule is armed by rt_schedule_start (or the first rt_schedule_post): the
+// caller hangs its dependents on `joined` first, so that an activation from a faster rank cannot pass them by.
+// Tokens that arrive earlier wait in the mailbox.
+static int activation_arm(rt_rank* c, rt_sched s) {
+  std::vector<rt_op> recvs;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    Schedule& sc = c->scheds[s];
+    if (sc.state) return RT_SUCCESS;                    // armed already
+    sc.state = (void*)1;
+    for (rt_op id : sc.ops)
+      if (c->ops[id] && c->ops[id]->type == T_RECV) recvs.push_back(id);
+  }
+  for (rt_op rv : recvs) rt_op_post(c, rv);
+  return RT_SUCCESS;
+}
+
 // Activation from any rank: the activator sends a token to everybody; on every rank the
 // `joined` no-op (OR) completes once per activation, whether it was local or remote.
 // With an all-to-all fabric there is no need for the reference's forwarding tree.
@@ -1023,7 +1040,12 @@ rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined) {
     rt_op_hb(c, rv, join);
     rt_op_hb(c, rv, rv);
     rt_schedule_add_op(c, s, rv);
-    rt_op_post(c, rv);
+  }
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    c->scheds[s].finalized = true;                      // wired by hand
+    c->scheds[s].start_fn = activation_arm;
+    c->scheds[s].post_fn = activation_arm;              // the reference arms it with ffschedule_post
   }
   *activate = act;
   *joined = join;

@@ -140,7 +140,8 @@ int rt_schedule_print_visjs(rt_rank* c, rt_sched s, char* out, int64_t cap);   /
 
 /* collectives */
 rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int op);   /* snd == RT_INPLACE: in place */
-/* activation: any rank posts `activate`; every rank's `joined` op completes once per activation */
+/* activation: any rank posts `activate`; every rank's `joined` op completes once per activation.  A rank listens from
+ * rt_schedule_start (or rt_schedule_post) of the returned schedule on: hang the dependents on `joined` before that */
 rt_sched rt_activation(rt_rank* c, int tag, rt_op* activate, rt_op* joined);
 /* limiter: posting `start` fires async[0..n-1] in turn, then sync, round-robin */
 int rt_limiter(rt_rank* c, int num_async, rt_op* start, rt_op* async_ops, rt_op* sync_op);

@@ -220,9 +220,13 @@ class Rank:
     def allreduce(self, snd: int, rcv: int, tag: int, op=SUM) -> int:
         return lib().rt_allreduce(self.h, snd, rcv, tag, op)
 
-    def activation(self, tag: int) -> Tuple[int, int, int]:
+    def activation(self, tag: int, arm: bool = True) -> Tuple[int, int, int]:
+        """(schedule, activate, joined).  With ``arm=False`` the rank does not listen yet: hang dependents on ``joined``
+        first and call ``schedule_start`` then, so that an activation from a faster rank cannot pass them by."""
         a, j = C.c_int64(), C.c_int64()
         s = lib().rt_activation(self.h, tag, C.byref(a), C.byref(j))
+        if arm:
+            lib().rt_schedule_start(self.h, s)
         return s, a.value, j.value
 
     def limiter(self, num_async: int) -> Tuple[int, List[int], int]:

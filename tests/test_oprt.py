@@ -603,9 +603,10 @@ def test_activation_feeds_a_computation_on_every_rank():
         def body(r):
             acc, inc = np.zeros(1, dtype=np.int32), np.ones(1, dtype=np.int32)
             ba, bi = r.buffer(acc), r.buffer(inc)
-            s, act, joined = r.activation(tag=0)
+            s, act, joined = r.activation(tag=0, arm=False)
             add = r.comp(ba, bi, ba, R.SUM)
             r.hb(joined, add)
+            assert r.schedule_post(s) == R.SUCCESS                  # listen only now that the dependent is wired
             for k, who in enumerate(activators):
                 if who == r.id:
                     r.post(act)
