@@ -168,6 +168,14 @@ class Visitor:
         raise NotImplementedError("no visitor method for op type %s" % op.op_type)
 
 
+class EmptyVisitor(Visitor):
+    """A visitor that passes over operators it has no method for instead of raising (the reference's
+    ``EmptyOnnxBaseVisitor``, deep500/utils/onnx_interop/onnx_base_visitor.py): override the few you care about."""
+
+    def visit_default(self, op: Operation, graph: Graph):
+        return None
+
+
 class OpCounter(Visitor):
     """Counts operations per type (an 'empty operations visitor' that does something useful)."""
 

@@ -41,3 +41,14 @@ def rank_env() -> dict:
     """RANK / LOCAL_RANK / WORLD_SIZE of this process (single-process defaults when not launched as a rank)."""
     return {"rank": int(os.environ.get("RANK", 0)), "local_rank": int(os.environ.get("LOCAL_RANK", 0)),
             "world": int(os.environ.get("WORLD_SIZE", 1))}
+
+
+def end_barrier() -> None:
+    """Meet the other ranks once more and leave the process group, if this process is a rank of one; nothing
+    otherwise.  The last line of a program that may or may not have been forked into ranks (the reference's
+    ``mpi_end_barrier``, deep500/utils/mpi_helper.py:48-57)."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        from ..parallel.group import finalize
+        finalize()

@@ -5,7 +5,8 @@ tensors, executed on the native executor and on the CPU oracles, compared with a
 
 The reference picks a case from the onnx package's backend test data (deep500 samples/onnxtest.py:10-34,
 utils/onnx_interop/onnx_test_parser.py); that package is not available here, so the cases are generated in the
-same shape: ``<case>/model.onnx`` and ``<case>/test_data_set_0/{input_k,output_k}.npy``.
+same layout — ``<case>/model.onnx`` and ``<case>/test_data_set_0/{input_k,output_k}.pb`` (serialized tensors) — and read
+back through ``eagersgd_b200.graph.OnnxTestParser``, which reads a copy of the real suite's data just as well.
 """
 import random
 import tempfile
@@ -16,23 +17,16 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-from eagersgd_b200.graph import Graph, GraphNetwork, ReferenceGraphExecutor, load_onnx, save_onnx  # noqa: E402
-from eagersgd_b200.train.metrics import L2Error  # noqa: E402
+from eagersgd_b200.graph import Graph, OnnxTestData, OnnxTestParser, write_case  # noqa: E402
 
 
 def _case(root, name, op_type, inputs, attrs, fn):
     g = Graph("test_" + name)
-    names = []
-    for k, a in enumerate(inputs):
-        names.append(g.add_input("in%d" % k))
+    names = [g.add_input("in%d" % k) for k in range(len(inputs))]
     g.add(op_type, names, ["out"], **attrs)
     g.add_output("out")
-    d = os.path.join(root, "test_" + name, "test_data_set_0")
-    os.makedirs(d, exist_ok=True)
-    save_onnx(g, os.path.join(root, "test_" + name, "model.onnx"))
-    for k, a in enumerate(inputs):
-        np.save(os.path.join(d, "input_%d.npy" % k), a)
-    np.save(os.path.join(d, "output_0.npy"), fn(*[torch.as_tensor(a) for a in inputs]).numpy())
+    want = fn(*[torch.as_tensor(a) for a in inputs]).numpy()
+    write_case(root, name, g, [OnnxTestData(list(inputs), [want])])      # model.onnx + test_data_set_0/{input,output}_k.pb
 
 
 def generate(root):
@@ -51,18 +45,9 @@ def generate(root):
 
 
 def run_case(root, name):
-    case = os.path.join(root, name)
-    g = load_onnx(os.path.join(case, "model.onnx"))
-    d = os.path.join(case, "test_data_set_0")
-    ins = [np.load(os.path.join(d, "input_%d.npy" % k)) for k in range(len(g.inputs))]
-    want = np.load(os.path.join(d, "output_0.npy"))
-    feeds = dict(zip(g.inputs, ins))
-    with torch.no_grad():
-        native = GraphNetwork(g).eval()(torch.as_tensor(ins[0]), **{k: torch.as_tensor(v) for k, v in list(feeds.items())[1:]})
-    native = (native[0] if isinstance(native, (list, tuple)) else native).numpy()
-    oracle = ReferenceGraphExecutor(g, training=False).inference(feeds)[0]
-    m = L2Error()
-    e_native, e_oracle = m.measure(ins, native, want), m.measure(ins, np.asarray(oracle, np.float32).reshape(want.shape), want)
+    parser = OnnxTestParser(root)
+    e_native = parser.run_test(name, "native")[0][0]
+    e_oracle = parser.run_test(name, "reference")[0][0]
     print("%-18s L2 error: native %.2e, CPU oracle %.2e" % (name, e_native, e_oracle))
     return e_native, e_oracle
 

@@ -481,3 +481,52 @@ def test_torch_lstm_models_become_onnx_lstm_nodes(batch_first, layers, tmp_path)
         path = export_network(m, str(tmp_path / "lstm.onnx"), example_inputs=(x,))
         again = GraphNetwork(load_onnx(path)).eval()(x)
     assert torch.allclose(got, want, atol=1e-5) and torch.allclose(again, want, atol=1e-5)
+
+
+def test_onnx_backend_test_layout_is_read_and_run(tmp_path):
+    """Cases in the layout of the ONNX backend test suite (model.onnx, test_data_set_k/{input,output}_i.pb or .npy, in
+    folders per kind) are found, read without the onnx package and run on both executors
+    (deep500/utils/onnx_interop/onnx_test_parser.py)."""
+    from eagersgd_b200.graph import (EmptyVisitor, Graph, OnnxTestData, OnnxTestParser, OpCounter, load_tensor_pb,
+                                     save_tensor_pb, write_case)
+    rng = np.random.RandomState(0)
+    a, b = rng.randn(3, 4).astype(np.float32), rng.randn(3, 4).astype(np.float32)
+    g = Graph("test_add")
+    g.add("Add", [g.add_input("x"), g.add_input("y")], ["z"])
+    g.add_output("z")
+    write_case(str(tmp_path / "node"), "add", g, [OnnxTestData([a, b], [a + b]), OnnxTestData([b, b], [2 * b])])
+    g2 = Graph("test_gemm")
+    g2.add_initializer("w", rng.randn(4, 5).astype(np.float32))
+    g2.add("MatMul", [g2.add_input("x"), "w"], ["h"])
+    g2.add("Relu", ["h"], ["y"])
+    g2.add_output("y")
+    write_case(str(tmp_path / "simple"), "test_gemm_relu", g2, [OnnxTestData([a], [np.maximum(a @ g2.initializers["w"], 0)])],
+               as_numpy=True)
+    p = OnnxTestParser(str(tmp_path))
+    assert p.all_tests() == {"node": ["test_add"], "simple": ["test_gemm_relu"]}
+    t = p.get_test("add")
+    assert len(t.data_sets) == 2 and [op.op_type for op in t.model.ops] == ["Add"]
+    assert np.array_equal(t.data_sets[1].inputs[0], b) and np.array_equal(t.data_sets[0].outputs[0], a + b)
+    for ex in ("native", "reference"):
+        errs = p.run_test("test_add", ex)
+        assert len(errs) == 2 and max(max(e) for e in errs) < 1e-6
+        assert p.run_test("test_gemm_relu", ex)[0][0] < 1e-4
+    with pytest.raises(KeyError, match="there are 2"):
+        p.get_test("nothing")
+    # tensor files: every element type the reader knows survives, names and scalars included
+    for arr in (np.arange(6, dtype=np.int64).reshape(2, 3), np.float64(2.5), np.array([True, False]), a.astype(np.float16)):
+        save_tensor_pb(str(tmp_path / "t.pb"), arr, "t")
+        back = load_tensor_pb(str(tmp_path / "t.pb"))
+        assert back.dtype == np.asarray(arr).dtype and back.shape == np.asarray(arr).shape and np.array_equal(back, arr)
+    # a visitor that passes over what it has no method for
+
+    class OnlyRelu(EmptyVisitor):
+        def begin(self, graph):
+            self.seen = []
+
+        def visit_relu(self, op, graph):
+            self.seen.append(op.outputs[0])
+
+        def end(self, graph):
+            return self.seen
+    assert g2.accept(OnlyRelu()) == ["y"] and g2.accept(OpCounter()) == {"MatMul": 1, "Relu": 1}

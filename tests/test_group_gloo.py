@@ -36,8 +36,9 @@ def _group_methods(rank, world):
     g.reduce_from_neighbors(n)
     left, right = (rank - 1) % world, (rank + 1) % world
     res["neighbours"] = bool(torch.all(n == float(rank + 1 + left + 1 + right + 1)))
-    g.barrier()
-    es.finalize()
+    from eagersgd_b200.utils.launch import end_barrier
+    end_barrier()                                               # meets the others once more and leaves the group
+    res["left_group"] = not torch.distributed.is_initialized()
     return res
 
 

@@ -234,3 +234,9 @@ def test_c_sample_of_the_runtime_partial_allreduce(tmp_path, mode):
                    libs + ["-lpthread", "-o", exe], check=True, capture_output=True, text=True)
     r = subprocess.run([exe, "4", "4096", "12", str(mode), "5"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "PASSED" in r.stdout and "2 synchronous" in r.stdout, r.stdout + r.stderr
+
+
+def test_end_barrier_is_a_no_op_outside_a_process_group():
+    from eagersgd_b200.utils.launch import end_barrier, rank_env
+    end_barrier()                                               # no group: returns at once
+    assert rank_env()["world"] >= 1
