@@ -16,6 +16,23 @@ import torch
 from ..train.metrics import L2Error, MaxError, TestMetric, WallclockTime
 
 
+def DefaultOpMetrics() -> List[TestMetric]:
+    """The metrics an operator test reports when none are named (deep500/lv0/validation/metrics.py:4-9)."""
+    from ..train.metrics import DiffHeatmap
+    return [L2Error(), MaxError(), DiffHeatmap(), WallclockTime()]
+
+
+def DefaultOptimizerMetrics() -> List[TestMetric]:
+    """deep500/lv2/validation/optimizer.py:8-9."""
+    return [L2Error(), WallclockTime()]
+
+
+def DefaultTrainingMetrics() -> List[TestMetric]:
+    """deep500/lv2/validation/metrics.py:9-10."""
+    from ..train.metrics import TestAccuracy, TrainingAccuracy
+    return [TrainingAccuracy(), TestAccuracy()]
+
+
 def _as_list(x):
     return list(x) if isinstance(x, (tuple, list)) else [x]
 

@@ -14,6 +14,14 @@ import numpy as np
 from .events import EpochSummary, StopTraining, SummaryGeneratorEvent, TrainingStatistics
 
 
+def DefaultTrainerEvents(epochs: int = 0, stream=None):
+    """What a run shows when no events are named: the progress bar on the terminal (deep500/lv2/trainer.py:18-19)."""
+    import sys
+
+    from .events import TerminalBarEvent
+    return [TerminalBarEvent(stream or sys.stderr)]
+
+
 class Trainer:
     def __init__(self, training_sampler, validation_sampler, executor, optimizer, output_node: str = "output",
                  network_output: str = "output"):

@@ -183,3 +183,18 @@ def test_norm_difference_over_lists_and_orders():
     with pytest.raises(ValueError):
         M.L1Error().measure(None, [a], [b, b])
     assert isinstance(M.MaxError(), M.NormDifference) and M.MaxError().ord == np.inf
+
+
+def test_default_event_and_metric_sets():
+    from eagersgd_b200.ops.validation import DefaultOpMetrics, DefaultOptimizerMetrics, DefaultTrainingMetrics
+    from eagersgd_b200.train import events as E, metrics as M
+    from eagersgd_b200.train.trainer import DefaultTrainerEvents
+    assert [type(m) for m in DefaultOpMetrics()] == [M.L2Error, M.MaxError, M.DiffHeatmap, M.WallclockTime]
+    assert [type(m) for m in DefaultOptimizerMetrics()] == [M.L2Error, M.WallclockTime]
+    assert [type(m) for m in DefaultTrainingMetrics()] == [M.TrainingAccuracy, M.TestAccuracy]
+    out = io.StringIO()
+    ev = DefaultTrainerEvents(1, out)
+    assert len(ev) == 1 and isinstance(ev[0], E.TerminalBarEvent)
+    tr, _ = _trainer()
+    tr.run_loop(1, ev)
+    assert "epoch 0: loss" in out.getvalue()
