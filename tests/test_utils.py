@@ -240,3 +240,32 @@ def test_end_barrier_is_a_no_op_outside_a_process_group():
     from eagersgd_b200.utils.launch import end_barrier, rank_env
     end_barrier()                                               # no group: returns at once
     assert rank_env()["world"] >= 1
+
+
+def test_every_name_the_migration_guide_gives_can_be_imported():
+    """docs/migrating.md maps the reference's names to this package's: each dotted ``eagersgd_b200...`` name in it exists,
+    and so does every ``rt_`` function it names in the C header."""
+    import importlib
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "docs", "migrating.md")).read()
+    names = sorted(set(re.findall(r"`(eagersgd_b200(?:\.[A-Za-z_][A-Za-z_0-9]*)+)", text)))
+    assert len(names) > 25
+    for n in names:
+        parts = n.split(".")
+        for k in range(len(parts), 0, -1):
+            try:
+                obj = importlib.import_module(".".join(parts[:k]))
+                break
+            except ImportError:
+                continue
+        for a in parts[k:]:
+            assert hasattr(obj, a), n
+            obj = getattr(obj, a)
+    header = open(os.path.join(root, "eagersgd_b200", "csrc", "host", "oprt.h")).read()
+    for fn in sorted(set(re.findall(r"`(rt_[a-z_]+)", text))):
+        if fn.endswith("_"):
+            assert fn in header, fn                              # a prefix such as rt_schedule_
+        else:
+            assert re.search(r"\b%s\w*\(" % fn, header), fn
