@@ -1095,6 +1095,7 @@ struct Partial {
   std::mutex mu;
   bool fresh = false;      // the stage holds a contribution that no round has taken yet
   int64_t posts = 0, posted_by_user = 0, started = 0, begun = 0, done = 0, queued = 0;
+  int64_t token_wish = -1;   // newest round a peer's token has asked for
   bool running = false;
   int64_t activated = 0, late = 0, sync_rounds = 0, overwritten = 0, last_contributors = 0, last_round = -1;
 
@@ -1131,13 +1132,20 @@ void fill_neutral(void* p, int64_t n, int dtype, int oper) {
 }
 
 // Ask for every round up to j.  Returns how many times cb_begin has to be posted now (0 or 1).  Called with st->mu held.
-int request_upto_locked(Partial* st, int64_t j) {
+// `own_post`: the request comes from this rank's post of round j.  A token from a peer never takes a rank across a
+// synchronous round that the rank has not posted itself (a peer that posts ahead without waiting could send one): what
+// the token asked for is remembered and granted when the rank's own post has begun that round.
+int request_upto_locked(Partial* st, int64_t j, bool own_post) {
   int post_now = 0;
+  if (!own_post && j > st->token_wish) st->token_wish = j;
   while (st->started <= j) {
+    // a synchronous round begins on a rank with that rank's own post of this very round, and with nothing else
+    if (st->is_sync(st->started) && !(own_post && st->started == j)) break;
     st->started++;
     if (st->running) st->queued++;
     else { st->running = true; post_now = 1; }
   }
+  if (own_post && st->token_wish >= st->started) post_now |= request_upto_locked(st, st->token_wish, false);
   return post_now;
 }
 
@@ -1152,11 +1160,11 @@ void partial_on_post(rt_op, void* arg) {
     j = st->posts++;
     const bool sync = st->is_sync(j);
     if (st->started <= j) {
-      if (sync) post_now = request_upto_locked(st, j);
+      if (sync) post_now = request_upto_locked(st, j, true);
       else if (st->mode == 0 || st->activator(j) == st->c->id) {
         activate = true;
         st->activated++;
-        post_now = request_upto_locked(st, j);
+        post_now = request_upto_locked(st, j, true);
       }
     } else if (!sync) {
       st->late++;
@@ -1177,7 +1185,7 @@ void partial_on_token(rt_op, void* arg) {
   int post_now = 0;
   {
     std::lock_guard<std::mutex> g(st->mu);
-    if (t >= st->started) post_now = request_upto_locked(st, t);
+    if (t >= st->started) post_now = request_upto_locked(st, t, false);
   }
   if (post_now) rt_op_post(st->c, st->cb_begin);
 }

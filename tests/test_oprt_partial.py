@@ -379,3 +379,40 @@ def test_several_collectives_side_by_side_on_balanced_ranks(kind):
                 assert r.partial_info(s)["rounds"] == iters
                 r.schedule_delete(s)
         _run(w, body)
+
+
+def test_a_rank_that_posts_ahead_cannot_pull_others_across_a_synchronous_round():
+    """Rank 0 posts four rounds without waiting in between (limiter 1: rounds 1 and 3 are synchronous).  Its token for
+    round 2 reaches rank 1 before rank 1 has posted round 1; rank 1 must not begin rounds 1 and 2 on the token's word —
+    round 1 has to contain rank 1's own contribution."""
+    log = [[], []]
+    with R.World(2) as w:
+        gate = threading.Barrier(2)
+
+        def body(r):
+            snd, rcv = np.full(4, 1 << r.id, dtype=np.int32), np.zeros(4, dtype=np.int32)
+            s = r.solo_allreduce(r.buffer(snd), r.buffer(rcv), tag=6, limiter=1)
+            settled = _observe(r, s, rcv, log[r.id])
+            r.schedule_start(s)
+            gate.wait()
+            if r.id == 0:
+                for _ in range(4):
+                    assert r.schedule_post(s) == R.SUCCESS
+                time.sleep(0.05)                                # rank 1 has seen whatever tokens there are
+                gate.wait()
+                for _ in range(4):
+                    assert r.schedule_wait(s, 20.0) == R.SUCCESS
+            else:
+                gate.wait()
+                assert r.partial_info(s)["rounds"] == 1         # round 0 ran on the token; round 1 waits for the post
+                for _ in range(4):
+                    r.schedule_post(s)
+                    assert r.schedule_wait(s, 20.0) == R.SUCCESS
+            settled(4)
+            gate.wait()
+            r.schedule_delete(s)
+        _run(w, body)
+    assert [e[:2] for e in log[0]] == [e[:2] for e in log[1]]
+    values = [e[1] for e in log[0]]
+    assert values[1] & 2 and values[3] & 2, log[0]               # rank 1 is in both synchronous rounds
+    # (rank 0's four posts came faster than the rounds could take them: some of its contributions replaced each other)
