@@ -13,7 +13,7 @@ train/     trainer, events, metrics, flags, imbalance injectors, command-line ma
 ckpt/      checkpoints in the tf-models ResNet variable layout, rank-0 re-sync
 ref/       CPU oracles (numpy / C++) for every kernel
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from .parallel.group import Group, init, finalize, rank, world_size  # noqa: F401
 from .parallel.partial_allreduce import PartialAllreduce  # noqa: F401
