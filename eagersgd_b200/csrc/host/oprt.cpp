@@ -1199,6 +1199,12 @@ void partial_on_begin(rt_op, void* arg) {
   std::lock_guard<std::mutex> g(st->mu);
   const int64_t round = st->begun++;
   if (st->is_sync(round)) st->sync_rounds++;
+  if (st->options & RT_PARTIAL_LIVE) {                 // the reference's way: whatever the send buffer holds right now
+    memcpy(rt_buffer_data(st->c, st->work), rt_buffer_data(st->c, st->snd), bytes);
+    *flag = st->fresh ? 1 : 0;
+    st->fresh = false;
+    return;
+  }
   if (st->fresh && !keeps_last) {
     // the staged contribution becomes the round's working vector by exchanging the two buffers' storage: the
     // stage is rewritten by the next post anyway
@@ -1253,6 +1259,10 @@ int partial_post(rt_rank* c, rt_sched s) {
   Partial* st = (Partial*)rt_schedule_get_state(c, s);
   if (!st || !st->started_flag) return RT_ERROR;
   const void* snd = rt_buffer_data(c, st->snd);
+  if (st->options & RT_PARTIAL_LIVE) {                   // nothing is copied here: rounds read the send buffer themselves
+    { std::lock_guard<std::mutex> g(st->mu); st->fresh = true; st->posted_by_user++; }
+    return rt_op_post(c, st->cb_post);
+  }
   {
     std::lock_guard<std::mutex> g(st->mu);
     void* stage = rt_buffer_data(c, st->stage);          // under the lock: a round that begins exchanges stage and work

@@ -53,6 +53,9 @@ enum { RT_SUM = 0, RT_PROD = 1, RT_MAX = 2, RT_MIN = 3, RT_IDENTITY = 4, RT_CUST
                                         neutral element, so that only fresh contributions count */
 #define RT_PARTIAL_ACCUMULATE 0x1000 /* a contribution that no round has taken yet is combined with the next one instead of
                                         being replaced by it: nothing a rank posts is lost */
+#define RT_PARTIAL_LIVE 0x2000       /* a round reads the send buffer at the moment it begins on the rank, posted or not, and
+                                        post copies nothing: exactly the reference's semantics (the caller must not write the
+                                        buffer while a round may begin, and clears it itself if a contribution is to count once) */
 /* Buffers are always handles into the rank's table (the reference's FFBUFFER_IDX); a handle made around user memory
  * is its FFBUFFER_PTR, and every collective takes handles, so user-managed buffers (FFCOLL_BUFFERS) are the rule. */
 #define RT_INPLACE ((int64_t)-2)

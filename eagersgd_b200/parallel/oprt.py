@@ -23,7 +23,7 @@ OPERATOR = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_
 SCHED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64)
 SCHED_WAIT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_double)
 DEP_IGNORE_VERSION, DEP_NO_AUTOPOST, DEP_CONSTRAINED, DEP_SKIP_OLD_VERSIONS = 0x10, 0x20, 0x40, 0x80
-PARTIAL_STALE, PARTIAL_ACCUMULATE = 0x800, 0x1000
+PARTIAL_STALE, PARTIAL_ACCUMULATE, PARTIAL_LIVE = 0x800, 0x1000, 0x2000
 NONE = -1
 
 _lib = None

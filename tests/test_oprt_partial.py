@@ -416,3 +416,86 @@ def test_a_rank_that_posts_ahead_cannot_pull_others_across_a_synchronous_round()
     values = [e[1] for e in log[0]]
     assert values[1] & 2 and values[3] & 2, log[0]               # rank 1 is in both synchronous rounds
     # (rank 0's four posts came faster than the rounds could take them: some of its contributions replaced each other)
+
+
+@pytest.mark.parametrize("kind,world", [("solo", 2), ("solo", 3), ("solo", 5), ("majority", 4)])
+def test_fenced_rounds_equal_a_full_allreduce(kind, world):
+    """evaluation/solo_allreduce_correctness.c and rand_allreduce_correctness.c: every rank increments its vector, then
+    barrier, post, wait, barrier; with the rounds fenced like this everybody's data is in every round, so the result
+    must equal a plain allreduce of the vectors.  PARTIAL_LIVE gives the reference's semantics (a round reads the send
+    buffer when it begins); without it the same holds once the rounds are counted together with what a late post left
+    for the next one, which is what the last, synchronous round shows."""
+    iters, n = 21, 19
+    with R.World(world) as w:
+        fence = threading.Barrier(world)
+
+        def body(r):
+            to_reduce, reduced, res = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+            make = r.solo_allreduce if kind == "solo" else (lambda *a, **k: r.rand_allreduce(*a, seed=34495645 % (2 ** 31), **k))
+            s = make(r.buffer(to_reduce), r.buffer(reduced), tag=0, limiter=20, options=R.PARTIAL_LIVE)
+            r.schedule_start(s)
+            for it in range(iters):
+                to_reduce += 1
+                fence.wait()
+                r.schedule_post(s)
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                fence.wait()
+                k, rnd = r.partial_read(s, res)
+                assert rnd == it and np.all(res == world * (it + 1)), (r.id, it, rnd, res[:3])
+                assert np.array_equal(reduced, res)
+                fence.wait()
+            info = r.partial_info(s)
+            assert info["rounds"] == iters and info["sync_rounds"] == 1
+            r.schedule_delete(s)
+        _run(w, body)
+
+
+@pytest.mark.parametrize("kind", ["solo", "majority"])
+def test_three_imbalance_regimes_keep_every_contribution(kind):
+    """evaluation/ssgd_synch_send.c, rsgd_synch_send.c and their _recv twins: a balanced phase, a phase in which two
+    ranks drawn anew in every iteration sleep, and a phase in which ranks 0 and 1 always sleep.  Those programs print
+    the reduced arrays for the reader to judge; here the invariants are asserted: every rank runs every round and sees
+    the same rounds; with accumulation on, the rounds up to each synchronous one hold every post made until then exactly
+    once; and in the constant phase the ranks that are never late do not wait for the two that always are (solo)."""
+    world, per_phase, limiter, nap = 4, 12, 5, 0.004               # 36 rounds; 5, 11, 17, ... are synchronous
+    steps = 3 * per_phase
+    rng = np.random.RandomState(6545343 % (2 ** 31))
+    sleepers = [set()] * per_phase + [set(rng.choice(world, 2, replace=False).tolist()) for _ in range(per_phase)] + \
+               [{0, 1}] * per_phase
+    logs = [[] for _ in range(world)]
+    waits = np.zeros((world, 3))
+    with R.World(world) as w:
+        gate = threading.Barrier(world)
+
+        def body(r):
+            snd, rcv = np.full(8, 1 << (8 * r.id), dtype=np.int64), np.zeros(8, dtype=np.int64)   # a byte per rank
+            opts = dict(tag=0, limiter=limiter, options=R.PARTIAL_ACCUMULATE)
+            s = r.solo_allreduce(r.buffer(snd), r.buffer(rcv), **opts) if kind == "solo" else \
+                r.rand_allreduce(r.buffer(snd), r.buffer(rcv), seed=6545343 % (2 ** 31), **opts)
+            settled = _observe(r, s, rcv, logs[r.id])
+            r.schedule_start(s)
+            gate.wait()
+            for it in range(steps):
+                if r.id in sleepers[it]:
+                    time.sleep(nap)
+                r.schedule_post(s)
+                t0 = time.perf_counter()
+                assert r.schedule_wait(s, 20.0) == R.SUCCESS
+                waits[r.id, it // per_phase] += time.perf_counter() - t0
+            settled(steps)
+            gate.wait()
+            info = r.partial_info(s)
+            assert info["rounds"] == steps and info["overwritten"] == 0 and info["pending"] == 0
+            r.schedule_delete(s)
+        _run(w, body)
+    for q in range(1, world):
+        assert logs[q] == logs[0]                                   # every rank saw the same rounds
+    total = 0
+    for rnd, value, k in logs[0]:
+        total += value
+        if rnd % (limiter + 1) == limiter:                          # a synchronous round: everybody has posted rnd + 1 times
+            assert k == world
+            assert [(total >> (8 * q)) & 0xff for q in range(world)] == [rnd + 1] * world, (rnd, hex(total))
+    if kind == "solo":
+        # ranks 2 and 3 are never late in the constant phase; they wait only in its two synchronous rounds
+        assert waits[2:, 2].max() < 2 * (limiter + 1) * nap + 0.25 * per_phase * nap + 0.05, waits
