@@ -1,5 +1,6 @@
 """Batch transformations applied by samplers (deep500/frameworks/reference/augmentation.py:10-204):
-ReplicateBatch, Crop (random / centre, with padding), Resize, Normalize, RandomFlip, Cutout.
+ReplicateBatch, Crop (random / centre, with padding), Resize, Normalize, RandomFlip, Cutout, and the per-image
+standardisation plus the CIFAR-10 recipe of the reference's main program.
 Batches are dicts of numpy arrays with images in NCHW under ``data_node``."""
 from __future__ import annotations
 
@@ -108,3 +109,30 @@ class Cutout(_Transform):
             x0, x1 = max(0, cx - self.length // 2), min(w, cx + self.length // 2)
             out[i, :, y0:y1, x0:x1] = 0
         return out
+
+
+
+class PerImageStandardization(_Transform):
+    """(x - mean) / max(std, 1 / sqrt(elements)) over each image by itself — ``tf.image.per_image_standardization``,
+    the last step of the reference's CIFAR-10 pipeline (official/resnet/cifar10_main.py:119-121)."""
+
+    def apply(self, x):
+        x = x.astype(np.float32, copy=False)
+        flat = x.reshape(x.shape[0], -1)
+        mean = flat.mean(axis=1)
+        std = np.maximum(flat.std(axis=1), np.float32(1.0 / np.sqrt(flat.shape[1])))     # a float64 scalar would widen the batch
+        shape = (-1,) + (1,) * (x.ndim - 1)
+        return (x - mean.reshape(shape)) / std.reshape(shape)
+
+
+def cifar10_transforms(is_training: bool, seed: Optional[int] = None, batchaug: int = 1, data_node: str = "x"):
+    """The reference's CIFAR-10 input pipeline as a list of batch transformations: for training every image is padded
+    by four pixels on each side, cropped back to 32 x 32 at a random offset and flipped with probability one half, then
+    standardised by itself; for evaluation only the last step (official/resnet/cifar10_main.py:97-125).  With
+    ``batchaug`` M every sample first appears M times, so that each copy gets its own crop and flip (:86-92)."""
+    kw = dict(data_node=data_node)
+    if not is_training:
+        return [PerImageStandardization(**kw)]
+    head = [ReplicateBatch(batchaug, **kw)] if batchaug and batchaug > 1 else []
+    return head + [Crop((32, 32), random_crop=True, padding=(4, 4), seed=seed, **kw),
+                   RandomFlip(seed=None if seed is None else seed + 1, **kw), PerImageStandardization(**kw)]

@@ -125,16 +125,38 @@ def collate_sequences(seqs: List[np.ndarray], labels: np.ndarray) -> Dict[str, n
 
 
 def load_cifar10(path: str):
-    """CIFAR-10 python batches from a local directory (no download): returns train/test NumpyDatasets."""
+    """CIFAR-10 from a local directory (no download): returns train / test ``NumpyDataset``s of float32 images in
+    [0, 1], NCHW, with int64 labels.  Both published forms are read: the binary one the reference's main program uses
+    (``cifar-10-batches-bin/data_batch_{1..5}.bin`` and ``test_batch.bin``, records of one label byte followed by
+    3 x 32 x 32 pixel bytes, channel-major: official/resnet/cifar10_main.py:33-95) and the pickled "python" one
+    (``cifar-10-batches-py/data_batch_{1..5}``, ``test_batch``).  ``path`` is the directory with the batch files or
+    the one that holds the ``cifar-10-batches-*`` folder."""
     import pickle
 
-    def _read(fn):
+    for sub in ("", "cifar-10-batches-bin", "cifar-10-batches-py"):
+        d = os.path.join(path, sub)
+        if os.path.exists(os.path.join(d, "data_batch_1.bin")) or os.path.exists(os.path.join(d, "data_batch_1")):
+            path = d
+            break
+    else:
+        raise FileNotFoundError("no CIFAR-10 batch files (data_batch_1.bin or data_batch_1) under %s" % path)
+
+    def _read_bin(fn):
+        raw = np.fromfile(os.path.join(path, fn), dtype=np.uint8)
+        if raw.size % 3073:
+            raise ValueError("%s is not a sequence of 3073-byte CIFAR-10 records" % fn)
+        rec = raw.reshape(-1, 3073)
+        return rec[:, 1:].reshape(-1, 3, 32, 32).astype(np.float32) / 255.0, rec[:, 0].astype(np.int64)
+
+    def _read_py(fn):
         with open(os.path.join(path, fn), "rb") as f:
             d = pickle.load(f, encoding="bytes")
         return d[b"data"].reshape(-1, 3, 32, 32).astype(np.float32) / 255.0, np.asarray(d[b"labels"], dtype=np.int64)
 
-    xs, ys = zip(*[_read("data_batch_%d" % i) for i in range(1, 6)])
-    tx, ty = _read("test_batch")
+    binary = os.path.exists(os.path.join(path, "data_batch_1.bin"))
+    read, ext = (_read_bin, ".bin") if binary else (_read_py, "")
+    xs, ys = zip(*[read("data_batch_%d%s" % (i, ext)) for i in range(1, 6)])
+    tx, ty = read("test_batch" + ext)
     return NumpyDataset(np.concatenate(xs), "x", np.concatenate(ys), "y"), NumpyDataset(tx, "x", ty, "y")
 
 

@@ -25,7 +25,8 @@ import torch
 
 from .model_helpers import past_stop_threshold
 from .. import ckpt
-from ..data import OrderedSampler, ReplicateBatch, ShuffleSampler, SyntheticImageDataset, load_cifar10, partition
+from ..data import (OrderedSampler, ReplicateBatch, ShuffleSampler, SyntheticImageDataset, cifar10_transforms, load_cifar10,
+                    partition)
 from ..models.resnet import cifar_resnet, imagenet_resnet
 from ..optim.lars import LARS, poly_rate_schedule
 from ..parallel.group import init as init_group, finalize
@@ -73,7 +74,16 @@ def build_data(args, info, group):
     workers = max(group.world // m, 1)
     shard = partition(train, min(group.rank // m, workers - 1), workers)
     seed = args.baseseed + 17 + (group.rank // m if m > 1 else 0)
-    return ShuffleSampler(shard, args.batch_size, seed=seed), OrderedSampler(val, args.batch_size)
+    train_sampler, val_sampler = ShuffleSampler(shard, args.batch_size, seed=seed), OrderedSampler(val, args.batch_size)
+    train_sampler.replicates = False
+    if args.dataset == "cifar10" and not (args.use_synthetic_data or args.data_dir is None):
+        # pad + random crop + flip + per-image standardisation; copies for batch augmentation are made before them
+        for t in cifar10_transforms(True, seed=args.baseseed + 1000 * (group.rank + 1), batchaug=args.batchaug):
+            train_sampler.add_input_transformation(t)
+        for t in cifar10_transforms(False):
+            val_sampler.add_input_transformation(t)
+        train_sampler.replicates = True
+    return train_sampler, val_sampler
 
 
 def make_injector(args, group, step_time):
@@ -158,7 +168,7 @@ def main(argv=None):
     eps_hook = ExamplesPerSecondHook(global_batch, every_n_steps=max(args.train_acc_steps, 1), warm_steps=5,
                                      metric_logger=logger if group.rank == 0 else _Quiet())
     profiler = ProfilerHook(os.path.join(args.model_dir, str(group.rank))) if "ProfilerHook" in hooks else None
-    replicate = ReplicateBatch(args.batchaug) if args.batchaug and args.batchaug > 1 else None
+    replicate = ReplicateBatch(args.batchaug) if args.batchaug and args.batchaug > 1 and not train_sampler.replicates else None
     injector = None
     t_step = None
     captured = False

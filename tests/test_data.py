@@ -1,4 +1,5 @@
 import numpy as np
+import pytest
 from eagersgd_b200 import data as D
 
 
@@ -260,3 +261,84 @@ def test_imagenet_preprocessing_over_random_image_sizes():
         assert out.min() >= -130.0 and out.max() <= 160.0          # 0..255 minus channel means of 104..124
 
     check()
+
+
+def _write_cifar10_bin(root, per_file=16, seed=0):
+    """A miniature cifar-10-batches-bin: records of one label byte and 3072 pixel bytes, channel-major."""
+    import os
+    d = os.path.join(root, "cifar-10-batches-bin")
+    os.makedirs(d, exist_ok=True)
+    rng = np.random.RandomState(seed)
+    everything = []
+    for name in ["data_batch_%d.bin" % i for i in range(1, 6)] + ["test_batch.bin"]:
+        labels = rng.randint(0, 10, size=per_file).astype(np.uint8)
+        pixels = rng.randint(0, 256, size=(per_file, 3, 32, 32)).astype(np.uint8)
+        np.concatenate([labels[:, None], pixels.reshape(per_file, -1)], axis=1).tofile(os.path.join(d, name))
+        everything.append((labels, pixels))
+    return d, everything
+
+
+def test_cifar10_binary_files_and_the_reference_pipeline(tmp_path):
+    """The binary CIFAR-10 files the reference's main program reads, and its input pipeline: pad by four, random crop,
+    random flip, per-image standardisation; copies for batch augmentation are made before the random steps
+    (official/resnet/cifar10_main.py:33-125)."""
+    import pickle
+    from eagersgd_b200.data import (OrderedSampler, PerImageStandardization, ShuffleSampler, cifar10_transforms,
+                                    load_cifar10)
+    d, files = _write_cifar10_bin(str(tmp_path))
+    for path in (str(tmp_path), d):                                 # the folder itself or its parent
+        train, test = load_cifar10(path)
+        assert len(train) == 80 and len(test) == 16
+        assert np.array_equal(train[16:32]["y"], files[1][0]) and np.allclose(train[16:32]["x"] * 255, files[1][1])
+        assert np.array_equal(test[:]["y"], files[5][0]) and test[0]["x"].shape == (3, 32, 32)
+    py = tmp_path / "py" / "cifar-10-batches-py"                    # the pickled form gives the same data
+    py.mkdir(parents=True)
+    for k, name in enumerate(["data_batch_%d" % i for i in range(1, 6)] + ["test_batch"]):
+        with open(py / name, "wb") as f:
+            pickle.dump({b"data": files[k][1].reshape(16, -1), b"labels": files[k][0].tolist()}, f)
+    train_py, _ = load_cifar10(str(tmp_path / "py"))
+    assert np.array_equal(train_py[:]["x"], train[:]["x"]) and np.array_equal(train_py[:]["y"], train[:]["y"])
+    with pytest.raises(FileNotFoundError):
+        load_cifar10(str(tmp_path / "nothing"))
+    (tmp_path / "bad").mkdir()
+    for i in range(1, 6):
+        (tmp_path / "bad" / ("data_batch_%d.bin" % i)).write_bytes(b"x" * 100)
+    with pytest.raises(ValueError, match="3073"):
+        load_cifar10(str(tmp_path / "bad"))
+    # standardisation: zero mean, unit variance per image; a constant image does not divide by zero
+    x = np.concatenate([train[:4]["x"], np.full((1, 3, 32, 32), 0.25, np.float32)])
+    z = PerImageStandardization().apply(x)
+    assert np.allclose(z[:4].reshape(4, -1).mean(1), 0, atol=1e-5) and np.allclose(z[:4].reshape(4, -1).std(1), 1, atol=1e-4)
+    assert np.all(z[4] == 0) and z.dtype == np.float32
+    # training pipeline: three copies of every sample, each with its own crop / flip of the padded image
+    s = ShuffleSampler(train, 8, seed=1)
+    for t in cifar10_transforms(True, seed=5, batchaug=3):
+        s.add_input_transformation(t)
+    b = s()
+    assert b["x"].shape == (24, 3, 32, 32) and b["x"].dtype == np.float32
+    assert b["y"].shape == (24,) and np.array_equal(b["y"][0::3], b["y"][1::3])
+    assert np.allclose(b["x"].reshape(24, -1).mean(1), 0, atol=1e-4)
+    copies = b["x"][:3]
+    assert not np.allclose(copies[0], copies[1]) or not np.allclose(copies[0], copies[2])
+    # without the last step the crop is a window of the zero-padded original, possibly mirrored
+    crop, flip = cifar10_transforms(True, seed=9)[:2]
+    one = train[:1]
+    out = flip(crop(one))["x"][0]
+    padded = np.pad(one["x"][0], ((0, 0), (4, 4), (4, 4)))
+    windows = [padded[:, t:t + 32, l:l + 32] for t in range(9) for l in range(9)]
+    assert any(np.array_equal(out, wnd) or np.array_equal(out, wnd[:, :, ::-1]) for wnd in windows)
+    # evaluation: standardisation only, order kept
+    v = OrderedSampler(test, 16)
+    for t in cifar10_transforms(False):
+        v.add_input_transformation(t)
+    e = v()
+    assert np.array_equal(e["y"], files[5][0]) and np.allclose(e["x"], PerImageStandardization().apply(test[:]["x"]))
+
+
+def test_cifar10_main_trains_from_binary_files(tmp_path):
+    from eagersgd_b200.train import resnet_main
+    _write_cifar10_bin(str(tmp_path / "data"), per_file=16)
+    rc = resnet_main.main(["--dataset", "cifar10", "--data_dir", str(tmp_path / "data"), "-rs", "8", "-bs", "8", "--train_epochs", "1",
+                           "--max_train_steps", "3", "--mode", "sync", "--dtype", "fp32", "--batchaug", "2",
+                           "--model_dir", str(tmp_path / "m"), "--train_acc_steps", "1"])
+    assert rc == 0 and (tmp_path / "m" / "0" / "checkpoint").exists()
