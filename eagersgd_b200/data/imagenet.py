@@ -97,6 +97,8 @@ class _ImageDataset(Dataset):
     data_node, label_node = "x", "y"
 
     num_parallel_calls = 1      # threads that decode and pre-process the images of one batch
+    batchaug = 1                # training batches hold every sample this many times, each copy cropped and flipped by itself
+                                # (the reference tiles the encoded image before its pre-processing: imagenet_main_eagersgd.py:149-154)
 
     def _init_common(self, is_training, size, seed, label_offset):
         self.is_training, self.size, self.label_offset = is_training, size, label_offset
@@ -111,6 +113,8 @@ class _ImageDataset(Dataset):
             return {"x": preprocess_image(decode_image(self._raw(int(index))), self.is_training, self.rng, self.size),
                     "y": self.labels[index] + self.label_offset}
         idx = list(range(*index.indices(len(self)))) if isinstance(index, slice) else list(index)
+        if self.is_training and self.batchaug > 1:
+            idx = [i for i in idx for _ in range(self.batchaug)]
         if self.num_parallel_calls > 1:       # like dataset.map(parse_record, num_parallel_calls=n) in the reference
             if self._pool is None:
                 from concurrent.futures import ThreadPoolExecutor

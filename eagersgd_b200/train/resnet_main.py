@@ -68,6 +68,7 @@ def build_data(args, info, group):
             val = ImageNetFolder(args.data_dir, "val", seed=args.baseseed)
         info["train"], info["val"] = len(train), len(val)
         train.num_parallel_calls = val.num_parallel_calls = max(int(args.num_parallel_calls), 1)
+        train.batchaug = max(int(args.batchaug), 1)      # copies are made before the random crop and flip
     # dataset.take(n // num_workers) in the reference (:94-96); with --shuffleaug M the workers are groups of M
     # consecutive ranks that share a part of the data and a shuffle seed (:82-88, :494-507)
     m = max(int(getattr(args, "shuffleaug", 1)), 1)
@@ -75,7 +76,7 @@ def build_data(args, info, group):
     shard = partition(train, min(group.rank // m, workers - 1), workers)
     seed = args.baseseed + 17 + (group.rank // m if m > 1 else 0)
     train_sampler, val_sampler = ShuffleSampler(shard, args.batch_size, seed=seed), OrderedSampler(val, args.batch_size)
-    train_sampler.replicates = False
+    train_sampler.replicates = getattr(train, "batchaug", 1) > 1      # the data set hands out the copies itself
     if args.dataset == "cifar10" and not (args.use_synthetic_data or args.data_dir is None):
         # pad + random crop + flip + per-image standardisation; copies for batch augmentation are made before them
         for t in cifar10_transforms(True, seed=args.baseseed + 1000 * (group.rank + 1), batchaug=args.batchaug):

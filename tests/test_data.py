@@ -120,6 +120,15 @@ def test_imagenet_from_disk_folder_shards_and_preprocessing(tmp_path):
     train = ImageNetFolder(root, "train", seed=3, label_offset=1)
     b = train[[0, 5, 9]]
     assert b["x"].shape == (3, 3, 224, 224) and list(b["y"]) == [1, 2, 3]          # 1001-class convention
+    train.batchaug = 3                                   # every sample three times, each copy with its own crop and flip
+    a = train[[0, 5]]
+    assert a["x"].shape == (6, 3, 224, 224) and list(a["y"]) == [1, 1, 1, 2, 2, 2]
+    assert not (np.array_equal(a["x"][0], a["x"][1]) and np.array_equal(a["x"][0], a["x"][2]))
+    train.num_parallel_calls = 2
+    assert train[[0, 5]]["x"].shape == (6, 3, 224, 224)
+    train.batchaug, train.num_parallel_calls = 1, 1
+    val.batchaug = 3
+    assert val[[0, 1]]["x"].shape == (2, 3, 224, 224)    # evaluation batches are never replicated
     rng = np.random.default_rng(0)
     for _ in range(50):
         t, l, ch, cw = random_crop_box(60, 80, rng)
@@ -341,4 +350,16 @@ def test_cifar10_main_trains_from_binary_files(tmp_path):
     rc = resnet_main.main(["--dataset", "cifar10", "--data_dir", str(tmp_path / "data"), "-rs", "8", "-bs", "8", "--train_epochs", "1",
                            "--max_train_steps", "3", "--mode", "sync", "--dtype", "fp32", "--batchaug", "2",
                            "--model_dir", str(tmp_path / "m"), "--train_acc_steps", "1"])
+    assert rc == 0 and (tmp_path / "m" / "0" / "checkpoint").exists()
+
+
+def test_imagenet_main_trains_from_a_folder_on_disk(tmp_path):
+    """The main program on ImageNet read from class folders: decode, the reference's pre-processing, batch-augmentation
+    copies made before it, a step, an evaluation pass, a checkpoint."""
+    from eagersgd_b200.data import write_synthetic_imagenet
+    from eagersgd_b200.train import resnet_main
+    root = write_synthetic_imagenet(str(tmp_path / "inet"), classes=3, per_class=4)
+    rc = resnet_main.main(["--dataset", "imagenet", "--data_dir", root, "-rs", "18", "-bs", "2", "--train_epochs", "1",
+                           "--max_train_steps", "2", "--mode", "sync", "--dtype", "fp32", "--batchaug", "2",
+                           "--num_parallel_calls", "2", "--model_dir", str(tmp_path / "m"), "--train_acc_steps", "1"])
     assert rc == 0 and (tmp_path / "m" / "0" / "checkpoint").exists()
