@@ -73,6 +73,8 @@ def define_resnet(p, default_size=50, sizes=(18, 34, 50, 101, 152, 200)):
     g.add_argument("--poly_rate", type=float, default=0.0)
     g.add_argument("--train_acc_steps", type=int, default=10)
     g.add_argument("--resync_epochs", type=int, default=10, help="re-synchronise replicas from rank 0 every N epochs")
+    g.add_argument("--weight_decay", type=float, default=None,
+                   help="L2 coefficient (default: the reference's value for the data set, 1e-4)")
     g.add_argument("--imbalance", default="none",
                    choices=["none", "sleep", "random_rank", "exponential", "constant"])
     g.add_argument("--imbalance_seconds", type=float, default=0.32)

@@ -39,8 +39,10 @@ from .schedule import cifar10_schedule, imagenet_schedule
 from .step import TrainStep
 
 DATASETS = {
-    "imagenet": dict(train=1281167, val=50000, classes=1001, shape=(3, 224, 224), wd=1e-4, default_size=50),
-    "cifar10": dict(train=50000, val=10000, classes=10, shape=(3, 32, 32), wd=2e-4, default_size=32),
+    # weight decay 1e-4 in both programs (imagenet_main_eagersgd.py:358, cifar10_main.py:242); the ImageNet objective
+    # leaves the batch-norm variables out of the L2 term, the CIFAR-10 one includes every variable (cifar10_main.py:244-250)
+    "imagenet": dict(train=1281167, val=50000, classes=1001, shape=(3, 224, 224), wd=1e-4, decay_norm=False, default_size=50),
+    "cifar10": dict(train=50000, val=10000, classes=10, shape=(3, 32, 32), wd=1e-4, decay_norm=True, default_size=32),
 }
 
 
@@ -148,11 +150,13 @@ def main(argv=None):
                                   regime=args.regime)
     else:
         lr_fn = cifar10_schedule(global_batch, info["train"])
+    wd = info["wd"] if args.weight_decay is None else args.weight_decay
     step = TrainStep(model, group, impl="ddp" if args.mode == "ddp" else "ours", mode=args.mode if args.mode != "ddp" else "sync",
                      limiter=args.limiter, bucket_mb=args.bucket_mb, lr=lr_fn(0) * args.lrmult, momentum=0.9,
-                     weight_decay=info["wd"], compute_dtype=getattr(torch, args.torch_dtype),
-                     inner_optimizer=(lambda ps, **kw: LARS(ps, lr=kw["lr"], momentum=0.9, weight_decay=info["wd"]))
-                     if args.lars else None, loss_scale=args.loss_scale, accumulate=args.accumulate)
+                     weight_decay=wd, compute_dtype=getattr(torch, args.torch_dtype),
+                     inner_optimizer=(lambda ps, **kw: LARS(ps, lr=kw["lr"], momentum=0.9, weight_decay=wd))
+                     if args.lars else None, loss_scale=args.loss_scale, accumulate=args.accumulate,
+                     decay_norm_params=info["decay_norm"])
     if args.pretrained_model_checkpoint_path:
         ckpt.import_tf_layout(step.model, args.pretrained_model_checkpoint_path, exclude=("dense",))
         if hasattr(step.opt, "refresh_master_from_params"):

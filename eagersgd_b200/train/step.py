@@ -44,7 +44,11 @@ class TrainStep:
     def __init__(self, model: nn.Module, group: Group, impl: str = "ours", mode: str = "solo", limiter: int = 32,
                  bucket_mb: float = 25.0, lr: float = 0.01, momentum: float = 0.9, weight_decay: float = 1e-4,
                  compute_dtype=torch.bfloat16, loss_fn=None, inner_optimizer=None, loss_scale: float = 1.0,
-                 accumulate: bool = False):
+                 accumulate: bool = False, decay_norm_params: bool = True):
+        """``decay_norm_params=False`` keeps weight decay off the scale and shift of the normalisation layers, as the
+        reference's ImageNet objective does (its L2 term skips every variable with 'batch_normalization' in its name,
+        resnet_run_loop_solo_imagenet_300.py:328-339; its CIFAR-10 objective includes them, cifar10_main.py:244-250):
+        the optimizer then has two parameter groups."""
         self.group, self.impl, self.device = group, impl, group.device
         self.compute_dtype = compute_dtype if self.device.type == "cuda" else torch.float32
         self.loss_scale = float(loss_scale)
@@ -59,7 +63,8 @@ class TrainStep:
                 from torch.nn.parallel import DistributedDataParallel as DDP
                 self.net = DDP(self.model, device_ids=[self.device.index] if self.device.type == "cuda" else None,
                                bucket_cap_mb=bucket_mb, gradient_as_bucket_view=True)
-            self.opt = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
+            self.opt = torch.optim.SGD(self._param_groups(self.model, weight_decay, decay_norm_params), lr=lr,
+                                       momentum=momentum, weight_decay=weight_decay)
             self.autocast = self.device.type == "cuda"
         else:
             self.model = prepare_model(model, self.device, self.compute_dtype)
@@ -67,7 +72,8 @@ class TrainStep:
             if inner_optimizer is not None:      # any torch optimizer can be wrapped (LARS, Adam, ...)
                 inner = inner_optimizer(self.model.parameters(), lr=lr)
             else:
-                inner = torch.optim.SGD(self.model.parameters(), lr=lr, momentum=momentum, weight_decay=weight_decay)
+                inner = torch.optim.SGD(self._param_groups(self.model, weight_decay, decay_norm_params), lr=lr,
+                                        momentum=momentum, weight_decay=weight_decay)
             cls = {"solo": SoloAllreduceOptimizer, "majority": MajorityAllreduceOptimizer,
                    "sync": SyncAllreduceOptimizer}[mode]
             kw = dict(bucket_mb=bucket_mb, accumulate=accumulate)
@@ -81,6 +87,18 @@ class TrainStep:
         self._xbuf = self._ybuf = None
         self._graph = None
         self.graph_kernel_launches = 0
+
+    @staticmethod
+    def _param_groups(model: nn.Module, weight_decay: float, decay_norm_params: bool):
+        """All parameters in one group, or — to keep weight decay off the normalisation layers — two."""
+        if decay_norm_params or not weight_decay:
+            return list(model.parameters())
+        norm = {id(p) for m in model.modules() if isinstance(m, nn.modules.batchnorm._BatchNorm) for p in m.parameters(recurse=False)}
+        decayed = [p for p in model.parameters() if id(p) not in norm]
+        plain = [p for p in model.parameters() if id(p) in norm]
+        if not plain:
+            return decayed
+        return [{"params": decayed}, {"params": plain, "weight_decay": 0.0}]
 
     def capture(self, x: torch.Tensor, y: torch.Tensor, warmup: int = 2) -> None:
         """Capture the whole step (forward, backward, bucketed partial allreduce with the

@@ -346,3 +346,32 @@ def test_update_rule_optimizers_follow_torch_optim_over_random_hyperparameters()
             assert torch.allclose(p, q, rtol=1e-4, atol=1e-5), (kind, (p - q).abs().max())
 
     check()
+
+
+def test_weight_decay_skips_normalisation_layers_when_asked():
+    """The reference's ImageNet objective keeps the batch-norm variables out of its L2 term
+    (resnet_run_loop_solo_imagenet_300.py:328-339), its CIFAR-10 objective includes them (cifar10_main.py:244-250).
+    With a loss that has no gradient only weight decay moves the weights, which shows who is decayed."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.models import cifar_resnet
+    from eagersgd_b200.train.resnet_main import DATASETS
+    from eagersgd_b200.train.step import TrainStep
+    assert DATASETS["imagenet"]["wd"] == DATASETS["cifar10"]["wd"] == 1e-4
+    assert DATASETS["imagenet"]["decay_norm"] is False and DATASETS["cifar10"]["decay_norm"] is True
+    x, y = torch.randn(4, 3, 32, 32), torch.zeros(4, dtype=torch.long)
+    ddp = TrainStep(cifar_resnet(8), es.Group(), impl="ddp", weight_decay=0.1, compute_dtype=torch.float32, decay_norm_params=False)
+    assert [(g["weight_decay"], len(g["params"])) for g in ddp.opt.param_groups] == [(0.1, 12), (0.0, 20)]   # the plain arm too
+    for decay_norm, impl in ((False, "ours"), (True, "ours")):
+        torch.manual_seed(0)
+        step = TrainStep(cifar_resnet(8), es.Group(), impl=impl, mode="sync", lr=0.5, momentum=0.0, weight_decay=0.1,
+                         compute_dtype=torch.float32, loss_fn=lambda out, t: out.sum() * 0.0, decay_norm_params=decay_norm)
+        bn = next(m for m in step.model.modules() if isinstance(m, torch.nn.BatchNorm2d))
+        g0, w0 = bn.weight.detach().clone(), step.model.stem.weight.detach().clone()
+        step.run_device(x, y)
+        assert torch.allclose(step.model.stem.weight, w0 * (1 - 0.5 * 0.1), atol=1e-6)       # convolutions are always decayed
+        if decay_norm:
+            assert torch.allclose(bn.weight, g0 * (1 - 0.5 * 0.1), atol=1e-6)
+        else:
+            assert torch.equal(bn.weight, g0)
+        if hasattr(step.opt, "close"):
+            step.opt.close()
