@@ -60,7 +60,8 @@ def define_resnet(p, default_size=50, sizes=(18, 34, 50, 101, 152, 200)):
     g.add_argument("--accumulate", action="store_true",
                    help="fold a gradient that no round picked up into the rank's next one (default: it is superseded, "
                         "as in the reference)")
-    g.add_argument("--baseseed", type=int, default=0)
+    g.add_argument("--baseseed", "-bse", type=int, default=1234,
+                   help="seed of the replicas' initial weights, of the data order and of the injected delays")
     g.add_argument("--shuffleaug", "-saug", type=int, default=1,
                    help="groups of this many consecutive ranks read the same samples in the same order (each with its own "
                         "augmentation); the data are divided among world / shuffleaug groups")

@@ -210,7 +210,7 @@ def test_flags_that_change_behaviour(tmp_path):
     rc = resnet_main.main(["--dataset", "cifar10", "--synthetic", "--synthetic_train_size", "8", "--resnet_size", "8",
                            "--batch_size", "4", "--max_train_steps", "2", "--train_epochs", "1", "--dtype", "fp32",
                            "--model_dir", str(tmp_path / "md"), "--fine_tune", "--batchaug", "2", "--hooks",
-                           "ExamplesPerSecondHook"])
+                           "ExamplesPerSecondHook", "--baseseed", "0"])
     assert rc == 0
     state = torch.load(str(tmp_path / "md" / "0" / "ckpt-2.pt"), weights_only=False)["model"]
     torch.manual_seed(0)
