@@ -41,8 +41,13 @@ from .step import TrainStep
 DATASETS = {
     # weight decay 1e-4 in both programs (imagenet_main_eagersgd.py:358, cifar10_main.py:242); the ImageNet objective
     # leaves the batch-norm variables out of the L2 term, the CIFAR-10 one includes every variable (cifar10_main.py:244-250)
-    "imagenet": dict(train=1281167, val=50000, classes=1001, shape=(3, 224, 224), wd=1e-4, decay_norm=False, default_size=50),
-    "cifar10": dict(train=50000, val=10000, classes=10, shape=(3, 32, 32), wd=1e-4, decay_norm=True, default_size=32),
+    # defaults when the flags are not given: ResNet-50 for 90 epochs with an evaluation after each (the reference runs them
+    # as 1 + 9 x 10 in chained jobs, daint_eagersgd_imagenet.sh:34-44); ResNet-32 for 190 epochs, evaluated every 10
+    # (cifar10_main.py:274-279)
+    "imagenet": dict(train=1281167, val=50000, classes=1001, shape=(3, 224, 224), wd=1e-4, decay_norm=False, default_size=50,
+                     train_epochs=90, epochs_between_evals=1),
+    "cifar10": dict(train=50000, val=10000, classes=10, shape=(3, 32, 32), wd=1e-4, decay_norm=True, default_size=32,
+                    train_epochs=190, epochs_between_evals=10),
 }
 
 
@@ -121,8 +126,15 @@ def main(argv=None):
     p = F.build_parser(__doc__.split("\n")[0])
     p.add_argument("--dataset", default="imagenet", choices=sorted(DATASETS))
     p.add_argument("--synthetic_train_size", type=int, default=None, help="samples per epoch of synthetic data")
+    p.set_defaults(resnet_size=None, train_epochs=None, epochs_between_evals=None)      # filled in per data set below
     args = F.resolve(p.parse_args(argv))
     info = DATASETS[args.dataset]
+    if args.resnet_size is None:
+        args.resnet_size = info["default_size"]
+    if args.train_epochs is None:
+        args.train_epochs = info["train_epochs"]
+    if args.epochs_between_evals is None:
+        args.epochs_between_evals = info["epochs_between_evals"]
     group = init_group()
     device = group.device
     torch.manual_seed(args.baseseed)      # identical initial replicas without a broadcast

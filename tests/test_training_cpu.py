@@ -375,3 +375,25 @@ def test_weight_decay_skips_normalisation_layers_when_asked():
             assert torch.equal(bn.weight, g0)
         if hasattr(step.opt, "close"):
             step.opt.close()
+
+
+def test_main_program_defaults_follow_the_data_set(monkeypatch):
+    """Without -rs / -te / -ebe the CIFAR-10 program is ResNet-32 for 190 epochs evaluated every 10
+    (cifar10_main.py:274-279), the ImageNet one ResNet-50 for 90 epochs evaluated after each."""
+    from eagersgd_b200.train import resnet_main
+    seen = {}
+
+    class Stop(Exception):
+        pass
+
+    def fake_build_model(args, info):
+        seen[args.dataset] = (args.resnet_size, args.train_epochs, args.epochs_between_evals)
+        raise Stop()
+    monkeypatch.setattr(resnet_main, "build_model", fake_build_model)
+    for ds in ("cifar10", "imagenet"):
+        with pytest.raises(Stop):
+            resnet_main.main(["--dataset", ds, "--synthetic"])
+    assert seen == {"cifar10": (32, 190, 10), "imagenet": (50, 90, 1)}
+    with pytest.raises(Stop):
+        resnet_main.main(["--dataset", "cifar10", "--synthetic", "-rs", "56", "-te", "3", "-ebe", "2"])
+    assert seen["cifar10"] == (56, 3, 2)
