@@ -201,25 +201,48 @@ class TimeAbortImmediateEvent(TrainingEvent):
             raise StopTraining("time budget used up")
 
 
-class EpochHPSchedule(TrainingEvent):
-    """Set optimizer hyper-parameters from ``schedule(epoch) -> dict`` at every epoch start."""
+class HyperparameterSchedule(TrainingEvent):
+    """Set optimizer hyper-parameters while training, once per epoch or once per step.  Each hyper-parameter is given
+    either as a function of the epoch (step) number or as a list of ``(epoch or step, value)`` pairs, which is a
+    piecewise-constant schedule: the value of the last pair whose position has been reached
+    (deep500/lv2/events/hyperparameter_schedule.py:8-63)."""
 
-    def __init__(self, **schedules: Callable[[int], float]):
-        self.schedules = schedules
+    def __init__(self, per_epoch: bool, **schedules):
+        self.per_epoch, self.step = per_epoch, 0
+        self.schedules = {}
+        for name, sch in schedules.items():
+            if callable(sch):
+                self.schedules[name] = sch
+            else:
+                pairs = sorted(((int(k), v) for k, v in sch), key=lambda kv: kv[0])
+                self.schedules[name] = (lambda pos, pairs=pairs: next((v for k, v in reversed(pairs) if pos >= k), None))
+
+    def _apply(self, optimizer, position: int):
+        for name, fn in self.schedules.items():
+            value = fn(position)
+            if value is not None:                        # a list schedule says nothing before its first position
+                optimizer.set_parameter(name, value)
 
     def before_epoch(self, epoch, runner, training_stats):
-        for name, fn in self.schedules.items():
-            runner.optimizer.set_parameter(name, fn(epoch))
-
-
-class StepHPSchedule(TrainingEvent):
-    def __init__(self, **schedules: Callable[[int], float]):
-        self.schedules, self.step = schedules, 0
+        if self.per_epoch:
+            self._apply(runner.optimizer, epoch)
 
     def before_optimizer_step(self, executor, optimizer, inputs):
-        for name, fn in self.schedules.items():
-            optimizer.set_parameter(name, fn(self.step))
-        self.step += 1
+        if not self.per_epoch:
+            self._apply(optimizer, self.step)
+            self.step += 1
+
+
+class EpochHPSchedule(HyperparameterSchedule):
+    """``EpochHPSchedule(learning_rate=lambda epoch: ...)`` or ``EpochHPSchedule(learning_rate=[(0, 0.1), (81, 0.01)])``."""
+
+    def __init__(self, **schedules):
+        super().__init__(True, **schedules)
+
+
+class StepHPSchedule(HyperparameterSchedule):
+    def __init__(self, **schedules):
+        super().__init__(False, **schedules)
 
 
 class CsvWriterEvent(TrainingEvent):

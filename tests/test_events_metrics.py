@@ -198,3 +198,26 @@ def test_default_event_and_metric_sets():
     tr, _ = _trainer()
     tr.run_loop(1, ev)
     assert "epoch 0: loss" in out.getvalue()
+
+
+def test_schedules_given_as_lists_of_positions_and_values():
+    """EpochHPSchedule(lr=[(0, 1e-1), (81, 1e-2), ...]) as the reference's recipes write it."""
+    from eagersgd_b200.train import events as E
+    seen = []
+
+    class Spy(E.TrainingEvent):
+        def after_optimizer_step(self, executor, optimizer, loss):
+            seen.append((optimizer.hyper["learning_rate"], optimizer.hyper.get("momentum")))
+
+    from eagersgd_b200.optim.base import MomentumOptimizer
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import Trainer
+    ds, tr, te = _toy()
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
+    opt = MomentumOptimizer(ex, learning_rate=1.0, momentum=0.5)
+    sched = E.EpochHPSchedule(learning_rate=[(2, 0.01), (0, 0.1), (1, 0.05)])            # any order
+    per_step = E.StepHPSchedule(momentum=[(4, 0.9)])                                        # silent before step 4
+    assert isinstance(sched, E.HyperparameterSchedule) and sched.per_epoch and not per_step.per_epoch
+    Trainer(tr, te, ex, opt).run_loop(3, [sched, per_step, Spy()])
+    assert [lr for lr, _ in seen] == [0.1] * 8 + [0.05] * 8 + [0.01] * 8
+    assert [m for _, m in seen] == [0.5] * 4 + [0.9] * 20
