@@ -35,12 +35,17 @@ class ReplicateBatch(_Transform):
 
 
 class Crop(_Transform):
-    def __init__(self, crop_size: Sequence[int], random_crop: bool = False, padding: Sequence[int] = (0, 0),
-                 fill: float = 0.0, **kw):
+    """Random or centre crop with optional constant padding; ``resize=True`` scales the crop back to the size the
+    images had (nearest neighbour).  Arguments in the reference's order (augmentation.py:64-76)."""
+
+    def __init__(self, crop_size: Sequence[int], resize: bool = False, random_crop: bool = False,
+                 padding: Optional[Sequence[int]] = None, fill: float = 0.0, **kw):
         super().__init__(**kw)
-        self.size, self.random, self.padding, self.fill = tuple(crop_size), random_crop, tuple(padding), fill
+        self.size, self.resize, self.random = tuple(crop_size), bool(resize), random_crop
+        self.padding, self.fill = tuple(padding) if padding is not None else (0, 0), fill
 
     def apply(self, x):
+        h0, w0 = x.shape[-2:]
         ph, pw = self.padding
         if ph or pw:
             x = np.pad(x, ((0, 0), (0, 0), (ph, ph), (pw, pw)), constant_values=self.fill)
@@ -53,15 +58,15 @@ class Crop(_Transform):
             else:
                 t, l = (h - ch) // 2, (w - cw) // 2
             out[i] = x[i, :, t:t + ch, l:l + cw]
-        return out
+        return Resize((h0, w0)).apply(out) if self.resize else out
 
 
 class Resize(_Transform):
-    """Nearest-neighbour resize to ``size`` (H, W)."""
+    """Nearest-neighbour resize to ``target_size`` (H, W)."""
 
-    def __init__(self, size: Sequence[int], **kw):
+    def __init__(self, target_size: Sequence[int], **kw):
         super().__init__(**kw)
-        self.size = tuple(size)
+        self.size = tuple(target_size)
 
     def apply(self, x):
         n, c, h, w = x.shape
@@ -72,44 +77,51 @@ class Resize(_Transform):
 
 
 class Normalize(_Transform):
-    def __init__(self, mean: Sequence[float], std: Sequence[float], **kw):
+    """(x - mean) / stddev per channel; a single number stands for every channel (augmentation.py:136-150)."""
+
+    def __init__(self, mean=0.0, stddev=1.0, std=None, **kw):
         super().__init__(**kw)
         self.mean = np.asarray(mean, dtype=np.float32).reshape(1, -1, 1, 1)
-        self.std = np.asarray(std, dtype=np.float32).reshape(1, -1, 1, 1)
+        self.std = np.asarray(stddev if std is None else std, dtype=np.float32).reshape(1, -1, 1, 1)
 
     def apply(self, x):
         return (x - self.mean) / self.std
 
 
 class RandomFlip(_Transform):
-    def __init__(self, prob: float = 0.5, **kw):
+    """Mirror each sample along ``axis`` (default: the last, left-right) with probability ``p``
+    (augmentation.py:152-165; there the test is inverted, so its probability is 1 - p: the same for the default)."""
+
+    def __init__(self, axis: int = -1, p: float = 0.5, **kw):
         super().__init__(**kw)
-        self.prob = prob
+        self.axis, self.prob = axis, p
 
     def apply(self, x):
         flip = self.rng.rand(x.shape[0]) < self.prob
         out = x.copy()
-        out[flip] = out[flip, :, :, ::-1]
+        axis = self.axis if self.axis < 0 else self.axis + 1          # axes are counted within one sample
+        out[flip] = np.flip(out[flip], axis=axis)
         return out
 
 
 class Cutout(_Transform):
-    """Zero one random square of side ``length`` per image."""
+    """Blank ``holes`` random squares of side ``length`` in every image (zero, or with ``random_fill`` uniform noise
+    in [-0.5, 0.5)); arguments in the reference's order (augmentation.py:167-208)."""
 
-    def __init__(self, length: int, **kw):
+    def __init__(self, holes: int = 1, length: int = 16, random_fill: bool = False, **kw):
         super().__init__(**kw)
-        self.length = length
+        self.holes, self.length, self.random_fill = holes, length, random_fill
 
     def apply(self, x):
         out = x.copy()
-        n, _, h, w = x.shape
+        n, c, h, w = x.shape
         for i in range(n):
-            cy, cx = self.rng.randint(h), self.rng.randint(w)
-            y0, y1 = max(0, cy - self.length // 2), min(h, cy + self.length // 2)
-            x0, x1 = max(0, cx - self.length // 2), min(w, cx + self.length // 2)
-            out[i, :, y0:y1, x0:x1] = 0
+            for _ in range(self.holes):
+                cy, cx = self.rng.randint(h), self.rng.randint(w)
+                y0, y1 = max(0, cy - self.length // 2), min(h, cy + self.length // 2)
+                x0, x1 = max(0, cx - self.length // 2), min(w, cx + self.length // 2)
+                out[i, :, y0:y1, x0:x1] = (self.rng.rand(c, y1 - y0, x1 - x0) - 0.5) if self.random_fill else 0
         return out
-
 
 
 class PerImageStandardization(_Transform):

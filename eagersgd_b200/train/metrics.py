@@ -120,19 +120,40 @@ class WallclockTime(TestMetric):
 
 
 class TrainingAccuracy(TestMetric):
-    def __init__(self):
+    """Accuracy on the training set.  As an event in a trainer's list it reads the epoch summaries when training ends —
+    the last epoch's value, or with ``max_acc`` the best one (deep500/lv2/validation/metrics.py:13-27); fed by hand with
+    ``update(logits, labels)`` it is the running ratio of correct predictions."""
+
+    _summaries = "train_summaries"
+
+    def __init__(self, max_acc: bool = False):
         self.correct = self.total = 0
+        self.max_acc, self.accuracy = max_acc, -1.0
 
     def update(self, logits, labels):
         self.correct += int((_np(logits).argmax(-1) == _np(labels)).sum())
         self.total += len(_np(labels))
 
+    def after_training(self, runner, training_stats):
+        values = [s.accuracy for s in getattr(training_stats, self._summaries) if s.accuracy is not None]
+        if values:
+            self.accuracy = max(values) if self.max_acc else values[-1]
+
     def measure(self, *a):
-        return self.correct / max(self.total, 1)
+        if self.total:
+            return self.correct / self.total
+        return self.accuracy if self.accuracy >= 0 else 0.0
+
+    def __getattr__(self, name):               # the other hooks of a training event: nothing to do
+        if name.startswith(("before_", "after_")):
+            return lambda *a, **k: None
+        raise AttributeError(name)
 
 
 class TestAccuracy(TrainingAccuracy):
-    pass
+    """The same over the test passes (deep500/lv2/validation/metrics.py:30-44)."""
+
+    _summaries = "test_summaries"
 
 
 class DatasetAccuracy(TestMetric):

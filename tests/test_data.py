@@ -48,10 +48,18 @@ def test_augmentations():
     assert D.Resize((16, 16))(x)["x"].shape == (6, 3, 16, 16)
     n = D.Normalize([0.5] * 3, [0.25] * 3)(x)["x"]
     assert np.allclose(n, (x["x"] - 0.5) / 0.25)
-    f = D.RandomFlip(1.0)(x)["x"]
+    assert np.allclose(D.Normalize(0.5, stddev=2.0)(x)["x"], (x["x"] - 0.5) / 2.0)          # one number for every channel
+    f = D.RandomFlip(p=1.0)(x)["x"]
     assert np.array_equal(f, x["x"][:, :, :, ::-1])
-    c = D.Cutout(8, seed=0)(x)["x"]
-    assert (c == 0).sum() > 0
+    assert np.array_equal(D.RandomFlip(1, 1.0)(x)["x"], x["x"][:, :, ::-1, :])              # axis 1 of a sample: up-down
+    assert np.array_equal(D.RandomFlip(p=0.0)(x)["x"], x["x"])
+    c = D.Cutout(1, 8, seed=0)(x)["x"]                                                     # holes, length: the reference's order
+    assert 0 < (c == 0).sum() <= 6 * 3 * 64
+    two = D.Cutout(holes=2, length=4, random_fill=True, seed=0)(x)["x"]
+    changed = (two != x["x"])
+    assert 0 < changed.sum() <= 6 * 3 * 2 * 16 and two[changed].min() >= -0.5 and two[changed].max() < 0.5
+    back = D.Crop((16, 16), resize=True)(x)["x"]                                            # centre crop scaled back up
+    assert back.shape == (6, 3, 32, 32) and np.array_equal(back[:, :, ::2, ::2], x["x"][:, :, 8:24, 8:24])
     r = D.ReplicateBatch(3)(x)
     assert r["x"].shape[0] == 18 and r["y"].tolist() == [0, 0, 0, 1, 1, 1, 2, 2, 2, 3, 3, 3, 4, 4, 4, 5, 5, 5]
 

@@ -221,3 +221,15 @@ def test_schedules_given_as_lists_of_positions_and_values():
     Trainer(tr, te, ex, opt).run_loop(3, [sched, per_step, Spy()])
     assert [lr for lr, _ in seen] == [0.1] * 8 + [0.05] * 8 + [0.01] * 8
     assert [m for _, m in seen] == [0.5] * 4 + [0.9] * 20
+
+
+def test_accuracy_metrics_as_events_read_the_summaries():
+    """TestAccuracy(max_acc=True) in a trainer's event list, as the reference's recipes use it."""
+    from eagersgd_b200.train import metrics as M
+    tr, _ = _trainer(lr=0.5)
+    last, best, train = M.TestAccuracy(), M.TestAccuracy(max_acc=True), M.TrainingAccuracy()
+    stats = tr.run_loop(3, [last, best, train])
+    accs = [s.accuracy for s in stats.test_summaries]
+    assert last.measure() == accs[-1] and best.measure() == max(accs) and best.measure() >= last.measure()
+    assert train.measure() == stats.train_summaries[-1].accuracy
+    assert M.TestAccuracy().measure() == 0.0
