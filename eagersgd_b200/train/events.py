@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import csv
 import json
+import os
 import sys
 import time
 from typing import Callable, List, Optional
@@ -246,8 +247,8 @@ class StepHPSchedule(HyperparameterSchedule):
 
 
 class CsvWriterEvent(TrainingEvent):
-    def __init__(self, path: str):
-        self.path = path
+    def __init__(self, path: str, folder: Optional[str] = None):
+        self.path = path if folder is None else os.path.join(folder, path)
 
     def after_training(self, runner, training_stats):
         with open(self.path, "w", newline="") as f:
@@ -261,8 +262,8 @@ class CsvWriterEvent(TrainingEvent):
 class LossPlotGeneratorEvent(TrainingEvent):
     """Per-step loss series of every epoch (written as JSON: no plotting library here)."""
 
-    def __init__(self, path: str):
-        self.path = path
+    def __init__(self, path: str, folder: Optional[str] = None):
+        self.path = path if folder is None else os.path.join(folder, path)
 
     def after_training(self, runner, training_stats):
         with open(self.path + ".json", "w") as f:

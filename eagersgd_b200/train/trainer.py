@@ -109,7 +109,19 @@ class Trainer:
         return stats
 
 
-def test_training(executor, training_sampler, validation_sampler, optimizer, epochs: int = 1, events=None
+def test_training(executor, training_set, validation_set, optimizer, epochs: int = 1, batch_size: int = 64,
+                  output_node: Optional[str] = None, metrics: Optional[Sequence] = None, events: Optional[Sequence] = None
                   ) -> TrainingStatistics:
-    """Train for ``epochs`` and return the statistics (deep500 ``d5.test_training``)."""
-    return Trainer(training_sampler, validation_sampler, executor, optimizer).run_loop(epochs, events)
+    """Train for ``epochs`` and return the statistics (deep500 ``d5.test_training``, lv2/validation/training.py:10-86).
+    ``training_set`` / ``validation_set`` are samplers, or data sets, which are then drawn from in shuffled (training)
+    and sequential (validation) batches of ``batch_size``.  ``metrics`` that are events (``TestAccuracy`` ...) ride along
+    with ``events``; their ``measure()`` holds the result afterwards."""
+    from ..data.sampler import OrderedSampler, ShuffleSampler
+    if isinstance(batch_size, (list, tuple)):                # the events given as the sixth positional argument
+        events, batch_size = batch_size, 64
+    if training_set is not None and not callable(training_set):
+        training_set = ShuffleSampler(training_set, batch_size)
+    if validation_set is not None and not callable(validation_set):
+        validation_set = OrderedSampler(validation_set, batch_size)
+    trainer = Trainer(training_set, validation_set, executor, optimizer, **({"output_node": output_node} if output_node else {}))
+    return trainer.run_loop(epochs, list(events or []) + [m for m in (metrics or []) if hasattr(m, "after_training")])

@@ -233,3 +233,20 @@ def test_accuracy_metrics_as_events_read_the_summaries():
     assert last.measure() == accs[-1] and best.measure() == max(accs) and best.measure() >= last.measure()
     assert train.measure() == stats.train_summaries[-1].accuracy
     assert M.TestAccuracy().measure() == 0.0
+
+
+def test_test_training_takes_data_sets_and_metrics(tmp_path):
+    """d5.test_training(executor, training_set, validation_set, optimizer, epochs, batch_size, ..., metrics, events)."""
+    from eagersgd_b200.optim.base import GradientDescent
+    from eagersgd_b200.train import events as E, metrics as M
+    from eagersgd_b200.train.executor import GraphExecutor, classification_loss
+    from eagersgd_b200.train.trainer import test_training
+    torch.manual_seed(0)
+    ds, _, _ = _toy()
+    ex = GraphExecutor(torch.nn.Linear(16, 4), classification_loss)
+    acc = M.TestAccuracy(max_acc=True)
+    stats = test_training(ex, ds, ds, GradientDescent(ex, learning_rate=0.5), epochs=2, batch_size=32, metrics=[acc],
+                          events=[E.CsvWriterEvent("run.csv", str(tmp_path)), E.LossPlotGeneratorEvent("loss", str(tmp_path))])
+    assert len(stats.train_summaries) == 2 and len(stats.train_summaries[0].losses) == 8
+    assert acc.measure() == max(s.accuracy for s in stats.test_summaries) > 0.5
+    assert (tmp_path / "run.csv").exists() and (tmp_path / "loss.json").exists()
