@@ -8,3 +8,4 @@ from .augmentation import (ReplicateBatch, Crop, Resize, Normalize, RandomFlip, 
 from .video import VideoLoader, VideoFolderDataset, read_split, write_synthetic_ucf101, UCF101_MEAN, UCF101_STD  # noqa: F401
 from .imagenet import (ImageNetFolder, ShardedImageDataset, SyntheticImageNet, build_shards, preprocess_image,  # noqa: F401
                        random_crop_box, decode_image, write_synthetic_imagenet, CHANNEL_MEANS)
+from .registry import dataset_shape, dataset_loss, load_dataset, synthetic_task  # noqa: F401

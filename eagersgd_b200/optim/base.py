@@ -9,6 +9,7 @@ The update rules run on torch tensors, on whichever device the parameters live.
 """
 from __future__ import annotations
 
+import inspect
 from typing import Callable, Dict, Optional
 
 import torch
@@ -16,11 +17,27 @@ import torch
 
 
 class Optimizer:
-    def __init__(self, executor, loss: str = "loss"):
+    def __init__(self, executor, loss: str = "loss", gradient_modifier: Optional[Callable] = None):
         self.executor, self.loss = executor, loss
         self.network = executor.network
-        self.gradient_modifier: Optional[Callable] = None   # (name, grad tensor) -> grad tensor
+        # (name, grad) -> grad, or the reference's (name, parameter, grad) -> grad (deep500/lv2/optimizer.py:16-31)
+        self.gradient_modifier = gradient_modifier
         self.hyper: Dict[str, float] = {}
+
+    def _modify(self, name: str, param, grad):
+        """The gradient a step uses: what the ``gradient_modifier`` makes of it, if there is one."""
+        fn = self.gradient_modifier
+        if fn is None:
+            return grad
+        try:
+            three = len([q for q in inspect.signature(fn).parameters.values()
+                         if q.kind in (q.POSITIONAL_ONLY, q.POSITIONAL_OR_KEYWORD)]) >= 3
+        except (TypeError, ValueError):
+            three = False
+        if not three:
+            return fn(name, grad)
+        with torch.no_grad():                   # such modifiers may update the gradient in place (grad += wd * param)
+            return fn(name, param, grad)
 
     def set_parameter(self, name: str, value, predicate=None):
         self.hyper[name] = value
@@ -49,10 +66,7 @@ class FirstOrderOptimizer(Optimizer):
         for name, p in self.executor.module.named_parameters():
             if p.grad is None:
                 continue
-            g = p.grad
-            if self.gradient_modifier is not None:
-                g = self.gradient_modifier(name, g)
-            yield name, p, g
+            yield name, p, self._modify(name, p, p.grad)
 
 
 class ThreeStepOptimizer(FirstOrderOptimizer):
@@ -81,8 +95,8 @@ UpdateRuleOptimizer = ThreeStepOptimizer
 
 
 class GradientDescent(ThreeStepOptimizer):
-    def __init__(self, executor, loss="loss", learning_rate=0.1):
-        super().__init__(executor, loss)
+    def __init__(self, executor, loss="loss", learning_rate=0.1, **kw):
+        super().__init__(executor, loss, **kw)
         self.hyper["learning_rate"] = learning_rate
 
     def update_rule(self, grad, old_param, name):
@@ -92,8 +106,8 @@ class GradientDescent(ThreeStepOptimizer):
 class MomentumOptimizer(ThreeStepOptimizer):
     """acc = m*acc + g ; p -= lr*acc (reference optimizers.py:39-46)."""
 
-    def __init__(self, executor, loss="loss", learning_rate=0.1, momentum=0.9, weight_decay=0.0):
-        super().__init__(executor, loss)
+    def __init__(self, executor, loss="loss", learning_rate=0.1, momentum=0.9, weight_decay=0.0, **kw):
+        super().__init__(executor, loss, **kw)
         self.hyper.update(learning_rate=learning_rate, momentum=momentum, weight_decay=weight_decay)
         self.acc: Dict[str, torch.Tensor] = {}
 
@@ -106,8 +120,8 @@ class MomentumOptimizer(ThreeStepOptimizer):
 
 
 class AdamOptimizer(ThreeStepOptimizer):
-    def __init__(self, executor, loss="loss", learning_rate=1e-3, beta1=0.9, beta2=0.999, epsilon=1e-8):
-        super().__init__(executor, loss)
+    def __init__(self, executor, loss="loss", learning_rate=1e-3, beta1=0.9, beta2=0.999, epsilon=1e-8, **kw):
+        super().__init__(executor, loss, **kw)
         self.hyper.update(learning_rate=learning_rate, beta1=beta1, beta2=beta2, epsilon=epsilon)
         self.t = 0
         self.m: Dict[str, torch.Tensor] = {}
@@ -128,8 +142,8 @@ class AdamOptimizer(ThreeStepOptimizer):
 
 
 class AdaGradOptimizer(ThreeStepOptimizer):
-    def __init__(self, executor, loss="loss", learning_rate=0.01, epsilon=1e-8):
-        super().__init__(executor, loss)
+    def __init__(self, executor, loss="loss", learning_rate=0.01, epsilon=1e-8, **kw):
+        super().__init__(executor, loss, **kw)
         self.hyper.update(learning_rate=learning_rate, epsilon=epsilon)
         self.sq: Dict[str, torch.Tensor] = {}
 
@@ -145,8 +159,8 @@ class RMSPropOptimizer(ThreeStepOptimizer):
     """sq = d*sq + (1-d)*g^2 ; p -= lr * g / (sqrt(sq) + eps)  (the RMSProp of the reference's
     PyTorch backend, deep500/frameworks/pytorch/pytorch_optimizers.py)."""
 
-    def __init__(self, executor, loss="loss", learning_rate=1e-3, decay=0.9, epsilon=1e-8):
-        super().__init__(executor, loss)
+    def __init__(self, executor, loss="loss", learning_rate=1e-3, decay=0.9, epsilon=1e-8, **kw):
+        super().__init__(executor, loss, **kw)
         self.hyper.update(learning_rate=learning_rate, decay=decay, epsilon=epsilon)
         self.sq: Dict[str, torch.Tensor] = {}
 
@@ -162,8 +176,8 @@ class TorchOptimizer(FirstOrderOptimizer):
     """Any ``torch.optim`` optimizer (or one of this package's eager-SGD wrappers around it)
     driven through the executor, with the ``gradient_modifier`` hook applied before the step."""
 
-    def __init__(self, executor, torch_optimizer, loss="loss"):
-        super().__init__(executor, loss)
+    def __init__(self, executor, torch_optimizer, loss="loss", **kw):
+        super().__init__(executor, loss, **kw)
         self.opt = torch_optimizer
 
     def set_parameter(self, name, value, predicate=None):

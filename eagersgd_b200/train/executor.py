@@ -137,3 +137,20 @@ def classification_loss(outputs: torch.Tensor, batch: Dict[str, torch.Tensor]) -
 
 def mse_loss(outputs: torch.Tensor, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
     return torch.nn.functional.mse_loss(outputs.float(), batch["y"].float())
+
+
+def from_model(module: nn.Module, device=None, loss_fn: Optional[Callable] = classification_loss, events=None,
+               data_node: str = "x", label_node: str = "y", **kw) -> GraphExecutor:
+    """An executor around a ``torch.nn.Module`` on ``device`` (a ``torch.device``, a device descriptor of
+    ``utils.device`` or None for the GPU if there is one) — what recipes name as their ``executor``
+    (the reference's ``d5fw.from_model``, deep500/frameworks/pytorch/__init__.py)."""
+    if device is not None and not isinstance(device, torch.device):
+        device = device.torch_device() if hasattr(device, "torch_device") else torch.device(str(device))
+    if device is not None and device.type == "cuda" and not torch.cuda.is_available():
+        import warnings
+        warnings.warn("no CUDA device here: the executor runs on the CPU")
+        device = torch.device("cpu")
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    return GraphExecutor(module.to(device), loss_fn, device=device, events=events, data_node=data_node,
+                         label_node=label_node, **kw)
