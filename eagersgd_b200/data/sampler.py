@@ -167,9 +167,17 @@ class DistributedSampler(Sampler):
     """Every rank holds the whole dataset and draws its own batches with a rank-specific seed;
     an epoch is 1/world of the data (deep500/lv3/distributed_sampler.py:10-40)."""
 
-    def __init__(self, sampler: Sampler, rank: int, world: int):
+    def __init__(self, sampler: Sampler, rank=None, world: Optional[int] = None):
+        """``DistributedSampler(sampler, rank, world)``, or ``DistributedSampler(sampler, group)`` with a process group
+        (anything with ``rank`` and ``world`` attributes), as the reference passes its communicator; with neither, the
+        rank and size of the running job."""
+        if rank is not None and hasattr(rank, "rank") and hasattr(rank, "world"):
+            rank, world = rank.rank, rank.world
+        elif rank is None or world is None:
+            import os
+            rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
         self.__dict__.update(sampler.__dict__)
-        self.inner, self.rank, self.world = sampler, rank, world
+        self.inner, self.rank, self.world = sampler, int(rank), int(world)
         self.inner.rng = np.random.RandomState((sampler.seed or 0) * 9973 + rank)
         if hasattr(self.inner, "_perm"):
             self.inner._perm = self.inner.rng.permutation(len(sampler.dataset))
@@ -212,7 +220,9 @@ def partition(dataset: Dataset, rank: int, world: int) -> PartitionedDataset:
 
 
 class PartitionedDistributedSampler:
-    """Each rank samples only its contiguous shard (distributed_sampler.py:100-108)."""
+    """Each rank samples only its contiguous shard (distributed_sampler.py:100-108).  ``rank`` may be a process group."""
 
-    def __new__(cls, sampler_cls, dataset: Dataset, batch_size: int, rank: int, world: int, **kw):
+    def __new__(cls, sampler_cls, dataset: Dataset, batch_size: int, rank, world: Optional[int] = None, **kw):
+        if hasattr(rank, "rank") and hasattr(rank, "world"):
+            rank, world = rank.rank, rank.world
         return sampler_cls(partition(dataset, rank, world), batch_size, **kw)

@@ -40,6 +40,14 @@ def test_partitioned_and_distributed_samplers():
         assert seen[-1].min() == r * 25 and seen[-1].max() == r * 25 + 24
     d = D.DistributedSampler(D.ShuffleSampler(ds, 5, seed=1), rank=2, world=4)
     assert len(d) == 5 and len([b for b in d]) == 5
+    import types
+    comm = types.SimpleNamespace(rank=1, world=4)                  # a process group, as the reference passes its communicator
+    g = D.DistributedSampler(D.ShuffleSampler(ds, 5, seed=1), comm)
+    assert (g.rank, g.world, len(g)) == (1, 4, 5)
+    p = D.PartitionedDistributedSampler(D.OrderedSampler, ds, 5, comm)
+    assert np.concatenate([b["y"] for b in p]).tolist() == list(range(25, 50))
+    alone = D.DistributedSampler(D.OrderedSampler(ds, 10))         # no job: one rank
+    assert (alone.rank, alone.world, len(alone)) == (0, 1, 10)
 
 
 def test_augmentations():
