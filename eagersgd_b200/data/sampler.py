@@ -222,7 +222,14 @@ def partition(dataset: Dataset, rank: int, world: int) -> PartitionedDataset:
 class PartitionedDistributedSampler:
     """Each rank samples only its contiguous shard (distributed_sampler.py:100-108).  ``rank`` may be a process group."""
 
-    def __new__(cls, sampler_cls, dataset: Dataset, batch_size: int, rank, world: Optional[int] = None, **kw):
+    def __new__(cls, sampler_cls, dataset=None, batch_size: Optional[int] = None, rank=None, world: Optional[int] = None, **kw):
+        if isinstance(sampler_cls, Sampler):
+            # the reference's form: PartitionedDistributedSampler(sampler, comm) narrows a ready sampler to the rank's shard
+            s, comm = sampler_cls, dataset
+            rank, world = (comm.rank, comm.world) if comm is not None else (0, 1)
+            s.dataset = partition(s.dataset, rank, world)
+            s.reset()                                       # a shuffled order is drawn again over the shard
+            return s
         if hasattr(rank, "rank") and hasattr(rank, "world"):
             rank, world = rank.rank, rank.world
         return sampler_cls(partition(dataset, rank, world), batch_size, **kw)

@@ -46,6 +46,9 @@ def test_partitioned_and_distributed_samplers():
     assert (g.rank, g.world, len(g)) == (1, 4, 5)
     p = D.PartitionedDistributedSampler(D.OrderedSampler, ds, 5, comm)
     assert np.concatenate([b["y"] for b in p]).tolist() == list(range(25, 50))
+    q = D.PartitionedDistributedSampler(D.ShuffleSampler(ds, 5, seed=3), comm)       # a ready sampler and a group
+    assert sorted(np.concatenate([b["y"] for b in q]).tolist()) == list(range(25, 50))
+    assert len(D.PartitionedDistributedSampler(D.OrderedSampler(ds, 10), None)) == 10  # no group: everything
     alone = D.DistributedSampler(D.OrderedSampler(ds, 10))         # no job: one rank
     assert (alone.rank, alone.world, len(alone)) == (0, 1, 10)
 

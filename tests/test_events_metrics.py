@@ -250,3 +250,28 @@ def test_test_training_takes_data_sets_and_metrics(tmp_path):
     assert len(stats.train_summaries) == 2 and len(stats.train_summaries[0].losses) == 8
     assert acc.measure() == max(s.accuracy for s in stats.test_summaries) > 0.5
     assert (tmp_path / "run.csv").exists() and (tmp_path / "loss.json").exists()
+
+
+def test_communication_volume_as_an_event_finds_the_eager_optimizer():
+    """metrics = d5.DefaultTrainingMetrics() + [d5.CommunicationVolume()] handed to test_training, as the reference's
+    distributed sample does."""
+    import eagersgd_b200 as es
+    from eagersgd_b200.ops.validation import DefaultTrainingMetrics
+    from eagersgd_b200.optim.base import TorchOptimizer
+    from eagersgd_b200.train import metrics as M
+    from eagersgd_b200.train.executor import from_model
+    from eagersgd_b200.train.trainer import test_training
+    torch.manual_seed(0)
+    ds, _, _ = _toy()
+    model = torch.nn.Linear(16, 4)
+    ex = from_model(model, torch.device("cpu"))
+    eager = es.SoloAllreduceOptimizer(torch.optim.SGD(model.parameters(), lr=0.1), es.Group())
+    try:
+        vol = M.CommunicationVolume()
+        assert vol.measure()["steps"] == 0
+        metrics = DefaultTrainingMetrics() + [vol]
+        test_training(ex, ds, ds, TorchOptimizer(ex, eager), 1, 32, metrics=metrics)
+        assert vol.opt is eager and vol.measure()["steps"] == 8 and vol.measure()["bytes_published"] > 0
+        assert 0 < metrics[1].measure() <= 1.0
+    finally:
+        eager.close()
