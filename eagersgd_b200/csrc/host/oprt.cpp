@@ -486,6 +486,12 @@ void free_op_locked(rt_rank* c, rt_op id) {
   c->free_ops.push_back(id);
 }
 
+// Handle checks (called with c->mu held): a handle that was never given out, or was given back, is refused with
+// RT_ERROR instead of being used as an index.
+inline bool ok_buf(rt_rank* c, rt_buf b) { return b >= 0 && b < (rt_buf)c->bufs.size() && c->bufs[b].alive; }
+inline bool ok_op(rt_rank* c, rt_op id) { return id >= 0 && id < (rt_op)c->ops.size() && c->ops[id] && c->ops[id]->alive; }
+inline bool ok_sched(rt_rank* c, rt_sched s) { return s >= 0 && s < (rt_sched)c->scheds.size() && c->scheds[s].alive; }
+
 }  // namespace
 
 extern "C" {
@@ -546,6 +552,7 @@ int rt_buffer_delete(rt_rank* c, rt_buf id) {
 
 int rt_buffer_resize(rt_rank* c, rt_buf id, void* user_ptr, int64_t count) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_buf(c, id) || count < 0) return RT_ERROR;
   Buffer& b = c->bufs[id];
   b.count = count;
   if (user_ptr) { b.ptr = user_ptr; b.own.clear(); }
@@ -553,8 +560,8 @@ int rt_buffer_resize(rt_rank* c, rt_buf id, void* user_ptr, int64_t count) {
   return RT_SUCCESS;
 }
 
-int64_t rt_buffer_count(rt_rank* c, rt_buf b) { std::lock_guard<std::mutex> g(c->mu); return c->bufs[b].count; }
-void* rt_buffer_data(rt_rank* c, rt_buf b) { std::lock_guard<std::mutex> g(c->mu); return c->bufs[b].data(); }
+int64_t rt_buffer_count(rt_rank* c, rt_buf b) { std::lock_guard<std::mutex> g(c->mu); return ok_buf(c, b) ? c->bufs[b].count : RT_ERROR; }
+void* rt_buffer_data(rt_rank* c, rt_buf b) { std::lock_guard<std::mutex> g(c->mu); return ok_buf(c, b) ? c->bufs[b].data() : nullptr; }
 
 rt_op rt_op_nop(rt_rank* c, int options) { return new_op(c, T_NOP, options); }
 
@@ -566,6 +573,11 @@ rt_op rt_op_callback(rt_rank* c, rt_callback_fn fn, void* arg, int options) {
 }
 
 rt_op rt_op_comp(rt_rank* c, rt_buf a, rt_buf b, rt_buf out, int oper, int options) {
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!ok_buf(c, a) || !ok_buf(c, out) || (oper != RT_IDENTITY && !ok_buf(c, b))) return RT_ERROR;
+    if (oper >= RT_CUSTOM0 && (oper - RT_CUSTOM0 >= (int)c->custom_ops.size())) return RT_ERROR;
+  }
   rt_op id = new_op(c, T_COMP, options);
   std::lock_guard<std::mutex> g(c->mu);
   Op& op = *c->ops[id];
@@ -574,6 +586,10 @@ rt_op rt_op_comp(rt_rank* c, rt_buf a, rt_buf b, rt_buf out, int oper, int optio
 }
 
 rt_op rt_op_send(rt_rank* c, rt_buf b, int peer, int tag, int options) {
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!ok_buf(c, b) || peer < 0 || peer >= c->world->n) return RT_ERROR;
+  }
   rt_op id = new_op(c, T_SEND, options);
   std::lock_guard<std::mutex> g(c->mu);
   Op& op = *c->ops[id];
@@ -582,6 +598,10 @@ rt_op rt_op_send(rt_rank* c, rt_buf b, int peer, int tag, int options) {
 }
 
 rt_op rt_op_recv(rt_rank* c, rt_buf b, int peer, int tag, int options) {
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!ok_buf(c, b) || peer < 0 || peer >= c->world->n) return RT_ERROR;
+  }
   rt_op id = new_op(c, T_RECV, options);
   std::lock_guard<std::mutex> g(c->mu);
   Op& op = *c->ops[id];
@@ -700,6 +720,7 @@ int rt_op_cancel(rt_rank* c, rt_op id) {
 
 int rt_op_wait(rt_rank* c, rt_op id, double timeout_s) {
   std::unique_lock<std::mutex> lk(c->mu);
+  if (!ok_op(c, id)) return RT_ERROR;
   Op& op = *c->ops[id];
   const int64_t want = op.waited.load() + 1;
   auto pred = [&] { return op.completed.load() >= want; };
@@ -724,12 +745,13 @@ int rt_op_wait(rt_rank* c, rt_op id, double timeout_s) {
 
 int rt_op_test(rt_rank* c, rt_op id) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_op(c, id)) return RT_ERROR;
   Op& op = *c->ops[id];
   if (op.completed.load() > op.waited.load()) { op.waited.fetch_add(1); return RT_COMPLETED; }
   return RT_SUCCESS;
 }
 
-int64_t rt_op_completions(rt_rank* c, rt_op id) { std::lock_guard<std::mutex> g(c->mu); return c->ops[id]->completed.load(); }
+int64_t rt_op_completions(rt_rank* c, rt_op id) { std::lock_guard<std::mutex> g(c->mu); return ok_op(c, id) ? c->ops[id]->completed.load() : RT_ERROR; }
 
 rt_sched rt_schedule_create(rt_rank* c) {
   rt_op b = rt_op_nop(c, 0), e = rt_op_nop(c, 0);
@@ -781,29 +803,32 @@ int rt_schedule_delete(rt_rank* c, rt_sched s) {
 
 int rt_schedule_add_part(rt_rank* c, rt_sched s, rt_sched part) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_sched(c, s) || !ok_sched(c, part) || s == part) return RT_ERROR;
   c->scheds[s].parts.push_back(part);
   return RT_SUCCESS;
 }
 
 int rt_schedule_own_buffer(rt_rank* c, rt_sched s, rt_buf b) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_sched(c, s) || !ok_buf(c, b)) return RT_ERROR;
   c->scheds[s].owned_bufs.push_back(b);
   return RT_SUCCESS;
 }
 
 int rt_schedule_set_state(rt_rank* c, rt_sched s, void* state) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_sched(c, s)) return RT_ERROR;
   c->scheds[s].state = state;
   return RT_SUCCESS;
 }
-void* rt_schedule_get_state(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return c->scheds[s].state; }
+void* rt_schedule_get_state(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return ok_sched(c, s) ? c->scheds[s].state : nullptr; }
 
-int rt_schedule_set_start_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].start_fn = f; return RT_SUCCESS; }
-int rt_schedule_set_post_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].post_fn = f; return RT_SUCCESS; }
-int rt_schedule_set_test_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].test_fn = f; return RT_SUCCESS; }
-int rt_schedule_set_delete_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].delete_fn = f; return RT_SUCCESS; }
-int rt_schedule_set_wait_fun(rt_rank* c, rt_sched s, rt_sched_wait_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].wait_fn = f; return RT_SUCCESS; }
-int rt_schedule_set_print_fun(rt_rank* c, rt_sched s, rt_sched_print_fn f) { std::lock_guard<std::mutex> g(c->mu); c->scheds[s].print_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_start_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].start_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_post_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].post_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_test_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].test_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_delete_fun(rt_rank* c, rt_sched s, rt_sched_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].delete_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_wait_fun(rt_rank* c, rt_sched s, rt_sched_wait_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].wait_fn = f; return RT_SUCCESS; }
+int rt_schedule_set_print_fun(rt_rank* c, rt_sched s, rt_sched_print_fn f) { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; c->scheds[s].print_fn = f; return RT_SUCCESS; }
 
 // The default behaviours, callable from an override (ffschedule_default_*).
 int rt_schedule_default_post(rt_rank* c, rt_sched s) {
@@ -839,13 +864,14 @@ int rt_schedule_default_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
 // ffsolo_allreduce.c:97-101).  The default does nothing.
 int rt_schedule_start(rt_rank* c, rt_sched s) {
   rt_sched_fn f;
-  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].start_fn; }
+  { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; f = c->scheds[s].start_fn; }
   rt_schedule_finalize(c, s);
   return f ? f(c, s) : RT_SUCCESS;
 }
 
 int rt_schedule_add_op(rt_rank* c, rt_sched s, rt_op op) {
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_sched(c, s) || !ok_op(c, op)) return RT_ERROR;
   c->scheds[s].ops.push_back(op);
   return RT_SUCCESS;
 }
@@ -857,6 +883,7 @@ int rt_schedule_finalize(rt_rank* c, rt_sched s) {
   rt_op b, e;
   {
     std::lock_guard<std::mutex> g(c->mu);
+    if (!ok_sched(c, s)) return RT_ERROR;
     Schedule& sc = c->scheds[s];
     if (sc.finalized) return RT_SUCCESS;
     sc.finalized = true;
@@ -872,22 +899,22 @@ int rt_schedule_finalize(rt_rank* c, rt_sched s) {
   return RT_SUCCESS;
 }
 
-rt_op rt_schedule_begin_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return c->scheds[s].begin; }
-rt_op rt_schedule_end_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return c->scheds[s].end; }
+rt_op rt_schedule_begin_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return ok_sched(c, s) ? c->scheds[s].begin : RT_NONE; }
+rt_op rt_schedule_end_op(rt_rank* c, rt_sched s) { std::lock_guard<std::mutex> g(c->mu); return ok_sched(c, s) ? c->scheds[s].end : RT_NONE; }
 
 int rt_schedule_post(rt_rank* c, rt_sched s) {
   rt_sched_fn f;
-  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].post_fn; }
+  { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; f = c->scheds[s].post_fn; }
   return f ? f(c, s) : rt_schedule_default_post(c, s);
 }
 int rt_schedule_wait(rt_rank* c, rt_sched s, double timeout_s) {
   rt_sched_wait_fn f;
-  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].wait_fn; }
+  { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; f = c->scheds[s].wait_fn; }
   return f ? f(c, s, timeout_s) : rt_schedule_default_wait(c, s, timeout_s);
 }
 int rt_schedule_test(rt_rank* c, rt_sched s) {
   rt_sched_fn f;
-  { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].test_fn; }
+  { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; f = c->scheds[s].test_fn; }
   return f ? f(c, s) : rt_schedule_default_test(c, s);
 }
 
@@ -895,7 +922,7 @@ int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
   static const char* names[] = {"nop", "callback", "comp", "send", "recv"};
   {
     rt_sched_print_fn f;
-    { std::lock_guard<std::mutex> g(c->mu); f = c->scheds[s].print_fn; }
+    { std::lock_guard<std::mutex> g(c->mu); if (!ok_sched(c, s)) return RT_ERROR; f = c->scheds[s].print_fn; }
     if (f) return f(c, s, out, cap);
   }
   std::lock_guard<std::mutex> g(c->mu);
@@ -926,6 +953,7 @@ int rt_schedule_print(rt_rank* c, rt_sched s, char* out, int64_t cap) {
 int rt_schedule_print_visjs(rt_rank* c, rt_sched s, char* out, int64_t cap) {
   static const char* names[] = {"nop", "callback", "comp", "send", "recv"};
   std::lock_guard<std::mutex> g(c->mu);
+  if (!ok_sched(c, s)) return RT_ERROR;
   Schedule& sc = c->scheds[s];
   std::vector<rt_op> all = sc.ops;
   all.push_back(sc.begin);
@@ -954,6 +982,10 @@ int rt_schedule_print_visjs(rt_rank* c, rt_sched s, char* out, int64_t cap) {
 // partner, the power-of-two core exchanges in log2 rounds, and the result is sent back.
 rt_sched rt_allreduce(rt_rank* c, rt_buf snd, rt_buf rcv, int tag, int oper) {
   const int P = c->world->n, me = c->id;
+  {
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!ok_buf(c, rcv) || (snd != RT_INPLACE && !ok_buf(c, snd))) return RT_ERROR;
+  }
   rt_sched s = rt_schedule_create(c);
   int p2 = 1;
   while (p2 * 2 <= P) p2 *= 2;

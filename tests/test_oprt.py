@@ -615,3 +615,32 @@ def test_activation_feeds_a_computation_on_every_rank():
             assert acc[0] == len(activators) and r.completions(add) == len(activators)
         gate = threading.Barrier(world)
         _run(w, body)
+
+
+def test_handles_that_were_never_given_out_are_refused():
+    """Every entry point checks the handles it is given: a stale or made-up one gets RT_ERROR (or a null pointer),
+    never an out-of-range index."""
+    import ctypes as C
+    with R.World(2) as w:
+        r, L = w.ranks[0], R.lib()
+        x = np.zeros(4, dtype=np.int32)
+        b = r.buffer(x)
+        assert L.rt_buffer_count(r.h, 99) == R.ERROR and L.rt_buffer_data(r.h, -5) is None
+        assert L.rt_buffer_resize(r.h, 99, None, 4) == R.ERROR and r.buffer_delete(99) == R.ERROR
+        assert r.send(99, 1, 0) == R.ERROR and r.recv(b, 7, 0) == R.ERROR and r.recv(b, -1, 0) == R.ERROR
+        assert r.comp(b, 99, b) == R.ERROR and r.comp(b, b, b, R.CUSTOM0 + 3 if hasattr(R, "CUSTOM0") else 19) == R.ERROR
+        assert r.comp(b, R.NONE, b, R.IDENTITY) >= 0                   # the second input of a copy may be absent
+        assert r.allreduce(99, b, 0) == R.ERROR and r.allreduce(R.INPLACE, 99, 0) == R.ERROR
+        assert r.solo_allreduce(b, 99, 0) == R.ERROR
+        for bad in (-1, 10 ** 6):
+            assert r.post(bad) == R.ERROR and r.wait(bad, 0.1) == R.ERROR and r.test(bad) == R.ERROR
+            assert r.completions(bad) == R.ERROR and r.cancel(bad) == R.ERROR and r.free(bad) == R.ERROR
+            assert r.schedule_post(bad) == R.ERROR and r.schedule_wait(bad, 0.1) == R.ERROR and r.schedule_test(bad) == R.ERROR
+            assert r.schedule_start(bad) == R.ERROR and r.schedule_delete(bad) == R.ERROR and r.schedule_end(bad) == R.NONE
+            assert r.schedule_dot(bad) == "" and r.schedule_visjs(bad) == {}
+        s = r.schedule()
+        n = r.nop()
+        assert r.schedule_add(s, 10 ** 6) == R.ERROR and r.schedule_add(s, n) == R.SUCCESS
+        assert r.schedule_add_part(s, s) == R.ERROR and r.schedule_add_part(s, 123) == R.ERROR
+        assert r.free(n) == R.SUCCESS and r.post(n) == R.ERROR and r.wait(n, 0.1) == R.ERROR       # freed: stale
+        assert r.schedule_delete(s) == R.SUCCESS and r.schedule_post(s) == R.ERROR
