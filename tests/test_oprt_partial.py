@@ -499,3 +499,21 @@ def test_three_imbalance_regimes_keep_every_contribution(kind):
     if kind == "solo":
         # ranks 2 and 3 are never late in the constant phase; they wait only in its two synchronous rounds
         assert waits[2:, 2].max() < 2 * (limiter + 1) * nap + 0.25 * per_phase * nap + 0.05, waits
+
+
+@pytest.mark.parametrize("kind", ["solo", "majority"])
+def test_a_world_of_one_rank(kind):
+    with R.World(1) as w:
+        r = w.ranks[0]
+        x, y, res = np.arange(5, dtype=np.float64), np.zeros(5), np.zeros(5)
+        s = r.solo_allreduce(r.buffer(x), r.buffer(y), 0, limiter=2) if kind == "solo" else \
+            r.rand_allreduce(r.buffer(x), r.buffer(y), 0, seed=1, limiter=2)
+        r.schedule_start(s)
+        for it in range(7):
+            x[:] = np.arange(5) + it
+            assert r.schedule_post(s) == R.SUCCESS and r.schedule_wait(s, 5.0) == R.SUCCESS
+            k, rnd = r.partial_read(s, res)
+            assert (k, rnd) == (1, it) and np.array_equal(res, np.arange(5) + it)
+        i = r.partial_info(s)
+        assert (i["rounds"], i["sync_rounds"], i["late"], i["pending"]) == (7, 2, 0, 0)
+        assert r.schedule_delete(s) == R.SUCCESS
