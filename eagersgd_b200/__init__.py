@@ -19,3 +19,13 @@ from .parallel.group import Group, init, finalize, rank, world_size  # noqa: F40
 from .parallel.partial_allreduce import PartialAllreduce  # noqa: F401
 from .optim.eager import (EagerOptimizer, SoloAllreduceOptimizer, MajorityAllreduceOptimizer,  # noqa: F401
                           SyncAllreduceOptimizer)
+
+_SUBPACKAGES = ("train", "data", "models", "optim", "ops", "graph", "ckpt", "utils", "recipes", "parallel", "ref")
+
+
+def __getattr__(name):
+    """``import eagersgd_b200 as es; es.train.prepare_model(...)``: sub-packages are imported when first asked for."""
+    if name in _SUBPACKAGES:
+        import importlib
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

@@ -269,3 +269,18 @@ def test_every_name_the_migration_guide_gives_can_be_imported():
             assert fn in header, fn                              # a prefix such as rt_schedule_
         else:
             assert re.search(r"\b%s\w*\(" % fn, header), fn
+
+
+def test_the_readme_snippet_names_resolve():
+    """``import eagersgd_b200 as es`` alone gives access to the sub-packages the README uses."""
+    import subprocess
+    import sys
+    code = ("import eagersgd_b200 as es\n"
+            "assert callable(es.train.prepare_model) and callable(es.data.ShuffleSampler) and callable(es.models.create_model)\n"
+            "assert callable(es.SoloAllreduceOptimizer) and callable(es.PartialAllreduce) and callable(es.init)\n"
+            "assert callable(es.graph.load_onnx) and callable(es.ckpt.save) and callable(es.recipes.run_recipe)\n"
+            "try:\n    es.no_such_thing\nexcept AttributeError:\n    print('ok')\n")
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-2000:]
