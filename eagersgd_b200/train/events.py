@@ -61,6 +61,13 @@ class EpochSummary:
     def mean_loss(self):
         return sum(self.losses) / max(len(self.losses), 1)
 
+    def to_dict(self) -> dict:
+        """One row of the statistics table, with the reference's column names (deep500/lv2/summaries.py:28-39)."""
+        inf = self.time_used_inference
+        return {"epoch": self.epoch, "avg_loss": self.mean_loss, "accuracy": self.accuracy, "n_batches": len(self.losses),
+                "avg_time_inference": sum(inf) / len(inf) if inf else 0.0, "train": self.training, "time_used": self.time,
+                "lr": self.lr}
+
 
 class TrainingStatistics:
     def __init__(self):
@@ -70,6 +77,21 @@ class TrainingStatistics:
 
     def current_summary(self, training=True) -> EpochSummary:
         return (self.train_summaries if training else self.test_summaries)[-1]
+
+    def clear(self) -> None:
+        self.train_summaries, self.test_summaries = [], []
+        self.start_time = time.time()
+
+    def to_dict(self):
+        """(training rows, test rows): every epoch's ``EpochSummary.to_dict()`` plus ``total_used_time``, the time of
+        all epochs up to and including it (deep500/lv2/summaries.py:54-68 builds two data frames of these rows)."""
+        def rows(summaries):
+            out, total = [], 0.0
+            for s in summaries:
+                total += s.time or 0.0
+                out.append(dict(s.to_dict(), total_used_time=total))
+            return out
+        return rows(self.train_summaries), rows(self.test_summaries)
 
     def as_dict(self) -> dict:
         conv = lambda s: {"epoch": s.epoch, "loss": s.mean_loss, "accuracy": s.accuracy, "time": s.time, "lr": s.lr}

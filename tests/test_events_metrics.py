@@ -275,3 +275,15 @@ def test_communication_volume_as_an_event_finds_the_eager_optimizer():
         assert 0 < metrics[1].measure() <= 1.0
     finally:
         eager.close()
+
+
+def test_statistics_tables():
+    tr, _ = _trainer()
+    stats = tr.run_loop(2, [])
+    train_rows, test_rows = stats.to_dict()
+    assert [r["epoch"] for r in train_rows] == [0, 1] and [r["epoch"] for r in test_rows] == [-1, 0, 1]
+    assert train_rows[0]["n_batches"] == 8 and train_rows[0]["train"] and not test_rows[0]["train"]
+    assert train_rows[1]["total_used_time"] == pytest.approx(train_rows[0]["time_used"] + train_rows[1]["time_used"])
+    assert train_rows[1]["avg_loss"] == pytest.approx(stats.train_summaries[1].mean_loss)
+    stats.clear()
+    assert stats.to_dict() == ([], [])
