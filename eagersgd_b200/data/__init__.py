@@ -9,3 +9,4 @@ from .video import VideoLoader, VideoFolderDataset, read_split, write_synthetic_
 from .imagenet import (ImageNetFolder, ShardedImageDataset, SyntheticImageNet, build_shards, preprocess_image,  # noqa: F401
                        random_crop_box, decode_image, write_synthetic_imagenet, CHANNEL_MEANS)
 from .registry import dataset_shape, dataset_loss, load_dataset, synthetic_task  # noqa: F401
+from .dataset import load_cifar100, normalize_cifar, cifar_learning_rate, CIFAR_MEAN, CIFAR_STD  # noqa: F401

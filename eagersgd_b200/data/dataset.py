@@ -160,6 +160,48 @@ def load_cifar10(path: str):
     return NumpyDataset(np.concatenate(xs), "x", np.concatenate(ys), "y"), NumpyDataset(tx, "x", ty, "y")
 
 
+# channel statistics and the fast learning-rate schedule the reference ships with its CIFAR loaders
+# (deep500/datasets/cifar.py:58-78)
+CIFAR_MEAN = {"cifar10": (0.4914, 0.4822, 0.4465), "cifar100": (0.5071, 0.4867, 0.4408)}
+CIFAR_STD = {"cifar10": (0.2023, 0.1994, 0.2010), "cifar100": (0.2675, 0.2565, 0.2761)}
+
+
+def cifar_learning_rate(epoch: int, init: float = 0.1) -> float:
+    """init x 0.2 ^ k with k = 1, 2, 3 after epochs 60, 120, 160."""
+    return init * 0.2 ** sum(epoch > e for e in (60, 120, 160))
+
+
+def normalize_cifar(ds: "NumpyDataset", name: str = "cifar10") -> "NumpyDataset":
+    """Subtract the data set's channel means and divide by its channel deviations (images in [0, 1])."""
+    mean = np.asarray(CIFAR_MEAN[name], dtype=np.float32).reshape(1, 3, 1, 1)
+    std = np.asarray(CIFAR_STD[name], dtype=np.float32).reshape(1, 3, 1, 1)
+    both = ds[:]
+    return NumpyDataset((both[ds.data_node] - mean) / std, ds.data_node, both[ds.label_node], ds.label_node)
+
+
+def load_cifar100(path: str):
+    """CIFAR-100 in its binary form (``cifar-100-binary/train.bin``, ``test.bin``: records of a coarse-label byte, a
+    fine-label byte and 3 x 32 x 32 pixel bytes): train / test ``NumpyDataset``s with the fine labels
+    (deep500/datasets/cifar.py:80-116 reads the same files)."""
+    for sub in ("", "cifar-100-binary"):
+        d = os.path.join(path, sub)
+        if os.path.exists(os.path.join(d, "train.bin")):
+            path = d
+            break
+    else:
+        raise FileNotFoundError("no CIFAR-100 files (train.bin, test.bin) under %s" % path)
+
+    def _read(fn):
+        raw = np.fromfile(os.path.join(path, fn), dtype=np.uint8)
+        if raw.size % 3074:
+            raise ValueError("%s is not a sequence of 3074-byte CIFAR-100 records" % fn)
+        rec = raw.reshape(-1, 3074)
+        return rec[:, 2:].reshape(-1, 3, 32, 32).astype(np.float32) / 255.0, rec[:, 1].astype(np.int64)
+
+    (x, y), (tx, ty) = _read("train.bin"), _read("test.bin")
+    return NumpyDataset(x, "x", y, "y"), NumpyDataset(tx, "x", ty, "y")
+
+
 def load_mnist(path: str):
     """MNIST idx files from a local directory."""
     import gzip

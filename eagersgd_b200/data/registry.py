@@ -14,7 +14,7 @@ from typing import Callable, Dict, Optional, Tuple
 
 import numpy as np
 
-from .dataset import Dataset, NumpyDataset, load_cifar10, load_mnist
+from .dataset import Dataset, NumpyDataset, load_cifar10, load_cifar100, load_mnist, normalize_cifar
 
 # name -> (classes, channels, height, width)
 _SHAPES: Dict[str, Tuple[int, int, int, int]] = {
@@ -55,17 +55,21 @@ def _renamed(ds: Dataset, input_node: str, label_node: str) -> Dataset:
 
 
 def load_dataset(name: str, input_node: str = "x", label_node: str = "y", path: Optional[str] = None,
-                 synthetic_samples: int = 512, seed: int = 0, noise: float = 1.0) -> Tuple[Dataset, Dataset]:
+                 synthetic_samples: int = 512, seed: int = 0, noise: float = 1.0, normalize: bool = True
+                 ) -> Tuple[Dataset, Dataset]:
     """(training set, validation set) with the given node names.  ``path``: where the files are (CIFAR-10 batch files,
-    MNIST / Fashion-MNIST idx files, ImageNet class folders); without it, synthetic data of the right shape
+    CIFAR-100 ``train.bin`` / ``test.bin``, MNIST / Fashion-MNIST idx files, ImageNet class folders; CIFAR images are
+    normalised by the data set's channel statistics unless ``normalize=False``); without it, synthetic data of the right shape
     (``synthetic_samples`` training samples with Gaussian noise of standard deviation ``noise`` around the templates)."""
     classes, *shape = dataset_shape(name)
     if path is None:
         return (synthetic_task(classes, tuple(shape), synthetic_samples, input_node, label_node, seed=seed + 1, noise=noise),
                 synthetic_task(classes, tuple(shape), max(synthetic_samples // 4, 32), input_node, label_node, seed=seed + 2,
                                noise=noise))
-    if name == "cifar10":
-        train, test = load_cifar10(path)
+    if name in ("cifar10", "cifar100"):
+        train, test = (load_cifar10 if name == "cifar10" else load_cifar100)(path)
+        if normalize:                           # the reference's loaders normalise by the channel statistics by default
+            train, test = normalize_cifar(train, name), normalize_cifar(test, name)
     elif name in ("mnist", "fashion_mnist"):
         train, test = load_mnist(path)
     elif name == "imagenet":

@@ -382,3 +382,37 @@ def test_imagenet_main_trains_from_a_folder_on_disk(tmp_path):
                            "--max_train_steps", "2", "--mode", "sync", "--dtype", "fp32", "--batchaug", "2",
                            "--num_parallel_calls", "2", "--model_dir", str(tmp_path / "m"), "--train_acc_steps", "1"])
     assert rc == 0 and (tmp_path / "m" / "0" / "checkpoint").exists()
+
+
+def test_cifar100_files_the_registry_and_the_fast_schedule(tmp_path):
+    """CIFAR-100's binary records carry a coarse and a fine label; the registry reads either CIFAR by name and
+    normalises by the channel statistics as the reference's loaders do (deep500/datasets/cifar.py:58-128)."""
+    import os
+    d = tmp_path / "c100" / "cifar-100-binary"
+    os.makedirs(d)
+    rng = np.random.RandomState(0)
+    data = {}
+    for name, n in (("train.bin", 24), ("test.bin", 8)):
+        coarse, fine = rng.randint(0, 20, n).astype(np.uint8), rng.randint(0, 100, n).astype(np.uint8)
+        px = rng.randint(0, 256, size=(n, 3, 32, 32)).astype(np.uint8)
+        np.concatenate([coarse[:, None], fine[:, None], px.reshape(n, -1)], axis=1).tofile(d / name)
+        data[name] = (fine, px)
+    train, test = D.load_cifar100(str(tmp_path / "c100"))
+    assert len(train) == 24 and np.array_equal(train[:]["y"], data["train.bin"][0]) and np.allclose(test[:]["x"] * 255, data["test.bin"][1])
+    tr, te = D.load_dataset("cifar100", "input", "label", path=str(tmp_path / "c100"))
+    b = tr[:]
+    assert set(b) == {"input", "label"} and np.array_equal(b["label"], data["train.bin"][0])
+    mean = np.asarray(D.CIFAR_MEAN["cifar100"], np.float32).reshape(1, 3, 1, 1)
+    std = np.asarray(D.CIFAR_STD["cifar100"], np.float32).reshape(1, 3, 1, 1)
+    assert np.allclose(b["input"], (data["train.bin"][1] / 255.0 - mean) / std, atol=1e-5)
+    raw, _ = D.load_dataset("cifar100", path=str(tmp_path / "c100"), normalize=False)
+    assert raw[:]["x"].min() >= 0 and raw[:]["x"].max() <= 1
+    _write_cifar10_bin(str(tmp_path / "c10"), per_file=4)
+    t10, _ = D.load_dataset("cifar10", path=str(tmp_path / "c10"))
+    assert len(t10) == 20 and t10[:]["x"].min() < 0                   # normalised
+    assert D.dataset_shape("cifar100") == (100, 3, 32, 32) and D.dataset_shape("mnist") == (10, 1, 28, 28)
+    with pytest.raises(KeyError):
+        D.dataset_shape("svhn")
+    syn_tr, syn_te = D.load_dataset("fashion_mnist", synthetic_samples=64)
+    assert syn_tr[:]["x"].shape == (64, 1, 28, 28) and len(syn_te) == 32
+    assert [round(D.cifar_learning_rate(e), 6) for e in (0, 60, 61, 121, 161)] == [0.1, 0.1, 0.02, 0.004, 0.0008]
