@@ -18,6 +18,22 @@ class MnistNet(nn.Module):
         return self.fc2(F.relu(self.fc1(torch.flatten(x, 1))))
 
 
+class SimpleCNN(nn.Module):
+    """conv5(10) - pool - conv5(20) - pool - fc50 - fc for square images of any size and channel count: the
+    'simple_cnn' the reference's samples train on MNIST and CIFAR (deep500/networks/pytorch_mnist.py:18-36)."""
+
+    def __init__(self, in_channels: int = 1, size: int = 28, classes: int = 10):
+        super().__init__()
+        self.conv1, self.conv2 = nn.Conv2d(in_channels, 10, 5), nn.Conv2d(10, 20, 5)
+        self.side = (((size - 4) // 2) - 4) // 2                 # what two valid 5x5 convolutions and two poolings leave
+        self.fc1, self.fc2 = nn.Linear(self.side * self.side * 20, 50), nn.Linear(50, classes)
+
+    def forward(self, x):
+        x = F.relu(F.max_pool2d(self.conv1(x), 2))
+        x = F.relu(F.max_pool2d(self.conv2(x), 2))
+        return self.fc2(F.relu(self.fc1(torch.flatten(x, 1))))
+
+
 class DeepMnistNet(nn.Module):
     """conv5-pool-conv5-pool-fc1024-fc10 (the 'deep MNIST' tutorial network)."""
 

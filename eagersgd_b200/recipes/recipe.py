@@ -76,11 +76,7 @@ def run_recipe_dicts(fixed: Dict, mutable: Dict, metrics: List[Tuple]) -> bool:
     if isinstance(model, str) and os.path.isfile(model):
         module = GraphNetwork(load_onnx(model))
     elif isinstance(model, str):
-        kw = dict(comps["model_kwargs"])
-        if model == "resnet":
-            kw.setdefault("dataset", ds if isinstance(ds, str) and ds == "imagenet" else "cifar10")
-            kw.setdefault("num_classes", classes)
-        module = create_model(model, *comps["model_args"], **kw)
+        module = create_model(model, batch, *comps["model_args"], classes=classes, shape=sample_shape, **comps["model_kwargs"])
     else:
         module = model(batch, *comps["model_args"], classes=classes, shape=sample_shape, **comps["model_kwargs"])
     input_node, label_node = "x", "y"

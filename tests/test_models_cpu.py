@@ -13,6 +13,20 @@ def test_model_factory_shapes():
     assert create_model("resnet", dataset="imagenet", depth=18, num_classes=7)(torch.randn(1, 3, 64, 64)).shape == (1, 7)
 
 
+def test_model_factory_in_the_reference_call_form():
+    """create_model(name, batch_size, classes=, shape=) as deep500.networks.create_model is called."""
+    cnn = create_model("simple_cnn", 64, classes=7, shape=(3, 32, 32))
+    assert cnn(torch.randn(2, 3, 32, 32)).shape == (2, 7) and cnn.side == 5
+    assert create_model("simple_cnn")(torch.randn(2, 1, 28, 28)).shape == (2, 10)
+    assert create_model("deep_mnist", 8, classes=5)(torch.randn(2, 1, 28, 28)).shape == (2, 5)
+    small = create_model("resnet", 32, classes=10, shape=(3, 32, 32), depth=8)            # CIFAR-sized input: the 6n+2 family
+    assert small(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+    big = create_model("resnet", 32, classes=11, shape=(3, 224, 224), depth=18)
+    assert big(torch.randn(1, 3, 64, 64)).shape == (1, 11)
+    with pytest.raises(KeyError, match="unknown model"):
+        create_model("alexnet")
+
+
 def test_lstm_reference_matches_torch_lstm():
     torch.manual_seed(0)
     T, B, I, H = 6, 3, 5, 7
