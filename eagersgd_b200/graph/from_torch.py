@@ -251,16 +251,24 @@ def from_torch_module(module: nn.Module, name: Optional[str] = None, example_inp
     return _Builder(module, name or type(module).__name__, example_inputs).build()
 
 
-def export_network(name_or_module, file_path: str, example_inputs=None, **kwargs) -> str:
+def export_network(name_or_module, file_path=None, example_inputs=None, **kwargs) -> str:
     """Write a network as an ``.onnx`` file and return the path: ``name_or_module`` is a module or a name that
-    ``models.create_model`` knows ("simple_mnist", "deep_mnist", "wide_resnet", "resnet"); keyword arguments go to the
-    constructor."""
+    ``models.create_model`` knows ("simple_cnn", "simple_mnist", "deep_mnist", "wide_resnet", "resnet"); keyword
+    arguments go to the constructor.  In the reference's call form the second argument is a batch size and the file
+    goes to ``file_path=`` or, by default, ``<name>.onnx`` in the working directory
+    (``export_network(name, batch_size, classes=..., shape=...)``, deep500/networks/__init__.py:6-21)."""
     from .onnx_io import save_onnx
+    if file_path is None or isinstance(file_path, int):
+        file_path = kwargs.pop("file_path", None) or "%s.onnx" % (name_or_module if isinstance(name_or_module, str) else
+                                                                 type(name_or_module).__name__.lower())
     if isinstance(name_or_module, nn.Module):
         module = name_or_module
     else:
         from ..models import create_model
+        shape = kwargs.get("shape")
         module = create_model(name_or_module, **kwargs)
+        if example_inputs is None and shape is not None:
+            example_inputs = (torch.zeros(1, *shape),)
     module = module.eval()
     from ..models.resnet import ResNet
     if isinstance(module, ResNet):

@@ -33,7 +33,11 @@ def create_model(name: str, *args, **kw):
     return _FACTORIES[name](**kw)
 
 
-def export_network(name: str, file_path: str, **kw) -> str:
-    """Write a network of this zoo as an ``.onnx`` file and return the path (deep500/networks/__init__.py:6-21)."""
+def export_network(name: str, path_or_batch_size=None, *, file_path=None, **kw) -> str:
+    """Write a network of this zoo as an ``.onnx`` file and return the path: ``export_network(name, path, **model_kwargs)``,
+    or in the reference's call form ``export_network(name, batch_size, classes=, shape=, file_path=...)``, where the file
+    defaults to ``<name>.onnx`` in the working directory (deep500/networks/__init__.py:6-21)."""
     from ..graph.from_torch import export_network as _export
+    if isinstance(path_or_batch_size, str) and file_path is None:
+        file_path = path_or_batch_size
     return _export(name, file_path, **kw)

@@ -78,3 +78,20 @@ def test_imagenet_resnets_of_every_size(size, version, params, tmp_path):
     assert ckpt.import_tf_layout(m2, path) == 0               # the global step the file carries
     with torch.no_grad():
         assert torch.equal(m2(torch.ones(1, 3, 64, 64)), m(torch.ones(1, 3, 64, 64)))
+
+
+def test_export_network_in_the_reference_call_form(tmp_path, monkeypatch):
+    """onnx_file = export_network(name, BATCH_SIZE, classes=, shape=) and load it back, as the reference's distributed
+    sample does (deep500/samples/distributed_training.py:36-39)."""
+    from eagersgd_b200.graph import GraphNetwork, load_onnx
+    from eagersgd_b200.models import export_network
+    monkeypatch.chdir(tmp_path)
+    path = export_network("simple_cnn", 64, classes=10, shape=(1, 28, 28))
+    assert path == "simple_cnn.onnx" and (tmp_path / path).exists()
+    g = load_onnx(path)
+    assert len(g.inputs) == 1 and len(g.outputs) == 1
+    x = torch.randn(3, 1, 28, 28)
+    out = GraphNetwork(g).eval()(x)
+    out = out[0] if isinstance(out, (list, tuple)) else out
+    assert out.shape == (3, 10)
+    assert export_network("deep_mnist", 8, file_path=str(tmp_path / "d.onnx")) == str(tmp_path / "d.onnx")
