@@ -13,7 +13,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..train.metrics import L2Error, MaxError, TestMetric, WallclockTime
+from ..train.metrics import DatasetBias, L2Error, MaxError, TestMetric, WallclockTime
 
 
 def DefaultOpMetrics() -> List[TestMetric]:
@@ -181,8 +181,38 @@ def test_optimizer(optimizer, sampler, steps: int = 10, device: Optional[torch.d
     return {"median_step_ms": ms, "first_loss": losses[0], "last_loss": losses[-1]}
 
 
-def test_sampler(sampler, batches: int = 10) -> Dict[str, float]:
+def test_sampler(sampler, batches: int = 10, expected_output=None, metrics: Optional[List[TestMetric]] = None,
+                 events: Optional[Sequence] = None):
+    """Draw ``batches`` batches and report the median time per batch and how many distinct sample shapes came out.
+
+    With ``metrics`` (and optionally ``events``) it is the reference's harness: metrics that have sampler hooks
+    (``before_sampling`` / ``after_sampling`` — ``SamplerEventMetric``, ``DatasetBias``) are attached to the sampler
+    for the duration, every metric's ``begin`` / ``end`` brackets the draws (``reruns`` of them, at least ``batches``
+    when the metric has no ``reruns``), and the list of ``measure(sampler, last batch, expected_output)`` results is
+    returned (deep500/lv2/validation/sampler.py:6-66)."""
     import time
+    if metrics is not None:
+        attached = [m for m in metrics if hasattr(type(m), "before_sampling") or hasattr(type(m), "after_sampling")]
+        attached += [e for e in (events or []) if e not in attached]
+        sampler.events.extend(attached)
+        last = None
+        try:
+            for m in metrics:
+                m.begin(sampler)
+            for _ in range(max([int(getattr(m, "reruns", 0) or 0) for m in metrics] + [batches])):
+                last = sampler()
+                if last is None:
+                    sampler.reset()
+                    last = sampler()
+                for m in metrics:
+                    if isinstance(m, DatasetBias):               # the histogram of the labels that were drawn
+                        m.update(last[getattr(sampler.dataset, "label_node", "y")])
+            for m in metrics:
+                m.end(last)
+        finally:
+            if attached:
+                del sampler.events[-len(attached):]
+        return [m.measure(sampler, last, expected_output) for m in metrics]
     t = []
     shapes = set()
     for _ in range(batches):

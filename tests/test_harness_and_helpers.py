@@ -283,3 +283,19 @@ def test_process_wide_logger_and_per_device_batch(tmp_path):
     assert per_device_batch_size(256, 1) == 256 and per_device_batch_size(256, 8) == 32
     with pytest.raises(ValueError, match="try --batch_size=96"):
         per_device_batch_size(100, 8)
+
+
+def test_sampler_harness_with_metrics():
+    """d5.test_sampler(sampler, metrics=[...]) as the reference's dataset_latency and mnist_bias samples call it."""
+    from eagersgd_b200.data import NumpyDataset, ShuffleSampler
+    from eagersgd_b200.ops.validation import test_sampler
+    from eagersgd_b200.train import metrics as M
+    y = np.repeat(np.arange(4), [10, 20, 30, 4])
+    ds = NumpyDataset(np.zeros((64, 2), np.float32), "x", y, "y")
+    s = ShuffleSampler(ds, 16, seed=0)
+    latency, bias = M.SamplerEventMetric(), M.DatasetBias(4)
+    t, hist = test_sampler(s, batches=4, metrics=[latency, bias])
+    assert len(latency.times) == 4 and t == latency.measure() and t >= 0
+    assert hist.tolist() == [10, 20, 30, 4]                       # one epoch: the data set's own class counts
+    assert s.events == []                                          # the metrics were detached again
+    assert set(test_sampler(s, batches=3)) == {"median_batch_ms", "distinct_sample_shapes"}
