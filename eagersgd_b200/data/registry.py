@@ -17,9 +17,10 @@ import numpy as np
 from .dataset import Dataset, NumpyDataset, load_cifar10, load_cifar100, load_mnist, normalize_cifar
 
 # name -> (classes, channels, height, width)
-_SHAPES: Dict[str, Tuple[int, int, int, int]] = {
+_SHAPES: Dict[str, Tuple] = {
     "mnist": (10, 1, 28, 28), "fashion_mnist": (10, 1, 28, 28), "cifar10": (10, 3, 32, 32), "cifar100": (100, 3, 32, 32),
     "imagenet": (1000, 3, 224, 224),
+    "ucf101": (101, None, 3, 240, 320),            # clips of any number of frames (deep500/datasets/ucf101.py:18-19)
 }
 
 
@@ -62,6 +63,12 @@ def load_dataset(name: str, input_node: str = "x", label_node: str = "y", path: 
     normalised by the data set's channel statistics unless ``normalize=False``); without it, synthetic data of the right shape
     (``synthetic_samples`` training samples with Gaussian noise of standard deviation ``noise`` around the templates)."""
     classes, *shape = dataset_shape(name)
+    if name == "ucf101":
+        if path is None:
+            raise FileNotFoundError("ucf101 needs path= (frame folders and the trainlist / testlist split files)")
+        from .video import VideoFolderDataset
+        return (VideoFolderDataset(path, "trainlist01.txt", data_node=input_node, label_node=label_node),
+                VideoFolderDataset(path, "testlist01.txt", data_node=input_node, label_node=label_node))
     if path is None:
         return (synthetic_task(classes, tuple(shape), synthetic_samples, input_node, label_node, seed=seed + 1, noise=noise),
                 synthetic_task(classes, tuple(shape), max(synthetic_samples // 4, 32), input_node, label_node, seed=seed + 2,

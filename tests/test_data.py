@@ -416,3 +416,12 @@ def test_cifar100_files_the_registry_and_the_fast_schedule(tmp_path):
     syn_tr, syn_te = D.load_dataset("fashion_mnist", synthetic_samples=64)
     assert syn_tr[:]["x"].shape == (64, 1, 28, 28) and len(syn_te) == 32
     assert [round(D.cifar_learning_rate(e), 6) for e in (0, 60, 61, 121, 161)] == [0.1, 0.1, 0.02, 0.004, 0.0008]
+
+
+def test_ucf101_through_the_registry(tmp_path):
+    root = D.write_synthetic_ucf101(str(tmp_path / "ucf"), classes=2, clips_per_class=3)
+    assert D.dataset_shape("ucf101") == (101, None, 3, 240, 320)
+    train, test = D.load_dataset("ucf101", "frames", "label", path=root)
+    assert len(train) + len(test) == 6 and (train.data_node, train.label_node) == ("frames", "label")
+    with pytest.raises(FileNotFoundError, match="path="):
+        D.load_dataset("ucf101")
