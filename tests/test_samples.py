@@ -41,3 +41,18 @@ def test_peer_collectives_sample_runs_emulated_on_one_gpu():
                        capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "expected 6.0" in r.stdout and "[6.0, 6.0]" in r.stdout and "status words: [0, 0, 0, 0]" in r.stdout
+
+
+@pytest.mark.parametrize("scheme", ["solo", "pssgd", "mavg"])
+def test_distributed_training_sample_on_cpu_ranks(scheme):
+    """samples/distributed_training.py as two gloo ranks: an eager scheme, a parameter server and model averaging."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "samples", "distributed_training.py"), "--scheme", scheme,
+           "--steps", "12", "--dim", "64", "--sleep-ms", "2"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
