@@ -73,6 +73,9 @@ class Sampler:
 
     def reset(self):
         self.batch_idx = 0
+        for e in self.events:
+            if hasattr(e, "on_sampler_reset"):
+                e.on_sampler_reset(self)
         self.epoch += 1
 
 

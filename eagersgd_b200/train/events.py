@@ -31,6 +31,11 @@ class TrainingEvent:
     def after_epoch(self, epoch, runner, training_stats): ...
     def before_training_step(self, executor, optimizer, inputs): ...
     def after_training_step(self, executor, optimizer, outputs, loss): ...
+    def before_training_set(self, runner, training_stats, sampler): ...      # around the training pass of an epoch
+    def after_training_set(self, runner, training_stats): ...
+    def before_test_batch(self, runner, training_stats, batch): ...           # the reference's names for the test steps
+    def after_test_batch(self, runner, training_stats, outputs): ...
+    def on_sampler_reset(self, sampler): ...
     def before_test_set(self, runner, training_stats, sampler): ...
     def after_test_set(self, runner, training_stats, sampler): ...
     def before_test_step(self, executor, inputs): ...

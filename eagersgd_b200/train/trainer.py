@@ -14,6 +14,10 @@ import numpy as np
 from .events import EpochSummary, StopTraining, SummaryGeneratorEvent, TrainingStatistics
 
 
+def _nothing(*a, **k):
+    return None
+
+
 def DefaultTrainerEvents(epochs: int = 0, stream=None):
     """What a run shows when no events are named: the progress bar on the terminal (deep500/lv2/trainer.py:18-19)."""
     import sys
@@ -44,6 +48,7 @@ class Trainer:
                 break
             for e in events:
                 e.before_test_step(self.executor, batch)
+                getattr(e, "before_test_batch", _nothing)(self, stats, batch)
             out = self.executor.inference(batch)
             pred = out["output"].float().argmax(-1).cpu().numpy()
             labels = np.asarray(batch[self.executor.label_node])
@@ -55,6 +60,7 @@ class Trainer:
                 if hasattr(e, "record"):
                     e.record(pred, labels)
                 e.after_test_step(self.executor, out)
+                getattr(e, "after_test_batch", _nothing)(self, stats, out)
         summary.accuracy = correct / max(total, 1)
         summary.time = time.time() - t0
         stats.test_summaries.append(summary)
@@ -98,8 +104,10 @@ class Trainer:
             for epoch in range(epochs):
                 for e in events:
                     e.before_epoch(epoch, self, stats)
+                    getattr(e, "before_training_set", _nothing)(self, stats, self.train_set)
                 self._train_epoch(epoch, stats, events)
                 for e in events:
+                    getattr(e, "after_training_set", _nothing)(self, stats)
                     e.after_epoch(epoch, self, stats)
                 self._accuracy(self.test_set, stats, events, epoch)
         except StopTraining:

@@ -287,3 +287,26 @@ def test_statistics_tables():
     assert train_rows[1]["avg_loss"] == pytest.approx(stats.train_summaries[1].mean_loss)
     stats.clear()
     assert stats.to_dict() == ([], [])
+
+
+def test_every_hook_of_the_reference_event_interface_fires():
+    """before / after_training_set, before / after_test_batch and on_sampler_reset (deep500/lv2/event.py) beside the
+    epoch, step and test-set hooks."""
+    from eagersgd_b200.train import events as E
+    calls = []
+
+    class Recorder(E.TrainingEvent):
+        def before_training_set(self, runner, stats, sampler): calls.append("train_set+")
+        def after_training_set(self, runner, stats): calls.append("train_set-")
+        def before_test_batch(self, runner, stats, batch): calls.append("test_batch+")
+        def after_test_batch(self, runner, stats, outputs): calls.append("test_batch-")
+        def on_sampler_reset(self, sampler): calls.append("reset")
+        def before_epoch(self, epoch, runner, stats): calls.append("epoch+")
+        def after_epoch(self, epoch, runner, stats): calls.append("epoch-")
+
+    rec = Recorder()
+    tr, _ = _trainer(events=[rec])                 # the training sampler knows the event too
+    tr.run_loop(1, [rec])
+    assert calls.count("test_batch+") == calls.count("test_batch-") == 8                 # two test passes of four batches
+    i = calls.index("epoch+")
+    assert calls[i:i + 3] == ["epoch+", "train_set+", "reset"] and calls.index("train_set-") < calls.index("epoch-")
